@@ -1,0 +1,117 @@
+"""In-tree build of libAFIRRuntimeCAPI.so (CUDA kernels for sm_100a + the C++ host runtime).
+
+Explicit nvcc / g++ commands, objects cached under ascend_mlir_b200/build/, the shared library
+written to ascend_mlir_b200/lib/.  nvcc cross-compiles without a GPU.
+"""
+import hashlib
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+CSRC = PKG / "csrc"
+BUILD = PKG / "build"
+LIBDIR = PKG / "lib"
+LIB = LIBDIR / "libAFIRRuntimeCAPI.so"
+
+CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+NVCC = str(CUDA_HOME / "bin" / "nvcc")
+CXX = "g++"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", str(CSRC), "-I", str(ROOT / "include"),
+]
+# Bandwidth-bound kernels must round after every op: no mul+add contraction.
+NO_FMA = ["-fmad=false"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wextra", "-I", str(CSRC),
+             "-I", str(ROOT / "include"), "-I", str(CUDA_HOME / "include")]
+
+CU_SOURCES = {
+    "kernels/elementwise.cu": NO_FMA,
+    "kernels/row_reduce.cu": NO_FMA,
+    "kernels/gather.cu": NO_FMA,
+    "kernels/transpose.cu": [],
+    "kernels/matmul_tcgen05.cu": [],
+}
+CPP_SOURCES = ["common/json.cpp", "runtime/descriptor.cpp", "runtime/launcher.cpp", "runtime/executor.cpp",
+               "runtime/capi.cpp"]
+
+
+def _headers_digest() -> str:
+    h = hashlib.sha256()
+    for p in sorted(list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")) + list((ROOT / "include").rglob("*.h"))):
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def _stale(obj: Path, src: Path, stamp: str) -> bool:
+    tag = obj.with_suffix(obj.suffix + ".stamp")
+    want = hashlib.sha256(src.read_bytes()).hexdigest() + stamp
+    if obj.exists() and tag.exists() and tag.read_text() == want:
+        return False
+    return True
+
+
+def _mark(obj: Path, src: Path, stamp: str) -> None:
+    obj.with_suffix(obj.suffix + ".stamp").write_text(hashlib.sha256(src.read_bytes()).hexdigest() + stamp)
+
+
+def _run(cmd, verbose):
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("build step failed: " + " ".join(cmd))
+    return res.stdout + res.stderr
+
+
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
+    BUILD.mkdir(exist_ok=True)
+    LIBDIR.mkdir(exist_ok=True)
+    hdr = _headers_digest()
+    jobs, objs = [], []
+    for rel, extra in CU_SOURCES.items():
+        src = CSRC / rel
+        obj = BUILD / (rel.replace("/", "_") + ".o")
+        objs.append(obj)
+        stamp = hdr + "|".join(NVCC_FLAGS + extra)
+        if force or _stale(obj, src, stamp):
+            cmd = [NVCC] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", str(src), "-o", str(obj)]
+            jobs.append((cmd, obj, src, stamp))
+    for rel in CPP_SOURCES:
+        src = CSRC / rel
+        obj = BUILD / (rel.replace("/", "_") + ".o")
+        objs.append(obj)
+        stamp = hdr + "|".join(CXX_FLAGS)
+        if force or _stale(obj, src, stamp):
+            cmd = [CXX] + CXX_FLAGS + ["-c", str(src), "-o", str(obj)]
+            jobs.append((cmd, obj, src, stamp))
+
+    def work(job):
+        cmd, obj, src, stamp = job
+        out = _run(cmd, verbose)
+        _mark(obj, src, stamp)
+        return out
+
+    logs = []
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
+            logs = list(pool.map(work, jobs))
+    if jobs or not LIB.exists():
+        link = [CXX, "-shared", "-o", str(LIB)] + [str(o) for o in objs] + [
+            "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread",
+            "-Wl,--no-undefined", "-Wl,-z,defs"]
+        _run(link, verbose)
+    if ptxas_info:
+        print("".join(logs))
+    return LIB
+
+
+if __name__ == "__main__":
+    path = build(verbose="-v" in sys.argv, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    print(path)

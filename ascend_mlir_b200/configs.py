@@ -1,0 +1,176 @@
+"""The five benchmark fused groups: seeded synthetic inputs, launch descriptors, algorithmic work.
+
+Inputs are synthetic (numpy default_rng, seed 0) with the shapes, dtypes and value distributions the
+benchmark configuration names; no dataset is involved.  Every group shards on its independent leading
+axis: `shard(rank, world)` returns the slice of the work one GPU owns, with no data-path collective
+(the gather table, the matmul B operand and the bias vectors are replicated).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import numpy as np
+
+from . import descriptors
+from .descriptors import KernelSpec
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even f32 -> bf16 bit patterns (finite inputs)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+@dataclass
+class Workload:
+    name: str
+    spec: KernelSpec
+    shape: Dict[str, int]              # shape keys of the tiling space
+    inputs: List[np.ndarray]           # host tensors in kernel-argument order (bf16 as uint16 bits)
+    out_shape: Tuple[int, ...]
+    out_dtype: np.dtype                # uint16 for bf16
+    algorithmic_bytes: int = 0         # HBM bytes one pass must move
+    flops: int = 0
+    bound: str = "hbm"
+    units: int = 0                     # leading-axis units (rows) this workload holds
+    notes: str = ""
+    # (rank, world) -> Workload for that shard
+    sharder: Optional[Callable[[int, int], "Workload"]] = field(default=None, repr=False)
+
+    def tiling(self, **tile_params: int) -> bytes:
+        return self.spec.pack(self.shape, **tile_params)
+
+    def new_output(self) -> np.ndarray:
+        return np.zeros(self.out_shape, self.out_dtype)
+
+    def shard(self, rank: int, world: int) -> "Workload":
+        if world == 1:
+            return self
+        assert self.sharder is not None
+        return self.sharder(rank, world)
+
+
+def row_range(total: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous, balanced partition of `total` leading-axis units."""
+    base, rem = divmod(total, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+# ---- config 1: out = (a + b) * b, f32 [M, N] --------------------------------------------------------------
+def elementwise_chain(M: int = 4096, N: int = 4096, seed: int = 0) -> Workload:
+    rng = np.random.default_rng(seed)
+    a = rng.uniform(-1.0, 1.0, (M, N)).astype(np.float32)
+    b = rng.uniform(-1.0, 1.0, (M, N)).astype(np.float32)
+    spec = descriptors.add_mul("f32")
+
+    def make(a_, b_):
+        m = a_.shape[0]
+        w = Workload("elementwise_chain", spec, {"M": m, "N": N}, [a_, b_], (m, N), np.dtype(np.float32),
+                     algorithmic_bytes=3 * m * N * 4, units=m)
+        w.sharder = lambda r, k: make(*(np.ascontiguousarray(t[slice(*row_range(m, r, k))]) for t in (a_, b_)))
+        return w
+
+    return make(a, b)
+
+
+# ---- config 2: split-relu-broadcast-add-mul, f16 -------------------------------------------------------------
+def split_relu_broadcast_add_mul(B: int = 32, R: int = 1024, C: int = 1024, bias_axis: int = 1, seed: int = 0) -> Workload:
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((B, R, 2 * C), dtype=np.float32).astype(np.float16)
+    bias = (rng.standard_normal(R if bias_axis == 1 else C, dtype=np.float32) * np.float32(0.1)).astype(np.float16)
+    spec = descriptors.split_relu_bias_mul(bias_axis, "f16")
+
+    def make(x_):
+        b = x_.shape[0]
+        w = Workload("split_relu_broadcast_add_mul", spec,
+                     {"B": b, "R": R, "C2": 2 * C, "C": C, "BIAS": bias.shape[0]}, [x_, bias], (b, R, C),
+                     np.dtype(np.float16), algorithmic_bytes=b * R * 2 * C * 2 + bias.nbytes + b * R * C * 2, units=b,
+                     notes=f"bias indexed by axis {bias_axis}")
+        w.sharder = lambda r, k: make(np.ascontiguousarray(x_[slice(*row_range(b, r, k))]))
+        return w
+
+    return make(x)
+
+
+# ---- config 3: broadcast-add-reduce, f32 -----------------------------------------------------------------------
+def broadcast_add_reduce(M: int = 8192, N: int = 8192, seed: int = 0) -> Workload:
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(-1.0, 1.0, (M, N)).astype(np.float32)
+    b = rng.uniform(-1.0, 1.0, M).astype(np.float32)
+    spec = descriptors.bcast_add_rowsum("f32")
+
+    def make(b_, x_):
+        m = x_.shape[0]
+        w = Workload("broadcast_add_reduce", spec, {"M": m, "N": N}, [b_, x_], (m,), np.dtype(np.float32),
+                     algorithmic_bytes=m * N * 4 + m * 4 + m * 4, units=m)
+        w.sharder = lambda r, k: make(*(np.ascontiguousarray(t[slice(*row_range(m, r, k))]) for t in (b_, x_)))
+        return w
+
+    return make(b, x)
+
+
+# ---- config 4: gather-elementwise fusion, bf16 -------------------------------------------------------------------
+def gather_indices(rows: int, table_rows: int, dup_fraction: float, rng) -> np.ndarray:
+    """`rows` int32 indices into [0, table_rows): unique draws plus ~dup_fraction copies of earlier ones, shuffled."""
+    dups = int(round(rows * dup_fraction))
+    uniq = min(rows - dups, table_rows)
+    dups = rows - uniq
+    first = rng.choice(table_rows, size=uniq, replace=False)
+    extra = first[rng.integers(0, uniq, size=dups)] if dups else first[:0]
+    idx = np.concatenate([first, extra])
+    rng.shuffle(idx)
+    return idx.astype(np.int32)
+
+
+def gather_elementwise(table_rows: int = 1048576, width: int = 256, rows: int = 262144, seed: int = 0) -> Workload:
+    rng = np.random.default_rng(seed)
+    table = f32_to_bf16_bits(rng.standard_normal((table_rows, width), dtype=np.float32))
+    idx = gather_indices(rows, table_rows, 0.05, rng)
+    scale = f32_to_bf16_bits(rng.uniform(0.5, 1.5, width).astype(np.float32))
+    resid = f32_to_bf16_bits(rng.standard_normal((rows, width), dtype=np.float32))
+    spec = descriptors.gather_rows_scale_resid("bf16", "i32")
+
+    def make(idx_, resid_):
+        r = idx_.shape[0]
+        w = Workload("gather_elementwise", spec, {"T": table_rows, "W": width, "R": r}, [table, idx_, scale, resid_],
+                     (r, width), np.dtype(np.uint16),
+                     algorithmic_bytes=r * 4 + r * width * 2 + width * 2 + r * width * 2 + r * width * 2, units=r,
+                     notes="table replicated per GPU; each gathered row counted once")
+        w.sharder = lambda rk, k: make(*(np.ascontiguousarray(t[slice(*row_range(r, rk, k))]) for t in (idx_, resid_)))
+        return w
+
+    return make(idx, resid)
+
+
+# ---- config 5: matmul-add-leakyrelu, bf16 ---------------------------------------------------------------------------
+def matmul_add_leakyrelu(M: int = 8192, N: int = 8192, K: int = 8192, alpha: float = 0.01, seed: int = 0) -> Workload:
+    rng = np.random.default_rng(seed)
+    A = f32_to_bf16_bits(rng.standard_normal((M, K), dtype=np.float32) * np.float32(0.02))
+    Bm = f32_to_bf16_bits(rng.standard_normal((K, N), dtype=np.float32) * np.float32(0.02))
+    bias = f32_to_bf16_bits(rng.standard_normal(N, dtype=np.float32) * np.float32(0.1))
+    spec = descriptors.matmul_bias_leakyrelu("bf16", "bf16", "bf16", alpha)
+
+    def make(A_):
+        m = A_.shape[0]
+        w = Workload("matmul_add_leakyrelu", spec, {"M": m, "N": N, "K": K}, [A_, Bm, bias], (m, N), np.dtype(np.uint16),
+                     algorithmic_bytes=(m * K + K * N + m * N) * 2 + N * 2, flops=2 * m * N * K, bound="tensor", units=m,
+                     notes="B and bias replicated per GPU")
+        w.sharder = lambda r, k: make(np.ascontiguousarray(A_[slice(*row_range(m, r, k))]))
+        return w
+
+    return make(A)
+
+
+CONFIGS: Dict[str, Callable[..., Workload]] = {
+    "elementwise_chain": elementwise_chain,
+    "split_relu_broadcast_add_mul": split_relu_broadcast_add_mul,
+    "broadcast_add_reduce": broadcast_add_reduce,
+    "gather_elementwise": gather_elementwise,
+    "matmul_add_leakyrelu": matmul_add_leakyrelu,
+}

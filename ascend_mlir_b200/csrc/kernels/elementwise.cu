@@ -1,0 +1,268 @@
+// Elementwise / broadcast / split / concat fused groups (the all-parallel linalg.generic class the
+// reference lowers in lib/Conversion/LinalgToAscendC/ComputeConversion.cpp:750-1624, with split and
+// concat folded into view offsets as lib/Conversion/Passes.td:72-102 does for concat).
+//
+// HBM-bound: every thread keeps UNROLL independent 16-byte loads per view in flight, inputs read
+// once are loaded with the streaming (evict-first) policy, broadcast operands through the read-only
+// path.  No shared memory: there is no reuse to stage.  Arithmetic rounds after every op.
+#include "kernels/ew_common.cuh"
+
+#include <algorithm>
+#include <mutex>
+
+namespace afir {
+namespace kernels {
+namespace {
+
+struct EwParams {
+  const char *vbase[kMaxViews];
+  long long vs0[kMaxViews], vs1[kMaxViews], vs2[kMaxViews];
+  char *obase;
+  long long os0, os1;
+  unsigned int vecPerRow;  // vectors (or elements, scalar variant) along the inner dim
+  unsigned int d1;
+  unsigned int totalVec;
+  unsigned int numTiles;
+  FastDiv divVpr, divD1;
+  int flat;  // inner dim is the whole domain: skip the row arithmetic
+  int numViews;
+  BodyProgram prog;
+};
+
+template <class P> __device__ __forceinline__ void storeScalar(void *p, P v);
+template <> __device__ __forceinline__ void storeScalar<PackF32>(void *p, PackF32 v) {
+  *reinterpret_cast<float *>(p) = v.x;
+}
+template <> __device__ __forceinline__ void storeScalar<PackF16>(void *p, PackF16 v) {
+  *reinterpret_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
+}
+template <> __device__ __forceinline__ void storeScalar<PackBF16>(void *p, PackBF16 v) {
+  *reinterpret_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
+}
+
+template <class P, int BODY, int UNROLL, bool VECTOR>
+__global__ void __launch_bounds__(512) elementwiseKernel(const __grid_constant__ EwParams prm) {
+  using B = Body<BODY>;
+  constexpr int NV = B::kViews;
+  constexpr int kElems = VECTOR ? Vec16<P>::kElems : 1;
+  constexpr int kElemBytes = sizeof(typename P::Scalar);
+  const unsigned int tileVecs = blockDim.x * UNROLL;
+
+  for (unsigned int tile = blockIdx.x; tile < prm.numTiles; tile += gridDim.x) {
+    const unsigned int g0 = tile * tileVecs + threadIdx.x;
+    uint4 raw[UNROLL][NV];
+    long long ooff[UNROLL];
+    bool live[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const unsigned int g = g0 + u * blockDim.x;
+      live[u] = g < prm.totalVec;
+      unsigned int col = g, i0 = 0, i1 = 0;
+      if (!prm.flat) {
+        const unsigned int row = fastDivide(g, prm.divVpr);
+        col = g - row * prm.vecPerRow;
+        i0 = fastDivide(row, prm.divD1);
+        i1 = row - i0 * prm.d1;
+      }
+      ooff[u] = (static_cast<long long>(i0) * prm.os0 + static_cast<long long>(i1) * prm.os1 +
+                 static_cast<long long>(col) * kElems) * kElemBytes;
+      if (live[u]) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          if (k < prm.numViews) {
+            const long long e = static_cast<long long>(i0) * prm.vs0[k] + static_cast<long long>(i1) * prm.vs1[k] +
+                                static_cast<long long>(col) * kElems * prm.vs2[k];
+            const char *src = prm.vbase[k] + e * kElemBytes;
+            if (VECTOR && prm.vs2[k] == 1) {
+              raw[u][k] = loadStream16(src);
+            } else {
+              const unsigned int s = P::splat(src).bits();
+              raw[u][k] = make_uint4(s, s, s, s);
+            }
+          } else {
+            raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      if (!live[u]) continue;
+      if (VECTOR) {
+        Vec16<P> in[NV];
+#pragma unroll
+        for (int k = 0; k < NV; ++k) in[k] = Vec16<P>::fromRaw(raw[u][k]);
+        Vec16<P> out;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          P v[NV];
+#pragma unroll
+          for (int k = 0; k < NV; ++k) v[k] = in[k].p[q];
+          out.p[q] = B::template eval<P>(v, prm.prog);
+        }
+        storeStream16(prm.obase + ooff[u], out.raw());
+      } else {
+        P v[NV];
+#pragma unroll
+        for (int k = 0; k < NV; ++k) v[k] = P::fromBits(raw[u][k].x);
+        storeScalar<P>(prm.obase + ooff[u], B::template eval<P>(v, prm.prog));
+      }
+    }
+  }
+}
+
+using KernelFn = void (*)(const EwParams);
+
+template <class P, int BODY> KernelFn pickUnroll(int unroll) {
+  switch (unroll) {
+  case 1: return elementwiseKernel<P, BODY, 1, true>;
+  case 2: return elementwiseKernel<P, BODY, 2, true>;
+  default: return elementwiseKernel<P, BODY, 4, true>;
+  }
+}
+
+template <class P> KernelFn pickVector(int body, int unroll) {
+  switch (body) {
+  case kBodyCopy: return pickUnroll<P, kBodyCopy>(unroll);
+  case kBodyAdd: return pickUnroll<P, kBodyAdd>(unroll);
+  case kBodyMul: return pickUnroll<P, kBodyMul>(unroll);
+  case kBodyAddMulRhs: return pickUnroll<P, kBodyAddMulRhs>(unroll);
+  case kBodyAddMul: return pickUnroll<P, kBodyAddMul>(unroll);
+  case kBodyMulAdd: return pickUnroll<P, kBodyMulAdd>(unroll);
+  case kBodyReluAdd: return pickUnroll<P, kBodyReluAdd>(unroll);
+  case kBodyReluAddMul: return pickUnroll<P, kBodyReluAddMul>(unroll);
+  case kBodyRelu: return pickUnroll<P, kBodyRelu>(unroll);
+  default: return elementwiseKernel<P, kBodyInterpreted, 2, true>;
+  }
+}
+
+template <class P> KernelFn pickScalar() { return elementwiseKernel<P, kBodyInterpreted, 2, false>; }
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+} // namespace
+
+// ---- body matching (host) ------------------------------------------------------------------------
+namespace {
+bool srcIs(const BodySrc &s, int kind, int index) { return s.kind == kind && s.index == index; }
+bool srcIsZero(const BodySrc &s) { return s.kind == kSrcConst && s.value == 0.0f; }
+// op(a,b) with commutative matching for add/mul/max/min
+bool opIs(const BodyOp &o, int code, int ak, int ai, int bk, int bi) {
+  if (o.op != code) return false;
+  if (srcIs(o.a, ak, ai) && srcIs(o.b, bk, bi)) return true;
+  bool commutative = code == kOpAdd || code == kOpMul || code == kOpMax || code == kOpMin;
+  return commutative && srcIs(o.a, bk, bi) && srcIs(o.b, ak, ai);
+}
+bool isRelu(const BodyOp &o, int view) {
+  return o.op == kOpMax && ((srcIs(o.a, kSrcView, view) && srcIsZero(o.b)) || (srcIs(o.b, kSrcView, view) && srcIsZero(o.a)));
+}
+} // namespace
+
+int matchBody(const BodyProgram &p, int numViews) {
+  const BodyOp *o = p.ops;
+  if (p.numOps == 0 && numViews >= 1) return kBodyCopy;
+  if (p.numOps == 1) {
+    if (opIs(o[0], kOpAdd, kSrcView, 0, kSrcView, 1)) return kBodyAdd;
+    if (opIs(o[0], kOpMul, kSrcView, 0, kSrcView, 1)) return kBodyMul;
+    if (isRelu(o[0], 0)) return kBodyRelu;
+  }
+  if (p.numOps == 2) {
+    if (opIs(o[0], kOpAdd, kSrcView, 0, kSrcView, 1) && opIs(o[1], kOpMul, kSrcOp, 0, kSrcView, 1)) return kBodyAddMulRhs;
+    if (opIs(o[0], kOpAdd, kSrcView, 0, kSrcView, 1) && opIs(o[1], kOpMul, kSrcOp, 0, kSrcView, 2)) return kBodyAddMul;
+    if (opIs(o[0], kOpMul, kSrcView, 0, kSrcView, 1) && opIs(o[1], kOpAdd, kSrcOp, 0, kSrcView, 2)) return kBodyMulAdd;
+    if (isRelu(o[0], 0) && opIs(o[1], kOpAdd, kSrcOp, 0, kSrcView, 1)) return kBodyReluAdd;
+  }
+  if (p.numOps == 3) {
+    if (isRelu(o[0], 0) && opIs(o[1], kOpAdd, kSrcOp, 0, kSrcView, 1) && opIs(o[2], kOpMul, kSrcOp, 1, kSrcView, 2))
+      return kBodyReluAddMul;
+  }
+  return kBodyInterpreted;
+}
+
+int deviceSmCount(int device) {
+  static std::mutex mu;
+  static int cached[64];
+  std::lock_guard<std::mutex> lock(mu);
+  if (device < 0 || device >= 64) return 148;
+  if (cached[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+    cached[device] = n;
+  }
+  return cached[device];
+}
+
+const char *cudaErrorText(int code) { return cudaGetErrorString(static_cast<cudaError_t>(code)); }
+
+int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *launched) {
+  if (launched) *launched = 0;
+  const int64_t total = l.dims[0] * l.dims[1] * l.dims[2];
+  if (total == 0) return cudaSuccess;
+  if (l.numViews < 1 || l.numViews > kMaxViews || l.outStride[2] != 1) return cudaErrorInvalidValue;
+
+  const int eb = elemBytes(l.elemType);
+  const int vecElems = 16 / eb;
+  // The 16-byte path needs every contiguous view (and the output) to start on a 16-byte boundary
+  // with all outer strides and the inner extent multiples of the vector; inner strides 0 or 1.
+  bool vector = l.dims[2] % vecElems == 0 && aligned16(l.outBase) && l.outStride[0] % vecElems == 0 &&
+                l.outStride[1] % vecElems == 0;
+  for (int k = 0; k < l.numViews && vector; ++k) {
+    const ViewAccess &v = l.views[k];
+    if (v.stride[2] == 1)
+      vector = aligned16(v.base) && v.stride[0] % vecElems == 0 && v.stride[1] % vecElems == 0;
+    else if (v.stride[2] != 0)
+      vector = false;
+  }
+  const int perVec = vector ? vecElems : 1;
+  const int64_t vecPerRow = l.dims[2] / perVec;
+  const int64_t totalVec = l.dims[0] * l.dims[1] * vecPerRow;
+  if (totalVec >= (1ll << 32) - (1 << 20) || l.dims[1] >= (1ll << 31) || vecPerRow >= (1ll << 31))
+    return cudaErrorInvalidValue;
+
+  EwParams p = {};
+  for (int k = 0; k < l.numViews; ++k) {
+    p.vbase[k] = static_cast<const char *>(l.views[k].base);
+    p.vs0[k] = l.views[k].stride[0];
+    p.vs1[k] = l.views[k].stride[1];
+    p.vs2[k] = l.views[k].stride[2];
+  }
+  p.obase = static_cast<char *>(l.outBase);
+  p.os0 = l.outStride[0];
+  p.os1 = l.outStride[1];
+  p.vecPerRow = static_cast<unsigned int>(vecPerRow);
+  p.d1 = static_cast<unsigned int>(l.dims[1]);
+  p.totalVec = static_cast<unsigned int>(totalVec);
+  p.divVpr = makeFastDiv(p.vecPerRow);
+  p.divD1 = makeFastDiv(p.d1);
+  p.flat = (l.dims[0] == 1 && l.dims[1] == 1) ? 1 : 0;
+  p.numViews = l.numViews;
+  p.prog = l.body;
+
+  int threads = l.ctaThreads > 0 ? l.ctaThreads : 256;
+  threads = std::max(32, std::min(512, (threads / 32) * 32));
+  int unroll = l.unroll > 0 ? l.unroll : 4;
+  unroll = unroll >= 4 ? 4 : (unroll >= 2 ? 2 : 1);
+  const int body = vector ? matchBody(l.body, l.numViews) : kBodyInterpreted;
+  if (!vector || body == kBodyInterpreted) unroll = 2;
+
+  KernelFn fn = nullptr;
+  if (vector) {
+    fn = l.elemType == kF32 ? pickVector<PackF32>(body, unroll)
+         : l.elemType == kF16 ? pickVector<PackF16>(body, unroll)
+                              : pickVector<PackBF16>(body, unroll);
+  } else {
+    fn = l.elemType == kF32 ? pickScalar<PackF32>() : l.elemType == kF16 ? pickScalar<PackF16>() : pickScalar<PackBF16>();
+  }
+
+  const int64_t tileVecs = static_cast<int64_t>(threads) * unroll;
+  const int64_t numTiles = (totalVec + tileVecs - 1) / tileVecs;
+  p.numTiles = static_cast<unsigned int>(numTiles);
+  int64_t grid = l.gridBlocks > 0 ? l.gridBlocks : numTiles;
+  grid = std::max<int64_t>(1, std::min<int64_t>(grid, numTiles));
+  fn<<<static_cast<unsigned int>(grid), threads, 0, stream>>>(p);
+  if (launched) *launched = 1;
+  return cudaGetLastError();
+}
+
+} // namespace kernels
+} // namespace afir

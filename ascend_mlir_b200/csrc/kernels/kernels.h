@@ -1,0 +1,177 @@
+// Host-visible launch interface of the sm_100a fused-group kernel library.
+// Plain structs and pointers only: the runtime (.cpp, compiled by g++) fills these in from a
+// launch descriptor plus TilingData values, the .cu files turn them into kernel launches.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+typedef struct CUstream_st *cudaStream_t;
+
+namespace afir {
+namespace kernels {
+
+enum ElemType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
+enum IndexType : int { kI32 = 0, kI64 = 1 };
+
+inline int elemBytes(int t) { return t == kF32 ? 4 : 2; }
+
+// ---------------------------------------------------------------------------------------------
+// Fused elementwise bodies.  A body is a short chain of arith ops over the values loaded from
+// the group's views; every op rounds to the element type (no FMA contraction).
+// ---------------------------------------------------------------------------------------------
+enum BodyOpCode : int { kOpAdd = 0, kOpSub = 1, kOpMul = 2, kOpDiv = 3, kOpMax = 4, kOpMin = 5 };
+enum BodySrcKind : int { kSrcView = 0, kSrcOp = 1, kSrcConst = 2 };
+
+constexpr int kMaxViews = 6;   // loaded views per group (the gathered value counts as one)
+constexpr int kMaxBodyOps = 8;
+
+struct BodySrc {
+  int kind;     // BodySrcKind
+  int index;    // view index or op index
+  float value;  // constant (already representable in the element type)
+};
+struct BodyOp {
+  int op;  // BodyOpCode
+  BodySrc a, b;
+};
+struct BodyProgram {
+  int numOps;  // 0 = identity of view 0
+  BodyOp ops[kMaxBodyOps];
+};
+
+// Ids of the bodies compiled as straight-line specialisations (everything else runs through
+// the op-by-op interpreter kernel, same results, lower throughput).
+enum BodyId : int {
+  kBodyInterpreted = -1,
+  kBodyCopy = 0,          // v0
+  kBodyAdd,               // v0 + v1
+  kBodyMul,               // v0 * v1
+  kBodyAddMulRhs,         // (v0 + v1) * v1
+  kBodyAddMul,            // (v0 + v1) * v2
+  kBodyMulAdd,            // v0 * v1 + v2
+  kBodyReluAdd,           // max(v0, 0) + v1
+  kBodyReluAddMul,        // (max(v0, 0) + v1) * v2
+  kBodyRelu,              // max(v0, 0)
+  kNumBodies
+};
+
+// Returns the specialised body id computing `prog`, or kBodyInterpreted.
+int matchBody(const BodyProgram &prog, int numViews);
+
+// ---------------------------------------------------------------------------------------------
+// Elementwise / broadcast / split / concat groups.
+// Iteration domain collapsed to dims[0..2] (dims[2] innermost).  Each view is a device pointer
+// (slice offsets already applied) with an element stride per domain dim; stride[2] is 1
+// (contiguous, vector access) or 0 (broadcast along the inner dim, scalar access).
+// ---------------------------------------------------------------------------------------------
+struct ViewAccess {
+  const void *base;
+  int64_t stride[3];
+};
+
+struct ElementwiseLaunch {
+  int elemType;
+  int64_t dims[3];
+  int numViews;
+  ViewAccess views[kMaxViews];
+  void *outBase;
+  int64_t outStride[3];  // outStride[2] must be 1
+  BodyProgram body;
+  int ctaThreads;  // 0 = library default
+  int unroll;      // vectors in flight per thread: 1, 2, 4 or 8; 0 = default
+  int gridBlocks;  // 0 = library default
+};
+// Returns a cudaError_t value (0 = success); *launched gets the number of kernels launched.
+int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *launched);
+
+// ---------------------------------------------------------------------------------------------
+// Row reduction: out[m] = sum_n body(views)(m, n), f32 accumulation from zero.
+// dims = {rows, cols}; view strides are per (row, col) with the col stride 1 or 0.
+// ---------------------------------------------------------------------------------------------
+struct RowReduceLaunch {
+  int elemType;
+  int64_t rows, cols;
+  int numViews;
+  struct View2 { const void *base; int64_t rowStride; int64_t colStride; } views[kMaxViews];
+  void *out;  // [rows], elemType
+  BodyProgram body;
+  int ctaThreads;   // 0 = default
+  int splitCols;    // column slices per row (>1 uses `workspace` for the partial sums); 0 = choose
+  void *workspace;  // device scratch, at least rowReduceWorkspaceBytes(...) when splitCols > 1
+  size_t workspaceBytes;
+  int gridBlocks;
+};
+size_t rowReduceWorkspaceBytes(int64_t rows, int splitCols);
+int chooseRowReduceSplit(int64_t rows, int64_t cols, int smCount);
+int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched);
+
+// ---------------------------------------------------------------------------------------------
+// Gather + elementwise.  axis 0 (row gather, "embedding"): g(i,j) = table[idx[i], j];
+// axis 1 (column gather, "index_select"): g(i,j) = table[i, idx[j]].  The gathered value is view 0
+// of the body; views[1..] are ordinary (row, col) views.  Out-of-range indices leave the output
+// element(s) untouched and raise *status (a device int64 counter) by one per bad index read.
+// ---------------------------------------------------------------------------------------------
+struct GatherLaunch {
+  int elemType;
+  int axis;
+  int indexType;
+  int64_t rows, cols;        // output shape
+  const void *table;
+  int64_t tableRows, tableCols, tableRowStride;
+  const void *indices;
+  int numViews;              // including the gathered value as view 0 (its ViewAccess is ignored)
+  RowReduceLaunch::View2 views[kMaxViews];
+  void *out;
+  int64_t outRowStride;
+  BodyProgram body;
+  unsigned long long *status;  // device counter of out-of-range indices (may be null)
+  int ctaThreads, unroll, gridBlocks;
+};
+int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched);
+
+// ---------------------------------------------------------------------------------------------
+// 2-D transpose out[c, r] = in[r, c] through a padded shared-memory tile (2- or 4-byte elements).
+// ---------------------------------------------------------------------------------------------
+struct TransposeLaunch {
+  int elemBytes;
+  int64_t rows, cols;  // shape of `in`
+  const void *in;
+  int64_t inRowStride;
+  void *out;
+  int64_t outRowStride;
+};
+int launchTranspose(const TransposeLaunch &l, cudaStream_t stream, int *launched);
+
+// ---------------------------------------------------------------------------------------------
+// Matmul + bias + LeakyReLU:  out = epilogue(A[M,K] . B[K,N] + bias[N]); row-major, 16-bit inputs,
+// f32 accumulation in tensor memory (tcgen05), operands staged by TMA.
+// ---------------------------------------------------------------------------------------------
+enum EpilogueKind : int { kEpiNone = 0, kEpiBiasAdd = 1, kEpiBiasAddLeakyRelu = 2, kEpiBiasAddRelu = 3 };
+
+struct MatmulLaunch {
+  int inType;    // kF16 or kBF16 (A and B)
+  int outType;   // kF32, kF16 or kBF16
+  int biasType;  // kF32, kF16 or kBF16
+  int64_t M, N, K;
+  const void *A;  // [M,K] row-major
+  const void *B;  // [K,N] row-major
+  const void *bias;  // [N] or null
+  void *out;      // [M,N] row-major
+  int epilogue;
+  float alpha;
+  int gridBlocks;  // 0 = one persistent CTA per SM
+  int stages;      // 0 = default
+};
+// errorText (optional, >= 256 bytes) receives a description when the launch is refused or the
+// kernel reports a bounded-wait timeout.
+int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char *errorText);
+// After the stream has been synchronised: non-zero when a kernel wait gave up (see matmul_tcgen05.cu).
+int matmulCheckStatus(int device, char *errorText);
+
+// Library-wide helpers.
+int deviceSmCount(int device);
+const char *cudaErrorText(int code);
+
+} // namespace kernels
+} // namespace afir

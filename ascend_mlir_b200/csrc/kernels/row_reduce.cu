@@ -1,0 +1,255 @@
+// Broadcast + elementwise + row reduction groups: out[m] = sum_n body(views)(m, n)
+// (the [parallel, reduction] linalg.generic class, lib/Conversion/LinalgToAscendC/ComputeConversion.cpp:244-748;
+// zero-initialised accumulator per :508-521; 16-bit inputs are summed as f32 and cast back,
+// lib/Target/CannKernel/CannTranslation.cpp:2446-2461).
+//
+// HBM-bound streaming read.  L threads cooperate on one row (L = 32..CTA size), each keeping four
+// 16-byte loads per view in flight; warp-shuffle tree, then a shared-memory tree across warps, f32
+// accumulators throughout.  Short-and-wide problems split each row into column slices whose partial
+// sums go to the workspace and are added in slice order by a second kernel (deterministic).
+#include "kernels/ew_common.cuh"
+
+#include <algorithm>
+
+namespace afir {
+namespace kernels {
+namespace {
+
+struct RrParams {
+  const char *vbase[kMaxViews];
+  long long rowStride[kMaxViews];
+  int colStride[kMaxViews];
+  int numViews;
+  long long rows;
+  unsigned int vecPerRow;    // vectors (or elements) per full row
+  unsigned int vecPerSlice;  // vectors per column slice
+  int slices;
+  int lanesPerRow;           // power of two, 32..blockDim.x
+  float *partial;            // [rows, slices] when slices > 1
+  void *out;
+  BodyProgram prog;
+};
+
+template <class P> __device__ __forceinline__ void storeSum(void *out, long long row, float v);
+template <> __device__ __forceinline__ void storeSum<PackF32>(void *out, long long row, float v) {
+  static_cast<float *>(out)[row] = v;
+}
+template <> __device__ __forceinline__ void storeSum<PackF16>(void *out, long long row, float v) {
+  static_cast<__half *>(out)[row] = __float2half_rn(v);
+}
+template <> __device__ __forceinline__ void storeSum<PackBF16>(void *out, long long row, float v) {
+  static_cast<__nv_bfloat16 *>(out)[row] = __float2bfloat16_rn(v);
+}
+
+template <class P, int BODY, bool VECTOR>
+__global__ void __launch_bounds__(512) rowReduceKernel(const __grid_constant__ RrParams prm) {
+  using B = Body<BODY>;
+  constexpr int NV = B::kViews;
+  constexpr int kElems = VECTOR ? Vec16<P>::kElems : 1;
+  constexpr int kElemBytes = sizeof(typename P::Scalar);
+  constexpr int kBatch = 4;
+  __shared__ float warpSums[16];
+
+  const int L = prm.lanesPerRow;
+  const int rowsPerCta = blockDim.x / L;
+  const int sub = threadIdx.x / L;   // which row of this CTA
+  const int lane = threadIdx.x % L;  // position within the row team
+  const long long rowGroups = (prm.rows + rowsPerCta - 1) / rowsPerCta;
+  const long long work = rowGroups * prm.slices;
+
+  for (long long w = blockIdx.x; w < work; w += gridDim.x) {
+    const long long row = (w / prm.slices) * rowsPerCta + sub;
+    const int slice = static_cast<int>(w % prm.slices);
+    const bool rowLive = row < prm.rows;
+    const unsigned int vBegin = static_cast<unsigned int>(slice) * prm.vecPerSlice;
+    const unsigned int vEnd = min(vBegin + prm.vecPerSlice, prm.vecPerRow);
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (rowLive) {
+      const char *rowBase[NV];
+      uint4 bcast[NV];
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        rowBase[k] = nullptr;
+        bcast[k] = make_uint4(0u, 0u, 0u, 0u);
+        if (k < prm.numViews) {
+          rowBase[k] = prm.vbase[k] + row * prm.rowStride[k] * kElemBytes;
+          if (prm.colStride[k] == 0) {
+            const unsigned int s = P::splat(rowBase[k]).bits();
+            bcast[k] = make_uint4(s, s, s, s);
+          }
+        }
+      }
+      for (unsigned int v0 = vBegin + lane; v0 < vEnd; v0 += kBatch * L) {
+        uint4 raw[kBatch][NV];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const unsigned int v = v0 + u * L;
+#pragma unroll
+          for (int k = 0; k < NV; ++k) {
+            raw[u][k] = bcast[k];
+            if (k < prm.numViews && prm.colStride[k] != 0 && v < vEnd) {
+              const char *src = rowBase[k] + static_cast<long long>(v) * kElems * prm.colStride[k] * kElemBytes;
+              if (VECTOR) raw[u][k] = loadStream16(src);
+              else {
+                const unsigned int s = P::splat(src).bits();
+                raw[u][k] = make_uint4(s, s, s, s);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          if (v0 + u * L < vEnd) {
+#pragma unroll
+            for (int q = 0; q < (VECTOR ? 4 : 1); ++q) {
+              P vals[NV];
+#pragma unroll
+              for (int k = 0; k < NV; ++k) {
+                const unsigned int bits = q == 0 ? raw[u][k].x : q == 1 ? raw[u][k].y : q == 2 ? raw[u][k].z : raw[u][k].w;
+                vals[k] = P::fromBits(bits);
+              }
+              const P y = B::template eval<P>(vals, prm.prog);
+              acc[q] += y.lane(0);
+              if (VECTOR && P::kLanes == 2) acc[q] += y.lane(1);
+            }
+          }
+        }
+      }
+    }
+    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    // team reduction: shuffle tree inside each warp, then a shared-memory tree across the team's warps
+    const int width = L < 32 ? L : 32;
+    for (int off = width / 2; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off, width);
+    if (L > 32) {
+      const int warp = threadIdx.x >> 5;
+      const int warpsPerTeam = L >> 5;
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) warpSums[warp] = sum;
+      __syncthreads();
+      if (lane == 0) {
+        float t = 0.f;
+        for (int i = 0; i < warpsPerTeam; ++i) t += warpSums[sub * warpsPerTeam + i];
+        sum = t;
+      }
+    }
+    if (lane == 0 && rowLive) {
+      if (prm.slices > 1) prm.partial[row * prm.slices + slice] = sum;
+      else storeSum<P>(prm.out, row, sum);
+    }
+  }
+}
+
+template <class P>
+__global__ void rowReduceFinalizeKernel(const float *__restrict__ partial, void *out, long long rows, int slices) {
+  const long long row = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  float t = 0.f;
+  for (int s = 0; s < slices; ++s) t += partial[row * slices + s];
+  storeSum<P>(out, row, t);
+}
+
+using KernelFn = void (*)(const RrParams);
+
+template <class P, bool VECTOR> KernelFn pickBody(int body) {
+  switch (body) {
+  case kBodyCopy: return rowReduceKernel<P, kBodyCopy, VECTOR>;
+  case kBodyAdd: return rowReduceKernel<P, kBodyAdd, VECTOR>;
+  case kBodyMul: return rowReduceKernel<P, kBodyMul, VECTOR>;
+  default: return rowReduceKernel<P, kBodyInterpreted, VECTOR>;
+  }
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+} // namespace
+
+size_t rowReduceWorkspaceBytes(int64_t rows, int splitCols) {
+  return splitCols > 1 ? static_cast<size_t>(rows) * static_cast<size_t>(splitCols) * sizeof(float) : 0;
+}
+
+// Rows alone fill the machine when there are at least two CTAs' worth per SM; otherwise slice the
+// columns until there are, keeping each slice at least 4096 elements long.
+int chooseRowReduceSplit(int64_t rows, int64_t cols, int smCount) {
+  if (rows <= 0 || cols <= 0) return 1;
+  const int64_t want = 2ll * smCount;
+  if (rows >= want) return 1;
+  int64_t s = (want + rows - 1) / rows;
+  const int64_t maxByLength = std::max<int64_t>(1, cols / 4096);
+  s = std::min<int64_t>(s, maxByLength);
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(s, 1024)));
+}
+
+int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched) {
+  if (launched) *launched = 0;
+  if (l.rows == 0) return cudaSuccess;
+  if (l.numViews < 1 || l.numViews > kMaxViews) return cudaErrorInvalidValue;
+  const int eb = elemBytes(l.elemType);
+  const int vecElems = 16 / eb;
+
+  bool vector = l.cols % vecElems == 0;
+  for (int k = 0; k < l.numViews && vector; ++k) {
+    const auto &v = l.views[k];
+    if (v.colStride == 1) vector = aligned16(v.base) && v.rowStride % vecElems == 0;
+    else if (v.colStride != 0) vector = false;
+  }
+  const int perVec = vector ? vecElems : 1;
+  const int64_t vecPerRow = l.cols / perVec;
+  if (vecPerRow >= (1ll << 31)) return cudaErrorInvalidValue;
+
+  int slices = l.splitCols > 0 ? l.splitCols : 1;
+  slices = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(slices, std::max<int64_t>(1, vecPerRow))));
+  if (slices > 1 && (!l.workspace || l.workspaceBytes < rowReduceWorkspaceBytes(l.rows, slices)))
+    return cudaErrorInvalidValue;
+  const int64_t vecPerSlice = (vecPerRow + slices - 1) / slices;
+
+  int threads = l.ctaThreads > 0 ? l.ctaThreads : 256;
+  threads = threads >= 512 ? 512 : threads >= 256 ? 256 : threads >= 128 ? 128 : threads >= 64 ? 64 : 32;
+  // team size: enough lanes that each does about one batch of four vectors, at least a warp
+  int lanes = 32;
+  while (lanes < threads && static_cast<int64_t>(lanes) * 4 < vecPerSlice) lanes <<= 1;
+
+  RrParams p = {};
+  for (int k = 0; k < l.numViews; ++k) {
+    p.vbase[k] = static_cast<const char *>(l.views[k].base);
+    p.rowStride[k] = l.views[k].rowStride;
+    p.colStride[k] = static_cast<int>(l.views[k].colStride);
+  }
+  p.numViews = l.numViews;
+  p.rows = l.rows;
+  p.vecPerRow = static_cast<unsigned int>(vecPerRow);
+  p.vecPerSlice = static_cast<unsigned int>(vecPerSlice);
+  p.slices = slices;
+  p.lanesPerRow = lanes;
+  p.partial = static_cast<float *>(l.workspace);
+  p.out = l.out;
+  p.prog = l.body;
+
+  const int body = matchBody(l.body, l.numViews);
+  KernelFn fn;
+  if (l.elemType == kF32) fn = vector ? pickBody<PackF32, true>(body) : pickBody<PackF32, false>(body);
+  else if (l.elemType == kF16) fn = vector ? pickBody<PackF16, true>(body) : pickBody<PackF16, false>(body);
+  else fn = vector ? pickBody<PackBF16, true>(body) : pickBody<PackBF16, false>(body);
+
+  const int rowsPerCta = threads / lanes;
+  const int64_t work = ((l.rows + rowsPerCta - 1) / rowsPerCta) * slices;
+  int64_t grid = l.gridBlocks > 0 ? l.gridBlocks : work;
+  grid = std::max<int64_t>(1, std::min<int64_t>(grid, std::min<int64_t>(work, 0x7fffffff)));
+  fn<<<static_cast<unsigned int>(grid), threads, 0, stream>>>(p);
+  int n = 1;
+  cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess && slices > 1) {
+    const int ft = 256;
+    const unsigned int fg = static_cast<unsigned int>((l.rows + ft - 1) / ft);
+    if (l.elemType == kF32) rowReduceFinalizeKernel<PackF32><<<fg, ft, 0, stream>>>(p.partial, l.out, l.rows, slices);
+    else if (l.elemType == kF16) rowReduceFinalizeKernel<PackF16><<<fg, ft, 0, stream>>>(p.partial, l.out, l.rows, slices);
+    else rowReduceFinalizeKernel<PackBF16><<<fg, ft, 0, stream>>>(p.partial, l.out, l.rows, slices);
+    n = 2;
+    err = cudaGetLastError();
+  }
+  if (launched) *launched = n;
+  return err;
+}
+
+} // namespace kernels
+} // namespace afir

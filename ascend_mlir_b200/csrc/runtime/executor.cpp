@@ -1,0 +1,236 @@
+#include "runtime/executor.h"
+
+#include <cuda_runtime_api.h>
+
+#include <cstdio>
+#include <cstring>
+
+namespace afir {
+namespace {
+
+Status cudaFail(cudaError_t e, const char *what) {
+  return Status::error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+uint64_t fnv1a(const uint8_t *p, size_t n) {
+  uint64_t h = 1469598103934665603ull;
+  for (size_t i = 0; i < n; ++i) { h ^= p[i]; h *= 1099511628211ull; }
+  return h ^ (static_cast<uint64_t>(n) << 1);
+}
+
+} // namespace
+
+CudaExecutor::~CudaExecutor() {
+  if (!initialized_) return;
+  if (cudaSetDevice(device_) != cudaSuccess) return;
+  for (auto &s : slots_)
+    if (s.ptr) cudaFree(s.ptr);
+  if (workspace_.ptr) cudaFree(workspace_.ptr);
+  if (stream_) cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
+}
+
+Status CudaExecutor::initialize(int deviceId) {
+  if (deviceId < 0) return Status::error("device id must be non-negative");
+  device_ = deviceId;
+  initialized_ = true;  // the device itself is first touched by the first run (the reference defers too)
+  return Status::success();
+}
+
+Status CudaExecutor::ensureStream() {
+  cudaError_t e = cudaSetDevice(device_);
+  if (e != cudaSuccess) return cudaFail(e, "cudaSetDevice");
+  if (!stream_) {
+    cudaStream_t s;
+    e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return cudaFail(e, "cudaStreamCreate");
+    stream_ = s;
+  }
+  return Status::success();
+}
+
+Status CudaExecutor::slotFor(size_t index, size_t bytes, void **out) {
+  if (slots_.size() <= index) slots_.resize(index + 1);
+  Slot &s = slots_[index];
+  const size_t need = bytes ? bytes : 16;
+  if (s.capacity < need) {
+    if (s.ptr) cudaFree(s.ptr);
+    s.ptr = nullptr;
+    s.capacity = 0;
+    cudaError_t e = cudaMalloc(&s.ptr, need);
+    if (e != cudaSuccess) return cudaFail(e, "device allocation failed");
+    s.capacity = need;
+  }
+  *out = s.ptr;
+  return Status::success();
+}
+
+Status CudaExecutor::ownWorkspace(size_t bytes) {
+  if (workspace_.capacity >= bytes) return Status::success();
+  if (workspace_.ptr) cudaFree(workspace_.ptr);
+  workspace_ = Slot();
+  cudaError_t e = cudaMalloc(&workspace_.ptr, bytes);
+  if (e != cudaSuccess) return cudaFail(e, "workspace allocation failed");
+  workspace_.capacity = bytes;
+  return Status::success();
+}
+
+Status CudaExecutor::validate(const RunRequest &req, std::shared_ptr<const LaunchDescriptor> &desc,
+                              std::map<std::string, int64_t> &tiling) {
+  if (!initialized_) return Status::error("executor has not been initialized");
+  if (!req.binary || req.binaryLen == 0) return Status::error("binary data is required");
+  if (req.functionName.empty()) return Status::error("function name is required");
+  if (req.numInputs < 0 || req.numOutputs <= 0) return Status::error("invalid input/output binding counts");
+  if ((req.numInputs > 0 && (!req.inputPtrs || !req.inputBytes)) || !req.outputPtrs || !req.outputBytes)
+    return Status::error("input/output pointer arrays are required");
+  if (req.magic != kMagicVec && req.magic != kMagicCube) {
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "unsupported kernel magic: 0x%08x", req.magic);
+    return Status::error(buf);
+  }
+  const uint64_t key = fnv1a(req.binary, req.binaryLen);
+  auto it = cache_.find(key);
+  if (it == cache_.end()) {
+    auto d = std::make_shared<LaunchDescriptor>();
+    if (Status s = parseDescriptorBinary(req.binary, req.binaryLen, *d); !s) return s.withStage("cuda:artifact");
+    it = cache_.emplace(key, std::move(d)).first;
+  }
+  desc = it->second;
+  if (desc->kernel != req.functionName)
+    return Status::error("[cuda:artifact] kernel binary defines '" + desc->kernel + "', not '" + req.functionName + "'");
+  if (req.numInputs != desc->numInputs || req.numOutputs != desc->numOutputs)
+    return Status::error("[cuda:bindings] kernel '" + desc->kernel + "' takes " + std::to_string(desc->numInputs) +
+                         " inputs and " + std::to_string(desc->numOutputs) + " outputs, got " +
+                         std::to_string(req.numInputs) + " and " + std::to_string(req.numOutputs));
+  for (int i = 0; i < req.numInputs; ++i)
+    if (!req.inputPtrs[i] && req.inputBytes[i]) return Status::error("[cuda:bindings] input " + std::to_string(i) + " is null");
+  for (int i = 0; i < req.numOutputs; ++i)
+    if (!req.outputPtrs[i] && req.outputBytes[i]) return Status::error("[cuda:bindings] output " + std::to_string(i) + " is null");
+  if (Status s = unpackTiling(*desc, req.tiling, req.tilingLen, tiling); !s) return s.withStage("cuda:bindings");
+  return Status::success();
+}
+
+Status CudaExecutor::runHost(const RunRequest &req) {
+  std::shared_ptr<const LaunchDescriptor> desc;
+  std::map<std::string, int64_t> tiling;
+  if (Status s = validate(req, desc, tiling); !s) return s;
+  if (Status s = ensureStream(); !s) return s.withStage("cuda:device");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  LaunchArgs args;
+  args.device = device_;
+  args.stream = stream;
+  args.blockDim = req.blockDim;
+  const size_t numArgs = static_cast<size_t>(req.numInputs + req.numOutputs);
+  args.argPtrs.resize(numArgs);
+  args.argBytes.resize(numArgs);
+  for (int i = 0; i < req.numInputs; ++i) {
+    args.argBytes[i] = req.inputBytes[i];
+    if (Status s = slotFor(i, req.inputBytes[i], &args.argPtrs[i]); !s) return s.withStage("cuda:memory");
+  }
+  for (int i = 0; i < req.numOutputs; ++i) {
+    const size_t k = static_cast<size_t>(req.numInputs + i);
+    args.argBytes[k] = req.outputBytes[i];
+    if (Status s = slotFor(k, req.outputBytes[i], &args.argPtrs[k]); !s) return s.withStage("cuda:memory");
+  }
+  size_t wsBytes = 0;
+  if (Status s = requiredWorkspaceBytes(*desc, tiling, device_, wsBytes); !s) return s.withStage("cuda:bindings");
+  if (Status s = ownWorkspace(wsBytes); !s) return s.withStage("cuda:memory");
+  args.workspace = workspace_.ptr;
+  args.workspaceBytes = workspace_.capacity;
+
+  cudaError_t e;
+  for (int i = 0; i < req.numInputs; ++i) {
+    if (!req.inputBytes[i]) continue;
+    e = cudaMemcpyAsync(args.argPtrs[i], req.inputPtrs[i], req.inputBytes[i], cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] host-to-device copy failed");
+  }
+  e = cudaMemsetAsync(workspace_.ptr, 0, kWorkspaceStatusBytes, stream);
+  if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] workspace clear failed");
+
+  LaunchInfo info;
+  Status ls = launchDescriptor(*desc, tiling, args, info);
+  lastLaunchCount_ = info.kernelsLaunched;
+  totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
+  if (!ls) {
+    cudaStreamSynchronize(stream);
+    return ls.withStage("cuda:kernel_launch");
+  }
+  for (int i = 0; i < req.numOutputs; ++i) {
+    if (!req.outputBytes[i]) continue;
+    e = cudaMemcpyAsync(req.outputPtrs[i], args.argPtrs[req.numInputs + i], req.outputBytes[i], cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] device-to-host copy failed");
+  }
+  statusPending_ = info.usesStatusBlock;
+  statusWorkspace_ = workspace_.ptr;
+  matmulPending_ = desc->kernelClass == KernelClass::Matmul;
+  return synchronize(stream_);
+}
+
+Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream) {
+  std::shared_ptr<const LaunchDescriptor> desc;
+  std::map<std::string, int64_t> tiling;
+  if (Status s = validate(req, desc, tiling); !s) return s;
+  cudaError_t e = cudaSetDevice(device_);
+  if (e != cudaSuccess) return cudaFail(e, "[cuda:device] cudaSetDevice");
+
+  LaunchArgs args;
+  args.device = device_;
+  args.stream = static_cast<cudaStream_t>(stream);
+  args.blockDim = req.blockDim;
+  for (int i = 0; i < req.numInputs; ++i) {
+    args.argPtrs.push_back(const_cast<void *>(req.inputPtrs[i]));
+    args.argBytes.push_back(req.inputBytes[i]);
+  }
+  for (int i = 0; i < req.numOutputs; ++i) {
+    args.argPtrs.push_back(req.outputPtrs[i]);
+    args.argBytes.push_back(req.outputBytes[i]);
+  }
+  if (workspace) {
+    args.workspace = workspace;
+    args.workspaceBytes = workspaceBytes;
+  } else {
+    size_t wsBytes = 0;
+    if (Status s = requiredWorkspaceBytes(*desc, tiling, device_, wsBytes); !s) return s.withStage("cuda:bindings");
+    if (Status s = ownWorkspace(wsBytes); !s) return s.withStage("cuda:memory");
+    args.workspace = workspace_.ptr;
+    args.workspaceBytes = workspace_.capacity;
+  }
+  LaunchInfo info;
+  if (desc->kernelClass == KernelClass::Gather && args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes) {
+    e = cudaMemsetAsync(args.workspace, 0, 8, args.stream);
+    if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] workspace clear failed");
+  }
+  Status ls = launchDescriptor(*desc, tiling, args, info);
+  lastLaunchCount_ = info.kernelsLaunched;
+  totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
+  if (!ls) return ls.withStage("cuda:kernel_launch");
+  statusPending_ = info.usesStatusBlock;
+  statusWorkspace_ = args.workspace;
+  matmulPending_ = desc->kernelClass == KernelClass::Matmul;
+  return Status::success();
+}
+
+Status CudaExecutor::synchronize(void *stream) {
+  if (!initialized_) return Status::error("executor has not been initialized");
+  cudaError_t e = cudaSetDevice(device_);
+  if (e != cudaSuccess) return cudaFail(e, "[cuda:device] cudaSetDevice");
+  cudaStream_t s = static_cast<cudaStream_t>(stream ? stream : stream_);
+  e = s ? cudaStreamSynchronize(s) : cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cudaFail(e, "[cuda:kernel_launch] kernel execution failed");
+  if (statusPending_ && statusWorkspace_) {
+    statusPending_ = false;
+    unsigned long long bad = 0;
+    e = cudaMemcpy(&bad, statusWorkspace_, sizeof(bad), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] status read failed");
+    if (bad) return Status::error("[cuda:kernel_launch] gather index out of range (" + std::to_string(bad) + " indices)");
+  }
+  if (matmulPending_) {
+    matmulPending_ = false;
+    char text[256] = {0};
+    if (kernels::matmulCheckStatus(device_, text) != 0)
+      return Status::error(std::string("[cuda:kernel_launch] ") + (text[0] ? text : "matmul kernel reported a wait timeout"));
+  }
+  return Status::success();
+}
+
+} // namespace afir

@@ -1,0 +1,80 @@
+// CUDA execution runner: the B200 counterpart of the reference's NativeExecutionRunner
+// (lib/Runtime/Execution/NativeExecutionRunner.cpp:126-154,372-528): per call it stages the
+// inputs on the device, launches the kernel named by the binary, waits, and copies the outputs
+// back.  Device buffers are pooled per executor instead of being allocated and freed per call.
+#pragma once
+
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "runtime/descriptor.h"
+#include "runtime/launcher.h"
+
+namespace afir {
+
+constexpr uint32_t kMagicVec = 0x41415246u;   // vector / mixed kernels
+constexpr uint32_t kMagicCube = 0x41494343u;  // cube (matmul-only) kernels
+
+struct RunRequest {
+  const uint8_t *binary = nullptr;
+  size_t binaryLen = 0;
+  std::string functionName;
+  int numInputs = 0;
+  const void *const *inputPtrs = nullptr;
+  const size_t *inputBytes = nullptr;
+  int numOutputs = 0;
+  void *const *outputPtrs = nullptr;
+  const size_t *outputBytes = nullptr;
+  const uint8_t *tiling = nullptr;
+  size_t tilingLen = 0;
+  int blockDim = 0;
+  uint32_t magic = kMagicVec;
+};
+
+class CudaExecutor {
+public:
+  CudaExecutor() = default;
+  ~CudaExecutor();
+  CudaExecutor(const CudaExecutor &) = delete;
+  CudaExecutor &operator=(const CudaExecutor &) = delete;
+
+  Status initialize(int deviceId);
+  bool initialized() const { return initialized_; }
+  int device() const { return device_; }
+
+  // Host-pointer path: H2D, launch, D2H, synchronise, status checks.
+  Status runHost(const RunRequest &req);
+  // Device-pointer path: validates and enqueues the launch on `stream` and returns.
+  Status launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream);
+  // Waits for `stream` (null = the executor's own) and surfaces device-side status words.
+  Status synchronize(void *stream);
+
+  int lastLaunchCount() const { return lastLaunchCount_; }
+  uint64_t totalLaunchCount() const { return totalLaunchCount_; }
+
+private:
+  struct Slot { void *ptr = nullptr; size_t capacity = 0; };
+  Status validate(const RunRequest &req, std::shared_ptr<const LaunchDescriptor> &desc, std::map<std::string, int64_t> &tiling);
+  Status slotFor(size_t index, size_t bytes, void **out);
+  Status ensureStream();
+  Status ownWorkspace(size_t bytes);
+
+  bool initialized_ = false;
+  int device_ = 0;
+  void *stream_ = nullptr;
+  std::vector<Slot> slots_;
+  Slot workspace_;
+  std::unordered_map<uint64_t, std::shared_ptr<const LaunchDescriptor>> cache_;
+  int lastLaunchCount_ = 0;
+  uint64_t totalLaunchCount_ = 0;
+  bool statusPending_ = false;
+  void *statusWorkspace_ = nullptr;
+  bool matmulPending_ = false;
+};
+
+} // namespace afir

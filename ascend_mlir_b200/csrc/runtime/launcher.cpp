@@ -1,0 +1,386 @@
+#include "runtime/launcher.h"
+
+#include <algorithm>
+#include <cstring>
+
+namespace afir {
+namespace {
+
+Status evalDim(const DimExpr &e, const std::map<std::string, int64_t> &tiling, int64_t &out) {
+  if (e.literal) { out = e.value; return Status::success(); }
+  auto it = tiling.find(e.field);
+  if (it == tiling.end()) return Status::error("tiling field '" + e.field + "' is not in the kernel's TilingData");
+  out = it->second;
+  if (out < 0) return Status::error("tiling field '" + e.field + "' is negative");
+  return Status::success();
+}
+
+Status evalDims(const std::vector<DimExpr> &es, const std::map<std::string, int64_t> &tiling, std::vector<int64_t> &out) {
+  out.resize(es.size());
+  for (size_t i = 0; i < es.size(); ++i)
+    if (Status s = evalDim(es[i], tiling, out[i]); !s) return s;
+  return Status::success();
+}
+
+int64_t optionalField(const std::string &name, const std::map<std::string, int64_t> &tiling) {
+  if (name.empty()) return 0;
+  auto it = tiling.find(name);
+  return it == tiling.end() ? 0 : it->second;
+}
+
+int toElemType(DType t, bool &ok) {
+  ok = true;
+  switch (t) {
+  case DType::F32: return kernels::kF32;
+  case DType::F16: return kernels::kF16;
+  case DType::BF16: return kernels::kBF16;
+  default: ok = false; return 0;
+  }
+}
+
+// A view resolved against concrete sizes: element strides per iteration dim and a base offset.
+struct ResolvedView {
+  int arg = -1;
+  size_t elemBytes = 0;
+  int64_t baseOffset = 0;       // elements
+  std::vector<int64_t> stride;  // per domain dim
+};
+
+Status resolveView(const ViewSpec &v, const std::vector<int64_t> &domain, const std::map<std::string, int64_t> &tiling,
+                   const LaunchArgs &args, const char *what, ResolvedView &out) {
+  std::vector<int64_t> shape, offset;
+  if (Status s = evalDims(v.shape, tiling, shape); !s) return s;
+  if (v.offset.empty()) offset.assign(shape.size(), 0);
+  else if (Status s = evalDims(v.offset, tiling, offset); !s) return s;
+  out.arg = v.arg;
+  out.elemBytes = dtypeBytes(v.dtype);
+  int64_t elems = 1;
+  for (int64_t d : shape) elems *= d;
+  const size_t want = static_cast<size_t>(elems) * out.elemBytes;
+  if (v.arg >= static_cast<int>(args.argBytes.size())) return Status::error(std::string(what) + ": argument index out of range");
+  if (args.argBytes[v.arg] != want)
+    return Status::error(std::string(what) + ": argument " + std::to_string(v.arg) + " is " +
+                         std::to_string(args.argBytes[v.arg]) + " bytes, the tiling dims imply " + std::to_string(want));
+  out.stride.assign(domain.size(), 0);
+  out.baseOffset = 0;
+  int64_t ts = 1;
+  for (int t = static_cast<int>(shape.size()) - 1; t >= 0; --t) {
+    const int d = v.map.empty() ? -1 : v.map[t];
+    const int64_t extent = d >= 0 ? domain[d] : 1;
+    if (offset[t] < 0 || offset[t] + extent > shape[t])
+      return Status::error(std::string(what) + ": view exceeds argument " + std::to_string(v.arg) + " along dim " + std::to_string(t));
+    if (d >= 0) out.stride[d] += ts;
+    out.baseOffset += offset[t] * ts;
+    ts *= shape[t];
+  }
+  return Status::success();
+}
+
+// Collapses the iteration space: drops extent-1 dims and merges neighbours that every view walks
+// contiguously (a broadcast view, stride 0 on both, merges too).  Strides are rewritten in place.
+void collapseDomain(std::vector<int64_t> &domain, std::vector<ResolvedView *> &views) {
+  for (size_t d = 0; d < domain.size() && domain.size() > 1;) {
+    if (domain[d] == 1) {
+      domain.erase(domain.begin() + d);
+      for (auto *v : views) v->stride.erase(v->stride.begin() + d);
+    } else ++d;
+  }
+  for (size_t d = 0; d + 1 < domain.size();) {
+    bool mergeable = true;
+    for (auto *v : views)
+      if (v->stride[d] != v->stride[d + 1] * domain[d + 1]) { mergeable = false; break; }
+    if (mergeable) {
+      domain[d + 1] *= domain[d];
+      domain.erase(domain.begin() + d);
+      for (auto *v : views) v->stride.erase(v->stride.begin() + d);
+    } else ++d;
+  }
+}
+
+void *argAt(const LaunchArgs &args, const ResolvedView &v) {
+  return static_cast<char *>(args.argPtrs[v.arg]) + static_cast<size_t>(v.baseOffset) * v.elemBytes;
+}
+
+Status cudaStatus(int code, const char *what) {
+  if (code == 0) return Status::success();
+  return Status::error(std::string(what) + ": " + kernels::cudaErrorText(code));
+}
+
+Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                              const LaunchArgs &args, LaunchInfo &info) {
+  bool ok;
+  const int et = toElemType(d.dtype, ok);
+  if (!ok) return Status::error("elementwise groups compute in f32, f16 or bf16");
+  std::vector<int64_t> domain;
+  if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+  std::vector<ResolvedView> loads(g.loads.size());
+  ResolvedView store;
+  for (size_t i = 0; i < g.loads.size(); ++i) {
+    if (g.loads[i].dtype != d.dtype) return Status::error("load " + std::to_string(i) + " differs from the group element type");
+    if (Status s = resolveView(g.loads[i], domain, tiling, args, "load", loads[i]); !s) return s;
+  }
+  if (Status s = resolveView(g.store, domain, tiling, args, "store", store); !s) return s;
+  std::vector<ResolvedView *> all;
+  for (auto &v : loads) all.push_back(&v);
+  all.push_back(&store);
+  collapseDomain(domain, all);
+  if (domain.size() > 3) return Status::error("iteration space does not collapse to three dims");
+  while (domain.size() < 3) {
+    domain.insert(domain.begin(), 1);
+    for (auto *v : all) v->stride.insert(v->stride.begin(), 0);
+  }
+  if (store.stride[2] != 1 && domain[2] != 1) return Status::error("the store must be contiguous along the inner dim");
+
+  kernels::ElementwiseLaunch l = {};
+  l.elemType = et;
+  for (int i = 0; i < 3; ++i) l.dims[i] = domain[i];
+  l.numViews = static_cast<int>(loads.size());
+  for (size_t i = 0; i < loads.size(); ++i) {
+    l.views[i].base = argAt(args, loads[i]);
+    for (int k = 0; k < 3; ++k) l.views[i].stride[k] = loads[i].stride[k];
+    if (domain[2] == 1) l.views[i].stride[2] = 1;
+  }
+  l.outBase = argAt(args, store);
+  for (int k = 0; k < 3; ++k) l.outStride[k] = store.stride[k];
+  l.outStride[2] = 1;
+  l.body = g.body;
+  l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
+  l.unroll = static_cast<int>(optionalField(d.unrollField, tiling));
+  l.gridBlocks = args.blockDim;
+  int n = 0;
+  Status s = cudaStatus(kernels::launchElementwise(l, args.stream, &n), "elementwise launch");
+  info.kernelsLaunched += n;
+  return s;
+}
+
+Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                            const LaunchArgs &args, LaunchInfo &info) {
+  bool ok;
+  const int et = toElemType(d.dtype, ok);
+  if (!ok) return Status::error("row reductions compute in f32, f16 or bf16");
+  std::vector<int64_t> domain;
+  if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+  if (domain.size() < 2) return Status::error("row reduction needs a [rows..., cols] domain");
+  std::vector<ResolvedView> loads(g.loads.size());
+  ResolvedView store;
+  for (size_t i = 0; i < g.loads.size(); ++i)
+    if (Status s = resolveView(g.loads[i], domain, tiling, args, "load", loads[i]); !s) return s;
+  if (Status s = resolveView(g.store, domain, tiling, args, "store", store); !s) return s;
+  if (store.stride.back() != 0) return Status::error("the reduced dim must not index the output");
+  std::vector<ResolvedView *> all;
+  for (auto &v : loads) all.push_back(&v);
+  all.push_back(&store);
+  // keep the reduced (last) dim apart: collapse only the leading dims
+  const int64_t cols = domain.back();
+  std::vector<int64_t> outer(domain.begin(), domain.end() - 1);
+  std::vector<int64_t> colStride;
+  for (auto *v : all) { colStride.push_back(v->stride.back()); v->stride.pop_back(); }
+  collapseDomain(outer, all);
+  if (outer.size() != 1) return Status::error("row reduction: leading dims do not collapse to one row dim");
+  if (store.stride[0] != 1 && outer[0] != 1) return Status::error("row reduction: output rows must be contiguous");
+
+  kernels::RowReduceLaunch l = {};
+  l.elemType = et;
+  l.rows = outer[0];
+  l.cols = cols;
+  l.numViews = static_cast<int>(loads.size());
+  for (size_t i = 0; i < loads.size(); ++i) {
+    l.views[i].base = argAt(args, loads[i]);
+    l.views[i].rowStride = loads[i].stride[0];
+    l.views[i].colStride = colStride[i];
+  }
+  l.out = argAt(args, store);
+  l.body = g.body;
+  l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
+  int split = static_cast<int>(optionalField(d.splitColsField, tiling));
+  if (split <= 0) split = kernels::chooseRowReduceSplit(l.rows, l.cols, kernels::deviceSmCount(args.device));
+  l.splitCols = split;
+  if (split > 1) {
+    const size_t need = kWorkspaceStatusBytes + kernels::rowReduceWorkspaceBytes(l.rows, split);
+    if (!args.workspace || args.workspaceBytes < need)
+      return Status::error("row reduction split into " + std::to_string(split) + " column slices needs " +
+                           std::to_string(need) + " workspace bytes, " + std::to_string(args.workspaceBytes) + " given");
+    l.workspace = static_cast<char *>(args.workspace) + kWorkspaceStatusBytes;
+    l.workspaceBytes = args.workspaceBytes - kWorkspaceStatusBytes;
+  }
+  l.gridBlocks = args.blockDim;
+  int n = 0;
+  Status s = cudaStatus(kernels::launchRowReduce(l, args.stream, &n), "row-reduce launch");
+  info.kernelsLaunched += n;
+  return s;
+}
+
+Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                         const LaunchArgs &args, LaunchInfo &info) {
+  bool ok;
+  const int et = toElemType(d.dtype, ok);
+  if (!ok) return Status::error("gather groups compute in f32, f16 or bf16");
+  std::vector<int64_t> domain;
+  if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+  // table: a plain 2-D argument
+  const ViewSpec &tv = g.loads[0];
+  std::vector<int64_t> tshape;
+  if (Status s = evalDims(tv.shape, tiling, tshape); !s) return s;
+  if (tshape.size() != 2) return Status::error("gather table must be 2-D");
+  if (args.argBytes[tv.arg] != static_cast<size_t>(tshape[0] * tshape[1]) * dtypeBytes(tv.dtype))
+    return Status::error("gather table: argument " + std::to_string(tv.arg) + " byte size does not match the tiling dims");
+  if (tv.dtype != d.dtype) return Status::error("gather table differs from the group element type");
+  std::vector<int64_t> ishape;
+  if (Status s = evalDims(g.indices.shape, tiling, ishape); !s) return s;
+  const int64_t wantIdx = g.gatherAxis == 0 ? domain[0] : domain[1];
+  if (ishape.size() != 1 || ishape[0] != wantIdx) return Status::error("gather indices: expected a vector of " + std::to_string(wantIdx));
+  if (args.argBytes[g.indices.arg] != static_cast<size_t>(wantIdx) * dtypeBytes(g.indices.dtype))
+    return Status::error("gather indices: argument byte size does not match");
+  if (g.gatherAxis == 0 && tshape[1] != domain[1]) return Status::error("row gather: table width differs from the output width");
+  if (g.gatherAxis == 1 && tshape[0] != domain[0]) return Status::error("column gather: table rows differ from the output rows");
+
+  std::vector<ResolvedView> loads(g.loads.size());
+  ResolvedView store;
+  for (size_t i = 1; i < g.loads.size(); ++i) {
+    if (g.loads[i].dtype != d.dtype) return Status::error("load " + std::to_string(i) + " differs from the group element type");
+    if (Status s = resolveView(g.loads[i], domain, tiling, args, "load", loads[i]); !s) return s;
+  }
+  if (Status s = resolveView(g.store, domain, tiling, args, "store", store); !s) return s;
+  if (store.stride[1] != 1 && domain[1] != 1) return Status::error("gather: output must be contiguous along the inner dim");
+
+  kernels::GatherLaunch l = {};
+  l.elemType = et;
+  l.axis = g.gatherAxis;
+  l.indexType = g.indices.dtype == DType::I64 ? kernels::kI64 : kernels::kI32;
+  l.rows = domain[0];
+  l.cols = domain[1];
+  l.table = args.argPtrs[tv.arg];
+  l.tableRows = tshape[0];
+  l.tableCols = tshape[1];
+  l.tableRowStride = tshape[1];
+  l.indices = args.argPtrs[g.indices.arg];
+  l.numViews = static_cast<int>(g.loads.size());
+  for (size_t i = 1; i < loads.size(); ++i) {
+    l.views[i].base = argAt(args, loads[i]);
+    l.views[i].rowStride = loads[i].stride[0];
+    l.views[i].colStride = loads[i].stride[1];
+  }
+  l.out = argAt(args, store);
+  l.outRowStride = store.stride[0];
+  l.body = g.body;
+  if (args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes) {
+    l.status = static_cast<unsigned long long *>(args.workspace);
+    info.usesStatusBlock = true;
+  }
+  l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
+  l.unroll = static_cast<int>(optionalField(d.unrollField, tiling));
+  l.gridBlocks = args.blockDim;
+  int n = 0;
+  Status s = cudaStatus(kernels::launchGather(l, args.stream, &n), "gather launch");
+  info.kernelsLaunched += n;
+  return s;
+}
+
+Status launchTransposeGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                            const LaunchArgs &args, LaunchInfo &info) {
+  // domain = output shape [C, R]; loads[0] is the [R, C] input read as (d1, d0)
+  std::vector<int64_t> domain;
+  if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+  if (domain.size() != 2 || g.loads.size() != 1 || g.body.numOps != 0)
+    return Status::error("transpose groups are a bare 2-D permutation of one input");
+  ResolvedView in, store;
+  if (Status s = resolveView(g.loads[0], domain, tiling, args, "load", in); !s) return s;
+  if (Status s = resolveView(g.store, domain, tiling, args, "store", store); !s) return s;
+  if (in.stride[0] != 1 || store.stride[1] != 1) return Status::error("transpose: expected the input to be read column-wise");
+  kernels::TransposeLaunch l = {};
+  l.elemBytes = static_cast<int>(dtypeBytes(d.dtype));
+  l.rows = domain[1];
+  l.cols = domain[0];
+  l.in = argAt(args, in);
+  l.inRowStride = in.stride[1];
+  l.out = argAt(args, store);
+  l.outRowStride = store.stride[0];
+  int n = 0;
+  Status s = cudaStatus(kernels::launchTranspose(l, args.stream, &n), "transpose launch");
+  info.kernelsLaunched += n;
+  return s;
+}
+
+Status launchMatmulDescriptor(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args,
+                              LaunchInfo &info) {
+  const MatmulSpec &m = d.matmul;
+  int64_t M, N, K;
+  if (Status s = evalDim(m.m, tiling, M); !s) return s;
+  if (Status s = evalDim(m.n, tiling, N); !s) return s;
+  if (Status s = evalDim(m.k, tiling, K); !s) return s;
+  bool ok1, ok2, ok3;
+  kernels::MatmulLaunch l = {};
+  l.inType = toElemType(m.inType, ok1);
+  l.outType = toElemType(m.outType, ok2);
+  l.biasType = toElemType(m.biasType, ok3);
+  if (!ok1 || !ok2 || !ok3 || m.inType == DType::F32) return Status::error("matmul: inputs are f16 or bf16; bias/out f32, f16 or bf16");
+  auto check = [&](int arg, int64_t elems, DType t, const char *name) -> Status {
+    const size_t want = static_cast<size_t>(elems) * dtypeBytes(t);
+    if (args.argBytes[arg] != want)
+      return Status::error(std::string("matmul ") + name + ": argument " + std::to_string(arg) + " is " +
+                           std::to_string(args.argBytes[arg]) + " bytes, the tiling dims imply " + std::to_string(want));
+    return Status::success();
+  };
+  if (Status s = check(m.aArg, M * K, m.inType, "A"); !s) return s;
+  if (Status s = check(m.bArg, K * N, m.inType, "B"); !s) return s;
+  if (m.biasArg >= 0)
+    if (Status s = check(m.biasArg, N, m.biasType, "bias"); !s) return s;
+  if (Status s = check(m.outArg, M * N, m.outType, "out"); !s) return s;
+  l.M = M; l.N = N; l.K = K;
+  l.A = args.argPtrs[m.aArg];
+  l.B = args.argPtrs[m.bArg];
+  l.bias = m.biasArg >= 0 ? args.argPtrs[m.biasArg] : nullptr;
+  l.out = args.argPtrs[m.outArg];
+  l.epilogue = m.epilogue;
+  l.alpha = static_cast<float>(m.alpha);
+  l.gridBlocks = args.blockDim;
+  l.stages = static_cast<int>(optionalField(d.stagesField, tiling));
+  int n = 0;
+  char text[256] = {0};
+  const int code = kernels::launchMatmul(l, args.stream, &n, text);
+  info.kernelsLaunched += n;
+  if (code != 0) return Status::error(text[0] ? std::string(text) : std::string("matmul launch: ") + kernels::cudaErrorText(code));
+  return Status::success();
+}
+
+} // namespace
+
+Status requiredWorkspaceBytes(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, int device, size_t &bytes) {
+  bytes = kWorkspaceStatusBytes;
+  if (d.kernelClass != KernelClass::RowReduce) return Status::success();
+  for (const auto &g : d.groups) {
+    std::vector<int64_t> domain;
+    if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+    if (domain.size() < 2) continue;
+    int64_t rows = 1;
+    for (size_t i = 0; i + 1 < domain.size(); ++i) rows *= domain[i];
+    int split = static_cast<int>(optionalField(d.splitColsField, tiling));
+    if (split <= 0) split = kernels::chooseRowReduceSplit(rows, domain.back(), kernels::deviceSmCount(device));
+    bytes = std::max(bytes, kWorkspaceStatusBytes + kernels::rowReduceWorkspaceBytes(rows, split));
+  }
+  return Status::success();
+}
+
+Status launchDescriptor(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args,
+                        LaunchInfo &info) {
+  info = LaunchInfo();
+  const size_t numArgs = static_cast<size_t>(d.numInputs + d.numOutputs);
+  if (args.argPtrs.size() != numArgs || args.argBytes.size() != numArgs)
+    return Status::error("kernel '" + d.kernel + "' takes " + std::to_string(d.numInputs) + " inputs and " +
+                         std::to_string(d.numOutputs) + " outputs");
+  if (d.kernelClass == KernelClass::Matmul) return launchMatmulDescriptor(d, tiling, args, info);
+  for (const auto &g : d.groups) {
+    Status s;
+    switch (d.kernelClass) {
+    case KernelClass::Elementwise: s = launchElementwiseGroup(d, g, tiling, args, info); break;
+    case KernelClass::RowReduce: s = launchRowReduceGroup(d, g, tiling, args, info); break;
+    case KernelClass::Gather: s = launchGatherGroup(d, g, tiling, args, info); break;
+    case KernelClass::Transpose: s = launchTransposeGroup(d, g, tiling, args, info); break;
+    default: s = Status::error("unsupported kernel class"); break;
+    }
+    if (!s) return s;
+  }
+  return Status::success();
+}
+
+} // namespace afir

@@ -1,0 +1,41 @@
+// Turns a launch descriptor + TilingData values + device pointers into kernel launches.
+// Device-side argument order is the reference's canonical kernel signature
+// (inputs..., outputs..., workspace, TilingData),
+// lib/Conversion/CanonicalizeCannSignature/CanonicalizeCannSignaturePass.cpp:57-140.
+#pragma once
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "runtime/descriptor.h"
+
+namespace afir {
+
+// Workspace layout: a 256-byte status block (offset 0: u64 count of out-of-range gather indices),
+// then kernel scratch (row-reduction partial sums).
+constexpr size_t kWorkspaceStatusBytes = 256;
+
+struct LaunchArgs {
+  std::vector<void *> argPtrs;  // device pointers, inputs first then outputs
+  std::vector<size_t> argBytes;
+  void *workspace = nullptr;
+  size_t workspaceBytes = 0;
+  int blockDim = 0;  // CTAs to launch; <= 0 lets the library choose
+  cudaStream_t stream = nullptr;
+  int device = 0;
+};
+
+struct LaunchInfo {
+  int kernelsLaunched = 0;
+  bool usesStatusBlock = false;  // caller should zero it before and check it after
+};
+
+// Scratch bytes (status block included) the descriptor needs at these tiling values.
+Status requiredWorkspaceBytes(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, int device,
+                              size_t &bytes);
+
+Status launchDescriptor(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args,
+                        LaunchInfo &info);
+
+} // namespace afir

@@ -1,0 +1,54 @@
+/* Device-resident entry points of libAFIRRuntimeCAPI.so.
+ *
+ * The reference runtime keeps tensors on the device only inside one call
+ * (lib/Runtime/Execution/NativeExecutionRunner.cpp:372-511 allocates, copies in, launches, copies
+ * out and frees).  Callers that already hold their tensors in GPU memory use the functions below
+ * to reach the same kernels without the host round trip; everything else (binary, function name,
+ * TilingData, block_dim, magic, error convention) is as in CAPI/Runtime.h.
+ */
+#ifndef AFIR_CAPI_RUNTIME_CUDA_H
+#define AFIR_CAPI_RUNTIME_CUDA_H
+
+#include "CAPI/Runtime.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The launch half of NativeExecutionRunner::runWithHandle (reference
+ * lib/Runtime/Execution/NativeExecutionRunner.cpp:436-476: argument list
+ * [inputs..., outputs..., workspace, tiling] then rtKernelLaunch).  input_ptrs/output_ptrs are
+ * DEVICE pointers on the executor's device.  workspace may be NULL (the executor then owns one;
+ * that path may allocate) or a device buffer of workspace_bytes.  cuda_stream is a cudaStream_t
+ * (NULL = default stream).  Returns after enqueueing; nothing is synchronised. */
+int afirt_executor_launch_device(AfirtExecutor executor, const uint8_t *binary_data, size_t binary_len,
+                                 const char *function_name, int num_inputs, const void **input_ptrs,
+                                 const size_t *input_bytes, int num_outputs, void **output_ptrs,
+                                 const size_t *output_bytes, const uint8_t *tiling_data, size_t tiling_len,
+                                 int block_dim, uint32_t magic, void *workspace, size_t workspace_bytes,
+                                 void *cuda_stream, char *err_buf, size_t err_len);
+
+/* The wait half (reference NativeExecutionRunner.cpp:484-489, rtStreamSynchronize failure is an
+ * error): waits for cuda_stream (NULL = the executor's own stream, or the device) and reports
+ * device-side status words (gather index out of range, bounded-wait timeout in the matmul). */
+int afirt_executor_synchronize(AfirtExecutor executor, void *cuda_stream, char *err_buf, size_t err_len);
+
+/* Scratch bytes afirt_executor_launch_device needs for this binary at these tiling values
+ * (the reference sizes the workspace per task, include/Runtime/Execution/TaskGraph.h:54). */
+int afirt_executor_workspace_bytes(AfirtExecutor executor, const uint8_t *binary_data, size_t binary_len,
+                                   const uint8_t *tiling_data, size_t tiling_len, size_t *out_bytes,
+                                   char *err_buf, size_t err_len);
+
+/* Kernels launched by the most recent run / launch on this executor, and since creation
+ * (the launch counters the reference keeps per session, lib/Runtime/Execution/ExecutionSession.cpp:191-199). */
+int afirt_executor_last_launch_count(AfirtExecutor executor);
+uint64_t afirt_executor_total_launch_count(AfirtExecutor executor);
+
+/* Library identification: "afir-b200 <version> sm_100a". */
+const char *afirt_runtime_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* AFIR_CAPI_RUNTIME_CUDA_H */

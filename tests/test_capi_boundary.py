@@ -1,0 +1,138 @@
+"""The C-ABI boundary without a GPU: the library loads, exports every symbol the headers declare,
+and keeps the reference's error convention (lib/CAPI/Runtime/Runtime.cpp:306-481;
+test/tools/runtime/test_capi_runtime.cpp:168,176,189: the error buffer stays empty on success)."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from ascend_mlir_b200 import descriptors
+from ascend_mlir_b200.runtime import CompilerError, ExecutorError, compile_kernel
+from ascend_mlir_b200.runtime._capi import EXPORTS, get_lib
+from ascend_mlir_b200.runtime.executor import CudaRuntime
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    names = set()
+    for h in (ROOT / "include").rglob("*.h"):
+        names |= set(re.findall(r"\b(afirt_[a-z_]+)\s*\(", h.read_text()))
+    return names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = get_lib()
+    declared = _declared_symbols()
+    assert declared, "no declarations found under include/"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+    assert declared == set(EXPORTS)
+    assert b"sm_100a" in lib.afirt_runtime_version()
+
+
+def test_reference_seven_entry_points_present():
+    seven = ["afirt_compiler_create", "afirt_compiler_destroy", "afirt_compiler_compile", "afirt_executor_create",
+             "afirt_executor_destroy", "afirt_executor_initialize", "afirt_executor_run", "afirt_executor_run_file"]
+    text = (ROOT / "include" / "CAPI" / "Runtime.h").read_text()
+    for name in seven:
+        assert name in text and hasattr(get_lib(), name)
+
+
+def _run_expect_error(rt, spec, inputs, outputs, tiling, **kw):
+    with pytest.raises(ExecutorError) as e:
+        rt.run(spec.binary, kw.pop("fn", spec.name), inputs, outputs, tiling, **kw)
+    return str(e.value)
+
+
+def test_run_before_initialize_is_an_error():
+    spec = descriptors.add_mul()
+    rt = CudaRuntime()
+    a = np.zeros((2, 4), np.float32)
+    msg = _run_expect_error(rt, spec, [a, a], [a.copy()], spec.pack({"M": 2, "N": 4}))
+    assert msg == "executor has not been initialized"
+
+
+def test_initialize_rejects_negative_device_and_leaves_buffer_empty_on_success():
+    lib = get_lib()
+    h = lib.afirt_executor_create()
+    err = ctypes.create_string_buffer(256)
+    assert lib.afirt_executor_initialize(ctypes.c_void_p(h), -1, err, len(err)) != 0
+    assert err.value == b"device id must be non-negative"
+    err = ctypes.create_string_buffer(256)
+    assert lib.afirt_executor_initialize(ctypes.c_void_p(h), 0, err, len(err)) == 0
+    assert err.value == b""
+    lib.afirt_executor_destroy(ctypes.c_void_p(h))
+
+
+def test_argument_validation_messages():
+    spec = descriptors.add_mul()
+    rt = CudaRuntime()
+    rt.set_device(0)
+    a = np.zeros((2, 4), np.float32)
+    til = spec.pack({"M": 2, "N": 4})
+    assert _run_expect_error(rt, spec, [a, a], [a.copy()], til, magic=0x12345678) == "unsupported kernel magic: 0x12345678"
+    assert "function name is required" in _run_expect_error(rt, spec, [a, a], [a.copy()], til, fn="")
+    assert "defines 'add_mul', not 'other'" in _run_expect_error(rt, spec, [a, a], [a.copy()], til, fn="other")
+    assert "takes 2 inputs and 1 outputs" in _run_expect_error(rt, spec, [a], [a.copy()], til)
+    assert "tiling data is 8 bytes" in _run_expect_error(rt, spec, [a, a], [a.copy()], til[:8])
+    with pytest.raises(ExecutorError, match="binary data is required"):
+        rt.run(b"", spec.name, [a, a], [a.copy()], til)
+    with pytest.raises(ExecutorError, match="neither an AFCU container nor a launch descriptor"):
+        rt.run(b"\x7fELF not ours", spec.name, [a, a], [a.copy()], til)
+
+
+def test_error_text_is_truncated_and_terminated():
+    lib = get_lib()
+    h = lib.afirt_executor_create()
+    err = ctypes.create_string_buffer(b"\xff" * 8, 8)
+    rc = lib.afirt_executor_synchronize(ctypes.c_void_p(h), None, err, len(err))
+    assert rc != 0 and err.raw[7:8] == b"\0" and err.value == b"executo"
+    lib.afirt_executor_destroy(ctypes.c_void_p(h))
+
+
+def test_compile_writes_container_and_manifest(tmp_path):
+    spec = descriptors.bcast_add_rowsum("f32")
+    src = tmp_path / "k.cuda.json"
+    src.write_text(spec.descriptor_json())
+    out = compile_kernel(src, tmp_path / "out", spec.name)
+    blob = out.read_bytes()
+    assert out.name == f"{spec.name}.bin" and blob[:4] == b"AFCU"
+    assert int.from_bytes(blob[4:8], "little") == 1 and int.from_bytes(blob[8:12], "little") == len(blob) - 12
+    assert blob[12:].decode() == spec.descriptor_json()
+    manifest = dict(line.split("=", 1) for line in (tmp_path / "out" / "manifest.txt").read_text().splitlines())
+    assert manifest["kernel_name"] == spec.name and manifest["device_binary_path"] == str(out)
+    assert manifest["kernel_kind"] == "vec" and manifest["soc_version"] == "sm_100a"
+    # accepted reference arch names
+    compile_kernel(src, tmp_path / "out2", spec.name, arch="dav-c220-vec")
+    with pytest.raises(CompilerError, match="not 'wrong_name'"):
+        compile_kernel(src, tmp_path / "out", "wrong_name")
+    with pytest.raises(CompilerError, match="unsupported arch"):
+        compile_kernel(src, tmp_path / "out", spec.name, arch="sm_90a")
+    bad = tmp_path / "bad.json"
+    bad.write_text('{"format": "afir-cuda-launch", "version": 1, "kernel": "x", "kernel_class": "nope"}')
+    with pytest.raises(CompilerError, match="unknown kernel_class"):
+        compile_kernel(bad, tmp_path / "out", "x")
+    with pytest.raises(CompilerError, match="cannot open"):
+        compile_kernel(tmp_path / "missing.json", tmp_path / "out", "x")
+
+
+def test_descriptor_body_validation(tmp_path):
+    spec = descriptors.add_mul()
+    d = spec.descriptor
+    for mutate, needle in [
+        (lambda x: x["body"].__setitem__(0, {"op": "powf", "a": "v0", "b": "v1"}), "unsupported body op"),
+        (lambda x: x["body"].__setitem__(0, {"op": "addf", "a": "v0", "b": "v7"}), "not loaded"),
+        (lambda x: x["body"].__setitem__(0, {"op": "addf", "a": "%0", "b": "v1"}), "before it is defined"),
+        (lambda x: x.__setitem__("arch", "sm_90a"), "sm_100a only"),
+        (lambda x: x["store"].__setitem__("arg", 0), "must name an output"),
+    ]:
+        import copy, json
+        dd = copy.deepcopy(d)
+        mutate(dd)
+        p = tmp_path / "m.json"
+        p.write_text(json.dumps(dd))
+        with pytest.raises(CompilerError, match=needle):
+            compile_kernel(p, tmp_path / "o", spec.name)

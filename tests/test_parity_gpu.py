@@ -1,0 +1,238 @@
+"""GPU parity: every fused-group kernel, called through the afirt_* C-ABI, against the CPU oracle on the
+same seeded inputs, plus the reference's own golden fixtures.  Bars: bit-exact for f32 elementwise,
+for f16/bf16 chains (per-op rounding on both sides) and for all indexing; reductions within
+1e-5 * sum|x| per row."""
+import numpy as np
+import pytest
+
+from ascend_mlir_b200 import configs, descriptors
+from ascend_mlir_b200.runtime import ExecutorError
+from ascend_mlir_b200.runtime.executor import CudaRuntime
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def rt():
+    r = CudaRuntime()
+    r.set_device(0)
+    return r
+
+
+def run(rt, spec, inputs, out, shape, block_dim=0, **tile):
+    rt.run(spec.binary, spec.name, inputs, [out], spec.pack(shape, **tile), block_dim=block_dim, magic=spec.magic)
+    assert rt.last_launch_count >= 1
+    return out
+
+
+def bits(x):
+    return np.ascontiguousarray(x).view(np.uint16) if x.dtype == np.float16 else x
+
+
+# ---- elementwise chain ----------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N", [(4096, 512), (1, 4), (3, 5), (257, 1023), (64, 4096), (1, 1)])
+def test_add_mul_f32_bit_exact(rt, M, N):
+    w = configs.elementwise_chain(M, N, seed=3)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    assert np.array_equal(out.view(np.uint32), oracle.add_mul_f32(*w.inputs).view(np.uint32))
+
+
+@pytest.mark.parametrize("threads,unroll,block_dim", [(128, 1, 0), (256, 2, 7), (512, 4, 148), (256, 4, 1)])
+def test_add_mul_tile_params_do_not_change_results(rt, threads, unroll, block_dim):
+    w = configs.elementwise_chain(513, 1024, seed=4)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape, block_dim=block_dim, CTA_THREADS=threads, UNROLL=unroll)
+    assert np.array_equal(out, oracle.add_mul_f32(*w.inputs))
+
+
+def test_add_mul_empty(rt):
+    w = configs.elementwise_chain(0, 16)
+    out = run_empty = np.zeros((0, 16), np.float32)
+    rt.run(w.spec.binary, w.spec.name, w.inputs, [out], w.tiling())
+    assert run_empty.size == 0
+
+
+def test_add_mul_special_values(rt):
+    a = np.array([[np.nan, np.inf, -np.inf, -0.0, 1e-45, 3.4e38, 1.0, -1.0]], np.float32)
+    b = np.array([[1.0, -np.inf, 2.0, 0.0, 1e-45, 3.4e38, np.nan, 1e-30]], np.float32)
+    spec = descriptors.add_mul()
+    out = run(rt, spec, [a, b], np.zeros_like(a), {"M": 1, "N": 8})
+    want = oracle.add_mul_f32(a, b)
+    assert np.array_equal(np.isnan(out), np.isnan(want))
+    m = ~np.isnan(want)
+    assert np.array_equal(out.view(np.uint32)[m], want.view(np.uint32)[m])
+
+
+# ---- split / broadcast ------------------------------------------------------------------------------
+@pytest.mark.parametrize("B,R,C,axis", [(4, 64, 256, 1), (4, 64, 256, 2), (2, 3, 8, 1), (3, 5, 7, 1), (1, 17, 24, 2)])
+def test_split_relu_bias_mul_f16_bit_exact(rt, B, R, C, axis):
+    w = configs.split_relu_broadcast_add_mul(B, R, C, bias_axis=axis, seed=5)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    want = oracle.split_relu_bias_mul_f16(w.inputs[0], w.inputs[1], bias_axis=axis)
+    assert np.array_equal(bits(out), bits(want))
+
+
+def test_split_relu_negative_zero_and_nan(rt):
+    x = np.zeros((1, 2, 16), np.float16)
+    x[0, 0, :8] = [-0.0, 0.0, -1.0, np.nan, 6e-8, -6e-8, 65504, -65504]
+    x[0, :, 8:] = 1.0
+    bias = np.array([-0.0, 0.0], np.float16)
+    spec = descriptors.split_relu_bias_mul(1)
+    shape = {"B": 1, "R": 2, "C2": 16, "C": 8, "BIAS": 2}
+    out = run(rt, spec, [x, bias], np.zeros((1, 2, 8), np.float16), shape)
+    want = oracle.split_relu_bias_mul_f16(x, bias, 1)
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(out), nan)
+    assert np.array_equal(bits(out)[~nan], bits(want)[~nan])
+
+
+def test_reference_split_example_golden(rt, golden_dir):
+    g = dict(np.load(golden_dir / "split_relu_brc_add_mul.npz"))
+    spec = descriptors.split_rows_relu_bias_scale()
+    M, N = g["input_a"].shape
+    out = run(rt, spec, [g["input_a"], g["bias0"], g["bias1"], g["scale0"], g["scale1"]], np.zeros((M, N), np.float16),
+              {"M": M, "N": N, "HM": M // 2})
+    assert rt.last_launch_count == 2  # two halves, written in place of the concat
+    want = oracle.split_rows_relu_bias_scale_f16(g["input_a"], g["bias0"], g["bias1"], g["scale0"], g["scale1"])
+    assert np.array_equal(bits(out), bits(want))
+    fails, _, _ = oracle.compare(out.astype(np.float32), g["output"].astype(np.float32), 1e-2, 1e-2)
+    assert fails == 0
+
+
+def test_reference_concat_example_golden(rt, golden_dir):
+    g = dict(np.load(golden_dir / "add_broadcast_concat.npz"))
+    spec = descriptors.add_mul_concat()
+    M, N = g["input_b"].shape
+    out = run(rt, spec, [g["input_a"], g["input_b"], g["input_c"], g["input_d"]], np.zeros((2 * M, N), np.float16),
+              {"M": M, "N": N, "M2": 2 * M})
+    assert np.array_equal(bits(out), bits(g["output"]))
+
+
+def test_reference_transpose_example_golden_memcmp(rt, golden_dir):
+    g = dict(np.load(golden_dir / "relu_broadcast_transpose.npz"))
+    spec = descriptors.relu_bcast_transpose_add()
+    N, M = g["input_data1"].shape
+    out = run(rt, spec, [g["input_data0"], g["input_data1"]], np.zeros((N, M), np.float16), {"M": M, "N": N})
+    assert out.tobytes() == g["output_expected"].tobytes()
+
+
+@pytest.mark.parametrize("R,C,dtype", [(640, 500, np.float16), (65, 129, np.float32), (1, 7, np.float16), (2048, 1024, np.float32)])
+def test_transpose_2d(rt, R, C, dtype):
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((R, C)).astype(dtype)
+    spec = descriptors.transpose_2d("f16" if dtype == np.float16 else "f32")
+    out = run(rt, spec, [x], np.zeros((C, R), dtype), {"R": R, "C": C})
+    assert out.tobytes() == oracle.transpose_2d(x).tobytes()
+
+
+def test_interpreted_body_matches_oracle_chain(rt):
+    # a chain with no straight-line specialisation: ((a - b) / b) min a
+    spec = descriptors.add_mul()
+    import copy
+    d = copy.deepcopy(spec.descriptor)
+    d["kernel"] = "sub_div_min"
+    d["body"] = [descriptors.op("subf", "v0", "v1"), descriptors.op("divf", "%0", "v1"), descriptors.op("minimumf", "%1", "v0")]
+    rng = np.random.default_rng(8)
+    a = rng.uniform(-1, 1, (33, 64)).astype(np.float32)
+    b = rng.uniform(0.5, 1.5, (33, 64)).astype(np.float32)
+    out = np.zeros_like(a)
+    rt.run(descriptors.container(d), "sub_div_min", [a, b], [out], spec.pack({"M": 33, "N": 64}))
+    assert np.array_equal(out, np.minimum((a - b) / b, a))
+
+
+# ---- row reduction ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N", [(256, 8192), (7, 33), (1, 1), (300, 1000), (4, 65536), (1000, 32)])
+def test_bcast_add_rowsum_f32_within_bound(rt, M, N):
+    w = configs.broadcast_add_reduce(M, N, seed=9)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    ref, s64, abs64 = oracle.bcast_add_rowsum_f32(w.inputs[0], w.inputs[1], with_bounds=True)
+    # |gpu - exact| <= 1e-5 * sum|x_ij + b_i|; the sequential CPU sum sits inside the same bound
+    assert np.all(np.abs(out - s64) <= 1e-5 * abs64 + 1e-30)
+    assert np.all(np.abs(ref - s64) <= 1e-5 * abs64 + 1e-30)
+
+
+@pytest.mark.parametrize("split", [1, 2, 5, 16])
+def test_rowsum_split_columns_use_workspace(rt, split):
+    w = configs.broadcast_add_reduce(5, 40000, seed=10)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape, SPLIT_N=split)
+    assert rt.last_launch_count == (2 if split > 1 else 1)
+    _, s64, abs64 = oracle.bcast_add_rowsum_f32(w.inputs[0], w.inputs[1], with_bounds=True)
+    assert np.all(np.abs(out - s64) <= 1e-5 * abs64)
+
+
+def test_reference_reduce_example_golden(rt, golden_dir):
+    g = dict(np.load(golden_dir / "broadcast_add_reduce.npz"))
+    spec = descriptors.bcast_add_rowsum("f16")
+    M, N = g["input_b"].shape
+    out = run(rt, spec, [g["input_a"], g["input_b"]], np.zeros(M, np.float16), {"M": M, "N": N})
+    want = oracle.bcast_add_rowsum_f16(g["input_a"], g["input_b"])
+    # f32 accumulation order differs; after the final f16 rounding at most one ulp apart
+    assert np.max(np.abs(out.astype(np.float32) - want.astype(np.float32))) <= np.max(np.abs(want.astype(np.float32))) * 2.0 ** -10
+    fails, _, _ = oracle.compare(out.astype(np.float32), g["output_c"].astype(np.float32), 10.0, 1e-2)
+    assert fails == 0
+
+
+# ---- gather ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T,W,R", [(4096, 256, 2048), (100, 8, 33), (50, 7, 20), (10, 256, 1), (65536, 64, 5000)])
+def test_gather_rows_bf16_bit_exact(rt, T, W, R):
+    w = configs.gather_elementwise(T, W, R, seed=11)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(*w.inputs))
+
+
+def test_gather_rows_edges_and_duplicates(rt):
+    w = configs.gather_elementwise(1000, 64, 512, seed=12)
+    idx = w.inputs[1]
+    idx[:4] = [0, 999, 0, 999]
+    idx[100:200] = idx[300]  # heavy duplication
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(*w.inputs))
+
+
+def test_gather_rows_out_of_range_index_is_reported_not_clamped(rt):
+    w = configs.gather_elementwise(100, 16, 40, seed=13)
+    w.inputs[1][7] = 100
+    w.inputs[1][9] = -1
+    out = np.full(w.out_shape, 0x7FC0, np.uint16)
+    with pytest.raises(ExecutorError, match=r"gather index out of range \(2 indices\)"):
+        rt.run(w.spec.binary, w.spec.name, w.inputs, [out], w.tiling())
+    # the context survives and the next call works
+    w.inputs[1][[7, 9]] = 0
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(*w.inputs))
+
+
+def test_reference_gather_example_golden_exact(rt, golden_dir):
+    g = dict(np.load(golden_dir / "gather_elementwise_fusion.npz"))
+    spec = descriptors.relu_gather_cols_bias()
+    M, N = g["input_data"].shape
+    K = g["input_indices"].shape[0]
+    out = run(rt, spec, [g["input_data"], g["input_indices"], g["input_bias"]], np.zeros((M, K), np.float16),
+              {"M": M, "N": N, "K": K})
+    assert out.tobytes() == g["output_out"].tobytes()
+
+
+def test_gather_cols_i32_and_odd_shapes(rt):
+    rng = np.random.default_rng(14)
+    data = rng.standard_normal((37, 91)).astype(np.float16)
+    idx = rng.integers(0, 91, 53).astype(np.int32)
+    bias = rng.standard_normal(53).astype(np.float16)
+    spec = descriptors.relu_gather_cols_bias("f16", "i32")
+    out = run(rt, spec, [data, idx, bias], np.zeros((37, 53), np.float16), {"M": 37, "N": 91, "K": 53})
+    assert np.array_equal(bits(out), bits(oracle.relu_gather_cols_bias_f16(data, idx.astype(np.int64), bias)))
+
+
+# ---- shape errors surface before any launch -------------------------------------------------------------------
+def test_byte_size_mismatch_is_refused(rt):
+    w = configs.elementwise_chain(8, 16)
+    with pytest.raises(ExecutorError, match="bytes, the tiling dims imply"):
+        rt.run(w.spec.binary, w.spec.name, w.inputs, [w.new_output()], w.spec.pack({"M": 8, "N": 32}))
+
+
+def test_run_file_matches_run(rt, tmp_path):
+    w = configs.elementwise_chain(64, 64, seed=15)
+    p = tmp_path / "k.bin"
+    p.write_bytes(w.spec.binary)
+    out = w.new_output()
+    rt.run_file(str(p), w.spec.name, w.inputs, [out], w.tiling())
+    assert np.array_equal(out, oracle.add_mul_f32(*w.inputs))
