@@ -97,6 +97,7 @@ struct RowReduceLaunch {
   void *out;  // [rows], elemType
   BodyProgram body;
   int ctaThreads;   // 0 = default
+  int teamLanes;    // threads cooperating on one row (power of two, 32..ctaThreads); 0 = choose
   int splitCols;    // column slices per row (>1 uses `workspace` for the partial sums); 0 = choose
   void *workspace;  // device scratch, at least rowReduceWorkspaceBytes(...) when splitCols > 1
   size_t workspaceBytes;

@@ -1,10 +1,537 @@
+// Matmul + bias + LeakyReLU fused group for sm_100a:
+//     out[M,N] = epilogue(A[M,K] . B[K,N] + bias[N]),  epilogue(x) = max(x, alpha * x)
+// (semantics: lib/Conversion/MarkStructuredOps/AnnotateMixMatmulSemanticsPass.cpp:171-242 --
+// BiasAdd then maximumf(x, mulf(x, alpha)); the reference runs the matmul on the cube unit and
+// re-reads C from global memory for the LeakyRelu, lib/Target/CannKernel/CannTranslation.cpp:1573-1615;
+// here the epilogue is applied to the accumulator before it ever leaves the SM).
+//
+// Structure (one persistent CTA per SM, no clusters, no multicast):
+//   warp 0      TMA producer: A tile [TM x 64] (K-major, 128B swizzle) and B tile [64 x 256]
+//               (N-major, four 64x64 boxes, 128B swizzle) into a ring of shared-memory stages;
+//   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::f16, 128x256x16 per instruction,
+//               f32 accumulators in tensor memory (2 x 256 columns); also owns TMEM alloc/free;
+//   warps 2..   epilogue: tcgen05.ld the accumulator (one row per thread), + bias, LeakyReLU,
+//               convert, 16-byte stores.
+// TM = 128 * MB.  MB = 1: the two TMEM accumulators double-buffer consecutive tiles (epilogue of tile
+// i overlaps the mainloop of tile i+1).  MB = 2: a 256x256 tile uses both accumulators, halving the
+// L2->SM operand traffic per flop (A and B are each read once per 256 rows/columns instead of 128).
+//
+// Every wait on an mbarrier is bounded: after ~2 s the waiting thread records a status word, raises a
+// CTA-wide abort flag and every role leaves its loop; the CTA then waits (bounded) for TMA copies still
+// in flight, frees its tensor memory and returns.  The host reports the status as an error.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
 #include <cstdio>
+#include <mutex>
+
 #include "kernels/kernels.h"
-namespace afir { namespace kernels {
-int launchMatmul(const MatmulLaunch &, cudaStream_t, int *launched, char *errorText) {
+
+namespace afir {
+namespace kernels {
+namespace {
+
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;           // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kTmemCols = 512;
+constexpr int kBBoxBytes = 64 * 64 * 2;   // one 64(k) x 64(n) box
+constexpr int kBStageBytes = 4 * kBBoxBytes;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+// status word: 0 = ok, else (code << 8) | role
+__device__ unsigned int g_matmulStatus = 0;
+
+struct GemmParams {
+  int M, N, K;
+  int numTilesM, numTilesN, numKBlocks;
+  const void *bias;
+  void *out;
+  int biasType, epilogue;
+  float alpha;
+  unsigned int idesc;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned int smemAddr(const void *p) {
+  return static_cast<unsigned int>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long globalTimerNs() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbarInit(unsigned int bar, unsigned int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbarExpectTx(unsigned int bar, unsigned int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(unsigned int bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(unsigned int bar, unsigned int parity) {
+  unsigned int done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait.  Returns false when the abort flag is (or becomes) raised.
+__device__ __forceinline__ bool mbarWait(unsigned int bar, unsigned int parity, volatile int *abortFlag, unsigned int role) {
+  if (mbarTryWait(bar, parity)) return true;
+  const unsigned long long t0 = globalTimerNs();
+  unsigned int spins = 0;
+  while (true) {
+    if (mbarTryWait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*abortFlag) return false;
+      if (globalTimerNs() - t0 > kWaitLimitNs) {
+        *abortFlag = 1;
+        atomicCAS(&g_matmulStatus, 0u, (1u << 8) | role);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tmaLoad2d(unsigned int dst, const CUtensorMap *map, int x, int y, unsigned int bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void prefetchTensorMap(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ void tcgen05FenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05FenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmemAlloc(unsigned int dstSmem, unsigned int cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dstSmem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmemRelinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmemDealloc(unsigned int taddr, unsigned int cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void ummaF16(unsigned int dTmem, unsigned long long aDesc, unsigned long long bDesc,
+                                        unsigned int idesc, unsigned int accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void ummaCommit(unsigned int bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmemLoad32(unsigned int taddr, unsigned int (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading/stride byte offsets (>>4),
+// descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ unsigned long long smemDesc(unsigned int addr, unsigned int lboBytes, unsigned int sboBytes) {
+  unsigned long long d = 0;
+  d |= static_cast<unsigned long long>((addr & 0x3FFFFu) >> 4);
+  d |= static_cast<unsigned long long>((lboBytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<unsigned long long>((sboBytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // descriptor version (Blackwell)
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ float loadBias(const void *bias, int type, int n) {
+  if (type == kF32) return __ldg(static_cast<const float *>(bias) + n);
+  if (type == kF16) return __half2float(__ldg(static_cast<const __half *>(bias) + n));
+  return __bfloat162float(__ldg(static_cast<const __nv_bfloat16 *>(bias) + n));
+}
+
+template <int OUT> struct OutPack;
+template <> struct OutPack<kF32> {
+  static constexpr int kBytes = 4;
+  // 8 consecutive columns -> two 16-byte stores
+  __device__ __forceinline__ static void store8(void *dst, const float *v) {
+    float4 *p = static_cast<float4 *>(dst);
+    p[0] = make_float4(v[0], v[1], v[2], v[3]);
+    p[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct OutPack<kBF16> {
+  static constexpr int kBytes = 2;
+  __device__ __forceinline__ static void store8(void *dst, const float *v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 u;
+    u.x = *reinterpret_cast<unsigned int *>(&a);
+    u.y = *reinterpret_cast<unsigned int *>(&b);
+    u.z = *reinterpret_cast<unsigned int *>(&c);
+    u.w = *reinterpret_cast<unsigned int *>(&d);
+    *static_cast<uint4 *>(dst) = u;
+  }
+};
+template <> struct OutPack<kF16> {
+  static constexpr int kBytes = 2;
+  __device__ __forceinline__ static void store8(void *dst, const float *v) {
+    __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+    __half2 c = __floats2half2_rn(v[4], v[5]), d = __floats2half2_rn(v[6], v[7]);
+    uint4 u;
+    u.x = *reinterpret_cast<unsigned int *>(&a);
+    u.y = *reinterpret_cast<unsigned int *>(&b);
+    u.z = *reinterpret_cast<unsigned int *>(&c);
+    u.w = *reinterpret_cast<unsigned int *>(&d);
+    *static_cast<uint4 *>(dst) = u;
+  }
+};
+
+// shared-memory control block (after the operand ring)
+template <int STAGES> struct Control {
+  unsigned long long full[STAGES];
+  unsigned long long empty[STAGES];
+  unsigned long long tmemFull[2];
+  unsigned long long tmemEmpty[2];
+  unsigned int tmemBase;
+  int abortFlag;
+};
+
+template <int MB> struct Shape {
+  static constexpr int kTileM = 128 * MB;
+  static constexpr int kAStageBytes = kTileM * kBlockK * 2;
+  static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+  static constexpr int kStages = MB == 1 ? 4 : 3;
+  static constexpr int kEpilogueWarps = 4 * MB;
+  static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+  static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + sizeof(Control<kStages>);
+};
+
+template <int MB, int OUT>
+__global__ void __launch_bounds__(Shape<MB>::kThreads, 1)
+matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                    const __grid_constant__ GemmParams prm) {
+  using S = Shape<MB>;
+  constexpr int STAGES = S::kStages;
+  extern __shared__ unsigned char smemRaw[];
+  // 128-byte-swizzled tiles want 1024-byte alignment
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+  Control<STAGES> *ctl = reinterpret_cast<Control<STAGES> *>(smem + static_cast<size_t>(STAGES) * S::kStageBytes);
+  volatile int *abortFlag = &ctl->abortFlag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int numTiles = prm.numTilesM * prm.numTilesN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbarInit(smemAddr(&ctl->full[s]), 1);
+      mbarInit(smemAddr(&ctl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbarInit(smemAddr(&ctl->tmemFull[a]), 1);
+      mbarInit(smemAddr(&ctl->tmemEmpty[a]), MB == 1 ? 4 : 4);  // one arrival per epilogue warp of that accumulator
+    }
+    ctl->abortFlag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    prefetchTensorMap(&mapA);
+    prefetchTensorMap(&mapB);
+  }
+  if (warp == 1) {
+    tmemAlloc(smemAddr(&ctl->tmemBase), kTmemCols);
+    tmemRelinquish();
+  }
+  tcgen05FenceBefore();
+  __syncthreads();
+  tcgen05FenceAfter();
+  const unsigned int tmemBase = ctl->tmemBase;
+
+  // Tile order: M fastest inside bands of 16 tile-rows so that concurrently running CTAs share
+  // A row-panels and B column-panels in L2.
+  auto tileCoords = [&](int t, int &tm, int &tn) {
+    constexpr int kBand = 16;
+    const int bandTiles = kBand * prm.numTilesN;
+    const int band = t / bandTiles;
+    const int within = t - band * bandTiles;
+    const int rowsInBand = min(kBand, prm.numTilesM - band * kBand);
+    tm = band * kBand + within % rowsInBand;
+    tn = within / rowsInBand;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      unsigned int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tileCoords(t, tm, tn);
+        for (int kb = 0; kb < prm.numKBlocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const unsigned int phase = (it / STAGES) & 1u;
+          if (!mbarWait(smemAddr(&ctl->empty[s]), phase ^ 1u, abortFlag, 0)) { ok = false; break; }
+          const unsigned int full = smemAddr(&ctl->full[s]);
+          mbarExpectTx(full, S::kStageBytes);
+          unsigned char *stage = smem + static_cast<size_t>(s) * S::kStageBytes;
+          tmaLoad2d(smemAddr(stage), &mapA, kb * kBlockK, tm * S::kTileM, full);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tmaLoad2d(smemAddr(stage + S::kAStageBytes + j * kBBoxBytes), &mapB, tn * kBlockN + j * 64, kb * kBlockK, full);
+        }
+      }
+      if (!ok) {
+        // loads already issued still land in this CTA's shared memory: give them time before leaving
+        for (int s = 0; s < STAGES; ++s) {
+          const unsigned long long t0 = globalTimerNs();
+          while (!mbarTryWait(smemAddr(&ctl->full[s]), 0) && !mbarTryWait(smemAddr(&ctl->full[s]), 1) &&
+                 globalTimerNs() - t0 < 1000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      unsigned int it = 0, tileIter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileIter) {
+        // accumulator(s) of this tile and the parity of their "drained" barrier
+        const int acc0 = MB == 1 ? static_cast<int>(tileIter & 1u) : 0;
+        const unsigned int use = MB == 1 ? (tileIter >> 1) : tileIter;  // how many times this accumulator was used before
+        for (int h = 0; h < MB && ok; ++h)
+          if (!mbarWait(smemAddr(&ctl->tmemEmpty[acc0 + h]), (use & 1u) ^ 1u, abortFlag, 1)) ok = false;
+        if (!ok) break;
+        tcgen05FenceAfter();
+        for (int kb = 0; kb < prm.numKBlocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const unsigned int phase = (it / STAGES) & 1u;
+          if (!mbarWait(smemAddr(&ctl->full[s]), phase, abortFlag, 1)) { ok = false; break; }
+          tcgen05FenceAfter();
+          const unsigned int aBase = smemAddr(smem + static_cast<size_t>(s) * S::kStageBytes);
+          const unsigned int bBase = aBase + S::kAStageBytes;
+#pragma unroll
+          for (int h = 0; h < MB; ++h) {
+            const unsigned int dTmem = tmemBase + static_cast<unsigned int>((acc0 + h) * kBlockN);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              // A: K-major, rows 128 B apart, 8-row groups 1024 B apart; 16 k-elements = 32 bytes along the row
+              const unsigned long long aDesc = smemDesc(aBase + h * (128 * kBlockK * 2) + k * (kUmmaK * 2), 16, 1024);
+              // B: N-major, 64-column blocks 8192 B apart (leading), 8-row k-groups 1024 B apart (stride);
+              // 16 k-rows = two k-groups = 2048 bytes
+              const unsigned long long bDesc = smemDesc(bBase + k * (kUmmaK * 128), kBBoxBytes, 1024);
+              ummaF16(dTmem, aDesc, bDesc, prm.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+          }
+          ummaCommit(smemAddr(&ctl->empty[s]));  // frees the stage when these MMAs have read it
+        }
+        if (!ok) break;
+        for (int h = 0; h < MB; ++h) ummaCommit(smemAddr(&ctl->tmemFull[acc0 + h]));
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int ew = warp - 2;                 // 0 .. 4*MB-1
+    const int half = ew / 4;                 // which accumulator of an MB=2 tile
+    const int quarter = warp & 3;            // TMEM lanes this warp may touch: [32*quarter, 32*quarter+32)
+    unsigned int tileIter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileIter) {
+      int tm, tn;
+      tileCoords(t, tm, tn);
+      const int acc = MB == 1 ? static_cast<int>(tileIter & 1u) : half;
+      const unsigned int use = MB == 1 ? (tileIter >> 1) : tileIter;
+      if (!mbarWait(smemAddr(&ctl->tmemFull[acc]), use & 1u, abortFlag, 2)) { ok = false; break; }
+      tcgen05FenceAfter();
+      const int row = tm * S::kTileM + half * 128 + quarter * 32 + lane;
+      const unsigned int taddr = tmemBase + static_cast<unsigned int>(acc * kBlockN) + (static_cast<unsigned int>(quarter * 32) << 16);
+      unsigned char *outRow = static_cast<unsigned char *>(prm.out) + static_cast<size_t>(row) * prm.N * OutPack<OUT>::kBytes;
+#pragma unroll 1
+      for (int c = 0; c < kBlockN; c += 32) {
+        unsigned int r[32];
+        tmemLoad32(taddr + c, r);
+        tmemLoadWait();
+        const int n0 = tn * kBlockN + c;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float x = __uint_as_float(r[j + e]);
+            const int n = n0 + j + e;
+            if (prm.epilogue != kEpiNone && n < prm.N) x += loadBias(prm.bias, prm.biasType, n);
+            if (prm.epilogue == kEpiBiasAddLeakyRelu) x = fmaxf(x, x * prm.alpha);
+            else if (prm.epilogue == kEpiBiasAddRelu) x = fmaxf(x, 0.0f);
+            v[e] = x;
+          }
+          if (row < prm.M && n0 + j < prm.N)  // N is a multiple of 8: whole 8-column groups are in or out
+            OutPack<OUT>::store8(outRow + static_cast<size_t>(n0 + j) * OutPack<OUT>::kBytes, v);
+        }
+      }
+      tcgen05FenceBefore();
+      __syncwarp();
+      if (lane == 0) mbarArrive(smemAddr(&ctl->tmemEmpty[acc]));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tcgen05FenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05FenceAfter();
+    tmemDealloc(tmemBase, kTmemCols);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+bool makeMap2d(CUtensorMap *map, CUtensorMapDataType type, const void *base, uint64_t inner, uint64_t outer,
+               uint64_t rowBytes, uint32_t boxInner, uint32_t boxOuter) {
+  EncodeTiledFn fn = encodeTiled();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {rowBytes};
+  cuuint32_t box[2] = {boxInner, boxOuter};
+  cuuint32_t elemStrides[2] = {1, 1};
+  return fn(map, type, 2, const_cast<void *>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+void fail(char *errorText, const char *msg) {
+  if (errorText) std::snprintf(errorText, 256, "%s", msg);
+}
+
+template <int MB, int OUT>
+int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmParams &p, int grid, cudaStream_t stream,
+                  char *errorText) {
+  using S = Shape<MB>;
+  auto kernel = matmulBiasActKernel<MB, OUT>;
+  static std::once_flag once;
+  static cudaError_t attrErr = cudaSuccess;
+  std::call_once(once, [&] {
+    attrErr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kSmemBytes));
+  });
+  if (attrErr != cudaSuccess) {
+    fail(errorText, "matmul: cannot reserve shared memory for the operand ring");
+    return static_cast<int>(attrErr);
+  }
+  kernel<<<grid, S::kThreads, S::kSmemBytes, stream>>>(mapA, mapB, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+} // namespace
+
+int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char *errorText) {
   if (launched) *launched = 0;
-  if (errorText) std::snprintf(errorText, 256, "matmul kernel not built yet");
+  if (l.M == 0 || l.N == 0) return 0;
+  if (l.inType != kF16 && l.inType != kBF16) { fail(errorText, "matmul: A and B must be f16 or bf16"); return 1; }
+  if (l.K <= 0) { fail(errorText, "matmul: K must be positive"); return 1; }
+  if (l.K % 8 != 0 || l.N % 8 != 0) {
+    fail(errorText, "matmul: K and N must be multiples of 8 (16-byte rows for the TMA tensor maps)");
+    return 1;
+  }
+  if ((reinterpret_cast<uintptr_t>(l.A) | reinterpret_cast<uintptr_t>(l.B) | reinterpret_cast<uintptr_t>(l.out)) & 15u) {
+    fail(errorText, "matmul: A, B and out must be 16-byte aligned");
+    return 1;
+  }
+  if (l.M >= (1ll << 31) || l.N >= (1ll << 31) || l.K >= (1ll << 31)) { fail(errorText, "matmul: dimension too large"); return 1; }
+  if (l.epilogue != kEpiNone && !l.bias) { fail(errorText, "matmul: the epilogue needs a bias vector"); return 1; }
+
+  int device = 0;
+  cudaGetDevice(&device);
+  const int sms = deviceSmCount(device);
+  // 256-row tiles when they still give every SM work; 128-row tiles otherwise
+  const int64_t tiles256 = ((l.M + 255) / 256) * ((l.N + kBlockN - 1) / kBlockN);
+  const int mb = (l.stages == 1) ? 1 : (l.stages == 2) ? 2 : (tiles256 >= sms ? 2 : 1);
+  const int tileM = 128 * mb;
+
+  const CUtensorMapDataType dt = l.inType == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap mapA, mapB;
+  if (!makeMap2d(&mapA, dt, l.A, static_cast<uint64_t>(l.K), static_cast<uint64_t>(l.M), static_cast<uint64_t>(l.K) * 2, kBlockK,
+                 static_cast<uint32_t>(tileM)) ||
+      !makeMap2d(&mapB, dt, l.B, static_cast<uint64_t>(l.N), static_cast<uint64_t>(l.K), static_cast<uint64_t>(l.N) * 2, 64, kBlockK)) {
+    fail(errorText, "matmul: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)");
+    return 1;
+  }
+
+  GemmParams p = {};
+  p.M = static_cast<int>(l.M);
+  p.N = static_cast<int>(l.N);
+  p.K = static_cast<int>(l.K);
+  p.numTilesM = static_cast<int>((l.M + tileM - 1) / tileM);
+  p.numTilesN = static_cast<int>((l.N + kBlockN - 1) / kBlockN);
+  p.numKBlocks = static_cast<int>((l.K + kBlockK - 1) / kBlockK);
+  p.bias = l.bias;
+  p.out = l.out;
+  p.biasType = l.biasType;
+  p.epilogue = l.epilogue;
+  p.alpha = l.alpha;
+  const unsigned int fmt = l.inType == kF16 ? 0u : 1u;
+  // instruction descriptor: D=f32, A/B format, A K-major, B N-major, N=256, M=128
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) | ((kBlockN >> 3) << 17) | ((128u >> 4) << 24);
+
+  const int64_t numTiles = static_cast<int64_t>(p.numTilesM) * p.numTilesN;
+  int grid = l.gridBlocks > 0 ? l.gridBlocks : sms;
+  grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, numTiles)));
+
+  int rc;
+  if (mb == 1) {
+    rc = l.outType == kF32 ? launchVariant<1, kF32>(mapA, mapB, p, grid, stream, errorText)
+         : l.outType == kF16 ? launchVariant<1, kF16>(mapA, mapB, p, grid, stream, errorText)
+                             : launchVariant<1, kBF16>(mapA, mapB, p, grid, stream, errorText);
+  } else {
+    rc = l.outType == kF32 ? launchVariant<2, kF32>(mapA, mapB, p, grid, stream, errorText)
+         : l.outType == kF16 ? launchVariant<2, kF16>(mapA, mapB, p, grid, stream, errorText)
+                             : launchVariant<2, kBF16>(mapA, mapB, p, grid, stream, errorText);
+  }
+  if (rc == 0 && launched) *launched = 1;
+  return rc;
+}
+
+int matmulCheckStatus(int device, char *errorText) {
+  (void)device;
+  unsigned int status = 0;
+  if (cudaMemcpyFromSymbol(&status, g_matmulStatus, sizeof(status)) != cudaSuccess) return 0;
+  if (status == 0) return 0;
+  const unsigned int zero = 0;
+  cudaMemcpyToSymbol(g_matmulStatus, &zero, sizeof(zero));
+  static const char *roles[] = {"TMA producer", "MMA issuer", "epilogue"};
+  if (errorText)
+    std::snprintf(errorText, 256, "matmul: %s gave up waiting on a pipeline barrier after 2 s (status 0x%x)",
+                  roles[std::min(2u, status & 0xffu)], status);
   return 1;
 }
-int matmulCheckStatus(int, char *) { return 0; }
-}}
+
+} // namespace kernels
+} // namespace afir

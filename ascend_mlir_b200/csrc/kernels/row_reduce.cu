@@ -208,6 +208,10 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
   // team size: enough lanes that each does about one batch of four vectors, at least a warp
   int lanes = 32;
   while (lanes < threads && static_cast<int64_t>(lanes) * 4 < vecPerSlice) lanes <<= 1;
+  if (l.teamLanes >= 32) {
+    lanes = 32;
+    while (lanes * 2 <= l.teamLanes && lanes * 2 <= threads) lanes <<= 1;
+  }
 
   RrParams p = {};
   for (int k = 0; k < l.numViews; ++k) {

@@ -250,6 +250,7 @@ Status parseDescriptorJson(const json::Value &root, LaunchDescriptor &out) {
     out.unrollField = l->getString("unroll");
     out.splitColsField = l->getString("split_cols");
     out.stagesField = l->getString("stages");
+    out.teamLanesField = l->getString("team_lanes");
   }
 
   if (out.kernelClass == KernelClass::Matmul) {

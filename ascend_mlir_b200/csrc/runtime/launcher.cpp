@@ -192,6 +192,7 @@ Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const
   l.out = argAt(args, store);
   l.body = g.body;
   l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
+  l.teamLanes = static_cast<int>(optionalField(d.teamLanesField, tiling));
   int split = static_cast<int>(optionalField(d.splitColsField, tiling));
   if (split <= 0) split = kernels::chooseRowReduceSplit(l.rows, l.cols, kernels::deviceSmCount(args.device));
   l.splitCols = split;
