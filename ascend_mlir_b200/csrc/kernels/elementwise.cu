@@ -238,9 +238,9 @@ int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *laun
   p.numViews = l.numViews;
   p.prog = l.body;
 
-  int threads = l.ctaThreads > 0 ? l.ctaThreads : 256;
+  int threads = l.ctaThreads > 0 ? l.ctaThreads : 128;
   threads = std::max(32, std::min(512, (threads / 32) * 32));
-  int unroll = l.unroll > 0 ? l.unroll : 4;
+  int unroll = l.unroll > 0 ? l.unroll : 2;
   unroll = unroll >= 4 ? 4 : (unroll >= 2 ? 2 : 1);
   const int body = vector ? matchBody(l.body, l.numViews) : kBodyInterpreted;
   if (!vector || body == kBodyInterpreted) unroll = 2;

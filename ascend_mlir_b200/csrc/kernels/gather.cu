@@ -216,7 +216,7 @@ int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched) {
   p.status = l.status;
   p.prog = l.body;
 
-  int threads = l.ctaThreads > 0 ? l.ctaThreads : 256;
+  int threads = l.ctaThreads > 0 ? l.ctaThreads : 128;
   threads = std::max(32, std::min(512, (threads / 32) * 32));
   const int body = matchBody(l.body, l.numViews);
   KernelFn fn;
@@ -228,7 +228,7 @@ int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched) {
       if (l.views[k].colStride == 1) vector = aligned16(l.views[k].base) && l.views[k].rowStride % vecElems == 0;
       else if (l.views[k].colStride != 0) vector = false;
     }
-    int unroll = l.unroll > 0 ? l.unroll : 4;
+    int unroll = l.unroll > 0 ? l.unroll : 1;
     unroll = unroll >= 4 ? 4 : unroll >= 2 ? 2 : 1;
     if (!vector || body == kBodyInterpreted || (body != kBodyCopy && body != kBodyMulAdd && body != kBodyAdd && body != kBodyMul))
       unroll = 2;

@@ -203,7 +203,7 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
     return cudaErrorInvalidValue;
   const int64_t vecPerSlice = (vecPerRow + slices - 1) / slices;
 
-  int threads = l.ctaThreads > 0 ? l.ctaThreads : 256;
+  int threads = l.ctaThreads > 0 ? l.ctaThreads : 128;
   threads = threads >= 512 ? 512 : threads >= 256 ? 256 : threads >= 128 ? 128 : threads >= 64 ? 64 : 32;
   // team size: enough lanes that each does about one batch of four vectors, at least a warp
   int lanes = 32;

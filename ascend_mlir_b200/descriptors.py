@@ -80,7 +80,8 @@ def _spec(name, kernel_class, dtype, num_inputs, num_outputs, tile_params, dims,
                       defaults={p[0]: p[1] for p in tile_params}, magic=magic)
 
 
-_EW_TILE = [("CTA_THREADS", 256, (128, 256, 512)), ("UNROLL", 4, (1, 2, 4))]
+_EW_TILE = [("CTA_THREADS", 128, (128, 256, 512)), ("UNROLL", 2, (1, 2, 4))]
+_GATHER_TILE = [("CTA_THREADS", 128, (128, 256, 512)), ("UNROLL", 1, (1, 2, 4))]
 _EW_LAUNCH = {"cta_threads": "CTA_THREADS", "unroll": "UNROLL"}
 
 
@@ -174,7 +175,7 @@ def transpose_2d(dtype: str = "f16", name: str = "transpose_2d") -> KernelSpec:
 # ---- broadcast + add + row reduction -----------------------------------------------------------------
 def bcast_add_rowsum(dtype: str = "f32", name: str = "broadcast_add_reducesum") -> KernelSpec:
     """out[m] = sum_n (a[m] + b[m,n]) with f32 accumulation."""
-    tile = [("CTA_THREADS", 256, (128, 256, 512)), ("TEAM_LANES", 0, (0, 32, 64, 128, 256)), ("SPLIT_N", 0, (0,))]
+    tile = [("CTA_THREADS", 128, (128, 256, 512)), ("TEAM_LANES", 0, (0, 32, 64, 128, 256)), ("SPLIT_N", 0, (0,))]
     dims = [("dim_arg0_0", "M"), ("dim_arg1_1", "N")]
     dom = ["dim_arg0_0", "dim_arg1_1"]
     body = {"domain": dom,
@@ -196,7 +197,7 @@ def gather_rows_scale_resid(dtype: str = "bf16", index_dtype: str = "i32", name:
             "gather": {"axis": 0, "indices": {"arg": 1, "dtype": index_dtype, "shape": ["dim_arg1_0"]}},
             "store": {"arg": 4, "shape": dom, "map": [0, 1]},
             "body": [op("mulf", "v0", "v1"), op("addf", "%0", "v2")]}
-    return _spec(name, "gather", dtype, 4, 1, _EW_TILE, dims, body, _EW_LAUNCH)
+    return _spec(name, "gather", dtype, 4, 1, _GATHER_TILE, dims, body, _EW_LAUNCH)
 
 
 def relu_gather_cols_bias(dtype: str = "f16", index_dtype: str = "i64", name: str = "relu_index_select_add") -> KernelSpec:
@@ -208,7 +209,7 @@ def relu_gather_cols_bias(dtype: str = "f16", index_dtype: str = "i64", name: st
             "gather": {"axis": 1, "indices": {"arg": 1, "dtype": index_dtype, "shape": ["dim_arg1_0"]}},
             "store": {"arg": 3, "shape": dom, "map": [0, 1]},
             "body": [op("maximumf", "v0", 0.0), op("addf", "%0", "v1")]}
-    return _spec(name, "gather", dtype, 3, 1, _EW_TILE, dims, body, _EW_LAUNCH)
+    return _spec(name, "gather", dtype, 3, 1, _GATHER_TILE, dims, body, _EW_LAUNCH)
 
 
 # ---- matmul + bias + LeakyReLU -----------------------------------------------------------------------------

@@ -236,3 +236,89 @@ def test_run_file_matches_run(rt, tmp_path):
     out = w.new_output()
     rt.run_file(str(p), w.spec.name, w.inputs, [out], w.tiling())
     assert np.array_equal(out, oracle.add_mul_f32(*w.inputs))
+
+
+# ---- matmul + bias + LeakyReLU (tcgen05) ---------------------------------------------------------------------
+def _matmul_check(rt, M, N, K, mb, seed=0):
+    w = configs.matmul_add_leakyrelu(M, N, K, seed=seed)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape, STAGES=mb)
+    got = oracle.bf16_to_f32(out)
+    want = oracle.bf16_to_f32(oracle.matmul_bias_leakyrelu_bf16(*w.inputs, 0.01))
+    # bar: relative error <= 1e-2 (bf16 output rounding alone is 2^-9); tiny absolute floor for values near zero
+    assert np.all(np.abs(got - want) <= 1e-2 * np.abs(want) + 1e-3)
+    # and tight in aggregate: at most one bf16 ulp apart almost everywhere
+    assert np.mean(np.abs(got - want) <= 2.0 ** -8 * np.abs(want) + 1e-6) > 0.999
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 320), (100, 136, 72), (1, 8, 8),
+                                   (130, 264, 1032), (1024, 1024, 1024)])
+@pytest.mark.parametrize("mb", [1, 2])
+def test_matmul_bias_leakyrelu_bf16(rt, M, N, K, mb):
+    _matmul_check(rt, M, N, K, mb, seed=M + N + K)
+
+
+def test_matmul_many_tiles_per_cta(rt):
+    # more tiles than SMs: every CTA walks several tiles, both TMEM accumulators and all ring phases wrap
+    _matmul_check(rt, 2048, 4096, 512, 1, seed=21)
+    _matmul_check(rt, 4096, 4096, 256, 2, seed=22)
+
+
+def test_reference_matmul_example_golden_max_abs_diff_zero(rt, golden_dir):
+    g = dict(np.load(golden_dir / "matmul_add_leakyrelu.npz"))
+    spec = descriptors.matmul_bias_leakyrelu("f16", "f32", "f32", alpha=0.001)
+    M, K = g["input_a"].shape
+    N = g["input_b"].shape[1]
+    out = run(rt, spec, [g["input_a"], g["input_b"], g["input_bias"]], np.zeros((M, N), np.float32), {"M": M, "N": N, "K": K})
+    # integer-valued operands: every partial sum is exact, so the tensor-core result equals the golden
+    # wherever the epilogue is the identity, and differs by one f32 rounding of alpha*x elsewhere
+    pos = g["output"] >= 0
+    assert np.array_equal(out[pos], g["output"][pos])
+    assert np.max(np.abs(out - g["output"])) <= 1e-6 * np.max(np.abs(g["output"]))
+    want = oracle.matmul_bias_leakyrelu_f16_f32(g["input_a"], g["input_b"], g["input_bias"], 0.001)
+    assert np.array_equal(out, want)  # against the oracle (same f32 alpha): max_abs_diff == 0
+
+
+@pytest.mark.parametrize("epilogue", ["None", "BiasAdd", "BiasAddRelu"])
+def test_matmul_other_epilogues(rt, epilogue):
+    rng = np.random.default_rng(23)
+    M, N, K = 192, 320, 128
+    A = rng.integers(-4, 5, (M, K)).astype(np.float16)
+    B = rng.integers(-4, 5, (K, N)).astype(np.float16)
+    bias = rng.integers(-8, 9, N).astype(np.float32)
+    spec = descriptors.matmul_bias_leakyrelu("f16", "f32", "f32", alpha=0.0, epilogue=epilogue)
+    out = run(rt, spec, [A, B, bias], np.zeros((M, N), np.float32), {"M": M, "N": N, "K": K})
+    x = A.astype(np.float32) @ B.astype(np.float32)
+    if epilogue != "None":
+        x = x + bias
+    if epilogue == "BiasAddRelu":
+        x = np.maximum(x, 0)
+    assert np.array_equal(out, x)
+
+
+def test_matmul_refuses_rows_tma_cannot_address(rt):
+    w = configs.matmul_add_leakyrelu(64, 64, 36)
+    with pytest.raises(ExecutorError, match="multiples of 8"):
+        rt.run(w.spec.binary, w.spec.name, w.inputs, [w.new_output()], w.tiling())
+
+
+def test_matmul_linearity_at_scale(rt):
+    # size-independent property at a size the CPU oracle would take minutes for:
+    # with epilogue None, (2A).B == 2 (A.B) exactly (power-of-two scaling commutes with every rounding)
+    rng = np.random.default_rng(24)
+    M = N = K = 2048
+    A = configs.f32_to_bf16_bits(rng.standard_normal((M, K), dtype=np.float32) * np.float32(0.02))
+    B = configs.f32_to_bf16_bits(rng.standard_normal((K, N), dtype=np.float32) * np.float32(0.02))
+    A2 = configs.f32_to_bf16_bits(configs.bf16_bits_to_f32(A) * np.float32(2))
+    bias = np.zeros(N, np.uint16)
+    spec = descriptors.matmul_bias_leakyrelu("bf16", "bf16", "bf16", alpha=0.0, epilogue="None")
+    shape = {"M": M, "N": N, "K": K}
+    o1 = run(rt, spec, [A, B, bias], np.zeros((M, N), np.uint16), shape)
+    o2 = run(rt, spec, [A2, B, bias], np.zeros((M, N), np.uint16), shape)
+    assert np.array_equal(configs.bf16_bits_to_f32(o2), configs.bf16_bits_to_f32(o1) * np.float32(2))
+    # sampled f64 check of the fused form
+    w_bias = configs.f32_to_bf16_bits(rng.standard_normal(N, dtype=np.float32) * np.float32(0.1))
+    spec2 = descriptors.matmul_bias_leakyrelu()
+    o3 = configs.bf16_bits_to_f32(run(rt, spec2, [A, B, w_bias], np.zeros((M, N), np.uint16), shape))
+    for m, n in rng.integers(0, M, (64, 2)):
+        want = oracle.matmul_bias_leakyrelu_bf16_at(A, B, w_bias, 0.01, int(m), int(n))
+        assert abs(o3[m, n] - want) <= 1e-2 * abs(want) + 1e-3
