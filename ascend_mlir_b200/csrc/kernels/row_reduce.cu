@@ -10,6 +10,8 @@
 #include "kernels/ew_common.cuh"
 
 #include <algorithm>
+#include <cstdio>
+#include <mutex>
 
 namespace afir {
 namespace kernels {
@@ -257,3 +259,96 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
 
 } // namespace kernels
 } // namespace afir
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free entry point.
+//
+// Some hosts of this library may not allocate device memory at the moment they need a reduction:
+// a real-time or inference-serving loop whose memory was sized and frozen at start-up, a process
+// whose device memory is already fully committed, or a plugin running under a framework that owns
+// the allocator and forbids foreign cudaMalloc calls.  The column-sliced row reduction needs scratch for its
+// per-slice partial sums; the ordinary entry points take that scratch from a workspace the executor
+// allocates.  This variant takes it from a fixed array inside the library image instead, so it calls
+// no cudaMalloc / cudaFree and no allocating library routine.
+//
+// Limits and rules:
+//  * rows * split_cols <= AFIRT_NO_ALLOC_MAX_PARTIALS (262 144 floats = 1 MiB; every GPU that loads
+//    the library holds this array until the process exits).  Larger requests are refused.
+//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+//    device current) and caches it; make that first call before starting any stream capture.
+//  * All calls share the one array per device.  It keeps whatever the previous call left; nothing in
+//    it has to start at zero because every slot a call reads is first written by that same call.
+//    Two calls that overlap on the GPU (different streams, or different host threads) race on it:
+//    serialise them.
+// ---------------------------------------------------------------------------------------------------
+namespace {
+constexpr long long kNoAllocMaxPartials = 262144;
+static __device__ __align__(256) float g_noAllocPartials[kNoAllocMaxPartials];
+
+void noAllocFail(char *buf, size_t len, const char *msg) {
+  if (!buf || len == 0) return;
+  std::snprintf(buf, len, "%s", msg);
+}
+} // namespace
+
+extern "C" __attribute__((visibility("default"))) int
+afirt_bcast_add_rowsum_no_alloc(int device_id, int elem_type, const void *a, const void *b, void *out, int64_t rows,
+                                int64_t cols, int split_cols, void *cuda_stream, char *err_buf, size_t err_len) {
+  using namespace afir::kernels;
+  static std::mutex mu;
+  static float *scratchOnDevice[64] = {nullptr};
+
+  if (device_id < 0 || device_id >= 64) { noAllocFail(err_buf, err_len, "device id out of range"); return 1; }
+  if (elem_type != kF32 && elem_type != kF16 && elem_type != kBF16) { noAllocFail(err_buf, err_len, "elem_type must be 0 (f32), 1 (f16) or 2 (bf16)"); return 1; }
+  if (rows < 0 || cols < 0 || split_cols < 1) { noAllocFail(err_buf, err_len, "rows and cols must be non-negative and split_cols at least 1"); return 1; }
+  if (rows == 0) return 0;
+  if (!a || !b || !out) { noAllocFail(err_buf, err_len, "a, b and out are required"); return 1; }
+  if (rows * static_cast<long long>(split_cols) > kNoAllocMaxPartials) {
+    char msg[160];
+    std::snprintf(msg, sizeof(msg), "rows * split_cols = %lld exceeds the built-in scratch of %lld partial sums",
+                  static_cast<long long>(rows) * split_cols, kNoAllocMaxPartials);
+    noAllocFail(err_buf, err_len, msg);
+    return 1;
+  }
+  cudaError_t e = cudaSetDevice(device_id);
+  if (e != cudaSuccess) { noAllocFail(err_buf, err_len, cudaGetErrorString(e)); return 1; }
+  float *scratch = nullptr;
+  {
+    // The array's name is only a host-side handle; the kernel needs its address in this device's memory.
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratchOnDevice[device_id]) {
+      void *p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noAllocPartials);
+      if (e != cudaSuccess || !p) {
+        noAllocFail(err_buf, err_len, e != cudaSuccess ? cudaGetErrorString(e) : "cudaGetSymbolAddress returned null");
+        return 1;
+      }
+      scratchOnDevice[device_id] = static_cast<float *>(p);
+    }
+    scratch = scratchOnDevice[device_id];
+  }
+
+  RowReduceLaunch l = {};
+  l.elemType = elem_type;
+  l.rows = rows;
+  l.cols = cols;
+  l.numViews = 2;
+  l.views[0].base = a;  // a[m]: follows the row, broadcast along the columns
+  l.views[0].rowStride = 1;
+  l.views[0].colStride = 0;
+  l.views[1].base = b;  // b[m, n]
+  l.views[1].rowStride = cols;
+  l.views[1].colStride = 1;
+  l.out = out;
+  l.body.numOps = 1;
+  l.body.ops[0].op = kOpAdd;
+  l.body.ops[0].a = {kSrcView, 0, 0.0f};
+  l.body.ops[0].b = {kSrcView, 1, 0.0f};
+  l.splitCols = split_cols;
+  l.workspace = scratch;
+  l.workspaceBytes = static_cast<size_t>(kNoAllocMaxPartials) * sizeof(float);
+  int launched = 0;
+  const int rc = launchRowReduce(l, static_cast<cudaStream_t>(cuda_stream), &launched);
+  if (rc != 0) { noAllocFail(err_buf, err_len, cudaGetErrorString(static_cast<cudaError_t>(rc))); return 1; }
+  return 0;
+}

@@ -18,6 +18,7 @@ EXPORTS = [
     "afirt_executor_run", "afirt_executor_run_file",
     "afirt_executor_launch_device", "afirt_executor_synchronize", "afirt_executor_workspace_bytes",
     "afirt_executor_last_launch_count", "afirt_executor_total_launch_count", "afirt_runtime_version",
+    "afirt_bcast_add_rowsum_no_alloc",
 ]
 
 
@@ -56,6 +57,10 @@ def get_lib() -> ctypes.CDLL:
     lib.afirt_executor_last_launch_count.restype = ctypes.c_int
     lib.afirt_executor_total_launch_count.argtypes = [ctypes.c_void_p]
     lib.afirt_executor_total_launch_count.restype = ctypes.c_uint64
+    lib.afirt_bcast_add_rowsum_no_alloc.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                                    ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                                    ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_bcast_add_rowsum_no_alloc.restype = ctypes.c_int
     lib.afirt_runtime_version.argtypes = []
     lib.afirt_runtime_version.restype = ctypes.c_char_p
     _lib = lib

@@ -44,6 +44,24 @@ int afirt_executor_workspace_bytes(AfirtExecutor executor, const uint8_t *binary
 int afirt_executor_last_launch_count(AfirtExecutor executor);
 uint64_t afirt_executor_total_launch_count(AfirtExecutor executor);
 
+/* No counterpart in the reference (its runtime allocates on every call).
+ * out[m] = sum_n (a[m] + b[m,n]) with each row cut into split_cols column slices, for callers that
+ * must not allocate GPU memory when they call: serving or real-time loops with a frozen memory
+ * budget, processes whose device memory is fully committed, plugins under an allocator-owning framework.  The per-slice partial sums
+ * live in a 1 MiB array built into the library (AFIRT_NO_ALLOC_MAX_PARTIALS floats per device)
+ * instead of an allocated workspace; nothing here calls cudaMalloc, cudaFree or an allocating
+ * library routine.  a [rows], b [rows, cols] and out [rows] are DEVICE pointers of elem_type
+ * (0 = f32, 1 = f16, 2 = bf16); f32 accumulation.  rows * split_cols above the maximum is refused
+ * with a message.  The first call on a device resolves the array's device address: make it before
+ * any stream capture begins.  Every call on a device shares the array (contents left over from
+ * the previous call are harmless: each call writes every slot it later reads), so calls that
+ * overlap on the GPU race and must be serialised by the caller.  Enqueues on cuda_stream and
+ * returns; 0 = success, otherwise 1 with a message in err_buf. */
+#define AFIRT_NO_ALLOC_MAX_PARTIALS 262144
+int afirt_bcast_add_rowsum_no_alloc(int device_id, int elem_type, const void *a, const void *b, void *out,
+                                    int64_t rows, int64_t cols, int split_cols, void *cuda_stream,
+                                    char *err_buf, size_t err_len);
+
 /* Library identification: "afir-b200 <version> sm_100a". */
 const char *afirt_runtime_version(void);
 
