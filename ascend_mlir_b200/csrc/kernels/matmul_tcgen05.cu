@@ -159,46 +159,57 @@ __device__ __forceinline__ unsigned long long smemDesc(unsigned int addr, unsign
   return d;
 }
 
-__device__ __forceinline__ float loadBias(const void *bias, int type, int n) {
-  if (type == kF32) return __ldg(static_cast<const float *>(bias) + n);
-  if (type == kF16) return __half2float(__ldg(static_cast<const __half *>(bias) + n));
-  return __bfloat162float(__ldg(static_cast<const __nv_bfloat16 *>(bias) + n));
+// Eight consecutive bias values as f32 (n is a multiple of 8: 16-byte aligned for 16-bit types).
+__device__ __forceinline__ void loadBias8(const void *bias, int type, int n, float (&b)[8]) {
+  if (type == kF32) {
+    const float4 lo = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(bias) + n));
+    const float4 hi = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(bias) + n) + 1);
+    b[0] = lo.x; b[1] = lo.y; b[2] = lo.z; b[3] = lo.w; b[4] = hi.x; b[5] = hi.y; b[6] = hi.z; b[7] = hi.w;
+    return;
+  }
+  const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(static_cast<const unsigned short *>(bias) + n));
+  const unsigned int w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (type == kF16) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+      b[2 * i] = f.x;
+      b[2 * i + 1] = f.y;
+    } else {
+      b[2 * i] = __uint_as_float(w[i] << 16);
+      b[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
 }
 
+// Eight f32 results -> 16-byte pieces of the output row (two pieces for f32, one for 16-bit types).
 template <int OUT> struct OutPack;
 template <> struct OutPack<kF32> {
   static constexpr int kBytes = 4;
-  // 8 consecutive columns -> two 16-byte stores
-  __device__ __forceinline__ static void store8(void *dst, const float *v) {
-    float4 *p = static_cast<float4 *>(dst);
-    p[0] = make_float4(v[0], v[1], v[2], v[3]);
-    p[1] = make_float4(v[4], v[5], v[6], v[7]);
+  static constexpr int kPieces = 2;
+  __device__ __forceinline__ static void pack8(const float *v, uint4 *q) {
+    q[0] = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    q[1] = make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7]));
   }
 };
 template <> struct OutPack<kBF16> {
   static constexpr int kBytes = 2;
-  __device__ __forceinline__ static void store8(void *dst, const float *v) {
+  static constexpr int kPieces = 1;
+  __device__ __forceinline__ static void pack8(const float *v, uint4 *q) {
     __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
     __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
-    uint4 u;
-    u.x = *reinterpret_cast<unsigned int *>(&a);
-    u.y = *reinterpret_cast<unsigned int *>(&b);
-    u.z = *reinterpret_cast<unsigned int *>(&c);
-    u.w = *reinterpret_cast<unsigned int *>(&d);
-    *static_cast<uint4 *>(dst) = u;
+    q[0] = make_uint4(*reinterpret_cast<unsigned int *>(&a), *reinterpret_cast<unsigned int *>(&b),
+                      *reinterpret_cast<unsigned int *>(&c), *reinterpret_cast<unsigned int *>(&d));
   }
 };
 template <> struct OutPack<kF16> {
   static constexpr int kBytes = 2;
-  __device__ __forceinline__ static void store8(void *dst, const float *v) {
+  static constexpr int kPieces = 1;
+  __device__ __forceinline__ static void pack8(const float *v, uint4 *q) {
     __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
     __half2 c = __floats2half2_rn(v[4], v[5]), d = __floats2half2_rn(v[6], v[7]);
-    uint4 u;
-    u.x = *reinterpret_cast<unsigned int *>(&a);
-    u.y = *reinterpret_cast<unsigned int *>(&b);
-    u.z = *reinterpret_cast<unsigned int *>(&c);
-    u.w = *reinterpret_cast<unsigned int *>(&d);
-    *static_cast<uint4 *>(dst) = u;
+    q[0] = make_uint4(*reinterpret_cast<unsigned int *>(&a), *reinterpret_cast<unsigned int *>(&b),
+                      *reinterpret_cast<unsigned int *>(&c), *reinterpret_cast<unsigned int *>(&d));
   }
 };
 
@@ -219,7 +230,9 @@ template <int MB> struct Shape {
   static constexpr int kStages = MB == 1 ? 4 : 3;
   static constexpr int kEpilogueWarps = 4 * MB;
   static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
-  static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + sizeof(Control<kStages>);
+  static constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;  // per warp: 32 rows x 128 bytes
+  static constexpr size_t kSmemBytes =
+      1024 + static_cast<size_t>(kStages) * kStageBytes + kStagingBytes + sizeof(Control<kStages>);
 };
 
 template <int MB, int OUT>
@@ -231,7 +244,8 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   extern __shared__ unsigned char smemRaw[];
   // 128-byte-swizzled tiles want 1024-byte alignment
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
-  Control<STAGES> *ctl = reinterpret_cast<Control<STAGES> *>(smem + static_cast<size_t>(STAGES) * S::kStageBytes);
+  unsigned char *staging = smem + static_cast<size_t>(STAGES) * S::kStageBytes;
+  Control<STAGES> *ctl = reinterpret_cast<Control<STAGES> *>(staging + S::kStagingBytes);
   volatile int *abortFlag = &ctl->abortFlag;
 
   const int warp = threadIdx.x >> 5;
@@ -358,30 +372,56 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       const unsigned int use = MB == 1 ? (tileIter >> 1) : tileIter;
       if (!mbarWait(smemAddr(&ctl->tmemFull[acc]), use & 1u, abortFlag, 2)) { ok = false; break; }
       tcgen05FenceAfter();
-      const int row = tm * S::kTileM + half * 128 + quarter * 32 + lane;
+      // Each thread owns one accumulator row.  A 128-byte slice of 32 rows is converted and parked in
+      // this warp's shared-memory staging area (16-byte pieces XOR-swizzled by row so both phases are
+      // bank-conflict free), then written out with 8 lanes per row: every warp store covers four
+      // full 128-byte lines of the output instead of 32 scattered 16-byte pieces.
+      constexpr int kColsPerSlice = 128 / OutPack<OUT>::kBytes;  // 64 (16-bit) or 32 (f32)
+      const int rowBase = tm * S::kTileM + half * 128 + quarter * 32;
       const unsigned int taddr = tmemBase + static_cast<unsigned int>(acc * kBlockN) + (static_cast<unsigned int>(quarter * 32) << 16);
-      unsigned char *outRow = static_cast<unsigned char *>(prm.out) + static_cast<size_t>(row) * prm.N * OutPack<OUT>::kBytes;
+      unsigned char *stg = staging + ew * (32 * 128);
 #pragma unroll 1
-      for (int c = 0; c < kBlockN; c += 32) {
-        unsigned int r[32];
-        tmemLoad32(taddr + c, r);
-        tmemLoadWait();
-        const int n0 = tn * kBlockN + c;
+      for (int c = 0; c < kBlockN; c += kColsPerSlice) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          float v[8];
+        for (int hh = 0; hh < kColsPerSlice / 32; ++hh) {
+          unsigned int r[32];
+          tmemLoad32(taddr + c + hh * 32, r);
+          tmemLoadWait();
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            float x = __uint_as_float(r[j + e]);
-            const int n = n0 + j + e;
-            if (prm.epilogue != kEpiNone && n < prm.N) x += loadBias(prm.bias, prm.biasType, n);
-            if (prm.epilogue == kEpiBiasAddLeakyRelu) x = fmaxf(x, x * prm.alpha);
-            else if (prm.epilogue == kEpiBiasAddRelu) x = fmaxf(x, 0.0f);
-            v[e] = x;
+          for (int j = 0; j < 4; ++j) {
+            const int n = tn * kBlockN + c + hh * 32 + j * 8;
+            float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (prm.epilogue != kEpiNone && n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float x = __uint_as_float(r[j * 8 + e]) + bv[e];
+              if (prm.epilogue == kEpiBiasAddLeakyRelu) x = fmaxf(x, x * prm.alpha);
+              else if (prm.epilogue == kEpiBiasAddRelu) x = fmaxf(x, 0.0f);
+              v[e] = x;
+            }
+            uint4 q[OutPack<OUT>::kPieces];
+            OutPack<OUT>::pack8(v, q);
+#pragma unroll
+            for (int pce = 0; pce < OutPack<OUT>::kPieces; ++pce) {
+              const int piece = (hh * 4 + j) * OutPack<OUT>::kPieces + pce;  // 0..7 within the 128-byte slice
+              *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = q[pce];
+            }
           }
-          if (row < prm.M && n0 + j < prm.N)  // N is a multiple of 8: whole 8-column groups are in or out
-            OutPack<OUT>::store8(outRow + static_cast<size_t>(n0 + j) * OutPack<OUT>::kBytes, v);
         }
+        __syncwarp();
+        const int piece = lane & 7;
+        const int ncol = tn * kBlockN + c + piece * (16 / OutPack<OUT>::kBytes);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = i * 4 + (lane >> 3);
+          const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((piece ^ (rr & 7)) << 4));
+          const int grow = rowBase + rr;
+          if (grow < prm.M && ncol < prm.N)  // N is a multiple of 8: a 16-byte piece is wholly inside or outside
+            *reinterpret_cast<uint4 *>(static_cast<unsigned char *>(prm.out) +
+                                       (static_cast<size_t>(grow) * prm.N + ncol) * OutPack<OUT>::kBytes) = val;
+        }
+        __syncwarp();
       }
       tcgen05FenceBefore();
       __syncwarp();
