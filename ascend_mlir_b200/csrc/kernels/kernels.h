@@ -102,10 +102,15 @@ struct RowReduceLaunch {
   void *workspace;  // device scratch, at least rowReduceWorkspaceBytes(...) when splitCols > 1
   size_t workspaceBytes;
   int gridBlocks;
+  int streamStages;      // staged variant: ring depth per warp (0 = default)
+  int streamChunkBytes;  // staged variant: bytes per stage (0 = default)
+  int forcePlainLoads;  // 1 = never use the bulk-copy staged variant (tuning / comparison)
 };
 size_t rowReduceWorkspaceBytes(int64_t rows, int splitCols);
 int chooseRowReduceSplit(int64_t rows, int64_t cols, int smCount);
 int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched);
+// After the stream has been synchronised: non-zero when a staged-copy wait gave up.
+int rowReduceCheckStatus(int device, char *errorText);
 
 // ---------------------------------------------------------------------------------------------
 // Gather + elementwise.  axis 0 (row gather, "embedding"): g(i,j) = table[idx[i], j];

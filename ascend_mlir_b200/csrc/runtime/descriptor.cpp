@@ -251,6 +251,9 @@ Status parseDescriptorJson(const json::Value &root, LaunchDescriptor &out) {
     out.splitColsField = l->getString("split_cols");
     out.stagesField = l->getString("stages");
     out.teamLanesField = l->getString("team_lanes");
+    out.bulkCopyField = l->getString("bulk_copy");
+    out.streamStagesField = l->getString("stream_stages");
+    out.streamChunkField = l->getString("stream_chunk_bytes");
   }
 
   if (out.kernelClass == KernelClass::Matmul) {

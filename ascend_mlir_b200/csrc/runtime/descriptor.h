@@ -72,7 +72,7 @@ struct LaunchDescriptor {
   std::vector<GroupSpec> groups;
   MatmulSpec matmul;
   // names of the tiling fields carrying B200 launch parameters (empty = library default)
-  std::string ctaThreadsField, unrollField, splitColsField, stagesField, teamLanesField;
+  std::string ctaThreadsField, unrollField, splitColsField, stagesField, teamLanesField, bulkCopyField, streamStagesField, streamChunkField;
   size_t tilingBytes() const;
 };
 

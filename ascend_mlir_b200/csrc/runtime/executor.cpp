@@ -163,6 +163,7 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   statusPending_ = info.usesStatusBlock;
   statusWorkspace_ = workspace_.ptr;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
+  reducePending_ = desc->kernelClass == KernelClass::RowReduce;
   return synchronize(stream_);
 }
 
@@ -207,6 +208,7 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   statusPending_ = info.usesStatusBlock;
   statusWorkspace_ = args.workspace;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
+  reducePending_ = desc->kernelClass == KernelClass::RowReduce;
   return Status::success();
 }
 
@@ -223,6 +225,12 @@ Status CudaExecutor::synchronize(void *stream) {
     e = cudaMemcpy(&bad, statusWorkspace_, sizeof(bad), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] status read failed");
     if (bad) return Status::error("[cuda:kernel_launch] gather index out of range (" + std::to_string(bad) + " indices)");
+  }
+  if (reducePending_) {
+    reducePending_ = false;
+    char text[256] = {0};
+    if (kernels::rowReduceCheckStatus(device_, text) != 0)
+      return Status::error(std::string("[cuda:kernel_launch] ") + (text[0] ? text : "row reduction reported a wait timeout"));
   }
   if (matmulPending_) {
     matmulPending_ = false;

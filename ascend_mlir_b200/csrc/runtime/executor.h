@@ -75,6 +75,7 @@ private:
   bool statusPending_ = false;
   void *statusWorkspace_ = nullptr;
   bool matmulPending_ = false;
+  bool reducePending_ = false;
 };
 
 } // namespace afir

@@ -193,6 +193,12 @@ Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const
   l.body = g.body;
   l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
   l.teamLanes = static_cast<int>(optionalField(d.teamLanesField, tiling));
+  l.streamStages = static_cast<int>(optionalField(d.streamStagesField, tiling));
+  l.streamChunkBytes = static_cast<int>(optionalField(d.streamChunkField, tiling));
+  if (!d.bulkCopyField.empty()) {
+    auto it = tiling.find(d.bulkCopyField);
+    if (it != tiling.end() && it->second == 0) l.forcePlainLoads = 1;
+  }
   int split = static_cast<int>(optionalField(d.splitColsField, tiling));
   if (split <= 0) split = kernels::chooseRowReduceSplit(l.rows, l.cols, kernels::deviceSmCount(args.device));
   l.splitCols = split;

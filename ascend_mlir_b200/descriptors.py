@@ -175,14 +175,16 @@ def transpose_2d(dtype: str = "f16", name: str = "transpose_2d") -> KernelSpec:
 # ---- broadcast + add + row reduction -----------------------------------------------------------------
 def bcast_add_rowsum(dtype: str = "f32", name: str = "broadcast_add_reducesum") -> KernelSpec:
     """out[m] = sum_n (a[m] + b[m,n]) with f32 accumulation."""
-    tile = [("CTA_THREADS", 128, (128, 256, 512)), ("TEAM_LANES", 0, (0, 32, 64, 128, 256)), ("SPLIT_N", 0, (0,))]
+    tile = [("CTA_THREADS", 0, (0, 128, 256, 512)), ("TEAM_LANES", 0, (0, 32, 64, 128, 256)), ("SPLIT_N", 0, (0,)),
+            ("BULK_COPY", 1, (1, 0)), ("STREAM_STAGES", 0, (0, 4, 6, 8)), ("STREAM_CHUNK", 0, (0, 2048, 4096, 8192))]
     dims = [("dim_arg0_0", "M"), ("dim_arg1_1", "N")]
     dom = ["dim_arg0_0", "dim_arg1_1"]
     body = {"domain": dom,
             "loads": [{"arg": 0, "shape": ["dim_arg0_0"], "map": [0]}, {"arg": 1, "shape": dom, "map": [0, 1]}],
             "store": {"arg": 2, "shape": ["dim_arg0_0"], "map": [0]},
             "body": [op("addf", "v0", "v1")]}
-    return _spec(name, "row_reduce", dtype, 2, 1, tile, dims, body, {"cta_threads": "CTA_THREADS", "team_lanes": "TEAM_LANES", "split_cols": "SPLIT_N"})
+    return _spec(name, "row_reduce", dtype, 2, 1, tile, dims, body, {"cta_threads": "CTA_THREADS", "team_lanes": "TEAM_LANES", "split_cols": "SPLIT_N", "bulk_copy": "BULK_COPY", "stream_stages": "STREAM_STAGES",
+                  "stream_chunk_bytes": "STREAM_CHUNK"})
 
 
 # ---- gather + elementwise --------------------------------------------------------------------------------

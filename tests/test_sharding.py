@@ -1,0 +1,104 @@
+"""Row sharding of the fused groups (no collective on the data path) and the cross-rank bookkeeping,
+exercised with world_size-2 gloo ranks on CPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from ascend_mlir_b200 import configs
+from ascend_mlir_b200.configs import row_range
+from oracle import oracle
+
+
+@pytest.mark.parametrize("total,world", [(8192, 8), (10, 4), (3, 8), (0, 2), (32, 1), (262144, 3)])
+def test_row_range_is_a_balanced_contiguous_partition(total, world):
+    ranges = [row_range(total, r, world) for r in range(world)]
+    assert ranges[0][0] == 0 and ranges[-1][1] == total
+    for (a0, a1), (b0, b1) in zip(ranges, ranges[1:]):
+        assert a1 == b0
+    sizes = [b - a for a, b in ranges]
+    assert max(sizes) - min(sizes) <= 1
+
+
+def _oracle_out(w):
+    n = w.name
+    if n == "elementwise_chain":
+        return oracle.add_mul_f32(*w.inputs)
+    if n == "split_relu_broadcast_add_mul":
+        return oracle.split_relu_bias_mul_f16(w.inputs[0], w.inputs[1], 1).view(np.uint16)
+    if n == "broadcast_add_reduce":
+        return oracle.bcast_add_rowsum_f32(w.inputs[0], w.inputs[1])
+    if n == "gather_elementwise":
+        return oracle.gather_rows_scale_resid_bf16(*w.inputs)
+    return oracle.matmul_bias_leakyrelu_bf16(*w.inputs, 0.01)
+
+
+SMALL = {
+    "elementwise_chain": dict(M=37, N=64),
+    "split_relu_broadcast_add_mul": dict(B=5, R=16, C=32),
+    "broadcast_add_reduce": dict(M=29, N=128),
+    "gather_elementwise": dict(table_rows=200, width=32, rows=45),
+    "matmul_add_leakyrelu": dict(M=21, N=32, K=40),
+}
+
+
+@pytest.mark.parametrize("name", list(SMALL))
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_shards_reassemble_to_the_unsharded_result(name, world):
+    full = configs.CONFIGS[name](**SMALL[name])
+    want = _oracle_out(full)
+    parts = []
+    units = 0
+    for r in range(world):
+        s = full.shard(r, world)
+        units += s.units
+        assert s.spec is full.spec  # same kernel binary on every rank; only TilingData dims differ
+        parts.append(_oracle_out(s).reshape((s.units,) + want.shape[1:]))
+    assert units == full.units
+    assert np.array_equal(np.concatenate(parts, axis=0), want)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ascend_mlir_b200 import sharding
+        full = configs.broadcast_add_reduce(M=30, N=64, seed=0)
+        mine = full.shard(rank, world)
+        out = oracle.bcast_add_rowsum_f32(mine.inputs[0], mine.inputs[1])
+        # every rank reports its own fake step time; the job time is the slowest rank's
+        rate, ms = sharding.job_throughput(mine.algorithmic_bytes, 1.0 + rank)
+        assert sharding.world() == (rank, world)
+        q.put((rank, out, rate, ms, mine.algorithmic_bytes))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_shard_without_a_data_collective():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted((q.get(timeout=120) for _ in procs), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    full = configs.broadcast_add_reduce(M=30, N=64, seed=0)
+    want = oracle.bcast_add_rowsum_f32(full.inputs[0], full.inputs[1])
+    assert np.array_equal(np.concatenate([g[1] for g in got]), want)
+    total_bytes = sum(g[4] for g in got)
+    for _, _, rate, ms, _ in got:
+        assert ms == 2.0  # max over ranks of (1.0, 2.0)
+        assert rate == pytest.approx(total_bytes / 2e-3)
