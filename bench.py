@@ -121,7 +121,10 @@ def work_of(w):
 
 
 def time_cpu(name: str, steps: int, warmup: int):
+    # torchrun exports OMP_NUM_THREADS=1; the CPU leg is meant to use every host core
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from oracle import oracle
+    oracle.set_num_threads(os.cpu_count() or 1)
     w, fn, sample = cpu_sample(name)
     for _ in range(max(1, min(warmup, 1))):
         fn()

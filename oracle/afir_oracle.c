@@ -112,6 +112,13 @@ AFO_EXPORT void afo_f32_to_bf16(const float *src, uint16_t *dst, int64_t n) {
 AFO_EXPORT void afo_bf16_to_f32(const uint16_t *src, float *dst, int64_t n) {
   for (int64_t i = 0; i < n; ++i) dst[i] = bf16_to_f32(src[i]);
 }
+AFO_EXPORT void afo_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
 AFO_EXPORT int afo_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -42,6 +42,10 @@ def num_threads() -> int:
     return int(lib().afo_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    lib().afo_set_num_threads(ctypes.c_int(n))
+
+
 def _ptr(a: np.ndarray):
     assert a.flags["C_CONTIGUOUS"], "oracle wants C-contiguous arrays"
     return _p(a.ctypes.data)
