@@ -370,45 +370,15 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       tileCoords(t, tm, tn);
       const int acc = MB == 1 ? static_cast<int>(tileIter & 1u) : half;
       const unsigned int use = MB == 1 ? (tileIter >> 1) : tileIter;
-      if (!mbarWait(smemAddr(&ctl->tmemFull[acc]), use & 1u, abortFlag, 2)) { ok = false; break; }
-      tcgen05FenceAfter();
-      // Each thread owns one accumulator row.  A 128-byte slice of 32 rows is converted and parked in
-      // this warp's shared-memory staging area (16-byte pieces XOR-swizzled by row so both phases are
-      // bank-conflict free), then written out with 8 lanes per row: every warp store covers four
-      // full 128-byte lines of the output instead of 32 scattered 16-byte pieces.
       constexpr int kColsPerSlice = 128 / OutPack<OUT>::kBytes;  // 64 (16-bit) or 32 (f32)
       const int rowBase = tm * S::kTileM + half * 128 + quarter * 32;
       const unsigned int taddr = tmemBase + static_cast<unsigned int>(acc * kBlockN) + (static_cast<unsigned int>(quarter * 32) << 16);
       unsigned char *stg = staging + ew * (32 * 128);
-#pragma unroll 1
-      for (int c = 0; c < kBlockN; c += kColsPerSlice) {
-#pragma unroll
-        for (int hh = 0; hh < kColsPerSlice / 32; ++hh) {
-          unsigned int r[32];
-          tmemLoad32(taddr + c + hh * 32, r);
-          tmemLoadWait();
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int n = tn * kBlockN + c + hh * 32 + j * 8;
-            float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (prm.epilogue != kEpiNone && n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              float x = __uint_as_float(r[j * 8 + e]) + bv[e];
-              if (prm.epilogue == kEpiBiasAddLeakyRelu) x = fmaxf(x, x * prm.alpha);
-              else if (prm.epilogue == kEpiBiasAddRelu) x = fmaxf(x, 0.0f);
-              v[e] = x;
-            }
-            uint4 q[OutPack<OUT>::kPieces];
-            OutPack<OUT>::pack8(v, q);
-#pragma unroll
-            for (int pce = 0; pce < OutPack<OUT>::kPieces; ++pce) {
-              const int piece = (hh * 4 + j) * OutPack<OUT>::kPieces + pce;  // 0..7 within the 128-byte slice
-              *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = q[pce];
-            }
-          }
-        }
+
+      // Writes one 128-byte slice per row (parked in `stg`, 16-byte pieces XOR-swizzled by row so both
+      // phases are bank-conflict free) with 8 lanes per row: every warp store covers four full
+      // 128-byte lines of the output instead of 32 scattered 16-byte pieces.
+      auto storeSlice = [&](int c) {
         __syncwarp();
         const int piece = lane & 7;
         const int ncol = tn * kBlockN + c + piece * (16 / OutPack<OUT>::kBytes);
@@ -422,10 +392,91 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                                        (static_cast<size_t>(grow) * prm.N + ncol) * OutPack<OUT>::kBytes) = val;
         }
         __syncwarp();
+      };
+      auto activate = [&](float x) {
+        if (prm.epilogue == kEpiBiasAddLeakyRelu) return fmaxf(x, x * prm.alpha);
+        if (prm.epilogue == kEpiBiasAddRelu) return fmaxf(x, 0.0f);
+        return x;
+      };
+
+      if constexpr (OutPack<OUT>::kBytes == 2) {
+        // 16-bit outputs: the whole row (256 columns) fits in registers once converted, so the
+        // accumulator is drained first and tensor memory handed back to the MMA warp before any
+        // global store is issued; the stores then overlap the next tile's mainloop.
+        // Bias of the tile's 256 columns, as f32, sits in this warp's staging area during the drain
+        // (the area is idle until the store phase); it is fetched before waiting for the accumulator.
+        float *biasS = reinterpret_cast<float *>(stg);
+        if (prm.epilogue != kEpiNone) {
+          const int n = tn * kBlockN + lane * 8;
+          float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
+          reinterpret_cast<float4 *>(biasS + lane * 8)[0] = make_float4(bv[0], bv[1], bv[2], bv[3]);
+          reinterpret_cast<float4 *>(biasS + lane * 8)[1] = make_float4(bv[4], bv[5], bv[6], bv[7]);
+        }
+        __syncwarp();
+        if (!mbarWait(smemAddr(&ctl->tmemFull[acc]), use & 1u, abortFlag, 2)) { ok = false; break; }
+        tcgen05FenceAfter();
+        uint4 packed[kBlockN / 8];
+#pragma unroll
+        for (int cc = 0; cc < kBlockN / 32; ++cc) {
+          unsigned int r[32];
+          tmemLoad32(taddr + cc * 32, r);
+          tmemLoadWait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+            if (prm.epilogue != kEpiNone) {
+              b0 = *reinterpret_cast<const float4 *>(biasS + cc * 32 + j * 8);
+              b1 = *reinterpret_cast<const float4 *>(biasS + cc * 32 + j * 8 + 4);
+            }
+            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = activate(__uint_as_float(r[j * 8 + e]) + bv[e]);
+            OutPack<OUT>::pack8(v, &packed[cc * 4 + j]);
+          }
+        }
+        tcgen05FenceBefore();
+        __syncwarp();
+        if (lane == 0) mbarArrive(smemAddr(&ctl->tmemEmpty[acc]));
+#pragma unroll
+        for (int sl = 0; sl < kBlockN / kColsPerSlice; ++sl) {
+#pragma unroll
+          for (int piece = 0; piece < 8; ++piece)
+            *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = packed[sl * 8 + piece];
+          storeSlice(sl * kColsPerSlice);
+        }
+      } else {
+        // f32 outputs: a row does not fit in registers; convert and store slice by slice, then release.
+        if (!mbarWait(smemAddr(&ctl->tmemFull[acc]), use & 1u, abortFlag, 2)) { ok = false; break; }
+        tcgen05FenceAfter();
+#pragma unroll 1
+        for (int c = 0; c < kBlockN; c += kColsPerSlice) {
+          unsigned int r[32];
+          tmemLoad32(taddr + c, r);
+          tmemLoadWait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = tn * kBlockN + c + j * 8;
+            float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (prm.epilogue != kEpiNone && n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = activate(__uint_as_float(r[j * 8 + e]) + bv[e]);
+            uint4 q[OutPack<OUT>::kPieces];
+            OutPack<OUT>::pack8(v, q);
+#pragma unroll
+            for (int pce = 0; pce < OutPack<OUT>::kPieces; ++pce) {
+              const int piece = j * OutPack<OUT>::kPieces + pce;
+              *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = q[pce];
+            }
+          }
+          storeSlice(c);
+        }
+        tcgen05FenceBefore();
+        __syncwarp();
+        if (lane == 0) mbarArrive(smemAddr(&ctl->tmemEmpty[acc]));
       }
-      tcgen05FenceBefore();
-      __syncwarp();
-      if (lane == 0) mbarArrive(smemAddr(&ctl->tmemEmpty[acc]));
     }
   }
 
