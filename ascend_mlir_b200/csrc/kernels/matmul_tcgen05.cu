@@ -26,6 +26,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels/kernels.h"
@@ -53,6 +54,7 @@ struct GemmParams {
   int biasType, epilogue;
   float alpha;
   unsigned int idesc;
+  int band;  // tile-rows per raster band
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -91,6 +93,9 @@ __device__ __forceinline__ bool mbarWait(unsigned int bar, unsigned int parity, 
   unsigned int spins = 0;
   while (true) {
     if (mbarTryWait(bar, parity)) return true;
+    // epilogue warps wait a whole mainloop for their accumulator: back off instead of burning issue slots and power
+    if (role == 2) __nanosleep(256);
+    else if (role == 0) __nanosleep(64);  // the producer is normally a full ring ahead: poll lazily
     if ((++spins & 63u) == 0) {
       if (*abortFlag) return false;
       if (globalTimerNs() - t0 > kWaitLimitNs) {
@@ -235,6 +240,120 @@ template <int MB> struct Shape {
       1024 + static_cast<size_t>(kStages) * kStageBytes + kStagingBytes + sizeof(Control<kStages>);
 };
 
+// One accumulator tile of one epilogue warp: wait for the accumulator, + bias, activation, convert,
+// write 32 rows x 256 columns.  `arriveEmpty` (called by lane 0) hands the accumulator back to the MMA
+// warp.  Returns false when the bounded wait gave up.
+template <int OUT, class ArriveEmpty>
+__device__ __forceinline__ bool epilogueTile(const GemmParams &prm, unsigned char *stg, unsigned int taddr, int rowBase, int tn,
+                                             int lane, unsigned int fullBar, unsigned int fullParity,
+                                             volatile int *abortFlag, ArriveEmpty arriveEmpty) {
+      constexpr int kColsPerSlice = 128 / OutPack<OUT>::kBytes;  // 64 (16-bit) or 32 (f32)
+
+      // Writes one 128-byte slice per row (parked in `stg`, 16-byte pieces XOR-swizzled by row so both
+      // phases are bank-conflict free) with 8 lanes per row: every warp store covers four full
+      // 128-byte lines of the output instead of 32 scattered 16-byte pieces.
+      auto storeSlice = [&](int c) {
+        __syncwarp();
+        const int piece = lane & 7;
+        const int ncol = tn * kBlockN + c + piece * (16 / OutPack<OUT>::kBytes);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = i * 4 + (lane >> 3);
+          const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((piece ^ (rr & 7)) << 4));
+          const int grow = rowBase + rr;
+          if (grow < prm.M && ncol < prm.N)  // N is a multiple of 8: a 16-byte piece is wholly inside or outside
+            *reinterpret_cast<uint4 *>(static_cast<unsigned char *>(prm.out) +
+                                       (static_cast<size_t>(grow) * prm.N + ncol) * OutPack<OUT>::kBytes) = val;
+        }
+        __syncwarp();
+      };
+      auto activate = [&](float x) {
+        if (prm.epilogue == kEpiBiasAddLeakyRelu) return fmaxf(x, x * prm.alpha);
+        if (prm.epilogue == kEpiBiasAddRelu) return fmaxf(x, 0.0f);
+        return x;
+      };
+
+      if constexpr (OutPack<OUT>::kBytes == 2) {
+        // 16-bit outputs: the whole row (256 columns) fits in registers once converted, so the
+        // accumulator is drained first and tensor memory handed back to the MMA warp before any
+        // global store is issued; the stores then overlap the next tile's mainloop.
+        // Bias of the tile's 256 columns, as f32, sits in this warp's staging area during the drain
+        // (the area is idle until the store phase); it is fetched before waiting for the accumulator.
+        float *biasS = reinterpret_cast<float *>(stg);
+        if (prm.epilogue != kEpiNone) {
+          const int n = tn * kBlockN + lane * 8;
+          float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
+          reinterpret_cast<float4 *>(biasS + lane * 8)[0] = make_float4(bv[0], bv[1], bv[2], bv[3]);
+          reinterpret_cast<float4 *>(biasS + lane * 8)[1] = make_float4(bv[4], bv[5], bv[6], bv[7]);
+        }
+        __syncwarp();
+        if (!mbarWait(fullBar, fullParity, abortFlag, 2)) return false;
+        tcgen05FenceAfter();
+        uint4 packed[kBlockN / 8];
+#pragma unroll
+        for (int cc = 0; cc < kBlockN / 32; ++cc) {
+          unsigned int r[32];
+          tmemLoad32(taddr + cc * 32, r);
+          tmemLoadWait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+            if (prm.epilogue != kEpiNone) {
+              b0 = *reinterpret_cast<const float4 *>(biasS + cc * 32 + j * 8);
+              b1 = *reinterpret_cast<const float4 *>(biasS + cc * 32 + j * 8 + 4);
+            }
+            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = activate(__uint_as_float(r[j * 8 + e]) + bv[e]);
+            OutPack<OUT>::pack8(v, &packed[cc * 4 + j]);
+          }
+        }
+        tcgen05FenceBefore();
+        __syncwarp();
+        if (lane == 0) arriveEmpty();
+#pragma unroll
+        for (int sl = 0; sl < kBlockN / kColsPerSlice; ++sl) {
+#pragma unroll
+          for (int piece = 0; piece < 8; ++piece)
+            *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = packed[sl * 8 + piece];
+          storeSlice(sl * kColsPerSlice);
+        }
+      } else {
+        // f32 outputs: a row does not fit in registers; convert and store slice by slice, then release.
+        if (!mbarWait(fullBar, fullParity, abortFlag, 2)) return false;
+        tcgen05FenceAfter();
+#pragma unroll 1
+        for (int c = 0; c < kBlockN; c += kColsPerSlice) {
+          unsigned int r[32];
+          tmemLoad32(taddr + c, r);
+          tmemLoadWait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = tn * kBlockN + c + j * 8;
+            float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (prm.epilogue != kEpiNone && n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = activate(__uint_as_float(r[j * 8 + e]) + bv[e]);
+            uint4 q[OutPack<OUT>::kPieces];
+            OutPack<OUT>::pack8(v, q);
+#pragma unroll
+            for (int pce = 0; pce < OutPack<OUT>::kPieces; ++pce) {
+              const int piece = j * OutPack<OUT>::kPieces + pce;
+              *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = q[pce];
+            }
+          }
+          storeSlice(c);
+        }
+        tcgen05FenceBefore();
+        __syncwarp();
+        if (lane == 0) arriveEmpty();
+      }
+  return true;
+}
+
 template <int MB, int OUT>
 __global__ void __launch_bounds__(Shape<MB>::kThreads, 1)
 matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
@@ -279,7 +398,7 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   // Tile order: M fastest inside bands of 16 tile-rows so that concurrently running CTAs share
   // A row-panels and B column-panels in L2.
   auto tileCoords = [&](int t, int &tm, int &tn) {
-    constexpr int kBand = 16;
+    const int kBand = prm.band;
     const int bandTiles = kBand * prm.numTilesN;
     const int band = t / bandTiles;
     const int within = t - band * bandTiles;
@@ -370,112 +489,13 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       tileCoords(t, tm, tn);
       const int acc = MB == 1 ? static_cast<int>(tileIter & 1u) : half;
       const unsigned int use = MB == 1 ? (tileIter >> 1) : tileIter;
-      constexpr int kColsPerSlice = 128 / OutPack<OUT>::kBytes;  // 64 (16-bit) or 32 (f32)
       const int rowBase = tm * S::kTileM + half * 128 + quarter * 32;
       const unsigned int taddr = tmemBase + static_cast<unsigned int>(acc * kBlockN) + (static_cast<unsigned int>(quarter * 32) << 16);
-      unsigned char *stg = staging + ew * (32 * 128);
-
-      // Writes one 128-byte slice per row (parked in `stg`, 16-byte pieces XOR-swizzled by row so both
-      // phases are bank-conflict free) with 8 lanes per row: every warp store covers four full
-      // 128-byte lines of the output instead of 32 scattered 16-byte pieces.
-      auto storeSlice = [&](int c) {
-        __syncwarp();
-        const int piece = lane & 7;
-        const int ncol = tn * kBlockN + c + piece * (16 / OutPack<OUT>::kBytes);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int rr = i * 4 + (lane >> 3);
-          const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((piece ^ (rr & 7)) << 4));
-          const int grow = rowBase + rr;
-          if (grow < prm.M && ncol < prm.N)  // N is a multiple of 8: a 16-byte piece is wholly inside or outside
-            *reinterpret_cast<uint4 *>(static_cast<unsigned char *>(prm.out) +
-                                       (static_cast<size_t>(grow) * prm.N + ncol) * OutPack<OUT>::kBytes) = val;
-        }
-        __syncwarp();
-      };
-      auto activate = [&](float x) {
-        if (prm.epilogue == kEpiBiasAddLeakyRelu) return fmaxf(x, x * prm.alpha);
-        if (prm.epilogue == kEpiBiasAddRelu) return fmaxf(x, 0.0f);
-        return x;
-      };
-
-      if constexpr (OutPack<OUT>::kBytes == 2) {
-        // 16-bit outputs: the whole row (256 columns) fits in registers once converted, so the
-        // accumulator is drained first and tensor memory handed back to the MMA warp before any
-        // global store is issued; the stores then overlap the next tile's mainloop.
-        // Bias of the tile's 256 columns, as f32, sits in this warp's staging area during the drain
-        // (the area is idle until the store phase); it is fetched before waiting for the accumulator.
-        float *biasS = reinterpret_cast<float *>(stg);
-        if (prm.epilogue != kEpiNone) {
-          const int n = tn * kBlockN + lane * 8;
-          float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          if (n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
-          reinterpret_cast<float4 *>(biasS + lane * 8)[0] = make_float4(bv[0], bv[1], bv[2], bv[3]);
-          reinterpret_cast<float4 *>(biasS + lane * 8)[1] = make_float4(bv[4], bv[5], bv[6], bv[7]);
-        }
-        __syncwarp();
-        if (!mbarWait(smemAddr(&ctl->tmemFull[acc]), use & 1u, abortFlag, 2)) { ok = false; break; }
-        tcgen05FenceAfter();
-        uint4 packed[kBlockN / 8];
-#pragma unroll
-        for (int cc = 0; cc < kBlockN / 32; ++cc) {
-          unsigned int r[32];
-          tmemLoad32(taddr + cc * 32, r);
-          tmemLoadWait();
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
-            if (prm.epilogue != kEpiNone) {
-              b0 = *reinterpret_cast<const float4 *>(biasS + cc * 32 + j * 8);
-              b1 = *reinterpret_cast<const float4 *>(biasS + cc * 32 + j * 8 + 4);
-            }
-            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = activate(__uint_as_float(r[j * 8 + e]) + bv[e]);
-            OutPack<OUT>::pack8(v, &packed[cc * 4 + j]);
-          }
-        }
-        tcgen05FenceBefore();
-        __syncwarp();
-        if (lane == 0) mbarArrive(smemAddr(&ctl->tmemEmpty[acc]));
-#pragma unroll
-        for (int sl = 0; sl < kBlockN / kColsPerSlice; ++sl) {
-#pragma unroll
-          for (int piece = 0; piece < 8; ++piece)
-            *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = packed[sl * 8 + piece];
-          storeSlice(sl * kColsPerSlice);
-        }
-      } else {
-        // f32 outputs: a row does not fit in registers; convert and store slice by slice, then release.
-        if (!mbarWait(smemAddr(&ctl->tmemFull[acc]), use & 1u, abortFlag, 2)) { ok = false; break; }
-        tcgen05FenceAfter();
-#pragma unroll 1
-        for (int c = 0; c < kBlockN; c += kColsPerSlice) {
-          unsigned int r[32];
-          tmemLoad32(taddr + c, r);
-          tmemLoadWait();
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int n = tn * kBlockN + c + j * 8;
-            float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (prm.epilogue != kEpiNone && n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = activate(__uint_as_float(r[j * 8 + e]) + bv[e]);
-            uint4 q[OutPack<OUT>::kPieces];
-            OutPack<OUT>::pack8(v, q);
-#pragma unroll
-            for (int pce = 0; pce < OutPack<OUT>::kPieces; ++pce) {
-              const int piece = j * OutPack<OUT>::kPieces + pce;
-              *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = q[pce];
-            }
-          }
-          storeSlice(c);
-        }
-        tcgen05FenceBefore();
-        __syncwarp();
-        if (lane == 0) mbarArrive(smemAddr(&ctl->tmemEmpty[acc]));
+      const unsigned int emptyBar = smemAddr(&ctl->tmemEmpty[acc]);
+      if (!epilogueTile<OUT>(prm, staging + ew * (32 * 128), taddr, rowBase, tn, lane, smemAddr(&ctl->tmemFull[acc]), use & 1u,
+                             abortFlag, [&] { mbarArrive(emptyBar); })) {
+        ok = false;
+        break;
       }
     }
   }
@@ -486,6 +506,202 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   if (warp == 1) {
     tcgen05FenceAfter();
     tmemDealloc(tmemBase, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Two-CTA variant (tcgen05 cta_group::2): a cluster of two CTAs on neighbouring SMs computes one
+// 256x256 tile.  CTA r holds A rows [128r, 128r+128) and B columns [128r, 128r+128) of the tile in its own
+// shared memory and the accumulator rows [128r, 128r+128) x 256 columns in its own tensor memory; the
+// leader CTA (rank 0) issues one 256x256x16 instruction for the pair.  Per SM and k-block this moves
+// 32 KB into shared memory and reads 8 KB per instruction out of it, half of what the single-CTA kernel
+// needs, which is what shared-memory bandwidth allows at full tensor rate; the accumulator takes 256 of
+// the 512 tensor-memory columns, so two tiles are double-buffered and the epilogue overlaps the mainloop.
+// No multicast anywhere: every CTA loads its own operand halves; the peer's loads complete on the
+// leader's "full" barrier, the leader's commits arrive on both CTAs' "empty"/"accumulator full"
+// barriers (one commit each), the peer's epilogue warps arrive remotely on the leader's
+// "accumulator drained" barrier.  All waits are bounded as in the single-CTA kernel.
+// ---------------------------------------------------------------------------------------------------
+constexpr int k2Stages = 6;
+constexpr int k2AStageBytes = 128 * kBlockK * 2;
+constexpr int k2BStageBytes = 2 * kBBoxBytes;
+constexpr int k2StageBytes = k2AStageBytes + k2BStageBytes;
+constexpr int k2Threads = 192;
+constexpr int k2StagingBytes = 4 * 32 * 128;
+constexpr size_t k2SmemBytes = 1024 + static_cast<size_t>(k2Stages) * k2StageBytes + k2StagingBytes + sizeof(Control<k2Stages>);
+
+__device__ __forceinline__ unsigned int clusterCtaRank() {
+  unsigned int r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ unsigned int mapToCta(unsigned int addr, unsigned int rank) {
+  unsigned int r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void clusterSyncAll() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbarArriveRemote(unsigned int clusterAddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+__device__ __forceinline__ void tmaLoad2dPair(unsigned int dst, const CUtensorMap *map, int x, int y, unsigned int clusterBar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(clusterBar)
+      : "memory");
+}
+__device__ __forceinline__ void ummaF16Pair(unsigned int dTmem, unsigned long long aDesc, unsigned long long bDesc,
+                                            unsigned int idesc, unsigned int accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void ummaCommitPair(unsigned int clusterBar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(clusterBar) : "memory");
+}
+
+template <int OUT>
+__global__ void __launch_bounds__(k2Threads, 1)
+matmulBiasActPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                        const __grid_constant__ GemmParams prm) {
+  extern __shared__ unsigned char smemRaw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+  unsigned char *staging = smem + static_cast<size_t>(k2Stages) * k2StageBytes;
+  Control<k2Stages> *ctl = reinterpret_cast<Control<k2Stages> *>(staging + k2StagingBytes);
+  volatile int *abortFlag = &ctl->abortFlag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const unsigned int rank = clusterCtaRank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int numPairs = gridDim.x >> 1;
+  const int numTiles = prm.numTilesM * prm.numTilesN;  // 256 x 256 tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < k2Stages; ++s) {
+      mbarInit(smemAddr(&ctl->full[s]), 1);   // leader: its own arrive.expect_tx covers both CTAs' bytes
+      mbarInit(smemAddr(&ctl->empty[s]), 1);  // one commit from the leader
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbarInit(smemAddr(&ctl->tmemFull[a]), 1);
+      mbarInit(smemAddr(&ctl->tmemEmpty[a]), 8);  // four epilogue warps in each CTA (leader's copy is the one used)
+    }
+    ctl->abortFlag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    prefetchTensorMap(&mapA);
+    prefetchTensorMap(&mapB);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&ctl->tmemBase)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05FenceBefore();
+  __syncthreads();
+  clusterSyncAll();  // both CTAs' barriers exist before anyone signals across
+  tcgen05FenceAfter();
+  const unsigned int tmemBase = ctl->tmemBase;
+
+  auto tileCoords = [&](int t, int &tm, int &tn) {
+    const int kBand = prm.band;
+    const int bandTiles = kBand * prm.numTilesN;
+    const int band = t / bandTiles;
+    const int within = t - band * bandTiles;
+    const int rowsInBand = min(kBand, prm.numTilesM - band * kBand);
+    tm = band * kBand + within % rowsInBand;
+    tn = within / rowsInBand;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      unsigned int it = 0;
+      bool ok = true;
+      for (int t = pair; t < numTiles && ok; t += numPairs) {
+        int tm, tn;
+        tileCoords(t, tm, tn);
+        for (int kb = 0; kb < prm.numKBlocks; ++kb, ++it) {
+          const int s = it % k2Stages;
+          const unsigned int phase = (it / k2Stages) & 1u;
+          if (!mbarWait(smemAddr(&ctl->empty[s]), phase ^ 1u, abortFlag, 0)) { ok = false; break; }
+          const unsigned int fullLocal = smemAddr(&ctl->full[s]);
+          if (rank == 0) mbarExpectTx(fullLocal, 2 * k2StageBytes);
+          const unsigned int fullLeader = mapToCta(fullLocal, 0);
+          unsigned char *stage = smem + static_cast<size_t>(s) * k2StageBytes;
+          tmaLoad2dPair(smemAddr(stage), &mapA, kb * kBlockK, tm * 256 + static_cast<int>(rank) * 128, fullLeader);
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            tmaLoad2dPair(smemAddr(stage + k2AStageBytes + j * kBBoxBytes), &mapB,
+                          tn * kBlockN + static_cast<int>(rank) * 128 + j * 64, kb * kBlockK, fullLeader);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader only) ----------------
+    if (lane == 0 && rank == 0) {
+      unsigned int it = 0, tileIter = 0;
+      bool ok = true;
+      for (int t = pair; t < numTiles && ok; t += numPairs, ++tileIter) {
+        const int acc = static_cast<int>(tileIter & 1u);
+        const unsigned int use = tileIter >> 1;
+        if (!mbarWait(smemAddr(&ctl->tmemEmpty[acc]), (use & 1u) ^ 1u, abortFlag, 1)) break;
+        tcgen05FenceAfter();
+        const unsigned int dTmem = tmemBase + static_cast<unsigned int>(acc * kBlockN);
+        for (int kb = 0; kb < prm.numKBlocks; ++kb, ++it) {
+          const int s = it % k2Stages;
+          const unsigned int phase = (it / k2Stages) & 1u;
+          if (!mbarWait(smemAddr(&ctl->full[s]), phase, abortFlag, 1)) { ok = false; break; }
+          tcgen05FenceAfter();
+          const unsigned int aBase = smemAddr(smem + static_cast<size_t>(s) * k2StageBytes);
+          const unsigned int bBase = aBase + k2AStageBytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const unsigned long long aDesc = smemDesc(aBase + k * (kUmmaK * 2), 16, 1024);
+            const unsigned long long bDesc = smemDesc(bBase + k * (kUmmaK * 128), kBBoxBytes, 1024);
+            ummaF16Pair(dTmem, aDesc, bDesc, prm.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          const unsigned int emptyLocal = smemAddr(&ctl->empty[s]);
+          ummaCommitPair(emptyLocal);               // frees the stage in this CTA ...
+          ummaCommitPair(mapToCta(emptyLocal, 1));  // ... and in the peer
+        }
+        if (!ok) break;
+        const unsigned int fullAcc = smemAddr(&ctl->tmemFull[acc]);
+        ummaCommitPair(fullAcc);
+        ummaCommitPair(mapToCta(fullAcc, 1));
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 rows) ----------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    unsigned int tileIter = 0;
+    for (int t = pair; t < numTiles; t += numPairs, ++tileIter) {
+      int tm, tn;
+      tileCoords(t, tm, tn);
+      const int acc = static_cast<int>(tileIter & 1u);
+      const unsigned int use = tileIter >> 1;
+      const int rowBase = tm * 256 + static_cast<int>(rank) * 128 + quarter * 32;
+      const unsigned int taddr = tmemBase + static_cast<unsigned int>(acc * kBlockN) + (static_cast<unsigned int>(quarter * 32) << 16);
+      const unsigned int emptyLeader = mapToCta(smemAddr(&ctl->tmemEmpty[acc]), 0);
+      if (!epilogueTile<OUT>(prm, staging + ew * (32 * 128), taddr, rowBase, tn, lane, smemAddr(&ctl->tmemFull[acc]), use & 1u,
+                             abortFlag, [&] { mbarArriveRemote(emptyLeader); }))
+        break;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tcgen05FenceBefore();
+  __syncthreads();
+  clusterSyncAll();  // the peer must not free tensor memory the leader's instructions may still write
+  if (warp == 1) {
+    tcgen05FenceAfter();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -541,6 +757,34 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmPa
   return static_cast<int>(cudaGetLastError());
 }
 
+template <int OUT>
+int launchPairVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmParams &p, int grid, cudaStream_t stream,
+                      char *errorText) {
+  auto kernel = matmulBiasActPairKernel<OUT>;
+  static std::once_flag once;
+  static cudaError_t attrErr = cudaSuccess;
+  std::call_once(once, [&] {
+    attrErr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(k2SmemBytes));
+  });
+  if (attrErr != cudaSuccess) {
+    fail(errorText, "matmul: cannot reserve shared memory for the operand ring");
+    return static_cast<int>(attrErr);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned int>(grid), 1, 1);
+  cfg.blockDim = dim3(k2Threads, 1, 1);
+  cfg.dynamicSmemBytes = k2SmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, p));
+}
+
 } // namespace
 
 int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char *errorText) {
@@ -562,11 +806,14 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   int device = 0;
   cudaGetDevice(&device);
   const int sms = deviceSmCount(device);
-  // 256-row tiles when they still give every SM work; 128-row tiles otherwise
+  // Variant: 256-row tiles per CTA when they still fill the SMs; else 128-row tiles.
+  // l.stages forces one: 1 = 128-row single CTA, 2 = 256-row single CTA, 3 = CTA pair.
   const int64_t tiles256 = ((l.M + 255) / 256) * ((l.N + kBlockN - 1) / kBlockN);
-  const int mb = (l.stages == 1) ? 1 : (l.stages == 2) ? 2 : (tiles256 >= sms ? 2 : 1);
-  const int tileM = 128 * mb;
-
+  // (the pair kernel keeps the tensor pipe busier per clock but draws more power; under the board's power cap the
+  // single-CTA 256-row kernel sustains the higher throughput on B200, so the pair kernel is opt-in)
+  const bool pairKernel = l.stages == 3;
+  const int mb = pairKernel ? 1 : (l.stages == 1) ? 1 : (l.stages == 2) ? 2 : (tiles256 >= sms ? 2 : 1);
+  const int tileM = 128 * mb;  // rows per TMA box of A (the pair kernel loads 128 rows per CTA)
   const CUtensorMapDataType dt = l.inType == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap mapA, mapB;
   if (!makeMap2d(&mapA, dt, l.A, static_cast<uint64_t>(l.K), static_cast<uint64_t>(l.M), static_cast<uint64_t>(l.K) * 2, kBlockK,
@@ -580,7 +827,8 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   p.M = static_cast<int>(l.M);
   p.N = static_cast<int>(l.N);
   p.K = static_cast<int>(l.K);
-  p.numTilesM = static_cast<int>((l.M + tileM - 1) / tileM);
+  const int ctaTileM = pairKernel ? 256 : tileM;
+  p.numTilesM = static_cast<int>((l.M + ctaTileM - 1) / ctaTileM);
   p.numTilesN = static_cast<int>((l.N + kBlockN - 1) / kBlockN);
   p.numKBlocks = static_cast<int>((l.K + kBlockK - 1) / kBlockK);
   p.bias = l.bias;
@@ -588,16 +836,26 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   p.biasType = l.biasType;
   p.epilogue = l.epilogue;
   p.alpha = l.alpha;
+  p.band = pairKernel ? 8 : 16;
+  if (const char *e = std::getenv("AFIR_GEMM_BAND")) p.band = std::max(1, std::atoi(e));
   const unsigned int fmt = l.inType == kF16 ? 0u : 1u;
-  // instruction descriptor: D=f32, A/B format, A K-major, B N-major, N=256, M=128
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) | ((kBlockN >> 3) << 17) | ((128u >> 4) << 24);
+  // instruction descriptor: D=f32, A/B format, A K-major, B N-major, N=256, M=128 (256 across a CTA pair)
+  const unsigned int instrM = pairKernel ? 256u : 128u;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) | ((kBlockN >> 3) << 17) | ((instrM >> 4) << 24);
 
   const int64_t numTiles = static_cast<int64_t>(p.numTilesM) * p.numTilesN;
   int grid = l.gridBlocks > 0 ? l.gridBlocks : sms;
   grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, numTiles)));
 
   int rc;
-  if (mb == 1) {
+  if (pairKernel) {
+    grid = l.gridBlocks > 0 ? l.gridBlocks : sms;
+    grid = static_cast<int>(std::min<int64_t>(grid, 2 * numTiles)) & ~1;  // whole pairs
+    if (grid < 2) grid = 2;
+    rc = l.outType == kF32 ? launchPairVariant<kF32>(mapA, mapB, p, grid, stream, errorText)
+         : l.outType == kF16 ? launchPairVariant<kF16>(mapA, mapB, p, grid, stream, errorText)
+                             : launchPairVariant<kBF16>(mapA, mapB, p, grid, stream, errorText);
+  } else if (mb == 1) {
     rc = l.outType == kF32 ? launchVariant<1, kF32>(mapA, mapB, p, grid, stream, errorText)
          : l.outType == kF16 ? launchVariant<1, kF16>(mapA, mapB, p, grid, stream, errorText)
                              : launchVariant<1, kBF16>(mapA, mapB, p, grid, stream, errorText);

@@ -252,7 +252,7 @@ def _matmul_check(rt, M, N, K, mb, seed=0):
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 320), (100, 136, 72), (1, 8, 8),
                                    (130, 264, 1032), (1024, 1024, 1024)])
-@pytest.mark.parametrize("mb", [1, 2])
+@pytest.mark.parametrize("mb", [1, 2, 3])
 def test_matmul_bias_leakyrelu_bf16(rt, M, N, K, mb):
     _matmul_check(rt, M, N, K, mb, seed=M + N + K)
 
@@ -261,6 +261,8 @@ def test_matmul_many_tiles_per_cta(rt):
     # more tiles than SMs: every CTA walks several tiles, both TMEM accumulators and all ring phases wrap
     _matmul_check(rt, 2048, 4096, 512, 1, seed=21)
     _matmul_check(rt, 4096, 4096, 256, 2, seed=22)
+    _matmul_check(rt, 4096, 2048, 512, 3, seed=25)
+    _matmul_check(rt, 2000, 1032, 264, 3, seed=26)
 
 
 def test_reference_matmul_example_golden_max_abs_diff_zero(rt, golden_dir):
