@@ -2,7 +2,9 @@
 
 #include <cuda_runtime_api.h>
 
+#include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 namespace afir {
@@ -27,6 +29,9 @@ CudaExecutor::~CudaExecutor() {
     if (s.ptr) cudaFree(s.ptr);
   if (workspace_.ptr) cudaFree(workspace_.ptr);
   if (stream_) cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
+  if (copyIn_) cudaStreamDestroy(static_cast<cudaStream_t>(copyIn_));
+  if (copyOut_) cudaStreamDestroy(static_cast<cudaStream_t>(copyOut_));
+  for (void *e : events_) cudaEventDestroy(static_cast<cudaEvent_t>(e));
 }
 
 Status CudaExecutor::initialize(int deviceId) {
@@ -138,6 +143,21 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   args.workspace = workspace_.ptr;
   args.workspaceBytes = workspace_.capacity;
 
+  // Large runs whose work splits along the leading axis are pipelined: copies in, kernel and copies out
+  // of successive row chunks overlap (PCIe is full duplex), instead of three serial phases.
+  {
+    RowPipelinePlan plan;
+    if (Status s = planRowPipeline(*desc, tiling, args.argBytes, plan); !s) return s.withStage("cuda:bindings");
+    size_t total = 0;
+    for (size_t b : args.argBytes) total += b;
+    if (plan.possible && total >= (16u << 20) && plan.rows >= 2 && !std::getenv("AFIR_CUDA_NO_PIPELINE")) {
+      const int64_t quantum = desc->kernelClass == KernelClass::Matmul ? 256 : (plan.rows >= 64 ? 8 : 1);
+      int64_t chunkRows = (plan.rows + 5) / 6;
+      chunkRows = ((chunkRows + quantum - 1) / quantum) * quantum;
+      if (chunkRows < plan.rows) return runHostPipelined(req, *desc, tiling, args, plan, chunkRows);
+    }
+  }
+
   cudaError_t e;
   for (int i = 0; i < req.numInputs; ++i) {
     if (!req.inputBytes[i]) continue;
@@ -164,6 +184,102 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   statusWorkspace_ = workspace_.ptr;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
   reducePending_ = desc->kernelClass == KernelClass::RowReduce;
+  return synchronize(stream_);
+}
+
+Status CudaExecutor::ensureCopyStreams(size_t events) {
+  cudaError_t e;
+  if (!copyIn_) {
+    cudaStream_t s;
+    if ((e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking)) != cudaSuccess) return cudaFail(e, "cudaStreamCreate");
+    copyIn_ = s;
+  }
+  if (!copyOut_) {
+    cudaStream_t s;
+    if ((e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking)) != cudaSuccess) return cudaFail(e, "cudaStreamCreate");
+    copyOut_ = s;
+  }
+  while (events_.size() < events) {
+    cudaEvent_t ev;
+    if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return cudaFail(e, "cudaEventCreate");
+    events_.push_back(ev);
+  }
+  return Status::success();
+}
+
+Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescriptor &desc,
+                                      const std::map<std::string, int64_t> &tiling, LaunchArgs &args,
+                                      const RowPipelinePlan &plan, int64_t chunkRows) {
+  const int64_t numChunks = (plan.rows + chunkRows - 1) / chunkRows;
+  if (Status s = ensureCopyStreams(static_cast<size_t>(2 * numChunks + 1)); !s) return s.withStage("cuda:device");
+  cudaStream_t compute = static_cast<cudaStream_t>(stream_);
+  cudaStream_t in = static_cast<cudaStream_t>(copyIn_);
+  cudaStream_t out = static_cast<cudaStream_t>(copyOut_);
+  auto event = [&](size_t i) { return static_cast<cudaEvent_t>(events_[i]); };
+  cudaError_t e;
+
+  if ((e = cudaMemsetAsync(workspace_.ptr, 0, kWorkspaceStatusBytes, compute)) != cudaSuccess)
+    return cudaFail(e, "[cuda:memory] workspace clear failed");
+  // arguments every chunk needs in full go first
+  for (int i = 0; i < req.numInputs; ++i) {
+    if (plan.rowBytes[i] || !req.inputBytes[i]) continue;
+    if ((e = cudaMemcpyAsync(args.argPtrs[i], req.inputPtrs[i], req.inputBytes[i], cudaMemcpyHostToDevice, in)) != cudaSuccess)
+      return cudaFail(e, "[cuda:memory] host-to-device copy failed");
+  }
+  lastLaunchCount_ = 0;
+  bool usesStatus = false;
+  for (int64_t c = 0; c < numChunks; ++c) {
+    const int64_t b = c * chunkRows, en = std::min(plan.rows, b + chunkRows);
+    for (int i = 0; i < req.numInputs; ++i) {
+      const size_t rb = plan.rowBytes[i];
+      if (!rb) continue;
+      e = cudaMemcpyAsync(static_cast<char *>(args.argPtrs[i]) + static_cast<size_t>(b) * rb,
+                          static_cast<const char *>(req.inputPtrs[i]) + static_cast<size_t>(b) * rb,
+                          static_cast<size_t>(en - b) * rb, cudaMemcpyHostToDevice, in);
+      if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] host-to-device copy failed");
+    }
+    cudaEventRecord(event(2 * c), in);
+    cudaStreamWaitEvent(compute, event(2 * c), 0);
+    args.rowBegin = b;
+    args.rowEnd = en;
+    LaunchInfo info;
+    Status ls = launchDescriptor(desc, tiling, args, info);
+    lastLaunchCount_ += info.kernelsLaunched;
+    totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
+    usesStatus = usesStatus || info.usesStatusBlock;
+    if (!ls) {
+      cudaStreamSynchronize(in);
+      cudaStreamSynchronize(compute);
+      cudaStreamSynchronize(out);
+      return ls.withStage("cuda:kernel_launch");
+    }
+    cudaEventRecord(event(2 * c + 1), compute);
+    cudaStreamWaitEvent(out, event(2 * c + 1), 0);
+    for (int i = 0; i < req.numOutputs; ++i) {
+      const size_t k = static_cast<size_t>(req.numInputs + i);
+      const size_t rb = plan.rowBytes[k];
+      if (!rb || !req.outputBytes[i]) continue;
+      e = cudaMemcpyAsync(static_cast<char *>(req.outputPtrs[i]) + static_cast<size_t>(b) * rb,
+                          static_cast<const char *>(args.argPtrs[k]) + static_cast<size_t>(b) * rb,
+                          static_cast<size_t>(en - b) * rb, cudaMemcpyDeviceToHost, out);
+      if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] device-to-host copy failed");
+    }
+  }
+  // outputs that are not row-sliced (none today) would be copied here after the last chunk
+  for (int i = 0; i < req.numOutputs; ++i) {
+    const size_t k = static_cast<size_t>(req.numInputs + i);
+    if (plan.rowBytes[k] || !req.outputBytes[i]) continue;
+    cudaEventRecord(event(2 * numChunks), compute);
+    cudaStreamWaitEvent(out, event(2 * numChunks), 0);
+    e = cudaMemcpyAsync(req.outputPtrs[i], args.argPtrs[k], req.outputBytes[i], cudaMemcpyDeviceToHost, out);
+    if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] device-to-host copy failed");
+  }
+  if ((e = cudaStreamSynchronize(in)) != cudaSuccess) return cudaFail(e, "[cuda:memory] host-to-device copy failed");
+  if ((e = cudaStreamSynchronize(out)) != cudaSuccess) return cudaFail(e, "[cuda:kernel_launch] kernel execution failed");
+  statusPending_ = usesStatus;
+  statusWorkspace_ = workspace_.ptr;
+  matmulPending_ = desc.kernelClass == KernelClass::Matmul;
+  reducePending_ = desc.kernelClass == KernelClass::RowReduce;
   return synchronize(stream_);
 }
 

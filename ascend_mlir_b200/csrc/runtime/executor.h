@@ -63,10 +63,17 @@ private:
   Status slotFor(size_t index, size_t bytes, void **out);
   Status ensureStream();
   Status ownWorkspace(size_t bytes);
+  // Host path cut into leading-axis chunks: H2D of chunk i+1, the kernel on chunk i and D2H of chunk i-1 overlap.
+  Status runHostPipelined(const RunRequest &req, const LaunchDescriptor &desc, const std::map<std::string, int64_t> &tiling,
+                          LaunchArgs &args, const RowPipelinePlan &plan, int64_t chunkRows);
+  Status ensureCopyStreams(size_t events);
 
   bool initialized_ = false;
   int device_ = 0;
   void *stream_ = nullptr;
+  void *copyIn_ = nullptr;
+  void *copyOut_ = nullptr;
+  std::vector<void *> events_;
   std::vector<Slot> slots_;
   Slot workspace_;
   std::unordered_map<uint64_t, std::shared_ptr<const LaunchDescriptor>> cache_;

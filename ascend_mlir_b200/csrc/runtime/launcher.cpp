@@ -67,6 +67,7 @@ Status resolveView(const ViewSpec &v, const std::vector<int64_t> &domain, const 
   for (int t = static_cast<int>(shape.size()) - 1; t >= 0; --t) {
     const int d = v.map.empty() ? -1 : v.map[t];
     const int64_t extent = d >= 0 ? domain[d] : 1;
+    if (d == 0 && args.rowEnd >= 0) offset[t] += args.rowBegin;
     if (offset[t] < 0 || offset[t] + extent > shape[t])
       return Status::error(std::string(what) + ": view exceeds argument " + std::to_string(v.arg) + " along dim " + std::to_string(t));
     if (d >= 0) out.stride[d] += ts;
@@ -97,6 +98,16 @@ void collapseDomain(std::vector<int64_t> &domain, std::vector<ResolvedView *> &v
   }
 }
 
+// Restricts the leading iteration dim to the requested row range (no-op when none was asked for).
+Status applyRowRange(std::vector<int64_t> &domain, const LaunchArgs &args, int64_t *fullRows = nullptr) {
+  if (fullRows) *fullRows = domain.empty() ? 0 : domain[0];
+  if (args.rowEnd < 0) return Status::success();
+  if (domain.empty() || args.rowBegin < 0 || args.rowBegin > args.rowEnd || args.rowEnd > domain[0])
+    return Status::error("row range outside the leading iteration dim");
+  domain[0] = args.rowEnd - args.rowBegin;
+  return Status::success();
+}
+
 void *argAt(const LaunchArgs &args, const ResolvedView &v) {
   return static_cast<char *>(args.argPtrs[v.arg]) + static_cast<size_t>(v.baseOffset) * v.elemBytes;
 }
@@ -113,6 +124,7 @@ Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, con
   if (!ok) return Status::error("elementwise groups compute in f32, f16 or bf16");
   std::vector<int64_t> domain;
   if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+  if (Status s = applyRowRange(domain, args); !s) return s;
   std::vector<ResolvedView> loads(g.loads.size());
   ResolvedView store;
   for (size_t i = 0; i < g.loads.size(); ++i) {
@@ -161,6 +173,7 @@ Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const
   std::vector<int64_t> domain;
   if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
   if (domain.size() < 2) return Status::error("row reduction needs a [rows..., cols] domain");
+  if (Status s = applyRowRange(domain, args); !s) return s;
   std::vector<ResolvedView> loads(g.loads.size());
   ResolvedView store;
   for (size_t i = 0; i < g.loads.size(); ++i)
@@ -224,6 +237,9 @@ Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const st
   if (!ok) return Status::error("gather groups compute in f32, f16 or bf16");
   std::vector<int64_t> domain;
   if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+  int64_t fullRows = 0;
+  if (Status s = applyRowRange(domain, args, &fullRows); !s) return s;
+  const int64_t rowShift = args.rowEnd >= 0 ? args.rowBegin : 0;
   // table: a plain 2-D argument
   const ViewSpec &tv = g.loads[0];
   std::vector<int64_t> tshape;
@@ -234,12 +250,12 @@ Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const st
   if (tv.dtype != d.dtype) return Status::error("gather table differs from the group element type");
   std::vector<int64_t> ishape;
   if (Status s = evalDims(g.indices.shape, tiling, ishape); !s) return s;
-  const int64_t wantIdx = g.gatherAxis == 0 ? domain[0] : domain[1];
+  const int64_t wantIdx = g.gatherAxis == 0 ? fullRows : domain[1];
   if (ishape.size() != 1 || ishape[0] != wantIdx) return Status::error("gather indices: expected a vector of " + std::to_string(wantIdx));
   if (args.argBytes[g.indices.arg] != static_cast<size_t>(wantIdx) * dtypeBytes(g.indices.dtype))
     return Status::error("gather indices: argument byte size does not match");
   if (g.gatherAxis == 0 && tshape[1] != domain[1]) return Status::error("row gather: table width differs from the output width");
-  if (g.gatherAxis == 1 && tshape[0] != domain[0]) return Status::error("column gather: table rows differ from the output rows");
+  if (g.gatherAxis == 1 && tshape[0] != fullRows) return Status::error("column gather: table rows differ from the output rows");
 
   std::vector<ResolvedView> loads(g.loads.size());
   ResolvedView store;
@@ -257,10 +273,14 @@ Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const st
   l.rows = domain[0];
   l.cols = domain[1];
   l.table = args.argPtrs[tv.arg];
+  if (g.gatherAxis == 1)  // output row i reads table row i: a row range shifts the table too
+    l.table = static_cast<const char *>(l.table) + static_cast<size_t>(rowShift * tshape[1]) * dtypeBytes(tv.dtype);
   l.tableRows = tshape[0];
   l.tableCols = tshape[1];
   l.tableRowStride = tshape[1];
   l.indices = args.argPtrs[g.indices.arg];
+  if (g.gatherAxis == 0)
+    l.indices = static_cast<const char *>(l.indices) + static_cast<size_t>(rowShift) * dtypeBytes(g.indices.dtype);
   l.numViews = static_cast<int>(g.loads.size());
   for (size_t i = 1; i < loads.size(); ++i) {
     l.views[i].base = argAt(args, loads[i]);
@@ -288,6 +308,7 @@ Status launchTransposeGroup(const LaunchDescriptor &d, const GroupSpec &g, const
   // domain = output shape [C, R]; loads[0] is the [R, C] input read as (d1, d0)
   std::vector<int64_t> domain;
   if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+  if (args.rowEnd >= 0) return Status::error("transpose groups do not take a row range");
   if (domain.size() != 2 || g.loads.size() != 1 || g.body.numOps != 0)
     return Status::error("transpose groups are a bare 2-D permutation of one input");
   ResolvedView in, store;
@@ -333,11 +354,17 @@ Status launchMatmulDescriptor(const LaunchDescriptor &d, const std::map<std::str
   if (m.biasArg >= 0)
     if (Status s = check(m.biasArg, N, m.biasType, "bias"); !s) return s;
   if (Status s = check(m.outArg, M * N, m.outType, "out"); !s) return s;
-  l.M = M; l.N = N; l.K = K;
-  l.A = args.argPtrs[m.aArg];
+  int64_t r0 = 0, r1 = M;
+  if (args.rowEnd >= 0) {
+    if (args.rowBegin < 0 || args.rowBegin > args.rowEnd || args.rowEnd > M) return Status::error("row range outside M");
+    r0 = args.rowBegin;
+    r1 = args.rowEnd;
+  }
+  l.M = r1 - r0; l.N = N; l.K = K;
+  l.A = static_cast<const char *>(args.argPtrs[m.aArg]) + static_cast<size_t>(r0 * K) * dtypeBytes(m.inType);
   l.B = args.argPtrs[m.bArg];
   l.bias = m.biasArg >= 0 ? args.argPtrs[m.biasArg] : nullptr;
-  l.out = args.argPtrs[m.outArg];
+  l.out = static_cast<char *>(args.argPtrs[m.outArg]) + static_cast<size_t>(r0 * N) * dtypeBytes(m.outType);
   l.epilogue = m.epilogue;
   l.alpha = static_cast<float>(m.alpha);
   l.gridBlocks = args.blockDim;
@@ -387,6 +414,91 @@ Status launchDescriptor(const LaunchDescriptor &d, const std::map<std::string, i
     }
     if (!s) return s;
   }
+  return Status::success();
+}
+
+} // namespace afir
+
+namespace afir {
+namespace {
+
+// Marks argument `arg` as row-sliced with `bytes` per leading-dim row; conflicting uses make chunking impossible.
+bool noteSlice(std::vector<size_t> &rowBytes, std::vector<char> &seen, int arg, size_t bytes) {
+  if (arg < 0 || arg >= static_cast<int>(rowBytes.size())) return false;
+  if (seen[arg] && rowBytes[arg] != bytes) return false;
+  seen[arg] = 1;
+  rowBytes[arg] = bytes;
+  return true;
+}
+
+// A view is chunkable when the leading iteration dim does not index it at all (whole argument needed by
+// every chunk), or indexes its outermost tensor dim starting at offset 0 (rows are contiguous byte ranges).
+bool classifyView(const ViewSpec &v, const std::map<std::string, int64_t> &tiling, std::vector<size_t> &rowBytes,
+                  std::vector<char> &seen) {
+  int mapped = -1;
+  for (size_t t = 0; t < v.map.size(); ++t)
+    if (v.map[t] == 0) {
+      if (mapped >= 0) return false;
+      mapped = static_cast<int>(t);
+    }
+  if (mapped < 0) return noteSlice(rowBytes, seen, v.arg, 0);
+  if (mapped != 0) return false;
+  if (!v.offset.empty()) {
+    int64_t off = 0;
+    if (!evalDim(v.offset[0], tiling, off) || off != 0) return false;
+  }
+  std::vector<int64_t> shape;
+  if (!evalDims(v.shape, tiling, shape)) return false;
+  size_t bytes = dtypeBytes(v.dtype);
+  for (size_t t = 1; t < shape.size(); ++t) bytes *= static_cast<size_t>(shape[t]);
+  if (bytes == 0) return false;
+  return noteSlice(rowBytes, seen, v.arg, bytes);
+}
+
+} // namespace
+
+Status planRowPipeline(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling,
+                       const std::vector<size_t> &argBytes, RowPipelinePlan &plan) {
+  plan = RowPipelinePlan();
+  plan.rowBytes.assign(argBytes.size(), 0);
+  std::vector<char> seen(argBytes.size(), 0);
+  if (d.kernelClass == KernelClass::Matmul) {
+    const MatmulSpec &m = d.matmul;
+    int64_t M, N, K;
+    if (Status s = evalDim(m.m, tiling, M); !s) return s;
+    if (Status s = evalDim(m.n, tiling, N); !s) return s;
+    if (Status s = evalDim(m.k, tiling, K); !s) return s;
+    plan.rows = M;
+    plan.possible = noteSlice(plan.rowBytes, seen, m.aArg, static_cast<size_t>(K) * dtypeBytes(m.inType)) &&
+                    noteSlice(plan.rowBytes, seen, m.outArg, static_cast<size_t>(N) * dtypeBytes(m.outType)) && K > 0 && N > 0;
+    return Status::success();
+  }
+  if (d.kernelClass == KernelClass::Transpose || d.groups.size() != 1) return Status::success();
+  const GroupSpec &g = d.groups[0];
+  std::vector<int64_t> domain;
+  if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
+  if (domain.empty()) return Status::success();
+  plan.rows = domain[0];
+  bool ok = true;
+  const bool gather = d.kernelClass == KernelClass::Gather;
+  for (size_t i = 0; i < g.loads.size() && ok; ++i) {
+    if (gather && i == 0) {
+      // the table: whole for a row gather; row i of the output reads row i of it for a column gather
+      std::vector<int64_t> tshape;
+      if (!evalDims(g.loads[0].shape, tiling, tshape) || tshape.size() != 2) { ok = false; break; }
+      ok = noteSlice(plan.rowBytes, seen, g.loads[0].arg,
+                     g.gatherAxis == 1 ? static_cast<size_t>(tshape[1]) * dtypeBytes(g.loads[0].dtype) : 0);
+      continue;
+    }
+    ok = classifyView(g.loads[i], tiling, plan.rowBytes, seen);
+  }
+  if (ok && gather)
+    ok = noteSlice(plan.rowBytes, seen, g.indices.arg, g.gatherAxis == 0 ? dtypeBytes(g.indices.dtype) : 0);
+  if (ok) ok = classifyView(g.store, tiling, plan.rowBytes, seen) && plan.rowBytes[g.store.arg] > 0;
+  // every sliced argument must be exactly rows * rowBytes long
+  for (size_t a = 0; a < argBytes.size() && ok; ++a)
+    if (plan.rowBytes[a] && plan.rowBytes[a] * static_cast<size_t>(plan.rows) != argBytes[a]) ok = false;
+  plan.possible = ok;
   return Status::success();
 }
 

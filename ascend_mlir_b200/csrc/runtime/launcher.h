@@ -22,6 +22,10 @@ struct LaunchArgs {
   void *workspace = nullptr;
   size_t workspaceBytes = 0;
   int blockDim = 0;  // CTAs to launch; <= 0 lets the library choose
+  // Optional sub-range [rowBegin, rowEnd) of the leading iteration dim (single-group descriptors and
+  // matmul rows); rowEnd < 0 = everything.  Used to pipeline host copies with compute.
+  int64_t rowBegin = 0;
+  int64_t rowEnd = -1;
   cudaStream_t stream = nullptr;
   int device = 0;
 };
@@ -34,6 +38,18 @@ struct LaunchInfo {
 // Scratch bytes (status block included) the descriptor needs at these tiling values.
 Status requiredWorkspaceBytes(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, int device,
                               size_t &bytes);
+
+// How the host path may cut a run into leading-axis chunks: `rows` is the leading extent and, per
+// kernel argument, rowBytes > 0 means "rows [b, e) of the work touch bytes [b*rowBytes, e*rowBytes) of
+// this argument", 0 means the whole argument is needed by every chunk.  possible = false when the
+// descriptor cannot be chunked (several groups, permuted leading dims, sliced views).
+struct RowPipelinePlan {
+  bool possible = false;
+  int64_t rows = 0;
+  std::vector<size_t> rowBytes;
+};
+Status planRowPipeline(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling,
+                       const std::vector<size_t> &argBytes, RowPipelinePlan &plan);
 
 Status launchDescriptor(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args,
                         LaunchInfo &info);
