@@ -38,7 +38,12 @@ CU_SOURCES = {
     "kernels/matmul_tcgen05.cu": [],
 }
 CPP_SOURCES = ["common/json.cpp", "runtime/descriptor.cpp", "runtime/launcher.cpp", "runtime/executor.cpp",
-               "runtime/capi.cpp"]
+               "support/npy_io.cpp", "support/tiling_schema.cpp", "execution/output_comparator.cpp",
+               "execution/task_graph.cpp", "execution/run_manifest.cpp", "execution/artifact_compiler.cpp",
+               "execution/execution_session.cpp", "runtime/capi.cpp"]
+# command-line tools (reference: tools/runtime-session, tools/autotuner), linked with the same objects
+TOOLS = {"runtime-session": "tools/runtime_session_main.cpp", "autotuner": "tools/autotuner_main.cpp"}
+BINDIR = PKG / "bin"
 
 
 def _headers_digest() -> str:
@@ -102,11 +107,21 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
             logs = list(pool.map(work, jobs))
+    cuda_libs = ["-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread"]
     if jobs or not LIB.exists():
-        link = [CXX, "-shared", "-o", str(LIB)] + [str(o) for o in objs] + [
-            "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread",
-            "-Wl,--no-undefined", "-Wl,-z,defs"]
+        link = [CXX, "-shared", "-o", str(LIB)] + [str(o) for o in objs] + cuda_libs + ["-Wl,--no-undefined", "-Wl,-z,defs"]
         _run(link, verbose)
+    BINDIR.mkdir(exist_ok=True)
+    lib_objs = [str(o) for o in objs if not str(o).endswith("runtime_capi.cpp.o")]
+    for tool, rel in TOOLS.items():
+        src = CSRC / rel
+        exe = BINDIR / tool
+        tobj = BUILD / (rel.replace("/", "_") + ".o")
+        stamp = hdr + "|".join(CXX_FLAGS)
+        if force or jobs or _stale(tobj, src, stamp) or not exe.exists():
+            _run([CXX] + CXX_FLAGS + ["-c", str(src), "-o", str(tobj)], verbose)
+            _mark(tobj, src, stamp)
+            _run([CXX, "-o", str(exe), str(tobj)] + lib_objs + cuda_libs, verbose)
     if ptxas_info:
         print("".join(logs))
     return LIB

@@ -1,0 +1,71 @@
+#include "execution/artifact_compiler.h"
+
+#include <sys/stat.h>
+
+#include <cerrno>
+#include <cstring>
+#include <fstream>
+
+#include "runtime/descriptor.h"
+#include "support/tiling_schema.h"
+
+namespace afir {
+namespace {
+bool makeDirs(const std::string &path) {
+  std::string cur;
+  for (size_t i = 0; i <= path.size(); ++i) {
+    if (i == path.size() || path[i] == '/') {
+      if (!cur.empty() && ::mkdir(cur.c_str(), 0755) != 0 && errno != EEXIST) return false;
+    }
+    if (i < path.size()) cur.push_back(path[i]);
+  }
+  return true;
+}
+} // namespace
+
+Status compileArtifact(const CompileRequest &request, KernelArtifact &artifact) {
+  if (request.kernelSource.empty()) return Status::error("kernel source path is required");
+  if (request.outputDir.empty()) return Status::error("output directory is required");
+  const bool knownArch = request.arch == "sm_100a" || request.arch.find("dav-") == 0;
+  if (!knownArch) return Status::error("unsupported arch '" + request.arch + "' (this library is sm_100a only)");
+  std::vector<uint8_t> src;
+  if (Status s = readFileBytes(request.kernelSource, src); !s) return s;
+  LaunchDescriptor desc;
+  if (Status s = parseDescriptorBinary(src.data(), src.size(), desc); !s)
+    return Status::error(request.kernelSource + ": " + s.message());
+  const std::string name = request.kernelName.empty() ? desc.kernel : request.kernelName;
+  if (desc.kernel != name)
+    return Status::error(request.kernelSource + ": defines kernel '" + desc.kernel + "', not '" + name + "'");
+  if (!makeDirs(request.outputDir)) return Status::error("cannot create " + request.outputDir);
+  std::vector<uint8_t> bin;
+  if (src.size() >= 4 && std::memcmp(src.data(), "AFCU", 4) == 0) bin = src;
+  else bin = wrapDescriptorContainer(std::string(src.begin(), src.end()));
+  const std::string binPath = request.outputDir + "/" + name + ".bin";
+  {
+    std::ofstream os(binPath, std::ios::binary | std::ios::trunc);
+    os.write(reinterpret_cast<const char *>(bin.data()), static_cast<std::streamsize>(bin.size()));
+    if (!os) return Status::error("cannot write " + binPath);
+  }
+  const std::string manifestPath = request.outputDir + "/manifest.txt";
+  const bool matmul = desc.kernelClass == KernelClass::Matmul;
+  {
+    std::ofstream os(manifestPath, std::ios::trunc);
+    os << "kernel_name=" << desc.kernel << "\n"
+       << "soc_version=" << request.socVersion << "\n"
+       << "kernel_kind=" << (matmul ? "mix" : "vec") << "\n"
+       << "kernel_class=" << kernelClassName(desc.kernelClass) << "\n"
+       << "device_binary_path=" << binPath << "\n"
+       << "manifest_path=" << manifestPath << "\n";
+    if (!os) return Status::error("cannot write " + manifestPath);
+  }
+  artifact = KernelArtifact();
+  artifact.kernelName = desc.kernel;
+  artifact.kernelKind = matmul ? KernelKind::Mix : KernelKind::Vec;
+  artifact.socVersion = request.socVersion;
+  artifact.artifactRoot = request.outputDir;
+  artifact.deviceBinaryPath = binPath;
+  artifact.manifestPath = manifestPath;
+  return Status::success();
+}
+
+} // namespace afir

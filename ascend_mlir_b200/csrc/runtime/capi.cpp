@@ -13,6 +13,7 @@
 #include <string>
 #include <vector>
 
+#include "execution/artifact_compiler.h"
 #include "runtime/executor.h"
 
 using namespace afir;
@@ -92,44 +93,15 @@ AFIR_EXPORT int afirt_compiler_compile(AfirtCompiler compiler, const char *src_f
   if (!src_file || !*src_file) { writeErr(out_bin_path, buf_len, "kernel source path is required"); return 1; }
   if (!output_dir || !*output_dir) { writeErr(out_bin_path, buf_len, "output directory is required"); return 1; }
   if (!kernel_name || !*kernel_name) { writeErr(out_bin_path, buf_len, "kernel name is required"); return 1; }
-  const bool knownArch = h->arch == "sm_100a" || h->arch.find("dav-") == 0;
-  if (!knownArch) { writeErr(out_bin_path, buf_len, "unsupported arch '" + h->arch + "' (this library is sm_100a only)"); return 1; }
-
-  std::vector<uint8_t> src;
-  std::string err;
-  if (!readFile(src_file, src, err)) { writeErr(out_bin_path, buf_len, err); return 1; }
-  LaunchDescriptor desc;
-  if (Status s = parseDescriptorBinary(src.data(), src.size(), desc); !s) {
-    writeErr(out_bin_path, buf_len, std::string(src_file) + ": " + s.message());
-    return 1;
-  }
-  if (desc.kernel != kernel_name) {
-    writeErr(out_bin_path, buf_len, std::string(src_file) + ": defines kernel '" + desc.kernel + "', not '" + kernel_name + "'");
-    return 1;
-  }
-  const std::string dir = output_dir;
-  if (!makeDirs(dir)) { writeErr(out_bin_path, buf_len, "cannot create " + dir); return 1; }
-  // the container holds the descriptor text as given (bare JSON) or is passed through unchanged
-  std::vector<uint8_t> bin;
-  if (src.size() >= 4 && std::memcmp(src.data(), "AFCU", 4) == 0) bin = src;
-  else bin = wrapDescriptorContainer(std::string(src.begin(), src.end()));
-  const std::string binPath = dir + "/" + kernel_name + ".bin";
-  {
-    std::ofstream os(binPath, std::ios::binary | std::ios::trunc);
-    os.write(reinterpret_cast<const char *>(bin.data()), static_cast<std::streamsize>(bin.size()));
-    if (!os) { writeErr(out_bin_path, buf_len, "cannot write " + binPath); return 1; }
-  }
-  const std::string manifestPath = dir + "/manifest.txt";
-  {
-    std::ofstream os(manifestPath, std::ios::trunc);
-    os << "kernel_name=" << desc.kernel << "\n"
-       << "soc_version=" << h->socVersion << "\n"
-       << "kernel_kind=" << (desc.kernelClass == KernelClass::Matmul ? "mix" : "vec") << "\n"
-       << "kernel_class=" << kernelClassName(desc.kernelClass) << "\n"
-       << "device_binary_path=" << binPath << "\n"
-       << "manifest_path=" << manifestPath << "\n";
-    if (!os) { writeErr(out_bin_path, buf_len, "cannot write " + manifestPath); return 1; }
-  }
+  CompileRequest request;
+  request.kernelSource = src_file;
+  request.outputDir = output_dir;
+  request.kernelName = kernel_name;
+  request.socVersion = h->socVersion;
+  request.arch = h->arch;
+  KernelArtifact artifact;
+  if (Status s = compileArtifact(request, artifact); !s) { writeErr(out_bin_path, buf_len, s.message()); return 1; }
+  const std::string binPath = artifact.deviceBinaryPath;
   writeErr(out_bin_path, buf_len, binPath);
   return 0;
 }

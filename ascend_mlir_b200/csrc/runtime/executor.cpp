@@ -328,6 +328,48 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   return Status::success();
 }
 
+Status CudaExecutor::profileResident(const RunRequest &req, int repeats, double &medianMicroseconds) {
+  std::shared_ptr<const LaunchDescriptor> desc;
+  std::map<std::string, int64_t> tiling;
+  if (Status s = validate(req, desc, tiling); !s) return s;
+  if (Status s = ensureStream(); !s) return s.withStage("cuda:device");
+  const size_t numArgs = static_cast<size_t>(req.numInputs + req.numOutputs);
+  if (slots_.size() < numArgs) return Status::error("[cuda:profiling] no resident buffers: run the kernel first");
+  LaunchArgs args;
+  args.device = device_;
+  args.stream = static_cast<cudaStream_t>(stream_);
+  args.blockDim = req.blockDim;
+  for (int i = 0; i < req.numInputs; ++i) { args.argPtrs.push_back(slots_[i].ptr); args.argBytes.push_back(req.inputBytes[i]); }
+  for (int i = 0; i < req.numOutputs; ++i) {
+    args.argPtrs.push_back(slots_[req.numInputs + i].ptr);
+    args.argBytes.push_back(req.outputBytes[i]);
+  }
+  args.workspace = workspace_.ptr;
+  args.workspaceBytes = workspace_.capacity;
+  cudaEvent_t e0, e1;
+  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return Status::error("[cuda:profiling] cannot create events");
+  std::vector<float> times;
+  Status result = Status::success();
+  for (int r = 0; r < repeats + 2 && result; ++r) {  // two warm-up launches
+    cudaEventRecord(e0, args.stream);
+    LaunchInfo info;
+    Status ls = launchDescriptor(*desc, tiling, args, info);
+    cudaEventRecord(e1, args.stream);
+    totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
+    if (!ls) { result = ls.withStage("cuda:profiling"); break; }
+    if (cudaEventSynchronize(e1) != cudaSuccess) { result = Status::error("[cuda:profiling] kernel execution failed"); break; }
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (r >= 2) times.push_back(ms * 1000.0f);
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (!result) return result;
+  std::sort(times.begin(), times.end());
+  medianMicroseconds = times.empty() ? 0.0 : times[times.size() / 2];
+  return Status::success();
+}
+
 Status CudaExecutor::synchronize(void *stream) {
   if (!initialized_) return Status::error("executor has not been initialized");
   cudaError_t e = cudaSetDevice(device_);

@@ -54,6 +54,10 @@ public:
   // Waits for `stream` (null = the executor's own) and surfaces device-side status words.
   Status synchronize(void *stream);
 
+  // Re-launches the kernel of `req` on the device buffers the last runHost of the same request left
+  // resident and returns the median kernel time over `repeats` launches (CUDA events on the executor stream).
+  Status profileResident(const RunRequest &req, int repeats, double &medianMicroseconds);
+
   int lastLaunchCount() const { return lastLaunchCount_; }
   uint64_t totalLaunchCount() const { return totalLaunchCount_; }
 

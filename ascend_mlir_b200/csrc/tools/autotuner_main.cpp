@@ -1,0 +1,353 @@
+// autotuner: exhaustive search over the non-fixed parameters of a tiling_space.json; every candidate is
+// run through an execution session with validation and profiling, candidates are ranked by score
+// (median kernel microseconds, ascending) and the winner is written to best_config.json.
+// Command line, PASS/FAIL lines and best_config.json keys follow the reference's
+// tools/autotuner/autotuner_main.cpp:75-129,293-371,499-856; the parameters searched are B200 tile and
+// launch parameters (CTA size, vectors in flight, ring depth, ...) and the score is CUDA-event time.
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <fstream>
+#include <iostream>
+#include <sstream>
+
+#include "common/json.h"
+#include "execution/artifact_compiler.h"
+#include "execution/execution_session.h"
+#include "execution/run_manifest.h"
+#include "tools/cli_args.h"
+
+using namespace afir;
+
+namespace {
+
+struct TilingParam {
+  std::string name, type = "int64", shapeKey;
+  bool fixed = false;
+  std::vector<int64_t> values;
+};
+struct TilingSpace {
+  std::string kernelName, kernelFile, soc, blockDimExpr;
+  std::vector<TilingParam> params;
+};
+struct SearchResult {
+  std::map<std::string, int64_t> config;
+  int64_t blockDim = 0;
+  double score = 0.0;
+  double maxAbsDiff = 0.0;
+  bool passed = false;
+  std::string profilePath, error;
+};
+
+std::map<std::string, int64_t> parseKV(const std::string &s) {
+  std::map<std::string, int64_t> m;
+  std::istringstream ss(s);
+  std::string tok;
+  while (std::getline(ss, tok, ',')) {
+    const size_t eq = tok.find('=');
+    if (eq == std::string::npos) continue;
+    m[tok.substr(0, eq)] = std::strtoll(tok.c_str() + eq + 1, nullptr, 10);
+  }
+  return m;
+}
+
+int64_t lookupToken(const std::string &name, const std::map<std::string, int64_t> &vars) {
+  auto it = vars.find(name);
+  if (it != vars.end()) return it->second;
+  char *end = nullptr;
+  const long long v = std::strtoll(name.c_str(), &end, 10);
+  if (name.empty() || !end || *end != '\0') {
+    std::cerr << "Warning: unrecognized token in block_dim_expr: '" << name << "', treating as 1\n";
+    return 1;
+  }
+  return v;
+}
+
+// product of terms; a term is an integer, a name, "a/b" or "ceil(a/b)"
+int64_t evalBlockDimExpr(const std::string &expr, const std::map<std::string, int64_t> &vars) {
+  std::string e;
+  for (char c : expr)
+    if (c != ' ' && c != '\t') e.push_back(c);
+  if (e.empty()) return 0;
+  int64_t product = 1;
+  size_t pos = 0;
+  while (pos <= e.size()) {
+    size_t star = e.find('*', pos);
+    std::string term = e.substr(pos, star == std::string::npos ? std::string::npos : star - pos);
+    bool isCeil = false;
+    if (term.size() > 6 && term.compare(0, 5, "ceil(") == 0 && term.back() == ')') {
+      term = term.substr(5, term.size() - 6);
+      isCeil = true;
+    }
+    const size_t slash = term.find('/');
+    int64_t v;
+    if (slash == std::string::npos) v = lookupToken(term, vars);
+    else {
+      const int64_t a = lookupToken(term.substr(0, slash), vars), b = lookupToken(term.substr(slash + 1), vars);
+      v = b == 0 ? 1 : (isCeil ? (a + b - 1) / b : a / b);
+    }
+    product *= v;
+    if (star == std::string::npos) break;
+    pos = star + 1;
+  }
+  return product;
+}
+
+Status loadTilingSpace(const std::string &path, TilingSpace &ts) {
+  std::string text;
+  if (Status s = readFileText(path, text); !s) return Status::error("Cannot open " + path);
+  json::Value root;
+  std::string err;
+  if (!json::parse(text, root, err)) return Status::error("JSON parse error in " + path);
+  if (!root.isObject()) return Status::error("JSON root is not an object in " + path);
+  ts.kernelName = root.getString("kernel");
+  ts.kernelFile = root.getString("kernel_file");
+  ts.soc = root.getString("soc");
+  ts.blockDimExpr = root.getString("block_dim_expr");
+  const json::Value *params = root.find("tiling_params");
+  if (!params || !params->isArray()) return Status::error("Missing tiling_params in " + path);
+  for (const auto &pv : params->asArray()) {
+    if (!pv.isObject()) continue;
+    TilingParam p;
+    p.name = pv.getString("name");
+    p.type = pv.getString("type", "int64");
+    p.fixed = pv.getBool("fixed", false);
+    p.shapeKey = pv.getString("shape_key");
+    if (const json::Value *arr = pv.find("values"); arr && arr->isArray())
+      for (const auto &v : arr->asArray())
+        if (v.isInt()) p.values.push_back(v.asInt());
+    if (!p.fixed && p.values.empty() && pv.find("min")) {
+      const int64_t mn = pv.getInt("min"), mx = pv.getInt("max"), st = pv.getInt("step", 1);
+      if (st > 0)
+        for (int64_t x = mn; x <= mx; x += st) p.values.push_back(x);
+    }
+    if (p.fixed && pv.find("value")) p.values.insert(p.values.begin(), pv.getInt("value"));
+    ts.params.push_back(std::move(p));
+  }
+  return Status::success();
+}
+
+void enumerate(const std::vector<const TilingParam *> &vars, size_t idx, std::vector<int64_t> &cur,
+               std::vector<std::vector<int64_t>> &out) {
+  if (idx == vars.size()) { out.push_back(cur); return; }
+  for (int64_t v : vars[idx]->values) {
+    cur[idx] = v;
+    enumerate(vars, idx + 1, cur, out);
+  }
+}
+
+void usage() {
+  std::cout << "USAGE: autotuner --space <tiling_space.json> --inputs <a.npy,b.npy> --expected <out.npy> --shape M=..,N=..\n"
+               "                 [--kernel <descriptor>] [--artifact-root <dir>] [--output best_config.json]\n"
+               "                 [--soc <name>] [--atol 1.0] [--rtol 1e-2] [--profile-out <dir>] [--kernel-kind vec|cube|mix]\n";
+}
+
+} // namespace
+
+int main(int argc, char **argv) {
+  CliArgs args({"space", "kernel", "inputs", "expected", "shape", "output", "artifact-root", "kernel-kind", "soc", "atol", "rtol",
+                "profile-out"},
+               {});
+  std::string err;
+  if (!args.parse(argc, argv, err)) { std::cerr << "autotuner: " << err << "\n"; return 1; }
+  if (args.help()) { usage(); return 0; }
+  for (const char *required : {"space", "inputs", "expected", "shape"})
+    if (!args.has(required)) { std::cerr << "autotuner: for the --" << required << " option: must be specified at least once!\n"; return 1; }
+
+  TilingSpace ts;
+  if (Status s = loadTilingSpace(args.get("space"), ts); !s) { std::cerr << "Error: " << s.message() << "\n"; return 1; }
+  const std::map<std::string, int64_t> shape = parseKV(args.get("shape"));
+  const double atol = std::strtod(args.get("atol", "1.0").c_str(), nullptr);
+  const double rtol = std::strtod(args.get("rtol", "1e-2").c_str(), nullptr);
+
+  // artifact: an existing root, or compile the kernel once
+  KernelArtifact artifact;
+  char tmpl[] = "/tmp/afir-autotuner-XXXXXX";
+  if (!::mkdtemp(tmpl)) { std::cerr << "Error: cannot create a working directory under /tmp\n"; return 1; }
+  const std::string workDir = tmpl;
+  if (args.has("artifact-root")) {
+    if (Status s = loadArtifactFromRoot(args.get("artifact-root"), artifact); !s) { std::cerr << "Error: " << s.message() << "\n"; return 1; }
+  } else {
+    std::string kernelFile = args.get("kernel", ts.kernelFile);
+    if (kernelFile.empty()) { std::cerr << "Error: no kernel: give --kernel, --artifact-root or kernel_file in the tiling space\n"; return 1; }
+    if (!args.has("kernel") && kernelFile[0] != '/') {
+      const std::string space = args.get("space");
+      const size_t slash = space.rfind('/');
+      if (slash != std::string::npos) kernelFile = space.substr(0, slash + 1) + kernelFile;
+    }
+    CompileRequest request;
+    request.kernelSource = kernelFile;
+    request.kernelName = ts.kernelName;
+    request.outputDir = workDir + "/artifact";
+    request.socVersion = args.get("soc", ts.soc.empty() ? "sm_100a" : ts.soc);
+    if (Status s = compileArtifact(request, artifact); !s) { std::cerr << "Error: " << s.message() << "\n"; return 1; }
+  }
+
+  std::vector<std::string> inputFiles;
+  {
+    std::istringstream ss(args.get("inputs"));
+    std::string tok;
+    while (std::getline(ss, tok, ','))
+      if (!tok.empty()) inputFiles.push_back(tok);
+  }
+  NDArray expected;
+  if (Status s = loadNpy(args.get("expected"), expected); !s) { std::cerr << "Error: " << s.message() << "\n"; return 1; }
+
+  std::vector<const TilingParam *> searchVars;
+  for (const auto &p : ts.params)
+    if (!p.fixed && !p.values.empty()) searchVars.push_back(&p);
+  std::vector<std::vector<int64_t>> combos;
+  std::vector<int64_t> cur(searchVars.size(), 0);
+  enumerate(searchVars, 0, cur, combos);
+  std::cout << "Search space: " << combos.size() << " candidate(s) over " << searchVars.size() << " parameter(s)\n";
+
+  const char *dev = std::getenv("AFIR_CUDA_DEVICE");
+  auto driver = createCudaBackendDriver(dev && *dev ? std::atoi(dev) : 0);
+  ExecutionSession session("cuda", driver);
+  std::vector<SearchResult> results;
+  for (size_t ci = 0; ci < combos.size(); ++ci) {
+    SearchResult sr;
+    std::map<std::string, int64_t> vars = shape;
+    std::vector<std::pair<std::string, int64_t>> ordered;
+    std::string missing;
+    size_t searchIdx = 0;
+    for (const auto &p : ts.params) {
+      int64_t v = 0;
+      if (!p.fixed && !p.values.empty()) v = combos[ci][searchIdx++];
+      else if (!p.shapeKey.empty()) {
+        auto it = shape.find(p.shapeKey);
+        if (it == shape.end()) { missing = p.shapeKey; break; }
+        v = it->second;
+      } else if (!p.values.empty()) v = p.values.front();
+      ordered.emplace_back(p.name, v);
+      vars[p.name] = v;
+      sr.config[p.name] = v;
+    }
+    std::cout << "[" << (ci + 1) << "/" << combos.size() << "]";
+    for (size_t k = 0; k < searchVars.size(); ++k) std::cout << " " << searchVars[k]->name << "=" << combos[ci][k];
+    if (!missing.empty()) {
+      std::cout << " FAIL  shape key '" << missing << "' not given in --shape\n";
+      results.push_back(sr);
+      continue;
+    }
+    sr.blockDim = evalBlockDimExpr(ts.blockDimExpr, vars);
+    std::cout << " block_dim=" << sr.blockDim;
+
+    // tiling bytes in schema order
+    std::vector<uint8_t> bytes;
+    for (size_t i = 0; i < ordered.size(); ++i) {
+      const std::string &type = ts.params[i].type;
+      if (type == "int32" || type == "int32_t") {
+        const int32_t w = static_cast<int32_t>(ordered[i].second);
+        bytes.insert(bytes.end(), reinterpret_cast<const uint8_t *>(&w), reinterpret_cast<const uint8_t *>(&w) + 4);
+      } else {
+        const int64_t w = ordered[i].second;
+        bytes.insert(bytes.end(), reinterpret_cast<const uint8_t *>(&w), reinterpret_cast<const uint8_t *>(&w) + 8);
+      }
+    }
+    const std::string candDir = workDir + "/cand" + std::to_string(ci);
+    ::mkdir(candDir.c_str(), 0755);
+    const std::string tilingPath = candDir + "/tiling.bin";
+    {
+      std::ofstream os(tilingPath, std::ios::binary | std::ios::trunc);
+      os.write(reinterpret_cast<const char *>(bytes.data()), static_cast<std::streamsize>(bytes.size()));
+    }
+    RuntimeTask task;
+    task.taskId = "candidate" + std::to_string(ci);
+    task.artifact = artifact;
+    for (size_t i = 0; i < inputFiles.size(); ++i) {
+      TensorBinding b;
+      b.name = "input" + std::to_string(i);
+      b.path = inputFiles[i];
+      task.invocation.inputs.push_back(b);
+    }
+    TensorBinding out;
+    out.name = "out";
+    out.path = candDir + "/output0.npy";
+    out.shape = expected.shape;
+    out.dtype = expected.dtype;
+    task.invocation.outputs.push_back(out);
+    TensorBinding exp;
+    exp.name = "expected";
+    exp.path = args.get("expected");
+    task.invocation.expectedOutputs.push_back(exp);
+    task.invocation.tiling.present = true;
+    task.invocation.tiling.binaryPath = tilingPath;
+    task.invocation.blockDim = static_cast<int>(sr.blockDim);
+    task.invocation.enableProfiling = true;
+    task.invocation.atol = atol;
+    task.invocation.rtol = rtol;
+    TaskGraph graph;
+    graph.addTask(task);
+    const std::string profileRoot = args.has("profile-out") ? args.get("profile-out") + "/cand" + std::to_string(ci) : candDir;
+    SessionRunSummary summary = session.run(graph, profileRoot);
+    if (!summary.success) {
+      sr.error = summary.rawErrorMessage;
+      std::cout << " FAIL  " << summary.rawErrorMessage << "\n";
+      results.push_back(sr);
+      continue;
+    }
+    if (summary.profileTrace.events.empty()) {
+      std::cout << " FAIL  no profile score was produced\n";
+      results.push_back(sr);
+      continue;
+    }
+    sr.score = summary.profileTrace.events.front().score;
+    sr.profilePath = summary.profileTrace.events.front().artifactPath;
+    sr.maxAbsDiff = summary.results.empty() ? 0.0 : summary.results.front().comparison.maxAbsDiff;
+    sr.passed = true;
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "%.3f", sr.score);
+    std::cout << " PASS score=" << buf << "\n";
+    results.push_back(sr);
+  }
+
+  std::vector<SearchResult> passed;
+  for (const auto &r : results)
+    if (r.passed) passed.push_back(r);
+  std::stable_sort(passed.begin(), passed.end(), [](const SearchResult &a, const SearchResult &b) { return a.score < b.score; });
+  std::cout << "Candidates: " << results.size() << ", passed: " << passed.size() << "\n";
+  if (passed.empty()) {
+    std::cerr << "Error: no candidate passed validation\n";
+    return 1;
+  }
+  const SearchResult &best = passed.front();
+  json::Value root;
+  root.set("kernel_name", artifact.kernelName);
+  root.set("kernel_type", artifact.kernelKind == KernelKind::Cube ? "cube" : artifact.kernelKind == KernelKind::Mix ? "mix" : "vec");
+  root.set("soc", artifact.socVersion);
+  root.set("artifact_root", artifact.artifactRoot);
+  root.set("manifest_path", artifact.manifestPath);
+  root.set("device_binary_path", artifact.deviceBinaryPath);
+  if (args.has("profile-out")) root.set("profile_out", args.get("profile-out"));
+  root.set("kernel_file", ts.kernelFile);
+  json::Value bestObj;
+  bestObj.set("block_dim", best.blockDim);
+  bestObj.set("cycle_count", best.score);
+  bestObj.set("score", best.score);
+  bestObj.set("score_unit", "kernel_microseconds");
+  bestObj.set("max_abs_diff", best.maxAbsDiff);
+  bestObj.set("profile_path", best.profilePath);
+  root.set("best", std::move(bestObj));
+  json::Value config;
+  for (const auto &kv : best.config) config.set(kv.first, kv.second);
+  root.set("config", std::move(config));
+  json::Value shapeObj;
+  for (const auto &kv : shape) shapeObj.set(kv.first, kv.second);
+  root.set("shape", std::move(shapeObj));
+  const std::string outPath = args.get("output", "best_config.json");
+  {
+    std::ofstream os(outPath, std::ios::trunc);
+    os << json::dump(root, 2) << "\n";
+    if (!os) { std::cerr << "Error: cannot write best-config JSON\n"; return 1; }
+  }
+  char buf[64];
+  std::snprintf(buf, sizeof(buf), "%.3f", best.score);
+  std::cout << "Best: score=" << buf << " block_dim=" << best.blockDim;
+  for (size_t k = 0; k < searchVars.size(); ++k) std::cout << " " << searchVars[k]->name << "=" << best.config.at(searchVars[k]->name);
+  std::cout << "\nWrote " << outPath << "\n";
+  return 0;
+}

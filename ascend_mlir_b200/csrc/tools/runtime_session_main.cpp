@@ -1,0 +1,142 @@
+// runtime-session: plan and run a task graph of kernel launches on the CUDA backend.
+// Same command line, stdout/stderr key=value lines and exit codes (0 ok, 2 plan/run failure, 4 usage or
+// preparation failure) as the reference's tools/runtime-session/runtime_session_main.cpp:30-110,244-397.
+#include <cstdio>
+#include <cstdlib>
+#include <iostream>
+
+#include "execution/artifact_compiler.h"
+#include "execution/execution_session.h"
+#include "execution/run_manifest.h"
+#include "tools/cli_args.h"
+
+using namespace afir;
+
+namespace {
+
+// Testing-only driver: reports success without touching a device (the reference exposes the same seam as
+// --testing-driver npu-success).
+class SuccessfulTestingDriver final : public ExecutionBackendDriver {
+public:
+  Status run(const ExecutionRequest &request, ExecutionResult &result) override {
+    result = ExecutionResult();
+    result.taskId = request.task.taskId;
+    for (const TensorBinding &b : request.task.invocation.outputs) result.producedFiles.push_back(b.path);
+    ProfileEvent ev;
+    ev.taskId = request.task.taskId;
+    ev.backend = "cuda";
+    ev.artifactPath = request.workingDirectory + "/" + request.task.taskId + ".cuda-profile.json";
+    result.profileTrace.sessionId = request.sessionId;
+    result.profileTrace.events.push_back(ev);
+    return Status::success();
+  }
+};
+
+void usage() {
+  std::cout << "OVERVIEW: task graph runtime planning and execution CLI for artifacts and session graphs\n\n"
+               "USAGE: runtime-session [options]\n\nOPTIONS:\n"
+               "  --artifact-root=<dir>   Use an existing artifact root with a real manifest\n"
+               "  --kernel=<file>         Kernel source (launch descriptor) to compile into a runtime artifact\n"
+               "  --name=<string>         Kernel name override when compiling a new artifact\n"
+               "  --output=<dir>          Artifact output directory when compiling\n"
+               "  --soc=<string>          Target SoC version when compiling a new artifact\n"
+               "  --kernel-kind=<string>  Kernel kind when compiling: vec, cube, or mix\n"
+               "  --task-id=<string>      Task id to register in the task graph\n"
+               "  --run-manifest=<file>   JSON manifest describing artifact root, bindings, and execution settings\n"
+               "  --run                   Execute the prepared task graph runtime session\n";
+}
+
+void printRunError(const ExecutionSession &session, const SessionRunSummary &summary) {
+  std::cerr << "session.backend=" << session.backendName() << "\n";
+  std::cerr << "session.result=error\n";
+  if (summary.validationRan && summary.errorStage == "validate") std::cerr << "session.validation=fail\n";
+  if (!summary.errorStage.empty()) std::cerr << "session.error_stage=" << summary.errorStage << "\n";
+  std::cerr << "session.error=" << summary.errorMessage << "\n";
+  std::cerr << "Error: " << summary.rawErrorMessage << "\n";
+}
+
+} // namespace
+
+int main(int argc, char **argv) {
+  CliArgs args({"artifact-root", "kernel", "name", "output", "soc", "kernel-kind", "task-id", "run-manifest", "testing-driver",
+                "cann-mlir", "npy-dir"},
+               {"run"});
+  std::string err;
+  if (!args.parse(argc, argv, err)) {
+    std::cerr << "runtime-session: " << err << "\n";
+    return 1;
+  }
+  if (args.help()) { usage(); return 0; }
+
+  std::string backendName = "cuda";
+  TaskGraph graph;
+  if (args.has("run-manifest")) {
+    RunManifestSpec spec;
+    if (Status s = loadRunManifest(args.get("run-manifest"), spec); !s) { std::cerr << "Error: " << s.message() << "\n"; return 4; }
+    if (Status s = buildTaskGraph(spec, graph); !s) { std::cerr << "Error: " << s.message() << "\n"; return 4; }
+  } else {
+    const bool hasRoot = args.has("artifact-root"), hasKernel = args.has("kernel");
+    if (hasRoot == hasKernel) { std::cerr << "Error: provide exactly one of --artifact-root or --kernel\n"; return 4; }
+    KernelArtifact artifact;
+    if (hasRoot) {
+      if (Status s = loadArtifactFromRoot(args.get("artifact-root"), artifact); !s) { std::cerr << "Error: " << s.message() << "\n"; return 4; }
+    } else {
+      const std::string kind = args.get("kernel-kind", "mix");
+      if (kind != "vec" && kind != "cube" && kind != "mix") { std::cerr << "Error: unsupported kernel kind: " << kind << "\n"; return 4; }
+      CompileRequest request;
+      request.kernelSource = args.get("kernel");
+      request.kernelName = args.get("name");
+      request.outputDir = args.get("output", "./build/runtime-session-artifact");
+      request.socVersion = args.get("soc", "sm_100a");
+      if (Status s = compileArtifact(request, artifact); !s) { std::cerr << "Error: " << s.message() << "\n"; return 4; }
+    }
+    std::cout << "artifact.kernel_name=" << artifact.kernelName << "\n";
+    std::cout << "artifact.root=" << artifact.artifactRoot << "\n";
+    std::cout << "artifact.manifest=" << artifact.manifestPath << "\n";
+    std::cout << "artifact.soc=" << artifact.socVersion << "\n";
+    RuntimeTask task;
+    task.taskId = args.get("task-id", "main");
+    task.artifact = artifact;
+    if (Status s = graph.addTask(task); !s) { std::cerr << "Error: " << s.message() << "\n"; return 4; }
+  }
+
+  std::shared_ptr<ExecutionBackendDriver> driver;
+  const std::string testing = args.get("testing-driver");
+  if (testing.empty()) {
+    const char *dev = std::getenv("AFIR_CUDA_DEVICE");
+    driver = createCudaBackendDriver(dev && *dev ? std::atoi(dev) : 0);
+  } else if (testing == "success" || testing == "npu-success" || testing == "cuda-success") {
+    driver = std::make_shared<SuccessfulTestingDriver>();
+  } else {
+    std::cerr << "Error: unsupported testing driver: " << testing << "\n";
+    return 4;
+  }
+
+  ExecutionSession session(backendName, driver);
+  SessionPlan plan;
+  if (Status s = session.plan(graph, plan); !s) { std::cerr << "Error: " << s.message() << "\n"; return 2; }
+  std::cout << "session.plan.tasks=" << plan.orderedTaskIds.size() << "\n";
+  for (size_t i = 0; i < plan.orderedTaskIds.size(); ++i) std::cout << "session.plan[" << i << "]=" << plan.orderedTaskIds[i] << "\n";
+  if (!args.flag("run")) return 0;
+
+  SessionRunSummary summary = session.run(graph);
+  if (!summary.success) {
+    printRunError(session, summary);
+    return 2;
+  }
+  std::cout << "session.backend=" << session.backendName() << "\n";
+  std::cout << "session.result=success\n";
+  if (summary.validationRan && summary.validationPassed) std::cout << "session.validation=pass\n";
+  std::cout << "session.profile.session_id=" << summary.profileTrace.sessionId << "\n";
+  std::cout << "session.profile.count=" << summary.profileArtifactPaths.size() << "\n";
+  for (size_t i = 0; i < summary.profileArtifactPaths.size(); ++i)
+    std::cout << "session.profile[" << i << "]=" << summary.profileArtifactPaths[i] << "\n";
+  for (const auto &ev : summary.profileTrace.events) {
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "%.3f", ev.score);
+    std::cout << "session.profile.score." << ev.taskId << "=" << buf << "\n";
+  }
+  for (const auto &kv : summary.profileTrace.attributes) std::cout << "session.runtime.attribute." << kv.first << "=" << kv.second << "\n";
+  for (const auto &kv : summary.profileTrace.counters) std::cout << "session.runtime.counter." << kv.first << "=" << kv.second << "\n";
+  return 0;
+}

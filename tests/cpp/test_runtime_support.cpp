@@ -1,0 +1,256 @@
+// Hand-rolled checks of the host runtime (no GPU): npy I/O, tiling packing, output comparator, task graph,
+// run manifest, execution session with an injected driver.  Exit code = number of failed expectations,
+// the convention of the reference's test/tools/runtime/test_runtime.cpp and test_taskgraph_runtime.cpp.
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <iostream>
+
+#include "execution/execution_session.h"
+#include "execution/run_manifest.h"
+#include "support/npy_io.h"
+#include "support/tiling_schema.h"
+
+using namespace afir;
+
+static int g_pass = 0, g_fail = 0;
+#define EXPECT(cond, what)                                                    \
+  do {                                                                        \
+    if (cond) ++g_pass;                                                       \
+    else { ++g_fail; std::cerr << "FAIL: " << what << " (" << __LINE__ << ")\n"; } \
+  } while (0)
+
+static std::string g_dir;
+static std::string path(const std::string &leaf) { return g_dir + "/" + leaf; }
+static void writeText(const std::string &p, const std::string &text) { std::ofstream(p) << text; }
+
+static void testNpy() {
+  NDArray a;
+  a.dtype = NpyDType::F16;
+  a.shape = {2, 3};
+  a.allocate();
+  const uint16_t one = 0x3C00;
+  for (int i = 0; i < 6; ++i) std::memcpy(a.bytes.data() + 2 * i, &one, 2);
+  EXPECT(saveNpy(path("h.npy"), a).ok(), "save f16");
+  NDArray b;
+  EXPECT(loadNpy(path("h.npy"), b).ok(), "load f16");
+  EXPECT(b.dtype == NpyDType::F16 && b.shape == a.shape && b.bytes == a.bytes, "f16 round trip keeps 0x3C00");
+  std::ifstream f(path("h.npy"), std::ios::binary);
+  std::string head(10, '\0');
+  f.read(head.data(), 10);
+  const unsigned hlen = static_cast<unsigned char>(head[8]) | (static_cast<unsigned char>(head[9]) << 8);
+  EXPECT(head.compare(0, 6, "\x93NUMPY") == 0 && head[6] == 1 && head[7] == 0, "version 1.0 header");
+  EXPECT((10 + hlen) % 64 == 0, "header padded to 64 bytes");
+
+  NDArray c;
+  c.dtype = NpyDType::BF16;
+  c.shape = {4};
+  c.allocate();
+  const uint16_t bone = 0x3F80;
+  for (int i = 0; i < 4; ++i) std::memcpy(c.bytes.data() + 2 * i, &bone, 2);
+  EXPECT(saveNpy(path("b.npy"), c).ok(), "save bf16");
+  std::ifstream fb(path("b.npy"), std::ios::binary);
+  std::string all((std::istreambuf_iterator<char>(fb)), std::istreambuf_iterator<char>());
+  EXPECT(all.find("'descr': '<V2'") != std::string::npos, "bf16 stored as <V2");
+  EXPECT(all.find("'shape': (4,)") != std::string::npos, "1-D shape keeps the trailing comma");
+  NDArray d;
+  EXPECT(loadNpy(path("b.npy"), d).ok() && d.dtype == NpyDType::BF16 && d.bytes == c.bytes, "bf16 round trip keeps 0x3F80");
+
+  for (NpyDType t : {NpyDType::F32, NpyDType::INT8, NpyDType::INT32, NpyDType::INT64}) {
+    NDArray x;
+    x.dtype = t;
+    x.shape = {3, 1, 2};
+    x.allocate();
+    for (size_t i = 0; i < x.bytes.size(); ++i) x.bytes[i] = static_cast<uint8_t>(i * 7 + 1);
+    NDArray y;
+    EXPECT(saveNpy(path("t.npy"), x).ok() && loadNpy(path("t.npy"), y).ok() && y.dtype == t && y.shape == x.shape && y.bytes == x.bytes,
+           std::string("round trip ") + npyDTypeName(t));
+  }
+  NDArray e;
+  EXPECT(loadNpy(path("missing.npy"), e).message().find("Cannot open:") == 0, "missing file message");
+  writeText(path("junk.npy"), "not an npy file at all");
+  EXPECT(loadNpy(path("junk.npy"), e).message().find("Not a .npy file:") == 0, "bad magic message");
+  {
+    std::string trunc = all.substr(0, all.size() - 3);
+    std::ofstream(path("trunc.npy"), std::ios::binary) << trunc;
+    EXPECT(loadNpy(path("trunc.npy"), e).message().find("Truncated data in:") == 0, "truncated data message");
+  }
+  {
+    std::string f8 = all;
+    f8.replace(f8.find("<V2"), 3, "<f8");
+    std::ofstream(path("f8.npy"), std::ios::binary) << f8;
+    EXPECT(loadNpy(path("f8.npy"), e).message().find("Unsupported dtype '<f8':") == 0, "unsupported dtype message");
+  }
+}
+
+static void testTiling() {
+  writeText(path("space.json"), R"({"kernel":"k","tiling_params":[{"name":"TB_M","type":"int64"},{"name":"B","type":"int32"},{"name":"dim_arg0_0"}]})");
+  TilingSchema schema;
+  EXPECT(TilingSchema::fromJsonFile(path("space.json"), schema).ok() && schema.fields().size() == 3, "schema loads");
+  EXPECT(schema.fields()[2].type == "int64", "type defaults to int64");
+  std::vector<uint8_t> bytes;
+  EXPECT(schema.pack({{"TB_M", 16}, {"B", 2}, {"dim_arg0_0", 640}}, bytes).ok() && bytes.size() == 20, "int64 + int32 + int64 = 20 bytes");
+  int64_t a, c;
+  int32_t b;
+  std::memcpy(&a, bytes.data(), 8);
+  std::memcpy(&b, bytes.data() + 8, 4);
+  std::memcpy(&c, bytes.data() + 12, 8);
+  EXPECT(a == 16 && b == 2 && c == 640, "little-endian values in schema order");
+  EXPECT(schema.pack({{"TB_M", 16}}, bytes).message().find("tiling param count mismatch: got 1, expected 3 (TB_M, B, dim_arg0_0)") == 0, "count mismatch");
+  EXPECT(schema.pack({{"B", 1}, {"TB_M", 2}, {"dim_arg0_0", 3}}, bytes).message().find("tiling param name mismatch at position 0: got 'B', expected 'TB_M'") == 0,
+         "name mismatch");
+  TilingBinding tb;
+  EXPECT(packTilingBytes(tb, bytes).ok() && bytes.empty(), "absent tiling packs to nothing");
+  tb.present = true;
+  tb.schemaPath = path("space.json");
+  tb.params = "dim_arg0_0=640, B=2,TB_M=16";
+  EXPECT(packTilingBytes(tb, bytes).ok() && bytes.size() == 20, "schema + named params in any order");
+  tb.params = "TB_M=16,B=2";
+  EXPECT(packTilingBytes(tb, bytes).message() == "tiling params missing field: dim_arg0_0", "missing named field");
+  std::ofstream(path("tiling.bin"), std::ios::binary) << std::string("\x01\x02\x03\x04", 4);
+  tb.binaryPath = path("tiling.bin");
+  EXPECT(packTilingBytes(tb, bytes).ok() && bytes.size() == 4 && bytes[3] == 4, "binary file wins over schema");
+  TilingBinding only;
+  only.present = true;
+  only.params = "A=1";
+  EXPECT(packTilingBytes(only, bytes).message() == "tiling params require either a schema path or a binary path", "params alone are refused");
+  TilingSchema bad;
+  writeText(path("bad.json"), R"({"kernel":"k"})");
+  EXPECT(TilingSchema::fromJsonFile(path("bad.json"), bad).message().find("missing 'tiling_params' array") != std::string::npos, "missing tiling_params");
+}
+
+static NDArray f32Array(std::vector<float> v) {
+  NDArray a;
+  a.dtype = NpyDType::F32;
+  a.shape = {static_cast<int64_t>(v.size())};
+  a.allocate();
+  std::memcpy(a.bytes.data(), v.data(), v.size() * 4);
+  return a;
+}
+
+static void testComparator() {
+  OutputComparisonResult r;
+  EXPECT(compareRuntimeOutputs({f32Array({1, 2, 3})}, {f32Array({1, 2, 3})}, 0.0, 0.0, r).ok() && r.passed && r.maxAbsDiff == 0.0, "exact match passes at zero tolerance");
+  EXPECT(compareRuntimeOutputs({f32Array({1, 2, 3.5f})}, {f32Array({1, 2, 3})}, 0.1, 0.1, r).ok() && !r.passed, "mismatch fails");
+  EXPECT(r.maxAbsDiff == 0.5 && r.errorMessage.find("output comparison failed: max_abs_diff=0.5") == 0, "reports max_abs_diff");
+  EXPECT(compareRuntimeOutputs({f32Array({100.5f})}, {f32Array({100})}, 0.0, 1e-2, r).ok() && r.passed, "rtol scales with |expected|");
+  EXPECT(compareRuntimeOutputs({f32Array({1})}, {}, 1, 1, r).message() == "output count mismatch: got 1, expected 0", "count mismatch is structural");
+  EXPECT(compareRuntimeOutputs({f32Array({1, 2})}, {f32Array({1})}, 1, 1, r).message() == "output 0 shape mismatch", "shape mismatch");
+  NDArray h = f32Array({1});
+  h.dtype = NpyDType::INT32;
+  EXPECT(compareRuntimeOutputs({h}, {f32Array({1})}, 1, 1, r).message() == "output 0 dtype mismatch", "dtype mismatch");
+  NDArray half;
+  half.dtype = NpyDType::F16;
+  half.shape = {2};
+  half.allocate();
+  const uint16_t vals[2] = {0x3C00, 0x0001};
+  std::memcpy(half.bytes.data(), vals, 4);
+  EXPECT(elementAsFloat(half, 0) == 1.0f && elementAsFloat(half, 1) == 5.9604644775390625e-08f, "f16 widening incl. subnormals");
+}
+
+static RuntimeTask makeTask(const std::string &id, std::vector<std::string> deps = {}) {
+  RuntimeTask t;
+  t.taskId = id;
+  t.dependencies = std::move(deps);
+  t.artifact.kernelName = "k";
+  return t;
+}
+
+static void testTaskGraph() {
+  TaskGraph g;
+  EXPECT(g.addTask(makeTask("")).message() == "empty task id", "empty id");
+  EXPECT(g.addTask(makeTask("a")).ok() && g.addTask(makeTask("a")).message() == "duplicate task id", "duplicate id");
+  EXPECT(g.addTask(makeTask("c", {"b"})).ok() && g.addTask(makeTask("b", {"a"})).ok(), "add out of order");
+  std::vector<std::string> ids;
+  EXPECT(g.topologicalOrder(ids).ok() && ids == std::vector<std::string>({"a", "b", "c"}), "dependency order");
+  TaskGraph unknown;
+  unknown.addTask(makeTask("x", {"nope"}));
+  EXPECT(unknown.topologicalOrder(ids).message() == "unknown task dependency", "unknown dependency");
+  TaskGraph cyc;
+  cyc.addTask(makeTask("p", {"q"}));
+  cyc.addTask(makeTask("q", {"p"}));
+  EXPECT(cyc.topologicalOrder(ids).message() == "task graph contains a cycle", "cycle");
+}
+
+class RecordingDriver final : public ExecutionBackendDriver {
+public:
+  std::vector<std::string> order;
+  std::vector<std::string> seenInputs;
+  std::string failOn;
+  Status run(const ExecutionRequest &request, ExecutionResult &result) override {
+    order.push_back(request.task.taskId);
+    for (const auto &b : request.task.invocation.inputs) seenInputs.push_back(b.path);
+    result.taskId = request.task.taskId;
+    if (request.task.taskId == failOn) return Status::error("[cuda:kernel_launch] injected failure");
+    return Status::success();
+  }
+};
+
+static void testManifestAndSession() {
+  ::mkdir(path("art").c_str(), 0755);
+  writeText(path("art/k.bin"), "{}");
+  writeText(path("art/manifest.txt"), "kernel_name=k\nsoc_version=sm_100a\nkernel_kind=vec\ndevice_binary_path=" + path("art/k.bin") + "\nmanifest_path=x\n");
+  writeText(path("m.json"), std::string(R"({"backend":"cuda","artifact_root":")") + path("art") + R"(","tasks":[
+    {"task_id":"second","dependencies":["first"],"inputs":[{"name":"x","source":"task_output","upstream_task":"first","upstream_output":"y"}],
+     "outputs":[{"name":"z","shape":[4],"dtype":"f32"}],"block_dim":7,"atol":0.5,"rtol":0.25,"profiling":true,
+     "tiling":{"schema":"s.json","params":"A=1"}},
+    {"task_id":"first","inputs":[{"name":"in","path":"in.npy"}],"outputs":[{"name":"y","path":")" + path("y.npy") + R"(","shape":[2,2],"dtype":"bf16"}]}
+  ]})");
+  RunManifestSpec spec;
+  EXPECT(loadRunManifest(path("m.json"), spec).ok() && spec.tasks.size() == 2, "manifest with tasks[] loads");
+  const RuntimeTask &second = spec.tasks[0];
+  EXPECT(second.invocation.blockDim == 7 && second.invocation.atol == 0.5 && second.invocation.rtol == 0.25 && second.invocation.enableProfiling, "scalar fields");
+  EXPECT(second.invocation.inputs[0].sourceKind == BindingSourceKind::TaskOutput && second.invocation.inputs[0].upstreamOutputName == "y", "task_output binding");
+  EXPECT(second.invocation.tiling.present && second.invocation.tiling.params == "A=1", "tiling binding");
+  EXPECT(spec.tasks[1].invocation.outputs[0].dtype.value() == NpyDType::BF16 && spec.tasks[1].invocation.outputs[0].shape->size() == 2, "shape and dtype");
+  EXPECT(spec.tasks[1].invocation.atol == 1.0 && spec.tasks[1].invocation.rtol == 1e-2 && spec.tasks[1].invocation.workspaceSize == 8192, "reference defaults");
+  TaskGraph graph;
+  EXPECT(buildTaskGraph(spec, graph).ok(), "artifact roots resolve");
+
+  auto driver = std::make_shared<RecordingDriver>();
+  ExecutionSession session("cuda", driver);
+  SessionPlan plan;
+  EXPECT(session.plan(graph, plan).ok() && plan.orderedTaskIds == std::vector<std::string>({"first", "second"}), "plan is dependency ordered");
+  SessionRunSummary summary = session.run(graph, path("work"));
+  EXPECT(summary.success && driver->order == std::vector<std::string>({"first", "second"}), "runs in order");
+  EXPECT(driver->seenInputs.size() == 2 && driver->seenInputs[1] == path("y.npy"), "upstream output resolves to the producer's file");
+  EXPECT(summary.profileTrace.counters["planned_task_count"] == 2 && summary.profileTrace.counters["serialized_launch_count"] == 2, "counters");
+
+  auto failing = std::make_shared<RecordingDriver>();
+  failing->failOn = "first";
+  ExecutionSession s2("cuda", failing);
+  summary = s2.run(graph, path("work2"));
+  EXPECT(!summary.success && failing->order.size() == 1, "first failure stops the session");
+  EXPECT(summary.errorStage == "kernel_launch" && summary.errorMessage == "injected failure", "stage tag parsed out of the message");
+
+  RunManifestSpec badSpec;
+  writeText(path("bad1.json"), R"({"artifact_root":"x","task_id":"t"})");
+  EXPECT(loadRunManifest(path("bad1.json"), badSpec).message() == "missing required string field: backend", "backend is required");
+  writeText(path("bad2.json"), R"({"backend":"tpu","artifact_root":"x","task_id":"t"})");
+  EXPECT(loadRunManifest(path("bad2.json"), badSpec).message() == "unsupported backend: tpu", "unknown backend");
+  writeText(path("bad3.json"), R"({"backend":"cuda","task_id":"t"})");
+  EXPECT(loadRunManifest(path("bad3.json"), badSpec).message() == "missing required string field: artifact_root", "artifact_root is required");
+  writeText(path("bad4.json"), "{nope");
+  EXPECT(loadRunManifest(path("bad4.json"), badSpec).message().find("invalid JSON in run manifest:") == 0, "invalid JSON");
+  writeText(path("ok5.json"), std::string(R"({"backend":"sim","artifact_root":")") + path("art") + R"(","task_id":"solo"})");
+  EXPECT(loadRunManifest(path("ok5.json"), badSpec).ok() && badSpec.tasks.size() == 1 && badSpec.backendName == "sim", "single-task form; reference backend names accepted");
+  auto parts = parseErrorStage("[cuda:validate] output comparison failed");
+  EXPECT(parts.first == "validate" && parts.second == "output comparison failed", "parseErrorStage");
+  EXPECT(parseErrorStage("plain").first.empty(), "untagged message");
+}
+
+int main() {
+  char tmpl[] = "/tmp/afir-runtime-test-XXXXXX";
+  if (!::mkdtemp(tmpl)) return 99;
+  g_dir = tmpl;
+  testNpy();
+  testTiling();
+  testComparator();
+  testTaskGraph();
+  testManifestAndSession();
+  std::cout << g_pass << " passed, " << g_fail << " failed\n";
+  return g_fail;
+}

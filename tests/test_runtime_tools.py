@@ -1,0 +1,114 @@
+"""Host runtime and command-line tools without a GPU: the hand-rolled C++ checks of npy I/O, tiling packing,
+comparator, task graph, run manifest and session (driver injected), and the runtime-session CLI contract
+(exit codes 0/2/4 and key=value lines of the reference's tools/runtime-session)."""
+import json
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from ascend_mlir_b200 import build as lib_build
+from ascend_mlir_b200 import descriptors
+
+ROOT = Path(__file__).resolve().parent.parent
+BIN = ROOT / "ascend_mlir_b200" / "bin"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built():
+    lib_build.build()
+
+
+def test_cpp_runtime_support_checks(tmp_path):
+    exe = tmp_path / "test_runtime_support"
+    objs = [str(o) for o in sorted((ROOT / "ascend_mlir_b200" / "build").glob("*.o"))
+            if "capi" not in o.name and "tools_" not in o.name]
+    cmd = ["g++", "-std=c++17", "-O1", "-I", str(ROOT / "ascend_mlir_b200" / "csrc"), "-I", str(ROOT / "include"),
+           str(ROOT / "tests" / "cpp" / "test_runtime_support.cpp")] + objs + [
+        "-L", "/usr/local/cuda/lib64", "-lcudart_static", "-ldl", "-lrt", "-lpthread", "-o", str(exe)]
+    subprocess.run(cmd, check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert " passed, 0 failed" in res.stdout
+
+
+def run_tool(*args):
+    return subprocess.run([str(BIN / "runtime-session"), *map(str, args)], capture_output=True, text=True)
+
+
+def test_runtime_session_usage_errors_exit_4():
+    r = run_tool()
+    assert r.returncode == 4 and "Error: provide exactly one of --artifact-root or --kernel" in r.stderr
+    r = run_tool("--artifact-root", "/nonexistent", "--kernel", "x")
+    assert r.returncode == 4 and "provide exactly one of" in r.stderr
+    r = run_tool("--run-manifest", "/nonexistent/m.json")
+    assert r.returncode == 4 and "Error: cannot read run manifest: /nonexistent/m.json" in r.stderr
+    r = run_tool("--help")
+    assert r.returncode == 0 and "--run-manifest" in r.stdout
+
+
+def test_runtime_session_compiles_and_plans(tmp_path):
+    spec = descriptors.add_mul()
+    src = tmp_path / "add_mul.cuda.json"
+    src.write_text(spec.descriptor_json())
+    r = run_tool("--kernel", src, "--output", tmp_path / "artifact", "--task-id", "t0")
+    assert r.returncode == 0, r.stderr
+    lines = dict(l.split("=", 1) for l in r.stdout.splitlines())
+    assert lines["artifact.kernel_name"] == "add_mul" and lines["artifact.soc"] == "sm_100a"
+    assert lines["session.plan.tasks"] == "1" and lines["session.plan[0]"] == "t0"
+    assert (tmp_path / "artifact" / "add_mul.bin").exists()
+    # the artifact root is the resumable unit: plan again without recompiling
+    r = run_tool("--artifact-root", tmp_path / "artifact")
+    assert r.returncode == 0 and "session.plan[0]=main" in r.stdout
+    r = run_tool("--kernel", src, "--kernel-kind", "weird")
+    assert r.returncode == 4 and "unsupported kernel kind: weird" in r.stderr
+
+
+def _manifest(tmp_path, tasks):
+    spec = descriptors.add_mul()
+    src = tmp_path / "k.cuda.json"
+    src.write_text(spec.descriptor_json())
+    assert run_tool("--kernel", src, "--output", tmp_path / "art").returncode == 0
+    m = tmp_path / "m.json"
+    m.write_text(json.dumps({"backend": "cuda", "artifact_root": str(tmp_path / "art"), "tasks": tasks}))
+    return m
+
+
+def test_runtime_session_graph_errors_exit_2(tmp_path):
+    m = _manifest(tmp_path, [{"task_id": "a", "dependencies": ["b"]}, {"task_id": "b", "dependencies": ["a"]}])
+    r = run_tool("--run-manifest", m)
+    assert r.returncode == 2 and "Error: task graph contains a cycle" in r.stderr
+    m = _manifest(tmp_path, [{"task_id": "a", "dependencies": ["ghost"]}])
+    r = run_tool("--run-manifest", m)
+    assert r.returncode == 2 and "unknown task dependency" in r.stderr
+    m = _manifest(tmp_path, [{"task_id": "a"}, {"task_id": "a"}])
+    r = run_tool("--run-manifest", m)
+    assert r.returncode == 4 and "duplicate task id" in r.stderr
+
+
+def test_runtime_session_run_with_testing_driver(tmp_path):
+    m = _manifest(tmp_path, [{"task_id": "first", "outputs": [{"name": "y", "shape": [2], "dtype": "f32"}]},
+                             {"task_id": "second", "dependencies": ["first"],
+                              "inputs": [{"name": "x", "source": "task_output", "upstream_task": "first", "upstream_output": "y"}],
+                              "outputs": [{"name": "z", "shape": [2], "dtype": "f32"}]}])
+    r = run_tool("--run-manifest", m, "--run", "--testing-driver", "success")
+    assert r.returncode == 0, r.stderr
+    out = r.stdout.splitlines()
+    assert "session.plan[0]=first" in out and "session.plan[1]=second" in out
+    assert "session.backend=cuda" in out and "session.result=success" in out
+    assert "session.profile.count=2" in out
+    assert any(l.startswith("session.runtime.counter.planned_task_count=2") for l in out)
+    r = run_tool("--run-manifest", m, "--run", "--testing-driver", "bogus")
+    assert r.returncode == 4 and "unsupported testing driver: bogus" in r.stderr
+
+
+def test_runtime_session_reports_binding_stage_on_missing_input(tmp_path):
+    # the real CUDA driver fails in the bindings stage before touching any device
+    m = _manifest(tmp_path, [{"task_id": "t", "inputs": [{"name": "a", "path": str(tmp_path / "missing.npy")}],
+                              "outputs": [{"name": "y", "shape": [2], "dtype": "f32"}]}])
+    r = run_tool("--run-manifest", m, "--run")
+    assert r.returncode == 2
+    err = r.stderr.splitlines()
+    assert "session.result=error" in err and "session.error_stage=bindings" in err
+    assert any(l.startswith("session.error=Cannot open:") for l in err)

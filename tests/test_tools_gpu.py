@@ -1,0 +1,114 @@
+"""runtime-session and autotuner end to end on the GPU: manifests and tiling spaces in the reference's formats,
+inputs/expected tensors as .npy, validation against the CPU oracle's outputs."""
+import json
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from ascend_mlir_b200 import build as lib_build
+from ascend_mlir_b200 import configs, descriptors
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+BIN = ROOT / "ascend_mlir_b200" / "bin"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built():
+    lib_build.build()
+
+
+def tool(name, *args):
+    return subprocess.run([str(BIN / name), *map(str, args)], capture_output=True, text=True)
+
+
+def compile_artifact(tmp_path, spec, sub):
+    src = tmp_path / f"{spec.name}.cuda.json"
+    src.write_text(spec.descriptor_json())
+    (tmp_path / f"{spec.name}.tiling_space.json").write_text(spec.tiling_space_json())
+    r = tool("runtime-session", "--kernel", src, "--output", tmp_path / sub)
+    assert r.returncode == 0, r.stderr
+    return tmp_path / sub
+
+
+def test_two_task_graph_validates_and_profiles(tmp_path):
+    ew, rs = descriptors.add_mul(), descriptors.bcast_add_rowsum("f32")
+    art1, art2 = compile_artifact(tmp_path, ew, "art_ew"), compile_artifact(tmp_path, rs, "art_rs")
+    M, N = 300, 1024
+    rng = np.random.default_rng(51)
+    a = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+    b = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, M).astype(np.float32)
+    prod = oracle.add_mul_f32(a, b)
+    sums = oracle.bcast_add_rowsum_f32(bias, prod)
+    for name, arr in [("a", a), ("b", b), ("bias", bias), ("prod", prod), ("sums", sums)]:
+        np.save(tmp_path / f"{name}.npy", arr)
+    manifest = {"backend": "cuda", "tasks": [
+        {"task_id": "chain", "artifact_root": str(art1),
+         "inputs": [{"name": "a", "path": str(tmp_path / "a.npy")}, {"name": "b", "path": str(tmp_path / "b.npy")}],
+         "outputs": [{"name": "out", "path": str(tmp_path / "chain_out.npy"), "shape": [M, N], "dtype": "f32"}],
+         "expected_outputs": [{"name": "out", "path": str(tmp_path / "prod.npy")}],
+         "tiling": {"schema": str(tmp_path / "add_mul.tiling_space.json"),
+                    "params": f"CTA_THREADS=128,UNROLL=2,dim_arg0_0={M},dim_arg0_1={N}"},
+         "block_dim": 0, "atol": 0.0, "rtol": 0.0, "profiling": True},
+        {"task_id": "reduce", "artifact_root": str(art2), "dependencies": ["chain"],
+         "inputs": [{"name": "bias", "path": str(tmp_path / "bias.npy")},
+                    {"name": "x", "source": "task_output", "upstream_task": "chain", "upstream_output": "out"}],
+         "outputs": [{"name": "sums", "path": str(tmp_path / "sums_out.npy")}],
+         "expected_outputs": [{"name": "sums", "path": str(tmp_path / "sums.npy")}],
+         "tiling": {"schema": str(tmp_path / "broadcast_add_reducesum.tiling_space.json"),
+                    "params": f"CTA_THREADS=0,TEAM_LANES=0,SPLIT_N=0,BULK_COPY=1,STREAM_STAGES=0,STREAM_CHUNK=0,dim_arg0_0={M},dim_arg1_1={N}"},
+         "block_dim": 0, "atol": 1e-2, "rtol": 1e-4}]}
+    m = tmp_path / "run.json"
+    m.write_text(json.dumps(manifest))
+    r = tool("runtime-session", "--run-manifest", m, "--run")
+    assert r.returncode == 0, r.stdout + r.stderr
+    out = r.stdout.splitlines()
+    assert "session.result=success" in out and "session.validation=pass" in out and "session.backend=cuda" in out
+    assert "session.profile.count=1" in out
+    trace_path = [l.split("=", 1)[1] for l in out if l.startswith("session.profile[0]=")][0]
+    trace = json.loads(Path(trace_path).read_text())
+    assert trace["backend"] == "cuda" and trace["kernel_name"] == "add_mul" and trace["task_id"] == "chain"
+    assert trace["score"] == trace["elapsed_us"] == trace["cycle_count"] and trace["score"] > 0
+    assert trace["validation_passed"] is True and trace["inputs"][0]["shape"] == [M, N]
+    assert np.array_equal(np.load(tmp_path / "chain_out.npy"), prod)
+    assert np.allclose(np.load(tmp_path / "sums_out.npy"), sums, rtol=1e-4, atol=1e-2)
+
+    # a wrong expectation fails in the validate stage with exit code 2
+    np.save(tmp_path / "prod.npy", prod + 1.0)
+    r = tool("runtime-session", "--run-manifest", m, "--run")
+    assert r.returncode == 2
+    err = r.stderr.splitlines()
+    assert "session.result=error" in err and "session.validation=fail" in err and "session.error_stage=validate" in err
+    assert any("output comparison failed: max_abs_diff=1" in l for l in err)
+
+
+def test_autotuner_searches_tile_parameters(tmp_path):
+    spec = descriptors.split_relu_bias_mul(1)
+    src = tmp_path / f"{spec.name}.cuda.json"
+    src.write_text(spec.descriptor_json())
+    space = json.loads(spec.tiling_space_json())
+    space["kernel_file"] = src.name
+    (tmp_path / "tiling_space.json").write_text(json.dumps(space))
+    w = configs.split_relu_broadcast_add_mul(8, 256, 512, seed=52)
+    np.save(tmp_path / "x.npy", w.inputs[0])
+    np.save(tmp_path / "bias.npy", w.inputs[1])
+    np.save(tmp_path / "expected.npy", oracle.split_relu_bias_mul_f16(w.inputs[0], w.inputs[1], 1))
+    r = tool("autotuner", "--space", tmp_path / "tiling_space.json", "--inputs", f"{tmp_path / 'x.npy'},{tmp_path / 'bias.npy'}",
+             "--expected", tmp_path / "expected.npy", "--shape", "B=8,R=256,C2=1024,C=512,BIAS=256", "--atol", "0", "--rtol", "0",
+             "--output", tmp_path / "best_config.json")
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert r.stdout.count(" PASS score=") == 9 and "FAIL" not in r.stdout  # 3 CTA sizes x 3 unroll depths
+    best = json.loads((tmp_path / "best_config.json").read_text())
+    assert best["kernel_name"] == spec.name and best["soc"] == "sm_100a"
+    assert best["config"]["CTA_THREADS"] in (128, 256, 512) and best["config"]["UNROLL"] in (1, 2, 4)
+    assert best["config"]["dim_arg0_2"] == 1024 and best["shape"]["C"] == 512
+    assert best["best"]["score"] > 0 and best["best"]["max_abs_diff"] == 0
+    assert Path(best["best"]["profile_path"]).exists()
+    # a shape that contradicts the tensors is a failed candidate, not a crash
+    r = tool("autotuner", "--space", tmp_path / "tiling_space.json", "--inputs", f"{tmp_path / 'x.npy'},{tmp_path / 'bias.npy'}",
+             "--expected", tmp_path / "expected.npy", "--shape", "B=8,R=256,C2=1024,C=256,BIAS=256")
+    assert r.returncode == 1 and "FAIL" in r.stdout and "no candidate passed validation" in r.stderr
