@@ -40,15 +40,19 @@ CU_SOURCES = {
 CPP_SOURCES = ["common/json.cpp", "runtime/descriptor.cpp", "runtime/launcher.cpp", "runtime/executor.cpp",
                "support/npy_io.cpp", "support/tiling_schema.cpp", "execution/output_comparator.cpp",
                "execution/task_graph.cpp", "execution/run_manifest.cpp", "execution/artifact_compiler.cpp",
-               "execution/execution_session.cpp", "runtime/capi.cpp"]
+               "execution/execution_session.cpp", "front/mlir_text.cpp", "front/group_analysis.cpp", "runtime/capi.cpp"]
 # command-line tools (reference: tools/runtime-session, tools/autotuner), linked with the same objects
-TOOLS = {"runtime-session": "tools/runtime_session_main.cpp", "autotuner": "tools/autotuner_main.cpp"}
+TOOLS = {"runtime-session": "tools/runtime_session_main.cpp", "autotuner": "tools/autotuner_main.cpp",
+         "afir-opt": "tools/afir_opt_main.cpp", "afir-translate": "tools/afir_translate_main.cpp"}
+# the compiler front-end tools need no CUDA objects
+FRONT_ONLY = {"afir-opt", "afir-translate"}
 BINDIR = PKG / "bin"
 
 
 def _headers_digest() -> str:
     h = hashlib.sha256()
-    for p in sorted(list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")) + list((ROOT / "include").rglob("*.h"))):
+    for p in sorted(list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")) + list(CSRC.rglob("*.inc")) +
+                    list((ROOT / "include").rglob("*.h"))):
         h.update(p.read_bytes())
     return h.hexdigest()
 
@@ -121,7 +125,11 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         if force or jobs or _stale(tobj, src, stamp) or not exe.exists():
             _run([CXX] + CXX_FLAGS + ["-c", str(src), "-o", str(tobj)], verbose)
             _mark(tobj, src, stamp)
-            _run([CXX, "-o", str(exe), str(tobj)] + lib_objs + cuda_libs, verbose)
+            if tool in FRONT_ONLY:
+                front = [o for o in lib_objs if "front_" in o or "common_" in o]
+                _run([CXX, "-o", str(exe), str(tobj)] + front, verbose)
+            else:
+                _run([CXX, "-o", str(exe), str(tobj)] + lib_objs + cuda_libs, verbose)
     if ptxas_info:
         print("".join(logs))
     return LIB

@@ -1,0 +1,307 @@
+#include "front/mlir_text.h"
+
+#include <algorithm>
+#include <cctype>
+#include <cstdlib>
+
+namespace afir {
+namespace front {
+
+std::string Type::str() const {
+  if (!isTensor) return elem;
+  std::string s = "tensor<";
+  for (int64_t d : dims) s += (d < 0 ? std::string("?") : std::to_string(d)) + "x";
+  return s + elem + ">";
+}
+
+std::string AffineMap::str() const {
+  std::string s = "affine_map<(";
+  for (int i = 0; i < numDims; ++i) s += (i ? ", d" : "d") + std::to_string(i);
+  s += ") -> (";
+  for (size_t i = 0; i < results.size(); ++i)
+    s += (i ? ", " : "") + (results[i] < 0 ? std::string("0") : "d" + std::to_string(results[i]));
+  return s + ")>";
+}
+
+namespace {
+
+class Parser {
+public:
+  Parser(const std::string &text, Module &m) : s_(text), m_(m) {}
+
+  Status run() {
+    m_.source = s_;
+    skip();
+    while (!eof()) {
+      if (peek() == '#') {
+        if (Status st = mapAlias(); !st) return st;
+      } else if (lookingAt("module")) {
+        pos_ += 6;
+        skip();
+        if (lookingAt("attributes")) { pos_ += 10; skip(); if (Status st = skipBalanced('{', '}'); !st) return st; skip(); }
+        if (Status st = expect('{'); !st) return st;
+        moduleDepth_ += 1;
+      } else if (peek() == '}' && moduleDepth_ > 0) {
+        ++pos_;
+        moduleDepth_ -= 1;
+      } else if (lookingAt("func.func")) {
+        if (Status st = func(); !st) return st;
+      } else {
+        return fail("expected 'module', 'func.func' or an affine_map alias");
+      }
+      skip();
+    }
+    if (moduleDepth_ != 0) return fail("unterminated module");
+    return Status::success();
+  }
+
+private:
+  const std::string &s_;
+  Module &m_;
+  size_t pos_ = 0;
+  int moduleDepth_ = 0;
+
+  bool eof() const { return pos_ >= s_.size(); }
+  char peek() const { return eof() ? '\0' : s_[pos_]; }
+  int lineOf(size_t p) const { return 1 + static_cast<int>(std::count(s_.begin(), s_.begin() + std::min(p, s_.size()), '\n')); }
+  Status fail(const std::string &msg) const { return Status::error("line " + std::to_string(lineOf(pos_)) + ": " + msg); }
+
+  void skip() {
+    while (!eof()) {
+      const char c = s_[pos_];
+      if (c == ' ' || c == '\t' || c == '\n' || c == '\r') ++pos_;
+      else if (c == '/' && pos_ + 1 < s_.size() && s_[pos_ + 1] == '/') {
+        while (!eof() && s_[pos_] != '\n') ++pos_;
+      } else break;
+    }
+  }
+  bool lookingAt(const char *word) const {
+    const size_t n = std::char_traits<char>::length(word);
+    if (s_.compare(pos_, n, word) != 0) return false;
+    const char next = pos_ + n < s_.size() ? s_[pos_ + n] : '\0';
+    return !(std::isalnum(static_cast<unsigned char>(next)) || next == '_' || next == '.');
+  }
+  bool accept(char c) {
+    skip();
+    if (peek() == c) { ++pos_; return true; }
+    return false;
+  }
+  bool acceptWord(const char *w) {
+    skip();
+    if (!lookingAt(w)) return false;
+    pos_ += std::char_traits<char>::length(w);
+    return true;
+  }
+  Status expect(char c) {
+    skip();
+    if (peek() != c) return fail(std::string("expected '") + c + "'");
+    ++pos_;
+    return Status::success();
+  }
+  Status expectWord(const char *w) {
+    if (!acceptWord(w)) return fail(std::string("expected '") + w + "'");
+    return Status::success();
+  }
+  Status skipBalanced(char open, char close) {
+    skip();
+    if (peek() != open) return fail(std::string("expected '") + open + "'");
+    int depth = 0;
+    while (!eof()) {
+      const char c = s_[pos_++];
+      if (c == '"') {
+        while (!eof() && s_[pos_] != '"') pos_ += s_[pos_] == '\\' ? 2 : 1;
+        ++pos_;
+      } else if (c == open) ++depth;
+      else if (c == close && --depth == 0) return Status::success();
+    }
+    return fail("unbalanced brackets");
+  }
+  std::string ident() {  // bare identifier with dots: linalg.generic, d0, parallel
+    skip();
+    const size_t b = pos_;
+    while (!eof() && (std::isalnum(static_cast<unsigned char>(s_[pos_])) || s_[pos_] == '_' || s_[pos_] == '.' || s_[pos_] == '$')) ++pos_;
+    return s_.substr(b, pos_ - b);
+  }
+  Status ssa(std::string &out) {  // %name
+    skip();
+    if (peek() != '%') return fail("expected an SSA value");
+    ++pos_;
+    const size_t b = pos_;
+    while (!eof() && (std::isalnum(static_cast<unsigned char>(s_[pos_])) || s_[pos_] == '_' || s_[pos_] == '.' || s_[pos_] == '$' || s_[pos_] == '-')) ++pos_;
+    if (pos_ == b) return fail("empty SSA name");
+    out = s_.substr(b, pos_ - b);
+    return Status::success();
+  }
+  Status integer(int64_t &out) {
+    skip();
+    const size_t b = pos_;
+    if (peek() == '-' || peek() == '+') ++pos_;
+    while (!eof() && std::isdigit(static_cast<unsigned char>(s_[pos_]))) ++pos_;
+    if (pos_ == b || (pos_ == b + 1 && !std::isdigit(static_cast<unsigned char>(s_[b])))) return fail("expected an integer");
+    out = std::strtoll(s_.substr(b, pos_ - b).c_str(), nullptr, 10);
+    return Status::success();
+  }
+
+  Status type(Type &t) {
+    skip();
+    t = Type();
+    if (lookingAt("tensor") || lookingAt("memref")) {
+      pos_ += 6;
+      if (Status st = expect('<'); !st) return st;
+      t.isTensor = true;
+      while (true) {
+        skip();
+        if (peek() == '?') {
+          ++pos_;
+          t.dims.push_back(-1);
+        } else if (std::isdigit(static_cast<unsigned char>(peek()))) {
+          const size_t b = pos_;
+          while (std::isdigit(static_cast<unsigned char>(peek()))) ++pos_;
+          t.dims.push_back(std::strtoll(s_.substr(b, pos_ - b).c_str(), nullptr, 10));
+        } else break;
+        if (peek() != 'x') return fail("expected 'x' in a tensor shape");
+        ++pos_;
+      }
+      t.elem = ident();
+      if (t.elem.empty()) return fail("expected an element type");
+      return expect('>');
+    }
+    t.elem = ident();
+    if (t.elem.empty()) return fail("expected a type");
+    return Status::success();
+  }
+
+  Status affineMapBody(AffineMap &map) {  // after "affine_map"
+    if (Status st = expect('<'); !st) return st;
+    if (Status st = expect('('); !st) return st;
+    std::vector<std::string> dims;
+    if (!accept(')')) {
+      do { dims.push_back(ident()); } while (accept(','));
+      if (Status st = expect(')'); !st) return st;
+    }
+    map.numDims = static_cast<int>(dims.size());
+    skip();
+    if (s_.compare(pos_, 2, "->") != 0) return fail("expected '->' in an affine map");
+    pos_ += 2;
+    if (Status st = expect('('); !st) return st;
+    if (!accept(')')) {
+      do {
+        skip();
+        if (std::isdigit(static_cast<unsigned char>(peek()))) {
+          int64_t c;
+          if (Status st = integer(c); !st) return st;
+          if (c != 0) return fail("only the constant 0 is supported in indexing maps");
+          map.results.push_back(-1);
+        } else {
+          const std::string d = ident();
+          auto it = std::find(dims.begin(), dims.end(), d);
+          if (it == dims.end()) return fail("indexing maps must be projected permutations (got '" + d + "')");
+          map.results.push_back(static_cast<int>(it - dims.begin()));
+        }
+      } while (accept(','));
+      if (Status st = expect(')'); !st) return st;
+    }
+    return expect('>');
+  }
+
+  Status mapAlias() {  // #name = affine_map<...>
+    ++pos_;
+    const std::string name = ident();
+    if (Status st = expect('='); !st) return st;
+    if (!acceptWord("affine_map")) return fail("only affine_map attribute aliases are supported");
+    AffineMap map;
+    if (Status st = affineMapBody(map); !st) return st;
+    m_.mapAliases[name] = map;
+    return Status::success();
+  }
+
+  Status mapRef(AffineMap &map) {  // #alias or inline affine_map<...>
+    skip();
+    if (peek() == '#') {
+      ++pos_;
+      const std::string name = ident();
+      auto it = m_.mapAliases.find(name);
+      if (it == m_.mapAliases.end()) return fail("unknown affine map alias '#" + name + "'");
+      map = it->second;
+      return Status::success();
+    }
+    if (!acceptWord("affine_map")) return fail("expected an affine map");
+    return affineMapBody(map);
+  }
+
+  Status indexOperand(IndexOperand &io) {
+    skip();
+    if (peek() == '%') {
+      io.literal = false;
+      return ssa(io.ssa);
+    }
+    io.literal = true;
+    return integer(io.value);
+  }
+  Status indexList(std::vector<IndexOperand> &out) {  // [a, b, ...]
+    if (Status st = expect('['); !st) return st;
+    if (accept(']')) return Status::success();
+    do {
+      IndexOperand io;
+      if (Status st = indexOperand(io); !st) return st;
+      out.push_back(io);
+    } while (accept(','));
+    return expect(']');
+  }
+  Status ssaList(std::vector<std::string> &out) {
+    do {
+      std::string v;
+      if (Status st = ssa(v); !st) return st;
+      out.push_back(v);
+    } while (accept(','));
+    return Status::success();
+  }
+  Status typeList(std::vector<Type> &out) {
+    do {
+      Type t;
+      if (Status st = type(t); !st) return st;
+      out.push_back(t);
+    } while (accept(','));
+    return Status::success();
+  }
+
+  Status func();
+  Status op(Op &o, bool inBody);
+  Status generic(Op &o);
+  Status opList(std::vector<Op> &ops, bool inBody);
+};
+
+#include "front/mlir_text_ops.inc"
+
+} // namespace
+
+Status parseModule(const std::string &text, Module &out) {
+  out = Module();
+  Parser p(text, out);
+  return p.run();
+}
+
+std::string printModule(const Module &m) {
+  // collect insertions (position -> text), then splice from the back
+  std::vector<std::pair<size_t, std::string>> ins;
+  auto attrText = [](const std::vector<std::pair<std::string, std::string>> &attrs) {
+    std::string s;
+    for (size_t i = 0; i < attrs.size(); ++i) s += (i ? ", " : "") + attrs[i].first + " = " + attrs[i].second;
+    return s;
+  };
+  for (const Func &f : m.funcs) {
+    if (!f.addedAttrs.empty() && f.attrInsertPos) ins.emplace_back(f.attrInsertPos, "attributes {" + attrText(f.addedAttrs) + "} ");
+    for (const Op &o : f.ops) {
+      if (o.addedAttrs.empty() || !o.attrInsertPos) continue;
+      const bool generic = o.name == "linalg.generic";
+      ins.emplace_back(o.attrInsertPos, generic ? "attrs = {" + attrText(o.addedAttrs) + "} " : "{" + attrText(o.addedAttrs) + "} ");
+    }
+  }
+  std::sort(ins.begin(), ins.end(), [](const auto &a, const auto &b) { return a.first > b.first; });
+  std::string out = m.source;
+  for (const auto &i : ins) out.insert(i.first, i.second);
+  return out;
+}
+
+} // namespace front
+} // namespace afir

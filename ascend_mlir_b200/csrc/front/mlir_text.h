@@ -1,0 +1,93 @@
+// Self-contained reader for the textual MLIR subset the fused-group front end consumes (MLIR itself is not
+// a dependency): module / func.func, affine_map aliases, tensor types with dynamic dims, arith.constant,
+// tensor.{dim,empty,extract_slice,concat,extract}, linalg.{generic,matmul,fill,index,yield}, the arith ops
+// fused bodies use, afir.{add,sub,mul,div}, return.  This is the input language of the reference's examples
+// (examples/*/step0_input.mlir) and of its AFIR elementwise ops (include/Dialect/AFIR/Ops/Basic/math.td:60-121).
+// Anything outside the subset is a parse error naming the op: nothing is skipped silently.
+#pragma once
+
+#include <cstdint>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "common/status.h"
+
+namespace afir {
+namespace front {
+
+struct Type {
+  bool isTensor = false;
+  std::vector<int64_t> dims;  // -1 = dynamic
+  std::string elem;           // f16, bf16, f32, i32, i64, index, ...
+  std::string str() const;
+};
+
+// Projected permutation with optional constant-0 results: result r is iteration dim results[r], or -1 for 0.
+struct AffineMap {
+  int numDims = 0;
+  std::vector<int> results;
+  std::string str() const;
+};
+
+// An index operand that is either a literal or an SSA value.
+struct IndexOperand {
+  bool literal = true;
+  int64_t value = 0;
+  std::string ssa;
+};
+
+struct Op {
+  std::string name;                   // "linalg.generic", "arith.addf", ...
+  std::vector<std::string> results;   // SSA names without '%'
+  std::vector<std::string> operands;
+  std::vector<Type> operandTypes;
+  Type resultType;
+  // arith.constant
+  double constFloat = 0.0;
+  int64_t constInt = 0;
+  bool constIsFloat = false;
+  // linalg.generic / matmul / fill
+  std::vector<AffineMap> maps;
+  std::vector<std::string> iterators;
+  int numIns = 0;                     // operands[0..numIns) are ins, the rest outs
+  std::vector<std::string> blockArgs;
+  std::vector<Type> blockArgTypes;
+  std::vector<Op> body;
+  // tensor.extract_slice / tensor.empty / tensor.extract / linalg.index / tensor.concat
+  std::vector<IndexOperand> offsets, sizes, strides;
+  int64_t dim = 0;
+  // printing
+  size_t srcBegin = 0, srcEnd = 0;    // span in the source text
+  size_t attrInsertPos = 0;           // where "attrs = {...}" / "{...}" can be inserted (0 = none)
+  std::vector<std::pair<std::string, std::string>> addedAttrs;
+  int line = 0;
+};
+
+struct FuncArg {
+  std::string name;
+  Type type;
+};
+
+struct Func {
+  std::string name;
+  std::vector<FuncArg> args;
+  std::vector<Type> resultTypes;
+  std::vector<Op> ops;
+  size_t attrInsertPos = 0;           // just before the body's '{'
+  std::vector<std::pair<std::string, std::string>> addedAttrs;
+  int line = 0;
+};
+
+struct Module {
+  std::string source;
+  std::map<std::string, AffineMap> mapAliases;
+  std::vector<Func> funcs;
+};
+
+Status parseModule(const std::string &text, Module &out);
+// The source text with every added attribute spliced in.
+std::string printModule(const Module &m);
+
+} // namespace front
+} // namespace afir

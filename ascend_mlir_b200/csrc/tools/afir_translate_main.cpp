@@ -1,0 +1,77 @@
+// afir-translate -mlir-to-cuda: emits the launch descriptor (<kernel>.cuda.json) of a fused-group function
+// and, with --tiling-space-out, its tiling_space.json.  Counterpart of the reference's
+// `afir-translate -mlir-to-cann [--tiling-space-out f.json]` (tools/afir-translate/afir-translate.cpp:19-40),
+// which emits AscendC C++ instead: here the code is the prebuilt sm_100a kernel library and the translation
+// unit is the descriptor that selects and parameterises a kernel of it.
+#include <fstream>
+#include <iostream>
+#include <iterator>
+
+#include "front/group_analysis.h"
+
+using namespace afir;
+using namespace afir::front;
+
+int main(int argc, char **argv) {
+  std::string input, output, spaceOut, function;
+  bool toCuda = false;
+  for (int i = 1; i < argc; ++i) {
+    std::string a = argv[i];
+    auto value = [&](const std::string &name, std::string &dst) -> bool {
+      const std::string dd = "--" + name, d = "-" + name;
+      if (a == dd || a == d) {
+        if (i + 1 >= argc) { std::cerr << "afir-translate: " << a << " needs a value\n"; std::exit(1); }
+        dst = argv[++i];
+        return true;
+      }
+      if (a.compare(0, dd.size() + 1, dd + "=") == 0) { dst = a.substr(dd.size() + 1); return true; }
+      if (a.compare(0, d.size() + 1, d + "=") == 0) { dst = a.substr(d.size() + 1); return true; }
+      return false;
+    };
+    if (a == "-mlir-to-cuda" || a == "--mlir-to-cuda") toCuda = true;
+    else if (a == "-mlir-to-cann" || a == "--mlir-to-cann") {
+      std::cerr << "afir-translate: this build targets sm_100a; use -mlir-to-cuda (the AscendC emitter is not part of it)\n";
+      return 1;
+    } else if (value("o", output) || value("tiling-space-out", spaceOut) || value("function", function)) {
+    } else if (a == "--help" || a == "-h") {
+      std::cout << "USAGE: afir-translate -mlir-to-cuda <input.mlir> [-o <kernel>.cuda.json] [--tiling-space-out <file>] [--function <name>]\n";
+      return 0;
+    } else if (a.size() > 1 && a[0] == '-') {
+      std::cerr << "afir-translate: Unknown command line argument '" << a << "'\n";
+      return 1;
+    } else if (input.empty()) input = a;
+    else { std::cerr << "afir-translate: more than one input file\n"; return 1; }
+  }
+  if (!toCuda) { std::cerr << "afir-translate: no translation requested (use -mlir-to-cuda)\n"; return 1; }
+  std::string text;
+  if (input.empty() || input == "-") text.assign(std::istreambuf_iterator<char>(std::cin), std::istreambuf_iterator<char>());
+  else {
+    std::ifstream is(input);
+    if (!is) { std::cerr << "afir-translate: cannot open " << input << "\n"; return 1; }
+    text.assign(std::istreambuf_iterator<char>(is), std::istreambuf_iterator<char>());
+  }
+  Module module;
+  if (Status s = parseModule(text, module); !s) { std::cerr << (input.empty() ? "<stdin>" : input) << ": error: " << s.message() << "\n"; return 1; }
+  const Func *func = nullptr;
+  for (const Func &f : module.funcs)
+    if (function.empty() ? module.funcs.size() == 1 : f.name == function) func = &f;
+  if (!func) {
+    std::cerr << "afir-translate: " << (function.empty() ? "the module holds several functions; pick one with --function" : "no function named '" + function + "'") << "\n";
+    return 1;
+  }
+  GroupAnalysis ga;
+  if (Status s = analyzeFunction(module, *func, ga); !s) { std::cerr << (input.empty() ? "<stdin>" : input) << ": error: " << s.message() << "\n"; return 1; }
+  const std::string desc = json::dump(ga.descriptor, 2) + "\n";
+  if (output.empty() || output == "-") std::cout << desc;
+  else {
+    std::ofstream os(output, std::ios::trunc);
+    os << desc;
+    if (!os) { std::cerr << "afir-translate: cannot write " << output << "\n"; return 1; }
+  }
+  if (!spaceOut.empty()) {
+    std::ofstream os(spaceOut, std::ios::trunc);
+    os << json::dump(ga.tilingSpace, 2) << "\n";
+    if (!os) { std::cerr << "afir-translate: cannot write " << spaceOut << "\n"; return 1; }
+  }
+  return 0;
+}

@@ -1,0 +1,178 @@
+"""afir-opt / afir-translate on CPU: the five benchmark groups written as MLIR text translate to the descriptors the
+kernels expect, annotation passes add the attributes the reference's FileCheck tests look for
+(test/Conversion/mark-structured-ops.mlir, annotate-ascendc-kernel-kind.mlir, annotate-mix-matmul-semantics.mlir),
+and anything outside the supported subset fails loudly."""
+import json
+import subprocess
+from pathlib import Path
+
+import pytest
+
+from ascend_mlir_b200 import build as lib_build
+from ascend_mlir_b200 import descriptors
+
+ROOT = Path(__file__).resolve().parent.parent
+BIN = ROOT / "ascend_mlir_b200" / "bin"
+EXAMPLES = ROOT / "ascend_mlir_b200" / "examples"
+REFERENCE = Path("/root/reference/examples")
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built():
+    lib_build.build()
+
+
+def opt(*args, stdin=None):
+    return subprocess.run([str(BIN / "afir-opt"), *map(str, args)], capture_output=True, text=True, input=stdin)
+
+
+def translate(path, *extra):
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", str(path), *map(str, extra)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return json.loads(r.stdout) if r.stdout.strip() else None
+
+
+def body_of(d):
+    return [(o["op"], o["a"], o["b"]) for o in d.get("body", [])]
+
+
+def views_of(d):
+    return [(v["arg"], v.get("map"), v.get("offset")) for v in d["loads"]]
+
+
+@pytest.mark.parametrize("name,builder", [
+    ("elementwise_chain", lambda: descriptors.add_mul("f32")),
+    ("split_relu_broadcast_add_mul", lambda: descriptors.split_relu_bias_mul(1)),
+    ("broadcast_add_reduce", lambda: descriptors.bcast_add_rowsum("f32")),
+    ("gather_elementwise", lambda: descriptors.gather_rows_scale_resid()),
+])
+def test_config_groups_translate_to_the_expected_descriptor(name, builder):
+    got = translate(EXAMPLES / f"{name}.mlir")
+    want = builder().descriptor
+    assert got["format"] == "afir-cuda-launch" and got["arch"] == "sm_100a" and got["kernel"] == name
+    for key in ("kernel_class", "dtype", "num_inputs", "num_outputs"):
+        assert got[key] == want[key], key
+    assert body_of(got) == body_of(want)
+    assert [v[0] for v in views_of(got)] == [v[0] for v in views_of(want)]
+    assert [v[1] for v in views_of(got)] == [v[1] for v in views_of(want)]
+    assert got["store"]["arg"] == want["store"]["arg"] and got["store"]["map"] == want["store"]["map"]
+    if name == "gather_elementwise":
+        assert got["gather"]["axis"] == 0 and got["gather"]["indices"]["dtype"] == "i32" and got["gather"]["indices"]["arg"] == 1
+    if name == "split_relu_broadcast_add_mul":
+        # h1 is the same argument read at a column offset of C = bias length
+        assert got["loads"][2]["offset"] == [0, 0, "dim_arg1_0"] and "offset" not in got["loads"][0]
+
+
+def test_matmul_group_epilogue_and_tiling_space(tmp_path):
+    out, space = tmp_path / "k.cuda.json", tmp_path / "ts.json"
+    assert translate(EXAMPLES / "matmul_add_leakyrelu.mlir", "-o", out, "--tiling-space-out", space) is None
+    d = json.loads(out.read_text())
+    assert d["kernel_class"] == "matmul" and d["num_inputs"] == 3
+    mm = d["matmul"]
+    assert (mm["a"], mm["b"], mm["bias"], mm["out"]) == (0, 1, 2, 3)
+    assert mm["epilogue"] == "BiasAddLeakyRelu" and abs(mm["alpha"] - 0.01) < 1e-12
+    assert (mm["in_dtype"], mm["bias_dtype"], mm["out_dtype"]) == ("bf16", "bf16", "bf16")
+    assert (mm["m"], mm["n"], mm["k"]) == ("dim_arg0_0", "dim_arg1_1", "dim_arg0_1")
+    ts = json.loads(space.read_text())
+    assert ts["kernel"] == "matmul_add_leakyrelu" and ts["soc"] == "sm_100a" and ts["kernel_file"] == "matmul_add_leakyrelu.cuda.json"
+    names = [p["name"] for p in ts["tiling_params"]]
+    assert names == [t["name"] for t in d["tiling"]] == ["STAGES", "dim_arg0_0", "dim_arg0_1", "dim_arg1_1"]
+    fixed = {p["name"]: p["shape_key"] for p in ts["tiling_params"] if p.get("fixed")}
+    assert fixed == {"dim_arg0_0": "arg0_dim0", "dim_arg0_1": "arg0_dim1", "dim_arg1_1": "arg1_dim1"}
+
+
+def test_annotation_passes_add_the_reference_attributes():
+    r = opt("--mark-structured-ops", "--annotate-ascendc-kernel-kind", EXAMPLES / "gather_elementwise.mlir")
+    assert r.returncode == 0, r.stderr
+    assert 'attributes {ascendc.kernel_kind = "vec"}' in r.stdout
+    marked = [l for l in r.stdout.splitlines() if "attrs = {" in l]
+    assert len(marked) == 1 and "embedding_dim = 0 : i64" in marked[0] and "gather_dim" not in r.stdout
+    r = opt("--annotate-ascendc-kernel-kind", "--annotate-mix-matmul-semantics", EXAMPLES / "matmul_add_leakyrelu.mlir")
+    assert r.returncode == 0, r.stderr
+    for needle in ['ascendc.kernel_kind = "mix"', 'abi_matmul_epilogue_kind = "BiasAddLeakyRelu"', "abi_matmul_has_bias = true",
+                   'abi_matmul_layout_a = "ND"', 'abi_matmul_op_kind = "matmul"', "abi_matmul_trans_b = false"]:
+        assert needle in r.stdout, needle
+    r = opt("--mark-structured-ops", EXAMPLES / "elementwise_chain.mlir")
+    assert r.returncode == 0 and "gather_dim" not in r.stdout and "embedding_dim" not in r.stdout
+
+
+def test_column_gather_is_marked_gather_dim():
+    text = """
+#cols = affine_map<(d0, d1) -> (d1)>
+#full = affine_map<(d0, d1) -> (d0, d1)>
+func.func @index_select(%data: tensor<?x?xf16>, %idx: tensor<?xi64>) -> tensor<?x?xf16> {
+  %c0 = arith.constant 0 : index
+  %m = tensor.dim %data, %c0 : tensor<?x?xf16>
+  %k = tensor.dim %idx, %c0 : tensor<?xi64>
+  %e = tensor.empty(%m, %k) : tensor<?x?xf16>
+  %g = linalg.generic {indexing_maps = [#cols, #full], iterator_types = ["parallel", "parallel"]}
+      ins(%idx : tensor<?xi64>) outs(%e : tensor<?x?xf16>) {
+  ^bb0(%i: i64, %o: f16):
+    %r = linalg.index 0 : index
+    %c = arith.index_cast %i : i64 to index
+    %v = tensor.extract %data[%r, %c] : tensor<?x?xf16>
+    linalg.yield %v : f16
+  } -> tensor<?x?xf16>
+  return %g : tensor<?x?xf16>
+}
+"""
+    r = opt("--mark-structured-ops", "--convert-afir-to-cuda", stdin=text)
+    assert r.returncode == 0, r.stderr
+    assert "attrs = {gather_dim = 1 : i64}" in r.stdout and "embedding_dim" not in r.stdout
+    assert 'afir.cuda_kernel_class = "gather"' in r.stdout and "afir.cuda_launch = " in r.stdout
+
+
+def test_without_passes_the_module_prints_back_unchanged():
+    src = (EXAMPLES / "broadcast_add_reduce.mlir").read_text()
+    r = opt(EXAMPLES / "broadcast_add_reduce.mlir")
+    assert r.returncode == 0 and r.stdout == src
+    r = opt("--canonicalize", "--cse", "--linalg-fuse-elementwise-ops", EXAMPLES / "broadcast_add_reduce.mlir")
+    assert r.returncode == 0 and 'afir.fused_group = "row_reduce"' in r.stdout
+
+
+@pytest.mark.parametrize("text,needle", [
+    ("func.func @f(%a: tensor<4xf32>) -> tensor<4xf32> {\n  %0 = math.exp %a : tensor<4xf32>\n  return %0 : tensor<4xf32>\n}", "unsupported operation 'math.exp'"),
+    ("func.func @f(%a: tensor<4xf32>) -> tensor<4xf32> {\n  %0 = afir.exp %a : tensor<4xf32> -> tensor<4xf32>\n  return %0 : tensor<4xf32>\n}", "outside the supported elementwise set"),
+    ("func.func @f(%a: tensor<4x3xf32>, %b: tensor<5xf32>) -> tensor<4x3xf32> {\n  %0 = afir.add %a, %b : (tensor<4x3xf32>, tensor<5xf32>) -> tensor<4x3xf32>\n  return %0 : tensor<4x3xf32>\n}", "not broadcastable"),
+    ("func.func @f(%a: tensor<4xf32>) -> tensor<4xf32> {\n  return %a : tensor<4xf32>\n", "unterminated region"),
+])
+def test_inputs_outside_the_subset_fail_loudly(text, needle):
+    r = opt("--convert-afir-to-cuda", stdin=text)
+    assert r.returncode == 1 and needle in r.stderr, r.stderr
+    assert r.stdout == ""
+
+
+def test_unknown_flags_are_errors():
+    r = opt("--ascendc-buffer-placement", EXAMPLES / "elementwise_chain.mlir")
+    assert r.returncode == 1 and "Unknown command line argument" in r.stderr
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cann", str(EXAMPLES / "elementwise_chain.mlir")], capture_output=True, text=True)
+    assert r.returncode == 1 and "use -mlir-to-cuda" in r.stderr
+
+
+def test_afir_broadcast_follows_numpy_trailing_alignment():
+    text = """func.func @bias(%x: tensor<8x16xf32>, %b: tensor<16xf32>, %c: tensor<8x1xf32>) -> tensor<8x16xf32> {
+  %0 = afir.add %x, %b : (tensor<8x16xf32>, tensor<16xf32>) -> tensor<8x16xf32>
+  %1 = afir.mul %0, %c : (tensor<8x16xf32>, tensor<8x1xf32>) -> tensor<8x16xf32>
+  return %1 : tensor<8x16xf32>
+}"""
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-"], capture_output=True, text=True, input=text)
+    assert r.returncode == 0, r.stderr
+    d = json.loads(r.stdout)
+    assert [v["map"] for v in d["loads"]] == [[0, 1], [1], [0, -1]]
+    assert body_of(d) == [("addf", "v0", "v1"), ("mulf", "%0", "v2")]
+
+
+@pytest.mark.skipif(not REFERENCE.exists(), reason="reference tree not mounted")
+@pytest.mark.parametrize("example,cls", [("add-broadcast-concat", "elementwise"), ("broadcast-add-reduce", "row_reduce"),
+                                         ("gather-elementwise-fusion", "gather"), ("matmul-add-leakyrelu", "matmul"),
+                                         ("relu-broadcast-transpose", "elementwise"), ("split-relu-brc-add-mul", "elementwise")])
+def test_reference_example_inputs_translate(example, cls):
+    d = translate(REFERENCE / example / "step0_input.mlir")
+    assert d["kernel_class"] == cls
+    if example == "matmul-add-leakyrelu":
+        assert d["matmul"]["epilogue"] == "BiasAddLeakyRelu" and abs(d["matmul"]["alpha"] - 0.001) < 1e-12
+        assert (d["matmul"]["in_dtype"], d["matmul"]["out_dtype"], d["matmul"]["bias_dtype"]) == ("f16", "f32", "f32")
+    if example == "gather-elementwise-fusion":
+        assert d["gather"]["axis"] == 1 and body_of(d) == [("maximumf", "v0", 0.0), ("addf", "%0", "v1")]
+    if example in ("add-broadcast-concat", "split-relu-brc-add-mul"):
+        assert len(d["groups"]) == 2 and d["groups"][1]["store"]["offset"][0] != 0
