@@ -59,8 +59,9 @@ def test_config_groups_translate_to_the_expected_descriptor(name, builder):
     if name == "gather_elementwise":
         assert got["gather"]["axis"] == 0 and got["gather"]["indices"]["dtype"] == "i32" and got["gather"]["indices"]["arg"] == 1
     if name == "split_relu_broadcast_add_mul":
-        # h1 is the same argument read at a column offset of C = bias length
-        assert got["loads"][2]["offset"] == [0, 0, "dim_arg1_0"] and "offset" not in got["loads"][0]
+        # h1 is the same argument read at a column offset of C
+        assert got["loads"][2]["offset"] == [0, 0, 1024] and "offset" not in got["loads"][0]
+        assert got["domain"] == [32, 1024, 1024] and got["loads"][0]["shape"] == [32, 1024, 2048]
 
 
 def test_matmul_group_epilogue_and_tiling_space(tmp_path):
