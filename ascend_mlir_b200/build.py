@@ -40,7 +40,8 @@ CU_SOURCES = {
 CPP_SOURCES = ["common/json.cpp", "runtime/descriptor.cpp", "runtime/launcher.cpp", "runtime/executor.cpp",
                "support/npy_io.cpp", "support/tiling_schema.cpp", "execution/output_comparator.cpp",
                "execution/task_graph.cpp", "execution/run_manifest.cpp", "execution/artifact_compiler.cpp",
-               "execution/execution_session.cpp", "front/mlir_text.cpp", "front/group_analysis.cpp", "runtime/capi.cpp"]
+               "execution/execution_session.cpp", "execution/resource_scheduler.cpp", "execution/global_scheduler.cpp",
+               "front/mlir_text.cpp", "front/group_analysis.cpp", "runtime/capi.cpp"]
 # command-line tools (reference: tools/runtime-session, tools/autotuner), linked with the same objects
 TOOLS = {"runtime-session": "tools/runtime_session_main.cpp", "autotuner": "tools/autotuner_main.cpp",
          "afir-opt": "tools/afir_opt_main.cpp", "afir-translate": "tools/afir_translate_main.cpp"}

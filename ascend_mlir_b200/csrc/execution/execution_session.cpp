@@ -3,9 +3,12 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdlib>
 #include <fstream>
+#include <mutex>
+#include <thread>
 
 #include "common/json.h"
 #include "runtime/executor.h"
@@ -43,7 +46,18 @@ json::Value tensorArray(const std::vector<TensorBinding> &bindings, const std::v
 
 class CudaBackendDriver final : public ExecutionBackendDriver {
 public:
-  explicit CudaBackendDriver(int device) : device_(device) {}
+  CudaBackendDriver(int device, size_t maxStreams) : device_(device), maxStreams_(std::max<size_t>(maxStreams, 1)) {}
+
+  BackendCapabilities capabilities() const override {
+    BackendCapabilities caps;
+    caps.supportsConcurrentDispatch = true;
+    caps.supportsConcurrentExecution = true;
+    caps.requiresSerializedLaunch = false;
+    caps.maxConcurrentTasks = maxStreams_;
+    caps.maxConcurrentStreams = maxStreams_;
+    return caps;
+  }
+  ExecutionBackendKind kind() const override { return ExecutionBackendKind::Cuda; }
 
   Status run(const ExecutionRequest &request, ExecutionResult &result) override {
     const RuntimeTask &task = request.task;
@@ -83,10 +97,8 @@ public:
     if (Status s = readFileBytes(task.artifact.deviceBinaryPath, binary); !s) return s.withStage("cuda:artifact");
 
     // ---- launch ----
-    if (!executor_) {
-      executor_ = std::make_unique<CudaExecutor>();
-      if (Status s = executor_->initialize(device_); !s) return s.withStage("cuda:device");
-    }
+    ExecutorLease executor_(*this);
+    if (Status s = executor_.acquire(); !s) return s.withStage("cuda:device");
     std::vector<const void *> inPtrs;
     std::vector<size_t> inBytes;
     for (auto &a : inputs) { inPtrs.push_back(a.data()); inBytes.push_back(a.nbytes()); }
@@ -173,14 +185,46 @@ public:
   }
 
 private:
+  // One executor (stream + buffer pool) per task in flight; idle ones are kept for the next task.
+  class ExecutorLease {
+  public:
+    explicit ExecutorLease(CudaBackendDriver &owner) : owner_(owner) {}
+    ~ExecutorLease() {
+      if (!held_) return;
+      std::lock_guard<std::mutex> lock(owner_.mutex_);
+      owner_.idle_.push_back(std::move(held_));
+    }
+    Status acquire() {
+      {
+        std::lock_guard<std::mutex> lock(owner_.mutex_);
+        if (!owner_.idle_.empty()) {
+          held_ = std::move(owner_.idle_.back());
+          owner_.idle_.pop_back();
+          return Status::success();
+        }
+      }
+      auto fresh = std::make_unique<CudaExecutor>();
+      if (Status s = fresh->initialize(owner_.device_); !s) return s;
+      held_ = std::move(fresh);
+      return Status::success();
+    }
+    CudaExecutor *operator->() { return held_.get(); }
+
+  private:
+    CudaBackendDriver &owner_;
+    std::unique_ptr<CudaExecutor> held_;
+  };
+
   int device_;
-  std::unique_ptr<CudaExecutor> executor_;
+  size_t maxStreams_;
+  std::mutex mutex_;
+  std::vector<std::unique_ptr<CudaExecutor>> idle_;
 };
 
 } // namespace
 
-std::shared_ptr<ExecutionBackendDriver> createCudaBackendDriver(int deviceId) {
-  return std::make_shared<CudaBackendDriver>(deviceId);
+std::shared_ptr<ExecutionBackendDriver> createCudaBackendDriver(int deviceId, size_t maxStreams) {
+  return std::make_shared<CudaBackendDriver>(deviceId, maxStreams);
 }
 
 std::pair<std::string, std::string> parseErrorStage(const std::string &message) {
@@ -203,23 +247,200 @@ Status ExecutionSession::plan(const TaskGraph &graph, SessionPlan &plan) const {
   return graph.topologicalOrder(plan.orderedTaskIds);
 }
 
-SessionRunSummary ExecutionSession::run(const TaskGraph &graph, const std::string &workRoot) {
+// Everything the serial and the concurrent runners share.  `mutex` guards all of it in the concurrent case.
+struct ExecutionSession::RunState {
   SessionRunSummary summary;
+  std::vector<RuntimeTask> order;
+  std::string workDir;
+  std::string sessionId;
+  std::map<std::string, std::map<std::string, std::string>> producedByTask;  // task -> output name -> file
+  std::map<std::string, ExecutionResult> resultByTask;
+  std::string firstError;
+  std::mutex mutex;
+
+  // Upstream task outputs become files; outputs without a path get one in the session directory.
+  Status resolveBindings(RuntimeTask &task) const {
+    for (TensorBinding &in : task.invocation.inputs) {
+      if (in.sourceKind != BindingSourceKind::TaskOutput) continue;
+      auto t = producedByTask.find(in.upstreamTaskId);
+      if (t == producedByTask.end())
+        return Status::error("[cuda:bindings] input '" + in.name + "' refers to unknown upstream task '" + in.upstreamTaskId + "'");
+      auto o = t->second.find(in.upstreamOutputName);
+      if (o == t->second.end())
+        return Status::error("[cuda:bindings] upstream task '" + in.upstreamTaskId + "' has no output '" + in.upstreamOutputName + "'");
+      in.path = o->second;
+    }
+    for (TensorBinding &out : task.invocation.outputs)
+      if (out.path.empty()) out.path = workDir + "/" + task.taskId + "." + out.name + ".npy";
+    return Status::success();
+  }
+  void recordSuccess(const RuntimeTask &task, ExecutionResult &&result) {
+    for (const TensorBinding &out : task.invocation.outputs) producedByTask[task.taskId][out.name] = out.path;
+    for (const auto &c : result.profileTrace.counters) summary.profileTrace.counters[c.first] += c.second;
+    resultByTask[task.taskId] = std::move(result);
+  }
+  // Results, profile events and artifact paths in plan order, whatever order the tasks finished in.
+  void collect() {
+    for (const RuntimeTask &t : order) {
+      auto it = resultByTask.find(t.taskId);
+      if (it == resultByTask.end()) continue;
+      for (const ProfileEvent &ev : it->second.profileTrace.events) {
+        summary.profileTrace.events.push_back(ev);
+        summary.profileArtifactPaths.push_back(ev.artifactPath);
+      }
+      summary.results.push_back(std::move(it->second));
+    }
+  }
+};
+
+static bool serialSchedulerForced() {
+  for (const char *name : {"ASCEND_RUNTIME_FORCE_SERIAL_SCHEDULER", "AFIR_RUNTIME_FORCE_SERIAL_SCHEDULER"}) {
+    const char *v = std::getenv(name);
+    if (v && *v && std::string(v) != "0") return true;
+  }
+  return false;
+}
+
+void ExecutionSession::runSerial(RunState &st) {
+  ProfileTrace &trace = st.summary.profileTrace;
+  trace.attributes["scheduler"] = "serial";
+  trace.attributes["scheduler_mode"] = "serial";
+  int64_t launched = 0;
+  for (RuntimeTask task : st.order) {
+    if (Status s = st.resolveBindings(task); !s) {
+      st.firstError = s.message();
+      return;
+    }
+    ExecutionRequest request;
+    request.sessionId = st.sessionId;
+    request.task = task;
+    request.workingDirectory = st.workDir;
+    ExecutionResult result;
+    if (Status s = driver_->run(request, result); !s) {
+      st.resultByTask[task.taskId] = std::move(result);
+      st.firstError = s.message();
+      return;
+    }
+    st.recordSuccess(task, std::move(result));
+    ++launched;
+  }
+  trace.counters["serialized_launch_count"] = launched;
+  trace.counters["max_in_flight_tasks"] = st.order.empty() ? 0 : 1;
+}
+
+void ExecutionSession::runConcurrent(RunState &st, const TaskGraph &graph, const BackendCapabilities &caps) {
+  GlobalScheduler &scheduler = scheduler_ ? *scheduler_ : globalScheduler();
+  ProfileTrace &trace = st.summary.profileTrace;
+  trace.attributes["scheduler"] = "concurrent";
+  trace.attributes["scheduler_mode"] = "concurrent";
+  trace.attributes["scheduler_scope"] = "global";
+
+  SessionHandle handle;
+  Status submitted = scheduling_ ? scheduler.submit(driver_->kind(), caps, graph, *scheduling_, handle)
+                                 : scheduler.submit(driver_->kind(), caps, graph, handle);
+  if (!submitted) {
+    st.firstError = submitted.message();
+    return;
+  }
+  const std::string globalId = handle.sessionId();
+  int64_t roots = 0;
+  for (const RuntimeTask &t : st.order) roots += t.dependencies.empty();
+  trace.counters["frontier_count"] = 1;
+  trace.counters["max_frontier_width"] = roots;
+
+  size_t inFlight = 0, maxInFlight = 0;
+  auto noteError = [&](const std::string &message) {  // st.mutex held
+    if (st.firstError.empty()) st.firstError = message;
+  };
+  auto worker = [&]() {
+    while (true) {
+      std::optional<RuntimeTask> next;
+      if (Status s = scheduler.waitAndAcquireTask(globalId, next); !s) {
+        std::lock_guard<std::mutex> lock(st.mutex);
+        noteError(s.message());
+        return;
+      }
+      if (!next) return;  // drained: all done, or failed and nothing of ours still runs
+      RuntimeTask task = std::move(*next);
+      Status ready;
+      {
+        std::lock_guard<std::mutex> lock(st.mutex);
+        ready = st.resolveBindings(task);
+        if (ready) maxInFlight = std::max(maxInFlight, ++inFlight);
+        else noteError(ready.message());
+      }
+      if (!ready) {
+        scheduler.failTask(globalId, task.taskId);
+        continue;
+      }
+      ExecutionRequest request;
+      request.sessionId = st.sessionId;
+      request.task = task;
+      request.workingDirectory = st.workDir;
+      ExecutionResult result;
+      const Status ran = driver_->run(request, result);
+      {
+        std::lock_guard<std::mutex> lock(st.mutex);
+        --inFlight;
+        if (ran) st.recordSuccess(task, std::move(result));
+        else {
+          st.resultByTask[task.taskId] = std::move(result);
+          noteError(ran.message());
+        }
+      }
+      if (!ran) {
+        if (Status s = scheduler.failTask(globalId, task.taskId); !s) {
+          std::lock_guard<std::mutex> lock(st.mutex);
+          noteError(s.message());
+        }
+        continue;
+      }
+      size_t newlyReady = 0;
+      const Status done = scheduler.completeTask(globalId, task.taskId, &newlyReady);
+      std::lock_guard<std::mutex> lock(st.mutex);
+      if (!done) noteError(done.message());
+      else if (newlyReady > 0) {
+        trace.counters["frontier_count"] += static_cast<int64_t>(newlyReady);
+        trace.counters["max_frontier_width"] = std::max(trace.counters["max_frontier_width"], static_cast<int64_t>(newlyReady));
+      }
+    }
+  };
+
+  const size_t hardware = std::thread::hardware_concurrency() ? std::thread::hardware_concurrency() : 4;
+  const size_t workers = std::max<size_t>(1, std::min({st.order.size(), std::max<size_t>(caps.maxConcurrentTasks, 1), hardware}));
+  std::vector<std::thread> pool;
+  for (size_t i = 0; i < workers; ++i) pool.emplace_back(worker);
+  for (std::thread &t : pool) t.join();
+
+  const SchedulerObservabilitySnapshot snapshot = scheduler.observabilitySnapshot();
+  scheduler.releaseSession(globalId);
+  for (const auto &a : snapshot.attributes) trace.attributes[a.first] = a.second;
+  for (const auto &c : snapshot.counters) trace.counters[c.first] = c.second;
+  trace.counters["max_in_flight_tasks"] = static_cast<int64_t>(maxInFlight);
+  trace.counters["worker_count"] = static_cast<int64_t>(workers);
+  if (st.firstError.empty() && st.producedByTask.size() != st.order.size())
+    st.firstError = "scheduler terminated with " + std::to_string(st.producedByTask.size()) + "/" +
+                    std::to_string(st.order.size()) + " tasks completed";
+}
+
+SessionRunSummary ExecutionSession::run(const TaskGraph &graph, const std::string &workRoot) {
+  RunState st;
+  SessionRunSummary &summary = st.summary;
   auto fail = [&](const std::string &message) {
     summary.success = false;
+    summary.validationPassed = false;
     summary.rawErrorMessage = message;
     auto parts = parseErrorStage(message);
     summary.errorStage = parts.first;
     summary.errorMessage = parts.second;
-    return summary;
+    return std::move(summary);
   };
-  std::vector<RuntimeTask> order;
-  if (Status s = graph.orderedTasks(order); !s) return fail(s.message());
-  for (const auto &t : order)
+  if (Status s = graph.orderedTasks(st.order); !s) return fail(s.message());
+  for (const auto &t : st.order)
     if (!t.invocation.expectedOutputs.empty()) summary.validationRan = true;
 
-  std::string workDir = workRoot;
-  if (workDir.empty()) {
+  st.workDir = workRoot;
+  if (st.workDir.empty()) {
     const char *tmp = std::getenv("TMPDIR");
     const std::string base = std::string(tmp && *tmp ? tmp : "/tmp") + "/afir-cuda-runtime";
     if (!makeDirs(base)) return fail("cannot create runtime session directory: " + base);
@@ -227,56 +448,24 @@ SessionRunSummary ExecutionSession::run(const TaskGraph &graph, const std::strin
     std::vector<char> buf(pattern.begin(), pattern.end());
     buf.push_back('\0');
     if (!::mkdtemp(buf.data())) return fail("cannot create runtime session directory under: " + base);
-    workDir = buf.data();
-  } else if (!makeDirs(workDir)) {
-    return fail("cannot create runtime session directory: " + workDir);
+    st.workDir = buf.data();
+  } else if (!makeDirs(st.workDir)) {
+    return fail("cannot create runtime session directory: " + st.workDir);
   }
-  const std::string sessionId = workDir.substr(workDir.rfind('/') + 1);
-  summary.profileTrace.sessionId = sessionId;
-  summary.profileTrace.attributes["working_directory"] = workDir;
-  summary.profileTrace.attributes["scheduler"] = "serial";
-  summary.profileTrace.counters["planned_task_count"] = static_cast<int64_t>(order.size());
+  st.sessionId = st.workDir.substr(st.workDir.rfind('/') + 1);
+  summary.profileTrace.sessionId = st.sessionId;
+  summary.profileTrace.attributes["working_directory"] = st.workDir;
+  summary.profileTrace.counters["planned_task_count"] = static_cast<int64_t>(st.order.size());
   if (!driver_) return fail("[cuda:device] no execution backend driver");
 
-  std::map<std::string, std::map<std::string, std::string>> producedByTask;  // task -> output name -> file
-  int64_t launched = 0;
-  for (RuntimeTask task : order) {
-    // resolve bindings: upstream task outputs become files, unnamed outputs get a file in the session directory
-    for (TensorBinding &in : task.invocation.inputs) {
-      if (in.sourceKind != BindingSourceKind::TaskOutput) continue;
-      auto t = producedByTask.find(in.upstreamTaskId);
-      if (t == producedByTask.end()) return fail("[cuda:bindings] input '" + in.name + "' refers to unknown upstream task '" + in.upstreamTaskId + "'");
-      auto o = t->second.find(in.upstreamOutputName);
-      if (o == t->second.end())
-        return fail("[cuda:bindings] upstream task '" + in.upstreamTaskId + "' has no output '" + in.upstreamOutputName + "'");
-      in.path = o->second;
-    }
-    for (TensorBinding &out : task.invocation.outputs)
-      if (out.path.empty()) out.path = workDir + "/" + task.taskId + "." + out.name + ".npy";
-    ExecutionRequest request;
-    request.sessionId = sessionId;
-    request.task = task;
-    request.workingDirectory = workDir;
-    ExecutionResult result;
-    if (Status s = driver_->run(request, result); !s) {
-      summary.results.push_back(std::move(result));
-      summary.validationPassed = false;
-      return fail(s.message());
-    }
-    for (const TensorBinding &out : task.invocation.outputs) producedByTask[task.taskId][out.name] = out.path;
-    for (const ProfileEvent &ev : result.profileTrace.events) {
-      summary.profileTrace.events.push_back(ev);
-      summary.profileArtifactPaths.push_back(ev.artifactPath);
-    }
-    for (const auto &c : result.profileTrace.counters) summary.profileTrace.counters[c.first] += c.second;
-    ++launched;
-    summary.results.push_back(std::move(result));
-  }
-  summary.profileTrace.counters["serialized_launch_count"] = launched;
-  summary.profileTrace.counters["max_in_flight_tasks"] = order.empty() ? 0 : 1;
+  const BackendCapabilities caps = driver_->capabilities();
+  if (st.order.size() > 1 && caps.supportsConcurrentDispatch && !serialSchedulerForced()) runConcurrent(st, graph, caps);
+  else runSerial(st);
+  st.collect();
+  if (!st.firstError.empty()) return fail(st.firstError);
   summary.validationPassed = summary.validationRan;
   summary.success = true;
-  return summary;
+  return std::move(summary);
 }
 
 } // namespace afir

@@ -11,6 +11,7 @@
 #include <string>
 #include <vector>
 
+#include "execution/global_scheduler.h"
 #include "execution/output_comparator.h"
 #include "execution/task_graph.h"
 
@@ -48,10 +49,15 @@ class ExecutionBackendDriver {
 public:
   virtual ~ExecutionBackendDriver() = default;
   virtual Status run(const ExecutionRequest &request, ExecutionResult &result) = 0;
+  // What the scheduler may assume.  The default is a driver that runs one task at a time; a driver that
+  // reports supportsConcurrentDispatch must accept run() from several threads at once.
+  virtual BackendCapabilities capabilities() const { return BackendCapabilities(); }
+  virtual ExecutionBackendKind kind() const { return ExecutionBackendKind::Host; }
 };
 
-// Runs tasks on CUDA device `deviceId` (AFIR_CUDA_DEVICE, default 0).
-std::shared_ptr<ExecutionBackendDriver> createCudaBackendDriver(int deviceId);
+// Runs tasks on CUDA device `deviceId` (AFIR_CUDA_DEVICE, default 0).  Tasks dispatched at the same time
+// each get an executor of their own (own stream, own pooled buffers), up to `maxStreams` of them.
+std::shared_ptr<ExecutionBackendDriver> createCudaBackendDriver(int deviceId, size_t maxStreams = 4);
 
 struct SessionPlan {
   std::vector<std::string> orderedTaskIds;
@@ -76,10 +82,22 @@ public:
   // Never throws or returns an error: failures are reported in the summary.
   SessionRunSummary run(const TaskGraph &graph, const std::string &workRoot = "");
   const std::string &backendName() const { return backendName_; }
+  // Graphs of more than one task go through a GlobalScheduler (the process-wide one unless another is set
+  // here) when the driver supports concurrent dispatch and ASCEND_RUNTIME_FORCE_SERIAL_SCHEDULER /
+  // AFIR_RUNTIME_FORCE_SERIAL_SCHEDULER is not set to a non-zero value: independent tasks then run on
+  // worker threads, and the first failure cancels what has not started.
+  void setScheduler(GlobalScheduler *scheduler) { scheduler_ = scheduler; }
+  void setScheduling(const SessionSchedulingOptions &options) { scheduling_ = options; }
 
 private:
+  struct RunState;
+  void runSerial(RunState &state);
+  void runConcurrent(RunState &state, const TaskGraph &graph, const BackendCapabilities &caps);
+
   std::string backendName_;
   std::shared_ptr<ExecutionBackendDriver> driver_;
+  GlobalScheduler *scheduler_ = nullptr;
+  std::optional<SessionSchedulingOptions> scheduling_;
 };
 
 // "[cuda:validate] text" -> {"validate", "text"}; untagged messages give an empty stage.

@@ -20,12 +20,13 @@ def built():
     lib_build.build()
 
 
-def test_cpp_runtime_support_checks(tmp_path):
-    exe = tmp_path / "test_runtime_support"
+@pytest.mark.parametrize("source", ["test_runtime_support", "test_scheduler"])
+def test_cpp_checks(tmp_path, source):
+    exe = tmp_path / source
     objs = [str(o) for o in sorted((ROOT / "ascend_mlir_b200" / "build").glob("*.o"))
             if "capi" not in o.name and "tools_" not in o.name]
     cmd = ["g++", "-std=c++17", "-O1", "-I", str(ROOT / "ascend_mlir_b200" / "csrc"), "-I", str(ROOT / "include"),
-           str(ROOT / "tests" / "cpp" / "test_runtime_support.cpp")] + objs + [
+           str(ROOT / "tests" / "cpp" / f"{source}.cpp")] + objs + [
         "-L", "/usr/local/cuda/lib64", "-lcudart_static", "-ldl", "-lrt", "-lpthread", "-o", str(exe)]
     subprocess.run(cmd, check=True)
     res = subprocess.run([str(exe)], capture_output=True, text=True)

@@ -1,6 +1,7 @@
 """runtime-session and autotuner end to end on the GPU: manifests and tiling spaces in the reference's formats,
 inputs/expected tensors as .npy, validation against the CPU oracle's outputs."""
 import json
+import os
 import subprocess
 from pathlib import Path
 
@@ -69,6 +70,7 @@ def test_two_task_graph_validates_and_profiles(tmp_path):
     out = r.stdout.splitlines()
     assert "session.result=success" in out and "session.validation=pass" in out and "session.backend=cuda" in out
     assert "session.profile.count=1" in out
+    assert "session.runtime.attribute.scheduler_mode=concurrent" in out and "session.runtime.counter.scheduler.task.succeeded=2" in out
     trace_path = [l.split("=", 1)[1] for l in out if l.startswith("session.profile[0]=")][0]
     trace = json.loads(Path(trace_path).read_text())
     assert trace["backend"] == "cuda" and trace["kernel_name"] == "add_mul" and trace["task_id"] == "chain"
@@ -84,6 +86,51 @@ def test_two_task_graph_validates_and_profiles(tmp_path):
     err = r.stderr.splitlines()
     assert "session.result=error" in err and "session.validation=fail" in err and "session.error_stage=validate" in err
     assert any("output comparison failed: max_abs_diff=1" in l for l in err)
+
+
+def test_independent_tasks_run_through_the_scheduler_on_their_own_streams(tmp_path):
+    """Four independent roots and one task that joins two of them: the session admits the roots together (one
+    executor and stream each), every result equals the oracle's, and the serial runner gives the same files."""
+    ew = descriptors.add_mul()
+    art = compile_artifact(tmp_path, ew, "art_ew")
+    M, N = 513, 640
+    rng = np.random.default_rng(7)
+    tasks, want = [], {}
+    for i in range(4):
+        a = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+        b = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+        np.save(tmp_path / f"a{i}.npy", a)
+        np.save(tmp_path / f"b{i}.npy", b)
+        want[f"root{i}"] = oracle.add_mul_f32(a, b)
+        tasks.append({"task_id": f"root{i}", "artifact_root": str(art),
+                      "inputs": [{"name": "a", "path": str(tmp_path / f"a{i}.npy")}, {"name": "b", "path": str(tmp_path / f"b{i}.npy")}],
+                      "outputs": [{"name": "out", "path": str(tmp_path / f"root{i}_out.npy"), "shape": [M, N], "dtype": "f32"}],
+                      "tiling": {"schema": str(tmp_path / "add_mul.tiling_space.json"),
+                                 "params": f"CTA_THREADS=128,UNROLL=2,dim_arg0_0={M},dim_arg0_1={N}"},
+                      "block_dim": 0})
+    want["join"] = oracle.add_mul_f32(want["root0"], want["root1"])
+    tasks.append({"task_id": "join", "artifact_root": str(art), "dependencies": ["root0", "root1"],
+                  "inputs": [{"name": "a", "source": "task_output", "upstream_task": "root0", "upstream_output": "out"},
+                             {"name": "b", "source": "task_output", "upstream_task": "root1", "upstream_output": "out"}],
+                  "outputs": [{"name": "out", "path": str(tmp_path / "join_out.npy"), "shape": [M, N], "dtype": "f32"}],
+                  "tiling": tasks[0]["tiling"], "block_dim": 0})
+    m = tmp_path / "run.json"
+    m.write_text(json.dumps({"backend": "cuda", "tasks": tasks}))
+    r = tool("runtime-session", "--run-manifest", m, "--run")
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = dict(l.split("=", 1) for l in r.stdout.splitlines() if "=" in l)
+    assert lines["session.runtime.attribute.scheduler_mode"] == "concurrent"
+    assert lines["session.runtime.counter.scheduler.task.succeeded"] == "5"
+    assert lines["session.runtime.counter.worker_count"] == "4"
+    assert int(lines["session.runtime.counter.max_in_flight_tasks"]) >= 1
+    for name, arr in want.items():
+        assert np.array_equal(np.load(tmp_path / f"{name}_out.npy"), arr), name
+        (tmp_path / f"{name}_out.npy").unlink()
+    r = subprocess.run([str(BIN / "runtime-session"), "--run-manifest", str(m), "--run"], capture_output=True, text=True,
+                       env={**os.environ, "ASCEND_RUNTIME_FORCE_SERIAL_SCHEDULER": "1"})
+    assert r.returncode == 0 and "session.runtime.attribute.scheduler_mode=serial" in r.stdout
+    for name, arr in want.items():
+        assert np.array_equal(np.load(tmp_path / f"{name}_out.npy"), arr), name
 
 
 def test_autotuner_searches_tile_parameters(tmp_path):
