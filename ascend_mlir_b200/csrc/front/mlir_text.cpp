@@ -290,7 +290,20 @@ std::string printModule(const Module &m) {
     return s;
   };
   for (const Func &f : m.funcs) {
-    if (!f.addedAttrs.empty() && f.attrInsertPos) ins.emplace_back(f.attrInsertPos, "attributes {" + attrText(f.addedAttrs) + "} ");
+    // attributes the function already carries (from an earlier run over the same text) are not repeated;
+    // new ones join the existing dictionary instead of opening a second one
+    std::vector<std::pair<std::string, std::string>> fresh;
+    for (const auto &kv : f.addedAttrs) {
+      bool dup = f.existingAttrs.find(kv.first + " =") != std::string::npos;
+      for (const auto &seen : fresh) dup = dup || seen.first == kv.first;
+      if (!dup) fresh.push_back(kv);
+    }
+    if (!fresh.empty() && f.attrDictPos) {
+      const bool emptyDict = f.existingAttrs.find_first_not_of("{} \t\n") == std::string::npos;
+      ins.emplace_back(f.attrDictPos + 1, attrText(fresh) + (emptyDict ? "" : ", "));
+    } else if (!fresh.empty() && f.attrInsertPos) {
+      ins.emplace_back(f.attrInsertPos, "attributes {" + attrText(fresh) + "} ");
+    }
     for (const Op &o : f.ops) {
       if (o.addedAttrs.empty() || !o.attrInsertPos) continue;
       const bool generic = o.name == "linalg.generic";

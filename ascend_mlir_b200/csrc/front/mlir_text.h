@@ -75,6 +75,8 @@ struct Func {
   std::vector<Type> resultTypes;
   std::vector<Op> ops;
   size_t attrInsertPos = 0;           // just before the body's '{'
+  size_t attrDictPos = 0;             // position of the '{' of an existing "attributes {...}" (0 = none)
+  std::string existingAttrs;          // text of that dictionary, braces included
   std::vector<std::pair<std::string, std::string>> addedAttrs;
   int line = 0;
 };
