@@ -152,7 +152,16 @@ Status CudaExecutor::runHost(const RunRequest &req) {
     for (size_t b : args.argBytes) total += b;
     if (plan.possible && total >= (16u << 20) && plan.rows >= 2 && !std::getenv("AFIR_CUDA_NO_PIPELINE")) {
       const int64_t quantum = desc->kernelClass == KernelClass::Matmul ? 256 : (plan.rows >= 64 ? 8 : 1);
-      int64_t chunkRows = (plan.rows + 5) / 6;
+      // Chunks of about 16 MiB of sliced bytes, 4 to 12 of them: the copy-in stream never idles, so the time
+      // not hidden is one chunk's kernel and copy-out at the end; smaller chunks shorten that tail until the
+      // per-copy launch cost (a few microseconds each) starts to show (measured: flat from 8 to 24 chunks
+      // on 192 MiB, slower again at 32).
+      size_t sliced = 0;
+      for (size_t a = 0; a < args.argBytes.size(); ++a)
+        if (plan.rowBytes[a]) sliced += args.argBytes[a];
+      int64_t chunks = std::min<int64_t>(12, std::max<int64_t>(4, static_cast<int64_t>(sliced / (16u << 20))));
+      if (const char *forced = std::getenv("AFIR_CUDA_PIPELINE_CHUNKS")) chunks = std::max<int64_t>(2, std::atoll(forced));
+      int64_t chunkRows = (plan.rows + chunks - 1) / chunks;
       chunkRows = ((chunkRows + quantum - 1) / quantum) * quantum;
       if (chunkRows < plan.rows) return runHostPipelined(req, *desc, tiling, args, plan, chunkRows);
     }
