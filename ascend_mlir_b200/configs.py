@@ -167,6 +167,38 @@ def matmul_add_leakyrelu(M: int = 8192, N: int = 8192, K: int = 8192, alpha: flo
     return make(A)
 
 
+# ---- transpose-class groups (not among the five benchmark configurations; reference examples at scale) -----------
+def transpose_2d(R: int = 8192, C: int = 8192, seed: int = 0) -> Workload:
+    """out[c, r] = in[r, c] on f16: the standalone permutation group."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((R, C), dtype=np.float32).astype(np.float16)
+    spec = descriptors.transpose_2d("f16")
+    return Workload("transpose_2d", spec, {"R": R, "C": C}, [x], (C, R), np.dtype(np.float16),
+                    algorithmic_bytes=2 * R * C * 2, units=C, notes="64x64 shared-memory tiles")
+
+
+def relu_broadcast_transpose_add(M: int = 8192, N: int = 8192, seed: int = 0) -> Workload:
+    """out[n, m] = relu(d0[m, 0]) + d1[n, m] on f16 (the reference's relu-broadcast-transpose example)."""
+    rng = np.random.default_rng(seed)
+    d0 = rng.standard_normal((M, 1), dtype=np.float32).astype(np.float16)
+    d1 = rng.standard_normal((N, M), dtype=np.float32).astype(np.float16)
+    spec = descriptors.relu_bcast_transpose_add("f16")
+
+    def make(d1_):
+        n = d1_.shape[0]
+        w = Workload("relu_broadcast_transpose_add", spec, {"M": M, "N": n}, [d0, d1_], (n, M), np.dtype(np.float16),
+                     algorithmic_bytes=2 * n * M * 2 + M * 2, units=n, notes="d0 replicated per GPU")
+        w.sharder = lambda r, k: make(np.ascontiguousarray(d1_[slice(*row_range(n, r, k))]))
+        return w
+
+    return make(d1)
+
+
+EXTRA_CONFIGS: Dict[str, Callable[..., Workload]] = {
+    "transpose_2d": transpose_2d,
+    "relu_broadcast_transpose_add": relu_broadcast_transpose_add,
+}
+
 CONFIGS: Dict[str, Callable[..., Workload]] = {
     "elementwise_chain": elementwise_chain,
     "split_relu_broadcast_add_mul": split_relu_broadcast_add_mul,

@@ -137,7 +137,8 @@ struct GatherLaunch {
 int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched);
 
 // ---------------------------------------------------------------------------------------------
-// 2-D transpose out[c, r] = in[r, c] through a padded shared-memory tile (2- or 4-byte elements).
+// 2-D transpose out[c, r] = in[r, c] (2- or 4-byte elements): register-block kernel for 16-byte-aligned
+// operands, padded shared-memory tile kernel otherwise.
 // ---------------------------------------------------------------------------------------------
 struct TransposeLaunch {
   int elemBytes;
@@ -146,6 +147,11 @@ struct TransposeLaunch {
   int64_t inRowStride;
   void *out;
   int64_t outRowStride;
+  int warpRows = 0;         // warps of a CTA stacked along the input rows: 1, 2, 4 or 8 (0 = default)
+  int ctasPerSm = 0;        // persistent grid of SMs x this many CTAs (0 = one CTA per tile)
+  int diagonalOrder = 0;    // 1: tiles in diagonal order instead of row-major order
+  int variant = 0;          // 0: whole lines stored, 1: same with 2 blocks per thread, 2: whole lines loaded, 3: same, 2 blocks
+  int forceTileKernel = 0;  // 1: use the shared-memory tile kernel even when the operands are aligned
 };
 int launchTranspose(const TransposeLaunch &l, cudaStream_t stream, int *launched);
 

@@ -254,6 +254,11 @@ Status parseDescriptorJson(const json::Value &root, LaunchDescriptor &out) {
     out.bulkCopyField = l->getString("bulk_copy");
     out.streamStagesField = l->getString("stream_stages");
     out.streamChunkField = l->getString("stream_chunk_bytes");
+    out.warpRowsField = l->getString("warp_rows");
+    out.ctasPerSmField = l->getString("ctas_per_sm");
+    out.tileKernelField = l->getString("tile_kernel");
+    out.tileOrderField = l->getString("tile_order");
+    out.variantField = l->getString("variant");
   }
 
   if (out.kernelClass == KernelClass::Matmul) {

@@ -72,7 +72,8 @@ struct LaunchDescriptor {
   std::vector<GroupSpec> groups;
   MatmulSpec matmul;
   // names of the tiling fields carrying B200 launch parameters (empty = library default)
-  std::string ctaThreadsField, unrollField, splitColsField, stagesField, teamLanesField, bulkCopyField, streamStagesField, streamChunkField;
+  std::string ctaThreadsField, unrollField, splitColsField, stagesField, teamLanesField, bulkCopyField, streamStagesField, streamChunkField,
+      warpRowsField, ctasPerSmField, tileKernelField, tileOrderField, variantField;
   size_t tilingBytes() const;
 };
 

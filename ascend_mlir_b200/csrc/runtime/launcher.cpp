@@ -323,6 +323,11 @@ Status launchTransposeGroup(const LaunchDescriptor &d, const GroupSpec &g, const
   l.inRowStride = in.stride[1];
   l.out = argAt(args, store);
   l.outRowStride = store.stride[0];
+  l.warpRows = static_cast<int>(optionalField(d.warpRowsField, tiling));
+  l.ctasPerSm = static_cast<int>(optionalField(d.ctasPerSmField, tiling));
+  l.forceTileKernel = optionalField(d.tileKernelField, tiling) != 0;
+  l.diagonalOrder = optionalField(d.tileOrderField, tiling) != 0;
+  l.variant = static_cast<int>(optionalField(d.variantField, tiling));
   int n = 0;
   Status s = cudaStatus(kernels::launchTranspose(l, args.stream, &n), "transpose launch");
   info.kernelsLaunched += n;

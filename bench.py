@@ -5,7 +5,8 @@
 
 A step is one pass of one fused group over one batch of seeded synthetic input.  The default
 workload is the split-relu-broadcast-add-mul group (f16 [32,1024,2048] -> [32,1024,1024]); the other
-four benchmark groups are timed the same way and reported under "groups" in the same JSON line.
+four benchmark groups and two transpose-class groups (a plain 2-D transpose and the reference's
+relu-broadcast-transpose example at [8192,8192]) are timed the same way and reported under "groups".
 `value` is device-resident throughput (CUDA events on the launching stream), `e2e` the same pass
 through afirt_executor_run with pinned HOST buffers (H2D + kernel + D2H inside the timed region).
 With N > 1 (torchrun, one rank per GPU) every rank runs a full-size batch of its own (the leading
@@ -40,6 +41,7 @@ NCU_DRAM_BYTES_PER_LAUNCH = {
     "broadcast_add_reduce": 271949824,
     "gather_elementwise": 363983360,
     "matmul_add_leakyrelu": 951392256,
+    "transpose_2d": 217530624,
 }
 
 
@@ -123,6 +125,12 @@ def cpu_sample(name: str):
     if name == "matmul_add_leakyrelu":
         w = configs.matmul_add_leakyrelu(M=256)
         return w, (lambda: oracle.matmul_bias_leakyrelu_bf16(*w.inputs, 0.01)), "256 of 8192 output rows (N=K=8192)"
+    if name == "transpose_2d":
+        w = configs.transpose_2d()
+        return w, (lambda: oracle.transpose_2d(w.inputs[0])), "full size, f16 [8192,8192]"
+    if name == "relu_broadcast_transpose_add":
+        w = configs.relu_broadcast_transpose_add()
+        return w, (lambda: oracle.relu_bcast_transpose_add_f16(*w.inputs)), "full size, f16 [8192,8192]"
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -169,7 +177,8 @@ def run_reference_arm(args):
 
 def dtype_of(name):
     return {"elementwise_chain": "f32", "split_relu_broadcast_add_mul": "f16", "broadcast_add_reduce": "f32",
-            "gather_elementwise": "bf16", "matmul_add_leakyrelu": "bf16"}[name]
+            "gather_elementwise": "bf16", "matmul_add_leakyrelu": "bf16", "transpose_2d": "f16",
+            "relu_broadcast_transpose_add": "f16"}[name]
 
 
 # ---- GPU arm ------------------------------------------------------------------------------------------------
@@ -259,14 +268,15 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    names = [args.workload] + ([n for n in configs.CONFIGS if n != args.workload] if args.all_groups else [])
+    everything = {**configs.CONFIGS, **configs.EXTRA_CONFIGS}
+    names = [args.workload] + ([n for n in everything if n != args.workload] if args.all_groups else [])
     results, main = {}, None
     sampler = ClockSampler(local)
     sampler.start()
     for name in names:
         try:
             # weak scaling: every rank owns one full-size batch (a distinct seed per rank)
-            w = configs.CONFIGS[name](seed=rank)
+            w = everything[name](seed=rank)
             g = DeviceGroup(torch, rt, w, device, stream)
             steps = args.steps if name == args.workload else max(20, min(args.steps, 200))
             ms, launches = g.timed(steps, args.warmup, sync)
@@ -325,7 +335,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(configs.CONFIGS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(configs.CONFIGS) + list(configs.EXTRA_CONFIGS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--one-group", dest="all_groups", action="store_false", help="time only --workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-CPU baseline leg")

@@ -125,6 +125,38 @@ def test_transpose_2d(rt, R, C, dtype):
     assert out.tobytes() == oracle.transpose_2d(x).tobytes()
 
 
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("warp_rows", [1, 2, 4, 8])
+def test_transpose_2d_every_warp_arrangement(rt, dtype, warp_rows):
+    """Aligned operands take the register-block kernel: whole tiles, ragged tiles in both directions, and a
+    shape smaller than one block, for every arrangement of the CTA's warps and for the tile kernel."""
+    rng = np.random.default_rng(11)
+    spec = descriptors.transpose_2d("f16" if dtype == np.float16 else "f32")
+    for R, C in [(512, 256), (520, 264), (8, 8), (1000, 24), (24, 1000), (4, 4)]:
+        x = rng.standard_normal((R, C)).astype(dtype)
+        want = oracle.transpose_2d(x).tobytes()
+        out = run(rt, spec, [x], np.zeros((C, R), dtype), {"R": R, "C": C}, WARP_ROWS=warp_rows, CTAS_PER_SM=4)
+        assert out.tobytes() == want, (R, C, "blocks")
+        out = run(rt, spec, [x], np.zeros((C, R), dtype), {"R": R, "C": C}, WARP_ROWS=warp_rows, TILE_ORDER=1)
+        assert out.tobytes() == want, (R, C, "diagonal tile order")
+        for variant in (1, 2, 3):
+            out = run(rt, spec, [x], np.zeros((C, R), dtype), {"R": R, "C": C}, WARP_ROWS=warp_rows, VARIANT=variant)
+            assert out.tobytes() == want, (R, C, "variant", variant)
+        out = run(rt, spec, [x], np.zeros((C, R), dtype), {"R": R, "C": C}, TILE_KERNEL=1)
+        assert out.tobytes() == want, (R, C, "tiles")
+
+
+def test_transpose_2d_round_trip_at_full_size(rt):
+    """Size-independent property at the bench shape: transposing twice gives the input back, bit for bit."""
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((8192, 8192), dtype=np.float32).astype(np.float16)
+    spec = descriptors.transpose_2d("f16")
+    once = run(rt, spec, [x], np.zeros((8192, 8192), np.float16), {"R": 8192, "C": 8192})
+    assert once[5, 7] == x[7, 5] and once[8191, 0] == x[0, 8191]
+    twice = run(rt, spec, [once], np.zeros((8192, 8192), np.float16), {"R": 8192, "C": 8192})
+    assert twice.tobytes() == x.tobytes()
+
+
 def test_interpreted_body_matches_oracle_chain(rt):
     # a chain with no straight-line specialisation: ((a - b) / b) min a
     spec = descriptors.add_mul()
