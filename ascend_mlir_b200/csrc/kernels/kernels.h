@@ -133,6 +133,12 @@ struct GatherLaunch {
   BodyProgram body;
   unsigned long long *status;  // device counter of out-of-range indices (may be null)
   int ctaThreads, unroll, gridBlocks;
+  // row gather, bulk-copy staged kernel: opt-in (measured slower than the plain kernel on B200 for rows of
+  // 256 bytes to 8 KB), used only when stagedCopies is set and the shapes qualify
+  int stagedCopies = 0;
+  int streamStages = 0;            // ring depth per warp, 2..8 (0 = 3)
+  int streamRows = 0;              // rows per stage, 1..32 (0 = about 4 KB worth)
+  int streamWarps = 0;             // warps per CTA, 1..16 (0 = 8)
 };
 int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched);
 

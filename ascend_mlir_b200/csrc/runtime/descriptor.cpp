@@ -259,6 +259,8 @@ Status parseDescriptorJson(const json::Value &root, LaunchDescriptor &out) {
     out.tileKernelField = l->getString("tile_kernel");
     out.tileOrderField = l->getString("tile_order");
     out.variantField = l->getString("variant");
+    out.streamRowsField = l->getString("stream_rows");
+    out.streamWarpsField = l->getString("stream_warps");
   }
 
   if (out.kernelClass == KernelClass::Matmul) {

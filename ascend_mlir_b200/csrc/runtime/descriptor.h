@@ -73,7 +73,7 @@ struct LaunchDescriptor {
   MatmulSpec matmul;
   // names of the tiling fields carrying B200 launch parameters (empty = library default)
   std::string ctaThreadsField, unrollField, splitColsField, stagesField, teamLanesField, bulkCopyField, streamStagesField, streamChunkField,
-      warpRowsField, ctasPerSmField, tileKernelField, tileOrderField, variantField;
+      warpRowsField, ctasPerSmField, tileKernelField, tileOrderField, variantField, streamRowsField, streamWarpsField;
   size_t tilingBytes() const;
 };
 

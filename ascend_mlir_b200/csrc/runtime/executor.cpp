@@ -391,6 +391,8 @@ Status CudaExecutor::synchronize(void *stream) {
     unsigned long long bad = 0;
     e = cudaMemcpy(&bad, statusWorkspace_, sizeof(bad), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] status read failed");
+    constexpr unsigned long long kGatherTimeoutFlag = 1ull << 62;  // set by the staged gather kernel when a stage wait ran out
+    if (bad & kGatherTimeoutFlag) return Status::error("[cuda:kernel_launch] gather kernel gave up waiting for a staged copy");
     if (bad) return Status::error("[cuda:kernel_launch] gather index out of range (" + std::to_string(bad) + " indices)");
   }
   if (reducePending_) {

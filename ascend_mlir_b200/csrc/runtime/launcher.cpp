@@ -297,6 +297,13 @@ Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const st
   l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
   l.unroll = static_cast<int>(optionalField(d.unrollField, tiling));
   l.gridBlocks = args.blockDim;
+  if (!d.bulkCopyField.empty()) {
+    auto it = tiling.find(d.bulkCopyField);
+    if (it != tiling.end() && it->second == 1) l.stagedCopies = 1;
+  }
+  l.streamStages = static_cast<int>(optionalField(d.streamStagesField, tiling));
+  l.streamRows = static_cast<int>(optionalField(d.streamRowsField, tiling));
+  l.streamWarps = static_cast<int>(optionalField(d.streamWarpsField, tiling));
   int n = 0;
   Status s = cudaStatus(kernels::launchGather(l, args.stream, &n), "gather launch");
   info.kernelsLaunched += n;

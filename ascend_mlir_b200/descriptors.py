@@ -81,7 +81,12 @@ def _spec(name, kernel_class, dtype, num_inputs, num_outputs, tile_params, dims,
 
 
 _EW_TILE = [("CTA_THREADS", 128, (128, 256, 512)), ("UNROLL", 2, (1, 2, 4))]
-_GATHER_TILE = [("CTA_THREADS", 128, (128, 256, 512)), ("UNROLL", 1, (1, 2, 4))]
+_GATHER_TILE = [("CTA_THREADS", 128, (128, 256, 512)), ("UNROLL", 1, (1, 2, 4)), ("BULK_COPY", 0, (0, 1)),
+                ("STREAM_STAGES", 0, (0, 2, 3, 4, 6)), ("STREAM_ROWS", 0, (0, 2, 4, 8, 16)),
+                ("STREAM_WARPS", 0, (0, 4, 8, 16))]
+_GATHER_LAUNCH = {"cta_threads": "CTA_THREADS", "unroll": "UNROLL", "bulk_copy": "BULK_COPY",
+                  "stream_stages": "STREAM_STAGES", "stream_rows": "STREAM_ROWS",
+                  "stream_warps": "STREAM_WARPS"}
 _EW_LAUNCH = {"cta_threads": "CTA_THREADS", "unroll": "UNROLL"}
 
 
@@ -203,7 +208,7 @@ def gather_rows_scale_resid(dtype: str = "bf16", index_dtype: str = "i32", name:
             "gather": {"axis": 0, "indices": {"arg": 1, "dtype": index_dtype, "shape": ["dim_arg1_0"]}},
             "store": {"arg": 4, "shape": dom, "map": [0, 1]},
             "body": [op("mulf", "v0", "v1"), op("addf", "%0", "v2")]}
-    return _spec(name, "gather", dtype, 4, 1, _GATHER_TILE, dims, body, _EW_LAUNCH)
+    return _spec(name, "gather", dtype, 4, 1, _GATHER_TILE, dims, body, _GATHER_LAUNCH)
 
 
 def relu_gather_cols_bias(dtype: str = "f16", index_dtype: str = "i64", name: str = "relu_index_select_add") -> KernelSpec:
@@ -215,7 +220,7 @@ def relu_gather_cols_bias(dtype: str = "f16", index_dtype: str = "i64", name: st
             "gather": {"axis": 1, "indices": {"arg": 1, "dtype": index_dtype, "shape": ["dim_arg1_0"]}},
             "store": {"arg": 3, "shape": dom, "map": [0, 1]},
             "body": [op("maximumf", "v0", 0.0), op("addf", "%0", "v1")]}
-    return _spec(name, "gather", dtype, 3, 1, _GATHER_TILE, dims, body, _EW_LAUNCH)
+    return _spec(name, "gather", dtype, 3, 1, _GATHER_TILE, dims, body, _GATHER_LAUNCH)
 
 
 # ---- matmul + bias + LeakyReLU -----------------------------------------------------------------------------

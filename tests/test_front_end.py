@@ -45,6 +45,7 @@ def views_of(d):
     ("split_relu_broadcast_add_mul", lambda: descriptors.split_relu_bias_mul(1)),
     ("broadcast_add_reduce", lambda: descriptors.bcast_add_rowsum("f32")),
     ("gather_elementwise", lambda: descriptors.gather_rows_scale_resid()),
+    ("transpose_2d", lambda: descriptors.transpose_2d("f16")),
 ])
 def test_config_groups_translate_to_the_expected_descriptor(name, builder):
     got = translate(EXAMPLES / f"{name}.mlir")
@@ -56,6 +57,9 @@ def test_config_groups_translate_to_the_expected_descriptor(name, builder):
     assert [v[0] for v in views_of(got)] == [v[0] for v in views_of(want)]
     assert [v[1] for v in views_of(got)] == [v[1] for v in views_of(want)]
     assert got["store"]["arg"] == want["store"]["arg"] and got["store"]["map"] == want["store"]["map"]
+    if name == "transpose_2d":
+        # a bare permutation is the transpose class with that kernel's launch parameters, not an elementwise group
+        assert got["launch"] == want["launch"] and [t["name"] for t in got["tiling"]] == [t["name"] for t in want["tiling"]]
     if name == "gather_elementwise":
         assert got["gather"]["axis"] == 0 and got["gather"]["indices"]["dtype"] == "i32" and got["gather"]["indices"]["arg"] == 1
     if name == "split_relu_broadcast_add_mul":

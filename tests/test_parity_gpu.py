@@ -234,6 +234,48 @@ def test_gather_rows_out_of_range_index_is_reported_not_clamped(rt):
     assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(*w.inputs))
 
 
+@pytest.mark.parametrize("T,W,R,tile", [
+    (5000, 256, 40003, {"BULK_COPY": 1}),                     # default ring: 8 rows per stage, ragged last chunk
+    (70000, 64, 80001, {"BULK_COPY": 1}),                     # 128-byte rows: 32 rows per stage
+    (5000, 256, 40003, {"BULK_COPY": 1, "STREAM_STAGES": 2, "STREAM_ROWS": 4}),
+    (5000, 256, 40003, {"BULK_COPY": 1, "STREAM_STAGES": 6, "STREAM_ROWS": 2}),
+    (3000, 512, 30001, {"BULK_COPY": 1, "STREAM_STAGES": 4, "STREAM_ROWS": 16}),
+    (5000, 256, 80001, {"BULK_COPY": 1, "STREAM_STAGES": 3, "STREAM_ROWS": 4, "STREAM_WARPS": 16}),
+    (9000, 128, 160001, {"BULK_COPY": 1, "STREAM_WARPS": 4}),  # rows shorter than a warp of vectors
+    (5000, 256, 40003, {}),                                   # same shapes on the default plain-load kernel
+])
+def test_gather_rows_staged_kernel_bit_exact(rt, monkeypatch, T, W, R, tile):
+    """The opt-in bulk-copy staged kernel at shapes large enough for it, whole launch (the host path is told not
+    to cut the rows into chunks, which would fall below the kernel's size threshold)."""
+    monkeypatch.setenv("AFIR_CUDA_NO_PIPELINE", "1")
+    w = configs.gather_elementwise(T, W, R, seed=14)
+    w.inputs[1][:6] = [0, T - 1, 0, T - 1, 17, 17]
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape, **tile)
+    assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(*w.inputs))
+
+
+def test_gather_rows_staged_kernel_i64_indices_and_bad_indices(rt, monkeypatch):
+    monkeypatch.setenv("AFIR_CUDA_NO_PIPELINE", "1")
+    w = configs.gather_elementwise(5000, 256, 40003, seed=15)
+    spec = descriptors.gather_rows_scale_resid("bf16", "i64")
+    inputs = [w.inputs[0], w.inputs[1].astype(np.int64), w.inputs[2], w.inputs[3]]
+    want = oracle.gather_rows_scale_resid_bf16(*w.inputs)
+    out = run(rt, spec, inputs, w.new_output(), w.shape, BULK_COPY=1)
+    assert np.array_equal(out, want)
+    # out-of-range indices in the middle of a stage and in the ragged last chunk: counted; the other rows are right
+    bad_rows = [11, 12, 20001, 40002]
+    inputs[1][bad_rows] = [5000, -3, 1 << 40, 5000]
+    out = np.full(w.out_shape, 0x7FC0, np.uint16)
+    with pytest.raises(ExecutorError, match=r"gather index out of range \(4 indices\)"):
+        rt.run(spec.binary, spec.name, inputs, [out], spec.pack(w.shape, BULK_COPY=1))
+    keep = np.ones(40003, bool)
+    keep[bad_rows] = False
+    assert np.array_equal(out[keep], want[keep])
+    inputs[1][bad_rows] = 0
+    out = run(rt, spec, inputs, w.new_output(), w.shape, BULK_COPY=1)
+    assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(inputs[0], inputs[1].astype(np.int32), inputs[2], inputs[3]))
+
+
 def test_reference_gather_example_golden_exact(rt, golden_dir):
     g = dict(np.load(golden_dir / "gather_elementwise_fusion.npz"))
     spec = descriptors.relu_gather_cols_bias()

@@ -87,6 +87,15 @@ def test_gather_group_from_linalg(rt, tmp_path):
     assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(*w.inputs))
 
 
+def test_transpose_group_from_linalg(rt, tmp_path):
+    binary, space = compile_from_mlir("transpose_2d", tmp_path)
+    assert {p["name"] for p in space["tiling_params"] if not p.get("fixed")} >= {"WARP_ROWS", "VARIANT"}
+    x = np.random.default_rng(66).standard_normal((1000, 520)).astype(np.float16)
+    out = np.zeros((520, 1000), np.float16)
+    rt.run(binary, "transpose_2d", [x], [out], pack(space, [x, out]))
+    assert out.tobytes() == oracle.transpose_2d(x).tobytes()
+
+
 def test_matmul_group_from_linalg(rt, tmp_path):
     binary, space = compile_from_mlir("matmul_add_leakyrelu", tmp_path)
     w = configs.matmul_add_leakyrelu(512, 768, 320, seed=65)
