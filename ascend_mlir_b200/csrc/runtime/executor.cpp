@@ -3,6 +3,7 @@
 #include <cuda_runtime_api.h>
 
 #include <algorithm>
+#include <cctype>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -79,6 +80,46 @@ Status CudaExecutor::ownWorkspace(size_t bytes) {
   return Status::success();
 }
 
+// ASCEND_RUNTIME_TRACE_LAUNCH / AFIR_CUDA_TRACE_LAUNCH set to anything but 0/false/off/no: every launch prints
+// its arguments, their alignment and the tiling words to stderr, in the line format of the reference's launch
+// trace (lib/Runtime/Execution/LaunchTrace.cpp:40-103) with "cuda-launch" as the tag.
+static bool launchTraceEnabled() {
+  for (const char *name : {"ASCEND_RUNTIME_TRACE_LAUNCH", "AFIR_CUDA_TRACE_LAUNCH"}) {
+    const char *raw = std::getenv(name);
+    if (!raw || !*raw) continue;
+    std::string v(raw);
+    for (char &c : v) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+    if (v != "0" && v != "false" && v != "off" && v != "no") return true;
+  }
+  return false;
+}
+
+static void printLaunchTrace(const RunRequest &req, const LaunchDescriptor &desc, const LaunchArgs &args, int device, const char *path) {
+  auto ptr = [](const void *p) {
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "%p align512=%s", p, (reinterpret_cast<uintptr_t>(p) & 511u) == 0 ? "yes" : "no");
+    return std::string(buf);
+  };
+  std::fprintf(stderr, "[cuda-launch] kernel=%s class=%d path=%s magic=0x%08x device_id=%d block_dim=%d args_count=%d\n",
+               desc.kernel.c_str(), static_cast<int>(desc.kernelClass), path, req.magic, device, req.blockDim,
+               req.numInputs + req.numOutputs + 2);
+  std::fprintf(stderr, "[cuda-launch] inputs=%d outputs=%d workspace_size=%zu tiling_bytes=%zu tiling_words=%zu\n", req.numInputs,
+               req.numOutputs, args.workspaceBytes, req.tilingLen, (req.tilingLen + 7) / 8);
+  for (int i = 0; i < req.numInputs; ++i)
+    std::fprintf(stderr, "[cuda-launch] input[%d] bytes=%zu ptr=%s\n", i, args.argBytes[i], ptr(args.argPtrs[i]).c_str());
+  for (int i = 0; i < req.numOutputs; ++i)
+    std::fprintf(stderr, "[cuda-launch] output[%d] bytes=%zu ptr=%s\n", i, args.argBytes[req.numInputs + i],
+                 ptr(args.argPtrs[req.numInputs + i]).c_str());
+  std::fprintf(stderr, "[cuda-launch] workspace bytes=%zu ptr=%s\n", args.workspaceBytes, ptr(args.workspace).c_str());
+  const size_t words = std::min<size_t>((req.tilingLen + 7) / 8, 32);
+  for (size_t w = 0; w < words; ++w) {
+    uint64_t v = 0;
+    std::memcpy(&v, req.tiling + w * 8, std::min<size_t>(8, req.tilingLen - w * 8));
+    const char *name = w < desc.tiling.size() ? desc.tiling[w].name.c_str() : "";
+    std::fprintf(stderr, "[cuda-launch] tiling.word[%zu]=%llu %s\n", w, static_cast<unsigned long long>(v), name);
+  }
+}
+
 Status CudaExecutor::validate(const RunRequest &req, std::shared_ptr<const LaunchDescriptor> &desc,
                               std::map<std::string, int64_t> &tiling) {
   if (!initialized_) return Status::error("executor has not been initialized");
@@ -142,6 +183,7 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   if (Status s = ownWorkspace(wsBytes); !s) return s.withStage("cuda:memory");
   args.workspace = workspace_.ptr;
   args.workspaceBytes = workspace_.capacity;
+  if (launchTraceEnabled()) printLaunchTrace(req, *desc, args, device_, "host");
 
   // Large runs whose work splits along the leading axis are pipelined: copies in, kernel and copies out
   // of successive row chunks overlap (PCIe is full duplex), instead of three serial phases.
@@ -321,6 +363,7 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
     args.workspace = workspace_.ptr;
     args.workspaceBytes = workspace_.capacity;
   }
+  if (launchTraceEnabled()) printLaunchTrace(req, *desc, args, device_, "device");
   LaunchInfo info;
   if (desc->kernelClass == KernelClass::Gather && args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes) {
     e = cudaMemsetAsync(args.workspace, 0, 8, args.stream);

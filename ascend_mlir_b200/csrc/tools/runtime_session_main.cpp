@@ -3,10 +3,12 @@
 // preparation failure) as the reference's tools/runtime-session/runtime_session_main.cpp:30-110,244-397.
 #include <cstdio>
 #include <cstdlib>
+#include <fstream>
 #include <iostream>
 
 #include "execution/artifact_compiler.h"
 #include "execution/execution_session.h"
+#include "execution/profile_retention.h"
 #include "execution/run_manifest.h"
 #include "tools/cli_args.h"
 
@@ -26,6 +28,13 @@ public:
     ev.taskId = request.task.taskId;
     ev.backend = "cuda";
     ev.artifactPath = request.workingDirectory + "/" + request.task.taskId + ".cuda-profile.json";
+    ev.score = 1.0;
+    {  // a minimal artifact, so that retention has something to keep
+      std::ofstream os(ev.artifactPath, std::ios::trunc);
+      os << "{\"schema_version\": 1, \"backend\": \"cuda\", \"task_id\": \"" << request.task.taskId
+         << "\", \"score\": 1, \"cycle_count\": 1}\n";
+      if (!os) return Status::error("[cuda:profiling] cannot write profile artifact: " + ev.artifactPath);
+    }
     result.profileTrace.sessionId = request.sessionId;
     result.profileTrace.events.push_back(ev);
     return Status::success();
@@ -119,10 +128,35 @@ int main(int argc, char **argv) {
   for (size_t i = 0; i < plan.orderedTaskIds.size(); ++i) std::cout << "session.plan[" << i << "]=" << plan.orderedTaskIds[i] << "\n";
   if (!args.flag("run")) return 0;
 
+  // Session directories and retained profiles live under the temp directory; each root keeps its last 20.
+  constexpr size_t kSessionLimit = 20;
+  const char *tmp = std::getenv("TMPDIR");
+  const std::string tmpRoot = tmp && *tmp ? tmp : "/tmp";
+  const std::string workRoot = tmpRoot + "/afir-cuda-runtime";
+  const std::string retainRoot = tmpRoot + "/afir-cuda-runtime-profiles";
+  if (Status s = prepareRetainedRootForNewSession(workRoot, kSessionLimit); !s) { std::cerr << "Error: " << s.message() << "\n"; return 4; }
+
   SessionRunSummary summary = session.run(graph);
   if (!summary.success) {
     printRunError(session, summary);
     return 2;
+  }
+  std::string retainedSummary;
+  if (!summary.profileTrace.events.empty()) {
+    RetainedProfileArtifacts kept;
+    Status s = prepareRetainedRootForNewSession(retainRoot, kSessionLimit);
+    if (s) s = retainProfileArtifacts(summary.profileTrace, retainRoot, kept);
+    if (!s) {
+      summary.success = false;
+      summary.errorStage = "profiling";
+      summary.errorMessage = s.message();
+      printRunError(session, summary);
+      return 2;
+    }
+    summary.profileTrace = kept.trace;
+    summary.profileArtifactPaths.clear();
+    for (const ProfileEvent &ev : kept.trace.events) summary.profileArtifactPaths.push_back(ev.artifactPath);
+    retainedSummary = kept.summaryPath;
   }
   std::cout << "session.backend=" << session.backendName() << "\n";
   std::cout << "session.result=success\n";
@@ -131,6 +165,7 @@ int main(int argc, char **argv) {
   std::cout << "session.profile.count=" << summary.profileArtifactPaths.size() << "\n";
   for (size_t i = 0; i < summary.profileArtifactPaths.size(); ++i)
     std::cout << "session.profile[" << i << "]=" << summary.profileArtifactPaths[i] << "\n";
+  if (!retainedSummary.empty()) std::cout << "session.profile.summary=" << retainedSummary << "\n";
   for (const auto &ev : summary.profileTrace.events) {
     char buf[64];
     std::snprintf(buf, sizeof(buf), "%.3f", ev.score);

@@ -4,12 +4,16 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <chrono>
+#include <filesystem>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
 #include <iostream>
 
+#include "common/json.h"
 #include "execution/execution_session.h"
+#include "execution/profile_retention.h"
 #include "execution/run_manifest.h"
 #include "support/npy_io.h"
 #include "support/tiling_schema.h"
@@ -242,6 +246,59 @@ static void testManifestAndSession() {
   EXPECT(parseErrorStage("plain").first.empty(), "untagged message");
 }
 
+static void testProfileRetention() {
+  // two artifacts, one with its score on the event, one whose score is read back from the file
+  writeText(path("a.trace.json"), "{\"score\": 12.5, \"cycle_count\": 12.5}");
+  writeText(path("b.trace.json"), "{\"cycle_count\": 4}");
+  ProfileTrace trace;
+  trace.sessionId = "sess-1";
+  trace.attributes["scheduler_mode"] = "serial";
+  trace.counters["planned_task_count"] = 2;
+  trace.events.push_back({"a", "cuda", path("a.trace.json"), 12.5});
+  trace.events.push_back({"b", "cuda", path("b.trace.json"), 0.0});
+  RetainedProfileArtifacts kept;
+  const std::string root = path("retained");
+  EXPECT(retainProfileArtifacts(trace, root, kept).ok(), "retain two artifacts");
+  EXPECT(kept.summaryPath == root + "/sess-1/session_summary.json", "summary path");
+  EXPECT(kept.trace.events[0].artifactPath == root + "/sess-1/tasks/a.json" && kept.trace.events[1].artifactPath == root + "/sess-1/tasks/b.json",
+         "events point at the retained copies");
+  std::ifstream is(kept.summaryPath);
+  std::string text((std::istreambuf_iterator<char>(is)), std::istreambuf_iterator<char>());
+  json::Value summary;
+  std::string err;
+  EXPECT(json::parse(text, summary, err) && summary.isObject(), "summary is json");
+  EXPECT(summary.getInt("task_count", 0) == 2 && summary.getInt("failed_task_count", -1) == 0, "task counts");
+  EXPECT(summary.getDouble("total_score", 0) == 16.5 && summary.getDouble("total_cycle_count", 0) == 16.5, "score falls back to cycle_count");
+  EXPECT(summary.getString("session_id") == "sess-1" && summary.getString("backend") == "cuda", "session id and backend");
+
+  ProfileTrace missing = trace;
+  missing.events[0].artifactPath = path("nope.json");
+  Status s = retainProfileArtifacts(missing, root, kept);
+  EXPECT(!s.ok() && s.message().find("cannot retain profile artifact") == 0, "missing artifact is an error");
+  writeText(path("c.trace.json"), "[1, 2]");
+  ProfileTrace bad = trace;
+  bad.events = {{"c", "cuda", path("c.trace.json"), 0.0}};
+  s = retainProfileArtifacts(bad, root, kept);
+  EXPECT(!s.ok() && s.message().find("must be a json object") != std::string::npos, "non-object artifact is an error");
+
+  // pruning: newest directories stay, plain files are not touched, a missing root is fine
+  const std::string pr = path("prune");
+  for (int i = 0; i < 5; ++i) {
+    const std::string d = pr + "/s" + std::to_string(i);
+    std::filesystem::create_directories(d);
+    std::filesystem::last_write_time(d, std::filesystem::file_time_type::clock::now() - std::chrono::hours(10 - i));
+  }
+  writeText(pr + "/note.txt", "keep me");
+  EXPECT(pruneRetainedProfileDirectories(pr, 2).ok(), "prune");
+  EXPECT(std::filesystem::exists(pr + "/s4") && std::filesystem::exists(pr + "/s3") && !std::filesystem::exists(pr + "/s2") &&
+             !std::filesystem::exists(pr + "/s0") && std::filesystem::exists(pr + "/note.txt"),
+         "the two newest directories and the file remain");
+  EXPECT(pruneRetainedProfileDirectories(path("no-such-root"), 1).ok(), "missing root is not an error");
+  EXPECT(pruneKeepCountForNewSession(20) == 19 && pruneKeepCountForNewSession(0) == 0, "room for the new session");
+  EXPECT(prepareRetainedRootForNewSession(pr, 2).ok() && !std::filesystem::exists(pr + "/s3") && std::filesystem::exists(pr + "/s4"),
+         "preparing for a new session leaves limit - 1 directories");
+}
+
 int main() {
   char tmpl[] = "/tmp/afir-runtime-test-XXXXXX";
   if (!::mkdtemp(tmpl)) return 99;
@@ -251,6 +308,7 @@ int main() {
   testComparator();
   testTaskGraph();
   testManifestAndSession();
+  testProfileRetention();
   std::cout << g_pass << " passed, " << g_fail << " failed\n";
   return g_fail;
 }

@@ -2,6 +2,7 @@
 comparator, task graph, run manifest and session (driver injected), and the runtime-session CLI contract
 (exit codes 0/2/4 and key=value lines of the reference's tools/runtime-session)."""
 import json
+import os
 import subprocess
 from pathlib import Path
 
@@ -102,6 +103,40 @@ def test_runtime_session_run_with_testing_driver(tmp_path):
     assert any(l.startswith("session.runtime.counter.planned_task_count=2") for l in out)
     r = run_tool("--run-manifest", m, "--run", "--testing-driver", "bogus")
     assert r.returncode == 4 and "unsupported testing driver: bogus" in r.stderr
+
+
+def test_runtime_session_retains_profiles_and_prunes_old_sessions(tmp_path):
+    """Profile artifacts are copied to <tmp>/afir-cuda-runtime-profiles/<session>/tasks/<task>.json with a
+    session_summary.json beside them; both that root and the session work root keep their last 20 sessions."""
+    m = _manifest(tmp_path, [{"task_id": "only", "outputs": [{"name": "y", "shape": [2], "dtype": "f32"}]}])
+    env = {**os.environ, "TMPDIR": str(tmp_path / "tmp")}
+    (tmp_path / "tmp").mkdir()
+
+    def run_once():
+        r = subprocess.run([str(BIN / "runtime-session"), "--run-manifest", str(m), "--run", "--testing-driver", "success"],
+                           capture_output=True, text=True, env=env)
+        assert r.returncode == 0, r.stderr
+        return dict(l.split("=", 1) for l in r.stdout.splitlines() if "=" in l)
+
+    lines = run_once()
+    summary_path = Path(lines["session.profile.summary"])
+    session = lines["session.profile.session_id"]
+    assert summary_path == tmp_path / "tmp" / "afir-cuda-runtime-profiles" / session / "session_summary.json"
+    kept = Path(lines["session.profile[0]"])
+    assert kept == summary_path.parent / "tasks" / "only.json" and json.loads(kept.read_text())["task_id"] == "only"
+    summary = json.loads(summary_path.read_text())
+    assert summary["schema_version"] == 1 and summary["session_id"] == session and summary["backend"] == "cuda"
+    assert summary["task_count"] == summary["successful_task_count"] == 1 and summary["failed_task_count"] == 0
+    assert summary["tasks"] == [{"task_id": "only", "profile_path": str(kept), "score": 1.0, "cycle_count": 1.0}]
+    assert summary["total_score"] == 1.0 and summary["runtime"]["counters"]["planned_task_count"] == 1
+    assert summary["runtime"]["attributes"]["scheduler_mode"] == "serial"
+
+    for _ in range(23):
+        run_once()
+    for root in ("afir-cuda-runtime-profiles", "afir-cuda-runtime"):
+        sessions = [p for p in (tmp_path / "tmp" / root).iterdir() if p.is_dir()]
+        assert len(sessions) == 20, root
+    assert not summary_path.exists(), "the first session is the oldest and has been pruned"
 
 
 def test_runtime_session_reports_binding_stage_on_missing_input(tmp_path):

@@ -79,6 +79,22 @@ def test_two_task_graph_validates_and_profiles(tmp_path):
     assert np.array_equal(np.load(tmp_path / "chain_out.npy"), prod)
     assert np.allclose(np.load(tmp_path / "sums_out.npy"), sums, rtol=1e-4, atol=1e-2)
 
+    # the retained copy of the profile and the session summary
+    lines = dict(l.split("=", 1) for l in out if "=" in l)
+    summary = json.loads(Path(lines["session.profile.summary"]).read_text())
+    assert summary["tasks"][0]["task_id"] == "chain" and summary["tasks"][0]["score"] == trace["score"]
+    assert Path(summary["tasks"][0]["profile_path"]) == Path(trace_path) and "/tasks/chain.json" in trace_path
+
+    # launch tracing: arguments, alignment and named tiling words on stderr
+    r = subprocess.run([str(BIN / "runtime-session"), "--run-manifest", str(m), "--run"], capture_output=True, text=True,
+                       env={**os.environ, "ASCEND_RUNTIME_TRACE_LAUNCH": "1"})
+    assert r.returncode == 0, r.stderr
+    traced = r.stderr.splitlines()
+    assert any(l.startswith("[cuda-launch] kernel=add_mul ") and "path=host" in l for l in traced)
+    assert any(l.startswith("[cuda-launch] input[1] bytes=%d ptr=0x" % (M * N * 4)) and "align512=yes" in l for l in traced)
+    assert f"[cuda-launch] tiling.word[2]={M} dim_arg0_0" in traced and f"[cuda-launch] tiling.word[3]={N} dim_arg0_1" in traced
+    assert any(l.startswith("[cuda-launch] kernel=broadcast_add_reducesum ") for l in traced)
+
     # a wrong expectation fails in the validate stage with exit code 2
     np.save(tmp_path / "prod.npy", prod + 1.0)
     r = tool("runtime-session", "--run-manifest", m, "--run")
