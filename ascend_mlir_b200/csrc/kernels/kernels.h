@@ -81,6 +81,7 @@ struct ElementwiseLaunch {
   int ctaThreads;  // 0 = library default
   int unroll;      // vectors in flight per thread: 1, 2, 4 or 8; 0 = default
   int gridBlocks;  // 0 = library default
+  int forceElementAccess = 0;  // 1: never use the block variant for transposed operands (testing, tuning)
 };
 // Returns a cudaError_t value (0 = success); *launched gets the number of kernels launched.
 int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *launched);

@@ -168,6 +168,33 @@ def relu_bcast_transpose_add(dtype: str = "f16", name: str = "relu_transpose_bro
     return _spec(name, "elementwise", dtype, 2, 1, _EW_TILE, dims, body, _EW_LAUNCH)
 
 
+def transposed_add_mul(dtype: str = "f16", name: str = "transposed_add_mul") -> KernelSpec:
+    """out[n, m] = (a[m, n] + b[n, m]) * c[n]: `a` is read through a transposed view, `c` is constant along the
+    inner dim.  Arguments: a [M, N], b [N, M], c [N] -> out [N, M]."""
+    dims = [("dim_arg0_0", "M"), ("dim_arg0_1", "N")]
+    dom = ["dim_arg0_1", "dim_arg0_0"]
+    body = {"domain": dom,
+            "loads": [{"arg": 0, "shape": ["dim_arg0_0", "dim_arg0_1"], "map": [1, 0]},
+                      {"arg": 1, "shape": dom, "map": [0, 1]},
+                      {"arg": 2, "shape": ["dim_arg0_1"], "map": [0]}],
+            "store": {"arg": 3, "shape": dom, "map": [0, 1]},
+            "body": [op("addf", "v0", "v1"), op("mulf", "%0", "v2")]}
+    return _spec(name, "elementwise", dtype, 3, 1, _EW_TILE, dims, body, _EW_LAUNCH)
+
+
+def batched_transposed_relu_sub(dtype: str = "f32", name: str = "batched_transposed_relu_sub") -> KernelSpec:
+    """out[b, n, m] = max(a[b, m, n], 0) - bias[m]: a batch of transposed reads with a row-vector operand.
+    Arguments: a [B, M, N], bias [M] -> out [B, N, M]."""
+    dims = [("dim_arg0_0", "B"), ("dim_arg0_1", "M"), ("dim_arg0_2", "N")]
+    dom = ["dim_arg0_0", "dim_arg0_2", "dim_arg0_1"]
+    body = {"domain": dom,
+            "loads": [{"arg": 0, "shape": ["dim_arg0_0", "dim_arg0_1", "dim_arg0_2"], "map": [0, 2, 1]},
+                      {"arg": 1, "shape": ["dim_arg0_1"], "map": [2]}],
+            "store": {"arg": 2, "shape": dom, "map": [0, 1, 2]},
+            "body": [op("maximumf", "v0", 0.0), op("subf", "%0", "v1")]}
+    return _spec(name, "elementwise", dtype, 2, 1, _EW_TILE, dims, body, _EW_LAUNCH)
+
+
 def transpose_2d(dtype: str = "f16", name: str = "transpose_2d") -> KernelSpec:
     """out[c, r] = in[r, c]."""
     dims = [("dim_arg0_0", "R"), ("dim_arg0_1", "C")]

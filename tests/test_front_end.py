@@ -68,6 +68,13 @@ def test_config_groups_translate_to_the_expected_descriptor(name, builder):
         assert got["domain"] == [32, 1024, 1024] and got["loads"][0]["shape"] == [32, 1024, 2048]
 
 
+def test_transposed_operand_stays_one_elementwise_group_with_a_permuted_view():
+    got = translate(EXAMPLES / "transposed_add.mlir")
+    assert got["kernel_class"] == "elementwise" and body_of(got) == [("addf", "v0", "v1")]
+    assert views_of(got) == [(0, [1, 0], None), (1, [0, 1], None)]
+    assert got["domain"] == ["dim_arg1_0", "dim_arg1_1"] and got["store"]["map"] == [0, 1]
+
+
 def test_matmul_group_epilogue_and_tiling_space(tmp_path):
     out, space = tmp_path / "k.cuda.json", tmp_path / "ts.json"
     assert translate(EXAMPLES / "matmul_add_leakyrelu.mlir", "-o", out, "--tiling-space-out", space) is None

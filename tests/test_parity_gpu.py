@@ -157,6 +157,32 @@ def test_transpose_2d_round_trip_at_full_size(rt):
     assert twice.tobytes() == x.tobytes()
 
 
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("M,N", [(512, 256), (520, 264), (8, 8), (1000, 24), (24, 1000), (3, 5), (257, 129)])
+def test_elementwise_with_a_transposed_operand(rt, dtype, M, N):
+    """out[n, m] = (a[m, n] + b[n, m]) * c[n], rounding after every op: whole blocks, ragged blocks, shapes whose
+    strides are not multiples of 16 bytes (those take the element-wise kernel), all against numpy."""
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((M, N)).astype(dtype)
+    b = rng.standard_normal((N, M)).astype(dtype)
+    c = rng.standard_normal(N).astype(dtype)
+    want = ((a.T + b).astype(dtype) * c[:, None]).astype(dtype)
+    spec = descriptors.transposed_add_mul("f16" if dtype == np.float16 else "f32")
+    out = run(rt, spec, [a, b, c], np.zeros((N, M), dtype), {"M": M, "N": N})
+    assert out.tobytes() == want.tobytes()
+
+
+@pytest.mark.parametrize("B,M,N", [(3, 128, 64), (2, 100, 36), (1, 4, 4), (5, 33, 7)])
+def test_batched_transposed_operand_with_interpreted_body(rt, B, M, N):
+    rng = np.random.default_rng(22)
+    a = rng.standard_normal((B, M, N)).astype(np.float32)
+    bias = rng.standard_normal(M).astype(np.float32)
+    want = (np.maximum(a, np.float32(0)).transpose(0, 2, 1) - bias[None, None, :]).astype(np.float32)
+    spec = descriptors.batched_transposed_relu_sub("f32")
+    out = run(rt, spec, [a, bias], np.zeros((B, N, M), np.float32), {"B": B, "M": M, "N": N})
+    assert out.tobytes() == np.ascontiguousarray(want).tobytes()
+
+
 def test_interpreted_body_matches_oracle_chain(rt):
     # a chain with no straight-line specialisation: ((a - b) / b) min a
     spec = descriptors.add_mul()

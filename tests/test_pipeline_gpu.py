@@ -96,6 +96,16 @@ def test_transpose_group_from_linalg(rt, tmp_path):
     assert out.tobytes() == oracle.transpose_2d(x).tobytes()
 
 
+def test_transposed_operand_group_from_linalg(rt, tmp_path):
+    binary, space = compile_from_mlir("transposed_add", tmp_path)
+    rng = np.random.default_rng(67)
+    a = rng.standard_normal((520, 264)).astype(np.float16)
+    b = rng.standard_normal((264, 520)).astype(np.float16)
+    out = np.zeros((264, 520), np.float16)
+    rt.run(binary, "transposed_add", [a, b], [out], pack(space, [a, b, out]))
+    assert out.tobytes() == (a.T + b).astype(np.float16).tobytes()
+
+
 def test_matmul_group_from_linalg(rt, tmp_path):
     binary, space = compile_from_mlir("matmul_add_leakyrelu", tmp_path)
     w = configs.matmul_add_leakyrelu(512, 768, 320, seed=65)
