@@ -210,20 +210,50 @@ class DeviceGroup:
         self.rt.run_raw(self.w.spec.binary, self.w.spec.name, self.host_in_args, self.host_out_args, self.tiling, 0,
                         self.w.spec.magic)
 
-    def timed(self, steps, warmup, sync):
+    def timed(self, steps, warmup, sync, use_graph=True):
+        """Milliseconds per step, kernels launched, and how they were launched.  The K launches of the timed
+        region are captured once into a CUDA graph and replayed with a single graph launch, so the figure is
+        device time of K back-to-back kernels whatever K is; if capture is refused the launches are issued
+        one by one through the C-ABI as in the warm-up."""
         torch = self.torch
         for _ in range(warmup):
             self.launch()
         sync()
+        graph, mode = None, "direct"
+        if use_graph:
+            try:
+                before = self.rt.total_launch_count
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.stream, capture_error_mode="thread_local"):
+                    for _ in range(steps):
+                        self.rt.launch_device(self.w.spec.binary, self.w.spec.name, self.in_args, self.out_args, self.tiling, 0,
+                                              self.w.spec.magic, (self.ws.data_ptr(), self.ws.numel()),
+                                              torch.cuda.current_stream().cuda_stream)
+                launches = self.rt.total_launch_count - before
+                with torch.cuda.stream(self.stream):
+                    g.replay()  # one untimed replay: graph upload and first-use costs stay out of the timing
+                sync()
+                graph, mode = g, "cuda_graph"
+            except Exception as e:  # capture refused: fall back to direct launches, and say so
+                graph, mode = None, f"direct (graph capture failed: {type(e).__name__})"
+                sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        before = self.rt.total_launch_count
-        e0.record(self.stream)
-        for _ in range(steps):
-            self.launch()
-        e1.record(self.stream)
+        if graph is not None:
+            with torch.cuda.stream(self.stream):
+                e0.record(self.stream)
+                graph.replay()
+                e1.record(self.stream)
+        else:
+            before = self.rt.total_launch_count
+            e0.record(self.stream)
+            for _ in range(steps):
+                self.launch()
+            e1.record(self.stream)
+            launches = self.rt.total_launch_count - before
         sync()
         self.rt.synchronize(self.stream.cuda_stream)
-        return e0.elapsed_time(e1) / steps, self.rt.total_launch_count - before
+        self.launch_mode = mode
+        return e0.elapsed_time(e1) / steps, launches
 
     def timed_e2e(self, steps, warmup, sync):
         for _ in range(warmup):
@@ -279,11 +309,12 @@ def run_gpu_arm(args):
             w = everything[name](seed=rank)
             g = DeviceGroup(torch, rt, w, device, stream)
             steps = args.steps if name == args.workload else max(20, min(args.steps, 200))
-            ms, launches = g.timed(steps, args.warmup, sync)
+            ms, launches = g.timed(steps, args.warmup, sync, use_graph=not args.no_graph)
             ms = max_over_ranks(ms)
             work, unit, scale = work_of(w)
             value = world * work / (ms * 1e-3) / scale
             rec = {"value": value, "unit": unit, "ms_per_step": ms, "launches_per_step": launches / steps,
+                   "launch_mode": g.launch_mode,
                    "algorithmic_work_per_step": work}
             if name == args.workload:
                 e2e_steps = max(3, min(steps, 20))
@@ -318,6 +349,7 @@ def run_gpu_arm(args):
                 "config": {"workload": args.workload, "shape": w.shape, "per_gpu_batches": 1,
                            "sharding": "leading axis row-sharded, one full-size batch per GPU, no collective",
                            "l2": "working set per step exceeds the 126 MB L2; no flush between steps",
+                           "launch_mode": rec["launch_mode"],
                            "notes": w.notes},
                 "roofline": rec["roofline"], "e2e": rec["e2e"], "gpu_launches": rec["gpu_launches"], "clocks": clocks,
                 "groups": {k: v for k, v in results.items() if k != args.workload}}
@@ -339,6 +371,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--one-group", dest="all_groups", action="store_false", help="time only --workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="issue the timed launches one by one instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
