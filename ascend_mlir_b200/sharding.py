@@ -51,3 +51,27 @@ def job_throughput(work_this_rank: float, ms_this_rank: float, device=None) -> T
     ms = max_over_ranks(ms_this_rank, device)
     total = sum_over_ranks(work_this_rank, device)
     return total / (ms * 1e-3), ms
+
+
+# ---- the one exchange step of the path: a reduction whose axis is sharded ---------------------------------------
+def col_range(total: int, rank: int, world_size: int, quantum: int = 1) -> Tuple[int, int]:
+    """Contiguous, balanced partition of `total` columns in units of `quantum` (e.g. 4 for 16-byte f32 vectors)."""
+    units = (total + quantum - 1) // quantum
+    lo, hi = row_range(units, rank, world_size)
+    return min(total, lo * quantum), min(total, hi * quantum)
+
+
+def allreduce_partial_rowsums(partial):
+    """Sums per-rank partial row sums in place across the default process group and returns the tensor.
+
+    Row sharding (the default for every group) needs no collective.  When the *reduced* axis is sharded instead
+    (each rank holds a column slice of x), every rank reduces its slice with the row-reduction kernel in f32 and the
+    partial sums are added here: one all-reduce of rows x 4 bytes (32 KiB for 8192 rows), NCCL over NVLink on GPUs,
+    gloo on CPU.  The broadcast operand b[m] must be added on one rank only (or scaled by the slice widths), which
+    is why the helper takes finished partial sums and not the operands."""
+    rank, size = world()
+    if size == 1:
+        return partial
+    import torch.distributed as dist
+    dist.all_reduce(partial, op=dist.ReduceOp.SUM)
+    return partial

@@ -102,3 +102,52 @@ def test_two_gloo_ranks_shard_without_a_data_collective():
     for _, _, rate, ms, _ in got:
         assert ms == 2.0  # max over ranks of (1.0, 2.0)
         assert rate == pytest.approx(total_bytes / 2e-3)
+
+
+# ---- the reduced axis sharded: partial row sums + one all-reduce ---------------------------------------------------
+def _column_rank_main(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ascend_mlir_b200 import sharding
+        full = configs.broadcast_add_reduce(M=37, N=100, seed=5)
+        b, x = full.inputs
+        lo, hi = sharding.col_range(x.shape[1], rank, world, quantum=4)
+        # the row-broadcast operand counts once per column of the slice, exactly as in the unsharded sum
+        partial = oracle.bcast_add_rowsum_f32(b, np.ascontiguousarray(x[:, lo:hi]))
+        total = sharding.allreduce_partial_rowsums(torch.from_numpy(partial.copy()))
+        q.put((rank, (lo, hi), total.numpy()))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_col_range_partitions_in_vector_units():
+    from ascend_mlir_b200 import sharding
+    for total, world, quantum in [(100, 2, 4), (8192, 8, 4), (10, 4, 4), (7, 3, 1)]:
+        pieces = [sharding.col_range(total, r, world, quantum) for r in range(world)]
+        assert pieces[0][0] == 0 and pieces[-1][1] == total
+        assert all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
+        assert all(lo % quantum == 0 or lo == total for lo, _ in pieces)
+
+
+def test_two_gloo_ranks_column_sharded_reduction_needs_one_allreduce():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_column_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted((q.get(timeout=120) for _ in procs), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got[0][1] == (0, 52) and got[1][1] == (52, 100)
+    full = configs.broadcast_add_reduce(M=37, N=100, seed=5)
+    _, s64, abs64 = oracle.bcast_add_rowsum_f32(full.inputs[0], full.inputs[1], with_bounds=True)
+    for _, _, total in got:
+        assert np.array_equal(total, got[0][2]), "every rank ends with the same sums"
+        assert np.all(np.abs(total - s64) <= 1e-5 * abs64)
