@@ -70,6 +70,36 @@ Status CudaExecutor::slotFor(size_t index, size_t bytes, void **out) {
   return Status::success();
 }
 
+static size_t guardBytesFromEnv() {
+  const char *v = std::getenv("AFIR_CUDA_CANARY");
+  if (!v || !*v || std::string(v) == "0") return 0;
+  return 4096;  // a multiple of 512, so buffers keep the alignment cudaMalloc gave them
+}
+static constexpr unsigned char kGuardPattern = 0xA5;
+
+Status CudaExecutor::verifyGuards() {
+  if (guardChecks_.empty()) return Status::success();
+  std::vector<unsigned char> host(2 * guardBytes_);
+  Status result = Status::success();
+  for (const GuardCheck &g : guardChecks_) {
+    cudaError_t e = cudaMemcpy(host.data(), g.before, guardBytes_, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(host.data() + guardBytes_, g.after, guardBytes_, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { result = cudaFail(e, "[cuda:memory] guard band read failed"); break; }
+    for (size_t i = 0; i < host.size(); ++i) {
+      if (host[i] == kGuardPattern) continue;
+      const bool before = i < guardBytes_;
+      const long long off = before ? static_cast<long long>(i) - static_cast<long long>(guardBytes_) : static_cast<long long>(i - guardBytes_);
+      result = Status::error("[cuda:kernel_launch] output " + std::to_string(g.output) + ": the kernel wrote " +
+                             (before ? "before the start" : "past the end") + " of the buffer (first bad byte at offset " +
+                             std::to_string(off) + (before ? " from the start)" : " from the end)"));
+      break;
+    }
+    if (!result) break;
+  }
+  guardChecks_.clear();
+  return result;
+}
+
 Status CudaExecutor::ownWorkspace(size_t bytes) {
   if (workspace_.capacity >= bytes) return Status::success();
   if (workspace_.ptr) cudaFree(workspace_.ptr);
@@ -169,14 +199,30 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   const size_t numArgs = static_cast<size_t>(req.numInputs + req.numOutputs);
   args.argPtrs.resize(numArgs);
   args.argBytes.resize(numArgs);
+  guardBytes_ = guardBytesFromEnv();
+  guardChecks_.clear();
+  const size_t guard = guardBytes_;
   for (int i = 0; i < req.numInputs; ++i) {
     args.argBytes[i] = req.inputBytes[i];
-    if (Status s = slotFor(i, req.inputBytes[i], &args.argPtrs[i]); !s) return s.withStage("cuda:memory");
+    void *base = nullptr;
+    if (Status s = slotFor(i, req.inputBytes[i] + 2 * guard, &base); !s) return s.withStage("cuda:memory");
+    args.argPtrs[i] = static_cast<char *>(base) + guard;
   }
   for (int i = 0; i < req.numOutputs; ++i) {
     const size_t k = static_cast<size_t>(req.numInputs + i);
     args.argBytes[k] = req.outputBytes[i];
-    if (Status s = slotFor(k, req.outputBytes[i], &args.argPtrs[k]); !s) return s.withStage("cuda:memory");
+    void *base = nullptr;
+    if (Status s = slotFor(k, req.outputBytes[i] + 2 * guard, &base); !s) return s.withStage("cuda:memory");
+    args.argPtrs[k] = static_cast<char *>(base) + guard;
+    if (guard) {
+      unsigned char *b = static_cast<unsigned char *>(base);
+      unsigned char *after = b + guard + req.outputBytes[i];
+      // bands are written on the compute stream, ahead of every kernel of this run
+      cudaError_t ge = cudaMemsetAsync(b, kGuardPattern, guard, stream);
+      if (ge == cudaSuccess) ge = cudaMemsetAsync(after, kGuardPattern, guard, stream);
+      if (ge != cudaSuccess) return cudaFail(ge, "[cuda:memory] guard band fill failed");
+      guardChecks_.push_back({i, b, after});
+    }
   }
   size_t wsBytes = 0;
   if (Status s = requiredWorkspaceBytes(*desc, tiling, device_, wsBytes); !s) return s.withStage("cuda:bindings");
@@ -235,7 +281,9 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   statusWorkspace_ = workspace_.ptr;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
   reducePending_ = desc->kernelClass == KernelClass::RowReduce;
-  return synchronize(stream_);
+  Status done = synchronize(stream_);
+  Status guards = verifyGuards();
+  return done ? guards : done;
 }
 
 Status CudaExecutor::ensureCopyStreams(size_t events) {
@@ -331,7 +379,9 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
   statusWorkspace_ = workspace_.ptr;
   matmulPending_ = desc.kernelClass == KernelClass::Matmul;
   reducePending_ = desc.kernelClass == KernelClass::RowReduce;
-  return synchronize(stream_);
+  Status done = synchronize(stream_);
+  Status guards = verifyGuards();
+  return done ? guards : done;
 }
 
 Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream) {

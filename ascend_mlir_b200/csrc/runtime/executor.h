@@ -85,6 +85,13 @@ private:
   uint64_t totalLaunchCount_ = 0;
   bool statusPending_ = false;
   void *statusWorkspace_ = nullptr;
+  // Debug guard bands (AFIR_CUDA_CANARY=1): every host-path buffer gets `guard` bytes of a known pattern before and
+  // after it; the bands of the outputs are checked after the run, so a kernel that writes outside its output
+  // shows up as an error instead of silent corruption of a neighbouring allocation.
+  struct GuardCheck { int output; const unsigned char *before; const unsigned char *after; };
+  std::vector<GuardCheck> guardChecks_;
+  size_t guardBytes_ = 0;
+  Status verifyGuards();
   bool matmulPending_ = false;
   bool reducePending_ = false;
 };

@@ -424,3 +424,55 @@ def test_matmul_linearity_at_scale(rt):
     for m, n in rng.integers(0, M, (64, 2)):
         want = oracle.matmul_bias_leakyrelu_bf16_at(A, B, w_bias, 0.01, int(m), int(n))
         assert abs(o3[m, n] - want) <= 1e-2 * abs(want) + 1e-3
+
+
+# ---- guard bands -------------------------------------------------------------------------------------------------
+def test_no_kernel_writes_outside_its_output_at_ragged_shapes(rt, monkeypatch):
+    """With AFIR_CUDA_CANARY=1 every host-path buffer sits between two 4 KB bands of a known pattern and the bands of
+    the outputs are checked after the run: one ragged shape per kernel class (and per variant that has its own
+    store code) must leave them intact and still give the oracle's result."""
+    monkeypatch.setenv("AFIR_CUDA_CANARY", "1")
+    rng = np.random.default_rng(31)
+
+    w = configs.elementwise_chain(257, 1023, seed=31)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    assert np.array_equal(out, oracle.add_mul_f32(*w.inputs))
+
+    w = configs.split_relu_broadcast_add_mul(3, 37, 72, seed=31)
+    out = run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    assert np.array_equal(bits(out), bits(oracle.split_relu_bias_mul_f16(w.inputs[0], w.inputs[1], 1)))
+
+    w = configs.broadcast_add_reduce(1501, 4100, seed=31)
+    for tile in ({}, {"BULK_COPY": 0}, {"BULK_COPY": 0, "SPLIT_N": 4}):
+        out = run(rt, w.spec, w.inputs, w.new_output(), w.shape, **tile)
+        _, s64, abs64 = oracle.bcast_add_rowsum_f32(w.inputs[0], w.inputs[1], with_bounds=True)
+        assert np.all(np.abs(out - s64) <= 1e-5 * abs64), tile
+
+    monkeypatch.setenv("AFIR_CUDA_NO_PIPELINE", "1")
+    w = configs.gather_elementwise(5000, 256, 40003, seed=31)
+    for tile in ({}, {"BULK_COPY": 1}):
+        out = run(rt, w.spec, w.inputs, w.new_output(), w.shape, **tile)
+        assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(*w.inputs)), tile
+    monkeypatch.delenv("AFIR_CUDA_NO_PIPELINE")
+
+    x = rng.standard_normal((1001, 523)).astype(np.float16)
+    spec = descriptors.transpose_2d("f16")
+    for tile in ({}, {"TILE_KERNEL": 1}, {"VARIANT": 3}):
+        out = run(rt, spec, [x], np.zeros((523, 1001), np.float16), {"R": 1001, "C": 523}, **tile)
+        assert out.tobytes() == oracle.transpose_2d(x).tobytes(), tile
+    x = rng.standard_normal((1000, 520)).astype(np.float16)
+    out = run(rt, spec, [x], np.zeros((520, 1000), np.float16), {"R": 1000, "C": 520})
+    assert out.tobytes() == oracle.transpose_2d(x).tobytes()
+
+    a = rng.standard_normal((1000, 264)).astype(np.float16)
+    b = rng.standard_normal((264, 1000)).astype(np.float16)
+    c = rng.standard_normal(264).astype(np.float16)
+    out = run(rt, descriptors.transposed_add_mul("f16"), [a, b, c], np.zeros((264, 1000), np.float16), {"M": 1000, "N": 264})
+    assert out.tobytes() == ((a.T + b).astype(np.float16) * c[:, None]).astype(np.float16).tobytes()
+
+    for mb in (1, 2, 3):
+        w = configs.matmul_add_leakyrelu(300, 264, 136, seed=31)
+        out = run(rt, w.spec, w.inputs, w.new_output(), w.shape, STAGES=mb)
+        got = oracle.bf16_to_f32(out)
+        want = oracle.bf16_to_f32(oracle.matmul_bias_leakyrelu_bf16(*w.inputs, 0.01))
+        assert np.all(np.abs(got - want) <= 1e-2 * np.abs(want) + 1e-3), mb
