@@ -35,6 +35,47 @@ def test_cpp_checks(tmp_path, source):
     assert " passed, 0 failed" in res.stdout
 
 
+def test_cpp_checks_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """The host runtime (json, npy, tiling, comparator, task graph, manifest, session, scheduler, retention, front end)
+    rebuilt with -fsanitize=address,undefined and run through both C++ check programs: no report, all checks pass.
+    Device code cannot be sanitized here; the CUDA objects are linked in as they are and never called."""
+    csrc = ROOT / "ascend_mlir_b200" / "csrc"
+    host = [csrc / f for f in ("common/json.cpp", "execution/artifact_compiler.cpp", "execution/execution_session.cpp",
+                               "execution/global_scheduler.cpp", "execution/output_comparator.cpp",
+                               "execution/profile_retention.cpp", "execution/resource_scheduler.cpp",
+                               "execution/run_manifest.cpp", "execution/task_graph.cpp", "front/group_analysis.cpp",
+                               "front/mlir_text.cpp", "runtime/descriptor.cpp", "support/npy_io.cpp",
+                               "support/tiling_schema.cpp")]
+    objs = [str(o) for o in sorted((ROOT / "ascend_mlir_b200" / "build").glob("*.o"))
+            if o.name.startswith("kernels_") or o.name in ("runtime_executor.cpp.o", "runtime_launcher.cpp.o")]
+    env = {**os.environ, "ASAN_OPTIONS": "detect_leaks=1:abort_on_error=0", "UBSAN_OPTIONS": "print_stacktrace=1"}
+    flags = ["-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-I", str(csrc),
+             "-I", str(ROOT / "include"), "-I", "/usr/local/cuda/include"]
+    sources = host + [ROOT / "tests" / "cpp" / "test_runtime_support.cpp", ROOT / "tests" / "cpp" / "test_scheduler.cpp"]
+
+    def compile_one(src):
+        obj = tmp_path / (src.stem + ".san.o")
+        return obj, subprocess.run(["g++", *flags, "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        compiled = list(pool.map(compile_one, sources))
+    for obj, res in compiled:
+        assert res.returncode == 0, res.stderr[-3000:]
+    host_objs = [str(obj) for obj, _ in compiled[:len(host)]]
+    for (obj, _), source in zip(compiled[len(host):], ("test_runtime_support", "test_scheduler")):
+        exe = tmp_path / f"{source}.san"
+        linked = subprocess.run(["g++", "-fsanitize=address,undefined", str(obj), *host_objs, *objs, "-L", "/usr/local/cuda/lib64",
+                                 "-lcudart_static", "-ldl", "-lrt", "-lpthread", "-o", str(exe)], capture_output=True, text=True)
+        if linked.returncode != 0 and "cannot find" in linked.stderr and "san" in linked.stderr:
+            pytest.skip("sanitizer runtime libraries are not installed")
+        assert linked.returncode == 0, linked.stderr[-3000:]
+        res = subprocess.run([str(exe)], capture_output=True, text=True, env=env)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+        assert " passed, 0 failed" in res.stdout
+        assert "runtime error" not in res.stderr and "AddressSanitizer" not in res.stderr and "LeakSanitizer" not in res.stderr
+
+
 def run_tool(*args):
     return subprocess.run([str(BIN / "runtime-session"), *map(str, args)], capture_output=True, text=True)
 
