@@ -188,3 +188,37 @@ def test_reference_example_inputs_translate(example, cls):
         assert d["gather"]["axis"] == 1 and body_of(d) == [("maximumf", "v0", 0.0), ("addf", "%0", "v1")]
     if example in ("add-broadcast-concat", "split-relu-brc-add-mul"):
         assert len(d["groups"]) == 2 and d["groups"][1]["store"]["offset"][0] != 0
+
+
+def test_mutated_inputs_are_rejected_or_accepted_but_never_crash_the_tools():
+    """Seeded text mutations (deleted spans, duplicated spans, swapped characters, stray brackets) of the example
+    modules: afir-opt and afir-translate must answer with exit code 0 or 1 and, on 1, an 'error:' line."""
+    import random
+    rng = random.Random(20240607)
+    sources = [(EXAMPLES / n).read_text() for n in ("broadcast_add_reduce.mlir", "matmul_add_leakyrelu.mlir",
+                                                     "gather_elementwise.mlir", "split_relu_broadcast_add_mul.mlir")]
+    crashes = []
+    for trial in range(160):
+        text = sources[trial % len(sources)]
+        for _ in range(rng.randint(1, 3)):
+            i = rng.randrange(len(text))
+            kind = rng.randrange(4)
+            if kind == 0:
+                text = text[:i] + text[i + rng.randint(1, 12):]
+            elif kind == 1:
+                j = min(len(text), i + rng.randint(1, 20))
+                text = text[:j] + text[i:j] + text[j:]
+            elif kind == 2 and i + 1 < len(text):
+                text = text[:i] + text[i + 1] + text[i] + text[i + 2:]
+            else:
+                text = text[:i] + rng.choice("{}()<>[]%#:,") + text[i:]
+        r = subprocess.run([str(BIN / "afir-opt"), "--mark-structured-ops", "--convert-afir-to-cuda", "-"], input=text,
+                           capture_output=True, text=True)
+        if r.returncode not in (0, 1) or (r.returncode == 1 and "error" not in r.stderr.lower()):
+            crashes.append((trial, r.returncode, r.stderr[-200:]))
+            continue
+        if r.returncode == 0:
+            t = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-"], input=r.stdout, capture_output=True, text=True)
+            if t.returncode not in (0, 1) or (t.returncode == 1 and "error" not in t.stderr.lower()):
+                crashes.append((trial, "translate", t.returncode, t.stderr[-200:]))
+    assert not crashes, crashes[:5]
