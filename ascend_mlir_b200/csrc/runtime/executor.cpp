@@ -70,6 +70,13 @@ Status CudaExecutor::slotFor(size_t index, size_t bytes, void **out) {
   return Status::success();
 }
 
+// Launch-time failures are kernel_launch errors unless the launcher already named a more precise stage
+// (a tensor whose byte count contradicts the tiling dims is a bindings error).
+static Status launchStage(const Status &s) {
+  if (s.ok() || (!s.message().empty() && s.message()[0] == '[')) return s;
+  return s.withStage("cuda:kernel_launch");
+}
+
 static size_t guardBytesFromEnv() {
   const char *v = std::getenv("AFIR_CUDA_CANARY");
   if (!v || !*v || std::string(v) == "0") return 0;
@@ -270,7 +277,7 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
   if (!ls) {
     cudaStreamSynchronize(stream);
-    return ls.withStage("cuda:kernel_launch");
+    return launchStage(ls);
   }
   for (int i = 0; i < req.numOutputs; ++i) {
     if (!req.outputBytes[i]) continue;
@@ -350,7 +357,7 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
       cudaStreamSynchronize(in);
       cudaStreamSynchronize(compute);
       cudaStreamSynchronize(out);
-      return ls.withStage("cuda:kernel_launch");
+      return launchStage(ls);
     }
     cudaEventRecord(event(2 * c + 1), compute);
     cudaStreamWaitEvent(out, event(2 * c + 1), 0);
@@ -422,7 +429,7 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   Status ls = launchDescriptor(*desc, tiling, args, info);
   lastLaunchCount_ = info.kernelsLaunched;
   totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
-  if (!ls) return ls.withStage("cuda:kernel_launch");
+  if (!ls) return launchStage(ls);
   statusPending_ = info.usesStatusBlock;
   statusWorkspace_ = args.workspace;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;

@@ -59,7 +59,7 @@ Status resolveView(const ViewSpec &v, const std::vector<int64_t> &domain, const 
   const size_t want = static_cast<size_t>(elems) * out.elemBytes;
   if (v.arg >= static_cast<int>(args.argBytes.size())) return Status::error(std::string(what) + ": argument index out of range");
   if (args.argBytes[v.arg] != want)
-    return Status::error(std::string(what) + ": argument " + std::to_string(v.arg) + " is " +
+    return Status::error("[cuda:bindings] " + std::string(what) + ": argument " + std::to_string(v.arg) + " is " +
                          std::to_string(args.argBytes[v.arg]) + " bytes, the tiling dims imply " + std::to_string(want));
   out.stride.assign(domain.size(), 0);
   out.baseOffset = 0;
@@ -357,7 +357,7 @@ Status launchMatmulDescriptor(const LaunchDescriptor &d, const std::map<std::str
   auto check = [&](int arg, int64_t elems, DType t, const char *name) -> Status {
     const size_t want = static_cast<size_t>(elems) * dtypeBytes(t);
     if (args.argBytes[arg] != want)
-      return Status::error(std::string("matmul ") + name + ": argument " + std::to_string(arg) + " is " +
+      return Status::error(std::string("[cuda:bindings] matmul ") + name + ": argument " + std::to_string(arg) + " is " +
                            std::to_string(args.argBytes[arg]) + " bytes, the tiling dims imply " + std::to_string(want));
     return Status::success();
   };

@@ -136,3 +136,33 @@ def test_descriptor_body_validation(tmp_path):
         p.write_text(json.dumps(dd))
         with pytest.raises(CompilerError, match=needle):
             compile_kernel(p, tmp_path / "o", spec.name)
+
+
+def _build_c_caller(tmp_path):
+    """tests/cpp/test_capi_runtime.c compiled as C99 against include/CAPI/Runtime.h and linked to the built library."""
+    import subprocess
+    lib_dir = ROOT / "ascend_mlir_b200" / "lib"
+    exe = tmp_path / "test_capi_runtime"
+    cmd = ["gcc", "-std=c99", "-O1", "-Wall", "-Wextra", "-Werror", "-ffp-contract=off", "-I", str(ROOT / "include"),
+           str(ROOT / "tests" / "cpp" / "test_capi_runtime.c"), "-L", str(lib_dir), "-lAFIRRuntimeCAPI",
+           f"-Wl,-rpath,{lib_dir}", "-o", str(exe)]
+    built = subprocess.run(cmd, capture_output=True, text=True)
+    assert built.returncode == 0, built.stderr[-3000:]
+    return exe
+
+
+def test_plain_c_caller_sees_the_reference_error_convention(tmp_path):
+    import subprocess
+    get_lib()  # makes sure the library is built
+    res = subprocess.run([str(_build_c_caller(tmp_path)), "cpu"], capture_output=True, text=True)
+    assert res.returncode == 0 and " passed, 0 failed" in res.stdout, res.stdout + res.stderr
+
+
+@pytest.mark.gpu
+def test_plain_c_caller_runs_a_kernel_and_memcmps_the_result(tmp_path):
+    import subprocess
+    get_lib()
+    src = tmp_path / "add_mul.cuda.json"
+    src.write_text(descriptors.add_mul().descriptor_json())
+    res = subprocess.run([str(_build_c_caller(tmp_path)), "gpu", str(src), str(tmp_path / "artifact")], capture_output=True, text=True)
+    assert res.returncode == 0 and " passed, 0 failed" in res.stdout, res.stdout + res.stderr
