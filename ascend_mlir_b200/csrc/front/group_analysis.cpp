@@ -154,13 +154,14 @@ Elementwise argumentTensor(int arg, const Type &t) {
   return e;
 }
 
+// Body op names are the float spellings internally; integer groups are renamed when the body is emitted.
 std::string arithName(const std::string &op) {
-  if (op == "arith.addf" || op == "afir.add") return "addf";
-  if (op == "arith.subf" || op == "afir.sub") return "subf";
-  if (op == "arith.mulf" || op == "afir.mul") return "mulf";
-  if (op == "arith.divf" || op == "afir.div") return "divf";
-  if (op == "arith.maximumf") return "maximumf";
-  if (op == "arith.minimumf") return "minimumf";
+  if (op == "arith.addf" || op == "arith.addi" || op == "afir.add") return "addf";
+  if (op == "arith.subf" || op == "arith.subi" || op == "afir.sub") return "subf";
+  if (op == "arith.mulf" || op == "arith.muli" || op == "afir.mul") return "mulf";
+  if (op == "arith.divf" || op == "arith.divsi" || op == "afir.div") return "divf";
+  if (op == "arith.maximumf" || op == "arith.maxsi") return "maximumf";
+  if (op == "arith.minimumf" || op == "arith.minsi") return "minimumf";
   return "";
 }
 
@@ -210,8 +211,13 @@ Status evalGeneric(const Op &g, size_t opIndex, const Env &env, GroupAnalysis &g
   for (int i = 0; i < g.numIns; ++i) {
     auto it = env.values.find(g.operands[i]);
     if (it == env.values.end()) return err(g, "unknown operand '%" + g.operands[i] + "'");
-    const std::string elem = g.operandTypes[i].elem;
-    if (elem == "i32" || elem == "i64") {  // an index vector: only meaningful for a gather
+    // an integer input whose element is turned into an index by the body is the index vector of a gather;
+    // any other integer input is ordinary data of an integer group
+    bool castToIndex = false;
+    for (const Op &b : g.body)
+      castToIndex = castToIndex || (b.name == "arith.index_cast" && !b.operands.empty() && static_cast<size_t>(i) < g.blockArgs.size() &&
+                                    b.operands[0] == g.blockArgs[i]);
+    if (castToIndex) {
       isIndexInput[i] = true;
       continue;
     }

@@ -40,6 +40,10 @@ template <> __device__ __forceinline__ void storeScalar<PackF16>(void *p, PackF1
 template <> __device__ __forceinline__ void storeScalar<PackBF16>(void *p, PackBF16 v) {
   *reinterpret_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
 }
+template <> __device__ __forceinline__ void storeScalar<PackI32>(void *p, PackI32 v) { *reinterpret_cast<int *>(p) = v.x; }
+template <> __device__ __forceinline__ void storeScalar<PackI16>(void *p, PackI16 v) {
+  *reinterpret_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
+}
 
 template <class P, int BODY, int UNROLL, bool VECTOR>
 __global__ void __launch_bounds__(512) elementwiseKernel(const __grid_constant__ EwParams prm) {
@@ -288,9 +292,14 @@ bool tryLaunchBlocks(const ElementwiseLaunch &l, cudaStream_t stream, cudaError_
   int body = matchBody(l.body, l.numViews);
   if (body != kBodyCopy && body != kBodyAdd && body != kBodyMul && body != kBodyAddMul && body != kBodyMulAdd && body != kBodyReluAdd)
     body = kBodyInterpreted;
-  BlocksFn fn = l.elemType == kF32 ? pickBlocks<PackF32>(body, l.numViews)
-                : l.elemType == kF16 ? pickBlocks<PackF16>(body, l.numViews)
-                                     : pickBlocks<PackBF16>(body, l.numViews);
+  BlocksFn fn = nullptr;
+  if (l.elemType == kInt32 || l.elemType == kInt16) {  // integers: the interpreted body only
+    if (l.numViews <= 3) fn = l.elemType == kInt32 ? elementwiseBlocksKernel<PackI32, kBodyInterpreted, 3> : elementwiseBlocksKernel<PackI16, kBodyInterpreted, 3>;
+  } else {
+    fn = l.elemType == kF32 ? pickBlocks<PackF32>(body, l.numViews)
+         : l.elemType == kF16 ? pickBlocks<PackF16>(body, l.numViews)
+                              : pickBlocks<PackBF16>(body, l.numViews);
+  }
   if (!fn) return false;
   const long long tileRows = 2 * 4 * E, tileCols = 4 * 8 * E;
   const long long tilesX = (l.dims[2] + tileCols - 1) / tileCols, tilesY = (l.dims[1] + tileRows - 1) / tileRows;
@@ -425,7 +434,12 @@ int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *laun
   if (!vector || body == kBodyInterpreted) unroll = 2;
 
   KernelFn fn = nullptr;
-  if (vector) {
+  if (l.elemType == kInt32 || l.elemType == kInt16) {
+    // integer groups run the interpreted body (no specialised chains: they are not on a measured path)
+    unroll = 2;
+    if (l.elemType == kInt32) fn = vector ? elementwiseKernel<PackI32, kBodyInterpreted, 2, true> : pickScalar<PackI32>();
+    else fn = vector ? elementwiseKernel<PackI16, kBodyInterpreted, 2, true> : pickScalar<PackI16>();
+  } else if (vector) {
     fn = l.elemType == kF32 ? pickVector<PackF32>(body, unroll)
          : l.elemType == kF16 ? pickVector<PackF16>(body, unroll)
                               : pickVector<PackBF16>(body, unroll);

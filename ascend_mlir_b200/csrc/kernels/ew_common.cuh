@@ -126,6 +126,61 @@ struct PackBF16 {
   __device__ __forceinline__ float lane(int i) const { return i ? __high2float(x) : __low2float(x); }
 };
 
+// Integer packs (afir.add/sub/mul and arith.addi/subi/muli/divsi/maxsi/minsi bodies on i32 and i16 tensors):
+// two's-complement wrap-around for add, sub and mul; signed max/min; signed division truncates toward zero, a zero
+// divisor gives 0 and INT_MIN / -1 gives INT_MIN (both are undefined in the IR, so any value is admissible).
+struct PackI32 {
+  using Scalar = int;
+  static constexpr int kLanes = 1;
+  int x;
+  __device__ __forceinline__ static PackI32 fromBits(unsigned int u) { return {static_cast<int>(u)}; }
+  __device__ __forceinline__ unsigned int bits() const { return static_cast<unsigned int>(x); }
+  __device__ __forceinline__ static PackI32 splat(const void *p) { return {__ldg(reinterpret_cast<const int *>(p))}; }
+  __device__ __forceinline__ static PackI32 constant(float c) { return {static_cast<int>(c)}; }
+  __device__ __forceinline__ static PackI32 add(PackI32 a, PackI32 b) { return fromBits(a.bits() + b.bits()); }
+  __device__ __forceinline__ static PackI32 sub(PackI32 a, PackI32 b) { return fromBits(a.bits() - b.bits()); }
+  __device__ __forceinline__ static PackI32 mul(PackI32 a, PackI32 b) { return fromBits(a.bits() * b.bits()); }
+  __device__ __forceinline__ static int divide(int a, int b) {
+    if (b == 0) return 0;
+    if (b == -1) return static_cast<int>(0u - static_cast<unsigned int>(a));
+    return a / b;
+  }
+  __device__ __forceinline__ static PackI32 div(PackI32 a, PackI32 b) { return {divide(a.x, b.x)}; }
+  __device__ __forceinline__ static PackI32 max(PackI32 a, PackI32 b) { return {a.x > b.x ? a.x : b.x}; }
+  __device__ __forceinline__ static PackI32 min(PackI32 a, PackI32 b) { return {a.x < b.x ? a.x : b.x}; }
+  __device__ __forceinline__ float lane(int) const { return static_cast<float>(x); }
+};
+
+struct PackI16 {
+  using Scalar = short;
+  static constexpr int kLanes = 2;
+  unsigned int x;  // two 16-bit lanes
+  __device__ __forceinline__ static PackI16 fromBits(unsigned int u) { return {u}; }
+  __device__ __forceinline__ unsigned int bits() const { return x; }
+  __device__ __forceinline__ static PackI16 splat(const void *p) {
+    const unsigned int u = __ldg(reinterpret_cast<const unsigned short *>(p));
+    return {u | (u << 16)};
+  }
+  __device__ __forceinline__ static PackI16 constant(float c) {
+    const unsigned int u = static_cast<unsigned int>(static_cast<int>(c)) & 0xffffu;
+    return {u | (u << 16)};
+  }
+  __device__ __forceinline__ static int lo(unsigned int v) { return static_cast<short>(v & 0xffffu); }
+  __device__ __forceinline__ static int hi(unsigned int v) { return static_cast<short>(v >> 16); }
+  __device__ __forceinline__ static PackI16 join(int l, int h) {
+    return {(static_cast<unsigned int>(l) & 0xffffu) | (static_cast<unsigned int>(h) << 16)};
+  }
+  __device__ __forceinline__ static PackI16 add(PackI16 a, PackI16 b) { return {__vadd2(a.x, b.x)}; }
+  __device__ __forceinline__ static PackI16 sub(PackI16 a, PackI16 b) { return {__vsub2(a.x, b.x)}; }
+  __device__ __forceinline__ static PackI16 mul(PackI16 a, PackI16 b) { return join(lo(a.x) * lo(b.x), hi(a.x) * hi(b.x)); }
+  __device__ __forceinline__ static PackI16 div(PackI16 a, PackI16 b) {
+    return join(PackI32::divide(lo(a.x), lo(b.x)), PackI32::divide(hi(a.x), hi(b.x)));
+  }
+  __device__ __forceinline__ static PackI16 max(PackI16 a, PackI16 b) { return {__vmaxs2(a.x, b.x)}; }
+  __device__ __forceinline__ static PackI16 min(PackI16 a, PackI16 b) { return {__vmins2(a.x, b.x)}; }
+  __device__ __forceinline__ float lane(int i) const { return static_cast<float>(i ? hi(x) : lo(x)); }
+};
+
 // A 16-byte vector is four packs (4 x f32, 8 x f16, 8 x bf16).
 template <class P> struct Vec16 {
   P p[4];

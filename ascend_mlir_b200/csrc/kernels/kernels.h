@@ -11,10 +11,10 @@ typedef struct CUstream_st *cudaStream_t;
 namespace afir {
 namespace kernels {
 
-enum ElemType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
+enum ElemType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kInt32 = 3, kInt16 = 4 };  // integers: elementwise groups only
 enum IndexType : int { kI32 = 0, kI64 = 1 };
 
-inline int elemBytes(int t) { return t == kF32 ? 4 : 2; }
+inline int elemBytes(int t) { return (t == kF32 || t == kInt32) ? 4 : 2; }
 
 // ---------------------------------------------------------------------------------------------
 // Fused elementwise bodies.  A body is a short chain of arith ops over the values loaded from

@@ -12,6 +12,7 @@ const char *dtypeName(DType t) {
   case DType::I32: return "i32";
   case DType::I64: return "i64";
   case DType::U8: return "u8";
+  case DType::I16: return "i16";
   }
   return "?";
 }
@@ -23,6 +24,7 @@ bool parseDType(const std::string &s, DType &out) {
   else if (s == "i32" || s == "int32") out = DType::I32;
   else if (s == "i64" || s == "int64") out = DType::I64;
   else if (s == "u8" || s == "ui8" || s == "uint8") out = DType::U8;
+  else if (s == "i16" || s == "int16") out = DType::I16;
   else return false;
   return true;
 }
@@ -30,7 +32,7 @@ bool parseDType(const std::string &s, DType &out) {
 size_t dtypeBytes(DType t) {
   switch (t) {
   case DType::F32: case DType::I32: return 4;
-  case DType::F16: case DType::BF16: return 2;
+  case DType::F16: case DType::BF16: case DType::I16: return 2;
   case DType::I64: return 8;
   case DType::U8: return 1;
   }
@@ -150,12 +152,13 @@ Status parseBody(const json::Value *v, int numViews, kernels::BodyProgram &out) 
     if (!o.isObject()) return Status::error("body op must be an object");
     const std::string name = o.getString("op");
     int code;
-    if (name == "addf" || name == "add") code = kernels::kOpAdd;
-    else if (name == "subf" || name == "sub") code = kernels::kOpSub;
-    else if (name == "mulf" || name == "mul") code = kernels::kOpMul;
-    else if (name == "divf" || name == "div") code = kernels::kOpDiv;
-    else if (name == "maximumf" || name == "max") code = kernels::kOpMax;
-    else if (name == "minimumf" || name == "min") code = kernels::kOpMin;
+    // float and (signed) integer spellings name the same op; the group's dtype decides the arithmetic
+    if (name == "addf" || name == "addi" || name == "add") code = kernels::kOpAdd;
+    else if (name == "subf" || name == "subi" || name == "sub") code = kernels::kOpSub;
+    else if (name == "mulf" || name == "muli" || name == "mul") code = kernels::kOpMul;
+    else if (name == "divf" || name == "divsi" || name == "div") code = kernels::kOpDiv;
+    else if (name == "maximumf" || name == "maxsi" || name == "max") code = kernels::kOpMax;
+    else if (name == "minimumf" || name == "minsi" || name == "min") code = kernels::kOpMin;
     else return Status::error("unsupported body op '" + name + "'");
     const json::Value *a = o.find("a"), *b = o.find("b");
     if (!a || !b) return Status::error("body op '" + name + "' needs operands 'a' and 'b'");

@@ -16,7 +16,7 @@
 
 namespace afir {
 
-enum class DType { F32, F16, BF16, I32, I64, U8 };
+enum class DType { F32, F16, BF16, I32, I64, U8, I16 };
 const char *dtypeName(DType t);
 bool parseDType(const std::string &s, DType &out);
 size_t dtypeBytes(DType t);

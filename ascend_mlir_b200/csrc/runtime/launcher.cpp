@@ -28,12 +28,14 @@ int64_t optionalField(const std::string &name, const std::map<std::string, int64
   return it == tiling.end() ? 0 : it->second;
 }
 
-int toElemType(DType t, bool &ok) {
+int toElemType(DType t, bool &ok, bool integersToo = false) {
   ok = true;
   switch (t) {
   case DType::F32: return kernels::kF32;
   case DType::F16: return kernels::kF16;
   case DType::BF16: return kernels::kBF16;
+  case DType::I32: ok = integersToo; return kernels::kInt32;
+  case DType::I16: ok = integersToo; return kernels::kInt16;
   default: ok = false; return 0;
   }
 }
@@ -120,8 +122,8 @@ Status cudaStatus(int code, const char *what) {
 Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
                               const LaunchArgs &args, LaunchInfo &info) {
   bool ok;
-  const int et = toElemType(d.dtype, ok);
-  if (!ok) return Status::error("elementwise groups compute in f32, f16 or bf16");
+  const int et = toElemType(d.dtype, ok, /*integersToo=*/true);
+  if (!ok) return Status::error("elementwise groups compute in f32, f16, bf16, i32 or i16");
   std::vector<int64_t> domain;
   if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
   if (Status s = applyRowRange(domain, args); !s) return s;

@@ -75,6 +75,31 @@ def test_transposed_operand_stays_one_elementwise_group_with_a_permuted_view():
     assert got["domain"] == ["dim_arg1_0", "dim_arg1_1"] and got["store"]["map"] == [0, 1]
 
 
+def test_integer_afir_ops_and_arith_integer_bodies(tmp_path):
+    src = tmp_path / "ints.mlir"
+    src.write_text("""
+#id = affine_map<(d0, d1) -> (d0, d1)>
+module {
+  func.func @ints(%a: tensor<4x8xi32>, %b: tensor<8xi32>, %c: tensor<4x8xi32>) -> tensor<4x8xi32> {
+    %s = afir.add %a, %b : (tensor<4x8xi32>, tensor<8xi32>) -> tensor<4x8xi32>
+    %e = tensor.empty() : tensor<4x8xi32>
+    %r = linalg.generic {indexing_maps = [#id, #id, #id], iterator_types = ["parallel", "parallel"]}
+        ins(%s, %c : tensor<4x8xi32>, tensor<4x8xi32>) outs(%e : tensor<4x8xi32>) {
+    ^bb0(%x: i32, %y: i32, %o: i32):
+      %m = arith.muli %x, %y : i32
+      %q = arith.maxsi %m, %y : i32
+      linalg.yield %q : i32
+    } -> tensor<4x8xi32>
+    return %r : tensor<4x8xi32>
+  }
+}
+""")
+    d = translate(src)
+    assert d["kernel_class"] == "elementwise" and d["dtype"] == "i32"
+    assert body_of(d) == [("addi", "v0", "v1"), ("muli", "%0", "v2"), ("maxsi", "%1", "v2")]
+    assert views_of(d) == [(0, [0, 1], None), (1, [1], None), (2, [0, 1], None)]
+
+
 def test_matmul_group_epilogue_and_tiling_space(tmp_path):
     out, space = tmp_path / "k.cuda.json", tmp_path / "ts.json"
     assert translate(EXAMPLES / "matmul_add_leakyrelu.mlir", "-o", out, "--tiling-space-out", space) is None

@@ -426,6 +426,73 @@ def test_matmul_linearity_at_scale(rt):
         assert abs(o3[m, n] - want) <= 1e-2 * abs(want) + 1e-3
 
 
+# ---- integer element types ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,name", [(np.int32, "i32"), (np.int16, "i16")])
+@pytest.mark.parametrize("M,N", [(64, 256), (33, 1000), (7, 5), (1, 1)])
+def test_integer_elementwise_wraps_like_twos_complement(rt, dtype, name, M, N):
+    """afir.add then afir.mul on integer tensors: (a + b) * b with wrap-around, over the whole value range."""
+    rng = np.random.default_rng(41)
+    info = np.iinfo(dtype)
+    a = rng.integers(info.min, info.max, (M, N), dtype=dtype, endpoint=True)
+    b = rng.integers(info.min, info.max, (M, N), dtype=dtype, endpoint=True)
+    with np.errstate(over="ignore"):
+        want = ((a + b) * b).astype(dtype)
+    out = run(rt, descriptors.add_mul(name), [a, b], np.zeros((M, N), dtype), {"M": M, "N": N})
+    assert np.array_equal(out, want)
+
+
+@pytest.mark.parametrize("dtype,name", [(np.int32, "i32"), (np.int16, "i16")])
+def test_integer_body_ops_division_max_min_constants_and_a_transposed_operand(rt, dtype, name):
+    rng = np.random.default_rng(42)
+    M, N = 520, 264
+    a = rng.integers(-1000, 1000, (M, N)).astype(dtype)
+    b = rng.integers(-50, 50, (N, M)).astype(dtype)
+    b[b == 0] = 7
+    a[0, 0], b[0, 0] = np.iinfo(dtype).min, -1
+    # out[n, m] = min(max(a[m, n], -100) / b[n, m] - 3, 40): truncating division, constants, a transposed read
+    dims = [("dim_arg0_0", "M"), ("dim_arg0_1", "N")]
+    dom = ["dim_arg0_1", "dim_arg0_0"]
+    body = {"domain": dom,
+            "loads": [{"arg": 0, "shape": ["dim_arg0_0", "dim_arg0_1"], "map": [1, 0]}, {"arg": 1, "shape": dom, "map": [0, 1]}],
+            "store": {"arg": 2, "shape": dom, "map": [0, 1]},
+            "body": [descriptors.op("maxsi", "v0", -100), descriptors.op("divsi", "%0", "v1"), descriptors.op("subi", "%1", 3),
+                     descriptors.op("minsi", "%2", 40)]}
+    spec = descriptors._spec("int_chain", "elementwise", name, 2, 1, descriptors._EW_TILE, dims, body, descriptors._EW_LAUNCH)
+    t = np.maximum(a.T.astype(np.int64), -100)
+    q = np.trunc(t / b.astype(np.int64)).astype(np.int64)  # C-style truncation toward zero
+    want = np.minimum(q - 3, 40).astype(dtype)
+    out = run(rt, spec, [a, b], np.zeros((N, M), dtype), {"M": M, "N": N})
+    assert np.array_equal(out, want)
+    # same chain on a ragged shape (element-wise path)
+    a2, b2 = np.ascontiguousarray(a[:37, :29]), np.ascontiguousarray(b[:29, :37])
+    out = run(rt, spec, [a2, b2], np.zeros((29, 37), dtype), {"M": 37, "N": 29})
+    t = np.maximum(a2.T.astype(np.int64), -100)
+    assert np.array_equal(out, np.minimum(np.trunc(t / b2.astype(np.int64)).astype(np.int64) - 3, 40).astype(dtype))
+
+
+def test_integer_division_by_zero_is_defined_as_zero(rt):
+    a = np.array([[5, -7, 0, 9]], np.int32)
+    b = np.array([[0, 0, 0, 3]], np.int32)
+    dims = [("dim_arg0_0", "M"), ("dim_arg0_1", "N")]
+    shp = ["dim_arg0_0", "dim_arg0_1"]
+    view = lambda arg: {"arg": arg, "shape": shp, "map": [0, 1]}  # noqa: E731
+    body = {"domain": shp, "loads": [view(0), view(1)], "store": view(2), "body": [descriptors.op("divsi", "v0", "v1")]}
+    spec = descriptors._spec("int_div", "elementwise", "i32", 2, 1, descriptors._EW_TILE, dims, body, descriptors._EW_LAUNCH)
+    out = run(rt, spec, [a, b], np.zeros((1, 4), np.int32), {"M": 1, "N": 4})
+    assert out.tolist() == [[0, 0, 0, 3]]
+
+
+def test_integer_transpose_and_unsupported_classes(rt):
+    x = np.arange(520 * 264, dtype=np.int32).reshape(520, 264)
+    out = run(rt, descriptors.transpose_2d("i32"), [x], np.zeros((264, 520), np.int32), {"R": 520, "C": 264})
+    assert np.array_equal(out, x.T)
+    w = configs.broadcast_add_reduce(8, 16)
+    spec = descriptors.bcast_add_rowsum("i32")
+    with pytest.raises(ExecutorError, match="f32, f16 or bf16"):
+        rt.run(spec.binary, spec.name, [w.inputs[0].view(np.int32), w.inputs[1].view(np.int32)], [np.zeros(8, np.int32)],
+               spec.pack({"M": 8, "N": 16}))
+
+
 # ---- guard bands -------------------------------------------------------------------------------------------------
 def test_no_kernel_writes_outside_its_output_at_ragged_shapes(rt, monkeypatch):
     """With AFIR_CUDA_CANARY=1 every host-path buffer sits between two 4 KB bands of a known pattern and the bands of
