@@ -47,6 +47,11 @@ float elementAsFloat(const NDArray &a, size_t idx) {
     std::memcpy(&v, base + idx * 8, 8);
     return static_cast<float>(v);
   }
+  case NpyDType::INT16: {
+    int16_t v;
+    std::memcpy(&v, base + idx * 2, 2);
+    return static_cast<float>(v);
+  }
   }
   return 0.0f;
 }

@@ -16,6 +16,7 @@ const char *npyDTypeName(NpyDType t) {
   case NpyDType::INT8: return "i8";
   case NpyDType::INT32: return "i32";
   case NpyDType::INT64: return "i64";
+  case NpyDType::INT16: return "i16";
   }
   return "?";
 }
@@ -27,13 +28,14 @@ bool parseNpyDTypeName(const std::string &s, NpyDType &out) {
   else if (s == "i8" || s == "int8") out = NpyDType::INT8;
   else if (s == "i32" || s == "int32") out = NpyDType::INT32;
   else if (s == "i64" || s == "int64") out = NpyDType::INT64;
+  else if (s == "i16" || s == "int16") out = NpyDType::INT16;
   else return false;
   return true;
 }
 
 size_t npyDTypeBytes(NpyDType t) {
   switch (t) {
-  case NpyDType::F16: case NpyDType::BF16: return 2;
+  case NpyDType::F16: case NpyDType::BF16: case NpyDType::INT16: return 2;
   case NpyDType::F32: case NpyDType::INT32: return 4;
   case NpyDType::INT8: return 1;
   case NpyDType::INT64: return 8;
@@ -114,6 +116,7 @@ Status loadNpy(const std::string &path, NDArray &out) {
   else if (descr == "<i1" || descr == "=i1" || descr == "|i1") out.dtype = NpyDType::INT8;
   else if (descr == "<i4" || descr == "=i4") out.dtype = NpyDType::INT32;
   else if (descr == "<i8" || descr == "=i8") out.dtype = NpyDType::INT64;
+  else if (descr == "<i2" || descr == "=i2") out.dtype = NpyDType::INT16;
   else return Status::error("Unsupported dtype '" + descr + "': " + path);
   if (headerField(header, "fortran_order").find("True") != std::string::npos)
     return Status::error("Fortran-ordered arrays are not supported: " + path);
@@ -131,6 +134,7 @@ Status saveNpy(const std::string &path, const NDArray &arr) {
   case NpyDType::F32: descr = "<f4"; break;
   case NpyDType::INT8: descr = "|i1"; break;
   case NpyDType::INT32: descr = "<i4"; break;
+  case NpyDType::INT16: descr = "<i2"; break;
   case NpyDType::INT64: descr = "<i8"; break;
   }
   std::string shape = "(";

@@ -12,7 +12,7 @@
 
 namespace afir {
 
-enum class NpyDType { F16, BF16, F32, INT8, INT32, INT64 };
+enum class NpyDType { F16, BF16, F32, INT8, INT32, INT64, INT16 };
 const char *npyDTypeName(NpyDType t);       // "f16", "bf16", ...
 bool parseNpyDTypeName(const std::string &s, NpyDType &out);
 size_t npyDTypeBytes(NpyDType t);

@@ -67,6 +67,12 @@ def make_case(name: str, rng):
         bias = bf16(rng.standard_normal(512, dtype=np.float32) * np.float32(0.1))
         x = bf16_to_f32(A).astype(np.float64) @ bf16_to_f32(B).astype(np.float64) + bf16_to_f32(bias)[None, :]
         return [A, B, bias], bf16(np.maximum(x, 0.01 * x).astype(np.float32)), 1e-2, 1e-2
+    if name == "integer_chain":
+        a = rng.integers(-32768, 32767, (333, 1000), endpoint=True).astype(np.int16)
+        b = rng.integers(-32768, 32767, 1000, endpoint=True).astype(np.int16)
+        with np.errstate(over="ignore"):
+            want = ((a + b[None, :]).astype(np.int16) * a).astype(np.int16)
+        return [a, b], want, 0.0, 0.0
     if name == "transpose_2d":
         x = rng.standard_normal((1000, 520)).astype(np.float16)
         return [x], np.ascontiguousarray(x.T), 0.0, 0.0

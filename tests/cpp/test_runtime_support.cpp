@@ -49,6 +49,16 @@ static void testNpy() {
   EXPECT(head.compare(0, 6, "\x93NUMPY") == 0 && head[6] == 1 && head[7] == 0, "version 1.0 header");
   EXPECT((10 + hlen) % 64 == 0, "header padded to 64 bytes");
 
+  NDArray s16;
+  s16.dtype = NpyDType::INT16;
+  s16.shape = {3};
+  s16.allocate();
+  const int16_t vals[3] = {-32768, -1, 32767};
+  std::memcpy(s16.bytes.data(), vals, sizeof vals);
+  EXPECT(saveNpy(path("s16.npy"), s16).ok(), "save i16");
+  NDArray s16b;
+  EXPECT(loadNpy(path("s16.npy"), s16b).ok() && s16b.dtype == NpyDType::INT16 && s16b.bytes == s16.bytes, "i16 round trip (<i2)");
+
   NDArray c;
   c.dtype = NpyDType::BF16;
   c.shape = {4};

@@ -75,6 +75,26 @@ def test_transposed_operand_stays_one_elementwise_group_with_a_permuted_view():
     assert got["domain"] == ["dim_arg1_0", "dim_arg1_1"] and got["store"]["map"] == [0, 1]
 
 
+def test_afir_ops_on_dynamic_shapes_take_extents_from_the_operands(tmp_path):
+    src = tmp_path / "dyn.mlir"
+    src.write_text("""
+module {
+  func.func @dyn(%a: tensor<?x?xf32>, %b: tensor<?xf32>, %c: tensor<?x1xf32>) -> tensor<?x?xf32> {
+    %s = afir.add %a, %b : (tensor<?x?xf32>, tensor<?xf32>) -> tensor<?x?xf32>
+    %p = afir.mul %s, %c : (tensor<?x?xf32>, tensor<?x1xf32>) -> tensor<?x?xf32>
+    return %p : tensor<?x?xf32>
+  }
+}
+""")
+    d = translate(src)
+    assert d["domain"] == ["dim_arg0_0", "dim_arg0_1"]
+    assert [(l["shape"], l["map"]) for l in d["loads"]] == [(["dim_arg0_0", "dim_arg0_1"], [0, 1]), (["dim_arg1_0"], [1]),
+                                                            (["dim_arg2_0", 1], [0, -1])]
+    assert body_of(d) == [("addf", "v0", "v1"), ("mulf", "%0", "v2")]
+    fields = [t["name"] for t in d["tiling"]]
+    assert fields[-4:] == ["dim_arg0_0", "dim_arg0_1", "dim_arg1_0", "dim_arg2_0"]
+
+
 def test_integer_afir_ops_and_arith_integer_bodies(tmp_path):
     src = tmp_path / "ints.mlir"
     src.write_text("""
