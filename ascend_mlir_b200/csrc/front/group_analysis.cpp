@@ -127,13 +127,28 @@ Status inlineInto(Elementwise &dst, const Elementwise &src, const AffineMap &map
     dst.aArg = src.aArg; dst.bArg = src.bArg; dst.initArg = src.initArg;
     dst.inType = src.inType; dst.M = src.M; dst.N = src.N; dst.K = src.K;
   }
-  const int opBase = static_cast<int>(dst.ops.size());
+  // Ops are appended with their operands renumbered; an op the group already holds (the same producer read by two
+  // consumers, e.g. abs(x) = max(x, 0 - x)) is reused instead of being computed twice.
+  std::vector<int> opRemap(src.ops.size(), -1);
   auto remap = [&](Src s) {
     if (s.kind == Src::ViewValue) s.index = viewRemap[s.index];
-    else if (s.kind == Src::OpValue) s.index += opBase;
+    else if (s.kind == Src::OpValue) s.index = opRemap[s.index];
     return s;
   };
-  for (const BodyOp &b : src.ops) dst.ops.push_back({b.op, remap(b.a), remap(b.b)});
+  auto sameSrc = [](const Src &x, const Src &y) {
+    return x.kind == y.kind && (x.kind == Src::Constant ? x.value == y.value : x.index == y.index);
+  };
+  for (size_t i = 0; i < src.ops.size(); ++i) {
+    const BodyOp b{src.ops[i].op, remap(src.ops[i].a), remap(src.ops[i].b)};
+    int found = -1;
+    for (size_t j = 0; j < dst.ops.size() && found < 0; ++j)
+      if (dst.ops[j].op == b.op && sameSrc(dst.ops[j].a, b.a) && sameSrc(dst.ops[j].b, b.b)) found = static_cast<int>(j);
+    if (found < 0) {
+      dst.ops.push_back(b);
+      found = static_cast<int>(dst.ops.size()) - 1;
+    }
+    opRemap[i] = found;
+  }
   out = remap(src.result);
   return Status::success();
 }

@@ -5,8 +5,10 @@ The reference does this step with torch-mlir (python/torch/torch2linalg/convert.
 traced with `torch.export` and the ATen graph is written out directly as `linalg.generic` / `linalg.fill` /
 `linalg.matmul` on tensors, one op per ATen node, for the operator subset of the fused-group path:
 
-    add sub mul div maximum minimum (tensor-tensor with numpy broadcasting, tensor-scalar), relu, leaky_relu, neg,
-    unsqueeze / squeeze of unit dimensions (views, no op emitted), sum over the last dimension,
+    add sub mul div maximum minimum (tensor-tensor with numpy broadcasting, tensor-scalar), relu, leaky_relu, neg, abs,
+    clamp / clamp_min / clamp_max with number bounds,
+    unsqueeze / squeeze of unit dimensions and t / transpose / permute (views, no op emitted: a permuted operand of
+    an elementwise op becomes a permuted indexing map), sum over the last dimension,
     mm / matmul of 2-D operands, addmm with a row-broadcast bias.
 
 Dynamic dimensions become `?` and are read back with `tensor.dim`.  Anything else raises UnsupportedTorchOp
@@ -28,8 +30,8 @@ class UnsupportedTorchOp(NotImplementedError):
 
 @dataclass
 class _Tensor:
-    """A value of the traced graph: a materialised tensor (`ssa`, `base` extents) seen through a view that may
-    have extra unit dimensions (entries None in `view`; other entries index `base` in increasing order)."""
+    """A value of the traced graph: a materialised tensor (`ssa`, `base` extents) seen through a view: every base
+    dimension appears once in `view` (in any order: a permutation), entries None are inserted unit dimensions."""
     ssa: str
     elem: str
     base: List[Size]
@@ -246,10 +248,10 @@ class _Emitter:
         return _Tensor(result, elem, sizes)
 
     def materialise(self, t: _Tensor) -> _Tensor:
-        """Structured ops other than elementwise ones need the value without view-only unit dimensions."""
-        if all(v is not None for v in t.view):
+        """Structured ops other than elementwise ones need the value itself, not a view of it."""
+        if t.view == list(range(len(t.base))):
             return t
-        raise UnsupportedTorchOp("a view with inserted unit dimensions feeds an op that needs a materialised tensor")
+        raise UnsupportedTorchOp("a view (inserted unit dimensions or a permutation) feeds an op that needs a materialised tensor")
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -305,6 +307,34 @@ def _lower_node(em: _Emitter, node, env: Dict[str, _Tensor]) -> _Tensor:
         return em.binary("maximumf", operand(0), 0.0)
     if target == aten.neg.default:
         return em.binary("subf", 0.0, operand(0))
+    if target == aten.abs.default:
+        x = operand(0)
+        return em.binary("maximumf", x, em.binary("subf", 0.0, x))
+    if target in (aten.clamp_min.default, aten.clamp_max.default, aten.clamp.default):
+        x = operand(0)
+        lo = arg(1) if target != aten.clamp_max.default else None
+        hi = arg(1) if target == aten.clamp_max.default else (arg(2) if target == aten.clamp.default else None)
+        if isinstance(lo, _Tensor) or isinstance(hi, _Tensor):
+            raise UnsupportedTorchOp("clamp with tensor bounds")
+        if lo is not None:
+            x = em.binary("maximumf", x, _scalar(lo))
+        if hi is not None:
+            x = em.binary("minimumf", x, _scalar(hi))
+        return x
+    if target in (aten.t.default, aten.transpose.int, aten.permute.default):
+        x = arg(0)
+        rank = len(x.view)
+        if target == aten.t.default:
+            perm = [1, 0] if rank == 2 else list(range(rank))
+        elif target == aten.transpose.int:
+            d0, d1 = (int(arg(1)) % rank, int(arg(2)) % rank)
+            perm = list(range(rank))
+            perm[d0], perm[d1] = perm[d1], perm[d0]
+        else:
+            perm = [int(d) % rank for d in arg(1)]
+        if sorted(perm) != list(range(rank)):
+            raise UnsupportedTorchOp(f"{name} with dims {perm}")
+        return _Tensor(x.ssa, x.elem, x.base, [x.view[d] for d in perm])
     if target == aten.leaky_relu.default:
         return em.leaky_relu(arg(0), float(arg(1, 0.01)))
     if target == aten.unsqueeze.default:
@@ -381,8 +411,8 @@ def torch_to_linalg(model: torch.nn.Module, inputs: Sequence[torch.Tensor], dyna
             raise UnsupportedTorchOp(f"graph node kind '{node.op}'")
     if result is None:
         raise UnsupportedTorchOp("model has no output")
-    if any(v is None for v in result.view):
-        raise UnsupportedTorchOp("the model output is a view with inserted unit dimensions")
+    if result.view != list(range(len(result.base))):
+        raise UnsupportedTorchOp("the model output is a bare view (inserted unit dimensions or a permutation) of another value")
     sig = ", ".join(f"{t.ssa}: {t.type}" for t in args)
     head = [f"{alias} = {text}" for text, alias in em.maps.items()]
     return "\n".join(head + ["module {", f"  func.func @{func_name}({sig}) -> {result.type} {{"] + em.lines +

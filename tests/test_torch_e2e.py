@@ -104,6 +104,31 @@ def test_scalars_views_and_broadcast_maps():
     assert "tensor<8x16xf32>" in text and "?" not in text
 
 
+def test_transposed_views_clamp_and_abs(tmp_path):
+    class M(torch.nn.Module):
+        def forward(self, a, b):
+            return torch.clamp((a.t() + b).abs(), 0.1, 2.0)
+    text = torch_to_linalg(M(), [torch.randn(8, 16), torch.randn(16, 8)])
+    assert "-> (d1, d0)>" in text, "a.t() is a permuted indexing map, not an op"
+    assert text.count("linalg.generic") == 5  # add, neg, max (abs), clamp low, clamp high
+    built = compile_model(M(), [TensorSpec(("M", "N"), torch.float32), TensorSpec(("N", "M"), torch.float32)], tmp_path / "t")
+    d = descriptor(built)
+    assert d["kernel_class"] == "elementwise" and [l["map"] for l in d["loads"]] == [[1, 0], [0, 1]]
+    assert [o["op"] for o in d["body"]] == ["addf", "subf", "maximumf", "maximumf", "minimumf"]
+
+    class Bad(torch.nn.Module):
+        def forward(self, a):
+            return a.t()
+    with pytest.raises(UnsupportedTorchOp, match="bare view"):
+        torch_to_linalg(Bad(), [torch.randn(4, 8)])
+
+    class BadSum(torch.nn.Module):
+        def forward(self, a):
+            return a.t().sum(dim=1)
+    with pytest.raises(UnsupportedTorchOp, match="materialised"):
+        torch_to_linalg(BadSum(), [torch.randn(4, 8)])
+
+
 def test_unsupported_models_are_refused():
     class Tanh(torch.nn.Module):
         def forward(self, x):

@@ -62,6 +62,15 @@ def test_addmm_leaky_relu():
                      TensorSpec((128,), torch.bfloat16)]
 
 
+@torch_e2e_test(verify_shapes={"M": 264, "N": 520}, atol=0.0, rtol=0.0)
+def test_transposed_operand_clamp_abs():
+    class Model(torch.nn.Module):
+        def forward(self, a, b):
+            return torch.clamp((a.t() + b).abs(), 0.1, 2.0)
+
+    return Model(), [TensorSpec(("M", "N"), torch.float32), TensorSpec(("N", "M"), torch.float32)]
+
+
 def test_kernel_output_matches_eager_bit_for_bit_on_f32_elementwise(tmp_path):
     """f32 elementwise chains have no rounding freedom: run the compiled group through the runtime and compare."""
     from ascend_mlir_b200.runtime import CudaRuntime, TilingSchema, compile_kernel
