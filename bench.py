@@ -207,8 +207,6 @@ class DeviceGroup:
         self.tiling = w.tiling()
         ws_bytes = rt.workspace_bytes(w.spec.binary, self.tiling)
         self.ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=device)
-        self.in_args = [(t.data_ptr(), t.numel() * t.element_size()) for t in self.dev_in]
-        self.out_args = [(self.dev_out.data_ptr(), self.dev_out.numel() * self.dev_out.element_size())]
         self.host_in_args = [(t.data_ptr(), t.numel() * t.element_size()) for t in self.host_in]
         self.host_out_args = [(self.host_out.data_ptr(), self.host_out.numel() * self.host_out.element_size())]
 
