@@ -90,6 +90,22 @@ int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *laun
 // Row reduction: out[m] = sum_n body(views)(m, n), f32 accumulation from zero.
 // dims = {rows, cols}; view strides are per (row, col) with the col stride 1 or 0.
 // ---------------------------------------------------------------------------------------------
+// Mailbox of a reduction whose reduced axis is sharded over GPUs (one process per GPU, or one process driving
+// several).  Every pointer is a device address as seen from the launching GPU; peerSlots[p] / peerFlags[p] point
+// into GPU p's mailbox (peer-mapped), at the place reserved for this rank.
+constexpr int kMaxExchangeRanks = 8;
+struct RowReduceExchange {
+  float *peerSlots[kMaxExchangeRanks];          // where this rank's partial sums go on rank p: [rows] f32
+  unsigned int *peerFlags[kMaxExchangeRanks];   // this rank's "sent" word on rank p (holds the last finished epoch)
+  const float *mySlots;                         // local mailbox of this epoch: [world, slotStride] f32, filled by the peers
+  unsigned int *myFlags;                        // local: [world] "sent" words written by the peers
+  unsigned int *doneCounter;                    // local: CTAs of this launch that have sent all their rows
+  unsigned int *status;                         // local: set to 1 when the wait for a peer ran out
+  int world;                                    // 0 = no exchange
+  unsigned int epoch;                           // 1, 2, ... identical on every rank for the same call
+  long long slotStride;                         // floats between two ranks' slots
+};
+
 struct RowReduceLaunch {
   int elemType;
   int64_t rows, cols;
@@ -106,6 +122,10 @@ struct RowReduceLaunch {
   int streamStages;      // staged variant: ring depth per warp (0 = default)
   int streamChunkBytes;  // staged variant: bytes per stage (0 = default)
   int forcePlainLoads;  // 1 = never use the bulk-copy staged variant (tuning / comparison)
+  // Not null: the per-row sums are partial (this GPU holds a column slice).  The kernel stores them as f32 into
+  // every rank's mailbox instead of `out`, and the last CTA to finish waits (2 s at most) for the other ranks'
+  // partial sums and writes out[m] = their sum in rank order.  Column slicing (splitCols) is not combined with it.
+  const RowReduceExchange *exchange = nullptr;
 };
 size_t rowReduceWorkspaceBytes(int64_t rows, int splitCols);
 int chooseRowReduceSplit(int64_t rows, int64_t cols, int smCount);

@@ -30,6 +30,7 @@ struct RrParams {
   float *partial;            // [rows, slices] when slices > 1
   void *out;
   BodyProgram prog;
+  RowReduceExchange xchg;    // world > 0: the sums are partial and go to every rank's mailbox
 };
 
 template <class P> __device__ __forceinline__ void storeSum(void *out, long long row, float v);
@@ -43,7 +44,93 @@ template <> __device__ __forceinline__ void storeSum<PackBF16>(void *out, long l
   static_cast<__nv_bfloat16 *>(out)[row] = __float2bfloat16_rn(v);
 }
 
-template <class P, int BODY, bool VECTOR>
+// ---- exchange of partial sums between GPUs (the reduced axis is sharded) ----------------------------------
+// Each row's partial sum is stored straight into every rank's mailbox (plain stores over NVLink; the own
+// mailbox is an ordinary local store).  When a CTA has sent all its rows it fences and counts itself done;
+// the CTA that completes the count publishes "epoch" in this rank's flag word on every rank, waits until
+// every rank's flag word here has reached the epoch, and adds the world's partial sums in rank order, so
+// all ranks produce the same bits.  The wait is bounded: after 2 s the status word is set and out stays
+// unwritten; the context remains usable.
+constexpr unsigned long long kExchangeWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ void sendPartial(const RowReduceExchange &x, long long row, float v) {
+  for (int p = 0; p < x.world; ++p) x.peerSlots[p][row] = v;
+}
+
+template <class P> __device__ __noinline__ void exchangeTail(const RowReduceExchange &x, void *out, long long rows) {
+  __shared__ int lastCta;
+  __syncthreads();  // every thread's mailbox stores are ordered before thread 0's fence
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // ... which makes them visible system-wide before this CTA is counted
+    lastCta = atomicAdd(x.doneCounter, 1u) == gridDim.x - 1u;
+  }
+  __syncthreads();
+  if (!lastCta) return;
+  // every CTA of this launch has sent and fenced its rows
+  bool ok = true;
+  if (threadIdx.x < static_cast<unsigned int>(x.world)) {
+    // release: ordered after everything the counter made visible to this CTA (all CTAs' fenced stores)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(x.peerFlags[threadIdx.x]), "r"(x.epoch) : "memory");
+    const unsigned int *flag = x.myFlags + threadIdx.x;
+    unsigned long long t0 = 0;
+    unsigned int spins = 0;
+    while (true) {
+      unsigned int seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+      if (static_cast<int>(seen - x.epoch) >= 0) break;
+      if (++spins > 2000u) __nanosleep(100);  // the ranks run in step: the flag is normally there within microseconds
+      if ((spins & 63u) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kExchangeWaitLimitNs) { ok = false; break; }
+      }
+    }
+  }
+  ok = __syncthreads_and(ok) != 0;  // the acquiring loads above order the slot reads of the whole CTA behind them
+  if (threadIdx.x == 0) *x.doneCounter = 0;  // the next launch on this stream counts from zero
+  if (!ok) {
+    if (threadIdx.x == 0) atomicExch(x.status, 1u);
+    return;
+  }
+  // out[m] = sum over ranks in rank order; four rows per 16-byte load, four such loads per rank in flight and
+  // no store between them (slotStride is a multiple of four floats and the mailbox is 512-byte aligned)
+  const long long quads = rows >> 2;
+  for (long long q0 = threadIdx.x; q0 < quads; q0 += 4ll * blockDim.x) {
+    float4 t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+    for (int p = 0; p < x.world; ++p) {
+      const float4 *slot = reinterpret_cast<const float4 *>(x.mySlots + p * x.slotStride);
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long q = q0 + static_cast<long long>(u) * blockDim.x;
+        v[u] = q < quads ? __ldcg(slot + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { t[u].x += v[u].x; t[u].y += v[u].y; t[u].z += v[u].z; t[u].w += v[u].w; }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long q = q0 + static_cast<long long>(u) * blockDim.x;
+      if (q < quads) {
+        storeSum<P>(out, 4 * q, t[u].x);
+        storeSum<P>(out, 4 * q + 1, t[u].y);
+        storeSum<P>(out, 4 * q + 2, t[u].z);
+        storeSum<P>(out, 4 * q + 3, t[u].w);
+      }
+    }
+  }
+  for (long long row = 4 * quads + threadIdx.x; row < rows; row += blockDim.x) {
+    float t = 0.f;
+    for (int p = 0; p < x.world; ++p) t += __ldcg(x.mySlots + p * x.slotStride + row);
+    storeSum<P>(out, row, t);
+  }
+}
+
+template <class P, int BODY, bool VECTOR, bool XCHG = false>
 __global__ void __launch_bounds__(512) rowReduceKernel(const __grid_constant__ RrParams prm) {
   using B = Body<BODY>;
   constexpr int NV = B::kViews;
@@ -136,10 +223,12 @@ __global__ void __launch_bounds__(512) rowReduceKernel(const __grid_constant__ R
       }
     }
     if (lane == 0 && rowLive) {
-      if (prm.slices > 1) prm.partial[row * prm.slices + slice] = sum;
+      if (XCHG) sendPartial(prm.xchg, row, sum);
+      else if (prm.slices > 1) prm.partial[row * prm.slices + slice] = sum;
       else storeSum<P>(prm.out, row, sum);
     }
   }
+  if constexpr (XCHG) exchangeTail<P>(prm.xchg, prm.out, prm.rows);
 }
 
 // ---- bulk-copy staged variant -------------------------------------------------------------------------
@@ -173,11 +262,12 @@ struct RrStreamParams {
   unsigned int chunkBytes;       // multiple of 512
   void *out;
   BodyProgram prog;
+  RowReduceExchange xchg;        // world > 0: the sums are partial and go to every rank's mailbox
 };
 
 __device__ __forceinline__ unsigned int smemU32(const void *p) { return static_cast<unsigned int>(__cvta_generic_to_shared(p)); }
 
-template <class P, int BODY>
+template <class P, int BODY, bool XCHG = false>
 __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_constant__ RrStreamParams prm) {
   using B = Body<BODY>;
   constexpr int NV = B::kViews;
@@ -232,7 +322,8 @@ __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_con
   unsigned int phase = 0;
   unsigned int bcastNow[NV], bcastNext[NV];
   loadBcast(firstRow, bcastNow);
-  for (long long row = firstRow; row < prm.rows; row += totalWarps) {
+  bool alive = true;
+  for (long long row = firstRow; row < prm.rows && alive; row += totalWarps) {
     loadBcast(row + totalWarps, bcastNext);  // one row ahead: its latency hides behind this row's stream
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (unsigned int chunk = 0; chunk < chunksPerRow; ++chunk) {
@@ -250,9 +341,15 @@ __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_con
           if (t0 == 0) t0 = now;
           else if (now - t0 > kStreamWaitLimitNs) {
             atomicCAS(&g_rowReduceStatus, 0u, 1u);
-            return;  // nothing of this warp's is in flight on a barrier that never completed beyond this ring
+            if (!XCHG) return;  // nothing of this warp's is in flight on a barrier that never completed beyond this ring
+            alive = false;  // with an exchange the warp still has to reach the CTA's barriers below
+            break;
           }
         }
+      }
+      if constexpr (XCHG) {
+        alive = __all_sync(0xffffffffu, alive) != 0;  // leave the row loop as a whole warp
+        if (!alive) break;
       }
       const unsigned int bytes = min(kStreamChunkBytes, prm.rowBytes - chunk * kStreamChunkBytes);
       const unsigned int nvec = bytes >> 4;
@@ -283,10 +380,15 @@ __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_con
     float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
-    if (lane == 0) storeSum<P>(prm.out, row, sum);
+    if (XCHG && !alive) break;
+    if (lane == 0) {
+      if (XCHG) sendPartial(prm.xchg, row, sum);
+      else storeSum<P>(prm.out, row, sum);
+    }
 #pragma unroll
     for (int k = 0; k < NV; ++k) bcastNow[k] = bcastNext[k];
   }
+  if constexpr (XCHG) exchangeTail<P>(prm.xchg, prm.out, prm.rows);
 }
 
 template <class P>
@@ -307,6 +409,11 @@ template <class P, bool VECTOR> KernelFn pickBody(int body) {
   case kBodyMul: return rowReduceKernel<P, kBodyMul, VECTOR>;
   default: return rowReduceKernel<P, kBodyInterpreted, VECTOR>;
   }
+}
+
+// With an exchange only the add body is specialised; every other chain runs interpreted.
+template <class P, bool VECTOR> KernelFn pickBodyExchange(int body) {
+  return body == kBodyAdd ? rowReduceKernel<P, kBodyAdd, VECTOR, true> : rowReduceKernel<P, kBodyInterpreted, VECTOR, true>;
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -347,6 +454,10 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
   if (vecPerRow >= (1ll << 31)) return cudaErrorInvalidValue;
 
   int slices = l.splitCols > 0 ? l.splitCols : 1;
+  if (l.exchange) {
+    if (l.exchange->world < 1 || l.exchange->world > kMaxExchangeRanks || l.rows > l.exchange->slotStride) return cudaErrorInvalidValue;
+    slices = 1;
+  }
   slices = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(slices, std::max<int64_t>(1, vecPerRow))));
   if (slices > 1 && (!l.workspace || l.workspaceBytes < rowReduceWorkspaceBytes(l.rows, slices)))
     return cudaErrorInvalidValue;
@@ -377,6 +488,7 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
   p.partial = static_cast<float *>(l.workspace);
   p.out = l.out;
   p.prog = l.body;
+  if (l.exchange) p.xchg = *l.exchange;
 
   const int body = matchBody(l.body, l.numViews);
   // Long rows with exactly one streamed operand and enough rows to occupy every warp of the machine:
@@ -416,11 +528,17 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
       sp.chunkBytes = sChunk;
       sp.out = l.out;
       sp.prog = l.body;
+      if (l.exchange) sp.xchg = *l.exchange;
       using StreamFn = void (*)(const RrStreamParams);
       StreamFn sfn = nullptr;
       if (l.elemType == kF32) sfn = body == kBodyAdd ? rowReduceStreamKernel<PackF32, kBodyAdd> : body == kBodyCopy ? rowReduceStreamKernel<PackF32, kBodyCopy> : body == kBodyMul ? rowReduceStreamKernel<PackF32, kBodyMul> : rowReduceStreamKernel<PackF32, kBodyInterpreted>;
       else if (l.elemType == kF16) sfn = body == kBodyAdd ? rowReduceStreamKernel<PackF16, kBodyAdd> : body == kBodyCopy ? rowReduceStreamKernel<PackF16, kBodyCopy> : body == kBodyMul ? rowReduceStreamKernel<PackF16, kBodyMul> : rowReduceStreamKernel<PackF16, kBodyInterpreted>;
       else sfn = body == kBodyAdd ? rowReduceStreamKernel<PackBF16, kBodyAdd> : body == kBodyCopy ? rowReduceStreamKernel<PackBF16, kBodyCopy> : body == kBodyMul ? rowReduceStreamKernel<PackBF16, kBodyMul> : rowReduceStreamKernel<PackBF16, kBodyInterpreted>;
+      if (l.exchange) {
+        if (l.elemType == kF32) sfn = body == kBodyAdd ? rowReduceStreamKernel<PackF32, kBodyAdd, true> : rowReduceStreamKernel<PackF32, kBodyInterpreted, true>;
+        else if (l.elemType == kF16) sfn = body == kBodyAdd ? rowReduceStreamKernel<PackF16, kBodyAdd, true> : rowReduceStreamKernel<PackF16, kBodyInterpreted, true>;
+        else sfn = body == kBodyAdd ? rowReduceStreamKernel<PackBF16, kBodyAdd, true> : rowReduceStreamKernel<PackBF16, kBodyInterpreted, true>;
+      }
       const size_t smem = static_cast<size_t>(kStreamWarps) * sStages * sChunk + static_cast<size_t>(kStreamWarps) * sStages * sizeof(unsigned long long);
       cudaError_t ae = cudaFuncSetAttribute(sfn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       if (ae != cudaSuccess) return ae;
@@ -436,6 +554,11 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
   if (l.elemType == kF32) fn = vector ? pickBody<PackF32, true>(body) : pickBody<PackF32, false>(body);
   else if (l.elemType == kF16) fn = vector ? pickBody<PackF16, true>(body) : pickBody<PackF16, false>(body);
   else fn = vector ? pickBody<PackBF16, true>(body) : pickBody<PackBF16, false>(body);
+  if (l.exchange) {
+    if (l.elemType == kF32) fn = vector ? pickBodyExchange<PackF32, true>(body) : pickBodyExchange<PackF32, false>(body);
+    else if (l.elemType == kF16) fn = vector ? pickBodyExchange<PackF16, true>(body) : pickBodyExchange<PackF16, false>(body);
+    else fn = vector ? pickBodyExchange<PackBF16, true>(body) : pickBodyExchange<PackBF16, false>(body);
+  }
 
   const int rowsPerCta = threads / lanes;
   const int64_t work = ((l.rows + rowsPerCta - 1) / rowsPerCta) * slices;

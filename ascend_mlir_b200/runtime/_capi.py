@@ -19,7 +19,11 @@ EXPORTS = [
     "afirt_executor_launch_device", "afirt_executor_synchronize", "afirt_executor_workspace_bytes",
     "afirt_executor_last_launch_count", "afirt_executor_total_launch_count", "afirt_runtime_version",
     "afirt_bcast_add_rowsum_no_alloc",
+    "afirt_rowsum_exchange_create", "afirt_rowsum_exchange_connect", "afirt_bcast_add_rowsum_exchange",
+    "afirt_rowsum_exchange_status", "afirt_rowsum_exchange_destroy",
 ]
+
+EXCHANGE_HANDLE_BYTES = 96  # AFIRT_EXCHANGE_HANDLE_BYTES
 
 
 def get_lib() -> ctypes.CDLL:
@@ -61,6 +65,19 @@ def get_lib() -> ctypes.CDLL:
                                                     ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
                                                     ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
     lib.afirt_bcast_add_rowsum_no_alloc.restype = ctypes.c_int
+    lib.afirt_rowsum_exchange_create.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, _vpp, _u8p,
+                                                 ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_rowsum_exchange_create.restype = ctypes.c_int
+    lib.afirt_rowsum_exchange_connect.argtypes = [ctypes.c_void_p, _u8p, ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_rowsum_exchange_connect.restype = ctypes.c_int
+    lib.afirt_bcast_add_rowsum_exchange.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                                    ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                                    ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_bcast_add_rowsum_exchange.restype = ctypes.c_int
+    lib.afirt_rowsum_exchange_status.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_rowsum_exchange_status.restype = ctypes.c_int
+    lib.afirt_rowsum_exchange_destroy.argtypes = [ctypes.c_void_p]
+    lib.afirt_rowsum_exchange_destroy.restype = None
     lib.afirt_runtime_version.argtypes = []
     lib.afirt_runtime_version.restype = ctypes.c_char_p
     _lib = lib

@@ -75,3 +75,68 @@ def allreduce_partial_rowsums(partial):
     import torch.distributed as dist
     dist.all_reduce(partial, op=dist.ReduceOp.SUM)
     return partial
+
+
+class RowsumExchange:
+    """The same exchange inside the reduction kernel: afirt_rowsum_exchange_* of the C-ABI library.
+
+    Every rank reduces its column slice and stores the partial row sums straight into all ranks' mailboxes over
+    NVLink; the kernel's last CTA waits (2 s at most) for the other ranks and adds the partial sums in rank order.
+    One launch per rank, no library collective, identical bits on every rank.  `connect()` gathers the mailbox
+    handles over the default process group (any backend; objects, not tensors); `connect_handles()` takes them
+    from elsewhere.  Every rank needs a GPU of its own."""
+
+    ELEM_TYPES = {"f32": 0, "f16": 1, "bf16": 2}
+
+    def __init__(self, device_id: int, rank: int, world_size: int, max_rows: int):
+        import ctypes
+        from .runtime._capi import EXCHANGE_HANDLE_BYTES, get_lib
+        self._ct = ctypes
+        self._lib = get_lib()
+        self.rank, self.world_size, self.max_rows = rank, world_size, max_rows
+        self._ptr = ctypes.c_void_p()
+        handle = (ctypes.c_uint8 * EXCHANGE_HANDLE_BYTES)()
+        err = ctypes.create_string_buffer(512)
+        if self._lib.afirt_rowsum_exchange_create(device_id, rank, world_size, max_rows, ctypes.byref(self._ptr), handle,
+                                                  err, len(err)):
+            raise RuntimeError(err.value.decode())
+        self.handle = bytes(handle)
+
+    def connect_handles(self, handles) -> None:
+        ct = self._ct
+        blob = b"".join(handles)
+        arr = (ct.c_uint8 * len(blob)).from_buffer_copy(blob)
+        err = ct.create_string_buffer(512)
+        if len(handles) != self.world_size:
+            raise ValueError(f"{len(handles)} handles for a world of {self.world_size}")
+        if self._lib.afirt_rowsum_exchange_connect(self._ptr, arr, err, len(err)):
+            raise RuntimeError(err.value.decode())
+
+    def connect(self) -> None:
+        if self.world_size == 1:
+            return self.connect_handles([self.handle])
+        import torch.distributed as dist
+        handles = [None] * self.world_size
+        dist.all_gather_object(handles, self.handle)
+        self.connect_handles(handles)
+
+    def bcast_add_rowsum(self, a_ptr: int, b_ptr: int, out_ptr: int, rows: int, cols: int, b_row_stride: int,
+                         elem_type: str = "f32", stream: int = 0) -> None:
+        """Enqueues out[m] = sum over ranks of sum_n (a[m] + b_r[m, n]); the pointers are device addresses."""
+        ct = self._ct
+        err = ct.create_string_buffer(512)
+        if self._lib.afirt_bcast_add_rowsum_exchange(self._ptr, self.ELEM_TYPES[elem_type], ct.c_void_p(a_ptr), ct.c_void_p(b_ptr),
+                                                     ct.c_void_p(out_ptr), rows, cols, b_row_stride, ct.c_void_p(stream),
+                                                     err, len(err)):
+            raise RuntimeError(err.value.decode())
+
+    def check(self) -> None:
+        """After the stream has been synchronised: raises when a wait inside the kernel ran out."""
+        err = self._ct.create_string_buffer(512)
+        if self._lib.afirt_rowsum_exchange_status(self._ptr, err, len(err)):
+            raise RuntimeError(err.value.decode())
+
+    def close(self) -> None:
+        if self._ptr:
+            self._lib.afirt_rowsum_exchange_destroy(self._ptr)
+            self._ptr = self._ct.c_void_p()

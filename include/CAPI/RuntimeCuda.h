@@ -62,6 +62,39 @@ int afirt_bcast_add_rowsum_no_alloc(int device_id, int elem_type, const void *a,
                                     int64_t rows, int64_t cols, int split_cols, void *cuda_stream,
                                     char *err_buf, size_t err_len);
 
+/* No counterpart in the reference (it runs on one device).  The row reduction with its REDUCED axis sharded
+ * over the GPUs of one node: rank r holds the column slice b_r [rows, cols_r] and every rank wants
+ *     out[m] = sum over ranks r of sum_n (a[m] + b_r[m, n]).
+ * One kernel per rank does the local reduction and the exchange: each row's partial sum is stored straight
+ * into every rank's mailbox over NVLink (peer-mapped memory), the last CTA to finish publishes a flag, waits
+ * for the other ranks' flags (2 s at most) and adds the partial sums in rank order, so every rank ends with
+ * the same bits.  No library collective is involved.
+ *
+ *   create   allocates this rank's mailbox on device_id (2 x world_size x max_rows floats plus flags) and
+ *            writes AFIRT_EXCHANGE_HANDLE_BYTES bytes describing it to out_handle;
+ *   connect  takes all ranks' handles in rank order (world_size x AFIRT_EXCHANGE_HANDLE_BYTES bytes, gathered
+ *            by the caller over any transport) and maps the peers' mailboxes: CUDA IPC between processes,
+ *            peer access inside one process;
+ *   the reduction call enqueues the kernel on cuda_stream and returns.  a [rows], b [rows, cols] with
+ *            b_row_stride elements between rows, out [rows] are DEVICE pointers of elem_type (0 f32, 1 f16,
+ *            2 bf16).  It is collective: every rank makes the same sequence of calls with the same rows, and
+ *            one rank's calls are ordered on one stream.  world_size 1 is allowed (a mailbox to itself);
+ *   status   after the stream has been synchronised: 0, or 1 with a message when a wait ran out (the
+ *            mailbox is then reset and can be used again once every rank has seen the failure);
+ *   destroy  unmaps and frees; the caller makes sure no peer is still sending (a barrier).
+ * Every rank needs its own GPU: ranks that wait for one another must never share a device. */
+typedef struct AfirtRowsumExchange_s *AfirtRowsumExchange;
+#define AFIRT_EXCHANGE_HANDLE_BYTES 96
+#define AFIRT_EXCHANGE_MAX_RANKS 8
+int afirt_rowsum_exchange_create(int device_id, int rank, int world_size, int64_t max_rows,
+                                 AfirtRowsumExchange *out_exchange, uint8_t *out_handle, char *err_buf, size_t err_len);
+int afirt_rowsum_exchange_connect(AfirtRowsumExchange exchange, const uint8_t *all_handles, char *err_buf, size_t err_len);
+int afirt_bcast_add_rowsum_exchange(AfirtRowsumExchange exchange, int elem_type, const void *a, const void *b, void *out,
+                                    int64_t rows, int64_t cols, int64_t b_row_stride, void *cuda_stream,
+                                    char *err_buf, size_t err_len);
+int afirt_rowsum_exchange_status(AfirtRowsumExchange exchange, char *err_buf, size_t err_len);
+void afirt_rowsum_exchange_destroy(AfirtRowsumExchange exchange);
+
 /* Library identification: "afir-b200 <version> sm_100a". */
 const char *afirt_runtime_version(void);
 
