@@ -95,15 +95,13 @@ int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *laun
 // into GPU p's mailbox (peer-mapped), at the place reserved for this rank.
 constexpr int kMaxExchangeRanks = 8;
 struct RowReduceExchange {
-  float *peerSlots[kMaxExchangeRanks];          // where this rank's partial sums go on rank p: [rows] f32
-  unsigned int *peerFlags[kMaxExchangeRanks];   // this rank's "sent" word on rank p (holds the last finished epoch)
-  const float *mySlots;                         // local mailbox of this epoch: [world, slotStride] f32, filled by the peers
-  unsigned int *myFlags;                        // local: [world] "sent" words written by the peers
-  unsigned int *doneCounter;                    // local: CTAs of this launch that have sent all their rows
-  unsigned int *status;                         // local: set to 1 when the wait for a peer ran out
-  int world;                                    // 0 = no exchange
-  unsigned int epoch;                           // 1, 2, ... identical on every rank for the same call
-  long long slotStride;                         // floats between two ranks' slots
+  unsigned long long *peerEntries[kMaxExchangeRanks];  // where this rank's entries go on rank p: [rows] x {f32 sum, epoch}
+  const unsigned long long *myEntries;                 // local mailbox of this epoch: [world, slotStride] entries, filled by all ranks
+  unsigned int *doneCounter;                           // local: CTAs of this launch that have sent all their rows
+  unsigned int *status;                                // local: set to 1 when the wait for a rank ran out
+  int world;                                           // 0 = no exchange
+  unsigned int epoch;                                  // 1, 2, ... identical on every rank for the same call, never 0
+  long long slotStride;                                // entries between two ranks' slots
 };
 
 struct RowReduceLaunch {
@@ -123,8 +121,8 @@ struct RowReduceLaunch {
   int streamChunkBytes;  // staged variant: bytes per stage (0 = default)
   int forcePlainLoads;  // 1 = never use the bulk-copy staged variant (tuning / comparison)
   // Not null: the per-row sums are partial (this GPU holds a column slice).  The kernel stores them as f32 into
-  // every rank's mailbox instead of `out`, and the last CTA to finish waits (2 s at most) for the other ranks'
-  // partial sums and writes out[m] = their sum in rank order.  Column slicing (splitCols) is not combined with it.
+  // every rank's mailbox instead of `out`, waits (2 s at most) for the other ranks' partial sums and writes
+  // out[m] = their sum in rank order.  Column slicing (splitCols) is not combined with it.
   const RowReduceExchange *exchange = nullptr;
 };
 size_t rowReduceWorkspaceBytes(int64_t rows, int splitCols);

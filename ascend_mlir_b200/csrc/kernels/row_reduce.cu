@@ -45,89 +45,99 @@ template <> __device__ __forceinline__ void storeSum<PackBF16>(void *out, long l
 }
 
 // ---- exchange of partial sums between GPUs (the reduced axis is sharded) ----------------------------------
-// Each row's partial sum is stored straight into every rank's mailbox (plain stores over NVLink; the own
-// mailbox is an ordinary local store).  When a CTA has sent all its rows it fences and counts itself done;
-// the CTA that completes the count publishes "epoch" in this rank's flag word on every rank, waits until
-// every rank's flag word here has reached the epoch, and adds the world's partial sums in rank order, so
-// all ranks produce the same bits.  The wait is bounded: after 2 s the status word is set and out stays
-// unwritten; the context remains usable.
+// A mailbox entry is eight bytes, {f32 partial sum, epoch}, written with ONE 8-byte store, so value and "it has
+// arrived" travel together and a reader never sees half an entry: no flags, no fences.  Each row's partial sum
+// is stored into every rank's mailbox (plain stores over NVLink; the own mailbox is a local store).  A reader
+// polls an entry until its epoch is the call's, then adds the world's partial sums in rank order, so all ranks
+// produce the same bits.  Who reads: in the persistent staged kernel the warp that sent a row reads that row
+// one row later (the NVLink latency hides behind the next row's stream; every rank walks its rows in the same
+// order and always sends before it reads, so no rank waits for something that itself waits); in the plain
+// kernel, whose CTAs need not all be resident, the last CTA to finish reads all rows.  Every wait is bounded:
+// after 2 s the status word is set, the remaining rows stay unwritten and the context remains usable.
 constexpr unsigned long long kExchangeWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ void sendPartial(const RowReduceExchange &x, long long row, float v) {
-  for (int p = 0; p < x.world; ++p) x.peerSlots[p][row] = v;
+  const unsigned long long entry = (static_cast<unsigned long long>(x.epoch) << 32) | __float_as_uint(v);
+  for (int p = 0; p < x.world; ++p)
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(x.peerEntries[p] + row), "l"(entry) : "memory");
 }
 
+__device__ __forceinline__ unsigned long long peekEntry(const unsigned long long *entry) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(entry) : "memory");
+  return w;
+}
+
+// Polls until the entry carries `epoch`; false when the time ran out.
+__device__ __forceinline__ bool awaitEntry(const unsigned long long *entry, unsigned int epoch, unsigned long long &w) {
+  unsigned long long t0 = 0;
+  unsigned int spins = 0;
+  while (true) {
+    w = peekEntry(entry);
+    if (static_cast<unsigned int>(w >> 32) == epoch) return true;
+    if (++spins > 1000u) __nanosleep(100);
+    if ((spins & 63u) == 0) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kExchangeWaitLimitNs) return false;
+    }
+  }
+}
+
+// One warp finishes one row: lane p fetches rank p's partial sum, all lanes add them in rank order.
+template <class P> __device__ __forceinline__ bool finishRowByWarp(const RowReduceExchange &x, void *out, long long row, int lane) {
+  unsigned long long w = 0;
+  bool ok = true;
+  if (lane < x.world) ok = awaitEntry(x.myEntries + lane * x.slotStride + row, x.epoch, w);
+  ok = __all_sync(0xffffffffu, ok) != 0;
+  float t = 0.f;
+  for (int p = 0; p < x.world; ++p) t += __uint_as_float(__shfl_sync(0xffffffffu, static_cast<unsigned int>(w), p));
+  if (ok && lane == 0) storeSum<P>(out, row, t);
+  return ok;
+}
+
+// Plain kernel: the last CTA to finish reads every row.
 template <class P> __device__ __noinline__ void exchangeTail(const RowReduceExchange &x, void *out, long long rows) {
   __shared__ int lastCta;
-  __syncthreads();  // every thread's mailbox stores are ordered before thread 0's fence
+  __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();  // ... which makes them visible system-wide before this CTA is counted
+    __threadfence();
     lastCta = atomicAdd(x.doneCounter, 1u) == gridDim.x - 1u;
   }
   __syncthreads();
   if (!lastCta) return;
-  // every CTA of this launch has sent and fenced its rows
-  bool ok = true;
-  if (threadIdx.x < static_cast<unsigned int>(x.world)) {
-    // release: ordered after everything the counter made visible to this CTA (all CTAs' fenced stores)
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(x.peerFlags[threadIdx.x]), "r"(x.epoch) : "memory");
-    const unsigned int *flag = x.myFlags + threadIdx.x;
-    unsigned long long t0 = 0;
-    unsigned int spins = 0;
-    while (true) {
-      unsigned int seen;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-      if (static_cast<int>(seen - x.epoch) >= 0) break;
-      if (++spins > 2000u) __nanosleep(100);  // the ranks run in step: the flag is normally there within microseconds
-      if ((spins & 63u) == 0) {
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > kExchangeWaitLimitNs) { ok = false; break; }
-      }
-    }
-  }
-  ok = __syncthreads_and(ok) != 0;  // the acquiring loads above order the slot reads of the whole CTA behind them
   if (threadIdx.x == 0) *x.doneCounter = 0;  // the next launch on this stream counts from zero
-  if (!ok) {
-    if (threadIdx.x == 0) atomicExch(x.status, 1u);
-    return;
-  }
-  // out[m] = sum over ranks in rank order; four rows per 16-byte load, four such loads per rank in flight and
-  // no store between them (slotStride is a multiple of four floats and the mailbox is 512-byte aligned)
-  const long long quads = rows >> 2;
-  for (long long q0 = threadIdx.x; q0 < quads; q0 += 4ll * blockDim.x) {
-    float4 t[4];
+  bool ok = true;
+  constexpr int kRowsInFlight = 4;
+  for (long long r0 = threadIdx.x; r0 < rows && ok; r0 += static_cast<long long>(kRowsInFlight) * blockDim.x) {
+    float t[kRowsInFlight];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 2
-    for (int p = 0; p < x.world; ++p) {
-      const float4 *slot = reinterpret_cast<const float4 *>(x.mySlots + p * x.slotStride);
-      float4 v[4];
+    for (int u = 0; u < kRowsInFlight; ++u) t[u] = 0.f;
+    for (int p = 0; p < x.world && ok; ++p) {
+      const unsigned long long *slot = x.myEntries + p * x.slotStride;
+      unsigned long long w[kRowsInFlight];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const long long q = q0 + static_cast<long long>(u) * blockDim.x;
-        v[u] = q < quads ? __ldcg(slot + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int u = 0; u < kRowsInFlight; ++u) {  // all four loads leave before the first is looked at
+        const long long row = r0 + static_cast<long long>(u) * blockDim.x;
+        w[u] = row < rows ? peekEntry(slot + row) : 0ull;
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) { t[u].x += v[u].x; t[u].y += v[u].y; t[u].z += v[u].z; t[u].w += v[u].w; }
+      for (int u = 0; u < kRowsInFlight; ++u) {
+        const long long row = r0 + static_cast<long long>(u) * blockDim.x;
+        if (row < rows && static_cast<unsigned int>(w[u] >> 32) != x.epoch) ok = ok && awaitEntry(slot + row, x.epoch, w[u]);
+        t[u] += __uint_as_float(static_cast<unsigned int>(w[u]));
+      }
     }
+    if (ok) {
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const long long q = q0 + static_cast<long long>(u) * blockDim.x;
-      if (q < quads) {
-        storeSum<P>(out, 4 * q, t[u].x);
-        storeSum<P>(out, 4 * q + 1, t[u].y);
-        storeSum<P>(out, 4 * q + 2, t[u].z);
-        storeSum<P>(out, 4 * q + 3, t[u].w);
+      for (int u = 0; u < kRowsInFlight; ++u) {
+        const long long row = r0 + static_cast<long long>(u) * blockDim.x;
+        if (row < rows) storeSum<P>(out, row, t[u]);
       }
     }
   }
-  for (long long row = 4 * quads + threadIdx.x; row < rows; row += blockDim.x) {
-    float t = 0.f;
-    for (int p = 0; p < x.world; ++p) t += __ldcg(x.mySlots + p * x.slotStride + row);
-    storeSum<P>(out, row, t);
-  }
+  if (!ok) atomicExch(x.status, 1u);
 }
 
 template <class P, int BODY, bool VECTOR, bool XCHG = false>
@@ -322,8 +332,9 @@ __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_con
   unsigned int phase = 0;
   unsigned int bcastNow[NV], bcastNext[NV];
   loadBcast(firstRow, bcastNow);
-  bool alive = true;
-  for (long long row = firstRow; row < prm.rows && alive; row += totalWarps) {
+  long long sentRow = -1;  // exchange: the row this warp has sent but not yet finished
+  bool peersAnswer = true;  // exchange: false once a wait for another rank ran out (the warp then only drains its stream)
+  for (long long row = firstRow; row < prm.rows; row += totalWarps) {
     loadBcast(row + totalWarps, bcastNext);  // one row ahead: its latency hides behind this row's stream
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (unsigned int chunk = 0; chunk < chunksPerRow; ++chunk) {
@@ -341,15 +352,9 @@ __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_con
           if (t0 == 0) t0 = now;
           else if (now - t0 > kStreamWaitLimitNs) {
             atomicCAS(&g_rowReduceStatus, 0u, 1u);
-            if (!XCHG) return;  // nothing of this warp's is in flight on a barrier that never completed beyond this ring
-            alive = false;  // with an exchange the warp still has to reach the CTA's barriers below
-            break;
+            return;  // nothing of this warp's is in flight on a barrier that never completed beyond this ring
           }
         }
-      }
-      if constexpr (XCHG) {
-        alive = __all_sync(0xffffffffu, alive) != 0;  // leave the row loop as a whole warp
-        if (!alive) break;
       }
       const unsigned int bytes = min(kStreamChunkBytes, prm.rowBytes - chunk * kStreamChunkBytes);
       const unsigned int nvec = bytes >> 4;
@@ -380,15 +385,20 @@ __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_con
     float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
-    if (XCHG && !alive) break;
-    if (lane == 0) {
-      if (XCHG) sendPartial(prm.xchg, row, sum);
-      else storeSum<P>(prm.out, row, sum);
+    if constexpr (XCHG) {
+      if (lane == 0) sendPartial(prm.xchg, row, sum);
+      if (sentRow >= 0 && peersAnswer) peersAnswer = finishRowByWarp<P>(prm.xchg, prm.out, sentRow, lane);
+      sentRow = row;
+    } else {
+      if (lane == 0) storeSum<P>(prm.out, row, sum);
     }
 #pragma unroll
     for (int k = 0; k < NV; ++k) bcastNow[k] = bcastNext[k];
   }
-  if constexpr (XCHG) exchangeTail<P>(prm.xchg, prm.out, prm.rows);
+  if constexpr (XCHG) {
+    if (sentRow >= 0 && peersAnswer) peersAnswer = finishRowByWarp<P>(prm.xchg, prm.out, sentRow, lane);
+    if (!peersAnswer && lane == 0) atomicExch(prm.xchg.status, 1u);
+  }
 }
 
 template <class P>
@@ -545,6 +555,7 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
       const int64_t rowGroups = (l.rows + kStreamWarps - 1) / kStreamWarps;
       int64_t sgrid = l.gridBlocks > 0 ? l.gridBlocks : sms;
       sgrid = std::max<int64_t>(1, std::min<int64_t>(sgrid, rowGroups));
+      if (l.exchange) sgrid = std::min<int64_t>(sgrid, sms);  // warps that wait for other ranks: one CTA per SM, all resident
       sfn<<<static_cast<unsigned int>(sgrid), kStreamWarps * 32, smem, stream>>>(sp);
       if (launched) *launched = 1;
       return cudaGetLastError();

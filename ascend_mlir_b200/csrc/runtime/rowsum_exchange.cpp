@@ -3,11 +3,12 @@
 // The device side is exchangeTail() in kernels/row_reduce.cu.
 //
 // Mailbox layout (one cudaMalloc, so that one IPC handle covers it):
-//   [0, 32)      flags[8]   u32, flags[r] = last epoch rank r finished sending
 //   [256, 260)   CTAs of the running launch that are done (local use)
 //   [260, 264)   status word (local use)
-//   [512, ...)   slots[2][world][maxRows rounded up to 4] f32; the epoch's parity picks the half, so a rank that is already
-//                sending epoch e+1 cannot overwrite sums a slower rank is still adding for epoch e
+//   [512, ...)   entries[2][world][maxRows], eight bytes each: {f32 partial sum, epoch}.  The epoch's parity picks
+//                the half, so a rank that is already sending call e+1 cannot overwrite an entry a slower rank has
+//                not yet read for call e; it can send call e+2 only after it finished e+1, which needs every
+//                rank's e+1 entries, which they send after they finished reading e.
 #include "CAPI/RuntimeCuda.h"
 #include "kernels/kernels.h"
 
@@ -19,7 +20,7 @@
 
 namespace {
 
-constexpr size_t kFlagsOffset = 0, kDoneOffset = 256, kStatusOffset = 260, kSlotsOffset = 512;
+constexpr size_t kDoneOffset = 256, kStatusOffset = 260, kSlotsOffset = 512;
 
 struct Handle {  // AFIRT_EXCHANGE_HANDLE_BYTES
   cudaIpcMemHandle_t ipc;  // 64 bytes
@@ -47,8 +48,8 @@ struct AfirtRowsumExchange_s {
   bool viaIpc[AFIRT_EXCHANGE_MAX_RANKS] = {false};
   bool connected = false;
   unsigned int epoch = 0;
-  int64_t slotStride() const { return (maxRows + 3) / 4 * 4; }  // floats; keeps every rank's slot 16-byte aligned
-  size_t slotsBytesPerHalf() const { return static_cast<size_t>(world) * static_cast<size_t>(slotStride()) * sizeof(float); }
+  int64_t slotStride() const { return maxRows; }  // entries
+  size_t slotsBytesPerHalf() const { return static_cast<size_t>(world) * static_cast<size_t>(slotStride()) * sizeof(unsigned long long); }
 };
 
 #define AFIRT_EXPORT extern "C" __attribute__((visibility("default")))
@@ -152,15 +153,13 @@ AFIRT_EXPORT int afirt_bcast_add_rowsum_exchange(AfirtRowsumExchange x, int elem
   cudaError_t e = cudaSetDevice(x->device);
   if (e != cudaSuccess) { fail(err_buf, err_len, "cudaSetDevice", e); return 1; }
 
-  const unsigned int epoch = x->epoch + 1;
+  unsigned int epoch = x->epoch + 1;
+  if (epoch == 0) epoch = 2;  // 0 is what an untouched entry holds; 2 keeps the alternation of the halves
   const size_t half = (epoch & 1u) * x->slotsBytesPerHalf();
   RowReduceExchange rx = {};
-  for (int p = 0; p < x->world; ++p) {
-    rx.peerSlots[p] = reinterpret_cast<float *>(x->peer[p] + kSlotsOffset + half) + static_cast<size_t>(x->rank) * x->slotStride();
-    rx.peerFlags[p] = reinterpret_cast<unsigned int *>(x->peer[p] + kFlagsOffset) + x->rank;
-  }
-  rx.mySlots = reinterpret_cast<const float *>(x->mailbox + kSlotsOffset + half);
-  rx.myFlags = reinterpret_cast<unsigned int *>(x->mailbox + kFlagsOffset);
+  for (int p = 0; p < x->world; ++p)
+    rx.peerEntries[p] = reinterpret_cast<unsigned long long *>(x->peer[p] + kSlotsOffset + half) + static_cast<size_t>(x->rank) * x->slotStride();
+  rx.myEntries = reinterpret_cast<const unsigned long long *>(x->mailbox + kSlotsOffset + half);
   rx.doneCounter = reinterpret_cast<unsigned int *>(x->mailbox + kDoneOffset);
   rx.status = reinterpret_cast<unsigned int *>(x->mailbox + kStatusOffset);
   rx.world = x->world;

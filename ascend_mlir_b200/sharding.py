@@ -80,9 +80,10 @@ def allreduce_partial_rowsums(partial):
 class RowsumExchange:
     """The same exchange inside the reduction kernel: afirt_rowsum_exchange_* of the C-ABI library.
 
-    Every rank reduces its column slice and stores the partial row sums straight into all ranks' mailboxes over
-    NVLink; the kernel's last CTA waits (2 s at most) for the other ranks and adds the partial sums in rank order.
-    One launch per rank, no library collective, identical bits on every rank.  `connect()` gathers the mailbox
+    Every rank reduces its column slice and stores each partial row sum straight into all ranks' mailboxes over
+    NVLink as an 8-byte {sum, call number} entry; the warp that sent a row reads the other ranks' entries for it one
+    row later (waiting 2 s at most) and adds them in rank order.  One launch per rank, no library collective,
+    identical bits on every rank.  `connect()` gathers the mailbox
     handles over the default process group (any backend; objects, not tensors); `connect_handles()` takes them
     from elsewhere.  Every rank needs a GPU of its own."""
 

@@ -66,11 +66,13 @@ int afirt_bcast_add_rowsum_no_alloc(int device_id, int elem_type, const void *a,
  * over the GPUs of one node: rank r holds the column slice b_r [rows, cols_r] and every rank wants
  *     out[m] = sum over ranks r of sum_n (a[m] + b_r[m, n]).
  * One kernel per rank does the local reduction and the exchange: each row's partial sum is stored straight
- * into every rank's mailbox over NVLink (peer-mapped memory), the last CTA to finish publishes a flag, waits
- * for the other ranks' flags (2 s at most) and adds the partial sums in rank order, so every rank ends with
- * the same bits.  No library collective is involved.
+ * into every rank's mailbox over NVLink (peer-mapped memory) as one 8-byte entry {f32 sum, call number}, so
+ * the value and the fact that it has arrived travel in the same store; the warp that sent a row picks up the
+ * other ranks' entries for it one row later (2 s at most) and adds them in rank order, so every rank ends with
+ * the same bits.  No flags, no fences, no library collective.  (Few or short rows take the kernel without
+ * the staged stream; there the last CTA to finish reads all rows.)
  *
- *   create   allocates this rank's mailbox on device_id (2 x world_size x max_rows floats plus flags) and
+ *   create   allocates this rank's mailbox on device_id (2 x world_size x max_rows entries of 8 bytes) and
  *            writes AFIRT_EXCHANGE_HANDLE_BYTES bytes describing it to out_handle;
  *   connect  takes all ranks' handles in rank order (world_size x AFIRT_EXCHANGE_HANDLE_BYTES bytes, gathered
  *            by the caller over any transport) and maps the peers' mailboxes: CUDA IPC between processes,
