@@ -91,6 +91,21 @@ for out, (b, xs, lo, hi, b_d, x_d) in zip(outs, wants):
     _, s64, abs64 = oracle.bcast_add_rowsum_f32(b, xs, with_bounds=True)
     assert np.all(np.abs(out.cpu().numpy() - s64) <= 1e-5 * abs64)
 dist.barrier()
+# a wait that runs out: rank 0 makes one more call, nobody answers; after 2 s the kernel gives up, the status
+# says so and the context is still usable
+if rank == 0:
+    out = torch.full((2048,), float("nan"), device="cuda")
+    x.bcast_add_rowsum(b_d.data_ptr(), x_d.data_ptr(), out.data_ptr(), 2048, 4096, 8192)
+    torch.cuda.synchronize()
+    try:
+        x.check()
+        raise SystemExit("the exchange did not report the missing rank")
+    except RuntimeError as e:
+        assert "gave up waiting" in str(e), str(e)
+    assert bool(torch.isnan(out).all())             # no row was finished
+    assert float(torch.ones(4, device="cuda").sum().item()) == 4.0  # the device still computes
+    x.check()                                       # and the status was cleared by the report
+dist.barrier()
 x.close()
 dist.destroy_process_group()
 print(f"rank {rank} ok", flush=True)
