@@ -375,14 +375,46 @@ int deviceSmCount(int device) {
 
 const char *cudaErrorText(int code) { return cudaGetErrorString(static_cast<cudaError_t>(code)); }
 
-int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *launched) {
+int launchElementwise(const ElementwiseLaunch &given, cudaStream_t stream, int *launched) {
   if (launched) *launched = 0;
-  const int64_t total = l.dims[0] * l.dims[1] * l.dims[2];
+  const int64_t total = given.dims[0] * given.dims[1] * given.dims[2];
   if (total == 0) return cudaSuccess;
-  if (l.numViews < 1 || l.numViews > kMaxViews || l.outStride[2] != 1) return cudaErrorInvalidValue;
+  if (given.numViews < 1 || given.numViews > kMaxViews || given.outStride[2] != 1) return cudaErrorInvalidValue;
+
+  // The block variant wants a transposed view contiguous along the MIDDLE dim.  All three dims are parallel, so
+  // when such a view is contiguous along the outer dim instead (out[i,j,k] = in[k,j,i]) the two outer dims
+  // trade places: same elements, same addresses, another walking order.
+  ElementwiseLaunch l = given;
+  if (!l.forceElementAccess) {
+    bool swapHelps = false, swapHurts = false;
+    for (int k = 0; k < l.numViews; ++k) {
+      const ViewAccess &v = l.views[k];
+      if (v.stride[2] == 0 || v.stride[2] == 1) continue;
+      if (v.stride[1] != 1 && v.stride[0] == 1 && l.dims[0] > 1) swapHelps = true;
+      if (v.stride[1] == 1) swapHurts = true;
+    }
+    if (swapHelps && !swapHurts) {
+      std::swap(l.dims[0], l.dims[1]);
+      std::swap(l.outStride[0], l.outStride[1]);
+      for (int k = 0; k < l.numViews; ++k) std::swap(l.views[k].stride[0], l.views[k].stride[1]);
+    }
+  }
 
   const int eb = elemBytes(l.elemType);
   const int vecElems = 16 / eb;
+  // A bare copy of one transposed 2-D view is a transpose: out[r, c] = in[c, r] with `in` c-major.
+  if (!l.forceElementAccess && l.numViews == 1 && l.dims[0] == 1 && l.views[0].stride[1] == 1 && l.views[0].stride[2] > 1 &&
+      (eb == 2 || eb == 4) && matchBody(l.body, 1) == kBodyCopy) {
+    TransposeLaunch t = {};
+    t.elemBytes = eb;
+    t.rows = l.dims[2];  // shape of the input as stored: [dims[2], dims[1]]
+    t.cols = l.dims[1];
+    t.in = l.views[0].base;
+    t.inRowStride = l.views[0].stride[2];
+    t.out = l.outBase;
+    t.outRowStride = l.outStride[1];
+    return launchTranspose(t, stream, launched);
+  }
   {  // a transposed operand: the block variant keeps every access 16 bytes wide
     cudaError_t berr = cudaSuccess;
     if (!l.forceElementAccess && tryLaunchBlocks(l, stream, berr)) {

@@ -174,7 +174,7 @@ struct TransposeLaunch {
   int64_t outRowStride;
   int warpRows = 0;         // warps of a CTA stacked along the input rows: 1, 2, 4 or 8 (0 = default)
   int ctasPerSm = 0;        // persistent grid of SMs x this many CTAs (0 = one CTA per tile)
-  int diagonalOrder = 0;    // 1: tiles in diagonal order instead of row-major order
+  int diagonalOrder = 0;    // tile order: 0 row-major (column-major when the input has few rows), 1 diagonal, 2 column-major
   int variant = 0;          // 0: whole lines stored, 1: same with 2 blocks per thread, 2: whole lines loaded, 3: same, 2 blocks
   int forceTileKernel = 0;  // 1: use the shared-memory tile kernel even when the operands are aligned
 };

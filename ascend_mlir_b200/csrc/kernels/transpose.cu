@@ -61,7 +61,7 @@ struct TrParams {
   long long inStrideBytes, outStrideBytes;
   unsigned int tilesX, tilesY;
   unsigned long long numTiles;
-  int diagonalOrder;  // 0: row-major tile order, 1: diagonal tile order
+  int diagonalOrder;  // 0: row-major tile order, 1: diagonal tile order, 2: column-major tile order
 };
 
 // WR warps of the CTA along the input rows, 8 / WR along the input columns.  A warp covers 8 x 4 blocks with
@@ -79,10 +79,15 @@ __global__ void __launch_bounds__(256) transposeBlocksKernel(const __grid_consta
   const int li = LOADFULL ? (lane >> 3) : (lane & 7);  // block row of the thread's first block inside the warp tile
   const int lj = LOADFULL ? (lane & 7) : (lane >> 3);
   for (unsigned long long t = blockIdx.x; t < p.numTiles; t += gridDim.x) {
-    const unsigned int tx = static_cast<unsigned int>(t % p.tilesX);
+    unsigned int tx = static_cast<unsigned int>(t % p.tilesX);
     unsigned int ty = static_cast<unsigned int>(t / p.tilesX);
     // Optional diagonal order: tiles running at the same time then differ in tile row and tile column.
-    if (p.diagonalOrder) ty = (ty + tx) % p.tilesY;
+    if (p.diagonalOrder == 1) ty = (ty + tx) % p.tilesY;
+    // Column-major order: neighbouring CTAs complete the same (short) output rows together.
+    if (p.diagonalOrder == 2) {
+      ty = static_cast<unsigned int>(t % p.tilesY);
+      tx = static_cast<unsigned int>(t / p.tilesY);
+    }
     const long long rw = static_cast<long long>(ty) * kTileRows + (warp / WC) * kWarpRows;
     const long long cw = static_cast<long long>(tx) * kTileCols + (warp % WC) * kWarpCols;
     long long r0[NB], c0[NB];
@@ -180,7 +185,11 @@ int launchTranspose(const TransposeLaunch &l, cudaStream_t stream, int *launched
     p.outStrideBytes = l.outRowStride * l.elemBytes;
     const int ctasPerSm = l.ctasPerSm > 0 ? l.ctasPerSm : 0;
     const int warpRows = l.warpRows > 0 ? l.warpRows : 2;
-    p.diagonalOrder = l.diagonalOrder ? 1 : 0;
+    p.diagonalOrder = l.diagonalOrder == 2 ? 2 : l.diagonalOrder ? 1 : 0;
+    // Few input rows (a wide-and-low input, a tall-and-thin output whose rows are at most 4 KB): in row-major tile
+    // order each output row would be finished by CTAs that run far apart in time, so the default walks the input
+    // rows fastest there.
+    if (l.diagonalOrder == 0 && l.rows * l.elemBytes <= 4096 && l.cols > l.rows) p.diagonalOrder = 2;
     if (l.elemBytes == 2) launchBlocks<2>(p, l.variant, warpRows, l.rows, l.cols, ctasPerSm, smCountOf(), stream);
     else launchBlocks<4>(p, l.variant, warpRows, l.rows, l.cols, ctasPerSm, smCountOf(), stream);
     if (launched) *launched = 1;

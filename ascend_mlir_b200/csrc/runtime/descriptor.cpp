@@ -173,7 +173,7 @@ Status parseBody(const json::Value *v, int numViews, kernels::BodyProgram &out) 
 Status parseGroup(const json::Value &g, const LaunchDescriptor &d, GroupSpec &out) {
   const int numArgs = d.numInputs + d.numOutputs;
   if (Status s = parseDimList(g.find("domain"), out.domain, "domain"); !s) return s;
-  if (out.domain.empty() || out.domain.size() > 4) return Status::error("'domain' must have 1 to 4 dims");
+  if (out.domain.empty() || out.domain.size() > 8) return Status::error("'domain' must have 1 to 8 dims");
   const json::Value *loads = g.find("loads");
   if (!loads || !loads->isArray() || loads->asArray().empty()) return Status::error("'loads' must be a non-empty array");
   if (loads->asArray().size() > static_cast<size_t>(kernels::kMaxViews))

@@ -138,7 +138,26 @@ Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, con
   for (auto &v : loads) all.push_back(&v);
   all.push_back(&store);
   collapseDomain(domain, all);
-  if (domain.size() > 3) return Status::error("iteration space does not collapse to three dims");
+  // The kernels walk three dims.  What is left above them after collapsing (a permutation of rank four or more
+  // that no merge simplifies) is walked here, one launch per index of those outer dims.
+  constexpr int64_t kMaxOuterLaunches = 4096;
+  std::vector<int64_t> outer;
+  std::vector<std::vector<int64_t>> outerStride(all.size());
+  while (domain.size() > 3) {
+    outer.push_back(domain.front());
+    domain.erase(domain.begin());
+    for (size_t i = 0; i < all.size(); ++i) {
+      outerStride[i].push_back(all[i]->stride.front());
+      all[i]->stride.erase(all[i]->stride.begin());
+    }
+  }
+  int64_t outerCount = 1;
+  for (int64_t e : outer) {
+    outerCount *= e;
+    if (outerCount > kMaxOuterLaunches)
+      return Status::error("iteration space keeps more than three dims after collapsing and the outer ones need more than " +
+                           std::to_string(kMaxOuterLaunches) + " launches");
+  }
   while (domain.size() < 3) {
     domain.insert(domain.begin(), 1);
     for (auto *v : all) v->stride.insert(v->stride.begin(), 0);
@@ -150,21 +169,34 @@ Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, con
   for (int i = 0; i < 3; ++i) l.dims[i] = domain[i];
   l.numViews = static_cast<int>(loads.size());
   for (size_t i = 0; i < loads.size(); ++i) {
-    l.views[i].base = argAt(args, loads[i]);
     for (int k = 0; k < 3; ++k) l.views[i].stride[k] = loads[i].stride[k];
     if (domain[2] == 1) l.views[i].stride[2] = 1;
   }
-  l.outBase = argAt(args, store);
   for (int k = 0; k < 3; ++k) l.outStride[k] = store.stride[k];
   l.outStride[2] = 1;
   l.body = g.body;
   l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
   l.unroll = static_cast<int>(optionalField(d.unrollField, tiling));
   l.gridBlocks = args.blockDim;
-  int n = 0;
-  Status s = cudaStatus(kernels::launchElementwise(l, args.stream, &n), "elementwise launch");
-  info.kernelsLaunched += n;
-  return s;
+  std::vector<int64_t> index(outer.size(), 0);
+  for (int64_t launch = 0; launch < outerCount; ++launch) {
+    auto shifted = [&](size_t view, const ResolvedView &v) {
+      int64_t elems = 0;
+      for (size_t j = 0; j < outer.size(); ++j) elems += index[j] * outerStride[view][j];
+      return static_cast<char *>(argAt(args, v)) + elems * v.elemBytes;
+    };
+    for (size_t i = 0; i < loads.size(); ++i) l.views[i].base = shifted(i, loads[i]);
+    l.outBase = shifted(loads.size(), store);
+    int n = 0;
+    Status s = cudaStatus(kernels::launchElementwise(l, args.stream, &n), "elementwise launch");
+    info.kernelsLaunched += n;
+    if (!s) return s;
+    for (int j = static_cast<int>(outer.size()) - 1; j >= 0; --j) {
+      if (++index[j] < outer[j]) break;
+      index[j] = 0;
+    }
+  }
+  return Status::success();
 }
 
 Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
@@ -335,7 +367,7 @@ Status launchTransposeGroup(const LaunchDescriptor &d, const GroupSpec &g, const
   l.warpRows = static_cast<int>(optionalField(d.warpRowsField, tiling));
   l.ctasPerSm = static_cast<int>(optionalField(d.ctasPerSmField, tiling));
   l.forceTileKernel = optionalField(d.tileKernelField, tiling) != 0;
-  l.diagonalOrder = optionalField(d.tileOrderField, tiling) != 0;
+  l.diagonalOrder = static_cast<int>(optionalField(d.tileOrderField, tiling));  // 0, 1 or 2
   l.variant = static_cast<int>(optionalField(d.variantField, tiling));
   int n = 0;
   Status s = cudaStatus(kernels::launchTranspose(l, args.stream, &n), "transpose launch");

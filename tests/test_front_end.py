@@ -267,3 +267,21 @@ def test_mutated_inputs_are_rejected_or_accepted_but_never_crash_the_tools():
             if t.returncode not in (0, 1) or (t.returncode == 1 and "error" not in t.stderr.lower()):
                 crashes.append((trial, "translate", t.returncode, t.stderr[-200:]))
     assert not crashes, crashes[:5]
+
+
+def test_permutation_of_rank_five_is_an_elementwise_group_with_a_permuted_view(tmp_path):
+    """The reference takes a bare transpose generic of any rank (ComputeConversion.cpp:775-826); only rank two has
+    a kernel class of its own here, the others read the input through its permuted view."""
+    from test_permutations_gpu import permutation_mlir
+    from ascend_mlir_b200.runtime import compile_kernel
+    perm, out_shape = (4, 2, 0, 3, 1), [2, 3, 4, 5, 8]
+    in_shape, text = permutation_mlir(perm, out_shape, "f16")
+    src = tmp_path / "p.mlir"
+    src.write_text(text)
+    got = translate(src)
+    assert got["kernel_class"] == "elementwise" and body_of(got) == []
+    assert got["domain"] == out_shape and got["store"]["map"] == [0, 1, 2, 3, 4]
+    assert views_of(got) == [(0, list(perm), None)] and got["loads"][0]["shape"] == in_shape
+    desc = tmp_path / "p.cuda.json"
+    desc.write_text(json.dumps(got))
+    assert compile_kernel(desc, tmp_path / "artifact", "permute").exists()  # the descriptor parser takes up to eight dims

@@ -139,6 +139,8 @@ def test_transpose_2d_every_warp_arrangement(rt, dtype, warp_rows):
         assert out.tobytes() == want, (R, C, "blocks")
         out = run(rt, spec, [x], np.zeros((C, R), dtype), {"R": R, "C": C}, WARP_ROWS=warp_rows, TILE_ORDER=1)
         assert out.tobytes() == want, (R, C, "diagonal tile order")
+        out = run(rt, spec, [x], np.zeros((C, R), dtype), {"R": R, "C": C}, WARP_ROWS=warp_rows, TILE_ORDER=2)
+        assert out.tobytes() == want, (R, C, "column-major tile order")
         for variant in (1, 2, 3):
             out = run(rt, spec, [x], np.zeros((C, R), dtype), {"R": R, "C": C}, WARP_ROWS=warp_rows, VARIANT=variant)
             assert out.tobytes() == want, (R, C, "variant", variant)
