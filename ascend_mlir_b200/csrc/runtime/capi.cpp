@@ -15,6 +15,7 @@
 
 #include "execution/artifact_compiler.h"
 #include "runtime/executor.h"
+#include "runtime/rowsum_exchange.h"
 
 using namespace afir;
 
@@ -162,6 +163,28 @@ AFIR_EXPORT int afirt_executor_launch_device(AfirtExecutor executor, const uint8
     writeErr(err_buf, err_len, s.message());
     return 1;
   }
+  return 0;
+}
+
+AFIR_EXPORT int afirt_executor_launch_device_exchange(AfirtExecutor executor, const uint8_t *binary_data, size_t binary_len,
+                                                      const char *function_name, int num_inputs, const void **input_ptrs,
+                                                      const size_t *input_bytes, int num_outputs, void **output_ptrs,
+                                                      const size_t *output_bytes, const uint8_t *tiling_data, size_t tiling_len,
+                                                      int block_dim, uint32_t magic, void *workspace, size_t workspace_bytes,
+                                                      void *cuda_stream, AfirtRowsumExchange exchange, char *err_buf, size_t err_len) {
+  auto *ex = reinterpret_cast<CudaExecutor *>(executor);
+  if (!ex || !ex->initialized()) { writeErr(err_buf, err_len, "executor has not been initialized"); return 1; }
+  kernels::RowReduceExchange record;
+  int mailboxDevice = 0;
+  if (Status s = nextExchangeCall(exchange, record, mailboxDevice); !s) { writeErr(err_buf, err_len, s.message()); return 1; }
+  if (mailboxDevice != ex->device()) { writeErr(err_buf, err_len, "the exchange's mailbox is on another device than the executor"); return 1; }
+  RunRequest r = makeRequest(binary_data, binary_len, function_name, num_inputs, input_ptrs, input_bytes, num_outputs,
+                             output_ptrs, output_bytes, tiling_data, tiling_len, block_dim, magic);
+  if (Status s = ex->launchDevice(r, workspace, workspace_bytes, cuda_stream, &record); !s) {
+    writeErr(err_buf, err_len, s.message());
+    return 1;
+  }
+  commitExchangeCall(exchange, record);
   return 0;
 }
 

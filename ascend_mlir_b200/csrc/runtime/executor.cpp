@@ -391,7 +391,8 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
   return done ? guards : done;
 }
 
-Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream) {
+Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream,
+                                  const kernels::RowReduceExchange *exchange) {
   std::shared_ptr<const LaunchDescriptor> desc;
   std::map<std::string, int64_t> tiling;
   if (Status s = validate(req, desc, tiling); !s) return s;
@@ -402,6 +403,7 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   args.device = device_;
   args.stream = static_cast<cudaStream_t>(stream);
   args.blockDim = req.blockDim;
+  args.exchange = exchange;
   for (int i = 0; i < req.numInputs; ++i) {
     args.argPtrs.push_back(const_cast<void *>(req.inputPtrs[i]));
     args.argBytes.push_back(req.inputBytes[i]);

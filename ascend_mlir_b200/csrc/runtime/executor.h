@@ -50,7 +50,10 @@ public:
   // Host-pointer path: H2D, launch, D2H, synchronise, status checks.
   Status runHost(const RunRequest &req);
   // Device-pointer path: validates and enqueues the launch on `stream` and returns.
-  Status launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream);
+  // exchange: not null for a row-reduction group whose reduced axis is sharded over GPUs (the kernel then
+  // exchanges its partial sums through that mailbox record)
+  Status launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream,
+                      const kernels::RowReduceExchange *exchange = nullptr);
   // Waits for `stream` (null = the executor's own) and surfaces device-side status words.
   Status synchronize(void *stream);
 

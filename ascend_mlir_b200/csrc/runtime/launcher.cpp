@@ -248,6 +248,14 @@ Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const
   }
   int split = static_cast<int>(optionalField(d.splitColsField, tiling));
   if (split <= 0) split = kernels::chooseRowReduceSplit(l.rows, l.cols, kernels::deviceSmCount(args.device));
+  if (args.exchange) {
+    if (args.rowEnd >= 0) return Status::error("row reduction: an exchange of partial sums does not take a row range");
+    if (l.rows > args.exchange->slotStride)
+      return Status::error("row reduction: " + std::to_string(l.rows) + " rows exceed the exchange's max_rows of " +
+                           std::to_string(args.exchange->slotStride));
+    l.exchange = args.exchange;
+    split = 1;  // the partial sums of the exchange take the place of column slices
+  }
   l.splitCols = split;
   if (split > 1) {
     const size_t need = kWorkspaceStatusBytes + kernels::rowReduceWorkspaceBytes(l.rows, split);
@@ -448,6 +456,8 @@ Status launchDescriptor(const LaunchDescriptor &d, const std::map<std::string, i
   if (args.argPtrs.size() != numArgs || args.argBytes.size() != numArgs)
     return Status::error("kernel '" + d.kernel + "' takes " + std::to_string(d.numInputs) + " inputs and " +
                          std::to_string(d.numOutputs) + " outputs");
+  if (args.exchange && (d.kernelClass != KernelClass::RowReduce || d.groups.size() != 1))
+    return Status::error("only a single row-reduction group exchanges partial sums between GPUs");
   if (d.kernelClass == KernelClass::Matmul) return launchMatmulDescriptor(d, tiling, args, info);
   for (const auto &g : d.groups) {
     Status s;

@@ -28,6 +28,9 @@ struct LaunchArgs {
   int64_t rowEnd = -1;
   cudaStream_t stream = nullptr;
   int device = 0;
+  // Row-reduction groups only: the reduced axis is sharded over GPUs and the kernel exchanges its partial sums
+  // through this mailbox record (see kernels::RowReduceExchange); null = an ordinary launch.
+  const kernels::RowReduceExchange *exchange = nullptr;
 };
 
 struct LaunchInfo {

@@ -9,8 +9,7 @@
 //                the half, so a rank that is already sending call e+1 cannot overwrite an entry a slower rank has
 //                not yet read for call e; it can send call e+2 only after it finished e+1, which needs every
 //                rank's e+1 entries, which they send after they finished reading e.
-#include "CAPI/RuntimeCuda.h"
-#include "kernels/kernels.h"
+#include "runtime/rowsum_exchange.h"
 
 #include <cuda_runtime.h>
 
@@ -153,18 +152,9 @@ AFIRT_EXPORT int afirt_bcast_add_rowsum_exchange(AfirtRowsumExchange x, int elem
   cudaError_t e = cudaSetDevice(x->device);
   if (e != cudaSuccess) { fail(err_buf, err_len, "cudaSetDevice", e); return 1; }
 
-  unsigned int epoch = x->epoch + 1;
-  if (epoch == 0) epoch = 2;  // 0 is what an untouched entry holds; 2 keeps the alternation of the halves
-  const size_t half = (epoch & 1u) * x->slotsBytesPerHalf();
   RowReduceExchange rx = {};
-  for (int p = 0; p < x->world; ++p)
-    rx.peerEntries[p] = reinterpret_cast<unsigned long long *>(x->peer[p] + kSlotsOffset + half) + static_cast<size_t>(x->rank) * x->slotStride();
-  rx.myEntries = reinterpret_cast<const unsigned long long *>(x->mailbox + kSlotsOffset + half);
-  rx.doneCounter = reinterpret_cast<unsigned int *>(x->mailbox + kDoneOffset);
-  rx.status = reinterpret_cast<unsigned int *>(x->mailbox + kStatusOffset);
-  rx.world = x->world;
-  rx.epoch = epoch;
-  rx.slotStride = x->slotStride();
+  int mailboxDevice = 0;
+  if (afir::Status st = afir::nextExchangeCall(x, rx, mailboxDevice); !st) { fail(err_buf, err_len, st.message().c_str()); return 1; }
 
   RowReduceLaunch l = {};
   l.elemType = elem_type;
@@ -186,9 +176,33 @@ AFIRT_EXPORT int afirt_bcast_add_rowsum_exchange(AfirtRowsumExchange x, int elem
   int launched = 0;
   const int rc = launchRowReduce(l, static_cast<cudaStream_t>(cuda_stream), &launched);
   if (rc != 0) { fail(err_buf, err_len, "launch", static_cast<cudaError_t>(rc)); return 1; }
-  x->epoch = epoch;
+  afir::commitExchangeCall(x, rx);
   return 0;
 }
+
+namespace afir {
+
+Status nextExchangeCall(AfirtRowsumExchange x, kernels::RowReduceExchange &rx, int &device) {
+  if (!x || !x->connected) return Status::error("exchange is not connected");
+  unsigned int epoch = x->epoch + 1;
+  if (epoch == 0) epoch = 2;  // 0 is what an untouched entry holds; 2 keeps the alternation of the halves
+  const size_t half = (epoch & 1u) * x->slotsBytesPerHalf();
+  rx = kernels::RowReduceExchange();
+  for (int p = 0; p < x->world; ++p)
+    rx.peerEntries[p] = reinterpret_cast<unsigned long long *>(x->peer[p] + kSlotsOffset + half) + static_cast<size_t>(x->rank) * x->slotStride();
+  rx.myEntries = reinterpret_cast<const unsigned long long *>(x->mailbox + kSlotsOffset + half);
+  rx.doneCounter = reinterpret_cast<unsigned int *>(x->mailbox + kDoneOffset);
+  rx.status = reinterpret_cast<unsigned int *>(x->mailbox + kStatusOffset);
+  rx.world = x->world;
+  rx.epoch = epoch;
+  rx.slotStride = x->slotStride();
+  device = x->device;
+  return Status::success();
+}
+
+void commitExchangeCall(AfirtRowsumExchange x, const kernels::RowReduceExchange &rx) { x->epoch = rx.epoch; }
+
+} // namespace afir
 
 AFIRT_EXPORT int afirt_rowsum_exchange_status(AfirtRowsumExchange x, char *err_buf, size_t err_len) {
   if (!x) { fail(err_buf, err_len, "exchange is required"); return 1; }

@@ -20,7 +20,7 @@ EXPORTS = [
     "afirt_executor_last_launch_count", "afirt_executor_total_launch_count", "afirt_runtime_version",
     "afirt_bcast_add_rowsum_no_alloc",
     "afirt_rowsum_exchange_create", "afirt_rowsum_exchange_connect", "afirt_bcast_add_rowsum_exchange",
-    "afirt_rowsum_exchange_status", "afirt_rowsum_exchange_destroy",
+    "afirt_rowsum_exchange_status", "afirt_rowsum_exchange_destroy", "afirt_executor_launch_device_exchange",
 ]
 
 EXCHANGE_HANDLE_BYTES = 96  # AFIRT_EXCHANGE_HANDLE_BYTES
@@ -52,6 +52,10 @@ def get_lib() -> ctypes.CDLL:
                                                  [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
                                                   ctypes.c_char_p, ctypes.c_size_t])
     lib.afirt_executor_launch_device.restype = ctypes.c_int
+    lib.afirt_executor_launch_device_exchange.argtypes = ([ctypes.c_void_p, _u8p, ctypes.c_size_t] + _RUN_TAIL +
+                                                          [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p,
+                                                           ctypes.c_char_p, ctypes.c_size_t])
+    lib.afirt_executor_launch_device_exchange.restype = ctypes.c_int
     lib.afirt_executor_synchronize.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
     lib.afirt_executor_synchronize.restype = ctypes.c_int
     lib.afirt_executor_workspace_bytes.argtypes = [ctypes.c_void_p, _u8p, ctypes.c_size_t, _u8p, ctypes.c_size_t,

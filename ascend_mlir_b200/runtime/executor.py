@@ -105,8 +105,12 @@ class CudaRuntime:
     # ---- device tensors ----------------------------------------------------------------------
     def launch_device(self, binary_data: bytes, function_name: str, inputs: Sequence[Tuple[int, int]],
                       outputs: Sequence[Tuple[int, int]], tiling_data: Optional[bytes] = None, block_dim: int = 0,
-                      magic: int = MAGIC_ELF_AIVEC, workspace: Tuple[int, int] = (0, 0), stream: int = 0) -> None:
-        """Enqueue on `stream` (a cudaStream_t as int); inputs/outputs are (device address, nbytes)."""
+                      magic: int = MAGIC_ELF_AIVEC, workspace: Tuple[int, int] = (0, 0), stream: int = 0,
+                      exchange=None) -> None:
+        """Enqueue on `stream` (a cudaStream_t as int); inputs/outputs are (device address, nbytes).
+
+        `exchange` (a connected sharding.RowsumExchange) makes a row-reduction group exchange its partial sums with
+        the other ranks inside the kernel: the arguments are this rank's column slice, the output the full sums."""
         lib = get_lib()
         bin_ptr, bin_len, _k1 = self._binary(binary_data)
         til_ptr, til_len, _k2 = _u8(tiling_data)
@@ -115,10 +119,13 @@ class CudaRuntime:
         out_ptrs = (ctypes.c_void_p * max(1, len(outputs)))(*[p for p, _ in outputs])
         out_bytes = (ctypes.c_size_t * max(1, len(outputs)))(*[n for _, n in outputs])
         err = ctypes.create_string_buffer(1024)
-        ret = lib.afirt_executor_launch_device(ctypes.c_void_p(self._handle), bin_ptr, bin_len, function_name.encode(),
-                                               len(inputs), in_ptrs, in_bytes, len(outputs), out_ptrs, out_bytes,
-                                               til_ptr, til_len, block_dim, magic, ctypes.c_void_p(workspace[0]),
-                                               workspace[1], ctypes.c_void_p(stream), err, len(err))
+        head = (ctypes.c_void_p(self._handle), bin_ptr, bin_len, function_name.encode(), len(inputs), in_ptrs, in_bytes,
+                len(outputs), out_ptrs, out_bytes, til_ptr, til_len, block_dim, magic, ctypes.c_void_p(workspace[0]),
+                workspace[1], ctypes.c_void_p(stream))
+        if exchange is None:
+            ret = lib.afirt_executor_launch_device(*head, err, len(err))
+        else:
+            ret = lib.afirt_executor_launch_device_exchange(*head, exchange.pointer, err, len(err))
         if ret != 0:
             raise ExecutorError(err.value.decode(errors="replace"))
 

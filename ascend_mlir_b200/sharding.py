@@ -103,6 +103,11 @@ class RowsumExchange:
             raise RuntimeError(err.value.decode())
         self.handle = bytes(handle)
 
+    @property
+    def pointer(self):
+        """The AfirtRowsumExchange handle as a ctypes pointer (CudaRuntime.launch_device(exchange=...) takes the object)."""
+        return self._ptr
+
     def connect_handles(self, handles) -> None:
         ct = self._ct
         blob = b"".join(handles)

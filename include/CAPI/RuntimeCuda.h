@@ -94,6 +94,17 @@ int afirt_rowsum_exchange_connect(AfirtRowsumExchange exchange, const uint8_t *a
 int afirt_bcast_add_rowsum_exchange(AfirtRowsumExchange exchange, int elem_type, const void *a, const void *b, void *out,
                                     int64_t rows, int64_t cols, int64_t b_row_stride, void *cuda_stream,
                                     char *err_buf, size_t err_len);
+/* The same exchange for ANY compiled row-reduction group: afirt_executor_launch_device with one more argument.
+ * The descriptor's tiling dims describe this rank's column slice (contiguous arguments, as always on that
+ * path); the kernel sends the slice's partial row sums through the exchange and writes the sums over all ranks
+ * to the output.  Refused for other kernel classes.  Collective like the call above, and counted in the same
+ * sequence of calls of the exchange; the executor and the exchange must be on the same device. */
+int afirt_executor_launch_device_exchange(AfirtExecutor executor, const uint8_t *binary_data, size_t binary_len,
+                                          const char *function_name, int num_inputs, const void **input_ptrs,
+                                          const size_t *input_bytes, int num_outputs, void **output_ptrs,
+                                          const size_t *output_bytes, const uint8_t *tiling_data, size_t tiling_len,
+                                          int block_dim, uint32_t magic, void *workspace, size_t workspace_bytes,
+                                          void *cuda_stream, AfirtRowsumExchange exchange, char *err_buf, size_t err_len);
 int afirt_rowsum_exchange_status(AfirtRowsumExchange exchange, char *err_buf, size_t err_len);
 void afirt_rowsum_exchange_destroy(AfirtRowsumExchange exchange);
 

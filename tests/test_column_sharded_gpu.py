@@ -90,6 +90,13 @@ for out, (b, xs, lo, hi, b_d, x_d) in zip(outs, wants):
     assert torch.equal(out, total), float((out - total).abs().max())
     _, s64, abs64 = oracle.bcast_add_rowsum_f32(b, xs, with_bounds=True)
     assert np.all(np.abs(out.cpu().numpy() - s64) <= 1e-5 * abs64)
+# the same through a compiled descriptor: afirt_executor_launch_device_exchange on this rank's contiguous slice
+out2 = torch.full((M,), float("nan"), device="cuda")
+rt.launch_device(spec.binary, spec.name, [(b_d.data_ptr(), nb(b_d)), (mine.data_ptr(), nb(mine))],
+                 [(out2.data_ptr(), nb(out2))], spec.pack({"M": M, "N": hi - lo}), 0, spec.magic, exchange=x)
+rt.synchronize()
+x.check()
+assert torch.equal(out2, total)
 dist.barrier()
 # a wait that runs out: rank 0 makes one more call, nobody answers; after 2 s the kernel gives up, the status
 # says so and the context is still usable

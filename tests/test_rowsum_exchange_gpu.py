@@ -77,6 +77,51 @@ def test_world_of_one_bf16_rounds_once_after_the_f32_sum():
         x.close()
 
 
+def test_compiled_row_reduction_group_through_the_exchange():
+    """afirt_executor_launch_device_exchange: any row-reduction descriptor, the exchange as one more argument."""
+    import torch
+    from ascend_mlir_b200.runtime.executor import ExecutorError
+    rt = CudaRuntime()
+    rt.set_device(0)
+    x = RowsumExchange(0, 0, 1, max_rows=2048)
+    x.connect()
+    try:
+        for dtype, tdt in (("f32", torch.float32), ("f16", torch.float16)):
+            spec = descriptors.bcast_add_rowsum(dtype)
+            for rows, cols in ((2048, 4096), (77, 130)):
+                g = torch.Generator(device="cuda").manual_seed(rows)
+                a = torch.randn(rows, device="cuda", generator=g).to(tdt)
+                b = torch.randn(rows, cols, device="cuda", generator=g).to(tdt)
+                out = torch.zeros(rows, dtype=tdt, device="cuda")
+                nb = lambda t: t.numel() * t.element_size()
+                rt.launch_device(spec.binary, spec.name, [(a.data_ptr(), nb(a)), (b.data_ptr(), nb(b))], [(out.data_ptr(), nb(out))],
+                                 spec.pack({"M": rows, "N": cols}), 0, spec.magic, exchange=x)
+                rt.synchronize()
+                x.check()
+                assert torch.equal(out, _ordinary(torch, rt, a, b, 0, cols, dtype)), (dtype, rows, cols)
+        # too many rows for the mailbox, and a class that has nothing to exchange
+        a = torch.zeros(4096, device="cuda")
+        b = torch.zeros(4096, 8, device="cuda")
+        out = torch.zeros(4096, device="cuda")
+        spec = descriptors.bcast_add_rowsum("f32")
+        with pytest.raises(ExecutorError, match="max_rows"):
+            rt.launch_device(spec.binary, spec.name, [(a.data_ptr(), 4096 * 4), (b.data_ptr(), 4096 * 32)], [(out.data_ptr(), 4096 * 4)],
+                             spec.pack({"M": 4096, "N": 8}), 0, spec.magic, exchange=x)
+        ew = descriptors.add_mul("f32")
+        m = torch.zeros(8, 8, device="cuda")
+        with pytest.raises(ExecutorError, match="only a single row-reduction group"):
+            rt.launch_device(ew.binary, ew.name, [(m.data_ptr(), 256), (m.data_ptr(), 256)], [(m.data_ptr(), 256)],
+                             ew.pack({"M": 8, "N": 8}), 0, ew.magic, exchange=x)
+        # the refused calls did not count: the next one still works
+        a = torch.ones(16, device="cuda"); b = torch.ones(16, 4, device="cuda"); out = torch.zeros(16, device="cuda")
+        x.bcast_add_rowsum(a.data_ptr(), b.data_ptr(), out.data_ptr(), 16, 4, 4)
+        torch.cuda.synchronize()
+        x.check()
+        assert torch.equal(out, torch.full((16,), 8.0, device="cuda"))
+    finally:
+        x.close()
+
+
 def test_argument_errors_leave_the_exchange_usable():
     import torch
     lib = get_lib()
