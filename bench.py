@@ -275,6 +275,115 @@ class DeviceGroup:
         return (time.perf_counter() - t0) * 1e3 / steps
 
 
+def column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local, steps=200, warmup=10):
+    """The one exchange step the path has: broadcast_add_reduce with its REDUCED axis sharded (strong scaling,
+    one 8192 x 8192 f32 matrix, every rank reads its column slice in place).  Times the slice kernel alone, the
+    slice kernel followed by an NCCL all-reduce of the partial sums, and the kernel that exchanges the partial
+    sums itself through peer-mapped mailboxes.  Every step that can fail on one rank only is followed by a MIN
+    over ranks, so either all ranks go on or all stop; the waits inside the kernel are bounded."""
+    from ascend_mlir_b200 import descriptors, sharding
+
+    def all_ok(flag):
+        t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    M, N = 8192, 8192
+    spec = descriptors.bcast_add_rowsum("f32")
+    lo, hi = sharding.col_range(N, rank, world, quantum=4)
+    exchange, error = None, None
+    try:
+        exchange = sharding.RowsumExchange(local, rank, world, max_rows=M)
+    except Exception as e:
+        error = f"{type(e).__name__}: {e}"
+    if not all_ok(exchange is not None):
+        if exchange is not None:
+            exchange.close()
+        return {"error": error or "another rank could not create its mailbox"}
+    try:
+        exchange.connect()
+    except Exception as e:
+        error = f"{type(e).__name__}: {e}"
+    if not all_ok(error is None):
+        exchange.close()
+        return {"error": error or "another rank could not map the mailboxes"}
+    try:
+        with torch.cuda.stream(stream):
+            g = torch.Generator(device=device).manual_seed(1)  # the same matrix on every rank
+            sets = [(torch.rand(M, device=device, generator=g) - 0.5, torch.rand(M, N, device=device, generator=g) - 0.5)
+                    for _ in range(3)]
+            slices = [(a, b[:, lo:hi].contiguous()) for a, b in sets]
+            out = torch.empty(M, device=device)
+            nbytes = lambda t: t.numel() * t.element_size()
+            tiling = spec.pack({"M": M, "N": hi - lo})
+            raw = stream.cuda_stream
+
+            def local_only(i):
+                a, mine = slices[i % 3]
+                rt.launch_device(spec.binary, spec.name, [(a.data_ptr(), nbytes(a)), (mine.data_ptr(), nbytes(mine))],
+                                 [(out.data_ptr(), nbytes(out))], tiling, 0, spec.magic, stream=raw)
+
+            def two_step(i):
+                local_only(i)
+                dist.all_reduce(out)
+
+            def fused(i):
+                a, b = sets[i % 3]
+                exchange.bcast_add_rowsum(a.data_ptr(), b.data_ptr() + lo * 4, out.data_ptr(), M, hi - lo, N, "f32", raw)
+
+            two_step(0)
+            want = out.clone()
+            fused(0)
+            stream.synchronize()
+            try:
+                exchange.check()
+                close = bool(torch.allclose(out, want, rtol=1e-5, atol=1e-3))
+                error = None if close else "the fused result differs from kernel + all-reduce"
+            except Exception as e:
+                error = f"{type(e).__name__}: {e}"
+            if not all_ok(error is None):
+                return {"error": error or "another rank failed the first exchange"}
+            micros = {}
+            for name, fn in (("slice_kernel_only", local_only), ("kernel_plus_nccl_allreduce", two_step), ("fused_exchange", fused)):
+                for i in range(warmup):
+                    fn(i)
+                stream.synchronize()
+                if name == "fused_exchange":
+                    try:
+                        exchange.check()
+                    except Exception as e:
+                        error = f"{type(e).__name__}: {e}"
+                    if not all_ok(error is None):
+                        return {"error": error or "another rank's exchange timed out"}
+                dist.barrier()
+                torch.cuda.synchronize(device)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for i in range(steps):
+                    fn(i)
+                e1.record(stream)
+                stream.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                micros[name] = float(t.item()) * 1000.0
+            exchange.check()
+        work = M * N * 4 + 2 * M * 4  # the matrix once, the broadcast operand and the result
+        return {"value": work / (micros["fused_exchange"] * 1e-6) / 1e9, "unit": "GB/s", "scaling": "strong",
+                "shape": {"M": M, "N": N, "dtype": "f32"}, "steps": steps, "launches_per_step": 1.0,
+                "microseconds_per_call": micros, "algorithmic_work_per_step": work,
+                "exchange": "partial row sums stored into every rank's peer-mapped mailbox by the reduction kernel itself; "
+                            "no library collective in the fused arm",
+                "fused_speedup_over_nccl": micros["kernel_plus_nccl_allreduce"] / micros["fused_exchange"]}
+    except Exception as e:
+        return {"error": f"{type(e).__name__}: {e}"}
+    finally:
+        try:
+            torch.cuda.synchronize(device)
+            dist.barrier()
+        finally:
+            exchange.close()
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -348,6 +457,8 @@ def run_gpu_arm(args):
             if name == args.workload:
                 sampler.finish()
                 raise
+    if world > 1 and args.all_groups:
+        results["broadcast_add_reduce_column_sharded"] = column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local)
     clocks = sampler.finish()
 
     if rank == 0:
