@@ -28,6 +28,8 @@ struct EwParams {
   int flat;  // inner dim is the whole domain: skip the row arithmetic
   int numViews;
   BodyProgram prog;
+  long long vOuterBytes[kMaxViews];  // OUTER kernels: byte offset per blockIdx.y, per view and for the output
+  long long oOuterBytes;
 };
 
 template <class P> __device__ __forceinline__ void storeScalar(void *p, P v);
@@ -45,7 +47,7 @@ template <> __device__ __forceinline__ void storeScalar<PackI16>(void *p, PackI1
   *reinterpret_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
 }
 
-template <class P, int BODY, int UNROLL, bool VECTOR>
+template <class P, int BODY, int UNROLL, bool VECTOR, bool OUTER = false>
 __global__ void __launch_bounds__(512) elementwiseKernel(const __grid_constant__ EwParams prm) {
   using B = Body<BODY>;
   constexpr int NV = B::kViews;
@@ -70,14 +72,14 @@ __global__ void __launch_bounds__(512) elementwiseKernel(const __grid_constant__
         i1 = row - i0 * prm.d1;
       }
       ooff[u] = (static_cast<long long>(i0) * prm.os0 + static_cast<long long>(i1) * prm.os1 +
-                 static_cast<long long>(col) * kElems) * kElemBytes;
+                 static_cast<long long>(col) * kElems) * kElemBytes + (OUTER ? blockIdx.y * prm.oOuterBytes : 0ll);
       if (live[u]) {
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
           if (k < prm.numViews) {
             const long long e = static_cast<long long>(i0) * prm.vs0[k] + static_cast<long long>(i1) * prm.vs1[k] +
                                 static_cast<long long>(col) * kElems * prm.vs2[k];
-            const char *src = prm.vbase[k] + e * kElemBytes;
+            const char *src = prm.vbase[k] + e * kElemBytes + (OUTER ? blockIdx.y * prm.vOuterBytes[k] : 0ll);
             if (VECTOR && prm.vs2[k] == 1) {
               raw[u][k] = loadStream16(src);
             } else {
@@ -142,6 +144,16 @@ template <class P> KernelFn pickVector(int body, int unroll) {
 }
 
 template <class P> KernelFn pickScalar() { return elementwiseKernel<P, kBodyInterpreted, 2, false>; }
+
+// Kernels that take one more outer dim from blockIdx.y: the copy body (permutations) and the interpreted body.
+template <class P> KernelFn pickOuter(int body, bool vector) {
+  if (!vector) return elementwiseKernel<P, kBodyInterpreted, 2, false, true>;
+  if (body == kBodyCopy) return elementwiseKernel<P, kBodyCopy, 2, true, true>;
+  return elementwiseKernel<P, kBodyInterpreted, 2, true, true>;
+}
+template <class P> KernelFn pickOuterInteger(bool vector) {
+  return vector ? elementwiseKernel<P, kBodyInterpreted, 2, true, true> : elementwiseKernel<P, kBodyInterpreted, 2, false, true>;
+}
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -381,6 +393,32 @@ int launchElementwise(const ElementwiseLaunch &given, cudaStream_t stream, int *
   if (total == 0) return cudaSuccess;
   if (given.numViews < 1 || given.numViews > kMaxViews || given.outStride[2] != 1) return cudaErrorInvalidValue;
 
+  // One more outer dim: as the grid's second dimension when every view is contiguous or constant along the inner
+  // dim (the 16-byte kernel or its element twin runs, nothing else), otherwise one launch per outer index.
+  bool outerInGrid = false;
+  if (given.outerCount > 1) {
+    outerInGrid = given.outerCount <= 65535;
+    for (int k = 0; k < given.numViews; ++k)
+      if (given.views[k].stride[2] != 0 && given.views[k].stride[2] != 1) outerInGrid = false;
+    if (!outerInGrid) {
+      const int ebytes = elemBytes(given.elemType);
+      ElementwiseLaunch one = given;
+      one.outerCount = 1;
+      int total = 0;
+      for (int64_t o = 0; o < given.outerCount; ++o) {
+        for (int k = 0; k < given.numViews; ++k)
+          one.views[k].base = static_cast<const char *>(given.views[k].base) + o * given.viewOuterStride[k] * ebytes;
+        one.outBase = static_cast<char *>(given.outBase) + o * given.outOuterStride * ebytes;
+        int n = 0;
+        const int rc = launchElementwise(one, stream, &n);
+        total += n;
+        if (launched) *launched = total;
+        if (rc != cudaSuccess) return rc;
+      }
+      return cudaSuccess;
+    }
+  }
+
   // The block variant wants a transposed view contiguous along the MIDDLE dim.  All three dims are parallel, so
   // when such a view is contiguous along the outer dim instead (out[i,j,k] = in[k,j,i]) the two outer dims
   // trade places: same elements, same addresses, another walking order.
@@ -429,10 +467,12 @@ int launchElementwise(const ElementwiseLaunch &given, cudaStream_t stream, int *
   for (int k = 0; k < l.numViews && vector; ++k) {
     const ViewAccess &v = l.views[k];
     if (v.stride[2] == 1)
-      vector = aligned16(v.base) && v.stride[0] % vecElems == 0 && v.stride[1] % vecElems == 0;
+      vector = aligned16(v.base) && v.stride[0] % vecElems == 0 && v.stride[1] % vecElems == 0 &&
+               (!outerInGrid || l.viewOuterStride[k] % vecElems == 0);
     else if (v.stride[2] != 0)
       vector = false;
   }
+  if (outerInGrid && l.outOuterStride % vecElems != 0) vector = false;
   const int perVec = vector ? vecElems : 1;
   const int64_t vecPerRow = l.dims[2] / perVec;
   const int64_t totalVec = l.dims[0] * l.dims[1] * vecPerRow;
@@ -457,6 +497,10 @@ int launchElementwise(const ElementwiseLaunch &given, cudaStream_t stream, int *
   p.flat = (l.dims[0] == 1 && l.dims[1] == 1) ? 1 : 0;
   p.numViews = l.numViews;
   p.prog = l.body;
+  if (outerInGrid) {
+    for (int k = 0; k < l.numViews; ++k) p.vOuterBytes[k] = l.viewOuterStride[k] * eb;
+    p.oOuterBytes = l.outOuterStride * eb;
+  }
 
   int threads = l.ctaThreads > 0 ? l.ctaThreads : 128;
   threads = std::max(32, std::min(512, (threads / 32) * 32));
@@ -479,12 +523,21 @@ int launchElementwise(const ElementwiseLaunch &given, cudaStream_t stream, int *
     fn = l.elemType == kF32 ? pickScalar<PackF32>() : l.elemType == kF16 ? pickScalar<PackF16>() : pickScalar<PackBF16>();
   }
 
+  if (outerInGrid) {
+    unroll = 2;
+    if (l.elemType == kInt32) fn = pickOuterInteger<PackI32>(vector);
+    else if (l.elemType == kInt16) fn = pickOuterInteger<PackI16>(vector);
+    else fn = l.elemType == kF32 ? pickOuter<PackF32>(body, vector) : l.elemType == kF16 ? pickOuter<PackF16>(body, vector)
+                                                                                         : pickOuter<PackBF16>(body, vector);
+  }
+
   const int64_t tileVecs = static_cast<int64_t>(threads) * unroll;
   const int64_t numTiles = (totalVec + tileVecs - 1) / tileVecs;
   p.numTiles = static_cast<unsigned int>(numTiles);
   int64_t grid = l.gridBlocks > 0 ? l.gridBlocks : numTiles;
   grid = std::max<int64_t>(1, std::min<int64_t>(grid, numTiles));
-  fn<<<static_cast<unsigned int>(grid), threads, 0, stream>>>(p);
+  const dim3 blocks(static_cast<unsigned int>(grid), outerInGrid ? static_cast<unsigned int>(l.outerCount) : 1u);
+  fn<<<blocks, threads, 0, stream>>>(p);
   if (launched) *launched = 1;
   return cudaGetLastError();
 }

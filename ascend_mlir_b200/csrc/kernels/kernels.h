@@ -82,6 +82,13 @@ struct ElementwiseLaunch {
   int unroll;      // vectors in flight per thread: 1, 2, 4 or 8; 0 = default
   int gridBlocks;  // 0 = library default
   int forceElementAccess = 0;  // 1: never use the block variant for transposed operands (testing, tuning)
+  // One more (outermost) iteration dim above dims[0], for domains that keep four dims after collapsing
+  // (out[b, h, s, d] = in[b, s, h, d]): extent and element strides per view and for the output.  Groups whose
+  // views are all contiguous or constant along the inner dim take it as the grid's second dimension, one launch;
+  // the others are launched once per index.
+  int64_t outerCount = 1;
+  int64_t viewOuterStride[kMaxViews] = {0, 0, 0, 0, 0, 0};
+  int64_t outOuterStride = 0;
 };
 // Returns a cudaError_t value (0 = success); *launched gets the number of kernels launched.
 int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *launched);

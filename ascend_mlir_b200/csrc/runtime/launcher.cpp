@@ -152,9 +152,9 @@ Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, con
     }
   }
   int64_t outerCount = 1;
-  for (int64_t e : outer) {
-    outerCount *= e;
-    if (outerCount > kMaxOuterLaunches)
+  for (size_t j = 0; j < outer.size(); ++j) {
+    outerCount *= outer[j];
+    if (j + 1 < outer.size() && outerCount > kMaxOuterLaunches)  // the last of them is not walked here (below)
       return Status::error("iteration space keeps more than three dims after collapsing and the outer ones need more than " +
                            std::to_string(kMaxOuterLaunches) + " launches");
   }
@@ -178,6 +178,16 @@ Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, con
   l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
   l.unroll = static_cast<int>(optionalField(d.unrollField, tiling));
   l.gridBlocks = args.blockDim;
+  // the innermost of the outer dims goes to the kernel library (it takes one as the grid's second dimension where
+  // the group allows, and walks it itself where not); the others are walked here
+  if (!outer.empty()) {
+    l.outerCount = outer.back();
+    for (size_t i = 0; i < loads.size(); ++i) l.viewOuterStride[i] = outerStride[i].back();
+    l.outOuterStride = outerStride[loads.size()].back();
+    outerCount /= outer.back();
+    outer.pop_back();
+    for (auto &strides : outerStride) strides.pop_back();
+  }
   std::vector<int64_t> index(outer.size(), 0);
   for (int64_t launch = 0; launch < outerCount; ++launch) {
     auto shifted = [&](size_t view, const ResolvedView &v) {

@@ -90,3 +90,11 @@ def test_rank_four_permutations_with_outer_dims_walked_by_the_launcher(rt, tmp_p
 
 def test_rank_five_permutation(rt, tmp_path):
     run_permutation(rt, tmp_path, (4, 2, 0, 3, 1), [2, 3, 4, 5, 8], "f16")
+
+
+def test_attention_style_permutation_is_one_launch(rt, tmp_path):
+    """out[b, h, s, d] = in[b, s, h, d] keeps four dims after collapsing; its views are contiguous along d, so the
+    batch dim rides in the grid's second dimension instead of costing one launch per batch."""
+    assert run_permutation(rt, tmp_path, (0, 2, 1, 3), [5, 6, 40, 64], "f16") == 1
+    assert run_permutation(rt, tmp_path, (0, 2, 1, 3), [3, 4, 7, 9], "f32") == 1       # unaligned: the element kernel, still one launch
+    assert run_permutation(rt, tmp_path, (2, 0, 3, 1), [3, 4, 8, 16], "f16") > 1        # a transposed inner pair: walked per index
