@@ -55,6 +55,7 @@ struct Elementwise {
   Dim indicesLen;
   // matmul (views[0] is the accumulator)
   bool hasMatmul = false;
+  bool transB = false;  // linalg.matmul_transpose_b: B is [N, K]
   int aArg = -1, bArg = -1, initArg = -1;
   std::string inType;
   Dim M, N, K;
@@ -126,6 +127,7 @@ Status inlineInto(Elementwise &dst, const Elementwise &src, const AffineMap &map
     dst.hasMatmul = true;
     dst.aArg = src.aArg; dst.bArg = src.bArg; dst.initArg = src.initArg;
     dst.inType = src.inType; dst.M = src.M; dst.N = src.N; dst.K = src.K;
+    dst.transB = src.transB;
   }
   // Ops are appended with their operands renumbered; an op the group already holds (the same producer read by two
   // consumers, e.g. abs(x) = max(x, 0 - x)) is reused instead of being computed twice.

@@ -199,13 +199,15 @@ struct MatmulLaunch {
   int biasType;  // kF32, kF16 or kBF16
   int64_t M, N, K;
   const void *A;  // [M,K] row-major
-  const void *B;  // [K,N] row-major
+  const void *B;  // [K,N] row-major, or [N,K] row-major when bTransposed
   const void *bias;  // [N] or null
   void *out;      // [M,N] row-major
   int epilogue;
   float alpha;
   int gridBlocks;  // 0 = one persistent CTA per SM
   int stages;      // 0 = default
+  int bTransposed = 0;  // 1: out = A x B^T with B stored [N,K] (no counterpart in the reference, whose matmul takes
+                        // no transposes; it is how torch.nn.Linear keeps its weight)
 };
 // errorText (optional, >= 256 bytes) receives a description when the launch is refused or the
 // kernel reports a bounded-wait timeout.

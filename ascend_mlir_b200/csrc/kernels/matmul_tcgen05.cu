@@ -55,6 +55,7 @@ struct GemmParams {
   float alpha;
   unsigned int idesc;
   int band;  // tile-rows per raster band
+  int bKMajor;  // 1: B is given as [N, K] (out = A x B^T, the layout of a torch Linear weight): K-major tiles like A's
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -423,9 +424,13 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           mbarExpectTx(full, S::kStageBytes);
           unsigned char *stage = smem + static_cast<size_t>(s) * S::kStageBytes;
           tmaLoad2d(smemAddr(stage), &mapA, kb * kBlockK, tm * S::kTileM, full);
+          if (prm.bKMajor) {  // one [256 n-rows x 64 k] box, the same bytes as the four N-major boxes
+            tmaLoad2d(smemAddr(stage + S::kAStageBytes), &mapB, kb * kBlockK, tn * kBlockN, full);
+          } else {
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            tmaLoad2d(smemAddr(stage + S::kAStageBytes + j * kBBoxBytes), &mapB, tn * kBlockN + j * 64, kb * kBlockK, full);
+            for (int j = 0; j < 4; ++j)
+              tmaLoad2d(smemAddr(stage + S::kAStageBytes + j * kBBoxBytes), &mapB, tn * kBlockN + j * 64, kb * kBlockK, full);
+          }
         }
       }
       if (!ok) {
@@ -467,7 +472,9 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
               const unsigned long long aDesc = smemDesc(aBase + h * (128 * kBlockK * 2) + k * (kUmmaK * 2), 16, 1024);
               // B: N-major, 64-column blocks 8192 B apart (leading), 8-row k-groups 1024 B apart (stride);
               // 16 k-rows = two k-groups = 2048 bytes
-              const unsigned long long bDesc = smemDesc(bBase + k * (kUmmaK * 128), kBBoxBytes, 1024);
+              // (given as [N, K]: K-major like A, n-rows 128 B apart, 8-row groups 1024 B apart, 32 bytes per k-step)
+              const unsigned long long bDesc = prm.bKMajor ? smemDesc(bBase + k * (kUmmaK * 2), 16, 1024)
+                                                           : smemDesc(bBase + k * (kUmmaK * 128), kBBoxBytes, 1024);
               ummaF16(dTmem, aDesc, bDesc, prm.idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
           }
@@ -811,14 +818,17 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   const int64_t tiles256 = ((l.M + 255) / 256) * ((l.N + kBlockN - 1) / kBlockN);
   // (the pair kernel keeps the tensor pipe busier per clock but draws more power; under the board's power cap the
   // single-CTA 256-row kernel sustains the higher throughput on B200, so the pair kernel is opt-in)
-  const bool pairKernel = l.stages == 3;
+  const bool pairKernel = l.stages == 3 && !l.bTransposed;  // the pair kernel splits N-major B tiles between its CTAs
   const int mb = pairKernel ? 1 : (l.stages == 1) ? 1 : (l.stages == 2) ? 2 : (tiles256 >= sms ? 2 : 1);
   const int tileM = 128 * mb;  // rows per TMA box of A (the pair kernel loads 128 rows per CTA)
   const CUtensorMapDataType dt = l.inType == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap mapA, mapB;
   if (!makeMap2d(&mapA, dt, l.A, static_cast<uint64_t>(l.K), static_cast<uint64_t>(l.M), static_cast<uint64_t>(l.K) * 2, kBlockK,
                  static_cast<uint32_t>(tileM)) ||
-      !makeMap2d(&mapB, dt, l.B, static_cast<uint64_t>(l.N), static_cast<uint64_t>(l.K), static_cast<uint64_t>(l.N) * 2, 64, kBlockK)) {
+      !(l.bTransposed ? makeMap2d(&mapB, dt, l.B, static_cast<uint64_t>(l.K), static_cast<uint64_t>(l.N), static_cast<uint64_t>(l.K) * 2,
+                                  kBlockK, kBlockN)
+                      : makeMap2d(&mapB, dt, l.B, static_cast<uint64_t>(l.N), static_cast<uint64_t>(l.K), static_cast<uint64_t>(l.N) * 2, 64,
+                                  kBlockK))) {
     fail(errorText, "matmul: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)");
     return 1;
   }
@@ -841,7 +851,9 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   const unsigned int fmt = l.inType == kF16 ? 0u : 1u;
   // instruction descriptor: D=f32, A/B format, A K-major, B N-major, N=256, M=128 (256 across a CTA pair)
   const unsigned int instrM = pairKernel ? 256u : 128u;
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) | ((kBlockN >> 3) << 17) | ((instrM >> 4) << 24);
+  p.bKMajor = l.bTransposed ? 1 : 0;
+  const unsigned int bMajor = l.bTransposed ? 0u : 1u;  // bit 16: 0 = B K-major, 1 = B N-major
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (bMajor << 16) | ((kBlockN >> 3) << 17) | ((instrM >> 4) << 24);
 
   const int64_t numTiles = static_cast<int64_t>(p.numTilesM) * p.numTilesN;
   int grid = l.gridBlocks > 0 ? l.gridBlocks : sms;

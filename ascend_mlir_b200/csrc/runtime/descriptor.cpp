@@ -289,6 +289,7 @@ Status parseDescriptorJson(const json::Value &root, LaunchDescriptor &out) {
     else return Status::error("matmul: unknown epilogue kind '" + epi + "'");
     if (ms.epilogue != kernels::kEpiNone && ms.biasArg < 0) return Status::error("matmul epilogue needs a bias argument");
     ms.alpha = m->getDouble("alpha", 0.0);
+    ms.transposeB = m->getBool("transpose_b", false);
     const json::Value *dm = m->find("m"), *dn = m->find("n"), *dk = m->find("k");
     if (!dm || !dn || !dk) return Status::error("matmul needs 'm', 'n' and 'k'");
     if (Status s = parseDim(*dm, ms.m, "matmul.m"); !s) return s;

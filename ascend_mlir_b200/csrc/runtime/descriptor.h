@@ -56,6 +56,7 @@ struct MatmulSpec {
   int epilogue = kernels::kEpiNone;
   double alpha = 0.0;
   DimExpr m, n, k;
+  bool transposeB = false;  // B is [N, K]: out = A x B^T
 };
 
 struct TilingField {

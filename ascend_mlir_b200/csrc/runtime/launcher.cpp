@@ -431,6 +431,7 @@ Status launchMatmulDescriptor(const LaunchDescriptor &d, const std::map<std::str
   l.out = static_cast<char *>(args.argPtrs[m.outArg]) + static_cast<size_t>(r0 * N) * dtypeBytes(m.outType);
   l.epilogue = m.epilogue;
   l.alpha = static_cast<float>(m.alpha);
+  l.bTransposed = m.transposeB ? 1 : 0;
   l.gridBlocks = args.blockDim;
   l.stages = static_cast<int>(optionalField(d.stagesField, tiling));
   int n = 0;

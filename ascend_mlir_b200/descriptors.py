@@ -252,12 +252,17 @@ def relu_gather_cols_bias(dtype: str = "f16", index_dtype: str = "i64", name: st
 
 # ---- matmul + bias + LeakyReLU -----------------------------------------------------------------------------
 def matmul_bias_leakyrelu(in_dtype: str = "bf16", out_dtype: str = "bf16", bias_dtype: str = "bf16", alpha: float = 0.01,
-                          epilogue: str = "BiasAddLeakyRelu", name: str = "matmul_add_leakyrelu") -> KernelSpec:
+                          epilogue: str = "BiasAddLeakyRelu", name: str = "matmul_add_leakyrelu",
+                          transpose_b: bool = False) -> KernelSpec:
     """E = max(x, alpha*x), x = A[M,K].B[K,N] + bias[N].  Arguments (a, b, bias, out): `out` is the
-    reference's init/result tensor (its initial contents are not read)."""
+    reference's init/result tensor (its initial contents are not read).  transpose_b: B is given as [N,K]
+    (x = A.B^T, a torch Linear weight); the reference's ABI names the attribute (abi_matmul_trans_b) and always
+    sets it false."""
     tile = [("STAGES", 0, (0,))]
     dims = [("dim_arg3_0", "M"), ("dim_arg3_1", "N"), ("dim_arg0_1", "K")]
     body = {"matmul": {"a": 0, "b": 1, "bias": 2, "out": 3, "in_dtype": in_dtype, "out_dtype": out_dtype,
                        "bias_dtype": bias_dtype, "epilogue": epilogue, "alpha": alpha,
                        "m": "dim_arg3_0", "n": "dim_arg3_1", "k": "dim_arg0_1"}}
+    if transpose_b:
+        body["matmul"]["transpose_b"] = True
     return _spec(name, "matmul", in_dtype, 3, 1, tile, dims, body, {"stages": "STAGES"})

@@ -11,7 +11,7 @@
 """
 from .pipeline import PipelineError, compile_model, run_autotuner, torch_e2e_test
 from .tensor_spec import TensorSpec
-from .torch2linalg import UnsupportedTorchOp, torch_to_linalg
+from .torch2linalg import UnsupportedTorchOp, torch_to_linalg, torch_to_linalg_with_state
 
-__all__ = ["torch_e2e_test", "TensorSpec", "torch_to_linalg", "compile_model", "run_autotuner", "PipelineError",
+__all__ = ["torch_e2e_test", "TensorSpec", "torch_to_linalg", "torch_to_linalg_with_state", "compile_model", "run_autotuner", "PipelineError",
            "UnsupportedTorchOp"]

@@ -24,7 +24,7 @@ import numpy as np
 import torch
 
 from .tensor_spec import TensorSpec
-from .torch2linalg import torch_to_linalg
+from .torch2linalg import torch_to_linalg_with_state
 
 PACKAGE_ROOT = Path(__file__).resolve().parent.parent
 AFIR_OPT_STAGES = [
@@ -127,19 +127,22 @@ def compile_model(model: torch.nn.Module, specs: Sequence[TensorSpec], work_dir:
     per_input = [spec.dynamic_dims(pool) for spec in specs]
     dynamic_shapes = tuple(d or None for d in per_input) if any(per_input) else None
     trace_inputs = [spec.make_sample() for spec in specs]
-    (work_dir / "step0_linalg.mlir").write_text(torch_to_linalg(model, trace_inputs, dynamic_shapes, func_name=func_name))
+    # parameters and buffers of the model become kernel arguments after the user inputs
+    text, state = torch_to_linalg_with_state(model, trace_inputs, dynamic_shapes, func_name=func_name)
+    (work_dir / "step0_linalg.mlir").write_text(text)
     kernel = run_mlir_pipeline(work_dir)
     space = work_dir / "step8_kernel.tiling_space.json"
     patch_tiling_space(space)
 
-    verify_inputs = [spec.make_sample(verify_shapes or {}) for spec in specs]
+    user_inputs = [spec.make_sample(verify_shapes or {}) for spec in specs]
+    with torch.no_grad():
+        expected = model.eval()(*user_inputs)
+    verify_inputs = user_inputs + [t for _, t in state]
     for i, t in enumerate(verify_inputs):
         save_tensor(work_dir / f"input_{i}.npy", t)
-    with torch.no_grad():
-        expected = model.eval()(*verify_inputs)
     save_tensor(work_dir / "expected_0.npy", expected)
-    return {"kernel": kernel, "space": space, "inputs": verify_inputs, "expected": expected,
-            "shape": build_shape_string(space, verify_inputs)}
+    return {"kernel": kernel, "space": space, "inputs": verify_inputs, "expected": expected, "state": [n for n, _ in state],
+            "num_inputs": len(verify_inputs), "shape": build_shape_string(space, verify_inputs)}
 
 
 def run_autotuner(work_dir: Path, num_inputs: int, shape: str, atol: float = 1.0, rtol: float = 1e-2) -> Dict[str, object]:
@@ -148,8 +151,7 @@ def run_autotuner(work_dir: Path, num_inputs: int, shape: str, atol: float = 1.0
            "--inputs", ",".join(str(work_dir / f"input_{i}.npy") for i in range(num_inputs)),
            "--expected", work_dir / "expected_0.npy", "--output", work_dir / "best_config.json",
            "--atol", repr(atol), "--rtol", repr(rtol)]
-    if shape:
-        cmd += ["--shape", shape]
+    cmd += [f"--shape={shape}"]  # required by the tool even when every dim is static (then it is empty)
     proc = _run(cmd, "autotuner")
     (work_dir / "autotuner.log").write_text(proc.stdout + proc.stderr)
     return json.loads((work_dir / "best_config.json").read_text())
@@ -167,7 +169,7 @@ def torch_e2e_test(func=None, *, verify_shapes: Optional[Dict[str, int]] = None,
             model, specs = fn()
             work_dir = output_root() / fn.__name__
             built = compile_model(model, specs, work_dir, verify_shapes)
-            best = run_autotuner(work_dir, len(specs), built["shape"], atol, rtol)
+            best = run_autotuner(work_dir, built["num_inputs"], built["shape"], atol, rtol)
             print(f"torch_e2e {fn.__name__}: best {best.get('config')} score {best.get('best', {}).get('score')} us")
             return None
         return wrapper

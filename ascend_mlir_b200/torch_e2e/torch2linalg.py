@@ -198,19 +198,27 @@ class _Emitter:
 
     def matmul(self, a: _Tensor, b: _Tensor, bias: Optional[_Tensor] = None) -> _Tensor:
         """A . B accumulated in f32, optional bias[n] added in f32, rounded once to the operands' type."""
-        a, b = self.materialise(a), self.materialise(b)
+        # B read through a transpose (x @ w.t(), torch.nn.Linear) stays where it is: linalg.matmul_transpose_b takes
+        # it as [N, K], and the kernel loads K-major tiles of it
+        trans_b = len(b.base) == 2 and b.view == [1, 0]
+        a = self.materialise(a)
+        if not trans_b:
+            b = self.materialise(b)
         if len(a.base) != 2 or len(b.base) != 2 or a.elem != b.elem:
             raise UnsupportedTorchOp("matmul needs two rank-2 operands of one element type")
-        if a.base[1] != b.base[0]:
-            raise UnsupportedTorchOp(f"matmul inner extents differ: {a.base[1]} and {b.base[0]}")
-        sizes = [a.base[0], b.base[1]]
+        k_of_b, n_of_b = (b.base[1], b.base[0]) if trans_b else (b.base[0], b.base[1])
+        if a.base[1] != k_of_b:
+            raise UnsupportedTorchOp(f"matmul inner extents differ: {a.base[1]} and {k_of_b}")
+        sizes = [a.base[0], n_of_b]
+        b_type = _tensor_type(b.base, b.elem)
         acc_type = _tensor_type(sizes, "f32")
         zero = self.float_const(0.0, "f32")
         acc0 = self.empty(sizes, "f32")
         init = self.fresh("init")
         self.emit(f"{init} = linalg.fill ins({zero} : f32) outs({acc0} : {acc_type}) -> {acc_type}")
         prod = self.fresh("mm")
-        self.emit(f"{prod} = linalg.matmul ins({a.ssa}, {b.ssa} : {a.type}, {b.type}) outs({init} : {acc_type}) -> {acc_type}")
+        op = "linalg.matmul_transpose_b" if trans_b else "linalg.matmul"
+        self.emit(f"{prod} = {op} ins({a.ssa}, {b.ssa} : {a.type}, {b_type}) outs({init} : {acc_type}) -> {acc_type}")
         if a.elem == "f32" and bias is None:
             return _Tensor(prod, "f32", sizes)
         # epilogue generic: (+ bias) in f32, then the result type
@@ -251,7 +259,10 @@ class _Emitter:
         """Structured ops other than elementwise ones need the value itself, not a view of it."""
         if t.view == list(range(len(t.base))):
             return t
-        raise UnsupportedTorchOp("a view (inserted unit dimensions or a permutation) feeds an op that needs a materialised tensor")
+        if any(v is None for v in t.view):
+            raise UnsupportedTorchOp("a view with inserted unit dimensions feeds an op that needs a materialised tensor")
+        # a permutation: one copy generic that reads the value through the permuted map (a bare permutation group)
+        return self.elementwise([t], lambda args: ([], args[0]))
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -335,6 +346,9 @@ def _lower_node(em: _Emitter, node, env: Dict[str, _Tensor]) -> _Tensor:
         if sorted(perm) != list(range(rank)):
             raise UnsupportedTorchOp(f"{name} with dims {perm}")
         return _Tensor(x.ssa, x.elem, x.base, [x.view[d] for d in perm])
+    if target in (aten.contiguous.default, aten.clone.default):
+        x = arg(0)
+        return x if x.view == list(range(len(x.base))) else em.materialise(x)
     if target == aten.leaky_relu.default:
         return em.leaky_relu(arg(0), float(arg(1, 0.01)))
     if target == aten.unsqueeze.default:
@@ -362,6 +376,12 @@ def _lower_node(em: _Emitter, node, env: Dict[str, _Tensor]) -> _Tensor:
         return em.row_sum(x)
     if target in (aten.mm.default, aten.matmul.default):
         return em.matmul(arg(0), arg(1))
+    if target == aten.linear.default:  # x @ w.t() + b with w kept as [N, K]
+        w = arg(1)
+        if len(w.view) != 2:
+            raise UnsupportedTorchOp("linear needs a rank-2 weight")
+        wt = _Tensor(w.ssa, w.elem, w.base, [w.view[1], w.view[0]])
+        return em.matmul(arg(0), wt, bias=arg(2) if len(node.args) > 2 and node.args[2] is not None else None)
     if target == aten.addmm.default:
         if node.kwargs.get("beta", 1) != 1 or node.kwargs.get("alpha", 1) != 1:
             raise UnsupportedTorchOp("addmm with beta/alpha other than 1")
@@ -374,28 +394,48 @@ def torch_to_linalg(model: torch.nn.Module, inputs: Sequence[torch.Tensor], dyna
     """MLIR text (linalg on tensors) of `model(*inputs)`; `dynamic_shapes` as torch.export takes it.
 
     Same call shape as the reference's torch_to_linalg (python/torch/torch2linalg/convert.py:12-38).  Models
-    with parameters or buffers are not supported by this entry point: pass them as inputs.
+    with parameters or buffers are refused by this entry point (pass them as inputs, or use
+    torch_to_linalg_with_state, which appends them to the function's arguments).
     """
+    text, state = torch_to_linalg_with_state(model, inputs, dynamic_shapes, func_name)
+    if state:
+        raise UnsupportedTorchOp(f"model state '{state[0][0]}' (parameters and buffers must be passed as inputs)")
+    return text
+
+
+def torch_to_linalg_with_state(model: torch.nn.Module, inputs: Sequence[torch.Tensor], dynamic_shapes=None,
+                               func_name: str = "forward"):
+    """(MLIR text, [(name, tensor), ...]): parameters and buffers of the model become function arguments AFTER the
+    user inputs, in the order of the list; a caller passes `inputs + [t for _, t in state]`."""
     exported = torch.export.export(model.eval(), tuple(inputs), dynamic_shapes=dynamic_shapes)
     graph = exported.graph
-    user_inputs = {s.arg.name for s in exported.graph_signature.input_specs if s.kind.name == "USER_INPUT"}
+    sig = exported.graph_signature
+    user_inputs = {s.arg.name for s in sig.input_specs if s.kind.name == "USER_INPUT"}
+    state_of = {}
+    for spec in sig.input_specs:
+        if spec.kind.name in ("PARAMETER", "BUFFER") and spec.target in exported.state_dict:
+            state_of[spec.arg.name] = (spec.target, exported.state_dict[spec.target])
+        elif spec.kind.name in ("BUFFER", "CONSTANT_TENSOR") and spec.target in exported.constants:
+            state_of[spec.arg.name] = (spec.target, exported.constants[spec.target])
     em = _Emitter(func_name)
     env: Dict[str, _Tensor] = {}
     args: List[_Tensor] = []
+    state: List = []
     result: Optional[_Tensor] = None
     body_nodes = []
-    for node in graph.nodes:
-        if node.op == "placeholder":
-            if node.name not in user_inputs:
-                raise UnsupportedTorchOp(f"model state '{node.name}' (parameters and buffers must be passed as inputs)")
-            val = node.meta["val"]
-            if val.dtype not in ELEM_TYPES:
-                raise UnsupportedTorchOp(f"input '{node.name}' has unsupported dtype {val.dtype}")
-            t = _Tensor(f"%arg{len(args)}", ELEM_TYPES[val.dtype], [_size_of(s) for s in val.shape])
-            env[node.name] = t
-            args.append(t)
-        else:
-            body_nodes.append(node)
+    placeholders = [n for n in graph.nodes if n.op == "placeholder"]
+    body_nodes = [n for n in graph.nodes if n.op != "placeholder"]
+    for node in [n for n in placeholders if n.name in user_inputs] + [n for n in placeholders if n.name not in user_inputs]:
+        if node.name not in user_inputs:
+            if node.name not in state_of:
+                raise UnsupportedTorchOp(f"graph input '{node.name}' is neither a user input nor a parameter, buffer or constant tensor")
+            state.append((state_of[node.name][0], state_of[node.name][1].detach()))
+        val = node.meta["val"]
+        if val.dtype not in ELEM_TYPES:
+            raise UnsupportedTorchOp(f"input '{node.name}' has unsupported dtype {val.dtype}")
+        t = _Tensor(f"%arg{len(args)}", ELEM_TYPES[val.dtype], [_size_of(s) for s in val.shape])
+        env[node.name] = t
+        args.append(t)
     for t in args:
         em.bind_dims(t)
     for node in body_nodes:
@@ -412,8 +452,9 @@ def torch_to_linalg(model: torch.nn.Module, inputs: Sequence[torch.Tensor], dyna
     if result is None:
         raise UnsupportedTorchOp("model has no output")
     if result.view != list(range(len(result.base))):
-        raise UnsupportedTorchOp("the model output is a bare view (inserted unit dimensions or a permutation) of another value")
-    sig = ", ".join(f"{t.ssa}: {t.type}" for t in args)
+        result = em.materialise(result)  # a permuted output is written out by a copy group; unit-dim views are refused there
+    sig_text = ", ".join(f"{t.ssa}: {t.type}" for t in args)
     head = [f"{alias} = {text}" for text, alias in em.maps.items()]
-    return "\n".join(head + ["module {", f"  func.func @{func_name}({sig}) -> {result.type} {{"] + em.lines +
+    text = "\n".join(head + ["module {", f"  func.func @{func_name}({sig_text}) -> {result.type} {{"] + em.lines +
                      [f"    return {result.ssa} : {result.type}", "  }", "}"]) + "\n"
+    return text, state

@@ -285,3 +285,39 @@ def test_permutation_of_rank_five_is_an_elementwise_group_with_a_permuted_view(t
     desc = tmp_path / "p.cuda.json"
     desc.write_text(json.dumps(got))
     assert compile_kernel(desc, tmp_path / "artifact", "permute").exists()  # the descriptor parser takes up to eight dims
+
+
+def test_matmul_transpose_b_sets_the_abi_attribute_and_the_descriptor_flag(tmp_path):
+    """The reference's matmul ABI carries abi_matmul_trans_b (always false there: AnnotateMixMatmulSemanticsPass);
+    linalg.matmul_transpose_b sets it, and the descriptor asks the kernel for B as [N, K]."""
+    src = tmp_path / "mmt.mlir"
+    src.write_text("""#bias = affine_map<(d0, d1) -> (d1)>
+#id = affine_map<(d0, d1) -> (d0, d1)>
+module {
+  func.func @linear(%x: tensor<64x128xbf16>, %w: tensor<256x128xbf16>, %b: tensor<256xbf16>) -> tensor<64x256xbf16> {
+    %zero = arith.constant 0.0 : f32
+    %e = tensor.empty() : tensor<64x256xf32>
+    %init = linalg.fill ins(%zero : f32) outs(%e : tensor<64x256xf32>) -> tensor<64x256xf32>
+    %mm = linalg.matmul_transpose_b ins(%x, %w : tensor<64x128xbf16>, tensor<256x128xbf16>) outs(%init : tensor<64x256xf32>) -> tensor<64x256xf32>
+    %o = tensor.empty() : tensor<64x256xbf16>
+    %r = linalg.generic {indexing_maps = [#id, #bias, #id], iterator_types = ["parallel", "parallel"]}
+        ins(%mm, %b : tensor<64x256xf32>, tensor<256xbf16>) outs(%o : tensor<64x256xbf16>) {
+    ^bb0(%acc: f32, %bv: bf16, %out: bf16):
+      %bf = arith.extf %bv : bf16 to f32
+      %s = arith.addf %acc, %bf : f32
+      %t = arith.truncf %s : f32 to bf16
+      linalg.yield %t : bf16
+    } -> tensor<64x256xbf16>
+    return %r : tensor<64x256xbf16>
+  }
+}
+""")
+    got = translate(src)
+    mm = got["matmul"]
+    assert got["kernel_class"] == "matmul" and mm["transpose_b"] is True and mm["epilogue"] == "BiasAdd"
+    assert (mm["m"], mm["n"], mm["k"]) == (64, 256, 128) and (mm["a"], mm["b"], mm["bias"]) == (0, 1, 2)
+    converted = tmp_path / "mmt.converted.mlir"
+    r = subprocess.run([str(BIN / "afir-opt"), "--annotate-ascendc-kernel-kind", "--annotate-mix-matmul-semantics", str(src), "-o", str(converted)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert "abi_matmul_trans_b = true" in converted.read_text() and "abi_matmul_trans_a = false" in converted.read_text()

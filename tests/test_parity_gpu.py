@@ -359,6 +359,27 @@ def test_matmul_bias_leakyrelu_bf16(rt, M, N, K, mb):
     _matmul_check(rt, M, N, K, mb, seed=M + N + K)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (384, 768, 320), (100, 136, 72), (1, 8, 8), (130, 264, 1032), (1024, 1024, 1024),
+                                   (2048, 4096, 512)])
+@pytest.mark.parametrize("mb", [1, 2, 3])
+def test_matmul_with_b_given_as_n_by_k(rt, M, N, K, mb):
+    """out = A x B^T with B stored [N, K] (the layout of a torch Linear weight): the kernel loads K-major tiles of it.
+    Same oracle, fed the transpose; the two layouts must also agree with each other bit for bit (same products,
+    same accumulation order in the tensor core).  STAGES=3 asks for the CTA-pair kernel, which this layout
+    replaces by the single-CTA one."""
+    w = configs.matmul_add_leakyrelu(M, N, K, seed=M + N + K + 1)
+    a, b, bias = w.inputs
+    bt = np.ascontiguousarray(b.T)
+    spec_t = descriptors.matmul_bias_leakyrelu(transpose_b=True)
+    out_t = run(rt, spec_t, [a, bt, bias], w.new_output(), w.shape, STAGES=mb)
+    got = oracle.bf16_to_f32(out_t)
+    want = oracle.bf16_to_f32(oracle.matmul_bias_leakyrelu_bf16(a, b, bias, 0.01))
+    assert np.all(np.abs(got - want) <= 1e-2 * np.abs(want) + 1e-3)
+    assert np.mean(np.abs(got - want) <= 2.0 ** -8 * np.abs(want) + 1e-6) > 0.999
+    out_n = run(rt, w.spec, w.inputs, w.new_output(), w.shape, STAGES=min(mb, 2))
+    assert np.array_equal(out_t.view(np.uint16), out_n.view(np.uint16))
+
+
 def test_matmul_many_tiles_per_cta(rt):
     # more tiles than SMs: every CTA walks several tiles, both TMEM accumulators and all ring phases wrap
     _matmul_check(rt, 2048, 4096, 512, 1, seed=21)

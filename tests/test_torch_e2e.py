@@ -116,17 +116,17 @@ def test_transposed_views_clamp_and_abs(tmp_path):
     assert d["kernel_class"] == "elementwise" and [l["map"] for l in d["loads"]] == [[1, 0], [0, 1]]
     assert [o["op"] for o in d["body"]] == ["addf", "subf", "maximumf", "maximumf", "minimumf"]
 
-    class Bad(torch.nn.Module):
+    class Bare(torch.nn.Module):  # a permuted output is materialised by one copy group (a bare permutation)
         def forward(self, a):
             return a.t()
-    with pytest.raises(UnsupportedTorchOp, match="bare view"):
-        torch_to_linalg(Bad(), [torch.randn(4, 8)])
+    text = torch_to_linalg(Bare(), [torch.randn(4, 8)])
+    assert text.count("linalg.generic") == 1 and "linalg.yield %in0" in text and "-> tensor<8x4xf32>" in text
 
-    class BadSum(torch.nn.Module):
+    class Unit(torch.nn.Module):
         def forward(self, a):
-            return a.t().sum(dim=1)
-    with pytest.raises(UnsupportedTorchOp, match="materialised"):
-        torch_to_linalg(BadSum(), [torch.randn(4, 8)])
+            return a.unsqueeze(0)
+    with pytest.raises(UnsupportedTorchOp, match="inserted unit dimensions"):
+        torch_to_linalg(Unit(), [torch.randn(4, 8)])
 
 
 def test_unsupported_models_are_refused():
@@ -151,9 +151,37 @@ def test_unsupported_models_are_refused():
             return self.lin(x)
     with pytest.raises(UnsupportedTorchOp, match="parameters and buffers"):
         torch_to_linalg(WithState(), [torch.randn(4, 4)])
+    # the stateful entry point turns weight and bias into trailing arguments and keeps the weight as [N, K]
+    from ascend_mlir_b200.torch_e2e import torch_to_linalg_with_state
+    model = WithState()
+    text, state = torch_to_linalg_with_state(model, [torch.randn(6, 4)])
+    assert [n for n, _ in state] == ["lin.weight", "lin.bias"] and state[0][1].shape == (4, 4)
+    assert "func.func @forward(%arg0: tensor<6x4xf32>, %arg1: tensor<4x4xf32>, %arg2: tensor<4xf32>)" in text
+    assert "linalg.matmul_transpose_b ins(%arg0, %arg1 : tensor<6x4xf32>, tensor<4x4xf32>)" in text
 
     class Mixed(torch.nn.Module):
         def forward(self, a, b):
             return a + b
     with pytest.raises(UnsupportedTorchOp, match="mixed element types"):
         torch_to_linalg(Mixed(), [torch.randn(4, dtype=torch.float16), torch.randn(4, dtype=torch.float32)])
+
+
+def test_transposed_weight_and_materialised_permutations():
+    class MmT(torch.nn.Module):
+        def forward(self, a, w):
+            return torch.mm(a, w.t())
+    text = torch_to_linalg(MmT(), [torch.randn(8, 16).half(), torch.randn(12, 16).half()])
+    assert "linalg.matmul_transpose_b ins(%arg0, %arg1 : tensor<8x16xf16>, tensor<12x16xf16>)" in text
+    assert text.count("linalg.generic") == 1  # only the rounding epilogue: no copy of the weight
+
+    class Heads(torch.nn.Module):
+        def forward(self, x):
+            return x.permute(0, 2, 1, 3).contiguous()
+    text = torch_to_linalg(Heads(), [torch.randn(2, 3, 4, 8)])
+    assert "-> (d0, d2, d1, d3)>" in text and text.count("linalg.generic") == 1 and "tensor<2x4x3x8xf32>" in text
+
+    class BareView(torch.nn.Module):  # a permuted output is written out by one copy group
+        def forward(self, x):
+            return x.transpose(0, 1)
+    text = torch_to_linalg(BareView(), [torch.randn(5, 7)])
+    assert text.count("linalg.generic") == 1 and "-> tensor<7x5xf32>" in text

@@ -62,6 +62,31 @@ def test_addmm_leaky_relu():
                      TensorSpec((128,), torch.bfloat16)]
 
 
+@torch_e2e_test(verify_shapes={"M": 200}, atol=2e-2, rtol=2e-2)
+def test_linear_module_with_its_own_weights():
+    """torch.nn.Linear keeps its weight as [N, K]: the parameters become trailing kernel arguments and the matmul
+    reads the weight K-major, no transposed copy."""
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(3)
+            self.fc = torch.nn.Linear(256, 384).to(torch.bfloat16)
+
+        def forward(self, x):
+            return torch.nn.functional.leaky_relu(self.fc(x), 0.01)
+
+    return Model(), [TensorSpec(("M", 256), torch.bfloat16)]
+
+
+@torch_e2e_test(atol=0.0, rtol=0.0)
+def test_attention_heads_permutation():
+    class Model(torch.nn.Module):
+        def forward(self, x):
+            return x.permute(0, 2, 1, 3).contiguous()
+
+    return Model(), [TensorSpec((4, 24, 6, 64), torch.float16)]
+
+
 @torch_e2e_test(verify_shapes={"M": 264, "N": 520}, atol=0.0, rtol=0.0)
 def test_transposed_operand_clamp_abs():
     class Model(torch.nn.Module):
