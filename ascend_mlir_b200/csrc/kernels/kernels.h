@@ -193,6 +193,7 @@ int launchTranspose(const TransposeLaunch &l, cudaStream_t stream, int *launched
 // ---------------------------------------------------------------------------------------------
 enum EpilogueKind : int { kEpiNone = 0, kEpiBiasAdd = 1, kEpiBiasAddLeakyRelu = 2, kEpiBiasAddRelu = 3 };
 
+struct MatmulPlan;  // kernels/matmul_plan.h
 struct MatmulLaunch {
   int inType;    // kF16 or kBF16 (A and B)
   int outType;   // kF32, kF16 or kBF16
@@ -208,6 +209,7 @@ struct MatmulLaunch {
   int stages;      // 0 = default
   int bTransposed = 0;  // 1: out = A x B^T with B stored [N,K] (no counterpart in the reference, whose matmul takes
                         // no transposes; it is how torch.nn.Linear keeps its weight)
+  MatmulPlan *planOut = nullptr;  // receives the plan that was launched (variant, tile, grid, ...)
 };
 // errorText (optional, >= 256 bytes) receives a description when the launch is refused or the
 // kernel reports a bounded-wait timeout.

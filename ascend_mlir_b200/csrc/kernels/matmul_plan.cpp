@@ -1,0 +1,86 @@
+#include "kernels/matmul_plan.h"
+
+#include <algorithm>
+
+namespace afir {
+namespace kernels {
+namespace {
+
+constexpr int kTileN = 256, kTileK = 64;
+constexpr int kBStageBytes = kTileN * kTileK * 2;
+
+int64_t ceilDiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+} // namespace
+
+bool matmulPlannerSupports(const MatmulProblem &p) {
+  return p.M > 0 && p.N > 0 && p.K > 0 && p.batchShape.empty() && p.inElemBytes == 2 && p.M < (1ll << 31) && p.N < (1ll << 31) &&
+         p.K < (1ll << 31);
+}
+
+std::string buildMatmulPlan(const MatmulProblem &problem, const MatmulHints &hints, int smCount, MatmulPlan &plan) {
+  if (!problem.batchShape.empty()) return "matmul planner: batched problems are not supported";
+  if (problem.inElemBytes != 2) return "matmul planner: operands must be f16 or bf16";
+  if (!matmulPlannerSupports(problem)) return "matmul planner: M, N and K must be positive and below 2^31";
+  if (hints.variant < 0 || hints.variant > 3) return "matmul planner: variant hint must be 0 (choose), 1, 2 or 3";
+  if (smCount < 1) smCount = 1;
+
+  plan = MatmulPlan();
+  // 256-row tiles halve the operand bytes moved into shared memory per flop; they are the default whenever there
+  // are enough of them to give every SM one.  The CTA pair is never chosen by default (under the board's power cap
+  // it is no faster) and cannot take B as [N, K], whose tiles it would have to split along K-major rows.
+  const int64_t tiles256 = ceilDiv(problem.M, 256) * ceilDiv(problem.N, kTileN);
+  MatmulVariant v = tiles256 >= smCount ? MatmulVariant::Rows256 : MatmulVariant::Rows128;
+  if (hints.variant != 0) v = static_cast<MatmulVariant>(hints.variant);
+  if (v == MatmulVariant::CtaPair && problem.transposeB) v = MatmulVariant::Rows256;
+  plan.variant = v;
+  plan.tileN = kTileN;
+  plan.tileK = kTileK;
+  switch (v) {
+  case MatmulVariant::Rows128:
+    plan.tileM = 128; plan.stages = 4; plan.threads = 64 + 32 * 4;
+    plan.operandRingBytes = static_cast<size_t>(plan.stages) * (128 * kTileK * 2 + kBStageBytes);
+    plan.epilogueOverlapsMainloop = true;
+    break;
+  case MatmulVariant::Rows256:
+    plan.tileM = 256; plan.stages = 3; plan.threads = 64 + 32 * 8;
+    plan.operandRingBytes = static_cast<size_t>(plan.stages) * (256 * kTileK * 2 + kBStageBytes);
+    plan.epilogueOverlapsMainloop = false;
+    break;
+  case MatmulVariant::CtaPair:
+    plan.tileM = 256; plan.stages = 6; plan.threads = 192;
+    plan.operandRingBytes = static_cast<size_t>(plan.stages) * (128 * kTileK * 2 + kBStageBytes / 2);  // per CTA of the pair
+    plan.epilogueOverlapsMainloop = true;
+    break;
+  }
+  plan.tilesM = static_cast<int>(ceilDiv(problem.M, plan.tileM));
+  plan.tilesN = static_cast<int>(ceilDiv(problem.N, plan.tileN));
+  plan.kBlocks = static_cast<int>(ceilDiv(problem.K, plan.tileK));
+  plan.traverse = MatmulTraverse::FirstM;
+  plan.band = hints.band > 0 ? hints.band : (v == MatmulVariant::CtaPair ? 8 : 16);
+  const int64_t tiles = static_cast<int64_t>(plan.tilesM) * plan.tilesN;
+  int64_t ctas = hints.blockDim > 0 ? hints.blockDim : smCount;
+  if (v == MatmulVariant::CtaPair) {
+    // two CTAs per tile: an even grid, at most one pair per tile
+    ctas = std::min<int64_t>(ctas, 2 * tiles);
+    ctas = std::max<int64_t>(2, ctas - (ctas % 2));
+  } else {
+    ctas = std::max<int64_t>(1, std::min<int64_t>(ctas, tiles));
+  }
+  plan.blockDim = static_cast<uint32_t>(ctas);
+  plan.tmemColumns = 512;
+  return std::string();
+}
+
+std::string describeMatmulPlan(const MatmulPlan &p) {
+  const char *variant = p.variant == MatmulVariant::Rows128 ? "rows128" : p.variant == MatmulVariant::Rows256 ? "rows256" : "cta_pair";
+  return "planned_block_dim=" + std::to_string(p.blockDim) + " variant=" + variant + " traverse=" +
+         (p.traverse == MatmulTraverse::FirstN ? "FIRSTN" : "FIRSTM") + " band=" + std::to_string(p.band) + " tile=" +
+         std::to_string(p.tileM) + "x" + std::to_string(p.tileN) + "x" + std::to_string(p.tileK) + " stages=" +
+         std::to_string(p.stages) + " tiles=" + std::to_string(p.tilesM) + "x" + std::to_string(p.tilesN) + " k_blocks=" +
+         std::to_string(p.kBlocks) + " ring_bytes=" + std::to_string(p.operandRingBytes) + " tmem_cols=" +
+         std::to_string(p.tmemColumns) + " overlap_epilogue=" + (p.epilogueOverlapsMainloop ? "1" : "0");
+}
+
+} // namespace kernels
+} // namespace afir

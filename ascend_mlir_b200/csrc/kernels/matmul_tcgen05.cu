@@ -30,6 +30,7 @@
 #include <mutex>
 
 #include "kernels/kernels.h"
+#include "kernels/matmul_plan.h"
 
 namespace afir {
 namespace kernels {
@@ -813,13 +814,21 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   int device = 0;
   cudaGetDevice(&device);
   const int sms = deviceSmCount(device);
-  // Variant: 256-row tiles per CTA when they still fill the SMs; else 128-row tiles.
-  // l.stages forces one: 1 = 128-row single CTA, 2 = 256-row single CTA, 3 = CTA pair.
-  const int64_t tiles256 = ((l.M + 255) / 256) * ((l.N + kBlockN - 1) / kBlockN);
-  // (the pair kernel keeps the tensor pipe busier per clock but draws more power; under the board's power cap the
-  // single-CTA 256-row kernel sustains the higher throughput on B200, so the pair kernel is opt-in)
-  const bool pairKernel = l.stages == 3 && !l.bTransposed;  // the pair kernel splits N-major B tiles between its CTAs
-  const int mb = pairKernel ? 1 : (l.stages == 1) ? 1 : (l.stages == 2) ? 2 : (tiles256 >= sms ? 2 : 1);
+  // The plan (variant, grid, band) comes from the host planner; what follows launches exactly that.
+  // l.stages forces a variant: 1 = 128-row single CTA, 2 = 256-row single CTA, 3 = CTA pair.
+  MatmulProblem problem;
+  problem.M = l.M; problem.N = l.N; problem.K = l.K;
+  problem.transposeB = l.bTransposed != 0;
+  MatmulHints hints;
+  hints.variant = (l.stages >= 1 && l.stages <= 3) ? l.stages : 0;
+  hints.blockDim = l.gridBlocks > 0 ? l.gridBlocks : 0;
+  if (const char *e = std::getenv("AFIR_GEMM_BAND")) hints.band = std::max(1, std::atoi(e));
+  MatmulPlan plan;
+  const std::string refused = buildMatmulPlan(problem, hints, sms, plan);
+  if (!refused.empty()) { fail(errorText, refused.c_str()); return 1; }
+  if (l.planOut) *l.planOut = plan;
+  const bool pairKernel = plan.variant == MatmulVariant::CtaPair;
+  const int mb = plan.variant == MatmulVariant::Rows256 ? 2 : 1;
   const int tileM = 128 * mb;  // rows per TMA box of A (the pair kernel loads 128 rows per CTA)
   const CUtensorMapDataType dt = l.inType == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap mapA, mapB;
@@ -846,8 +855,7 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   p.biasType = l.biasType;
   p.epilogue = l.epilogue;
   p.alpha = l.alpha;
-  p.band = pairKernel ? 8 : 16;
-  if (const char *e = std::getenv("AFIR_GEMM_BAND")) p.band = std::max(1, std::atoi(e));
+  p.band = plan.band;
   const unsigned int fmt = l.inType == kF16 ? 0u : 1u;
   // instruction descriptor: D=f32, A/B format, A K-major, B N-major, N=256, M=128 (256 across a CTA pair)
   const unsigned int instrM = pairKernel ? 256u : 128u;
@@ -855,15 +863,10 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   const unsigned int bMajor = l.bTransposed ? 0u : 1u;  // bit 16: 0 = B K-major, 1 = B N-major
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (bMajor << 16) | ((kBlockN >> 3) << 17) | ((instrM >> 4) << 24);
 
-  const int64_t numTiles = static_cast<int64_t>(p.numTilesM) * p.numTilesN;
-  int grid = l.gridBlocks > 0 ? l.gridBlocks : sms;
-  grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, numTiles)));
+  const int grid = static_cast<int>(plan.blockDim);
 
   int rc;
   if (pairKernel) {
-    grid = l.gridBlocks > 0 ? l.gridBlocks : sms;
-    grid = static_cast<int>(std::min<int64_t>(grid, 2 * numTiles)) & ~1;  // whole pairs
-    if (grid < 2) grid = 2;
     rc = l.outType == kF32 ? launchPairVariant<kF32>(mapA, mapB, p, grid, stream, errorText)
          : l.outType == kF16 ? launchPairVariant<kF16>(mapA, mapB, p, grid, stream, errorText)
                              : launchPairVariant<kBF16>(mapA, mapB, p, grid, stream, errorText);

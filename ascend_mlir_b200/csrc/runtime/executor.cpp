@@ -279,6 +279,7 @@ Status CudaExecutor::runHost(const RunRequest &req) {
     cudaStreamSynchronize(stream);
     return launchStage(ls);
   }
+  if (launchTraceEnabled() && !info.plan.empty()) std::fprintf(stderr, "[cuda-launch] matmul plan: %s\n", info.plan.c_str());
   for (int i = 0; i < req.numOutputs; ++i) {
     if (!req.outputBytes[i]) continue;
     e = cudaMemcpyAsync(req.outputPtrs[i], args.argPtrs[req.numInputs + i], req.outputBytes[i], cudaMemcpyDeviceToHost, stream);
@@ -353,6 +354,8 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
     lastLaunchCount_ += info.kernelsLaunched;
     totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
     usesStatus = usesStatus || info.usesStatusBlock;
+    if (c == 0 && launchTraceEnabled() && !info.plan.empty())
+      std::fprintf(stderr, "[cuda-launch] matmul plan (first of the row chunks): %s\n", info.plan.c_str());
     if (!ls) {
       cudaStreamSynchronize(in);
       cudaStreamSynchronize(compute);
@@ -432,6 +435,7 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   lastLaunchCount_ = info.kernelsLaunched;
   totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
   if (!ls) return launchStage(ls);
+  if (launchTraceEnabled() && !info.plan.empty()) std::fprintf(stderr, "[cuda-launch] matmul plan: %s\n", info.plan.c_str());
   statusPending_ = info.usesStatusBlock;
   statusWorkspace_ = args.workspace;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;

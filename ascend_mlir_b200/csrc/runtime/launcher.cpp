@@ -1,4 +1,5 @@
 #include "runtime/launcher.h"
+#include "kernels/matmul_plan.h"
 
 #include <algorithm>
 #include <cstring>
@@ -436,9 +437,12 @@ Status launchMatmulDescriptor(const LaunchDescriptor &d, const std::map<std::str
   l.stages = static_cast<int>(optionalField(d.stagesField, tiling));
   int n = 0;
   char text[256] = {0};
+  kernels::MatmulPlan plan;
+  l.planOut = &plan;
   const int code = kernels::launchMatmul(l, args.stream, &n, text);
   info.kernelsLaunched += n;
   if (code != 0) return Status::error(text[0] ? std::string(text) : std::string("matmul launch: ") + kernels::cudaErrorText(code));
+  if (n > 0) info.plan = kernels::describeMatmulPlan(plan);
   return Status::success();
 }
 

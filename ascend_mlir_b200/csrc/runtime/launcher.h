@@ -36,6 +36,7 @@ struct LaunchArgs {
 struct LaunchInfo {
   int kernelsLaunched = 0;
   bool usesStatusBlock = false;  // caller should zero it before and check it after
+  std::string plan;              // matmul: the planner's one-line description of what was launched
 };
 
 // Scratch bytes (status block included) the descriptor needs at these tiling values.

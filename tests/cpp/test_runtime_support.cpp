@@ -15,6 +15,7 @@
 #include "execution/execution_session.h"
 #include "execution/profile_retention.h"
 #include "execution/run_manifest.h"
+#include "kernels/matmul_plan.h"
 #include "support/npy_io.h"
 #include "support/tiling_schema.h"
 
@@ -309,6 +310,56 @@ static void testProfileRetention() {
          "preparing for a new session leaves limit - 1 directories");
 }
 
+// The planner behaviours the reference pins in test/unittests/Runtime/NativeMatmulPlannerTest.cpp:25-100 (default
+// plan, hints honoured, batches refused, the plan is what gets applied, a deterministic description), for the
+// B200 kernel's choices.
+static void testMatmulPlanner() {
+  using namespace afir::kernels;
+  MatmulProblem big;
+  big.M = big.N = big.K = 8192;
+  MatmulPlan plan;
+  EXPECT(matmulPlannerSupports(big), "8192^3 is supported");
+  EXPECT(buildMatmulPlan(big, MatmulHints(), 148, plan).empty(), "default plan builds");
+  EXPECT(plan.variant == MatmulVariant::Rows256 && plan.tileM == 256 && plan.tileN == 256 && plan.tileK == 64, "enough 256-row tiles: 256x256x64");
+  EXPECT(plan.stages == 3 && plan.tilesM == 32 && plan.tilesN == 32 && plan.kBlocks == 128, "tile counts and ring depth");
+  EXPECT(plan.blockDim == 148 && plan.band == 16 && plan.traverse == MatmulTraverse::FirstM, "one persistent CTA per SM, M first in bands of 16");
+  EXPECT(plan.operandRingBytes == 3u * 65536u && plan.tmemColumns == 512 && !plan.epilogueOverlapsMainloop, "3 x 64 KB stages, all of tensor memory");
+  EXPECT(describeMatmulPlan(plan) == "planned_block_dim=148 variant=rows256 traverse=FIRSTM band=16 tile=256x256x64 stages=3 tiles=32x32 "
+                                     "k_blocks=128 ring_bytes=196608 tmem_cols=512 overlap_epilogue=0",
+         "description is stable: " + describeMatmulPlan(plan));
+  MatmulPlan again;
+  buildMatmulPlan(big, MatmulHints(), 148, again);
+  EXPECT(describeMatmulPlan(again) == describeMatmulPlan(plan), "same problem, same description");
+
+  MatmulProblem small;
+  small.M = 1024; small.N = 2048; small.K = 320;
+  EXPECT(buildMatmulPlan(small, MatmulHints(), 148, plan).empty(), "small plan builds");
+  EXPECT(plan.variant == MatmulVariant::Rows128 && plan.stages == 4 && plan.epilogueOverlapsMainloop, "too few 256-row tiles: 128-row tiles, double-buffered accumulators");
+  EXPECT(plan.tilesM == 8 && plan.tilesN == 8 && plan.kBlocks == 5 && plan.blockDim == 64, "grid capped by the number of tiles");
+
+  MatmulHints hints;
+  hints.variant = 3; hints.blockDim = 40; hints.band = 4;
+  EXPECT(buildMatmulPlan(big, hints, 148, plan).empty(), "hinted plan builds");
+  EXPECT(plan.variant == MatmulVariant::CtaPair && plan.blockDim == 40 && plan.band == 4 && plan.stages == 6, "hints are honoured");
+  hints.blockDim = 41;
+  buildMatmulPlan(big, hints, 148, plan);
+  EXPECT(plan.blockDim == 40, "a CTA pair grid is even");
+  big.transposeB = true;
+  buildMatmulPlan(big, hints, 148, plan);
+  EXPECT(plan.variant == MatmulVariant::Rows256, "B as [N, K] does not take the CTA pair");
+  big.transposeB = false;
+
+  MatmulProblem batched = big;
+  batched.batchShape = {4};
+  EXPECT(!matmulPlannerSupports(batched), "batched problems are unsupported");
+  EXPECT(buildMatmulPlan(batched, MatmulHints(), 148, plan).find("batched") != std::string::npos, "and refused with a reason");
+  MatmulProblem empty;
+  EXPECT(!buildMatmulPlan(empty, MatmulHints(), 148, plan).empty(), "zero extents are refused");
+  hints = MatmulHints();
+  hints.variant = 7;
+  EXPECT(!buildMatmulPlan(big, hints, 148, plan).empty(), "an unknown variant hint is refused");
+}
+
 int main() {
   char tmpl[] = "/tmp/afir-runtime-test-XXXXXX";
   if (!::mkdtemp(tmpl)) return 99;
@@ -319,6 +370,7 @@ int main() {
   testTaskGraph();
   testManifestAndSession();
   testProfileRetention();
+  testMatmulPlanner();
   std::cout << g_pass << " passed, " << g_fail << " failed\n";
   return g_fail;
 }

@@ -380,6 +380,18 @@ def test_matmul_with_b_given_as_n_by_k(rt, M, N, K, mb):
     assert np.array_equal(out_t.view(np.uint16), out_n.view(np.uint16))
 
 
+def test_launch_trace_carries_the_matmul_plan(rt, monkeypatch, capfd):
+    """With launch tracing on, the planner's one-line description of what was launched follows the argument lines."""
+    monkeypatch.setenv("AFIR_CUDA_TRACE_LAUNCH", "1")
+    w = configs.matmul_add_leakyrelu(384, 768, 320, seed=5)
+    run(rt, w.spec, w.inputs, w.new_output(), w.shape)
+    err = capfd.readouterr().err
+    assert "[cuda-launch] kernel=matmul_add_leakyrelu " in err
+    plan = [l for l in err.splitlines() if "matmul plan" in l]
+    assert plan and "variant=rows128" in plan[0] and "tile=128x256x64" in plan[0] and "tiles=3x3" in plan[0] and "k_blocks=5" in plan[0]
+    assert "planned_block_dim=9 " in plan[0]
+
+
 def test_matmul_many_tiles_per_cta(rt):
     # more tiles than SMs: every CTA walks several tiles, both TMEM accumulators and all ring phases wrap
     _matmul_check(rt, 2048, 4096, 512, 1, seed=21)
