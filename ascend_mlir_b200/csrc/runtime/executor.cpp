@@ -131,6 +131,16 @@ static bool launchTraceEnabled() {
   return false;
 }
 
+// First bytes of a buffer as hex, the reference's printNativeLaunchBufferSample line
+// (lib/Runtime/Execution/LaunchTrace.cpp:93-101; 64 bytes, NativeExecutionRunner.cpp:63).
+static constexpr size_t kLaunchTraceSampleBytes = 64;
+static void printBufferSample(const std::string &label, const unsigned char *bytes, size_t sampleBytes, size_t totalBytes) {
+  std::string hex;
+  static const char digits[] = "0123456789abcdef";
+  for (size_t i = 0; i < sampleBytes; ++i) { hex += digits[bytes[i] >> 4]; hex += digits[bytes[i] & 15]; }
+  std::fprintf(stderr, "[cuda-launch] %s bytes=%zu sample_bytes=%zu sample_hex=%s\n", label.c_str(), totalBytes, sampleBytes, hex.c_str());
+}
+
 static void printLaunchTrace(const RunRequest &req, const LaunchDescriptor &desc, const LaunchArgs &args, int device, const char *path) {
   auto ptr = [](const void *p) {
     char buf[64];
@@ -245,7 +255,8 @@ Status CudaExecutor::runHost(const RunRequest &req) {
     if (Status s = planRowPipeline(*desc, tiling, args.argBytes, plan); !s) return s.withStage("cuda:bindings");
     size_t total = 0;
     for (size_t b : args.argBytes) total += b;
-    if (plan.possible && total >= (16u << 20) && plan.rows >= 2 && !std::getenv("AFIR_CUDA_NO_PIPELINE")) {
+    // (not while tracing: the trace samples every buffer right after its copy, which wants the three plain phases)
+    if (plan.possible && total >= (16u << 20) && plan.rows >= 2 && !std::getenv("AFIR_CUDA_NO_PIPELINE") && !launchTraceEnabled()) {
       const int64_t quantum = desc->kernelClass == KernelClass::Matmul ? 256 : (plan.rows >= 64 ? 8 : 1);
       // Chunks of about 16 MiB of sliced bytes, 4 to 12 of them: the copy-in stream never idles, so the time
       // not hidden is one chunk's kernel and copy-out at the end; smaller chunks shorten that tail until the
@@ -267,6 +278,19 @@ Status CudaExecutor::runHost(const RunRequest &req) {
     if (!req.inputBytes[i]) continue;
     e = cudaMemcpyAsync(args.argPtrs[i], req.inputPtrs[i], req.inputBytes[i], cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] host-to-device copy failed");
+    if (launchTraceEnabled()) {
+      // what the host handed over, and the same bytes read back from the device (reference
+      // NativeExecutionRunner.cpp:391-416: input[i].host, h2d_roundtrip match=..., input[i].h2d_roundtrip)
+      const size_t sample = std::min(req.inputBytes[i], kLaunchTraceSampleBytes);
+      const unsigned char *host = static_cast<const unsigned char *>(req.inputPtrs[i]);
+      printBufferSample("input[" + std::to_string(i) + "].host", host, sample, req.inputBytes[i]);
+      unsigned char back[kLaunchTraceSampleBytes] = {0};
+      e = cudaMemcpyAsync(back, args.argPtrs[i], sample, cudaMemcpyDeviceToHost, stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+      if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] trace read-back failed");
+      std::fprintf(stderr, "[cuda-launch] input[%d].h2d_roundtrip match=%s\n", i, std::memcmp(back, host, sample) == 0 ? "yes" : "no");
+      printBufferSample("input[" + std::to_string(i) + "].h2d_roundtrip", back, sample, req.inputBytes[i]);
+    }
   }
   e = cudaMemsetAsync(workspace_.ptr, 0, kWorkspaceStatusBytes, stream);
   if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] workspace clear failed");
@@ -290,6 +314,10 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
   reducePending_ = desc->kernelClass == KernelClass::RowReduce;
   Status done = synchronize(stream_);
+  if (done && launchTraceEnabled())
+    for (int i = 0; i < req.numOutputs; ++i)
+      printBufferSample("output[" + std::to_string(i) + "].host_after_d2h", static_cast<const unsigned char *>(req.outputPtrs[i]),
+                        std::min(req.outputBytes[i], kLaunchTraceSampleBytes), req.outputBytes[i]);
   Status guards = verifyGuards();
   return done ? guards : done;
 }

@@ -94,6 +94,14 @@ def test_two_task_graph_validates_and_profiles(tmp_path):
     assert any(l.startswith("[cuda-launch] input[1] bytes=%d ptr=0x" % (M * N * 4)) and "align512=yes" in l for l in traced)
     assert f"[cuda-launch] tiling.word[2]={M} dim_arg0_0" in traced and f"[cuda-launch] tiling.word[3]={N} dim_arg0_1" in traced
     assert any(l.startswith("[cuda-launch] kernel=broadcast_add_reducesum ") for l in traced)
+    # buffer samples: what the host handed over, the same bytes read back from the device, the output after its copy
+    samples = [l for l in traced if "sample_hex=" in l]
+    first = next(l for l in samples if l.startswith("[cuda-launch] input[0].host "))
+    assert f"bytes={M * N * 4} sample_bytes=64 sample_hex=" in first and len(first.rsplit("=", 1)[1]) == 128
+    back = next(l for l in samples if l.startswith("[cuda-launch] input[0].h2d_roundtrip "))
+    assert back.rsplit("=", 1)[1] == first.rsplit("=", 1)[1]
+    assert "[cuda-launch] input[0].h2d_roundtrip match=yes" in traced and "[cuda-launch] input[1].h2d_roundtrip match=yes" in traced
+    assert any(l.startswith("[cuda-launch] output[0].host_after_d2h ") for l in samples)
 
     # a wrong expectation fails in the validate stage with exit code 2
     np.save(tmp_path / "prod.npy", prod + 1.0)
