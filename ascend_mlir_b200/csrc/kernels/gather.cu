@@ -38,6 +38,11 @@ struct GaParams {
   FastDiv divVpr;
   unsigned long long *status;
   BodyProgram prog;
+  // SHARDED kernels: the table's rows are split into contiguous shards of rowsPerShard rows, shard s at
+  // shardBase[s], which may be another GPU's memory (peer-mapped; read with plain loads over NVLink)
+  const char *shardBase[kMaxTableShards];
+  long long rowsPerShard;
+  FastDiv divRowsPerShard;  // valid when the table has fewer than 2^32 rows
 };
 
 __device__ __forceinline__ long long loadIndex(const void *idx, long long i, int is64) {
@@ -54,7 +59,7 @@ template <> __device__ __forceinline__ void storeOne<PackBF16>(void *p, PackBF16
 }
 
 // ---- axis 0 ------------------------------------------------------------------------------------
-template <class P, int BODY, int UNROLL, bool VECTOR>
+template <class P, int BODY, int UNROLL, bool VECTOR, bool SHARDED = false>
 __global__ void __launch_bounds__(512) gatherRowsKernel(const __grid_constant__ GaParams prm) {
   using B = Body<BODY>;
   constexpr int NV = B::kViews;
@@ -83,7 +88,14 @@ __global__ void __launch_bounds__(512) gatherRowsKernel(const __grid_constant__ 
         live[u] = false;
       }
       if (live[u]) {
-        const char *t = prm.table + (src[u] * prm.tableRowStride + static_cast<long long>(col[u]) * kElems) * kElemBytes;
+        const char *t;
+        if (SHARDED) {
+          const unsigned int shard = fastDivide(static_cast<unsigned int>(src[u]), prm.divRowsPerShard);
+          const long long local = src[u] - static_cast<long long>(shard) * prm.rowsPerShard;
+          t = prm.shardBase[shard] + (local * prm.tableRowStride + static_cast<long long>(col[u]) * kElems) * kElemBytes;
+        } else {
+          t = prm.table + (src[u] * prm.tableRowStride + static_cast<long long>(col[u]) * kElems) * kElemBytes;
+        }
         if (VECTOR) raw[u][0] = loadStream16(t);
         else {
           const unsigned int s = P::splat(t).bits();
@@ -459,6 +471,12 @@ template <class P, int BODY> KernelFn pickRowsUnroll(int unroll, bool vector) {
   return unroll >= 4 ? gatherRowsKernel<P, BODY, 4, true> : unroll >= 2 ? gatherRowsKernel<P, BODY, 2, true>
                                                                         : gatherRowsKernel<P, BODY, 1, true>;
 }
+// Sharded tables are NVLink-bound: the copy body and the interpreted one, two vectors in flight per thread.
+template <class P> KernelFn pickRowsSharded(int body, bool vector) {
+  if (!vector) return gatherRowsKernel<P, kBodyInterpreted, 2, false, true>;
+  return body == kBodyCopy ? gatherRowsKernel<P, kBodyCopy, 2, true, true> : gatherRowsKernel<P, kBodyInterpreted, 2, true, true>;
+}
+
 template <class P> KernelFn pickRows(int body, int unroll, bool vector) {
   switch (body) {
   case kBodyCopy: return pickRowsUnroll<P, kBodyCopy>(unroll, vector);
@@ -515,13 +533,27 @@ int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched) {
   p.status = l.status;
   p.prog = l.body;
 
+  bool shardsAligned = true;
+  if (l.numShards > 0) {
+    if (l.axis != 0 || l.numShards > kMaxTableShards || l.rowsPerShard <= 0 || l.tableRows >= (1ll << 32) ||
+        l.rowsPerShard * l.numShards < l.tableRows)
+      return cudaErrorInvalidValue;
+    for (int sh = 0; sh < l.numShards; ++sh) {
+      if (!l.tableShards[sh]) return cudaErrorInvalidValue;
+      p.shardBase[sh] = static_cast<const char *>(l.tableShards[sh]);
+      shardsAligned = shardsAligned && aligned16(l.tableShards[sh]);
+    }
+    p.rowsPerShard = l.rowsPerShard;
+    p.divRowsPerShard = makeFastDiv(static_cast<unsigned int>(std::min<int64_t>(l.rowsPerShard, 0xffffffffll)));
+  }
+
   int threads = l.ctaThreads > 0 ? l.ctaThreads : 128;
   threads = std::max(32, std::min(512, (threads / 32) * 32));
   const int body = matchBody(l.body, l.numViews);
   KernelFn fn;
   int64_t totalVec, numTiles;
   if (l.axis == 0) {
-    bool vector = l.cols % vecElems == 0 && aligned16(l.table) && l.tableRowStride % vecElems == 0 &&
+    bool vector = l.cols % vecElems == 0 && (l.numShards > 0 ? shardsAligned : aligned16(l.table)) && l.tableRowStride % vecElems == 0 &&
                   aligned16(l.out) && l.outRowStride % vecElems == 0;
     for (int k = 1; k < l.numViews && vector; ++k) {
       if (l.views[k].colStride == 1) vector = aligned16(l.views[k].base) && l.views[k].rowStride % vecElems == 0;
@@ -529,7 +561,7 @@ int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched) {
     }
     // Bulk-copy staged kernel, on request only: aligned rows of 128 bytes to 16 KB, every other view either one
     // row per output row or one row for all, enough chunks to give every warp of the machine a few.
-    if (vector && l.stagedCopies) {
+    if (vector && l.stagedCopies && l.numShards == 0) {
       const int64_t rowBytes = l.cols * eb;
       int numStreamed = 0;
       bool eligible = rowBytes >= 128 && rowBytes <= 16384 && (l.tableRowStride * eb) % 16 == 0 && (l.outRowStride * eb) % 16 == 0;
@@ -603,6 +635,12 @@ int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched) {
     fn = l.elemType == kF32 ? pickRows<PackF32>(body, unroll, vector)
          : l.elemType == kF16 ? pickRows<PackF16>(body, unroll, vector)
                               : pickRows<PackBF16>(body, unroll, vector);
+    if (l.numShards > 0) {
+      unroll = 2;
+      fn = l.elemType == kF32 ? pickRowsSharded<PackF32>(body, vector)
+           : l.elemType == kF16 ? pickRowsSharded<PackF16>(body, vector)
+                                : pickRowsSharded<PackBF16>(body, vector);
+    }
     const int64_t tileVecs = static_cast<int64_t>(threads) * unroll;
     numTiles = (totalVec + tileVecs - 1) / tileVecs;
   } else {

@@ -144,6 +144,7 @@ int rowReduceCheckStatus(int device, char *errorText);
 // of the body; views[1..] are ordinary (row, col) views.  Out-of-range indices leave the output
 // element(s) untouched and raise *status (a device int64 counter) by one per bad index read.
 // ---------------------------------------------------------------------------------------------
+constexpr int kMaxTableShards = 8;
 struct GatherLaunch {
   int elemType;
   int axis;
@@ -165,6 +166,13 @@ struct GatherLaunch {
   int streamStages = 0;            // ring depth per warp, 2..8 (0 = 3)
   int streamRows = 0;              // rows per stage, 1..32 (0 = about 4 KB worth)
   int streamWarps = 0;             // warps per CTA, 1..16 (0 = 8)
+  // Row gather from a table whose rows are split over several buffers (a table larger than one GPU's memory,
+  // sharded over the GPUs of a node): shard s holds rows [s * rowsPerShard, (s + 1) * rowsPerShard) at
+  // tableShards[s] with the same row stride; the pointers may be peer-mapped memory of other GPUs, read with plain
+  // loads.  numShards = 0: the single `table` above.
+  int numShards = 0;
+  const void *tableShards[kMaxTableShards] = {nullptr};
+  int64_t rowsPerShard = 0;
 };
 int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched);
 

@@ -188,6 +188,27 @@ AFIR_EXPORT int afirt_executor_launch_device_exchange(AfirtExecutor executor, co
   return 0;
 }
 
+AFIR_EXPORT int afirt_executor_launch_device_sharded_table(AfirtExecutor executor, const uint8_t *binary_data, size_t binary_len,
+                                                           const char *function_name, int num_inputs, const void **input_ptrs,
+                                                           const size_t *input_bytes, int num_outputs, void **output_ptrs,
+                                                           const size_t *output_bytes, const uint8_t *tiling_data, size_t tiling_len,
+                                                           int block_dim, uint32_t magic, void *workspace, size_t workspace_bytes,
+                                                           void *cuda_stream, int num_shards, const void **shard_ptrs,
+                                                           int64_t rows_per_shard, char *err_buf, size_t err_len) {
+  auto *ex = reinterpret_cast<CudaExecutor *>(executor);
+  if (!ex || !ex->initialized()) { writeErr(err_buf, err_len, "executor has not been initialized"); return 1; }
+  if (num_shards < 1 || !shard_ptrs) { writeErr(err_buf, err_len, "at least one table shard is required"); return 1; }
+  if (rows_per_shard < 1) { writeErr(err_buf, err_len, "rows_per_shard must be positive"); return 1; }
+  std::vector<const void *> shards(shard_ptrs, shard_ptrs + num_shards);
+  RunRequest r = makeRequest(binary_data, binary_len, function_name, num_inputs, input_ptrs, input_bytes, num_outputs,
+                             output_ptrs, output_bytes, tiling_data, tiling_len, block_dim, magic);
+  if (Status s = ex->launchDevice(r, workspace, workspace_bytes, cuda_stream, nullptr, shards, rows_per_shard); !s) {
+    writeErr(err_buf, err_len, s.message());
+    return 1;
+  }
+  return 0;
+}
+
 AFIR_EXPORT int afirt_executor_synchronize(AfirtExecutor executor, void *cuda_stream, char *err_buf, size_t err_len) {
   auto *ex = reinterpret_cast<CudaExecutor *>(executor);
   if (!ex || !ex->initialized()) { writeErr(err_buf, err_len, "executor has not been initialized"); return 1; }

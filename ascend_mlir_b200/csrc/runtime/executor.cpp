@@ -423,7 +423,8 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
 }
 
 Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream,
-                                  const kernels::RowReduceExchange *exchange) {
+                                  const kernels::RowReduceExchange *exchange, const std::vector<const void *> &tableShards,
+                                  int64_t rowsPerShard) {
   std::shared_ptr<const LaunchDescriptor> desc;
   std::map<std::string, int64_t> tiling;
   if (Status s = validate(req, desc, tiling); !s) return s;
@@ -435,6 +436,8 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   args.stream = static_cast<cudaStream_t>(stream);
   args.blockDim = req.blockDim;
   args.exchange = exchange;
+  args.tableShards = tableShards;
+  args.rowsPerShard = rowsPerShard;
   for (int i = 0; i < req.numInputs; ++i) {
     args.argPtrs.push_back(const_cast<void *>(req.inputPtrs[i]));
     args.argBytes.push_back(req.inputBytes[i]);

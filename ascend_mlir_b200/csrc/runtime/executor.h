@@ -52,8 +52,11 @@ public:
   // Device-pointer path: validates and enqueues the launch on `stream` and returns.
   // exchange: not null for a row-reduction group whose reduced axis is sharded over GPUs (the kernel then
   // exchanges its partial sums through that mailbox record)
+  // tableShards / rowsPerShard: not empty for a row-gather group whose table is given as row shards (possibly
+  // other GPUs' memory, peer-mapped) instead of its one argument
   Status launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream,
-                      const kernels::RowReduceExchange *exchange = nullptr);
+                      const kernels::RowReduceExchange *exchange = nullptr,
+                      const std::vector<const void *> &tableShards = {}, int64_t rowsPerShard = 0);
   // Waits for `stream` (null = the executor's own) and surfaces device-side status words.
   Status synchronize(void *stream);
 

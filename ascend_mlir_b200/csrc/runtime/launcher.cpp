@@ -331,6 +331,22 @@ Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const st
   l.tableRows = tshape[0];
   l.tableCols = tshape[1];
   l.tableRowStride = tshape[1];
+  if (!args.tableShards.empty()) {
+    if (g.gatherAxis != 0) return Status::error("a sharded table needs a row gather");
+    if (args.tableShards.size() > static_cast<size_t>(kernels::kMaxTableShards))
+      return Status::error("a table takes at most " + std::to_string(kernels::kMaxTableShards) + " shards");
+    if (args.rowsPerShard <= 0 || args.rowsPerShard * static_cast<int64_t>(args.tableShards.size()) < tshape[0])
+      return Status::error("table shards: " + std::to_string(args.tableShards.size()) + " shards of " + std::to_string(args.rowsPerShard) +
+                           " rows do not cover the table's " + std::to_string(tshape[0]) + " rows");
+    if (tshape[0] >= (1ll << 32)) return Status::error("a sharded table has fewer than 2^32 rows");
+    l.numShards = static_cast<int>(args.tableShards.size());
+    for (int sh = 0; sh < l.numShards; ++sh) {
+      if (!args.tableShards[sh]) return Status::error("table shard " + std::to_string(sh) + " is null");
+      l.tableShards[sh] = args.tableShards[sh];
+    }
+    l.rowsPerShard = args.rowsPerShard;
+    l.table = nullptr;
+  }
   l.indices = args.argPtrs[g.indices.arg];
   if (g.gatherAxis == 0)
     l.indices = static_cast<const char *>(l.indices) + static_cast<size_t>(rowShift) * dtypeBytes(g.indices.dtype);
@@ -473,6 +489,8 @@ Status launchDescriptor(const LaunchDescriptor &d, const std::map<std::string, i
                          std::to_string(d.numOutputs) + " outputs");
   if (args.exchange && (d.kernelClass != KernelClass::RowReduce || d.groups.size() != 1))
     return Status::error("only a single row-reduction group exchanges partial sums between GPUs");
+  if (!args.tableShards.empty() && (d.kernelClass != KernelClass::Gather || d.groups.size() != 1))
+    return Status::error("only a single gather group takes a sharded table");
   if (d.kernelClass == KernelClass::Matmul) return launchMatmulDescriptor(d, tiling, args, info);
   for (const auto &g : d.groups) {
     Status s;

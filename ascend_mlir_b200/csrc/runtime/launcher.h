@@ -31,6 +31,10 @@ struct LaunchArgs {
   // Row-reduction groups only: the reduced axis is sharded over GPUs and the kernel exchanges its partial sums
   // through this mailbox record (see kernels::RowReduceExchange); null = an ordinary launch.
   const kernels::RowReduceExchange *exchange = nullptr;
+  // Row-gather groups only: the table argument is given as row shards instead (possibly other GPUs' memory,
+  // peer-mapped).  Its entry in argPtrs is ignored (may be null); its entry in argBytes is the whole table's size.
+  std::vector<const void *> tableShards;
+  int64_t rowsPerShard = 0;
 };
 
 struct LaunchInfo {

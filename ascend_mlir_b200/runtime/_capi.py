@@ -21,7 +21,10 @@ EXPORTS = [
     "afirt_bcast_add_rowsum_no_alloc",
     "afirt_rowsum_exchange_create", "afirt_rowsum_exchange_connect", "afirt_bcast_add_rowsum_exchange",
     "afirt_rowsum_exchange_status", "afirt_rowsum_exchange_destroy", "afirt_executor_launch_device_exchange",
+    "afirt_executor_launch_device_sharded_table", "afirt_peer_export", "afirt_peer_import", "afirt_peer_release",
 ]
+
+PEER_HANDLE_BYTES = 96  # AFIRT_PEER_HANDLE_BYTES
 
 EXCHANGE_HANDLE_BYTES = 96  # AFIRT_EXCHANGE_HANDLE_BYTES
 
@@ -69,6 +72,16 @@ def get_lib() -> ctypes.CDLL:
                                                     ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
                                                     ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
     lib.afirt_bcast_add_rowsum_no_alloc.restype = ctypes.c_int
+    lib.afirt_executor_launch_device_sharded_table.argtypes = ([ctypes.c_void_p, _u8p, ctypes.c_size_t] + _RUN_TAIL +
+                                                               [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_int, _vpp,
+                                                                ctypes.c_int64, ctypes.c_char_p, ctypes.c_size_t])
+    lib.afirt_executor_launch_device_sharded_table.restype = ctypes.c_int
+    lib.afirt_peer_export.argtypes = [ctypes.c_void_p, _u8p, ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_peer_export.restype = ctypes.c_int
+    lib.afirt_peer_import.argtypes = [ctypes.c_int, _u8p, _vpp, ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_peer_import.restype = ctypes.c_int
+    lib.afirt_peer_release.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_peer_release.restype = ctypes.c_int
     lib.afirt_rowsum_exchange_create.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, _vpp, _u8p,
                                                  ctypes.c_char_p, ctypes.c_size_t]
     lib.afirt_rowsum_exchange_create.restype = ctypes.c_int

@@ -106,11 +106,13 @@ class CudaRuntime:
     def launch_device(self, binary_data: bytes, function_name: str, inputs: Sequence[Tuple[int, int]],
                       outputs: Sequence[Tuple[int, int]], tiling_data: Optional[bytes] = None, block_dim: int = 0,
                       magic: int = MAGIC_ELF_AIVEC, workspace: Tuple[int, int] = (0, 0), stream: int = 0,
-                      exchange=None) -> None:
+                      exchange=None, table_shards=None, rows_per_shard: int = 0) -> None:
         """Enqueue on `stream` (a cudaStream_t as int); inputs/outputs are (device address, nbytes).
 
         `exchange` (a connected sharding.RowsumExchange) makes a row-reduction group exchange its partial sums with
-        the other ranks inside the kernel: the arguments are this rank's column slice, the output the full sums."""
+        the other ranks inside the kernel: the arguments are this rank's column slice, the output the full sums.
+        `table_shards` (device addresses, other GPUs' memory included) with `rows_per_shard` gives the table of a
+        row-gather group as row shards; the table's own entry in `inputs` then only carries the whole table's size."""
         lib = get_lib()
         bin_ptr, bin_len, _k1 = self._binary(binary_data)
         til_ptr, til_len, _k2 = _u8(tiling_data)
@@ -122,7 +124,10 @@ class CudaRuntime:
         head = (ctypes.c_void_p(self._handle), bin_ptr, bin_len, function_name.encode(), len(inputs), in_ptrs, in_bytes,
                 len(outputs), out_ptrs, out_bytes, til_ptr, til_len, block_dim, magic, ctypes.c_void_p(workspace[0]),
                 workspace[1], ctypes.c_void_p(stream))
-        if exchange is None:
+        if table_shards is not None:
+            shards = (ctypes.c_void_p * len(table_shards))(*table_shards)
+            ret = lib.afirt_executor_launch_device_sharded_table(*head, len(table_shards), shards, rows_per_shard, err, len(err))
+        elif exchange is None:
             ret = lib.afirt_executor_launch_device(*head, err, len(err))
         else:
             ret = lib.afirt_executor_launch_device_exchange(*head, exchange.pointer, err, len(err))

@@ -146,3 +146,68 @@ class RowsumExchange:
         if self._ptr:
             self._lib.afirt_rowsum_exchange_destroy(self._ptr)
             self._ptr = self._ct.c_void_p()
+
+
+# ---- operands on other GPUs of the node: afirt_peer_* of the C-ABI library ----------------------------------------
+def export_peer(device_ptr: int) -> bytes:
+    """Handle (bytes) that lets another process on this node map the device memory at `device_ptr`."""
+    import ctypes
+    from .runtime._capi import PEER_HANDLE_BYTES, get_lib
+    handle = (ctypes.c_uint8 * PEER_HANDLE_BYTES)()
+    err = ctypes.create_string_buffer(512)
+    if get_lib().afirt_peer_export(ctypes.c_void_p(device_ptr), handle, err, len(err)):
+        raise RuntimeError(err.value.decode())
+    return bytes(handle)
+
+
+def import_peer(device_id: int, handle: bytes) -> int:
+    """Device address, valid on `device_id` in this process, of the memory another process exported."""
+    import ctypes
+    from .runtime._capi import get_lib
+    arr = (ctypes.c_uint8 * len(handle)).from_buffer_copy(handle)
+    out = ctypes.c_void_p()
+    err = ctypes.create_string_buffer(512)
+    if get_lib().afirt_peer_import(device_id, arr, ctypes.byref(out), err, len(err)):
+        raise RuntimeError(err.value.decode())
+    return int(out.value)
+
+
+def release_peer(device_ptr: int) -> None:
+    import ctypes
+    from .runtime._capi import get_lib
+    err = ctypes.create_string_buffer(512)
+    if get_lib().afirt_peer_release(ctypes.c_void_p(device_ptr), err, len(err)):
+        raise RuntimeError(err.value.decode())
+
+
+class ShardedTable:
+    """A gather table whose rows are split over the ranks' GPUs: rank r keeps rows [r * R, (r + 1) * R) in
+    `local_shard` (a contiguous CUDA tensor of R rows; the last rank's may be shorter).  After construction
+    `pointers[s]` is shard s as this rank's GPU addresses it (its own shard directly, the others through CUDA IPC),
+    ready for CudaRuntime.launch_device(table_shards=table.pointers, rows_per_shard=table.rows_per_shard).
+    The exchange of handles uses the default process group (objects; any backend).  Keep `local_shard` alive until
+    every rank has called close()."""
+
+    def __init__(self, local_shard, device_id: int, rows_per_shard: int):
+        rank, size = world()
+        self.local_shard, self.device_id, self.rows_per_shard = local_shard, device_id, rows_per_shard
+        mine = export_peer(local_shard.data_ptr())
+        handles = [mine]
+        if size > 1:
+            import torch.distributed as dist
+            handles = [None] * size
+            dist.all_gather_object(handles, mine)
+        self._imported = []
+        self.pointers = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                self.pointers.append(local_shard.data_ptr())
+            else:
+                p = import_peer(device_id, h)
+                self._imported.append(p)
+                self.pointers.append(p)
+
+    def close(self) -> None:
+        for p in self._imported:
+            release_peer(p)
+        self._imported = []

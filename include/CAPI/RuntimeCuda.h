@@ -108,6 +108,35 @@ int afirt_executor_launch_device_exchange(AfirtExecutor executor, const uint8_t 
 int afirt_rowsum_exchange_status(AfirtRowsumExchange exchange, char *err_buf, size_t err_len);
 void afirt_rowsum_exchange_destroy(AfirtRowsumExchange exchange);
 
+/* No counterpart in the reference (one device, one table).  A row-gather group whose TABLE is sharded by rows over
+ * the GPUs of a node (a table larger than one GPU's memory): afirt_executor_launch_device with the table given as
+ * num_shards device pointers, shard s holding rows [s * rows_per_shard, (s + 1) * rows_per_shard) with the table's
+ * row length.  The pointers may be other GPUs' memory mapped into this process (afirt_peer_import below, or peer
+ * access inside one process); the kernel reads remote rows with plain loads over NVLink, so no exchange step and
+ * no library collective is involved.  input_ptrs[table input] is ignored but must not be NULL (pass the first
+ * shard); input_bytes[table input] is the WHOLE table's size, as the descriptor's dims imply.  Indices, the other
+ * operands and the output are this GPU's, as always.  Refused for other kernel classes and for column gathers. */
+int afirt_executor_launch_device_sharded_table(AfirtExecutor executor, const uint8_t *binary_data, size_t binary_len,
+                                               const char *function_name, int num_inputs, const void **input_ptrs,
+                                               const size_t *input_bytes, int num_outputs, void **output_ptrs,
+                                               const size_t *output_bytes, const uint8_t *tiling_data, size_t tiling_len,
+                                               int block_dim, uint32_t magic, void *workspace, size_t workspace_bytes,
+                                               void *cuda_stream, int num_shards, const void **shard_ptrs,
+                                               int64_t rows_per_shard, char *err_buf, size_t err_len);
+
+/* Device memory of one process made addressable from another process's GPU on the same node (CUDA IPC).
+ *   export   writes AFIRT_PEER_HANDLE_BYTES bytes describing device_ptr, which may point INSIDE an allocation (a
+ *            framework's sub-allocation of a larger block); the memory must come from cudaMalloc;
+ *   import   maps it for device_id in the calling process and returns the pointer (inside the exporting process it
+ *            returns the original pointer, enabling peer access when device_id is another GPU); importing
+ *            several pointers of one allocation shares one mapping;
+ *   release  drops one import; the mapping goes with the last one.  The exporter keeps the memory alive until
+ *            every importer has released it. */
+#define AFIRT_PEER_HANDLE_BYTES 96
+int afirt_peer_export(const void *device_ptr, uint8_t *out_handle, char *err_buf, size_t err_len);
+int afirt_peer_import(int device_id, const uint8_t *handle, void **out_ptr, char *err_buf, size_t err_len);
+int afirt_peer_release(void *imported_ptr, char *err_buf, size_t err_len);
+
 /* Library identification: "afir-b200 <version> sm_100a". */
 const char *afirt_runtime_version(void);
 
