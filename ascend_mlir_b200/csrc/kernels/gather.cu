@@ -471,10 +471,17 @@ template <class P, int BODY> KernelFn pickRowsUnroll(int unroll, bool vector) {
   return unroll >= 4 ? gatherRowsKernel<P, BODY, 4, true> : unroll >= 2 ? gatherRowsKernel<P, BODY, 2, true>
                                                                         : gatherRowsKernel<P, BODY, 1, true>;
 }
-// Sharded tables are NVLink-bound: the copy body and the interpreted one, two vectors in flight per thread.
+// Sharded tables: the bodies with a specialised chain keep it (the interpreted body costs several times the
+// bandwidth-bound time even on local rows), two vectors in flight per thread.
 template <class P> KernelFn pickRowsSharded(int body, bool vector) {
   if (!vector) return gatherRowsKernel<P, kBodyInterpreted, 2, false, true>;
-  return body == kBodyCopy ? gatherRowsKernel<P, kBodyCopy, 2, true, true> : gatherRowsKernel<P, kBodyInterpreted, 2, true, true>;
+  switch (body) {
+  case kBodyCopy: return gatherRowsKernel<P, kBodyCopy, 2, true, true>;
+  case kBodyMulAdd: return gatherRowsKernel<P, kBodyMulAdd, 2, true, true>;
+  case kBodyAdd: return gatherRowsKernel<P, kBodyAdd, 2, true, true>;
+  case kBodyMul: return gatherRowsKernel<P, kBodyMul, 2, true, true>;
+  default: return gatherRowsKernel<P, kBodyInterpreted, 2, true, true>;
+  }
 }
 
 template <class P> KernelFn pickRows(int body, int unroll, bool vector) {
