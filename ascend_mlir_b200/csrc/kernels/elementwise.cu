@@ -95,7 +95,9 @@ __global__ void __launch_bounds__(512) elementwiseKernel(const __grid_constant__
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       if (!live[u]) continue;
-      if (VECTOR) {
+      if (VECTOR && BODY == kBodyInterpreted) {
+        storeStream16(prm.obase + ooff[u], evalVector16<BODY, P, NV>(raw[u], prm.prog));
+      } else if (VECTOR) {
         Vec16<P> in[NV];
 #pragma unroll
         for (int k = 0; k < NV; ++k) in[k] = Vec16<P>::fromRaw(raw[u][k]);

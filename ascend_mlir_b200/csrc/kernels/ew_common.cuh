@@ -272,5 +272,59 @@ template <> struct Body<kBodyInterpreted> {
   }
 };
 
+// ---- one 16-byte vector of every view through the body ---------------------------------------------------
+// The specialised bodies simply run once per 32-bit pack.  The interpreted body would pay its op decoding and
+// operand selection (select chains over every view and every earlier result) once per pack and stay far below the
+// memory roofline; here it decodes an op ONCE per vector and keeps views and results as 16-byte slots in a small
+// per-thread array that it indexes with the op's operand numbers (the array lives in local memory, i.e. L1:
+// two 16-byte loads and one 16-byte store per op), so an op costs about a dozen instructions per vector instead
+// of a few hundred.
+__device__ __forceinline__ unsigned int comp(const uint4 &v, int q) { return q == 0 ? v.x : q == 1 ? v.y : q == 2 ? v.z : v.w; }
+
+template <class P> __device__ __forceinline__ uint4 interpOperand(const BodySrc &s, const uint4 *slot) {
+  if (s.kind == kSrcConst) {
+    const unsigned int c = P::constant(s.value).bits();
+    return make_uint4(c, c, c, c);
+  }
+  return slot[s.kind == kSrcView ? s.index : kMaxViews + s.index];
+}
+
+template <int BODY, class P, int NV>
+__device__ __forceinline__ uint4 evalVector16(const uint4 (&raw)[NV], const BodyProgram &prog) {
+  if constexpr (BODY == kBodyInterpreted) {
+    uint4 slot[kMaxViews + kMaxBodyOps];
+#pragma unroll
+    for (int k = 0; k < kMaxViews; ++k) slot[k] = k < NV ? raw[k] : make_uint4(0u, 0u, 0u, 0u);
+    uint4 last = raw[0];
+    for (int i = 0; i < prog.numOps; ++i) {
+      const uint4 a = interpOperand<P>(prog.ops[i].a, slot);
+      const uint4 b = interpOperand<P>(prog.ops[i].b, slot);
+      const P a0 = P::fromBits(a.x), a1 = P::fromBits(a.y), a2 = P::fromBits(a.z), a3 = P::fromBits(a.w);
+      const P b0 = P::fromBits(b.x), b1 = P::fromBits(b.y), b2 = P::fromBits(b.z), b3 = P::fromBits(b.w);
+      switch (prog.ops[i].op) {
+      case kOpAdd: last = make_uint4(P::add(a0, b0).bits(), P::add(a1, b1).bits(), P::add(a2, b2).bits(), P::add(a3, b3).bits()); break;
+      case kOpSub: last = make_uint4(P::sub(a0, b0).bits(), P::sub(a1, b1).bits(), P::sub(a2, b2).bits(), P::sub(a3, b3).bits()); break;
+      case kOpMul: last = make_uint4(P::mul(a0, b0).bits(), P::mul(a1, b1).bits(), P::mul(a2, b2).bits(), P::mul(a3, b3).bits()); break;
+      case kOpDiv: last = make_uint4(P::div(a0, b0).bits(), P::div(a1, b1).bits(), P::div(a2, b2).bits(), P::div(a3, b3).bits()); break;
+      case kOpMax: last = make_uint4(P::max(a0, b0).bits(), P::max(a1, b1).bits(), P::max(a2, b2).bits(), P::max(a3, b3).bits()); break;
+      default: last = make_uint4(P::min(a0, b0).bits(), P::min(a1, b1).bits(), P::min(a2, b2).bits(), P::min(a3, b3).bits()); break;
+      }
+      slot[kMaxViews + i] = last;
+    }
+    return last;
+  } else {
+    using B = Body<BODY>;
+    unsigned int out[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      P v[NV];
+#pragma unroll
+      for (int k = 0; k < NV; ++k) v[k] = P::fromBits(comp(raw[k], q));
+      out[q] = B::template eval<P>(v, prog).bits();
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
 } // namespace kernels
 } // namespace afir

@@ -120,7 +120,9 @@ __global__ void __launch_bounds__(512) gatherRowsKernel(const __grid_constant__ 
     for (int u = 0; u < UNROLL; ++u) {
       if (!live[u]) continue;
       char *dst = prm.out + (static_cast<long long>(row[u]) * prm.outRowStride + static_cast<long long>(col[u]) * kElems) * kElemBytes;
-      if (VECTOR) {
+      if (VECTOR && BODY == kBodyInterpreted) {
+        storeStream16(dst, evalVector16<BODY, P, NV>(raw[u], prm.prog));
+      } else if (VECTOR) {
         Vec16<P> o;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {

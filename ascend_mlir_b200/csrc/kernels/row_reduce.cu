@@ -199,7 +199,17 @@ __global__ void __launch_bounds__(512) rowReduceKernel(const __grid_constant__ R
         }
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
-          if (v0 + u * L < vEnd) {
+          if (VECTOR && BODY == kBodyInterpreted) {
+            if (v0 + u * L < vEnd) {  // the interpreted body decodes its ops once per 16-byte vector
+              const uint4 y16 = evalVector16<BODY, P, NV>(raw[u], prm.prog);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const P y = P::fromBits(comp(y16, q));
+                acc[q] += y.lane(0);
+                if (P::kLanes == 2) acc[q] += y.lane(1);
+              }
+            }
+          } else if (v0 + u * L < vEnd) {
 #pragma unroll
             for (int q = 0; q < (VECTOR ? 4 : 1); ++q) {
               P vals[NV];
@@ -363,6 +373,19 @@ __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_con
       for (unsigned int v = lane; v < nvec; v += 32) {
         {
           const uint4 raw = *reinterpret_cast<const uint4 *>(stg + v * 16);
+          if constexpr (BODY == kBodyInterpreted) {
+            uint4 all[NV];
+#pragma unroll
+            for (int k = 0; k < NV; ++k)
+              all[k] = k == prm.streamViewIndex ? raw : make_uint4(bcastNow[k], bcastNow[k], bcastNow[k], bcastNow[k]);
+            const uint4 y16 = evalVector16<BODY, P, NV>(all, prm.prog);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const P y = P::fromBits(comp(y16, q));
+              acc[q] += y.lane(0);
+              if (P::kLanes == 2) acc[q] += y.lane(1);
+            }
+          } else
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const unsigned int bits = q == 0 ? raw.x : q == 1 ? raw.y : q == 2 ? raw.z : raw.w;
