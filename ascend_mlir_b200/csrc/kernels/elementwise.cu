@@ -353,6 +353,19 @@ bool isRelu(const BodyOp &o, int view) {
 }
 } // namespace
 
+void finishBodyProgram(BodyProgram &prog) {
+  int views = 1;
+  unsigned int mask = 0;
+  for (int i = 0; i < prog.numOps && i < kMaxBodyOps; ++i) {
+    for (const BodySrc *s : {&prog.ops[i].a, &prog.ops[i].b}) {
+      if (s->kind == kSrcView) views = std::max(views, s->index + 1);
+      if (s->kind == kSrcOp && s->index != i - 1 && s->index >= 0 && s->index < kMaxBodyOps) mask |= 1u << s->index;
+    }
+  }
+  prog.numViewsUsed = std::min(views, kMaxViews);
+  prog.storeMask = mask;
+}
+
 int matchBody(const BodyProgram &p, int numViews) {
   const BodyOp *o = p.ops;
   if (p.numOps == 0 && numViews >= 1) return kBodyCopy;

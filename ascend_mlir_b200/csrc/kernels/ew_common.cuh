@@ -281,11 +281,14 @@ template <> struct Body<kBodyInterpreted> {
 // of a few hundred.
 __device__ __forceinline__ unsigned int comp(const uint4 &v, int q) { return q == 0 ? v.x : q == 1 ? v.y : q == 2 ? v.z : v.w; }
 
-template <class P> __device__ __forceinline__ uint4 interpOperand(const BodySrc &s, const uint4 *slot) {
+// `last` is the previous op's result: a chain op reads it from registers instead of from its slot.
+template <class P>
+__device__ __forceinline__ uint4 interpOperand(const BodySrc &s, const uint4 *slot, const uint4 &last, int opIndex) {
   if (s.kind == kSrcConst) {
     const unsigned int c = P::constant(s.value).bits();
     return make_uint4(c, c, c, c);
   }
+  if (s.kind == kSrcOp && s.index == opIndex - 1) return last;
   return slot[s.kind == kSrcView ? s.index : kMaxViews + s.index];
 }
 
@@ -294,11 +297,12 @@ __device__ __forceinline__ uint4 evalVector16(const uint4 (&raw)[NV], const Body
   if constexpr (BODY == kBodyInterpreted) {
     uint4 slot[kMaxViews + kMaxBodyOps];
 #pragma unroll
-    for (int k = 0; k < kMaxViews; ++k) slot[k] = k < NV ? raw[k] : make_uint4(0u, 0u, 0u, 0u);
+    for (int k = 0; k < kMaxViews; ++k)
+      if (k < NV && k < prog.numViewsUsed) slot[k] = raw[k];
     uint4 last = raw[0];
     for (int i = 0; i < prog.numOps; ++i) {
-      const uint4 a = interpOperand<P>(prog.ops[i].a, slot);
-      const uint4 b = interpOperand<P>(prog.ops[i].b, slot);
+      const uint4 a = interpOperand<P>(prog.ops[i].a, slot, last, i);
+      const uint4 b = interpOperand<P>(prog.ops[i].b, slot, last, i);
       const P a0 = P::fromBits(a.x), a1 = P::fromBits(a.y), a2 = P::fromBits(a.z), a3 = P::fromBits(a.w);
       const P b0 = P::fromBits(b.x), b1 = P::fromBits(b.y), b2 = P::fromBits(b.z), b3 = P::fromBits(b.w);
       switch (prog.ops[i].op) {
@@ -309,7 +313,7 @@ __device__ __forceinline__ uint4 evalVector16(const uint4 (&raw)[NV], const Body
       case kOpMax: last = make_uint4(P::max(a0, b0).bits(), P::max(a1, b1).bits(), P::max(a2, b2).bits(), P::max(a3, b3).bits()); break;
       default: last = make_uint4(P::min(a0, b0).bits(), P::min(a1, b1).bits(), P::min(a2, b2).bits(), P::min(a3, b3).bits()); break;
       }
-      slot[kMaxViews + i] = last;
+      if ((prog.storeMask >> i) & 1) slot[kMaxViews + i] = last;  // only results a later, non-adjacent op reads
     }
     return last;
   } else {

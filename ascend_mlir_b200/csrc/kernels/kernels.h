@@ -38,7 +38,13 @@ struct BodyOp {
 struct BodyProgram {
   int numOps;  // 0 = identity of view 0
   BodyOp ops[kMaxBodyOps];
+  // Filled by finishBodyProgram() for the interpreted kernels: how many views the ops read (highest index + 1)
+  // and which op results some op other than the next one reads (those are the only ones kept in memory).
+  int numViewsUsed = kMaxViews;
+  unsigned int storeMask = 0xffffffffu;
 };
+// Derives numViewsUsed and storeMask from the ops; a program left as parsed (all views, every result kept) is valid too.
+void finishBodyProgram(BodyProgram &prog);
 
 // Ids of the bodies compiled as straight-line specialisations (everything else runs through
 // the op-by-op interpreter kernel, same results, lower throughput).

@@ -167,6 +167,7 @@ Status parseBody(const json::Value *v, int numViews, kernels::BodyProgram &out) 
     if (Status s = parseSrc(*b, numViews, static_cast<int>(i), out.ops[i].b); !s) return s;
   }
   out.numOps = static_cast<int>(ops.size());
+  kernels::finishBodyProgram(out);
   return Status::success();
 }
 
