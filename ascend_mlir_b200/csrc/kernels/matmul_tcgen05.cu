@@ -743,6 +743,25 @@ bool makeMap2d(CUtensorMap *map, CUtensorMapDataType type, const void *base, uin
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A function attribute belongs to the function ON THE CURRENT DEVICE: a process that runs the matmul on several
+// GPUs has to set it once on each of them.  `run` calls `set` the first time it is reached with a given device
+// current (and again after a failure) and returns that device's result.
+struct PerDeviceOnce {
+  std::mutex mu;
+  bool done[64] = {false};
+  template <class F> cudaError_t run(F set) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 0 || device >= 64) return set();
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[device]) return cudaSuccess;
+    e = set();
+    done[device] = e == cudaSuccess;
+    return e;
+  }
+};
+
 void fail(char *errorText, const char *msg) {
   if (errorText) std::snprintf(errorText, 256, "%s", msg);
 }
@@ -752,10 +771,9 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmPa
                   char *errorText) {
   using S = Shape<MB>;
   auto kernel = matmulBiasActKernel<MB, OUT>;
-  static std::once_flag once;
-  static cudaError_t attrErr = cudaSuccess;
-  std::call_once(once, [&] {
-    attrErr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kSmemBytes));
+  static PerDeviceOnce reserved;
+  const cudaError_t attrErr = reserved.run([&] {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S::kSmemBytes));
   });
   if (attrErr != cudaSuccess) {
     fail(errorText, "matmul: cannot reserve shared memory for the operand ring");
@@ -769,10 +787,9 @@ template <int OUT>
 int launchPairVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmParams &p, int grid, cudaStream_t stream,
                       char *errorText) {
   auto kernel = matmulBiasActPairKernel<OUT>;
-  static std::once_flag once;
-  static cudaError_t attrErr = cudaSuccess;
-  std::call_once(once, [&] {
-    attrErr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(k2SmemBytes));
+  static PerDeviceOnce reserved;
+  const cudaError_t attrErr = reserved.run([&] {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(k2SmemBytes));
   });
   if (attrErr != cudaSuccess) {
     fail(errorText, "matmul: cannot reserve shared memory for the operand ring");

@@ -633,6 +633,7 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
 //    the library holds this array until the process exits).  Larger requests are refused.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
 //    device current) and caches it; make that first call before starting any stream capture.
+//  * The call makes `device_id` current for the launch and restores the caller's current device before it returns.
 //  * All calls share the one array per device.  It keeps whatever the previous call left; nothing in
 //    it has to start at zero because every slot a call reads is first written by that same call.
 //    Two calls that overlap on the GPU (different streams, or different host threads) race on it:
@@ -660,15 +661,29 @@ afirt_bcast_add_rowsum_no_alloc(int device_id, int elem_type, const void *a, con
   if (rows < 0 || cols < 0 || split_cols < 1) { noAllocFail(err_buf, err_len, "rows and cols must be non-negative and split_cols at least 1"); return 1; }
   if (rows == 0) return 0;
   if (!a || !b || !out) { noAllocFail(err_buf, err_len, "a, b and out are required"); return 1; }
-  if (rows * static_cast<long long>(split_cols) > kNoAllocMaxPartials) {
-    char msg[160];
-    std::snprintf(msg, sizeof(msg), "rows * split_cols = %lld exceeds the built-in scratch of %lld partial sums",
-                  static_cast<long long>(rows) * split_cols, kNoAllocMaxPartials);
+  // rows > max / split_cols instead of rows * split_cols > max: the product of two caller-chosen numbers can wrap
+  if (split_cols > kNoAllocMaxPartials || rows > kNoAllocMaxPartials / split_cols) {
+    char msg[200];
+    std::snprintf(msg, sizeof(msg), "rows (%lld) x split_cols (%d) exceeds the built-in scratch of %lld partial sums",
+                  static_cast<long long>(rows), split_cols, kNoAllocMaxPartials);
     noAllocFail(err_buf, err_len, msg);
     return 1;
   }
-  cudaError_t e = cudaSetDevice(device_id);
+  // rows is at most 262 144 from here on; keep rows * cols * element size inside 63 bits before pointers are formed
+  if (cols > (1ll << 40)) { noAllocFail(err_buf, err_len, "cols exceeds 2^40"); return 1; }
+  // The launch needs `device_id` current; the caller's current device is put back before returning, on every path.
+  struct DeviceScope {
+    int previous = -1;
+    ~DeviceScope() { if (previous >= 0) cudaSetDevice(previous); }
+  } scope;
+  int current = -1;
+  cudaError_t e = cudaGetDevice(&current);
   if (e != cudaSuccess) { noAllocFail(err_buf, err_len, cudaGetErrorString(e)); return 1; }
+  if (current != device_id) {
+    e = cudaSetDevice(device_id);
+    if (e != cudaSuccess) { noAllocFail(err_buf, err_len, cudaGetErrorString(e)); return 1; }
+    scope.previous = current;
+  }
   float *scratch = nullptr;
   {
     // The array's name is only a host-side handle; the kernel needs its address in this device's memory.

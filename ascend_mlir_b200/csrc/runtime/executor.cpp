@@ -350,8 +350,19 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
   cudaStream_t compute = static_cast<cudaStream_t>(stream_);
   cudaStream_t in = static_cast<cudaStream_t>(copyIn_);
   cudaStream_t out = static_cast<cudaStream_t>(copyOut_);
-  auto event = [&](size_t i) { return static_cast<cudaEvent_t>(events_[i]); };
   cudaError_t e;
+  // `after` starts what it is given next only once everything queued on `before` so far has finished.  A failed
+  // record or wait would silently un-order copy and compute, so it ends the run (all three streams drained first).
+  auto order = [&](cudaStream_t before, cudaStream_t after, int64_t eventIndex) -> Status {
+    cudaEvent_t ev = static_cast<cudaEvent_t>(events_[static_cast<size_t>(eventIndex)]);
+    cudaError_t oe = cudaEventRecord(ev, before);
+    if (oe == cudaSuccess) oe = cudaStreamWaitEvent(after, ev, 0);
+    if (oe == cudaSuccess) return Status::success();
+    cudaStreamSynchronize(in);
+    cudaStreamSynchronize(compute);
+    cudaStreamSynchronize(out);
+    return cudaFail(oe, "[cuda:device] ordering the copy and compute streams failed");
+  };
 
   if ((e = cudaMemsetAsync(workspace_.ptr, 0, kWorkspaceStatusBytes, compute)) != cudaSuccess)
     return cudaFail(e, "[cuda:memory] workspace clear failed");
@@ -373,8 +384,7 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
                           static_cast<size_t>(en - b) * rb, cudaMemcpyHostToDevice, in);
       if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] host-to-device copy failed");
     }
-    cudaEventRecord(event(2 * c), in);
-    cudaStreamWaitEvent(compute, event(2 * c), 0);
+    if (Status o = order(in, compute, 2 * c); !o) return o;  // the kernel of chunk c waits for its copy-in
     args.rowBegin = b;
     args.rowEnd = en;
     LaunchInfo info;
@@ -390,8 +400,7 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
       cudaStreamSynchronize(out);
       return launchStage(ls);
     }
-    cudaEventRecord(event(2 * c + 1), compute);
-    cudaStreamWaitEvent(out, event(2 * c + 1), 0);
+    if (Status o = order(compute, out, 2 * c + 1); !o) return o;  // the copy-out of chunk c waits for its kernel
     for (int i = 0; i < req.numOutputs; ++i) {
       const size_t k = static_cast<size_t>(req.numInputs + i);
       const size_t rb = plan.rowBytes[k];
@@ -406,8 +415,7 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
   for (int i = 0; i < req.numOutputs; ++i) {
     const size_t k = static_cast<size_t>(req.numInputs + i);
     if (plan.rowBytes[k] || !req.outputBytes[i]) continue;
-    cudaEventRecord(event(2 * numChunks), compute);
-    cudaStreamWaitEvent(out, event(2 * numChunks), 0);
+    if (Status o = order(compute, out, 2 * numChunks); !o) return o;
     e = cudaMemcpyAsync(req.outputPtrs[i], args.argPtrs[k], req.outputBytes[i], cudaMemcpyDeviceToHost, out);
     if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] device-to-host copy failed");
   }

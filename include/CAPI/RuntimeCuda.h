@@ -55,8 +55,9 @@ uint64_t afirt_executor_total_launch_count(AfirtExecutor executor);
  * with a message.  The first call on a device resolves the array's device address: make it before
  * any stream capture begins.  Every call on a device shares the array (contents left over from
  * the previous call are harmless: each call writes every slot it later reads), so calls that
- * overlap on the GPU race and must be serialised by the caller.  Enqueues on cuda_stream and
- * returns; 0 = success, otherwise 1 with a message in err_buf. */
+ * overlap on the GPU race and must be serialised by the caller.  The call makes device_id current
+ * for the launch and puts the caller's current device back before it returns.  Enqueues on
+ * cuda_stream and returns; 0 = success, otherwise 1 with a message in err_buf. */
 #define AFIRT_NO_ALLOC_MAX_PARTIALS 262144
 int afirt_bcast_add_rowsum_no_alloc(int device_id, int elem_type, const void *a, const void *b, void *out,
                                     int64_t rows, int64_t cols, int split_cols, void *cuda_stream,

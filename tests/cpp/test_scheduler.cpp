@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <iostream>
 #include <limits>
+#include <functional>
 #include <set>
 #include <thread>
 
@@ -430,6 +431,11 @@ public:
     order.push_back(request.task.taskId);
     for (const TensorBinding &in : request.task.invocation.inputs) seenInputPaths.insert(in.path);
     maxInside = std::max(maxInside, ++inside_);
+    if (holdFirstUntil && order.size() == 1) {
+      // the very first task stays inside the driver until the condition holds (5 s at most), so that what the
+      // test wants to overlap with it really does, however fast the fake tasks are
+      for (int i = 0; i < 1000 && !holdFirstUntil(); ++i) cv_.wait_for(lock, std::chrono::milliseconds(5));
+    }
     if (request.task.taskId.rfind("meet", 0) == 0 && meetCount_ > 0) {
       ++met_;
       cv_.notify_all();
@@ -443,6 +449,7 @@ public:
   std::vector<std::string> order;
   std::set<std::string> seenInputPaths;
   int maxInside = 0;
+  std::function<bool()> holdFirstUntil;
 
 private:
   size_t streams_;
@@ -526,6 +533,8 @@ static void testSessionsShareStreams(const std::string &dir) {
   auto driver = std::make_shared<FakeConcurrentDriver>(4, 0);
   GlobalScheduler scheduler;
   scheduler.configureResourceScheduler(4, 1, 1 << 20, 1);
+  // whichever session gets the stream first keeps it until the other one has submitted its graph too
+  driver->holdFirstUntil = [&] { return scheduler.observabilitySnapshot().counters.at("scheduler.session_count") >= 2; };
   SessionRunSummary sums[2];
   std::thread threads[2];
   for (int i = 0; i < 2; ++i)
