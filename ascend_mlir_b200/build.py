@@ -37,7 +37,8 @@ CU_SOURCES = {
     "kernels/transpose.cu": [],
     "kernels/matmul_tcgen05.cu": [],
 }
-CPP_SOURCES = ["common/json.cpp", "kernels/matmul_plan.cpp", "runtime/descriptor.cpp", "runtime/launcher.cpp", "runtime/executor.cpp",
+CPP_SOURCES = ["common/json.cpp", "kernels/matmul_plan.cpp", "kernels/body_match.cpp", "codegen/kernel_source.cpp",
+               "codegen/nvrtc_compile.cpp", "codegen/embedded_headers.cpp", "runtime/device_module.cpp", "runtime/descriptor.cpp", "runtime/launcher.cpp", "runtime/executor.cpp",
                "support/npy_io.cpp", "support/tiling_schema.cpp", "execution/output_comparator.cpp",
                "execution/task_graph.cpp", "execution/run_manifest.cpp", "execution/artifact_compiler.cpp",
                "execution/execution_session.cpp", "execution/resource_scheduler.cpp", "execution/global_scheduler.cpp",
@@ -128,8 +129,10 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
             _run([CXX] + CXX_FLAGS + ["-c", str(src), "-o", str(tobj)], verbose)
             _mark(tobj, src, stamp)
             if tool in FRONT_ONLY:
-                front = [o for o in lib_objs if "front_" in o or "common_" in o]
-                _run([CXX, "-o", str(exe), str(tobj)] + front, verbose)
+                # parser, group analysis, descriptor, kernel generator and the NVRTC front: no CUDA objects
+                front = [o for o in lib_objs if any(tag in Path(o).name for tag in (
+                    "front_", "common_", "codegen_", "runtime_descriptor", "kernels_body_match", "support_tiling_schema"))]
+                _run([CXX, "-o", str(exe), str(tobj)] + front + ["-ldl"], verbose)
             else:
                 _run([CXX, "-o", str(exe), str(tobj)] + lib_objs + cuda_libs, verbose)
     if ptxas_info:

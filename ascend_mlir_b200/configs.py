@@ -41,6 +41,8 @@ class Workload:
     notes: str = ""
     # (rank, world) -> Workload for that shard
     sharder: Optional[Callable[[int, int], "Workload"]] = field(default=None, repr=False)
+    # generic chains: () -> the expected output (numpy, per-op rounding), for the bench's own parity check
+    expected: Optional[Callable[[], np.ndarray]] = field(default=None, repr=False)
 
     def tiling(self, **tile_params: int) -> bytes:
         return self.spec.pack(self.shape, **tile_params)
@@ -193,6 +195,100 @@ def relu_broadcast_transpose_add(M: int = 8192, N: int = 8192, seed: int = 0) ->
 
     return make(d1)
 
+
+# ---- generic chains: fused bodies the library has no straight-line kernel for ----------------------------------------
+# They run on the kernel generated for the group (codegen/kernel_source -> NVRTC); before the generator existed
+# they ran through the op-by-op interpreter at a third of the HBM roofline.
+def _chain_variant(name: str, body: list, dtype: str = "f32") -> KernelSpec:
+    import copy
+    base = descriptors.add_mul(dtype, name=name)
+    d = copy.deepcopy(base.descriptor)
+    d["body"] = body
+    space = copy.deepcopy(base.tiling_space)
+    return KernelSpec(name=name, descriptor=d, tiling_space=space, shape_keys=dict(base.shape_keys), defaults=dict(base.defaults))
+
+
+def _two_operand_chain(name: str, body: list, expected: Callable[[np.ndarray, np.ndarray], np.ndarray], M: int, N: int, seed: int) -> Workload:
+    rng = np.random.default_rng(seed)
+    a = rng.uniform(-1.0, 1.0, (M, N)).astype(np.float32)
+    b = rng.uniform(0.5, 1.5, (M, N)).astype(np.float32)
+    spec = _chain_variant(name, body)
+
+    def make(a_, b_):
+        m = a_.shape[0]
+        w = Workload(name, spec, {"M": m, "N": N}, [a_, b_], (m, N), np.dtype(np.float32), algorithmic_bytes=3 * m * N * 4, units=m,
+                     notes="generated kernel (no prebuilt body matches)")
+        w.expected = lambda: expected(a_, b_)
+        w.sharder = lambda r, k: make(*(np.ascontiguousarray(t[slice(*row_range(m, r, k))]) for t in (a_, b_)))
+        return w
+
+    return make(a, b)
+
+
+def chain_sub_div_min(M: int = 4096, N: int = 4096, seed: int = 0) -> Workload:
+    """out = min((a - b) / b, a), f32, every op rounded."""
+    op = descriptors.op
+    return _two_operand_chain("chain_sub_div_min", [op("subf", "v0", "v1"), op("divf", "%0", "v1"), op("minimumf", "%1", "v0")],
+                              lambda a, b: np.minimum((a - b) / b, a), M, N, seed)
+
+
+def chain_six_ops(M: int = 4096, N: int = 4096, seed: int = 0) -> Workload:
+    """r0 = a*b; out = min((max(r0 + a, 0.25) - b) * r0, 1.5), f32, every op rounded."""
+    op = descriptors.op
+    body = [op("mulf", "v0", "v1"), op("addf", "%0", "v0"), op("maximumf", "%1", 0.25), op("subf", "%2", "v1"),
+            op("mulf", "%3", "%0"), op("minimumf", "%4", 1.5)]
+
+    def expected(a, b):
+        r0 = a * b
+        return np.minimum((np.maximum(r0 + a, np.float32(0.25)) - b) * r0, np.float32(1.5))
+
+    return _two_operand_chain("chain_six_ops", body, expected, M, N, seed)
+
+
+def chain_torch_model(M: int = 4096, N: int = 4096, seed: int = 0, work_dir=None) -> Workload:
+    """A torch module through the torch_e2e front (torch.export -> linalg text -> afir-opt -> afir-translate):
+    out = clamp((x - shift) * scale, min=0) * y + x on f32 [M, N] with shift and scale [N] broadcast over the rows.
+    Needs torch and the built front-end tools; shapes are static in the traced IR."""
+    import json
+    import tempfile
+    from pathlib import Path
+
+    import torch
+
+    from .torch_e2e.pipeline import compile_model
+    from .torch_e2e.tensor_spec import TensorSpec
+
+    class GatedAffine(torch.nn.Module):
+        def forward(self, x, y, scale, shift):
+            return torch.clamp((x - shift) * scale, min=0.0) * y + x
+
+    specs = [TensorSpec((M, N), torch.float32), TensorSpec((M, N), torch.float32), TensorSpec((N,), torch.float32),
+             TensorSpec((N,), torch.float32)]
+    root = Path(work_dir) if work_dir else Path(tempfile.mkdtemp(prefix="afir_chain_torch_model_"))
+    torch.manual_seed(seed)
+    built = compile_model(GatedAffine(), specs, root / "chain_torch_model", func_name="chain_torch_model")
+    desc = json.loads(Path(built["kernel"]).read_text())
+    space = json.loads(Path(built["space"]).read_text())
+    tile_defaults = {p["name"]: p.get("default", (p.get("values") or [0])[0]) for p in space["tiling_params"] if not p.get("fixed")}
+    dims = {p["name"]: p["shape_key"] for p in space["tiling_params"] if p.get("fixed")}
+    spec = KernelSpec(name=desc["kernel"], descriptor=desc, tiling_space=space, shape_keys=dims, defaults=tile_defaults)
+    inputs = [t.numpy() for t in built["inputs"]]
+    shape = {}
+    for key in dims.values():
+        n, d = key[3:].split("_dim")
+        shape[key] = (inputs + [np.zeros((M, N), np.float32)])[int(n)].shape[int(d)]
+    w = Workload("chain_torch_model", spec, shape, inputs, (M, N), np.dtype(np.float32), algorithmic_bytes=3 * M * N * 4 + 2 * N * 4, units=M,
+                 notes="torch module traced by the torch_e2e front; generated kernel")
+    want = built["expected"].numpy()
+    w.expected = lambda: want
+    return w
+
+
+GENERIC_CHAINS: Dict[str, Callable[..., Workload]] = {
+    "chain_sub_div_min": chain_sub_div_min,
+    "chain_six_ops": chain_six_ops,
+    "chain_torch_model": chain_torch_model,
+}
 
 EXTRA_CONFIGS: Dict[str, Callable[..., Workload]] = {
     "transpose_2d": transpose_2d,

@@ -6,6 +6,7 @@
 #include <cstring>
 #include <fstream>
 
+#include "codegen/nvrtc_compile.h"
 #include "runtime/descriptor.h"
 #include "support/tiling_schema.h"
 
@@ -37,9 +38,41 @@ Status compileArtifact(const CompileRequest &request, KernelArtifact &artifact) 
   if (desc.kernel != name)
     return Status::error(request.kernelSource + ": defines kernel '" + desc.kernel + "', not '" + name + "'");
   if (!makeDirs(request.outputDir)) return Status::error("cannot create " + request.outputDir);
+  // The compile step proper: generate the group's kernel source and compile it for sm_100a (NVRTC, no GPU
+  // needed), as the reference generates AscendC and runs bisheng on it
+  // (lib/Runtime/Artifact/VecCubeArtifactBackend.cpp:123-189).  Matmul and bare-transpose groups are kernels of
+  // the library itself and get a descriptor-only container.
   std::vector<uint8_t> bin;
-  if (src.size() >= 4 && std::memcmp(src.data(), "AFCU", 4) == 0) bin = src;
-  else bin = wrapDescriptorContainer(std::string(src.begin(), src.end()));
+  std::string codegenNote = "library";
+  std::string sourcePath;
+  if (src.size() >= 4 && std::memcmp(src.data(), "AFCU", 4) == 0) {
+    bin = src;
+    codegenNote = containerCode(src.data(), src.size()).cubinLen ? "generated" : "library";
+  } else {
+    const codegen::GeneratedKernel kernel = codegen::generateKernelSource(desc);
+    std::vector<uint8_t> cubin;
+    std::string source;
+    if (!kernel.supported) {
+      codegenNote = "library (" + kernel.whyNot + ")";
+    } else {
+      codegen::CompiledKernel compiled;
+      if (Status s = codegen::compileToCubin(kernel, compiled); !s) {
+        // a compiler that cannot be loaded is not the kernel's fault: the group then runs on the library's kernels;
+        // source that does not compile is a bug and fails the step
+        if (!codegen::nvrtcUnavailableReason().empty()) codegenNote = "library (" + s.message() + ")";
+        else return Status::error(request.kernelSource + ": " + s.message());
+      } else {
+        cubin = std::move(compiled.cubin);
+        source = kernel.source;
+        codegenNote = "generated";
+        sourcePath = request.outputDir + "/" + name + ".cu";
+        std::ofstream os(sourcePath, std::ios::trunc);
+        os << source;
+        if (!os) return Status::error("cannot write " + sourcePath);
+      }
+    }
+    bin = wrapDescriptorContainer(std::string(src.begin(), src.end()), cubin, source);
+  }
   const std::string binPath = request.outputDir + "/" + name + ".bin";
   {
     std::ofstream os(binPath, std::ios::binary | std::ios::trunc);
@@ -55,7 +88,9 @@ Status compileArtifact(const CompileRequest &request, KernelArtifact &artifact) 
        << "kernel_kind=" << (matmul ? "mix" : "vec") << "\n"
        << "kernel_class=" << kernelClassName(desc.kernelClass) << "\n"
        << "device_binary_path=" << binPath << "\n"
-       << "manifest_path=" << manifestPath << "\n";
+       << "manifest_path=" << manifestPath << "\n"
+       << "codegen=" << codegenNote << "\n";
+    if (!sourcePath.empty()) os << "kernel_source_path=" << sourcePath << "\n";
     if (!os) return Status::error("cannot write " + manifestPath);
   }
   artifact = KernelArtifact();

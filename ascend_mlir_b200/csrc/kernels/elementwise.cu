@@ -5,7 +5,7 @@
 // HBM-bound: every thread keeps UNROLL independent 16-byte loads per view in flight, inputs read
 // once are loaded with the streaming (evict-first) policy, broadcast operands through the read-only
 // path.  No shared memory: there is no reuse to stage.  Arithmetic rounds after every op.
-#include "kernels/ew_common.cuh"
+#include "kernels/elementwise_skel.cuh"
 #include "kernels/reg_block.cuh"
 
 #include <algorithm>
@@ -15,109 +15,9 @@ namespace afir {
 namespace kernels {
 namespace {
 
-struct EwParams {
-  const char *vbase[kMaxViews];
-  long long vs0[kMaxViews], vs1[kMaxViews], vs2[kMaxViews];
-  char *obase;
-  long long os0, os1;
-  unsigned int vecPerRow;  // vectors (or elements, scalar variant) along the inner dim
-  unsigned int d1;
-  unsigned int totalVec;
-  unsigned int numTiles;
-  FastDiv divVpr, divD1;
-  int flat;  // inner dim is the whole domain: skip the row arithmetic
-  int numViews;
-  BodyProgram prog;
-  long long vOuterBytes[kMaxViews];  // OUTER kernels: byte offset per blockIdx.y, per view and for the output
-  long long oOuterBytes;
-};
-
-template <class P> __device__ __forceinline__ void storeScalar(void *p, P v);
-template <> __device__ __forceinline__ void storeScalar<PackF32>(void *p, PackF32 v) {
-  *reinterpret_cast<float *>(p) = v.x;
-}
-template <> __device__ __forceinline__ void storeScalar<PackF16>(void *p, PackF16 v) {
-  *reinterpret_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
-}
-template <> __device__ __forceinline__ void storeScalar<PackBF16>(void *p, PackBF16 v) {
-  *reinterpret_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
-}
-template <> __device__ __forceinline__ void storeScalar<PackI32>(void *p, PackI32 v) { *reinterpret_cast<int *>(p) = v.x; }
-template <> __device__ __forceinline__ void storeScalar<PackI16>(void *p, PackI16 v) {
-  *reinterpret_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
-}
-
 template <class P, int BODY, int UNROLL, bool VECTOR, bool OUTER = false>
 __global__ void __launch_bounds__(512) elementwiseKernel(const __grid_constant__ EwParams prm) {
-  using B = Body<BODY>;
-  constexpr int NV = B::kViews;
-  constexpr int kElems = VECTOR ? Vec16<P>::kElems : 1;
-  constexpr int kElemBytes = sizeof(typename P::Scalar);
-  const unsigned int tileVecs = blockDim.x * UNROLL;
-
-  for (unsigned int tile = blockIdx.x; tile < prm.numTiles; tile += gridDim.x) {
-    const unsigned int g0 = tile * tileVecs + threadIdx.x;
-    uint4 raw[UNROLL][NV];
-    long long ooff[UNROLL];
-    bool live[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const unsigned int g = g0 + u * blockDim.x;
-      live[u] = g < prm.totalVec;
-      unsigned int col = g, i0 = 0, i1 = 0;
-      if (!prm.flat) {
-        const unsigned int row = fastDivide(g, prm.divVpr);
-        col = g - row * prm.vecPerRow;
-        i0 = fastDivide(row, prm.divD1);
-        i1 = row - i0 * prm.d1;
-      }
-      ooff[u] = (static_cast<long long>(i0) * prm.os0 + static_cast<long long>(i1) * prm.os1 +
-                 static_cast<long long>(col) * kElems) * kElemBytes + (OUTER ? blockIdx.y * prm.oOuterBytes : 0ll);
-      if (live[u]) {
-#pragma unroll
-        for (int k = 0; k < NV; ++k) {
-          if (k < prm.numViews) {
-            const long long e = static_cast<long long>(i0) * prm.vs0[k] + static_cast<long long>(i1) * prm.vs1[k] +
-                                static_cast<long long>(col) * kElems * prm.vs2[k];
-            const char *src = prm.vbase[k] + e * kElemBytes + (OUTER ? blockIdx.y * prm.vOuterBytes[k] : 0ll);
-            if (VECTOR && prm.vs2[k] == 1) {
-              raw[u][k] = loadStream16(src);
-            } else {
-              const unsigned int s = P::splat(src).bits();
-              raw[u][k] = make_uint4(s, s, s, s);
-            }
-          } else {
-            raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      if (!live[u]) continue;
-      if (VECTOR && BODY == kBodyInterpreted) {
-        storeStream16(prm.obase + ooff[u], evalVector16<BODY, P, NV>(raw[u], prm.prog));
-      } else if (VECTOR) {
-        Vec16<P> in[NV];
-#pragma unroll
-        for (int k = 0; k < NV; ++k) in[k] = Vec16<P>::fromRaw(raw[u][k]);
-        Vec16<P> out;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          P v[NV];
-#pragma unroll
-          for (int k = 0; k < NV; ++k) v[k] = in[k].p[q];
-          out.p[q] = B::template eval<P>(v, prm.prog);
-        }
-        storeStream16(prm.obase + ooff[u], out.raw());
-      } else {
-        P v[NV];
-#pragma unroll
-        for (int k = 0; k < NV; ++k) v[k] = P::fromBits(raw[u][k].x);
-        storeScalar<P>(prm.obase + ooff[u], B::template eval<P>(v, prm.prog));
-      }
-    }
-  }
+  elementwiseTiles<P, Body<BODY>, UNROLL, VECTOR, OUTER>(prm);
 }
 
 using KernelFn = void (*)(const EwParams);
@@ -336,56 +236,6 @@ bool tryLaunchBlocks(const ElementwiseLaunch &l, cudaStream_t stream, cudaError_
 }
 
 } // namespace
-
-// ---- body matching (host) ------------------------------------------------------------------------
-namespace {
-bool srcIs(const BodySrc &s, int kind, int index) { return s.kind == kind && s.index == index; }
-bool srcIsZero(const BodySrc &s) { return s.kind == kSrcConst && s.value == 0.0f; }
-// op(a,b) with commutative matching for add/mul/max/min
-bool opIs(const BodyOp &o, int code, int ak, int ai, int bk, int bi) {
-  if (o.op != code) return false;
-  if (srcIs(o.a, ak, ai) && srcIs(o.b, bk, bi)) return true;
-  bool commutative = code == kOpAdd || code == kOpMul || code == kOpMax || code == kOpMin;
-  return commutative && srcIs(o.a, bk, bi) && srcIs(o.b, ak, ai);
-}
-bool isRelu(const BodyOp &o, int view) {
-  return o.op == kOpMax && ((srcIs(o.a, kSrcView, view) && srcIsZero(o.b)) || (srcIs(o.b, kSrcView, view) && srcIsZero(o.a)));
-}
-} // namespace
-
-void finishBodyProgram(BodyProgram &prog) {
-  int views = 1;
-  unsigned int mask = 0;
-  for (int i = 0; i < prog.numOps && i < kMaxBodyOps; ++i) {
-    for (const BodySrc *s : {&prog.ops[i].a, &prog.ops[i].b}) {
-      if (s->kind == kSrcView) views = std::max(views, s->index + 1);
-      if (s->kind == kSrcOp && s->index != i - 1 && s->index >= 0 && s->index < kMaxBodyOps) mask |= 1u << s->index;
-    }
-  }
-  prog.numViewsUsed = std::min(views, kMaxViews);
-  prog.storeMask = mask;
-}
-
-int matchBody(const BodyProgram &p, int numViews) {
-  const BodyOp *o = p.ops;
-  if (p.numOps == 0 && numViews >= 1) return kBodyCopy;
-  if (p.numOps == 1) {
-    if (opIs(o[0], kOpAdd, kSrcView, 0, kSrcView, 1)) return kBodyAdd;
-    if (opIs(o[0], kOpMul, kSrcView, 0, kSrcView, 1)) return kBodyMul;
-    if (isRelu(o[0], 0)) return kBodyRelu;
-  }
-  if (p.numOps == 2) {
-    if (opIs(o[0], kOpAdd, kSrcView, 0, kSrcView, 1) && opIs(o[1], kOpMul, kSrcOp, 0, kSrcView, 1)) return kBodyAddMulRhs;
-    if (opIs(o[0], kOpAdd, kSrcView, 0, kSrcView, 1) && opIs(o[1], kOpMul, kSrcOp, 0, kSrcView, 2)) return kBodyAddMul;
-    if (opIs(o[0], kOpMul, kSrcView, 0, kSrcView, 1) && opIs(o[1], kOpAdd, kSrcOp, 0, kSrcView, 2)) return kBodyMulAdd;
-    if (isRelu(o[0], 0) && opIs(o[1], kOpAdd, kSrcOp, 0, kSrcView, 1)) return kBodyReluAdd;
-  }
-  if (p.numOps == 3) {
-    if (isRelu(o[0], 0) && opIs(o[1], kOpAdd, kSrcOp, 0, kSrcView, 1) && opIs(o[2], kOpMul, kSrcOp, 1, kSrcView, 2))
-      return kBodyReluAddMul;
-  }
-  return kBodyInterpreted;
-}
 
 int deviceSmCount(int device) {
   static std::mutex mu;

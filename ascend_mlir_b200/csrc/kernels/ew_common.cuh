@@ -1,10 +1,23 @@
 // Shared device-side pieces of the bandwidth-bound fused-group kernels: 16-byte vector packs per
 // element type, per-op-rounded arithmetic, the specialised body functors and the body interpreter.
+//
+// This file and the *_skel.cuh files beside it are also compiled at run time: the kernel generator embeds them
+// and hands them to NVRTC as the headers of every generated kernel, so they use no host header.  A generated
+// translation unit defines AFIR_CG_F16 / AFIR_CG_BF16 when its group computes in that type; the 16-bit packs
+// (and the CUDA headers they need) are left out otherwise, which keeps an f32 or integer kernel's compile short.
 #pragma once
 
-#include <cuda_bf16.h>
+#if !defined(__CUDACC_RTC__) || defined(AFIR_CG_F16)
+#define AFIR_HAVE_F16 1
 #include <cuda_fp16.h>
+#endif
+#if !defined(__CUDACC_RTC__) || defined(AFIR_CG_BF16)
+#define AFIR_HAVE_BF16 1
+#include <cuda_bf16.h>
+#endif
+#ifndef __CUDACC_RTC__
 #include <cuda_runtime.h>
+#endif
 
 #include "kernels/kernels.h"
 
@@ -17,7 +30,7 @@ struct FastDiv {
   unsigned int shift;
   unsigned int divisor;
 };
-inline FastDiv makeFastDiv(unsigned int d) {
+__host__ __device__ inline FastDiv makeFastDiv(unsigned int d) {
   FastDiv f;
   f.divisor = d;
   unsigned int s = 0;
@@ -54,6 +67,7 @@ struct PackF32 {
     return {__ldg(reinterpret_cast<const float *>(p))};
   }
   __device__ __forceinline__ static PackF32 constant(float c) { return {c}; }
+  __device__ __forceinline__ static PackF32 constantOf(const BodySrc &s) { return constant(s.value); }
   __device__ __forceinline__ static PackF32 add(PackF32 a, PackF32 b) { return {__fadd_rn(a.x, b.x)}; }
   __device__ __forceinline__ static PackF32 sub(PackF32 a, PackF32 b) { return {__fsub_rn(a.x, b.x)}; }
   __device__ __forceinline__ static PackF32 mul(PackF32 a, PackF32 b) { return {__fmul_rn(a.x, b.x)}; }
@@ -72,6 +86,7 @@ struct PackF32 {
   __device__ __forceinline__ static unsigned short scalarBits(float) { return 0; }
 };
 
+#ifdef AFIR_HAVE_F16
 struct PackF16 {
   using Scalar = __half;
   static constexpr int kLanes = 2;
@@ -87,6 +102,7 @@ struct PackF16 {
     return fromBits(static_cast<unsigned int>(u) | (static_cast<unsigned int>(u) << 16));
   }
   __device__ __forceinline__ static PackF16 constant(float c) { return {__float2half2_rn(c)}; }
+  __device__ __forceinline__ static PackF16 constantOf(const BodySrc &s) { return constant(s.value); }
   __device__ __forceinline__ static PackF16 add(PackF16 a, PackF16 b) { return {__hadd2_rn(a.x, b.x)}; }
   __device__ __forceinline__ static PackF16 sub(PackF16 a, PackF16 b) { return {__hsub2_rn(a.x, b.x)}; }
   __device__ __forceinline__ static PackF16 mul(PackF16 a, PackF16 b) { return {__hmul2_rn(a.x, b.x)}; }
@@ -99,6 +115,9 @@ struct PackF16 {
   __device__ __forceinline__ float lane(int i) const { return i ? __high2float(x) : __low2float(x); }
 };
 
+#endif  // AFIR_HAVE_F16
+
+#ifdef AFIR_HAVE_BF16
 struct PackBF16 {
   using Scalar = __nv_bfloat16;
   static constexpr int kLanes = 2;
@@ -114,6 +133,7 @@ struct PackBF16 {
     return fromBits(static_cast<unsigned int>(u) | (static_cast<unsigned int>(u) << 16));
   }
   __device__ __forceinline__ static PackBF16 constant(float c) { return {__float2bfloat162_rn(c)}; }
+  __device__ __forceinline__ static PackBF16 constantOf(const BodySrc &s) { return constant(s.value); }
   __device__ __forceinline__ static PackBF16 add(PackBF16 a, PackBF16 b) { return {__hadd2_rn(a.x, b.x)}; }
   __device__ __forceinline__ static PackBF16 sub(PackBF16 a, PackBF16 b) { return {__hsub2_rn(a.x, b.x)}; }
   __device__ __forceinline__ static PackBF16 mul(PackBF16 a, PackBF16 b) { return {__hmul2_rn(a.x, b.x)}; }
@@ -126,6 +146,8 @@ struct PackBF16 {
   __device__ __forceinline__ float lane(int i) const { return i ? __high2float(x) : __low2float(x); }
 };
 
+#endif  // AFIR_HAVE_BF16
+
 // Integer packs (afir.add/sub/mul and arith.addi/subi/muli/divsi/maxsi/minsi bodies on i32 and i16 tensors):
 // two's-complement wrap-around for add, sub and mul; signed max/min; signed division truncates toward zero, a zero
 // divisor gives 0 and INT_MIN / -1 gives INT_MIN (both are undefined in the IR, so any value is admissible).
@@ -137,6 +159,8 @@ struct PackI32 {
   __device__ __forceinline__ unsigned int bits() const { return static_cast<unsigned int>(x); }
   __device__ __forceinline__ static PackI32 splat(const void *p) { return {__ldg(reinterpret_cast<const int *>(p))}; }
   __device__ __forceinline__ static PackI32 constant(float c) { return {static_cast<int>(c)}; }
+  __device__ __forceinline__ static PackI32 constantInt(int c) { return {c}; }
+  __device__ __forceinline__ static PackI32 constantOf(const BodySrc &s) { return {s.ivalue}; }
   __device__ __forceinline__ static PackI32 add(PackI32 a, PackI32 b) { return fromBits(a.bits() + b.bits()); }
   __device__ __forceinline__ static PackI32 sub(PackI32 a, PackI32 b) { return fromBits(a.bits() - b.bits()); }
   __device__ __forceinline__ static PackI32 mul(PackI32 a, PackI32 b) { return fromBits(a.bits() * b.bits()); }
@@ -161,10 +185,12 @@ struct PackI16 {
     const unsigned int u = __ldg(reinterpret_cast<const unsigned short *>(p));
     return {u | (u << 16)};
   }
-  __device__ __forceinline__ static PackI16 constant(float c) {
-    const unsigned int u = static_cast<unsigned int>(static_cast<int>(c)) & 0xffffu;
+  __device__ __forceinline__ static PackI16 constantInt(int c) {
+    const unsigned int u = static_cast<unsigned int>(c) & 0xffffu;
     return {u | (u << 16)};
   }
+  __device__ __forceinline__ static PackI16 constant(float c) { return constantInt(static_cast<int>(c)); }
+  __device__ __forceinline__ static PackI16 constantOf(const BodySrc &s) { return constantInt(s.ivalue); }
   __device__ __forceinline__ static int lo(unsigned int v) { return static_cast<short>(v & 0xffffu); }
   __device__ __forceinline__ static int hi(unsigned int v) { return static_cast<short>(v >> 16); }
   __device__ __forceinline__ static PackI16 join(int l, int h) {
@@ -208,6 +234,7 @@ template <int ID> struct Body;
 #define AFIR_BODY(ID, NVIEWS, EXPR)                                                       \
   template <> struct Body<ID> {                                                            \
     static constexpr int kViews = NVIEWS;                                                  \
+    static constexpr bool kInterpreted = false;                                            \
     template <class P> __device__ __forceinline__ static P eval(const P *v, const BodyProgram &) { \
       (void)v;                                                                             \
       return EXPR;                                                                         \
@@ -226,7 +253,7 @@ AFIR_BODY(kBodyRelu, 1, P::max(v[0], P::constant(0.0f)))
 
 // ---- interpreter: any chain of up to kMaxBodyOps ops over up to kMaxViews views --------------------
 template <class P> __device__ __forceinline__ P interpFetch(const BodySrc &s, const P *v, const P *r, int upto) {
-  if (s.kind == kSrcConst) return P::constant(s.value);
+  if (s.kind == kSrcConst) return P::constantOf(s);
   if (s.kind == kSrcView) {
     P x = v[0];
 #pragma unroll
@@ -243,6 +270,7 @@ template <class P> __device__ __forceinline__ P interpFetch(const BodySrc &s, co
 
 template <> struct Body<kBodyInterpreted> {
   static constexpr int kViews = kMaxViews;
+  static constexpr bool kInterpreted = true;
   template <class P> __device__ __forceinline__ static P eval(const P *v, const BodyProgram &prog) {
     P r[kMaxBodyOps];
 #pragma unroll
@@ -285,16 +313,16 @@ __device__ __forceinline__ unsigned int comp(const uint4 &v, int q) { return q =
 template <class P>
 __device__ __forceinline__ uint4 interpOperand(const BodySrc &s, const uint4 *slot, const uint4 &last, int opIndex) {
   if (s.kind == kSrcConst) {
-    const unsigned int c = P::constant(s.value).bits();
+    const unsigned int c = P::constantOf(s).bits();
     return make_uint4(c, c, c, c);
   }
   if (s.kind == kSrcOp && s.index == opIndex - 1) return last;
   return slot[s.kind == kSrcView ? s.index : kMaxViews + s.index];
 }
 
-template <int BODY, class P, int NV>
+template <class B, class P, int NV>
 __device__ __forceinline__ uint4 evalVector16(const uint4 (&raw)[NV], const BodyProgram &prog) {
-  if constexpr (BODY == kBodyInterpreted) {
+  if constexpr (B::kInterpreted) {
     uint4 slot[kMaxViews + kMaxBodyOps];
 #pragma unroll
     for (int k = 0; k < kMaxViews; ++k)
@@ -317,7 +345,6 @@ __device__ __forceinline__ uint4 evalVector16(const uint4 (&raw)[NV], const Body
     }
     return last;
   } else {
-    using B = Body<BODY>;
     unsigned int out[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {

@@ -13,7 +13,7 @@
 // (indices first, then table pieces + the other views).  Column gather: each thread produces one
 // 16-byte output vector from scalar loads of the (cache-resident) table row.
 // Indices outside the table raise *status and leave the output untouched; nothing is clamped.
-#include "kernels/ew_common.cuh"
+#include "kernels/gather_skel.cuh"
 
 #include <algorithm>
 
@@ -21,128 +21,9 @@ namespace afir {
 namespace kernels {
 namespace {
 
-struct GaParams {
-  const char *table;
-  long long tableRows, tableCols, tableRowStride;
-  const void *indices;
-  int index64;
-  const char *vbase[kMaxViews];
-  long long rowStride[kMaxViews];
-  int colStride[kMaxViews];
-  int numViews;
-  char *out;
-  long long outRowStride;
-  unsigned int vecPerRow;
-  unsigned int totalVec;
-  unsigned int numTiles;
-  FastDiv divVpr;
-  unsigned long long *status;
-  BodyProgram prog;
-  // SHARDED kernels: the table's rows are split into contiguous shards of rowsPerShard rows, shard s at
-  // shardBase[s], which may be another GPU's memory (peer-mapped; read with plain loads over NVLink)
-  const char *shardBase[kMaxTableShards];
-  long long rowsPerShard;
-  FastDiv divRowsPerShard;  // valid when the table has fewer than 2^32 rows
-};
-
-__device__ __forceinline__ long long loadIndex(const void *idx, long long i, int is64) {
-  return is64 ? __ldg(static_cast<const long long *>(idx) + i) : static_cast<long long>(__ldg(static_cast<const int *>(idx) + i));
-}
-
-template <class P> __device__ __forceinline__ void storeOne(void *p, P v);
-template <> __device__ __forceinline__ void storeOne<PackF32>(void *p, PackF32 v) { *static_cast<float *>(p) = v.x; }
-template <> __device__ __forceinline__ void storeOne<PackF16>(void *p, PackF16 v) {
-  *static_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
-}
-template <> __device__ __forceinline__ void storeOne<PackBF16>(void *p, PackBF16 v) {
-  *static_cast<unsigned short *>(p) = static_cast<unsigned short>(v.bits() & 0xffffu);
-}
-
-// ---- axis 0 ------------------------------------------------------------------------------------
 template <class P, int BODY, int UNROLL, bool VECTOR, bool SHARDED = false>
 __global__ void __launch_bounds__(512) gatherRowsKernel(const __grid_constant__ GaParams prm) {
-  using B = Body<BODY>;
-  constexpr int NV = B::kViews;
-  constexpr int kElems = VECTOR ? Vec16<P>::kElems : 1;
-  constexpr int kElemBytes = sizeof(typename P::Scalar);
-  const unsigned int tileVecs = blockDim.x * UNROLL;
-
-  for (unsigned int tile = blockIdx.x; tile < prm.numTiles; tile += gridDim.x) {
-    const unsigned int g0 = tile * tileVecs + threadIdx.x;
-    unsigned int row[UNROLL], col[UNROLL];
-    long long src[UNROLL];
-    bool live[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const unsigned int g = g0 + u * blockDim.x;
-      live[u] = g < prm.totalVec;
-      row[u] = fastDivide(g, prm.divVpr);
-      col[u] = g - row[u] * prm.vecPerRow;
-      src[u] = live[u] ? loadIndex(prm.indices, row[u], prm.index64) : 0;
-    }
-    uint4 raw[UNROLL][NV];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      if (live[u] && (src[u] < 0 || src[u] >= prm.tableRows)) {
-        if (col[u] == 0 && prm.status) atomicAdd(prm.status, 1ull);
-        live[u] = false;
-      }
-      if (live[u]) {
-        const char *t;
-        if (SHARDED) {
-          const unsigned int shard = fastDivide(static_cast<unsigned int>(src[u]), prm.divRowsPerShard);
-          const long long local = src[u] - static_cast<long long>(shard) * prm.rowsPerShard;
-          t = prm.shardBase[shard] + (local * prm.tableRowStride + static_cast<long long>(col[u]) * kElems) * kElemBytes;
-        } else {
-          t = prm.table + (src[u] * prm.tableRowStride + static_cast<long long>(col[u]) * kElems) * kElemBytes;
-        }
-        if (VECTOR) raw[u][0] = loadStream16(t);
-        else {
-          const unsigned int s = P::splat(t).bits();
-          raw[u][0] = make_uint4(s, s, s, s);
-        }
-#pragma unroll
-        for (int k = 1; k < NV; ++k) {
-          raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
-          if (k < prm.numViews) {
-            const char *p = prm.vbase[k] + (static_cast<long long>(row[u]) * prm.rowStride[k] +
-                                           static_cast<long long>(col[u]) * kElems * prm.colStride[k]) * kElemBytes;
-            if (VECTOR && prm.colStride[k] == 1) raw[u][k] = prm.rowStride[k] == 0 ? loadKeep16(p) : loadStream16(p);
-            else {
-              const unsigned int s = P::splat(p).bits();
-              raw[u][k] = make_uint4(s, s, s, s);
-            }
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      if (!live[u]) continue;
-      char *dst = prm.out + (static_cast<long long>(row[u]) * prm.outRowStride + static_cast<long long>(col[u]) * kElems) * kElemBytes;
-      if (VECTOR && BODY == kBodyInterpreted) {
-        storeStream16(dst, evalVector16<BODY, P, NV>(raw[u], prm.prog));
-      } else if (VECTOR) {
-        Vec16<P> o;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          P v[NV];
-#pragma unroll
-          for (int k = 0; k < NV; ++k) {
-            const unsigned int bits = q == 0 ? raw[u][k].x : q == 1 ? raw[u][k].y : q == 2 ? raw[u][k].z : raw[u][k].w;
-            v[k] = P::fromBits(bits);
-          }
-          o.p[q] = B::template eval<P>(v, prm.prog);
-        }
-        storeStream16(dst, o.raw());
-      } else {
-        P v[NV];
-#pragma unroll
-        for (int k = 0; k < NV; ++k) v[k] = P::fromBits(raw[u][k].x);
-        storeOne<P>(dst, B::template eval<P>(v, prm.prog));
-      }
-    }
-  }
+  gatherRowsTiles<P, Body<BODY>, UNROLL, VECTOR, SHARDED>(prm);
 }
 
 // ---- axis 1 ------------------------------------------------------------------------------------

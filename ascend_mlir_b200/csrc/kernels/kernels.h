@@ -3,8 +3,15 @@
 // launch descriptor plus TilingData values, the .cu files turn them into kernel launches.
 #pragma once
 
+#ifdef __CUDACC_RTC__
+// Compiled at run time for a generated kernel (no host headers there): the fixed-width names this file uses.
+typedef long long int64_t;
+typedef unsigned long long uint64_t;
+typedef unsigned long uintptr_t;
+#else
 #include <cstddef>
 #include <cstdint>
+#endif
 
 typedef struct CUstream_st *cudaStream_t;
 
@@ -14,7 +21,9 @@ namespace kernels {
 enum ElemType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kInt32 = 3, kInt16 = 4 };  // integers: elementwise groups only
 enum IndexType : int { kI32 = 0, kI64 = 1 };
 
+#ifndef __CUDACC_RTC__
 inline int elemBytes(int t) { return (t == kF32 || t == kInt32) ? 4 : 2; }
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Fused elementwise bodies.  A body is a short chain of arith ops over the values loaded from
@@ -30,6 +39,7 @@ struct BodySrc {
   int kind;     // BodySrcKind
   int index;    // view index or op index
   float value;  // constant (already representable in the element type)
+  int ivalue = 0;  // the same constant for integer element types, exact (a float holds integers up to 2^24 only)
 };
 struct BodyOp {
   int op;  // BodyOpCode
@@ -43,8 +53,10 @@ struct BodyProgram {
   int numViewsUsed = kMaxViews;
   unsigned int storeMask = 0xffffffffu;
 };
+#ifndef __CUDACC_RTC__
 // Derives numViewsUsed and storeMask from the ops; a program left as parsed (all views, every result kept) is valid too.
 void finishBodyProgram(BodyProgram &prog);
+#endif
 
 // Ids of the bodies compiled as straight-line specialisations (everything else runs through
 // the op-by-op interpreter kernel, same results, lower throughput).
@@ -62,8 +74,10 @@ enum BodyId : int {
   kNumBodies
 };
 
+#ifndef __CUDACC_RTC__
 // Returns the specialised body id computing `prog`, or kBodyInterpreted.
 int matchBody(const BodyProgram &prog, int numViews);
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Elementwise / broadcast / split / concat groups.
@@ -96,8 +110,10 @@ struct ElementwiseLaunch {
   int64_t viewOuterStride[kMaxViews] = {0, 0, 0, 0, 0, 0};
   int64_t outOuterStride = 0;
 };
+#ifndef __CUDACC_RTC__
 // Returns a cudaError_t value (0 = success); *launched gets the number of kernels launched.
 int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *launched);
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Row reduction: out[m] = sum_n body(views)(m, n), f32 accumulation from zero.
@@ -137,12 +153,35 @@ struct RowReduceLaunch {
   // every rank's mailbox instead of `out`, waits (2 s at most) for the other ranks' partial sums and writes
   // out[m] = their sum in rank order.  Column slicing (splitCols) is not combined with it.
   const RowReduceExchange *exchange = nullptr;
+  // Device word that the staged kernel sets to 1 when a wait for one of its copies runs out (the executor points
+  // it into its own workspace, so concurrent executors do not read each other's time-outs); null = a word of the
+  // library, one per device, read by rowReduceCheckStatus.
+  unsigned int *status = nullptr;
 };
+#ifndef __CUDACC_RTC__
 size_t rowReduceWorkspaceBytes(int64_t rows, int splitCols);
+#endif
+// How launchRowReduce runs a given reduction (see planRowReduce).
+struct RowReducePlan {
+  bool vector = false;        // 16-byte accesses (else one element at a time)
+  int64_t vecPerRow = 0, vecPerSlice = 0;
+  int slices = 1;             // column slices per row (> 1: partial sums through the workspace + a finalize kernel)
+  int threads = 128, lanes = 32;
+  int64_t grid = 1;
+  int finalizeThreads = 256;
+  int64_t finalizeGrid = 1;
+  bool staged = false;        // the bulk-copy staged kernel: one streamed view through per-warp shared-memory rings
+  int streamedView = -1, streamWarps = 0, streamStages = 0;
+  unsigned int streamChunkBytes = 0;
+  size_t smemBytes = 0;
+};
+#ifndef __CUDACC_RTC__
+int planRowReduce(const RowReduceLaunch &l, int smCount, RowReducePlan &plan);
 int chooseRowReduceSplit(int64_t rows, int64_t cols, int smCount);
 int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched);
 // After the stream has been synchronised: non-zero when a staged-copy wait gave up.
 int rowReduceCheckStatus(int device, char *errorText);
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Gather + elementwise.  axis 0 (row gather, "embedding"): g(i,j) = table[idx[i], j];
@@ -180,7 +219,9 @@ struct GatherLaunch {
   const void *tableShards[kMaxTableShards] = {nullptr};
   int64_t rowsPerShard = 0;
 };
+#ifndef __CUDACC_RTC__
 int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched);
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // 2-D transpose out[c, r] = in[r, c] (2- or 4-byte elements): register-block kernel for 16-byte-aligned
@@ -199,7 +240,9 @@ struct TransposeLaunch {
   int variant = 0;          // 0: whole lines stored, 1: same with 2 blocks per thread, 2: whole lines loaded, 3: same, 2 blocks
   int forceTileKernel = 0;  // 1: use the shared-memory tile kernel even when the operands are aligned
 };
+#ifndef __CUDACC_RTC__
 int launchTranspose(const TransposeLaunch &l, cudaStream_t stream, int *launched);
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Matmul + bias + LeakyReLU:  out = epilogue(A[M,K] . B[K,N] + bias[N]); row-major, 16-bit inputs,
@@ -225,6 +268,7 @@ struct MatmulLaunch {
                         // no transposes; it is how torch.nn.Linear keeps its weight)
   MatmulPlan *planOut = nullptr;  // receives the plan that was launched (variant, tile, grid, ...)
 };
+#ifndef __CUDACC_RTC__
 // errorText (optional, >= 256 bytes) receives a description when the launch is refused or the
 // kernel reports a bounded-wait timeout.
 int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char *errorText);
@@ -234,6 +278,8 @@ int matmulCheckStatus(int device, char *errorText);
 // Library-wide helpers.
 int deviceSmCount(int device);
 const char *cudaErrorText(int code);
+
+#endif
 
 } // namespace kernels
 } // namespace afir

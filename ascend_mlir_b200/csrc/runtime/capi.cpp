@@ -237,6 +237,11 @@ AFIR_EXPORT int afirt_executor_last_launch_count(AfirtExecutor executor) {
   return ex ? ex->lastLaunchCount() : 0;
 }
 
+AFIR_EXPORT int afirt_executor_last_launch_generated(AfirtExecutor executor) {
+  auto *ex = reinterpret_cast<CudaExecutor *>(executor);
+  return ex && ex->lastLaunchGenerated() ? 1 : 0;
+}
+
 AFIR_EXPORT uint64_t afirt_executor_total_launch_count(AfirtExecutor executor) {
   auto *ex = reinterpret_cast<CudaExecutor *>(executor);
   return ex ? ex->totalLaunchCount() : 0;

@@ -120,6 +120,11 @@ Status parseSrc(const json::Value &v, int numViews, int opIndex, kernels::BodySr
   if (v.isNumber()) {
     out.kind = kernels::kSrcConst;
     out.value = static_cast<float>(v.asDouble());
+    // integer element types read the constant from here: exact, where the float above rounds beyond 2^24
+    const double d = v.asDouble();
+    const long long wide = v.isInt() ? static_cast<long long>(v.asInt())
+                                     : (d >= -9.2e18 && d <= 9.2e18 ? static_cast<long long>(d) : 0ll);
+    out.ivalue = static_cast<int>(static_cast<unsigned int>(static_cast<unsigned long long>(wide)));  // wraps like the type
     return Status::success();
   }
   if (!v.isString() || v.asString().size() < 2) return Status::error("body operand must be \"v<k>\", \"%<k>\" or a number");
@@ -321,7 +326,7 @@ Status parseDescriptorBinary(const uint8_t *data, size_t len, LaunchDescriptor &
     uint32_t version, jsonLen;
     std::memcpy(&version, data + 4, 4);
     std::memcpy(&jsonLen, data + 8, 4);
-    if (version != kContainerVersion) return Status::error("unsupported kernel container version");
+    if (version != kContainerVersion && version != kContainerVersionWithCode) return Status::error("unsupported kernel container version");
     if (static_cast<size_t>(jsonLen) + 12 > len) return Status::error("truncated kernel container");
     text.assign(reinterpret_cast<const char *>(data + 12), jsonLen);
   } else {
@@ -336,14 +341,47 @@ Status parseDescriptorBinary(const uint8_t *data, size_t len, LaunchDescriptor &
   return parseDescriptorJson(root, out);
 }
 
-std::vector<uint8_t> wrapDescriptorContainer(const std::string &jsonText) {
-  std::vector<uint8_t> out(12 + jsonText.size());
+std::vector<uint8_t> wrapDescriptorContainer(const std::string &jsonText, const std::vector<uint8_t> &cubin, const std::string &source) {
+  const bool withCode = !cubin.empty() || !source.empty();
+  std::vector<uint8_t> out(12 + jsonText.size() + (withCode ? 8 + cubin.size() + source.size() : 0));
   std::memcpy(out.data(), "AFCU", 4);
-  const uint32_t version = kContainerVersion, n = static_cast<uint32_t>(jsonText.size());
+  const uint32_t version = withCode ? kContainerVersionWithCode : kContainerVersion, n = static_cast<uint32_t>(jsonText.size());
   std::memcpy(out.data() + 4, &version, 4);
   std::memcpy(out.data() + 8, &n, 4);
   std::memcpy(out.data() + 12, jsonText.data(), jsonText.size());
+  if (withCode) {
+    size_t off = 12 + jsonText.size();
+    const uint32_t cubinLen = static_cast<uint32_t>(cubin.size()), sourceLen = static_cast<uint32_t>(source.size());
+    std::memcpy(out.data() + off, &cubinLen, 4);
+    if (cubinLen) std::memcpy(out.data() + off + 4, cubin.data(), cubin.size());
+    off += 4 + cubin.size();
+    std::memcpy(out.data() + off, &sourceLen, 4);
+    if (sourceLen) std::memcpy(out.data() + off + 4, source.data(), source.size());
+  }
   return out;
+}
+
+ContainerCode containerCode(const uint8_t *data, size_t len) {
+  ContainerCode code;
+  if (!data || len < 12 || std::memcmp(data, "AFCU", 4) != 0) return code;
+  uint32_t version, jsonLen;
+  std::memcpy(&version, data + 4, 4);
+  std::memcpy(&jsonLen, data + 8, 4);
+  if (version != kContainerVersionWithCode) return code;
+  size_t off = 12 + static_cast<size_t>(jsonLen);
+  uint32_t cubinLen = 0, sourceLen = 0;
+  if (off + 4 > len) return code;
+  std::memcpy(&cubinLen, data + off, 4);
+  if (off + 4 + cubinLen + 4 > len) return code;
+  const uint8_t *cubin = data + off + 4;
+  off += 4 + cubinLen;
+  std::memcpy(&sourceLen, data + off, 4);
+  if (off + 4 + sourceLen > len) return code;
+  code.cubin = cubin;
+  code.cubinLen = cubinLen;
+  code.source = reinterpret_cast<const char *>(data + off + 4);
+  code.sourceLen = sourceLen;
+  return code;
 }
 
 Status unpackTiling(const LaunchDescriptor &d, const uint8_t *bytes, size_t len, std::map<std::string, int64_t> &out) {

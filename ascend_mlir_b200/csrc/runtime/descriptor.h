@@ -78,14 +78,26 @@ struct LaunchDescriptor {
   size_t tilingBytes() const;
 };
 
-// Container written by afirt_compiler_compile: "AFCU" | u32 version | u32 json length | json bytes.
+// Container written by afirt_compiler_compile: "AFCU" | u32 version | u32 json length | json bytes, and from
+// version 2 on the group's generated kernel: | u32 cubin length | cubin | u32 source length | CUDA source.
+// Version 1 (descriptor only) is what matmul and bare-transpose groups get: they run on the library's own kernels.
 constexpr uint32_t kContainerMagic = 0x55434641u;  // "AFCU" little-endian
 constexpr uint32_t kContainerVersion = 1;
+constexpr uint32_t kContainerVersionWithCode = 2;
 
 Status parseDescriptorJson(const json::Value &root, LaunchDescriptor &out);
 // Accepts the binary container or bare JSON text.
 Status parseDescriptorBinary(const uint8_t *data, size_t len, LaunchDescriptor &out);
-std::vector<uint8_t> wrapDescriptorContainer(const std::string &jsonText);
+std::vector<uint8_t> wrapDescriptorContainer(const std::string &jsonText, const std::vector<uint8_t> &cubin = {},
+                                             const std::string &source = std::string());
+// The generated kernel inside a container (pointers into `data`; null / 0 where the container holds none).
+struct ContainerCode {
+  const uint8_t *cubin = nullptr;
+  size_t cubinLen = 0;
+  const char *source = nullptr;
+  size_t sourceLen = 0;
+};
+ContainerCode containerCode(const uint8_t *data, size_t len);
 
 // Decodes packed tiling bytes (schema order, little-endian) into named values.
 Status unpackTiling(const LaunchDescriptor &d, const uint8_t *bytes, size_t len, std::map<std::string, int64_t> &out);

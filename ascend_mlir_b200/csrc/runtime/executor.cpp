@@ -2,6 +2,8 @@
 
 #include <cuda_runtime_api.h>
 
+#include "codegen/nvrtc_compile.h"
+
 #include <algorithm>
 #include <cctype>
 #include <cstdio>
@@ -167,8 +169,8 @@ static void printLaunchTrace(const RunRequest &req, const LaunchDescriptor &desc
   }
 }
 
-Status CudaExecutor::validate(const RunRequest &req, std::shared_ptr<const LaunchDescriptor> &desc,
-                              std::map<std::string, int64_t> &tiling) {
+Status CudaExecutor::validate(const RunRequest &req, CachedKernel *&kernel, std::map<std::string, int64_t> &tiling) {
+  std::shared_ptr<const LaunchDescriptor> desc;
   if (!initialized_) return Status::error("executor has not been initialized");
   if (!req.binary || req.binaryLen == 0) return Status::error("binary data is required");
   if (req.functionName.empty()) return Status::error("function name is required");
@@ -185,9 +187,14 @@ Status CudaExecutor::validate(const RunRequest &req, std::shared_ptr<const Launc
   if (it == cache_.end()) {
     auto d = std::make_shared<LaunchDescriptor>();
     if (Status s = parseDescriptorBinary(req.binary, req.binaryLen, *d); !s) return s.withStage("cuda:artifact");
-    it = cache_.emplace(key, std::move(d)).first;
+    CachedKernel fresh;
+    fresh.desc = std::move(d);
+    const ContainerCode code = containerCode(req.binary, req.binaryLen);
+    if (code.cubinLen) fresh.cubin.assign(code.cubin, code.cubin + code.cubinLen);
+    it = cache_.emplace(key, std::move(fresh)).first;
   }
-  desc = it->second;
+  kernel = &it->second;
+  desc = kernel->desc;
   if (desc->kernel != req.functionName)
     return Status::error("[cuda:artifact] kernel binary defines '" + desc->kernel + "', not '" + req.functionName + "'");
   if (req.numInputs != desc->numInputs || req.numOutputs != desc->numOutputs)
@@ -202,10 +209,62 @@ Status CudaExecutor::validate(const RunRequest &req, std::shared_ptr<const Launc
   return Status::success();
 }
 
+// AFIR_CUDA_CODEGEN: "auto" (default) runs a group on its generated kernel when the library's prebuilt kernels would
+// interpret its body; "always" whenever a generated kernel exists; "never" keeps every launch on the library.
+static int codegenMode() {
+  const char *v = std::getenv("AFIR_CUDA_CODEGEN");
+  if (!v || !*v) return 1;
+  const std::string s(v);
+  if (s == "never" || s == "0" || s == "off") return 0;
+  if (s == "always" || s == "2") return 2;
+  return 1;
+}
+
+bool CudaExecutor::prepareGenerated(CachedKernel &kernel) {
+  if (kernel.generatedTried) return kernel.generatedUsable;
+  kernel.generatedTried = true;
+  const LaunchDescriptor &d = *kernel.desc;
+  const uint8_t *cubin = kernel.cubin.data();
+  size_t cubinLen = kernel.cubin.size();
+  std::shared_ptr<const std::vector<uint8_t>> compiled;
+  if (cubinLen == 0) {
+    // a descriptor that did not go through afirt_compiler_compile: generate and compile now
+    const codegen::GeneratedKernel gen = codegen::generateKernelSource(d);
+    if (!gen.supported) { kernel.generatedNote = gen.whyNot; return false; }
+    if (Status s = codegen::compileToCubinCached(gen, compiled); !s) { kernel.generatedNote = s.message(); return false; }
+    cubin = compiled->data();
+    cubinLen = compiled->size();
+  }
+  if (Status s = DeviceModule::load(cubin, cubinLen, device_, kernel.binding.module); !s) { kernel.generatedNote = s.message(); return false; }
+  if (Status s = kernel.binding.module->function(d.kernel, kernel.binding.mainFn); !s) { kernel.generatedNote = s.message(); return false; }
+  if (d.kernelClass == KernelClass::RowReduce) {
+    // optional entries: a module without them simply never takes that plan
+    if (!kernel.binding.module->function(d.kernel + "__staged", kernel.binding.stagedFn)) kernel.binding.stagedFn = nullptr;
+    if (!kernel.binding.module->function(d.kernel + "__finalize", kernel.binding.finalizeFn)) kernel.binding.finalizeFn = nullptr;
+  }
+  kernel.generatedUsable = true;
+  return true;
+}
+
+Status CudaExecutor::dispatch(CachedKernel &kernel, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args, LaunchInfo &info) {
+  const LaunchDescriptor &d = *kernel.desc;
+  const int mode = codegenMode();
+  const bool classHasCode = d.kernelClass == KernelClass::Elementwise || d.kernelClass == KernelClass::RowReduce ||
+                            d.kernelClass == KernelClass::Gather;
+  if (mode != 0 && classHasCode && !(kernel.generatedTried && !kernel.generatedUsable) &&
+      (mode == 2 || prebuiltWouldInterpret(d)) && generatedLaunchApplies(d, tiling, args) && prepareGenerated(kernel)) {
+    Status s = launchGenerated(d, tiling, args, kernel.binding, info);
+    // sizes the generated loop does not count (beyond 32 bits of elements) go to the library's kernels
+    if (s || s.message().rfind("[generated:unsupported]", 0) != 0) return s;
+  }
+  return launchDescriptor(d, tiling, args, info);
+}
+
 Status CudaExecutor::runHost(const RunRequest &req) {
-  std::shared_ptr<const LaunchDescriptor> desc;
+  CachedKernel *kernel = nullptr;
   std::map<std::string, int64_t> tiling;
-  if (Status s = validate(req, desc, tiling); !s) return s;
+  if (Status s = validate(req, kernel, tiling); !s) return s;
+  const std::shared_ptr<const LaunchDescriptor> desc = kernel->desc;
   if (Status s = ensureStream(); !s) return s.withStage("cuda:device");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
@@ -269,7 +328,7 @@ Status CudaExecutor::runHost(const RunRequest &req) {
       if (const char *forced = std::getenv("AFIR_CUDA_PIPELINE_CHUNKS")) chunks = std::max<int64_t>(2, std::atoll(forced));
       int64_t chunkRows = (plan.rows + chunks - 1) / chunks;
       chunkRows = ((chunkRows + quantum - 1) / quantum) * quantum;
-      if (chunkRows < plan.rows) return runHostPipelined(req, *desc, tiling, args, plan, chunkRows);
+      if (chunkRows < plan.rows) return runHostPipelined(req, *kernel, tiling, args, plan, chunkRows);
     }
   }
 
@@ -296,13 +355,15 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] workspace clear failed");
 
   LaunchInfo info;
-  Status ls = launchDescriptor(*desc, tiling, args, info);
+  Status ls = dispatch(*kernel, tiling, args, info);
   lastLaunchCount_ = info.kernelsLaunched;
+  lastLaunchGenerated_ = info.generated;
   totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
   if (!ls) {
     cudaStreamSynchronize(stream);
     return launchStage(ls);
   }
+  if (launchTraceEnabled()) std::fprintf(stderr, "[cuda-launch] code=%s kernels=%d\n", info.generated ? "generated" : "library", info.kernelsLaunched);
   if (launchTraceEnabled() && !info.plan.empty()) std::fprintf(stderr, "[cuda-launch] matmul plan: %s\n", info.plan.c_str());
   for (int i = 0; i < req.numOutputs; ++i) {
     if (!req.outputBytes[i]) continue;
@@ -342,9 +403,10 @@ Status CudaExecutor::ensureCopyStreams(size_t events) {
   return Status::success();
 }
 
-Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescriptor &desc,
+Status CudaExecutor::runHostPipelined(const RunRequest &req, CachedKernel &kernel,
                                       const std::map<std::string, int64_t> &tiling, LaunchArgs &args,
                                       const RowPipelinePlan &plan, int64_t chunkRows) {
+  const LaunchDescriptor &desc = *kernel.desc;
   const int64_t numChunks = (plan.rows + chunkRows - 1) / chunkRows;
   if (Status s = ensureCopyStreams(static_cast<size_t>(2 * numChunks + 1)); !s) return s.withStage("cuda:device");
   cudaStream_t compute = static_cast<cudaStream_t>(stream_);
@@ -388,8 +450,9 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
     args.rowBegin = b;
     args.rowEnd = en;
     LaunchInfo info;
-    Status ls = launchDescriptor(desc, tiling, args, info);
+    Status ls = dispatch(kernel, tiling, args, info);
     lastLaunchCount_ += info.kernelsLaunched;
+    lastLaunchGenerated_ = info.generated;
     totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
     usesStatus = usesStatus || info.usesStatusBlock;
     if (c == 0 && launchTraceEnabled() && !info.plan.empty())
@@ -433,9 +496,10 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, const LaunchDescrip
 Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t workspaceBytes, void *stream,
                                   const kernels::RowReduceExchange *exchange, const std::vector<const void *> &tableShards,
                                   int64_t rowsPerShard) {
-  std::shared_ptr<const LaunchDescriptor> desc;
+  CachedKernel *kernel = nullptr;
   std::map<std::string, int64_t> tiling;
-  if (Status s = validate(req, desc, tiling); !s) return s;
+  if (Status s = validate(req, kernel, tiling); !s) return s;
+  const std::shared_ptr<const LaunchDescriptor> desc = kernel->desc;
   cudaError_t e = cudaSetDevice(device_);
   if (e != cudaSuccess) return cudaFail(e, "[cuda:device] cudaSetDevice");
 
@@ -466,26 +530,32 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   }
   if (launchTraceEnabled()) printLaunchTrace(req, *desc, args, device_, "device");
   LaunchInfo info;
-  if (desc->kernelClass == KernelClass::Gather && args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes) {
-    e = cudaMemsetAsync(args.workspace, 0, 8, args.stream);
+  // The status words (bad gather indices, a staged reduction's time-out) accumulate over the launches queued since
+  // the last synchronize: they are cleared only when nothing unread is pending on this workspace.
+  const bool hasStatusWords = (desc->kernelClass == KernelClass::Gather || desc->kernelClass == KernelClass::RowReduce) &&
+                              args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes;
+  if (hasStatusWords && !(statusPending_ && statusWorkspace_ == args.workspace)) {
+    e = cudaMemsetAsync(args.workspace, 0, kWorkspaceStatusReadBytes, args.stream);
     if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] workspace clear failed");
   }
-  Status ls = launchDescriptor(*desc, tiling, args, info);
+  Status ls = dispatch(*kernel, tiling, args, info);
   lastLaunchCount_ = info.kernelsLaunched;
+  lastLaunchGenerated_ = info.generated;
   totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
   if (!ls) return launchStage(ls);
   if (launchTraceEnabled() && !info.plan.empty()) std::fprintf(stderr, "[cuda-launch] matmul plan: %s\n", info.plan.c_str());
-  statusPending_ = info.usesStatusBlock;
-  statusWorkspace_ = args.workspace;
+  if (launchTraceEnabled()) std::fprintf(stderr, "[cuda-launch] code=%s kernels=%d\n", info.generated ? "generated" : "library", info.kernelsLaunched);
+  statusPending_ = statusPending_ || info.usesStatusBlock;
+  if (info.usesStatusBlock) statusWorkspace_ = args.workspace;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
   reducePending_ = desc->kernelClass == KernelClass::RowReduce;
   return Status::success();
 }
 
 Status CudaExecutor::profileResident(const RunRequest &req, int repeats, double &medianMicroseconds) {
-  std::shared_ptr<const LaunchDescriptor> desc;
+  CachedKernel *kernel = nullptr;
   std::map<std::string, int64_t> tiling;
-  if (Status s = validate(req, desc, tiling); !s) return s;
+  if (Status s = validate(req, kernel, tiling); !s) return s;
   if (Status s = ensureStream(); !s) return s.withStage("cuda:device");
   const size_t numArgs = static_cast<size_t>(req.numInputs + req.numOutputs);
   if (slots_.size() < numArgs) return Status::error("[cuda:profiling] no resident buffers: run the kernel first");
@@ -507,7 +577,7 @@ Status CudaExecutor::profileResident(const RunRequest &req, int repeats, double 
   for (int r = 0; r < repeats + 2 && result; ++r) {  // two warm-up launches
     cudaEventRecord(e0, args.stream);
     LaunchInfo info;
-    Status ls = launchDescriptor(*desc, tiling, args, info);
+    Status ls = dispatch(*kernel, tiling, args, info);
     cudaEventRecord(e1, args.stream);
     totalLaunchCount_ += static_cast<uint64_t>(info.kernelsLaunched);
     if (!ls) { result = ls.withStage("cuda:profiling"); break; }
@@ -533,9 +603,12 @@ Status CudaExecutor::synchronize(void *stream) {
   if (e != cudaSuccess) return cudaFail(e, "[cuda:kernel_launch] kernel execution failed");
   if (statusPending_ && statusWorkspace_) {
     statusPending_ = false;
-    unsigned long long bad = 0;
-    e = cudaMemcpy(&bad, statusWorkspace_, sizeof(bad), cudaMemcpyDeviceToHost);
+    unsigned long long words[kWorkspaceStatusReadBytes / 8] = {0, 0};
+    e = cudaMemcpy(words, statusWorkspace_, sizeof(words), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] status read failed");
+    const unsigned long long bad = words[0];
+    if (static_cast<unsigned int>(words[1] & 0xffffffffull) != 0)
+      return Status::error("[cuda:kernel_launch] row reduction: a warp gave up waiting for a bulk copy after 2 s");
     constexpr unsigned long long kGatherTimeoutFlag = 1ull << 62;  // set by the staged gather kernel when a stage wait ran out
     if (bad & kGatherTimeoutFlag) return Status::error("[cuda:kernel_launch] gather kernel gave up waiting for a staged copy");
     if (bad) return Status::error("[cuda:kernel_launch] gather index out of range (" + std::to_string(bad) + " indices)");

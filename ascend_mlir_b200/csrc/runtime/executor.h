@@ -64,17 +64,36 @@ public:
   // resident and returns the median kernel time over `repeats` launches (CUDA events on the executor stream).
   Status profileResident(const RunRequest &req, int repeats, double &medianMicroseconds);
 
+  // True when the last launch ran the group's generated kernel (compiled from its own source), false when it ran
+  // a prebuilt kernel of the library.
+  bool lastLaunchGenerated() const { return lastLaunchGenerated_; }
   int lastLaunchCount() const { return lastLaunchCount_; }
   uint64_t totalLaunchCount() const { return totalLaunchCount_; }
 
 private:
   struct Slot { void *ptr = nullptr; size_t capacity = 0; };
-  Status validate(const RunRequest &req, std::shared_ptr<const LaunchDescriptor> &desc, std::map<std::string, int64_t> &tiling);
+  // One kernel binary this executor has met: its descriptor and, once a launch wanted it, its generated kernel
+  // loaded on the executor's device (the reference's runner caches registered binaries the same way,
+  // lib/Runtime/Execution/NativeExecutionRunner.cpp:332).
+  struct CachedKernel {
+    std::shared_ptr<const LaunchDescriptor> desc;
+    std::vector<uint8_t> cubin;   // from the container; empty = compile on first use
+    bool generatedTried = false;
+    bool generatedUsable = false;
+    std::string generatedNote;    // why not, when unusable
+    GeneratedBinding binding;
+  };
+  Status validate(const RunRequest &req, CachedKernel *&kernel, std::map<std::string, int64_t> &tiling);
+  // Loads (compiling first when the container brought no device binary) the kernel's generated code.
+  bool prepareGenerated(CachedKernel &kernel);
+  // Runs the descriptor on its generated kernel when the policy (AFIR_CUDA_CODEGEN = auto | always | never) and
+  // the launch allow it, on the library's prebuilt kernels otherwise.
+  Status dispatch(CachedKernel &kernel, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args, LaunchInfo &info);
   Status slotFor(size_t index, size_t bytes, void **out);
   Status ensureStream();
   Status ownWorkspace(size_t bytes);
   // Host path cut into leading-axis chunks: H2D of chunk i+1, the kernel on chunk i and D2H of chunk i-1 overlap.
-  Status runHostPipelined(const RunRequest &req, const LaunchDescriptor &desc, const std::map<std::string, int64_t> &tiling,
+  Status runHostPipelined(const RunRequest &req, CachedKernel &kernel, const std::map<std::string, int64_t> &tiling,
                           LaunchArgs &args, const RowPipelinePlan &plan, int64_t chunkRows);
   Status ensureCopyStreams(size_t events);
 
@@ -86,8 +105,9 @@ private:
   std::vector<void *> events_;
   std::vector<Slot> slots_;
   Slot workspace_;
-  std::unordered_map<uint64_t, std::shared_ptr<const LaunchDescriptor>> cache_;
+  std::unordered_map<uint64_t, CachedKernel> cache_;
   int lastLaunchCount_ = 0;
+  bool lastLaunchGenerated_ = false;
   uint64_t totalLaunchCount_ = 0;
   bool statusPending_ = false;
   void *statusWorkspace_ = nullptr;

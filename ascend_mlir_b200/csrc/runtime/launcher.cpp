@@ -120,21 +120,31 @@ Status cudaStatus(int code, const char *what) {
   return Status::error(std::string(what) + ": " + kernels::cudaErrorText(code));
 }
 
-Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
-                              const LaunchArgs &args, LaunchInfo &info) {
+// Evaluates an elementwise group's domain and views at these tiling values and checks every argument's size and
+// every view's bounds (shared by the prebuilt and the generated launch).
+Status resolveElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                               const LaunchArgs &args, int &et, std::vector<int64_t> &domain, std::vector<ResolvedView> &loads,
+                               ResolvedView &store) {
   bool ok;
-  const int et = toElemType(d.dtype, ok, /*integersToo=*/true);
+  et = toElemType(d.dtype, ok, /*integersToo=*/true);
   if (!ok) return Status::error("elementwise groups compute in f32, f16, bf16, i32 or i16");
-  std::vector<int64_t> domain;
   if (Status s = evalDims(g.domain, tiling, domain); !s) return s;
   if (Status s = applyRowRange(domain, args); !s) return s;
-  std::vector<ResolvedView> loads(g.loads.size());
-  ResolvedView store;
+  loads.assign(g.loads.size(), ResolvedView());
   for (size_t i = 0; i < g.loads.size(); ++i) {
     if (g.loads[i].dtype != d.dtype) return Status::error("load " + std::to_string(i) + " differs from the group element type");
     if (Status s = resolveView(g.loads[i], domain, tiling, args, "load", loads[i]); !s) return s;
   }
-  if (Status s = resolveView(g.store, domain, tiling, args, "store", store); !s) return s;
+  return resolveView(g.store, domain, tiling, args, "store", store);
+}
+
+Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                              const LaunchArgs &args, LaunchInfo &info) {
+  int et = 0;
+  std::vector<int64_t> domain;
+  std::vector<ResolvedView> loads;
+  ResolvedView store;
+  if (Status s = resolveElementwiseGroup(d, g, tiling, args, et, domain, loads, store); !s) return s;
   std::vector<ResolvedView *> all;
   for (auto &v : loads) all.push_back(&v);
   all.push_back(&store);
@@ -210,8 +220,9 @@ Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, con
   return Status::success();
 }
 
-Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
-                            const LaunchArgs &args, LaunchInfo &info) {
+// Resolves a row-reduction group against concrete sizes and pointers: everything launchRowReduce needs.
+Status buildRowReduceLaunch(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                            const LaunchArgs &args, kernels::RowReduceLaunch &l) {
   bool ok;
   const int et = toElemType(d.dtype, ok);
   if (!ok) return Status::error("row reductions compute in f32, f16 or bf16");
@@ -237,7 +248,7 @@ Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const
   if (outer.size() != 1) return Status::error("row reduction: leading dims do not collapse to one row dim");
   if (store.stride[0] != 1 && outer[0] != 1) return Status::error("row reduction: output rows must be contiguous");
 
-  kernels::RowReduceLaunch l = {};
+  l = kernels::RowReduceLaunch();
   l.elemType = et;
   l.rows = outer[0];
   l.cols = cols;
@@ -276,15 +287,26 @@ Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const
     l.workspace = static_cast<char *>(args.workspace) + kWorkspaceStatusBytes;
     l.workspaceBytes = args.workspaceBytes - kWorkspaceStatusBytes;
   }
+  // wait time-outs of the staged kernel go to this launch's own status block (not to a word shared by the device)
+  if (args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes && !args.exchange)
+    l.status = reinterpret_cast<unsigned int *>(static_cast<char *>(args.workspace) + kWorkspaceReduceStatusOffset);
   l.gridBlocks = args.blockDim;
+  return Status::success();
+}
+
+Status launchRowReduceGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                            const LaunchArgs &args, LaunchInfo &info) {
+  kernels::RowReduceLaunch l;
+  if (Status s = buildRowReduceLaunch(d, g, tiling, args, l); !s) return s;
   int n = 0;
   Status s = cudaStatus(kernels::launchRowReduce(l, args.stream, &n), "row-reduce launch");
   info.kernelsLaunched += n;
+  if (l.status) info.usesStatusBlock = true;
   return s;
 }
 
-Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
-                         const LaunchArgs &args, LaunchInfo &info) {
+Status buildGatherLaunch(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                         const LaunchArgs &args, kernels::GatherLaunch &l, bool &usesStatusBlock) {
   bool ok;
   const int et = toElemType(d.dtype, ok);
   if (!ok) return Status::error("gather groups compute in f32, f16 or bf16");
@@ -319,7 +341,7 @@ Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const st
   if (Status s = resolveView(g.store, domain, tiling, args, "store", store); !s) return s;
   if (store.stride[1] != 1 && domain[1] != 1) return Status::error("gather: output must be contiguous along the inner dim");
 
-  kernels::GatherLaunch l = {};
+  l = kernels::GatherLaunch();
   l.elemType = et;
   l.axis = g.gatherAxis;
   l.indexType = g.indices.dtype == DType::I64 ? kernels::kI64 : kernels::kI32;
@@ -361,7 +383,7 @@ Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const st
   l.body = g.body;
   if (args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes) {
     l.status = static_cast<unsigned long long *>(args.workspace);
-    info.usesStatusBlock = true;
+    usesStatusBlock = true;
   }
   l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
   l.unroll = static_cast<int>(optionalField(d.unrollField, tiling));
@@ -373,6 +395,15 @@ Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const st
   l.streamStages = static_cast<int>(optionalField(d.streamStagesField, tiling));
   l.streamRows = static_cast<int>(optionalField(d.streamRowsField, tiling));
   l.streamWarps = static_cast<int>(optionalField(d.streamWarpsField, tiling));
+  return Status::success();
+}
+
+Status launchGatherGroup(const LaunchDescriptor &d, const GroupSpec &g, const std::map<std::string, int64_t> &tiling,
+                         const LaunchArgs &args, LaunchInfo &info) {
+  kernels::GatherLaunch l;
+  bool usesStatus = false;
+  if (Status s = buildGatherLaunch(d, g, tiling, args, l, usesStatus); !s) return s;
+  if (usesStatus) info.usesStatusBlock = true;
   int n = 0;
   Status s = cudaStatus(kernels::launchGather(l, args.stream, &n), "gather launch");
   info.kernelsLaunched += n;
@@ -504,6 +535,198 @@ Status launchDescriptor(const LaunchDescriptor &d, const std::map<std::string, i
     if (!s) return s;
   }
   return Status::success();
+}
+
+
+// ---- generated kernels ---------------------------------------------------------------------------------------------
+bool prebuiltWouldInterpret(const LaunchDescriptor &d) {
+  if (d.dtype == DType::I32 || d.dtype == DType::I16) return true;
+  for (const GroupSpec &g : d.groups) {
+    const int body = kernels::matchBody(g.body, static_cast<int>(g.loads.size()));
+    switch (d.kernelClass) {
+    case KernelClass::Elementwise:
+      if (body == kernels::kBodyInterpreted) return true;
+      break;
+    case KernelClass::RowReduce:
+      if (body != kernels::kBodyCopy && body != kernels::kBodyAdd && body != kernels::kBodyMul) return true;
+      break;
+    case KernelClass::Gather:
+      if (body != kernels::kBodyCopy && body != kernels::kBodyAdd && body != kernels::kBodyMul && body != kernels::kBodyMulAdd) return true;
+      break;
+    default: break;
+    }
+  }
+  return false;
+}
+
+bool generatedLaunchApplies(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args) {
+  if (args.exchange || !args.tableShards.empty()) return false;
+  if (!args.workspace || args.workspaceBytes < kWorkspaceStatusBytes) return false;  // status words live there
+  switch (d.kernelClass) {
+  case KernelClass::Elementwise: {
+    const int64_t unroll = optionalField(d.unrollField, tiling);
+    return unroll == 0 || unroll == 2;  // the generated loop keeps two vectors per thread in flight
+  }
+  case KernelClass::RowReduce: return true;
+  case KernelClass::Gather: {
+    if (d.groups.size() != 1 || d.groups[0].gatherAxis != 0) return false;
+    if (!d.bulkCopyField.empty()) {
+      auto it = tiling.find(d.bulkCopyField);
+      if (it != tiling.end() && it->second == 1) return false;  // the staged-copy experiment is a prebuilt kernel
+    }
+    const int64_t unroll = optionalField(d.unrollField, tiling);
+    return unroll == 0 || unroll == 1 || unroll == 2;
+  }
+  default: return false;
+  }
+}
+
+namespace {
+
+int clampThreads(int64_t requested) {
+  int threads = requested > 0 ? static_cast<int>(std::min<int64_t>(requested, 512)) : 128;
+  return std::max(32, std::min(512, (threads / 32) * 32));
+}
+
+// Kernel arguments in the reference's order: inputs..., outputs..., workspace, TilingData (all-int64: the
+// descriptor's fields, then the row window and the six plan words).
+struct GeneratedArgs {
+  std::vector<void *> pointers;
+  void *workspace = nullptr;
+  std::vector<int64_t> words;
+  std::vector<void *> params;
+
+  GeneratedArgs(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args) {
+    pointers = args.argPtrs;
+    workspace = args.workspace;
+    for (const TilingField &f : d.tiling) {
+      auto it = tiling.find(f.name);
+      words.push_back(it == tiling.end() ? 0 : it->second);
+    }
+    const size_t hidden = words.size();
+    words.resize(hidden + 8, 0);
+    words[hidden + 0] = args.rowEnd >= 0 ? args.rowBegin : 0;
+    words[hidden + 1] = args.rowEnd >= 0 ? args.rowEnd : -1;
+    planBase_ = hidden + 2;
+  }
+  void setPlan(int index, int64_t value) { words[planBase_ + static_cast<size_t>(index)] = value; }
+  void **finish() {
+    params.clear();
+    for (void *&p : pointers) params.push_back(&p);
+    params.push_back(&workspace);
+    params.push_back(words.data());
+    return params.data();
+  }
+
+private:
+  size_t planBase_ = 0;
+};
+
+} // namespace
+
+Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args,
+                       GeneratedBinding &binding, LaunchInfo &info) {
+  info = LaunchInfo();
+  info.generated = true;
+  const size_t numArgs = static_cast<size_t>(d.numInputs + d.numOutputs);
+  if (args.argPtrs.size() != numArgs || args.argBytes.size() != numArgs)
+    return Status::error("kernel '" + d.kernel + "' takes " + std::to_string(d.numInputs) + " inputs and " +
+                         std::to_string(d.numOutputs) + " outputs");
+  if (!binding.module || !binding.mainFn) return Status::error("kernel '" + d.kernel + "' has no generated code loaded");
+  GeneratedArgs ga(d, tiling, args);
+
+  if (d.kernelClass == KernelClass::Elementwise) {
+    const int threads = clampThreads(optionalField(d.ctaThreadsField, tiling));
+    int64_t tiles = 1;
+    int64_t totalElems = 0;
+    for (const GroupSpec &g : d.groups) {
+      int et = 0;
+      std::vector<int64_t> domain;
+      std::vector<ResolvedView> loads;
+      ResolvedView store;
+      if (Status s = resolveElementwiseGroup(d, g, tiling, args, et, domain, loads, store); !s) return s;
+      int64_t elems = 1;
+      for (int64_t e : domain) elems *= e;
+      // the kernel counts 16-byte vectors (or elements, when something is unaligned) in 32 bits
+      if (elems >= (1ll << 32) - (1 << 20)) return Status::error("[generated:unsupported] more than 2^32 elements in one group");
+      totalElems += elems;
+      const int64_t vecs = (elems + (16 / static_cast<int64_t>(dtypeBytes(d.dtype))) - 1) / (16 / static_cast<int64_t>(dtypeBytes(d.dtype)));
+      tiles = std::max(tiles, (vecs + threads * 2 - 1) / (threads * 2));
+    }
+    if (totalElems == 0) return Status::success();
+    int64_t grid = args.blockDim > 0 ? std::min<int64_t>(args.blockDim, tiles) : tiles;
+    grid = std::max<int64_t>(1, std::min<int64_t>(grid, 0x7fffffff));
+    if (Status s = launchDeviceFunction(binding.mainFn, static_cast<unsigned int>(grid), static_cast<unsigned int>(threads), 0, args.stream, ga.finish()); !s)
+      return s;
+    info.kernelsLaunched = 1;
+    return Status::success();
+  }
+
+  if (d.kernelClass == KernelClass::RowReduce) {
+    if (d.groups.size() != 1) return Status::error("one group per row-reduction kernel");
+    kernels::RowReduceLaunch l;
+    if (Status s = buildRowReduceLaunch(d, d.groups[0], tiling, args, l); !s) return s;
+    if (l.rows == 0) return Status::success();
+    kernels::RowReducePlan plan;
+    if (const int rc = kernels::planRowReduce(l, kernels::deviceSmCount(args.device), plan); rc != 0)
+      return cudaStatus(rc, "row-reduce launch");
+    info.usesStatusBlock = true;
+    if (plan.staged && binding.stagedFn) {
+      ga.setPlan(0, plan.streamStages);
+      ga.setPlan(1, plan.streamChunkBytes);
+      if (Status s = binding.module->reserveDynamicSharedMemory(binding.stagedFn, static_cast<int>(plan.smemBytes)); !s) return s;
+      if (Status s = launchDeviceFunction(binding.stagedFn, static_cast<unsigned int>(plan.grid), static_cast<unsigned int>(plan.threads),
+                                          plan.smemBytes, args.stream, ga.finish()); !s)
+        return s;
+      info.kernelsLaunched = 1;
+      return Status::success();
+    }
+    if (plan.staged) {  // no staged entry in this module: plan again for plain loads
+      l.forcePlainLoads = 1;
+      if (const int rc = kernels::planRowReduce(l, kernels::deviceSmCount(args.device), plan); rc != 0)
+        return cudaStatus(rc, "row-reduce launch");
+    }
+    ga.setPlan(0, plan.vector ? 1 : 0);
+    ga.setPlan(1, plan.slices);
+    ga.setPlan(2, plan.vecPerSlice);
+    ga.setPlan(3, plan.lanes);
+    if (Status s = launchDeviceFunction(binding.mainFn, static_cast<unsigned int>(plan.grid), static_cast<unsigned int>(plan.threads), 0,
+                                        args.stream, ga.finish()); !s)
+      return s;
+    info.kernelsLaunched = 1;
+    if (plan.slices > 1) {
+      if (!binding.finalizeFn) return Status::error("kernel '" + d.kernel + "' has no finalize entry for its column slices");
+      if (Status s = launchDeviceFunction(binding.finalizeFn, static_cast<unsigned int>(plan.finalizeGrid),
+                                          static_cast<unsigned int>(plan.finalizeThreads), 0, args.stream, ga.finish()); !s)
+        return s;
+      info.kernelsLaunched = 2;
+    }
+    return Status::success();
+  }
+
+  if (d.kernelClass == KernelClass::Gather) {
+    if (d.groups.size() != 1) return Status::error("one group per gather kernel");
+    kernels::GatherLaunch l;
+    bool usesStatus = false;
+    if (Status s = buildGatherLaunch(d, d.groups[0], tiling, args, l, usesStatus); !s) return s;
+    info.usesStatusBlock = true;
+    if (l.rows == 0 || l.cols == 0) return Status::success();
+    const int eb = kernels::elemBytes(l.elemType);
+    const int64_t vecPerRow = (l.cols + 16 / eb - 1) / (16 / eb);
+    if (l.rows * l.cols >= (1ll << 32) - (1 << 20)) return Status::error("[generated:unsupported] more than 2^32 elements in one group");
+    const int threads = clampThreads(l.ctaThreads);
+    const int inFlight = l.unroll == 2 ? 2 : 1;
+    ga.setPlan(0, inFlight);
+    const int64_t tileVecs = static_cast<int64_t>(threads) * inFlight;
+    const int64_t tiles = (l.rows * vecPerRow + tileVecs - 1) / tileVecs;
+    int64_t grid = args.blockDim > 0 ? std::min<int64_t>(args.blockDim, tiles) : tiles;
+    grid = std::max<int64_t>(1, std::min<int64_t>(grid, 0x7fffffff));
+    if (Status s = launchDeviceFunction(binding.mainFn, static_cast<unsigned int>(grid), static_cast<unsigned int>(threads), 0, args.stream, ga.finish()); !s)
+      return s;
+    info.kernelsLaunched = 1;
+    return Status::success();
+  }
+  return Status::error("kernel class has no generated code");
 }
 
 } // namespace afir

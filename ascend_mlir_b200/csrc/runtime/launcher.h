@@ -5,16 +5,20 @@
 #pragma once
 
 #include <map>
+#include <memory>
 #include <string>
 #include <vector>
 
 #include "runtime/descriptor.h"
+#include "runtime/device_module.h"
 
 namespace afir {
 
-// Workspace layout: a 256-byte status block (offset 0: u64 count of out-of-range gather indices),
-// then kernel scratch (row-reduction partial sums).
+// Workspace layout: a 256-byte status block (offset 0: u64 count of out-of-range gather indices, offset 8: u32
+// time-out flag of the staged row-reduction kernel), then kernel scratch (row-reduction partial sums).
 constexpr size_t kWorkspaceStatusBytes = 256;
+constexpr size_t kWorkspaceReduceStatusOffset = 8;  // u32: a staged row-reduction kernel gave up waiting for a copy
+constexpr size_t kWorkspaceStatusReadBytes = 16;    // what the executor reads back after a run
 
 struct LaunchArgs {
   std::vector<void *> argPtrs;  // device pointers, inputs first then outputs
@@ -40,6 +44,7 @@ struct LaunchArgs {
 struct LaunchInfo {
   int kernelsLaunched = 0;
   bool usesStatusBlock = false;  // caller should zero it before and check it after
+  bool generated = false;        // the launch ran the group's generated kernel, not a prebuilt one
   std::string plan;              // matmul: the planner's one-line description of what was launched
 };
 
@@ -61,5 +66,27 @@ Status planRowPipeline(const LaunchDescriptor &d, const std::map<std::string, in
 
 Status launchDescriptor(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args,
                         LaunchInfo &info);
+
+// ---- generated kernels -------------------------------------------------------------------------------------------
+// The kernel generated for one descriptor (codegen/kernel_source), loaded on one device.
+struct GeneratedBinding {
+  std::shared_ptr<DeviceModule> module;
+  void *mainFn = nullptr;      // <kernel>
+  void *stagedFn = nullptr;    // <kernel>__staged (row reductions with one streamed view), or null
+  void *finalizeFn = nullptr;  // <kernel>__finalize (row reductions), or null
+};
+
+// True when this launch can run on the descriptor's generated kernel: the features the generated code does not
+// cover (an exchange of partial sums between GPUs, a sharded gather table, a tuning value of the prebuilt
+// kernels' unroll or staged-copy options) stay on the library's kernels.
+bool generatedLaunchApplies(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args);
+// True when the library's prebuilt kernels would run this descriptor's body through the op-by-op interpreter
+// (no straight-line specialisation matches, or the element type is an integer).
+bool prebuiltWouldInterpret(const LaunchDescriptor &d);
+
+// Same contract as launchDescriptor, on the generated kernel: same checks of sizes and bounds, same launch plan,
+// the kernel arguments in the reference's order (inputs..., outputs..., workspace, TilingData).
+Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args,
+                       GeneratedBinding &binding, LaunchInfo &info);
 
 } // namespace afir

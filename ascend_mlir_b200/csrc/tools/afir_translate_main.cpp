@@ -3,18 +3,24 @@
 // `afir-translate -mlir-to-cann [--tiling-space-out f.json]` (tools/afir-translate/afir-translate.cpp:19-40),
 // which emits AscendC C++ instead: here the code is the prebuilt sm_100a kernel library and the translation
 // unit is the descriptor that selects and parameterises a kernel of it.
+// `-mlir-to-cuda-kernel` goes one step further and prints the CUDA C++ source of the group's generated kernel
+// (signature (in..., out..., workspace, TilingData), the text counterpart of the reference's emitted AscendC);
+// `--cubin-out` also compiles it for sm_100a with NVRTC (no GPU needed).  Matmul and bare-transpose groups run on
+// the hand-written kernels of the library and have no generated source: the tool says so and exits 1.
 #include <fstream>
 #include <iostream>
 #include <iterator>
 
+#include "codegen/nvrtc_compile.h"
 #include "front/group_analysis.h"
+#include "runtime/descriptor.h"
 
 using namespace afir;
 using namespace afir::front;
 
 int main(int argc, char **argv) {
-  std::string input, output, spaceOut, function;
-  bool toCuda = false;
+  std::string input, output, spaceOut, function, cubinOut;
+  bool toCuda = false, toKernel = false;
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     auto value = [&](const std::string &name, std::string &dst) -> bool {
@@ -29,12 +35,14 @@ int main(int argc, char **argv) {
       return false;
     };
     if (a == "-mlir-to-cuda" || a == "--mlir-to-cuda") toCuda = true;
+    else if (a == "-mlir-to-cuda-kernel" || a == "--mlir-to-cuda-kernel") toKernel = true;
     else if (a == "-mlir-to-cann" || a == "--mlir-to-cann") {
       std::cerr << "afir-translate: this build targets sm_100a; use -mlir-to-cuda (the AscendC emitter is not part of it)\n";
       return 1;
-    } else if (value("o", output) || value("tiling-space-out", spaceOut) || value("function", function)) {
+    } else if (value("o", output) || value("tiling-space-out", spaceOut) || value("function", function) || value("cubin-out", cubinOut)) {
     } else if (a == "--help" || a == "-h") {
-      std::cout << "USAGE: afir-translate -mlir-to-cuda <input.mlir> [-o <kernel>.cuda.json] [--tiling-space-out <file>] [--function <name>]\n";
+      std::cout << "USAGE: afir-translate -mlir-to-cuda <input.mlir> [-o <kernel>.cuda.json] [--tiling-space-out <file>] [--function <name>]\n"
+                   "       afir-translate -mlir-to-cuda-kernel <input.mlir> [-o <kernel>.cu] [--cubin-out <kernel>.cubin] [--tiling-space-out <file>]\n";
       return 0;
     } else if (a.size() > 1 && a[0] == '-') {
       std::cerr << "afir-translate: Unknown command line argument '" << a << "'\n";
@@ -42,7 +50,7 @@ int main(int argc, char **argv) {
     } else if (input.empty()) input = a;
     else { std::cerr << "afir-translate: more than one input file\n"; return 1; }
   }
-  if (!toCuda) { std::cerr << "afir-translate: no translation requested (use -mlir-to-cuda)\n"; return 1; }
+  if (!toCuda && !toKernel) { std::cerr << "afir-translate: no translation requested (use -mlir-to-cuda or -mlir-to-cuda-kernel)\n"; return 1; }
   std::string text;
   if (input.empty() || input == "-") text.assign(std::istreambuf_iterator<char>(std::cin), std::istreambuf_iterator<char>());
   else {
@@ -61,7 +69,25 @@ int main(int argc, char **argv) {
   }
   GroupAnalysis ga;
   if (Status s = analyzeFunction(module, *func, ga); !s) { std::cerr << (input.empty() ? "<stdin>" : input) << ": error: " << s.message() << "\n"; return 1; }
-  const std::string desc = json::dump(ga.descriptor, 2) + "\n";
+  std::string desc = json::dump(ga.descriptor, 2) + "\n";
+  if (toKernel) {
+    LaunchDescriptor parsed;
+    if (Status s = parseDescriptorJson(ga.descriptor, parsed); !s) { std::cerr << "afir-translate: " << s.message() << "\n"; return 1; }
+    const codegen::GeneratedKernel kernel = codegen::generateKernelSource(parsed);
+    if (!kernel.supported) {
+      std::cerr << "afir-translate: no kernel source is generated for '" << parsed.kernel << "': " << kernel.whyNot << "\n";
+      return 1;
+    }
+    desc = kernel.source;
+    if (!cubinOut.empty()) {
+      codegen::CompiledKernel compiled;
+      if (Status s = codegen::compileToCubin(kernel, compiled); !s) { std::cerr << "afir-translate: " << s.message() << "\n"; return 1; }
+      if (!compiled.log.empty()) std::cerr << compiled.log << "\n";
+      std::ofstream os(cubinOut, std::ios::binary | std::ios::trunc);
+      os.write(reinterpret_cast<const char *>(compiled.cubin.data()), static_cast<std::streamsize>(compiled.cubin.size()));
+      if (!os) { std::cerr << "afir-translate: cannot write " << cubinOut << "\n"; return 1; }
+    }
+  }
   if (output.empty() || output == "-") std::cout << desc;
   else {
     std::ofstream os(output, std::ios::trunc);

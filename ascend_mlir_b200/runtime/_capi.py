@@ -17,7 +17,8 @@ EXPORTS = [
     "afirt_executor_create", "afirt_executor_destroy", "afirt_executor_initialize",
     "afirt_executor_run", "afirt_executor_run_file",
     "afirt_executor_launch_device", "afirt_executor_synchronize", "afirt_executor_workspace_bytes",
-    "afirt_executor_last_launch_count", "afirt_executor_total_launch_count", "afirt_runtime_version",
+    "afirt_executor_last_launch_count", "afirt_executor_total_launch_count", "afirt_executor_last_launch_generated",
+    "afirt_runtime_version",
     "afirt_bcast_add_rowsum_no_alloc",
     "afirt_rowsum_exchange_create", "afirt_rowsum_exchange_connect", "afirt_bcast_add_rowsum_exchange",
     "afirt_rowsum_exchange_status", "afirt_rowsum_exchange_destroy", "afirt_executor_launch_device_exchange",
@@ -66,6 +67,8 @@ def get_lib() -> ctypes.CDLL:
     lib.afirt_executor_workspace_bytes.restype = ctypes.c_int
     lib.afirt_executor_last_launch_count.argtypes = [ctypes.c_void_p]
     lib.afirt_executor_last_launch_count.restype = ctypes.c_int
+    lib.afirt_executor_last_launch_generated.argtypes = [ctypes.c_void_p]
+    lib.afirt_executor_last_launch_generated.restype = ctypes.c_int
     lib.afirt_executor_total_launch_count.argtypes = [ctypes.c_void_p]
     lib.afirt_executor_total_launch_count.restype = ctypes.c_uint64
     lib.afirt_bcast_add_rowsum_no_alloc.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,

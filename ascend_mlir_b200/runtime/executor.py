@@ -154,6 +154,11 @@ class CudaRuntime:
         return int(get_lib().afirt_executor_last_launch_count(ctypes.c_void_p(self._handle)))
 
     @property
+    def last_launch_generated(self) -> bool:
+        """True when the last launch ran the group's generated kernel, False when it ran a prebuilt library kernel."""
+        return bool(get_lib().afirt_executor_last_launch_generated(ctypes.c_void_p(self._handle)))
+
+    @property
     def total_launch_count(self) -> int:
         return int(get_lib().afirt_executor_total_launch_count(ctypes.c_void_p(self._handle)))
 

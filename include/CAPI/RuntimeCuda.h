@@ -44,6 +44,15 @@ int afirt_executor_workspace_bytes(AfirtExecutor executor, const uint8_t *binary
 int afirt_executor_last_launch_count(AfirtExecutor executor);
 uint64_t afirt_executor_total_launch_count(AfirtExecutor executor);
 
+/* 1 when the most recent run / launch on this executor ran the group's GENERATED kernel -- the CUDA source that
+ * afirt_compiler_compile (or, for a bare descriptor, the executor on first use) produced for that fused group and
+ * compiled for sm_100a, loaded with cuModuleLoadData and started with cuLaunchKernel as
+ * <kernel>(inputs..., outputs..., workspace, TilingData), the reference's kernel signature
+ * (lib/Conversion/CanonicalizeCannSignature/CanonicalizeCannSignaturePass.cpp:57-140; registration and launch in
+ * lib/Runtime/Execution/NativeExecutionRunner.cpp:223,476) -- and 0 when it ran a prebuilt kernel of the library
+ * (matmul, bare transposes, and whatever AFIR_CUDA_CODEGEN = never | auto keeps there). */
+int afirt_executor_last_launch_generated(AfirtExecutor executor);
+
 /* No counterpart in the reference (its runtime allocates on every call).
  * out[m] = sum_n (a[m] + b[m,n]) with each row cut into split_cols column slices, for callers that
  * must not allocate GPU memory when they call: serving or real-time loops with a frozen memory

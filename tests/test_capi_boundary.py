@@ -100,11 +100,36 @@ def test_compile_writes_container_and_manifest(tmp_path):
     out = compile_kernel(src, tmp_path / "out", spec.name)
     blob = out.read_bytes()
     assert out.name == f"{spec.name}.bin" and blob[:4] == b"AFCU"
-    assert int.from_bytes(blob[4:8], "little") == 1 and int.from_bytes(blob[8:12], "little") == len(blob) - 12
-    assert blob[12:].decode() == spec.descriptor_json()
+    # version 2: descriptor, then the group's kernel compiled for sm_100a (an ELF cubin) and its CUDA source
+    json_len = int.from_bytes(blob[8:12], "little")
+    assert int.from_bytes(blob[4:8], "little") == 2
+    assert blob[12:12 + json_len].decode() == spec.descriptor_json()
+    off = 12 + json_len
+    cubin_len = int.from_bytes(blob[off:off + 4], "little")
+    cubin = blob[off + 4:off + 4 + cubin_len]
+    off += 4 + cubin_len
+    source_len = int.from_bytes(blob[off:off + 4], "little")
+    source = blob[off + 4:off + 4 + source_len].decode()
+    assert off + 4 + source_len == len(blob)
+    assert cubin[:4] == b"\x7fELF" and cubin_len > 1000
+    # the reference's kernel signature: inputs..., outputs..., workspace, TilingData
+    assert f'extern "C" __global__ void __launch_bounds__(512) {spec.name}(const void *arg0, const void *arg1, void *arg2, ' \
+           "void *workspace, const __grid_constant__ TilingData t)" in source
+    assert "struct TilingData {" in source and "long long SPLIT_N;" in source and "long long dim_arg1_1;" in source
     manifest = dict(line.split("=", 1) for line in (tmp_path / "out" / "manifest.txt").read_text().splitlines())
     assert manifest["kernel_name"] == spec.name and manifest["device_binary_path"] == str(out)
     assert manifest["kernel_kind"] == "vec" and manifest["soc_version"] == "sm_100a"
+    assert manifest["codegen"] == "generated"
+    assert (tmp_path / "out" / f"{spec.name}.cu").read_text() == source == Path(manifest["kernel_source_path"]).read_text()
+    # a matmul group is the library's hand-written kernel: descriptor-only container, and the manifest says why
+    mm = descriptors.matmul_bias_leakyrelu()
+    mm_src = tmp_path / "mm.cuda.json"
+    mm_src.write_text(mm.descriptor_json())
+    mm_out = compile_kernel(mm_src, tmp_path / "out_mm", mm.name)
+    mm_blob = mm_out.read_bytes()
+    assert int.from_bytes(mm_blob[4:8], "little") == 1 and int.from_bytes(mm_blob[8:12], "little") == len(mm_blob) - 12
+    mm_manifest = dict(line.split("=", 1) for line in (tmp_path / "out_mm" / "manifest.txt").read_text().splitlines())
+    assert mm_manifest["codegen"].startswith("library") and mm_manifest["kernel_kind"] == "mix"
     # accepted reference arch names
     compile_kernel(src, tmp_path / "out2", spec.name, arch="dav-c220-vec")
     with pytest.raises(CompilerError, match="not 'wrong_name'"):

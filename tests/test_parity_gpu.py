@@ -92,7 +92,8 @@ def test_reference_split_example_golden(rt, golden_dir):
     M, N = g["input_a"].shape
     out = run(rt, spec, [g["input_a"], g["bias0"], g["bias1"], g["scale0"], g["scale1"]], np.zeros((M, N), np.float16),
               {"M": M, "N": N, "HM": M // 2})
-    assert rt.last_launch_count == 2  # two halves, written in place of the concat
+    # two halves, written in place of the concat: two launches of the library's kernel, or the two groups as one generated kernel
+    assert rt.last_launch_count == (1 if rt.last_launch_generated else 2)
     want = oracle.split_rows_relu_bias_scale_f16(g["input_a"], g["bias0"], g["bias1"], g["scale0"], g["scale1"])
     assert np.array_equal(bits(out), bits(want))
     fails, _, _ = oracle.compare(out.astype(np.float32), g["output"].astype(np.float32), 1e-2, 1e-2)
