@@ -289,6 +289,7 @@ bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t 
   os << "    const long long vpr = vec ? d2 / " << ve << " : d2;\n";
   os << "    prm.vecPerRow = static_cast<unsigned int>(vpr);\n"
      << "    prm.d1 = static_cast<unsigned int>(d1);\n"
+     << "    prm.vprShift = exactLog2(prm.vecPerRow); prm.d1Shift = exactLog2(prm.d1);\n"
      << "    prm.totalVec = static_cast<unsigned int>(d0 * d1 * vpr);\n"
      << "    prm.flat = (d0 == 1 && d1 == 1) ? 1 : 0;\n"
      << "    prm.numViews = " << g.loads.size() << ";\n"
@@ -473,6 +474,7 @@ GeneratedKernel generateGatherRows(const LaunchDescriptor &d) {
       << "    const long long cols = " << cols << ";\n"
       << "    const bool vec = " << vec << ";\n"
       << "    prm.vecPerRow = static_cast<unsigned int>(vec ? cols / " << ve << " : cols);\n"
+      << "    prm.vprShift = exactLog2(prm.vecPerRow);\n"
       << "    prm.totalVec = static_cast<unsigned int>(rows0 * prm.vecPerRow);\n"
       << "    const unsigned int inFlight = t.afir_p0 == 1 ? 1u : 2u;\n"
       << "    const unsigned int tileVecs = blockDim.x * (vec ? inFlight : 2u);\n"

@@ -26,15 +26,44 @@ std::string buildMatmulPlan(const MatmulProblem &problem, const MatmulHints &hin
   if (smCount < 1) smCount = 1;
 
   plan = MatmulPlan();
-  // 256-row tiles halve the operand bytes moved into shared memory per flop; they are the default whenever there
-  // are enough of them to give every SM one.  The CTA pair is never chosen by default (under the board's power cap
-  // it is no faster) and cannot take B as [N, K], whose tiles it would have to split along K-major rows.
-  const int64_t tiles256 = ceilDiv(problem.M, 256) * ceilDiv(problem.N, kTileN);
-  MatmulVariant v = tiles256 >= smCount ? MatmulVariant::Rows256 : MatmulVariant::Rows128;
-  if (hints.variant != 0) v = static_cast<MatmulVariant>(hints.variant);
-  if (v == MatmulVariant::CtaPair && problem.transposeB) v = MatmulVariant::Rows256;
+  // Variant and tile width are chosen together by a small cost model of the persistent kernel: every CTA walks
+  // ceil(tiles / CTAs) tiles, so what counts is the number of WAVES times the cost of a tile, not the tile count.
+  // A 256-column tile that leaves the last wave half empty loses to a narrower one that fills it: 8192 x 8192 x
+  // 8192 M-sharded over 8 GPUs is 4 x 32 = 128 tiles of 256 x 256 on 148 SMs (one wave, 20 SMs idle) but
+  // 4 x 37 = 148 tiles of 256 x 224 (one full wave, each tile 12.5 % shorter).  Cost of a tile in microseconds,
+  // from a fit over K on B200: 12.3 ns per k of a 256 x 256 tile, scaled by the tile's area, plus 4.4 us while
+  // the accumulator drains before the next tile's first MMA (256-row tiles use both accumulators, so the drain is
+  // exposed; 128-row tiles double-buffer them and hide it but move twice the operand bytes per flop, which costs
+  // about 8 % under the board's power cap).  The CTA pair is never chosen by default (it is no faster under the
+  // power cap) and cannot take B as [N, K], whose tiles it would have to split along K-major rows.
+  int64_t ctasWanted = hints.blockDim > 0 ? hints.blockDim : smCount;
+  auto modelMicros = [&](MatmulVariant variant, int tileN) {
+    const int tileM = variant == MatmulVariant::Rows128 ? 128 : 256;
+    const int64_t tiles = ceilDiv(problem.M, tileM) * ceilDiv(problem.N, tileN);
+    const int64_t waves = ceilDiv(tiles, std::max<int64_t>(1, std::min<int64_t>(ctasWanted, tiles)));
+    const double area = (static_cast<double>(tileN) / 256.0) * (static_cast<double>(tileM) / 256.0);
+    const double perTile = variant == MatmulVariant::Rows128 ? 1.0 + 0.0123 * static_cast<double>(problem.K) * area * 1.08
+                                                             : 4.4 + 0.0123 * static_cast<double>(problem.K) * area;
+    return static_cast<double>(waves) * perTile;
+  };
+  MatmulVariant v = MatmulVariant::Rows256;
+  int tileN = kTileN;
+  if (hints.variant == static_cast<int>(MatmulVariant::CtaPair) && !problem.transposeB) {
+    v = MatmulVariant::CtaPair;
+  } else {
+    double best = -1.0;
+    for (MatmulVariant candidate : {MatmulVariant::Rows256, MatmulVariant::Rows128}) {
+      if (hints.variant != 0 && hints.variant != static_cast<int>(MatmulVariant::CtaPair) && hints.variant != static_cast<int>(candidate)) continue;
+      for (int width : {256, 224, 192, 160, 128}) {  // widest first: a tie keeps the wider tile
+        if (hints.tileN > 0 && width != hints.tileN) continue;
+        const double t = modelMicros(candidate, width);
+        if (best < 0.0 || t < best * 0.995) { best = t; v = candidate; tileN = width; }
+      }
+    }
+    if (best < 0.0) return "matmul planner: tile width hint must be 128, 160, 192, 224 or 256";
+  }
   plan.variant = v;
-  plan.tileN = kTileN;
+  plan.tileN = tileN;
   plan.tileK = kTileK;
   switch (v) {
   case MatmulVariant::Rows128:
@@ -59,7 +88,7 @@ std::string buildMatmulPlan(const MatmulProblem &problem, const MatmulHints &hin
   plan.traverse = MatmulTraverse::FirstM;
   plan.band = hints.band > 0 ? hints.band : (v == MatmulVariant::CtaPair ? 8 : 16);
   const int64_t tiles = static_cast<int64_t>(plan.tilesM) * plan.tilesN;
-  int64_t ctas = hints.blockDim > 0 ? hints.blockDim : smCount;
+  int64_t ctas = ctasWanted;
   if (v == MatmulVariant::CtaPair) {
     // two CTAs per tile: an even grid, at most one pair per tile
     ctas = std::min<int64_t>(ctas, 2 * tiles);

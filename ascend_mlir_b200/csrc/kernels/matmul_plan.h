@@ -32,12 +32,14 @@ struct MatmulHints {
   int variant = 0;    // 0 = choose; else a MatmulVariant value (the descriptor's launch.stages field)
   int blockDim = 0;   // 0 = one CTA per SM (capped by the number of tiles)
   int band = 0;       // 0 = default tile-rows per raster band
+  int tileN = 0;      // 0 = choose; else the tile width to use (128, 160, 192, 224 or 256; single-CTA variants)
 };
 
 struct MatmulPlan {
   MatmulVariant variant = MatmulVariant::Rows128;
   MatmulTraverse traverse = MatmulTraverse::FirstM;  // tile order inside a band of `band` tile-rows
-  int tileM = 128, tileN = 256, tileK = 64;           // per CTA (per CTA pair for CtaPair)
+  int tileM = 128, tileN = 256, tileK = 64;           // per CTA (per CTA pair for CtaPair); tileN may be narrower than
+                                                      // 256 when that fills the last wave of persistent CTAs
   int stages = 4;
   int threads = 192;
   int tilesM = 0, tilesN = 0, kBlocks = 0;

@@ -55,6 +55,7 @@ struct GemmParams {
   int biasType, epilogue;
   float alpha;
   unsigned int idesc;
+  int tileN;  // columns per CTA tile: 256, or less (a multiple of 32) when that fills the last wave of CTAs
   int band;  // tile-rows per raster band
   int bKMajor;  // 1: B is given as [N, K] (out = A x B^T, the layout of a torch Linear weight): K-major tiles like A's
 };
@@ -257,13 +258,14 @@ __device__ __forceinline__ bool epilogueTile(const GemmParams &prm, unsigned cha
       auto storeSlice = [&](int c) {
         __syncwarp();
         const int piece = lane & 7;
-        const int ncol = tn * kBlockN + c + piece * (16 / OutPack<OUT>::kBytes);
+        const int colInTile = c + piece * (16 / OutPack<OUT>::kBytes);
+        const int ncol = tn * prm.tileN + colInTile;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int rr = i * 4 + (lane >> 3);
           const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((piece ^ (rr & 7)) << 4));
           const int grow = rowBase + rr;
-          if (grow < prm.M && ncol < prm.N)  // N is a multiple of 8: a 16-byte piece is wholly inside or outside
+          if (grow < prm.M && ncol < prm.N && colInTile < prm.tileN)  // N and tileN are multiples of 8: a 16-byte piece is wholly inside or outside
             *reinterpret_cast<uint4 *>(static_cast<unsigned char *>(prm.out) +
                                        (static_cast<size_t>(grow) * prm.N + ncol) * OutPack<OUT>::kBytes) = val;
         }
@@ -283,7 +285,7 @@ __device__ __forceinline__ bool epilogueTile(const GemmParams &prm, unsigned cha
         // (the area is idle until the store phase); it is fetched before waiting for the accumulator.
         float *biasS = reinterpret_cast<float *>(stg);
         if (prm.epilogue != kEpiNone) {
-          const int n = tn * kBlockN + lane * 8;
+          const int n = tn * prm.tileN + lane * 8;
           float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
           if (n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
           reinterpret_cast<float4 *>(biasS + lane * 8)[0] = make_float4(bv[0], bv[1], bv[2], bv[3]);
@@ -295,6 +297,11 @@ __device__ __forceinline__ bool epilogueTile(const GemmParams &prm, unsigned cha
         uint4 packed[kBlockN / 8];
 #pragma unroll
         for (int cc = 0; cc < kBlockN / 32; ++cc) {
+          if (cc * 32 >= prm.tileN) {  // a narrower tile: these accumulator columns were not written
+#pragma unroll
+            for (int j = 0; j < 4; ++j) packed[cc * 4 + j] = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+          }
           unsigned int r[32];
           tmemLoad32(taddr + cc * 32, r);
           tmemLoadWait();
@@ -317,6 +324,7 @@ __device__ __forceinline__ bool epilogueTile(const GemmParams &prm, unsigned cha
         if (lane == 0) arriveEmpty();
 #pragma unroll
         for (int sl = 0; sl < kBlockN / kColsPerSlice; ++sl) {
+          if (sl * kColsPerSlice >= prm.tileN) continue;
 #pragma unroll
           for (int piece = 0; piece < 8; ++piece)
             *reinterpret_cast<uint4 *>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = packed[sl * 8 + piece];
@@ -327,13 +335,13 @@ __device__ __forceinline__ bool epilogueTile(const GemmParams &prm, unsigned cha
         if (!mbarWait(fullBar, fullParity, abortFlag, 2)) return false;
         tcgen05FenceAfter();
 #pragma unroll 1
-        for (int c = 0; c < kBlockN; c += kColsPerSlice) {
+        for (int c = 0; c < prm.tileN; c += kColsPerSlice) {
           unsigned int r[32];
           tmemLoad32(taddr + c, r);
           tmemLoadWait();
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const int n = tn * kBlockN + c + j * 8;
+            const int n = tn * prm.tileN + c + j * 8;
             float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (prm.epilogue != kEpiNone && n < prm.N) loadBias8(prm.bias, prm.biasType, n, bv);
             float v[8];
@@ -426,11 +434,11 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           unsigned char *stage = smem + static_cast<size_t>(s) * S::kStageBytes;
           tmaLoad2d(smemAddr(stage), &mapA, kb * kBlockK, tm * S::kTileM, full);
           if (prm.bKMajor) {  // one [256 n-rows x 64 k] box, the same bytes as the four N-major boxes
-            tmaLoad2d(smemAddr(stage + S::kAStageBytes), &mapB, kb * kBlockK, tn * kBlockN, full);
+            tmaLoad2d(smemAddr(stage + S::kAStageBytes), &mapB, kb * kBlockK, tn * prm.tileN, full);
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              tmaLoad2d(smemAddr(stage + S::kAStageBytes + j * kBBoxBytes), &mapB, tn * kBlockN + j * 64, kb * kBlockK, full);
+              tmaLoad2d(smemAddr(stage + S::kAStageBytes + j * kBBoxBytes), &mapB, tn * prm.tileN + j * 64, kb * kBlockK, full);
           }
         }
       }
@@ -840,6 +848,7 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   hints.variant = (l.stages >= 1 && l.stages <= 3) ? l.stages : 0;
   hints.blockDim = l.gridBlocks > 0 ? l.gridBlocks : 0;
   if (const char *e = std::getenv("AFIR_GEMM_BAND")) hints.band = std::max(1, std::atoi(e));
+  if (const char *e = std::getenv("AFIR_GEMM_TILE_N")) hints.tileN = std::atoi(e);  // tuning: force the tile width
   MatmulPlan plan;
   const std::string refused = buildMatmulPlan(problem, hints, sms, plan);
   if (!refused.empty()) { fail(errorText, refused.c_str()); return 1; }
@@ -865,7 +874,8 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   p.K = static_cast<int>(l.K);
   const int ctaTileM = pairKernel ? 256 : tileM;
   p.numTilesM = static_cast<int>((l.M + ctaTileM - 1) / ctaTileM);
-  p.numTilesN = static_cast<int>((l.N + kBlockN - 1) / kBlockN);
+  p.tileN = pairKernel ? kBlockN : plan.tileN;
+  p.numTilesN = static_cast<int>((l.N + p.tileN - 1) / p.tileN);
   p.numKBlocks = static_cast<int>((l.K + kBlockK - 1) / kBlockK);
   p.bias = l.bias;
   p.out = l.out;
@@ -874,11 +884,11 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   p.alpha = l.alpha;
   p.band = plan.band;
   const unsigned int fmt = l.inType == kF16 ? 0u : 1u;
-  // instruction descriptor: D=f32, A/B format, A K-major, B N-major, N=256, M=128 (256 across a CTA pair)
+  // instruction descriptor: D=f32, A/B format, A K-major, B N-major, N = the tile's columns, M=128 (256 across a CTA pair)
   const unsigned int instrM = pairKernel ? 256u : 128u;
   p.bKMajor = l.bTransposed ? 1 : 0;
   const unsigned int bMajor = l.bTransposed ? 0u : 1u;  // bit 16: 0 = B K-major, 1 = B N-major
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (bMajor << 16) | ((kBlockN >> 3) << 17) | ((instrM >> 4) << 24);
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (bMajor << 16) | ((static_cast<unsigned int>(p.tileN) >> 3) << 17) | ((instrM >> 4) << 24);
 
   const int grid = static_cast<int>(plan.blockDim);
 

@@ -209,8 +209,10 @@ Status CudaExecutor::validate(const RunRequest &req, CachedKernel *&kernel, std:
   return Status::success();
 }
 
-// AFIR_CUDA_CODEGEN: "auto" (default) runs a group on its generated kernel when the library's prebuilt kernels would
-// interpret its body; "always" whenever a generated kernel exists; "never" keeps every launch on the library.
+// AFIR_CUDA_CODEGEN: "auto" (default) runs elementwise / split / concat and row-reduction groups on the kernel
+// generated for them (measured at or above the library's straight-line kernels on every benchmark shape), and a
+// gather group when the library would otherwise interpret its body op by op; "always" uses generated code
+// whenever a generated kernel exists; "never" keeps every launch on the library's prebuilt kernels.
 static int codegenMode() {
   const char *v = std::getenv("AFIR_CUDA_CODEGEN");
   if (!v || !*v) return 1;
@@ -252,7 +254,8 @@ Status CudaExecutor::dispatch(CachedKernel &kernel, const std::map<std::string, 
   const bool classHasCode = d.kernelClass == KernelClass::Elementwise || d.kernelClass == KernelClass::RowReduce ||
                             d.kernelClass == KernelClass::Gather;
   if (mode != 0 && classHasCode && !(kernel.generatedTried && !kernel.generatedUsable) &&
-      (mode == 2 || prebuiltWouldInterpret(d)) && generatedLaunchApplies(d, tiling, args) && prepareGenerated(kernel)) {
+      (mode == 2 || d.kernelClass != KernelClass::Gather || prebuiltWouldInterpret(d)) && generatedLaunchApplies(d, tiling, args) &&
+      prepareGenerated(kernel)) {
     Status s = launchGenerated(d, tiling, args, kernel.binding, info);
     // sizes the generated loop does not count (beyond 32 bits of elements) go to the library's kernels
     if (s || s.message().rfind("[generated:unsupported]", 0) != 0) return s;

@@ -74,6 +74,18 @@ def test_config5_matmul_add_leakyrelu_full_size(rt):
     # every column's checksum over the sampled rows, accumulated in f64 on both sides
     assert np.allclose(got.astype(np.float64).sum(axis=0), want.astype(np.float64).sum(axis=0), rtol=1e-3, atol=1e-2)
 
+    # EVERY element of the 8192 x 8192 result against an f32 matmul on the CPU (torch: A.B in f32 from the exact bf16
+    # operands, + bias, max(x, 0.01 x), rounded once to bf16), within 1e-2 relative: a tile dropped or misplaced
+    # anywhere in the matrix shows here; the 160 oracle rows above stay the tight, order-exact check
+    import torch
+    a32 = torch.from_numpy(configs.bf16_bits_to_f32(A))
+    b32 = torch.from_numpy(configs.bf16_bits_to_f32(B))
+    x = a32 @ b32 + torch.from_numpy(configs.bf16_bits_to_f32(bias))[None, :]
+    full = torch.maximum(x, x * 0.01).to(torch.bfloat16).to(torch.float32).numpy()
+    assert np.all(np.abs(out - full) <= 1e-2 * np.abs(full) + 1e-3), "full-matrix comparison"
+    assert np.mean(np.abs(out - full) <= 2.0 ** -7 * np.abs(full) + 1e-6) > 0.999
+    del a32, b32, x, full
+
     # linearity of the unfused product at full size: (2A).B == 2 (A.B) bit for bit
     spec = descriptors.matmul_bias_leakyrelu("bf16", "bf16", "bf16", alpha=0.0, epilogue="None")
     shape = {"M": 8192, "N": 8192, "K": 8192}
