@@ -289,7 +289,7 @@ bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t 
   os << "    const long long vpr = vec ? d2 / " << ve << " : d2;\n";
   os << "    prm.vecPerRow = static_cast<unsigned int>(vpr);\n"
      << "    prm.d1 = static_cast<unsigned int>(d1);\n"
-     << "    prm.vprShift = exactLog2(prm.vecPerRow); prm.d1Shift = exactLog2(prm.d1);\n"
+
      << "    prm.totalVec = static_cast<unsigned int>(d0 * d1 * vpr);\n"
      << "    prm.flat = (d0 == 1 && d1 == 1) ? 1 : 0;\n"
      << "    prm.numViews = " << g.loads.size() << ";\n"
@@ -474,14 +474,16 @@ GeneratedKernel generateGatherRows(const LaunchDescriptor &d) {
       << "    const long long cols = " << cols << ";\n"
       << "    const bool vec = " << vec << ";\n"
       << "    prm.vecPerRow = static_cast<unsigned int>(vec ? cols / " << ve << " : cols);\n"
-      << "    prm.vprShift = exactLog2(prm.vecPerRow);\n"
+      << "    // multiply-shift constants of the division by vecPerRow, prepared by the host for both access widths\n"
+      << "    const unsigned long long mg = static_cast<unsigned long long>(vec ? t.afir_p1 : t.afir_p2);\n"
+      << "    prm.divVpr.magic = static_cast<unsigned int>(mg); prm.divVpr.shift = static_cast<unsigned int>(mg >> 32); prm.divVpr.divisor = prm.vecPerRow;\n"
       << "    prm.totalVec = static_cast<unsigned int>(rows0 * prm.vecPerRow);\n"
       << "    const unsigned int inFlight = t.afir_p0 == 1 ? 1u : 2u;\n"
       << "    const unsigned int tileVecs = blockDim.x * (vec ? inFlight : 2u);\n"
       << "    prm.numTiles = (prm.totalVec + tileVecs - 1u) / tileVecs;\n"
-      << "    if (!vec) gatherRowsTiles<" << ti.pack << ", FusedBody0, 2, false, false, true>(prm);\n"
-      << "    else if (inFlight == 1u) gatherRowsTiles<" << ti.pack << ", FusedBody0, 1, true, false, true>(prm);\n"
-      << "    else gatherRowsTiles<" << ti.pack << ", FusedBody0, 2, true, false, true>(prm);\n"
+      << "    if (!vec) gatherRowsTiles<" << ti.pack << ", FusedBody0, 2, false>(prm);\n"
+      << "    else if (inFlight == 1u) gatherRowsTiles<" << ti.pack << ", FusedBody0, 1, true>(prm);\n"
+      << "    else gatherRowsTiles<" << ti.pack << ", FusedBody0, 2, true>(prm);\n"
       << "  }\n}\n";
   out.source = src.str();
   out.entry = d.kernel;

@@ -35,7 +35,8 @@ enum HiddenWord : int { kRowBegin = 0, kRowEnd = 1, kPlan0 = 2 };  // kPlan0 .. 
 //                                         p3 = lanes per row
 //   row_reduce, entry <kernel>__staged:   p0 = ring stages per warp, p1 = bytes per stage
 //   row_reduce, entry <kernel>__finalize: p1 = column slices
-//   gather (rows): p0 = vectors in flight per thread (1 or 2)
+//   gather (rows): p0 = vectors in flight per thread (1 or 2); p1, p2 = multiply-shift constants (magic | shift << 32)
+//                  of the division by the row length in 16-byte vectors (p1) and in elements (p2)
 
 struct GeneratedKernel {
   bool supported = false;

@@ -49,7 +49,16 @@ Status compileArtifact(const CompileRequest &request, KernelArtifact &artifact) 
     bin = src;
     codegenNote = containerCode(src.data(), src.size()).cubinLen ? "generated" : "library";
   } else {
-    const codegen::GeneratedKernel kernel = codegen::generateKernelSource(desc);
+    const std::string srcText(src.begin(), src.end());
+    const std::string embedded = embeddedDescriptorJson(srcText);
+    codegen::GeneratedKernel kernel = codegen::generateKernelSource(desc);
+    // A kernel source file (afir-translate -mlir-to-cann): THAT text is what gets compiled, not a regenerated one;
+    // the descriptor it carries says how to launch it.  A source file of a library group holds no kernel.
+    if (!embedded.empty() && kernel.supported) {
+      if (srcText.find("extern \"C\" __global__") != std::string::npos) kernel.source = srcText;
+      else { kernel.supported = false; kernel.whyNot = "the source file defines no kernel"; }
+    }
+    const std::string descriptorText = embedded.empty() ? srcText : embedded;
     std::vector<uint8_t> cubin;
     std::string source;
     if (!kernel.supported) {
@@ -71,7 +80,7 @@ Status compileArtifact(const CompileRequest &request, KernelArtifact &artifact) 
         if (!os) return Status::error("cannot write " + sourcePath);
       }
     }
-    bin = wrapDescriptorContainer(std::string(src.begin(), src.end()), cubin, source);
+    bin = wrapDescriptorContainer(descriptorText, cubin, source);
   }
   const std::string binPath = request.outputDir + "/" + name + ".bin";
   {

@@ -280,6 +280,12 @@ Status evalGeneric(const Op &g, size_t opIndex, const Env &env, GroupAnalysis &g
       if (Status s = lookup(b.operands[0], v); !s) return s;
       yielded = v.src;
       haveYield = true;
+    } else if (b.name == "arith.constant") {
+      // a scalar constant defined inside the body (the reference's relu example writes its zero there)
+      LocalValue lv;
+      lv.src.kind = Src::Constant;
+      lv.src.value = b.constIsFloat ? b.constFloat : static_cast<double>(b.constInt);
+      local[b.results[0]] = lv;
     } else if (b.name == "linalg.index") {
       LocalValue lv;
       lv.kind = LocalValue::IterIndex;
@@ -326,10 +332,20 @@ Status evalGeneric(const Op &g, size_t opIndex, const Env &env, GroupAnalysis &g
       auto iv = env.values.find(g.operands[idxOperand]);
       if (iv == env.values.end() || iv->second.kind != Value::Tensor || iv->second.ew.views.size() != 1 || !iv->second.ew.ops.empty())
         return err(g, "the index vector must be a function argument");
-      if (!e.views.empty()) return err(g, "a gather cannot be combined with other inputs in the same generic");
       View gv = tv;
       gv.kind = ViewKind::Gathered;
-      e.views.push_back(gv);
+      if (!e.views.empty()) {
+        // the already-fused form (what --fuse-gather-elementwise produces: the gather generic also reads the
+        // broadcast extras of its post-ops): the gathered value must be view 0, so the views registered for the
+        // other inputs move up by one
+        if (e.views[0].kind != ViewKind::Argument || e.hasGather || e.hasMatmul) return err(g, "only one gather per fused group");
+        auto shift = [](Src &src) { if (src.kind == Src::ViewValue) ++src.index; };
+        for (auto &kv : local) shift(kv.second.src);
+        for (BodyOp &op : e.ops) { shift(op.a); shift(op.b); }
+        e.views.insert(e.views.begin(), gv);
+      } else {
+        e.views.push_back(gv);
+      }
       e.hasGather = true;
       e.gatherAxis = axis;
       e.indicesArg = iv->second.ew.views[0].arg;

@@ -38,7 +38,14 @@ public:
       } else if (lookingAt("module")) {
         pos_ += 6;
         skip();
-        if (lookingAt("attributes")) { pos_ += 10; skip(); if (Status st = skipBalanced('{', '}'); !st) return st; skip(); }
+        if (lookingAt("attributes")) {
+          m_.moduleAttrBegin = pos_;
+          pos_ += 10;
+          skip();
+          if (Status st = skipBalanced('{', '}'); !st) return st;
+          m_.moduleAttrEnd = pos_;
+          skip();
+        }
         if (Status st = expect('{'); !st) return st;
         moduleDepth_ += 1;
       } else if (peek() == '}' && moduleDepth_ > 0) {
@@ -46,8 +53,10 @@ public:
         moduleDepth_ -= 1;
       } else if (lookingAt("func.func")) {
         if (Status st = func(); !st) return st;
+      } else if (lookingAt("transform.named_sequence")) {
+        if (Status st = namedSequence(); !st) return st;
       } else {
-        return fail("expected 'module', 'func.func' or an affine_map alias");
+        return fail("expected 'module', 'func.func', 'transform.named_sequence' or an affine_map alias");
       }
       skip();
     }
@@ -265,6 +274,58 @@ private:
     return Status::success();
   }
 
+  // transform.named_sequence @name(%root : !transform.any_op {transform.readonly}) { ... }: the region is kept as
+  // text; the counts and names this backend uses are picked out of it.
+  Status namedSequence() {
+    TransformSchedule sched;
+    sched.srcBegin = pos_;
+    pos_ += std::char_traits<char>::length("transform.named_sequence");
+    skip();
+    if (peek() != '@') return fail("expected the sequence's symbol name");
+    ++pos_;
+    sched.name = ident();
+    if (Status st = skipBalanced('(', ')'); !st) return st;
+    skip();
+    if (s_.compare(pos_, 2, "->") == 0) {  // result types
+      pos_ += 2;
+      if (Status st = skipBalanced('(', ')'); !st) return st;
+      skip();
+    }
+    if (lookingAt("attributes")) { pos_ += 10; if (Status st = skipBalanced('{', '}'); !st) return st; }
+    const size_t bodyBegin = pos_;
+    if (Status st = skipBalanced('{', '}'); !st) return st;
+    sched.srcEnd = pos_;
+    const std::string body = s_.substr(bodyBegin, pos_ - bodyBegin);
+    if (body.find("transform.yield") == std::string::npos) return fail("transform.named_sequence without a transform.yield");
+    auto skipComment = [&](size_t at) {  // true when `at` lies in a // comment
+      const size_t lineStart = body.rfind('\n', at);
+      const size_t from = lineStart == std::string::npos ? 0 : lineStart;
+      const size_t slashes = body.find("//", from);
+      return slashes != std::string::npos && slashes < at;
+    };
+    for (size_t at = body.find("transform.func.add_index_args"); at != std::string::npos; at = body.find("transform.func.add_index_args", at + 1)) {
+      if (skipComment(at)) continue;
+      const size_t comma = body.find(',', at);
+      if (comma == std::string::npos) return fail("transform.func.add_index_args: expected '<function handle>, <count>'");
+      const long n = std::strtol(body.c_str() + comma + 1, nullptr, 10);
+      if (n <= 0) return fail("transform.func.add_index_args: number of arguments to add must be positive");
+      sched.indexArgs += static_cast<int>(n);
+    }
+    for (size_t at = body.find("tile_sizes"); at != std::string::npos; at = body.find("tile_sizes", at + 1)) {
+      if (skipComment(at)) continue;
+      const size_t open = body.find('[', at), close = open == std::string::npos ? open : body.find(']', open);
+      if (close == std::string::npos) return fail("tile_sizes: expected a bracketed list");
+      sched.tileSizes.push_back(body.substr(open, close - open + 1));
+    }
+    for (size_t at = body.find("transform.annotate"); at != std::string::npos; at = body.find("transform.annotate", at + 1)) {
+      if (skipComment(at)) continue;
+      const size_t open = body.find('"', at), close = open == std::string::npos ? open : body.find('"', open + 1);
+      if (close != std::string::npos) sched.annotations.push_back(body.substr(open + 1, close - open - 1));
+    }
+    m_.schedules.push_back(std::move(sched));
+    return Status::success();
+  }
+
   Status func();
   Status op(Op &o, bool inBody);
   Status generic(Op &o);
@@ -310,9 +371,15 @@ std::string printModule(const Module &m) {
       ins.emplace_back(o.attrInsertPos, generic ? "attrs = {" + attrText(o.addedAttrs) + "} " : "{" + attrText(o.addedAttrs) + "} ");
     }
   }
-  std::sort(ins.begin(), ins.end(), [](const auto &a, const auto &b) { return a.first > b.first; });
+  // erasures are spans [begin, end) replaced by nothing; they never overlap an insertion point
+  struct Edit { size_t at; size_t erase; std::string text; };
+  std::vector<Edit> edits;
+  for (const auto &i : ins) edits.push_back({i.first, 0, i.second});
+  for (const auto &e : m.erasures)
+    if (e.second > e.first && e.second <= m.source.size()) edits.push_back({e.first, e.second - e.first, std::string()});
+  std::sort(edits.begin(), edits.end(), [](const Edit &a, const Edit &b) { return a.at > b.at; });
   std::string out = m.source;
-  for (const auto &i : ins) out.insert(i.first, i.second);
+  for (const Edit &e : edits) out.replace(e.at, e.erase, e.text);
   return out;
 }
 

@@ -81,10 +81,27 @@ struct Func {
   int line = 0;
 };
 
+// A transform-dialect schedule found beside the payload functions (transform.named_sequence @__transform_main ...),
+// the form the reference's examples keep their tiling strategy in (examples/*/step2_transform.mlir).  It is not
+// interpreted op by op: what this backend needs from it is how many index arguments it adds to the kernel
+// (transform.func.add_index_args, lib/Dialect/AFIR/TransformOps/AFIRTransformOps.cpp:25-109: the tile parameters
+// of the TilingData struct) and, for the record, the tile sizes and annotations it names.
+struct TransformSchedule {
+  std::string name;                       // @__transform_main
+  int indexArgs = 0;                      // sum over transform.func.add_index_args
+  std::vector<std::string> tileSizes;     // the text of every tile_sizes [...] list, in order
+  std::vector<std::string> annotations;   // names given to transform.annotate ("ascendc.parallel", ...)
+  size_t srcBegin = 0, srcEnd = 0;        // span of the whole op in the source text
+};
+
 struct Module {
   std::string source;
   std::map<std::string, AffineMap> mapAliases;
   std::vector<Func> funcs;
+  std::vector<TransformSchedule> schedules;
+  size_t moduleAttrBegin = 0, moduleAttrEnd = 0;  // span of "attributes {...}" after the module keyword (0 = none)
+  // spans of the source text that printModule leaves out (a pass that removes the schedule fills this)
+  std::vector<std::pair<size_t, size_t>> erasures;
 };
 
 Status parseModule(const std::string &text, Module &out);

@@ -19,7 +19,6 @@ struct EwParams {
   unsigned int totalVec;
   unsigned int numTiles;
   FastDiv divVpr, divD1;
-  int vprShift, d1Shift;  // PLAINDIV kernels: log2 of vecPerRow / d1 when that is a power of two, else -1 (divide)
   int flat;  // inner dim is the whole domain: skip the row arithmetic
   int numViews;
   BodyProgram prog;
@@ -66,9 +65,9 @@ __device__ __forceinline__ void elementwiseTiles(const EwParams &prm) {
       live[u] = g < prm.totalVec;
       unsigned int col = g, i0 = 0, i1 = 0;
       if (!prm.flat) {
-        const unsigned int row = PLAINDIV ? (prm.vprShift >= 0 ? g >> prm.vprShift : g / prm.vecPerRow) : fastDivide(g, prm.divVpr);
+        const unsigned int row = PLAINDIV ? g / prm.vecPerRow : fastDivide(g, prm.divVpr);
         col = g - row * prm.vecPerRow;
-        i0 = PLAINDIV ? (prm.d1Shift >= 0 ? row >> prm.d1Shift : row / prm.d1) : fastDivide(row, prm.divD1);
+        i0 = PLAINDIV ? row / prm.d1 : fastDivide(row, prm.divD1);
         i1 = row - i0 * prm.d1;
       }
       ooff[u] = (static_cast<long long>(i0) * prm.os0 + static_cast<long long>(i1) * prm.os1 +

@@ -44,9 +44,6 @@ __device__ __forceinline__ unsigned int fastDivide(unsigned int n, const FastDiv
   return static_cast<unsigned int>(t >> f.shift);
 }
 
-// log2(n) when n is a power of two, else -1 (generated kernels: a shift instead of a division by a run-time extent).
-__device__ __forceinline__ int exactLog2(unsigned int n) { return (n != 0u && (n & (n - 1u)) == 0u) ? 31 - __clz(n) : -1; }
-
 // ---- streaming 16-byte global access ----------------------------------------------------------
 __device__ __forceinline__ uint4 loadStream16(const void *p) {
   return __ldcs(reinterpret_cast<const uint4 *>(p));

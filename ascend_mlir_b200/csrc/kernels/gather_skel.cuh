@@ -24,7 +24,6 @@ struct GaParams {
   unsigned int totalVec;
   unsigned int numTiles;
   FastDiv divVpr;
-  int vprShift;  // PLAINDIV kernels: log2(vecPerRow) when it is a power of two, else -1 (divide)
   unsigned long long *status;
   BodyProgram prog;
   // SHARDED kernels: the table's rows are split into contiguous shards of rowsPerShard rows, shard s at
@@ -68,7 +67,7 @@ __device__ __forceinline__ void gatherRowsTiles(const GaParams &prm) {
     for (int u = 0; u < UNROLL; ++u) {
       const unsigned int g = g0 + u * blockDim.x;
       live[u] = g < prm.totalVec;
-      row[u] = PLAINDIV ? (prm.vprShift >= 0 ? g >> prm.vprShift : g / prm.vecPerRow) : fastDivide(g, prm.divVpr);
+      row[u] = PLAINDIV ? g / prm.vecPerRow : fastDivide(g, prm.divVpr);
       col[u] = g - row[u] * prm.vecPerRow;
       src[u] = live[u] ? loadIndex(prm.indices, row[u], prm.index64) : 0;
     }

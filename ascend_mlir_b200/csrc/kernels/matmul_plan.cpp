@@ -26,16 +26,19 @@ std::string buildMatmulPlan(const MatmulProblem &problem, const MatmulHints &hin
   if (smCount < 1) smCount = 1;
 
   plan = MatmulPlan();
-  // Variant and tile width are chosen together by a small cost model of the persistent kernel: every CTA walks
-  // ceil(tiles / CTAs) tiles, so what counts is the number of WAVES times the cost of a tile, not the tile count.
-  // A 256-column tile that leaves the last wave half empty loses to a narrower one that fills it: 8192 x 8192 x
-  // 8192 M-sharded over 8 GPUs is 4 x 32 = 128 tiles of 256 x 256 on 148 SMs (one wave, 20 SMs idle) but
-  // 4 x 37 = 148 tiles of 256 x 224 (one full wave, each tile 12.5 % shorter).  Cost of a tile in microseconds,
-  // from a fit over K on B200: 12.3 ns per k of a 256 x 256 tile, scaled by the tile's area, plus 4.4 us while
-  // the accumulator drains before the next tile's first MMA (256-row tiles use both accumulators, so the drain is
-  // exposed; 128-row tiles double-buffer them and hide it but move twice the operand bytes per flop, which costs
-  // about 8 % under the board's power cap).  The CTA pair is never chosen by default (it is no faster under the
-  // power cap) and cannot take B as [N, K], whose tiles it would have to split along K-major rows.
+  // The variant is chosen by a small cost model of the persistent kernel: every CTA walks ceil(tiles / CTAs)
+  // tiles, so what counts is the number of WAVES times the cost of a tile, not the tile count.  Cost of a tile in
+  // microseconds, from a fit over K on B200: 12.3 ns per k of a 256 x 256 tile, scaled by the tile's area, plus
+  // 4.4 us while the accumulator drains before the next tile's first MMA (256-row tiles use both accumulators, so
+  // the drain is exposed; 128-row tiles double-buffer them and hide it but move twice the operand bytes per flop,
+  // which costs about 8 % under the board's power cap).  8192^3 M-sharded over 8 GPUs (M = 1024) therefore takes
+  // 128 tiles of 256 x 256 in ONE wave rather than 256 tiles of 128 x 256 in two.
+  // The tile can also be narrower than 256 columns (a hint only): 4 x 37 = 148 tiles of 256 x 224 would fill the
+  // 148 SMs exactly where 4 x 32 = 128 tiles of 256 x 256 leave 20 idle, but measured on B200 a 224-column tile takes
+  // as long as a 256-column one (100.3 us vs 103.1 us at M = 1024, 396 vs 385 us at M = 4096, 727 vs 767 us at
+  // M = 8192): the B stage is loaded 256 columns wide either way and the tile is not MMA-issue bound, so narrowing
+  // buys nothing and is never chosen by default.  The CTA pair is never chosen by default either (no faster under
+  // the power cap) and cannot take B as [N, K], whose tiles it would have to split along K-major rows.
   int64_t ctasWanted = hints.blockDim > 0 ? hints.blockDim : smCount;
   auto modelMicros = [&](MatmulVariant variant, int tileN) {
     const int tileM = variant == MatmulVariant::Rows128 ? 128 : 256;
@@ -54,8 +57,8 @@ std::string buildMatmulPlan(const MatmulProblem &problem, const MatmulHints &hin
     double best = -1.0;
     for (MatmulVariant candidate : {MatmulVariant::Rows256, MatmulVariant::Rows128}) {
       if (hints.variant != 0 && hints.variant != static_cast<int>(MatmulVariant::CtaPair) && hints.variant != static_cast<int>(candidate)) continue;
-      for (int width : {256, 224, 192, 160, 128}) {  // widest first: a tie keeps the wider tile
-        if (hints.tileN > 0 && width != hints.tileN) continue;
+      for (int width : {256, 224, 192, 160, 128}) {
+        if (width != (hints.tileN > 0 ? hints.tileN : kTileN)) continue;
         const double t = modelMicros(candidate, width);
         if (best < 0.0 || t < best * 0.995) { best = t; v = candidate; tileN = width; }
       }

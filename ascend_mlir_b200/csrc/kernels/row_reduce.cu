@@ -132,17 +132,18 @@ int planRowReduce(const RowReduceLaunch &l, int sms, RowReducePlan &plan) {
     int sWarps = l.ctaThreads >= 64 ? std::min(16, l.ctaThreads / 32) : kStreamWarpsDefault;
     unsigned int sChunk = l.streamChunkBytes > 0 ? static_cast<unsigned int>(std::min(kStreamMaxChunkBytes, (l.streamChunkBytes / 512) * 512))
                                                  : static_cast<unsigned int>(kStreamChunkBytesDefault);
-    if (l.streamChunkBytes <= 0 && rowBytes < 2 * static_cast<int64_t>(sChunk))  // shorter rows: at least two chunks per row
-      sChunk = static_cast<unsigned int>(std::max<int64_t>(512, (rowBytes / 2 / 512) * 512));
+    if (l.streamChunkBytes <= 0 && rowBytes < static_cast<int64_t>(sChunk))  // shorter rows: one copy per row, as large as a copy can be
+      sChunk = static_cast<unsigned int>(((rowBytes + 511) / 512) * 512);
     if (sChunk < 512) sChunk = 512;
     // Ring depth: what keeps HBM busy is the bytes an SM has in flight, warps x stages x chunk.  Two stages of
-    // 8 KB per warp are 128 KB per SM; when short rows shrink the chunk the ring deepens to keep that figure
-    // (a ring may span several rows: the producer's cursor runs ahead of the consumer's across row ends).
+    // 8 KB per warp are 128 KB per SM; when short rows shrink the chunk (a copy never spans two rows) the ring
+    // deepens to keep that figure: the producer's cursor runs ahead of the consumer's across row ends, so a
+    // warp has several whole rows in flight.
     int sStages = l.streamStages > 0 ? std::min(32, l.streamStages) : kStreamStagesDefault;
     if (l.streamStages <= 0)
       while (sStages < 16 && static_cast<size_t>(sWarps) * sStages * sChunk < kStreamBytesInFlight) ++sStages;
     while (static_cast<size_t>(sWarps) * sStages * sChunk > 200 * 1024 && sStages > 2) --sStages;
-    if (numStreamed == 1 && rowBytes >= 2 * static_cast<int64_t>(sChunk) && rowBytes < (1ll << 31) &&
+    if (numStreamed == 1 && rowBytes >= kStreamMinRowBytes && rowBytes < (1ll << 31) &&
         l.rows >= static_cast<int64_t>(sms) * sWarps) {
       plan.staged = true;
       plan.streamedView = streamed;

@@ -263,6 +263,7 @@ constexpr int kStreamStagesDefault = 2;
 constexpr int kStreamWarpsDefault = 8;
 constexpr int kStreamMaxChunkBytes = 16384;
 constexpr unsigned int kStreamBytesInFlight = 128 * 1024;  // per SM: warps x stages x chunk aims at this
+constexpr int kStreamMinRowBytes = 1024;                   // shorter rows go to the team-per-row kernel
 constexpr unsigned long long kStreamWaitLimitNs = 2000000000ull;
 
 struct RrStreamParams {

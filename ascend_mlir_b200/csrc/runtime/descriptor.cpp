@@ -1,5 +1,7 @@
 #include "runtime/descriptor.h"
 
+#include <algorithm>
+
 #include <cstring>
 
 namespace afir {
@@ -319,6 +321,28 @@ Status parseDescriptorJson(const json::Value &root, LaunchDescriptor &out) {
   return Status::success();
 }
 
+std::string embeddedDescriptorJson(const std::string &text) {
+  const size_t begin = text.find(kEmbeddedDescriptorBegin);
+  if (begin == std::string::npos) return std::string();
+  const size_t end = text.find(kEmbeddedDescriptorEnd, begin);
+  if (end == std::string::npos) return std::string();
+  std::string json;
+  size_t pos = text.find('\n', begin);
+  while (pos != std::string::npos && pos + 1 < end) {
+    const size_t lineEnd = text.find('\n', pos + 1);
+    std::string line = text.substr(pos + 1, (lineEnd == std::string::npos ? end : std::min(lineEnd, end)) - pos - 1);
+    if (line.compare(0, 3, "// ") == 0) json += line.substr(3);
+    else if (line.compare(0, 2, "//") == 0) json += line.substr(2);
+    pos = lineEnd;
+    if (lineEnd == std::string::npos || lineEnd >= end) break;
+  }
+  return json;
+}
+
+std::string embedDescriptorComment(const std::string &compactJson) {
+  return std::string(kEmbeddedDescriptorBegin) + "\n// " + compactJson + "\n" + kEmbeddedDescriptorEnd + "\n";
+}
+
 Status parseDescriptorBinary(const uint8_t *data, size_t len, LaunchDescriptor &out) {
   if (!data || len == 0) return Status::error("binary data is required");
   std::string text;
@@ -332,8 +356,13 @@ Status parseDescriptorBinary(const uint8_t *data, size_t len, LaunchDescriptor &
   } else {
     size_t i = 0;
     while (i < len && (data[i] == ' ' || data[i] == '\n' || data[i] == '\t' || data[i] == '\r')) ++i;
-    if (i == len || data[i] != '{') return Status::error("kernel binary is neither an AFCU container nor a launch descriptor");
-    text.assign(reinterpret_cast<const char *>(data), len);
+    if (i < len && data[i] == '{') {
+      text.assign(reinterpret_cast<const char *>(data), len);
+    } else {
+      // a kernel source file with its descriptor in the leading comment block
+      text = embeddedDescriptorJson(std::string(reinterpret_cast<const char *>(data), len));
+      if (text.empty()) return Status::error("kernel binary is neither an AFCU container, a launch descriptor nor a kernel source with one embedded");
+    }
   }
   json::Value root;
   std::string err;

@@ -85,6 +85,14 @@ constexpr uint32_t kContainerMagic = 0x55434641u;  // "AFCU" little-endian
 constexpr uint32_t kContainerVersion = 1;
 constexpr uint32_t kContainerVersionWithCode = 2;
 
+// A kernel SOURCE file (what `afir-translate -mlir-to-cann` writes, the counterpart of the reference's
+// step8_kernel.cpp) carries its launch descriptor in a leading comment block between these two marker lines, one
+// line of JSON behind "// ".  embeddedDescriptorJson returns that JSON, or "" when the text holds no such block.
+constexpr const char *kEmbeddedDescriptorBegin = "// afir-cuda-launch-descriptor-begin";
+constexpr const char *kEmbeddedDescriptorEnd = "// afir-cuda-launch-descriptor-end";
+std::string embeddedDescriptorJson(const std::string &sourceText);
+std::string embedDescriptorComment(const std::string &compactJson);
+
 Status parseDescriptorJson(const json::Value &root, LaunchDescriptor &out);
 // Accepts the binary container or bare JSON text.
 Status parseDescriptorBinary(const uint8_t *data, size_t len, LaunchDescriptor &out);

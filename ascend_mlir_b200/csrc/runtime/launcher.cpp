@@ -717,6 +717,15 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
     const int threads = clampThreads(l.ctaThreads);
     const int inFlight = l.unroll == 2 ? 2 : 1;
     ga.setPlan(0, inFlight);
+    auto divisionWord = [](int64_t divisor) {  // kernels::makeFastDiv, packed as magic | shift << 32
+      const unsigned int d = static_cast<unsigned int>(std::max<int64_t>(1, divisor));
+      unsigned int shift = 0;
+      while ((1ull << shift) < d) ++shift;
+      const unsigned int magic = static_cast<unsigned int>(((1ull << 32) * ((1ull << shift) - d)) / d + 1);
+      return static_cast<int64_t>(static_cast<uint64_t>(magic) | (static_cast<uint64_t>(shift) << 32));
+    };
+    ga.setPlan(1, divisionWord(l.cols / (16 / eb)));
+    ga.setPlan(2, divisionWord(l.cols));
     const int64_t tileVecs = static_cast<int64_t>(threads) * inFlight;
     const int64_t tiles = (l.rows * vecPerRow + tileVecs - 1) / tileVecs;
     int64_t grid = args.blockDim > 0 ? std::min<int64_t>(args.blockDim, tiles) : tiles;

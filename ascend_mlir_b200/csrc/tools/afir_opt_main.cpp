@@ -10,6 +10,25 @@
 //   --convert-afir-to-cuda              afir.cuda_kernel_class / afir.cuda_launch (descriptor JSON) on the function
 // Structural passes of upstream MLIR that do not change what the group computes (--canonicalize, --cse,
 // --afir-canonicalize, --afir-shape-inference, --linalg-fold-unit-extent-dims) verify and pass the module through.
+//
+// The reference's device-lowering stages are accepted under their own names, so that its example scripts and its
+// torch pipeline (examples/*/run.sh, python/torch/framework/pipeline.py:_run_mlir_pipeline) drive this tool with
+// only the tool path changed:
+//   --transform-interpreter             reads the transform.named_sequence beside the function: the number of index
+//                                       arguments it adds (transform.func.add_index_args = the tile parameters) and
+//                                       its tile sizes / annotations are recorded on the function (afir.tile_index_args,
+//                                       afir.tile_sizes, afir.schedule_annotations); no loops are materialised -- the
+//                                       sm_100a kernel is generated from the fused group as a whole and its launch
+//                                       parameters are tuned through the tiling space, not through scf.for nests
+//   --one-shot-bufferize[=opts], --ascendc-buffer-placement, --linalg-to-ascendc, --ascendc-parallelize,
+//   --ascendc-prepare-for-emit          bufferisation, on-chip buffer placement, AscendC op selection, multi-core
+//                                       dispatch and emit preparation have no counterpart on this target (global
+//                                       memory is addressed directly, the grid is the dispatch): each verifies that
+//                                       every function is still one fused group and records itself in afir.stages
+//   --canonicalize-cann-signature       removes the transform sequence and records cann.num_inputs / cann.num_outputs
+//                                       (the kernel-argument order inputs..., outputs..., workspace, tiling of
+//                                       lib/Conversion/CanonicalizeCannSignature/CanonicalizeCannSignaturePass.cpp:57-140
+//                                       is what the generated kernel takes)
 // Any other flag, and any op outside the subset, is an error.
 #include <fstream>
 #include <iostream>
@@ -37,6 +56,10 @@ int main(int argc, char **argv) {
                                                 "linalg-fuse-elementwise-ops", "fuse-gather-elementwise", "convert-afir-to-cuda"};
   const std::set<std::string> passThrough = {"canonicalize", "cse", "afir-canonicalize", "afir-shape-inference",
                                              "linalg-fold-unit-extent-dims", "allow-unregistered-dialect"};
+  // the reference's lowering stages (see the header comment)
+  const std::set<std::string> loweringStages = {"one-shot-bufferize", "ascendc-buffer-placement", "linalg-to-ascendc",
+                                                "ascendc-parallelize", "ascendc-prepare-for-emit"};
+  const std::set<std::string> scheduleStages = {"transform-interpreter", "canonicalize-cann-signature"};
   std::vector<std::string> passes;
   std::string input, output;
   for (int i = 1; i < argc; ++i) {
@@ -47,11 +70,15 @@ int main(int argc, char **argv) {
     } else if (a == "--help" || a == "-h") {
       std::cout << "USAGE: afir-opt [passes] <input.mlir> [-o <output.mlir>]\n";
       for (const auto &p : analysisPasses) std::cout << "  --" << p << "\n";
+      for (const auto &p : scheduleStages) std::cout << "  --" << p << "\n";
+      for (const auto &p : loweringStages) std::cout << "  --" << p << "\n";
       for (const auto &p : passThrough) std::cout << "  --" << p << "\n";
       return 0;
     } else if (a.size() > 1 && a[0] == '-' && a != "-") {
-      const std::string name = a.substr(a[1] == '-' ? 2 : 1);
-      if (!analysisPasses.count(name) && !passThrough.count(name)) {
+      std::string name = a.substr(a[1] == '-' ? 2 : 1);
+      const size_t eq = name.find('=');  // --one-shot-bufferize=bufferize-function-boundaries=true ...: options are not needed here
+      if (eq != std::string::npos) name = name.substr(0, eq);
+      if (!analysisPasses.count(name) && !passThrough.count(name) && !loweringStages.count(name) && !scheduleStages.count(name)) {
         std::cerr << "afir-opt: Unknown command line argument '" << a << "'\n";
         return 1;
       }
@@ -74,7 +101,12 @@ int main(int argc, char **argv) {
   if (Status s = parseModule(text, module); !s) { std::cerr << (input.empty() ? "<stdin>" : input) << ": error: " << s.message() << "\n"; return 1; }
 
   bool needAnalysis = false;
-  for (const auto &p : passes) needAnalysis = needAnalysis || analysisPasses.count(p);
+  for (const auto &p : passes) needAnalysis = needAnalysis || analysisPasses.count(p) || loweringStages.count(p) || scheduleStages.count(p);
+  for (const auto &p : passes)
+    if (p == "transform-interpreter" && module.schedules.empty()) {
+      std::cerr << (input.empty() ? "<stdin>" : input) << ": error: --transform-interpreter: the module holds no transform.named_sequence\n";
+      return 1;
+    }
   if (needAnalysis) {
     for (Func &f : module.funcs) {
       GroupAnalysis ga;
@@ -91,6 +123,26 @@ int main(int argc, char **argv) {
           bool have = false;
           for (const auto &kv : f.addedAttrs) have = have || kv.first == "afir.fused_group";
           if (!have) f.addedAttrs.push_back({"afir.fused_group", "\"" + ga.kernelClass + "\""});
+        } else if (p == "transform-interpreter") {
+          int indexArgs = 0;
+          std::string sizes, notes;
+          for (const TransformSchedule &sched : module.schedules) {
+            indexArgs += sched.indexArgs;
+            for (const std::string &t : sched.tileSizes) sizes += (sizes.empty() ? "" : ", ") + t;
+            for (const std::string &n : sched.annotations)
+              if (notes.find("\"" + n + "\"") == std::string::npos) notes += (notes.empty() ? "\"" : ", \"") + n + "\"";
+          }
+          f.addedAttrs.push_back({"afir.tile_index_args", std::to_string(indexArgs) + " : i64"});
+          f.addedAttrs.push_back({"afir.tile_sizes", escapeForAttr("[" + sizes + "]")});
+          f.addedAttrs.push_back({"afir.schedule_annotations", "[" + notes + "]"});
+        } else if (loweringStages.count(p)) {
+          // one attribute per stage: the printer never rewrites an attribute an earlier run left on the function
+          std::string key = "afir.stage.";
+          for (char c : p) key.push_back(c == '-' ? '_' : c);
+          f.addedAttrs.push_back({key, "true"});
+        } else if (p == "canonicalize-cann-signature") {
+          f.addedAttrs.push_back({"cann.num_inputs", std::to_string(ga.descriptor.getInt("num_inputs", 0)) + " : i64"});
+          f.addedAttrs.push_back({"cann.num_outputs", std::to_string(ga.descriptor.getInt("num_outputs", 0)) + " : i64"});
         } else if (p == "convert-afir-to-cuda") {
           f.addedAttrs.push_back({"afir.cuda_kernel_class", "\"" + ga.kernelClass + "\""});
           f.addedAttrs.push_back({"afir.cuda_launch", escapeForAttr(json::dump(ga.descriptor))});
@@ -98,6 +150,14 @@ int main(int argc, char **argv) {
       }
     }
   }
+  for (const auto &p : passes)
+    if (p == "canonicalize-cann-signature") {
+      // the schedule has done its job: drop it, and the module attribute that announced it
+      for (const TransformSchedule &sched : module.schedules) module.erasures.push_back({sched.srcBegin, sched.srcEnd});
+      if (module.moduleAttrEnd > module.moduleAttrBegin &&
+          module.source.substr(module.moduleAttrBegin, module.moduleAttrEnd - module.moduleAttrBegin).find("transform.with_named_sequence") != std::string::npos)
+        module.erasures.push_back({module.moduleAttrBegin, module.moduleAttrEnd});
+    }
   const std::string printed = printModule(module);
   if (output.empty() || output == "-") std::cout << printed;
   else {

@@ -20,7 +20,7 @@ using namespace afir::front;
 
 int main(int argc, char **argv) {
   std::string input, output, spaceOut, function, cubinOut;
-  bool toCuda = false, toKernel = false;
+  bool toCuda = false, toKernel = false, selfContained = false;
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     auto value = [&](const std::string &name, std::string &dst) -> bool {
@@ -37,8 +37,11 @@ int main(int argc, char **argv) {
     if (a == "-mlir-to-cuda" || a == "--mlir-to-cuda") toCuda = true;
     else if (a == "-mlir-to-cuda-kernel" || a == "--mlir-to-cuda-kernel") toKernel = true;
     else if (a == "-mlir-to-cann" || a == "--mlir-to-cann") {
-      std::cerr << "afir-translate: this build targets sm_100a; use -mlir-to-cuda (the AscendC emitter is not part of it)\n";
-      return 1;
+      // the reference's flag, for scripts written against it: the kernel source of THIS target (CUDA C++ where the
+      // reference writes AscendC C++), with the launch descriptor in a leading comment block so that the file alone is
+      // what afirt_compiler_compile needs
+      toKernel = true;
+      selfContained = true;
     } else if (value("o", output) || value("tiling-space-out", spaceOut) || value("function", function) || value("cubin-out", cubinOut)) {
     } else if (a == "--help" || a == "-h") {
       std::cout << "USAGE: afir-translate -mlir-to-cuda <input.mlir> [-o <kernel>.cuda.json] [--tiling-space-out <file>] [--function <name>]\n"
@@ -74,12 +77,18 @@ int main(int argc, char **argv) {
     LaunchDescriptor parsed;
     if (Status s = parseDescriptorJson(ga.descriptor, parsed); !s) { std::cerr << "afir-translate: " << s.message() << "\n"; return 1; }
     const codegen::GeneratedKernel kernel = codegen::generateKernelSource(parsed);
-    if (!kernel.supported) {
+    if (!kernel.supported && !selfContained) {
       std::cerr << "afir-translate: no kernel source is generated for '" << parsed.kernel << "': " << kernel.whyNot << "\n";
       return 1;
     }
     desc = kernel.source;
-    if (!cubinOut.empty()) {
+    if (selfContained) {
+      const std::string header = embedDescriptorComment(json::dump(ga.descriptor, -1));
+      desc = kernel.supported ? header + kernel.source
+                              : header + "// Kernel '" + parsed.kernel + "' is a kernel of the runtime library (" + kernel.whyNot +
+                                    "): this file holds its launch descriptor only.\n";
+    }
+    if (!cubinOut.empty() && kernel.supported) {
       codegen::CompiledKernel compiled;
       if (Status s = codegen::compileToCubin(kernel, compiled); !s) { std::cerr << "afir-translate: " << s.message() << "\n"; return 1; }
       if (!compiled.log.empty()) std::cerr << compiled.log << "\n";

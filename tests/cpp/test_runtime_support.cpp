@@ -335,22 +335,25 @@ static void testMatmulPlanner() {
   small.M = 1024; small.N = 2048; small.K = 320;
   EXPECT(buildMatmulPlan(small, MatmulHints(), 148, plan).empty(), "small plan builds");
   EXPECT(plan.variant == MatmulVariant::Rows128 && plan.stages == 4 && plan.epilogueOverlapsMainloop, "too few 256-row tiles: 128-row tiles, double-buffered accumulators");
-  EXPECT(plan.tileN == 128 && plan.tilesM == 8 && plan.tilesN == 16 && plan.kBlocks == 5 && plan.blockDim == 128,
-         "narrow tiles put a small problem on more SMs; the grid is capped by the number of tiles");
+  EXPECT(plan.tileN == 256 && plan.tilesM == 8 && plan.tilesN == 8 && plan.kBlocks == 5 && plan.blockDim == 64, "grid capped by the number of tiles");
 
-  // Wave quantisation: the 8192^3 problem M-sharded over 2, 4 and 8 GPUs.  256-column tiles would leave the last
-  // wave of 148 persistent CTAs half empty (512, 256 and 128 tiles); 224-column tiles fill it exactly.
+  // The 8192^3 problem M-sharded over 2, 4 and 8 GPUs: waves x tile cost keeps the 256-row tiles (at M = 1024, 128
+  // tiles in one wave beat 256 tiles of 128 rows in two).
   for (int gpus : {2, 4, 8}) {
     MatmulProblem shard = big;
     shard.M = 8192 / gpus;
     EXPECT(buildMatmulPlan(shard, MatmulHints(), 148, plan).empty(), "shard plan builds");
-    EXPECT(plan.variant == MatmulVariant::Rows256 && plan.tileN == 224 && plan.tilesN == 37 && plan.tilesM == 32 / gpus,
-           "M = 8192 / " + std::to_string(gpus) + ": 256 x 224 tiles, " + describeMatmulPlan(plan));
-    EXPECT((plan.tilesM * plan.tilesN) % 148 == 0 && plan.blockDim == 148, "whole waves of 148 CTAs");
+    EXPECT(plan.variant == MatmulVariant::Rows256 && plan.tileN == 256 && plan.tilesN == 32 && plan.tilesM == 32 / gpus,
+           "M = 8192 / " + std::to_string(gpus) + ": 256 x 256 tiles, " + describeMatmulPlan(plan));
   }
+  // a narrower tile is a hint: 148 tiles of 256 x 224 fill 148 SMs in whole waves
   MatmulHints width;
+  width.tileN = 224;
+  MatmulProblem eighth = big;
+  eighth.M = 1024;
+  EXPECT(buildMatmulPlan(eighth, width, 148, plan).empty() && plan.tileN == 224 && plan.tilesN == 37 && plan.blockDim == 148, "a tile-width hint is honoured");
   width.tileN = 192;
-  EXPECT(buildMatmulPlan(big, width, 148, plan).empty() && plan.tileN == 192 && plan.tilesN == 43, "a tile-width hint is honoured");
+  EXPECT(buildMatmulPlan(big, width, 148, plan).empty() && plan.tileN == 192 && plan.tilesN == 43, "another width");
   width.tileN = 100;
   EXPECT(!buildMatmulPlan(big, width, 148, plan).empty(), "a tile width the kernel does not have is refused");
 

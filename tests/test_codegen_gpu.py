@@ -115,9 +115,10 @@ def test_integer_constants_beyond_2_pow_24_are_exact(rt, monkeypatch):
 
 
 @pytest.mark.parametrize("M,N,split,launches", [(5, 40000, 4, 2), (300, 1000, 0, 1), (1500, 8192, 0, 1), (7, 33, 0, 1), (2000, 4096, 0, 1)])
-def test_row_reduction_plans_on_generated_code(rt, M, N, split, launches):
+def test_row_reduction_plans_on_generated_code(rt, monkeypatch, M, N, split, launches):
     """Teams with plain loads, column slices through the workspace + finalize, and the bulk-copy staged loop
     (1500 x 8192 f32 and 2000 x 4096: at least 148 x 8 rows of 16 KB or more), each with a body the library has no kernel for."""
+    monkeypatch.setenv("AFIR_CUDA_NO_PIPELINE", "1")  # one launch for the whole problem, not one per row chunk of the host path
     spec = descriptors.bcast_add_rowsum("f32")
     d = variant(spec, "sub_mul_rowsum", [descriptors.op("subf", "v1", "v0"), descriptors.op("mulf", "%0", "v1")])
     rng = np.random.default_rng(83)

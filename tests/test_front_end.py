@@ -203,10 +203,10 @@ def test_inputs_outside_the_subset_fail_loudly(text, needle):
 
 
 def test_unknown_flags_are_errors():
-    r = opt("--ascendc-buffer-placement", EXAMPLES / "elementwise_chain.mlir")
+    r = opt("--ascendc-vectorize-everything", EXAMPLES / "elementwise_chain.mlir")
     assert r.returncode == 1 and "Unknown command line argument" in r.stderr
-    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cann", str(EXAMPLES / "elementwise_chain.mlir")], capture_output=True, text=True)
-    assert r.returncode == 1 and "use -mlir-to-cuda" in r.stderr
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-llvmir", str(EXAMPLES / "elementwise_chain.mlir")], capture_output=True, text=True)
+    assert r.returncode == 1 and "Unknown command line argument" in r.stderr
 
 
 def test_afir_broadcast_follows_numpy_trailing_alignment():
@@ -324,3 +324,107 @@ module {
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     assert "abi_matmul_trans_b = true" in converted.read_text() and "abi_matmul_trans_a = false" in converted.read_text()
+
+
+# ---- the reference's stage names and schedule files --------------------------------------------------------------------
+REFERENCE_STAGES = [
+    [],                                      # stage 0: parse only
+    ["--linalg-fuse-elementwise-ops"],
+    ["--transform-interpreter", "--canonicalize", "--cse"],
+    ["--one-shot-bufferize=bufferize-function-boundaries=true allow-return-allocs-from-loops=true "
+     "function-boundary-type-conversion=identity-layout-map", "--cse"],
+    ["--ascendc-buffer-placement"],
+    ["--linalg-to-ascendc", "--canonicalize", "--cse"],
+    ["--ascendc-parallelize", "--canonicalize", "--cse"],
+    ["--ascendc-prepare-for-emit", "--canonicalize", "--cse"],
+    ["--canonicalize-cann-signature"],
+]
+
+
+def run_reference_stages(src, work):
+    """The command lines of the reference's examples/*/run.sh and python/torch/framework/pipeline.py:_run_mlir_pipeline,
+    stage by stage, each reading the previous stage's file; returns the last file."""
+    for i, flags in enumerate(REFERENCE_STAGES):
+        dst = work / f"stage{i}.mlir"
+        r = opt(*flags, src, "-o", dst)
+        assert r.returncode == 0, (flags, r.stderr)
+        src = dst
+    return src
+
+
+def test_reference_stage_names_drive_the_tools_end_to_end(tmp_path):
+    from ascend_mlir_b200.runtime.compiler import compile_kernel
+    last = run_reference_stages(EXAMPLES / "broadcast_add_reduce_scheduled.mlir", tmp_path)
+    text = last.read_text()
+    # the schedule was read (three index arguments, two tilings, two annotations) and then removed with its module attribute
+    assert "afir.tile_index_args = 3 : i64" in text
+    assert 'afir.tile_sizes = "[[%rows_per_group, 0], [%rows_per_step, %cols_per_step]]"' in text
+    assert 'afir.schedule_annotations = ["ascendc.parallel", "ascendc.unit"]' in text
+    assert "transform.named_sequence" not in text and "transform.with_named_sequence" not in text
+    assert "transform.named_sequence" in (tmp_path / "stage7.mlir").read_text()  # kept until the signature stage
+    assert "cann.num_inputs = 2 : i64" in text and "cann.num_outputs = 1 : i64" in text
+    for stage in ("one_shot_bufferize", "ascendc_buffer_placement", "linalg_to_ascendc", "ascendc_parallelize", "ascendc_prepare_for_emit"):
+        assert f"afir.stage.{stage} = true" in text
+    # stage 8 under the reference's flag name: a kernel SOURCE file that carries its launch descriptor
+    kernel_cpp, space = tmp_path / "step8_kernel.cpp", tmp_path / "step8_kernel.tiling_space.json"
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cann", str(last), "-o", str(kernel_cpp), "--tiling-space-out", str(space)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    source = kernel_cpp.read_text()
+    assert source.startswith("// afir-cuda-launch-descriptor-begin\n// {")
+    assert 'extern "C" __global__ void __launch_bounds__(512) broadcast_add_reduce_scheduled(const void *arg0, const void *arg1, void *arg2, ' in source
+    assert json.loads(space.read_text())["kernel"] == "broadcast_add_reduce_scheduled"
+    # ... which is what the compile step takes: that very text is compiled for sm_100a
+    blob = compile_kernel(kernel_cpp, tmp_path / "artifact", "broadcast_add_reduce_scheduled").read_bytes()
+    assert blob[:4] == b"AFCU" and int.from_bytes(blob[4:8], "little") == 2
+    json_len = int.from_bytes(blob[8:12], "little")
+    assert json.loads(blob[12:12 + json_len])["kernel_class"] == "row_reduce"
+    off = 12 + json_len
+    cubin_len = int.from_bytes(blob[off:off + 4], "little")
+    assert blob[off + 4:off + 8] == b"\x7fELF"
+    off += 4 + cubin_len
+    source_len = int.from_bytes(blob[off:off + 4], "little")
+    assert blob[off + 4:off + 4 + source_len].decode() == source
+
+
+def test_transform_interpreter_needs_a_schedule_and_checks_it(tmp_path):
+    r = opt("--transform-interpreter", EXAMPLES / "broadcast_add_reduce.mlir")
+    assert r.returncode == 1 and "holds no transform.named_sequence" in r.stderr
+    bad = (EXAMPLES / "broadcast_add_reduce_scheduled.mlir").read_text().replace("add_index_args %func, 3", "add_index_args %func, 0")
+    r = opt("--transform-interpreter", "-", stdin=bad)
+    assert r.returncode == 1 and "number of arguments to add must be positive" in r.stderr
+    r = opt("--ascendc-no-such-stage", EXAMPLES / "broadcast_add_reduce.mlir")
+    assert r.returncode == 1 and "Unknown command line argument" in r.stderr
+
+
+def test_library_group_source_file_holds_its_descriptor_only(tmp_path):
+    from ascend_mlir_b200.runtime.compiler import compile_kernel
+    out = tmp_path / "step8_kernel.cpp"
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cann", str(EXAMPLES / "matmul_add_leakyrelu.mlir"), "-o", str(out)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    text = out.read_text()
+    assert "is a kernel of the runtime library" in text and 'extern "C"' not in text
+    blob = compile_kernel(out, tmp_path / "artifact", "matmul_add_leakyrelu").read_bytes()
+    assert int.from_bytes(blob[4:8], "little") == 1
+    assert json.loads(blob[12:])["kernel_class"] == "matmul"
+
+
+@pytest.mark.skipif(REFERENCE is None or not REFERENCE.exists(), reason="AFIR_REFERENCE_EXAMPLES does not name the reference's examples/")
+@pytest.mark.parametrize("example", ["broadcast-add-reduce", "split-relu-brc-add-mul", "add-broadcast-concat",
+                                     "relu-broadcast-transpose", "gather-elementwise-fusion", "matmul-add-leakyrelu"])
+def test_reference_schedule_files_run_through_every_stage(tmp_path, example):
+    """The reference's own step2_transform.mlir files (payload already fused, schedule beside it) through the stage
+    sequence of its run.sh: same group as its step0_input.mlir gives."""
+    scheduled = REFERENCE / example / "step2_transform.mlir"
+    src = scheduled
+    for i, flags in enumerate(REFERENCE_STAGES[2:], start=2):
+        dst = tmp_path / f"stage{i}.mlir"
+        r = opt(*flags, src, "-o", dst)
+        assert r.returncode == 0, (flags, r.stderr)
+        src = dst
+    assert "afir.tile_index_args" in src.read_text() and "transform.named_sequence" not in src.read_text()
+    got = translate(src)
+    want = translate(REFERENCE / example / "step0_input.mlir")
+    assert got["kernel_class"] == want["kernel_class"]
+    assert body_of(got) == body_of(want) and got.get("matmul") == want.get("matmul")

@@ -404,9 +404,8 @@ def test_matmul_many_tiles_per_cta(rt):
 @pytest.mark.parametrize("tile_n", [128, 160, 192, 224, 256])
 @pytest.mark.parametrize("mb", [1, 2])
 def test_matmul_tile_widths(rt, monkeypatch, tile_n, mb):
-    """The planner narrows the CTA tile (256 -> 224 ... 128 columns) when that fills the last wave of persistent CTAs;
-    every width must give the same result: ragged N (1000 is not a multiple of any width), several tiles per CTA,
-    both layouts of B."""
+    """The CTA tile can be narrower than 256 columns (224 ... 128, a planner hint); every width must give the same
+    result: ragged N (1000 is not a multiple of any width), several tiles per CTA, both layouts of B."""
     monkeypatch.setenv("AFIR_GEMM_TILE_N", str(tile_n))
     _matmul_check(rt, 520, 1000, 320, mb, seed=tile_n + mb)
     _matmul_check(rt, 2048, 4096, 256, mb, seed=tile_n)
@@ -417,8 +416,8 @@ def test_matmul_tile_widths(rt, monkeypatch, tile_n, mb):
     assert np.array_equal(out, run(rt, w.spec, w.inputs, w.new_output(), w.shape, STAGES=mb))
 
 
-def test_matmul_m_sharded_shapes_take_narrow_tiles_by_default(rt):
-    """8192^3 M-sharded over 8 GPUs is M = 1024 per GPU: 148 tiles of 256 x 224 (one full wave) instead of 128 of 256 x 256."""
+def test_matmul_m_sharded_shapes(rt):
+    """8192^3 M-sharded over 8 and 4 GPUs is M = 1024 and 2048 per GPU (fewer tiles than two waves of SMs)."""
     _matmul_check(rt, 1024, 8192, 512, 0, seed=77)
     _matmul_check(rt, 2048, 8192, 256, 0, seed=78)
 
