@@ -80,7 +80,7 @@ def test_argument_validation_messages():
     assert "tiling data is 8 bytes" in _run_expect_error(rt, spec, [a, a], [a.copy()], til[:8])
     with pytest.raises(ExecutorError, match="binary data is required"):
         rt.run(b"", spec.name, [a, a], [a.copy()], til)
-    with pytest.raises(ExecutorError, match="neither an AFCU container nor a launch descriptor"):
+    with pytest.raises(ExecutorError, match="neither an AFCU container, a launch descriptor nor a kernel source"):
         rt.run(b"\x7fELF not ours", spec.name, [a, a], [a.copy()], til)
 
 
