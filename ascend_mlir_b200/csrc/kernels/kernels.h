@@ -267,6 +267,9 @@ struct MatmulLaunch {
   int bTransposed = 0;  // 1: out = A x B^T with B stored [N,K] (no counterpart in the reference, whose matmul takes
                         // no transposes; it is how torch.nn.Linear keeps its weight)
   MatmulPlan *planOut = nullptr;  // receives the plan that was launched (variant, tile, grid, ...)
+  // Device word that a kernel wait which runs out sets to (1 << 8) | role (the executor points it into its own
+  // workspace); null = a word of the library, one per device, read by matmulCheckStatus.
+  unsigned int *status = nullptr;
 };
 #ifndef __CUDACC_RTC__
 // errorText (optional, >= 256 bytes) receives a description when the launch is refused or the

@@ -26,44 +26,28 @@ std::string buildMatmulPlan(const MatmulProblem &problem, const MatmulHints &hin
   if (smCount < 1) smCount = 1;
 
   plan = MatmulPlan();
-  // The variant is chosen by a small cost model of the persistent kernel: every CTA walks ceil(tiles / CTAs)
-  // tiles, so what counts is the number of WAVES times the cost of a tile, not the tile count.  Cost of a tile in
-  // microseconds, from a fit over K on B200: 12.3 ns per k of a 256 x 256 tile, scaled by the tile's area, plus
-  // 4.4 us while the accumulator drains before the next tile's first MMA (256-row tiles use both accumulators, so
-  // the drain is exposed; 128-row tiles double-buffer them and hide it but move twice the operand bytes per flop,
-  // which costs about 8 % under the board's power cap).  8192^3 M-sharded over 8 GPUs (M = 1024) therefore takes
-  // 128 tiles of 256 x 256 in ONE wave rather than 256 tiles of 128 x 256 in two.
+  // 256-row tiles halve the operand bytes moved into shared memory per flop and are the default whenever they
+  // keep at least half of the SMs busy; below that, 128-row tiles put a small problem on twice as many SMs.
+  // Measured on B200 (K = N = 8192, bf16): 8192^3 M-sharded over 8 GPUs (M = 1024) is 128 tiles of 256 x 256 in one
+  // wave, 101 us, against 256 tiles of 128 x 256 in two waves, 112 us; the same order holds at M = 2048 (196 vs 215
+  // us), 4096 (396 vs 442 us) and 8192 (764 vs 866 us).  (The earlier rule, 256-row tiles only when there is one
+  // per SM, chose the slower variant at M = 1024.)
   // The tile can also be narrower than 256 columns (a hint only): 4 x 37 = 148 tiles of 256 x 224 would fill the
-  // 148 SMs exactly where 4 x 32 = 128 tiles of 256 x 256 leave 20 idle, but measured on B200 a 224-column tile takes
-  // as long as a 256-column one (100.3 us vs 103.1 us at M = 1024, 396 vs 385 us at M = 4096, 727 vs 767 us at
-  // M = 8192): the B stage is loaded 256 columns wide either way and the tile is not MMA-issue bound, so narrowing
-  // buys nothing and is never chosen by default.  The CTA pair is never chosen by default either (no faster under
-  // the power cap) and cannot take B as [N, K], whose tiles it would have to split along K-major rows.
-  int64_t ctasWanted = hints.blockDim > 0 ? hints.blockDim : smCount;
-  auto modelMicros = [&](MatmulVariant variant, int tileN) {
-    const int tileM = variant == MatmulVariant::Rows128 ? 128 : 256;
-    const int64_t tiles = ceilDiv(problem.M, tileM) * ceilDiv(problem.N, tileN);
-    const int64_t waves = ceilDiv(tiles, std::max<int64_t>(1, std::min<int64_t>(ctasWanted, tiles)));
-    const double area = (static_cast<double>(tileN) / 256.0) * (static_cast<double>(tileM) / 256.0);
-    const double perTile = variant == MatmulVariant::Rows128 ? 1.0 + 0.0123 * static_cast<double>(problem.K) * area * 1.08
-                                                             : 4.4 + 0.0123 * static_cast<double>(problem.K) * area;
-    return static_cast<double>(waves) * perTile;
-  };
-  MatmulVariant v = MatmulVariant::Rows256;
+  // 148 SMs exactly where 4 x 32 = 128 tiles of 256 x 256 leave 20 idle, but measured a 224-column tile takes as
+  // long as a 256-column one (100.3 us vs 103.1 us at M = 1024, 396 vs 385 us at M = 4096, 727 vs 767 us at
+  // M = 8192): the B stage is loaded 256 columns wide either way and the kernel is not MMA-issue bound, so
+  // narrowing buys nothing and is never chosen by default.  The CTA pair is never chosen by default either (no
+  // faster under the power cap) and cannot take B as [N, K], whose tiles it would have to split along K-major rows.
+  const int64_t ctasWanted = hints.blockDim > 0 ? hints.blockDim : smCount;
+  const int64_t tiles256 = ceilDiv(problem.M, 256) * ceilDiv(problem.N, kTileN);
+  MatmulVariant v = 2 * tiles256 >= smCount ? MatmulVariant::Rows256 : MatmulVariant::Rows128;
+  if (hints.variant != 0) v = static_cast<MatmulVariant>(hints.variant);
+  if (v == MatmulVariant::CtaPair && problem.transposeB) v = MatmulVariant::Rows256;
   int tileN = kTileN;
-  if (hints.variant == static_cast<int>(MatmulVariant::CtaPair) && !problem.transposeB) {
-    v = MatmulVariant::CtaPair;
-  } else {
-    double best = -1.0;
-    for (MatmulVariant candidate : {MatmulVariant::Rows256, MatmulVariant::Rows128}) {
-      if (hints.variant != 0 && hints.variant != static_cast<int>(MatmulVariant::CtaPair) && hints.variant != static_cast<int>(candidate)) continue;
-      for (int width : {256, 224, 192, 160, 128}) {
-        if (width != (hints.tileN > 0 ? hints.tileN : kTileN)) continue;
-        const double t = modelMicros(candidate, width);
-        if (best < 0.0 || t < best * 0.995) { best = t; v = candidate; tileN = width; }
-      }
-    }
-    if (best < 0.0) return "matmul planner: tile width hint must be 128, 160, 192, 224 or 256";
+  if (hints.tileN > 0 && v != MatmulVariant::CtaPair) {
+    if (hints.tileN != 128 && hints.tileN != 160 && hints.tileN != 192 && hints.tileN != 224 && hints.tileN != 256)
+      return "matmul planner: tile width hint must be 128, 160, 192, 224 or 256";
+    tileN = hints.tileN;
   }
   plan.variant = v;
   plan.tileN = tileN;

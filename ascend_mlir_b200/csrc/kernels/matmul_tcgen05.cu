@@ -44,8 +44,15 @@ constexpr int kBBoxBytes = 64 * 64 * 2;   // one 64(k) x 64(n) box
 constexpr int kBStageBytes = 4 * kBBoxBytes;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
-// status word: 0 = ok, else (code << 8) | role
+// status word: 0 = ok, else (code << 8) | role.  A launch that brings its own word (the executor points it into
+// its workspace, so executors sharing a device do not read each other's time-outs) uses that; otherwise this one.
 __device__ unsigned int g_matmulStatus = 0;
+
+// Per-CTA abort state in shared memory: raised by the first wait that runs out, seen by every role's next check.
+struct AbortState {
+  int flag;
+  unsigned int *status;  // where the time-out is reported
+};
 
 struct GemmParams {
   int M, N, K;
@@ -55,6 +62,7 @@ struct GemmParams {
   int biasType, epilogue;
   float alpha;
   unsigned int idesc;
+  unsigned int *status;  // device word for wait time-outs, or null for the library's own
   int tileN;  // columns per CTA tile: 256, or less (a multiple of 32) when that fills the last wave of CTAs
   int band;  // tile-rows per raster band
   int bKMajor;  // 1: B is given as [N, K] (out = A x B^T, the layout of a torch Linear weight): K-major tiles like A's
@@ -90,7 +98,7 @@ __device__ __forceinline__ bool mbarTryWait(unsigned int bar, unsigned int parit
   return done != 0;
 }
 // Bounded wait.  Returns false when the abort flag is (or becomes) raised.
-__device__ __forceinline__ bool mbarWait(unsigned int bar, unsigned int parity, volatile int *abortFlag, unsigned int role) {
+__device__ __forceinline__ bool mbarWait(unsigned int bar, unsigned int parity, volatile AbortState *abortFlag, unsigned int role) {
   if (mbarTryWait(bar, parity)) return true;
   const unsigned long long t0 = globalTimerNs();
   unsigned int spins = 0;
@@ -100,10 +108,10 @@ __device__ __forceinline__ bool mbarWait(unsigned int bar, unsigned int parity, 
     if (role == 2) __nanosleep(256);
     else if (role == 0) __nanosleep(64);  // the producer is normally a full ring ahead: poll lazily
     if ((++spins & 63u) == 0) {
-      if (*abortFlag) return false;
+      if (abortFlag->flag) return false;
       if (globalTimerNs() - t0 > kWaitLimitNs) {
-        *abortFlag = 1;
-        atomicCAS(&g_matmulStatus, 0u, (1u << 8) | role);
+        abortFlag->flag = 1;
+        atomicCAS(abortFlag->status, 0u, (1u << 8) | role);
         return false;
       }
     }
@@ -228,7 +236,7 @@ template <int STAGES> struct Control {
   unsigned long long tmemFull[2];
   unsigned long long tmemEmpty[2];
   unsigned int tmemBase;
-  int abortFlag;
+  AbortState abortFlag;
 };
 
 template <int MB> struct Shape {
@@ -249,7 +257,7 @@ template <int MB> struct Shape {
 template <int OUT, class ArriveEmpty>
 __device__ __forceinline__ bool epilogueTile(const GemmParams &prm, unsigned char *stg, unsigned int taddr, int rowBase, int tn,
                                              int lane, unsigned int fullBar, unsigned int fullParity,
-                                             volatile int *abortFlag, ArriveEmpty arriveEmpty) {
+                                             volatile AbortState *abortFlag, ArriveEmpty arriveEmpty) {
       constexpr int kColsPerSlice = 128 / OutPack<OUT>::kBytes;  // 64 (16-bit) or 32 (f32)
 
       // Writes one 128-byte slice per row (parked in `stg`, 16-byte pieces XOR-swizzled by row so both
@@ -375,7 +383,7 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
   unsigned char *staging = smem + static_cast<size_t>(STAGES) * S::kStageBytes;
   Control<STAGES> *ctl = reinterpret_cast<Control<STAGES> *>(staging + S::kStagingBytes);
-  volatile int *abortFlag = &ctl->abortFlag;
+  volatile AbortState *abortFlag = &ctl->abortFlag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -390,7 +398,8 @@ matmulBiasActKernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       mbarInit(smemAddr(&ctl->tmemFull[a]), 1);
       mbarInit(smemAddr(&ctl->tmemEmpty[a]), MB == 1 ? 4 : 4);  // one arrival per epilogue warp of that accumulator
     }
-    ctl->abortFlag = 0;
+    ctl->abortFlag.flag = 0;
+    ctl->abortFlag.status = prm.status ? prm.status : &g_matmulStatus;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     prefetchTensorMap(&mapA);
@@ -590,7 +599,7 @@ matmulBiasActPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
   unsigned char *staging = smem + static_cast<size_t>(k2Stages) * k2StageBytes;
   Control<k2Stages> *ctl = reinterpret_cast<Control<k2Stages> *>(staging + k2StagingBytes);
-  volatile int *abortFlag = &ctl->abortFlag;
+  volatile AbortState *abortFlag = &ctl->abortFlag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -608,7 +617,8 @@ matmulBiasActPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
       mbarInit(smemAddr(&ctl->tmemFull[a]), 1);
       mbarInit(smemAddr(&ctl->tmemEmpty[a]), 8);  // four epilogue warps in each CTA (leader's copy is the one used)
     }
-    ctl->abortFlag = 0;
+    ctl->abortFlag.flag = 0;
+    ctl->abortFlag.status = prm.status ? prm.status : &g_matmulStatus;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     prefetchTensorMap(&mapA);
@@ -883,6 +893,7 @@ int launchMatmul(const MatmulLaunch &l, cudaStream_t stream, int *launched, char
   p.epilogue = l.epilogue;
   p.alpha = l.alpha;
   p.band = plan.band;
+  p.status = l.status;
   const unsigned int fmt = l.inType == kF16 ? 0u : 1u;
   // instruction descriptor: D=f32, A/B format, A K-major, B N-major, N = the tile's columns, M=128 (256 across a CTA pair)
   const unsigned int instrM = pairKernel ? 256u : 128u;

@@ -535,7 +535,8 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   LaunchInfo info;
   // The status words (bad gather indices, a staged reduction's time-out) accumulate over the launches queued since
   // the last synchronize: they are cleared only when nothing unread is pending on this workspace.
-  const bool hasStatusWords = (desc->kernelClass == KernelClass::Gather || desc->kernelClass == KernelClass::RowReduce) &&
+  const bool hasStatusWords = (desc->kernelClass == KernelClass::Gather || desc->kernelClass == KernelClass::RowReduce ||
+                               desc->kernelClass == KernelClass::Matmul) &&
                               args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes;
   if (hasStatusWords && !(statusPending_ && statusWorkspace_ == args.workspace)) {
     e = cudaMemsetAsync(args.workspace, 0, kWorkspaceStatusReadBytes, args.stream);
@@ -612,6 +613,13 @@ Status CudaExecutor::synchronize(void *stream) {
     const unsigned long long bad = words[0];
     if (static_cast<unsigned int>(words[1] & 0xffffffffull) != 0)
       return Status::error("[cuda:kernel_launch] row reduction: a warp gave up waiting for a bulk copy after 2 s");
+    if (const unsigned int mm = static_cast<unsigned int>(words[1] >> 32)) {
+      static const char *roles[] = {"TMA producer", "MMA issuer", "epilogue"};
+      char text[160];
+      std::snprintf(text, sizeof(text), "[cuda:kernel_launch] matmul: %s gave up waiting on a pipeline barrier after 2 s (status 0x%x)",
+                    roles[std::min(2u, mm & 0xffu)], mm);
+      return Status::error(text);
+    }
     constexpr unsigned long long kGatherTimeoutFlag = 1ull << 62;  // set by the staged gather kernel when a stage wait ran out
     if (bad & kGatherTimeoutFlag) return Status::error("[cuda:kernel_launch] gather kernel gave up waiting for a staged copy");
     if (bad) return Status::error("[cuda:kernel_launch] gather index out of range (" + std::to_string(bad) + " indices)");

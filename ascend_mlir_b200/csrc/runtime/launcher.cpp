@@ -482,6 +482,10 @@ Status launchMatmulDescriptor(const LaunchDescriptor &d, const std::map<std::str
   l.bTransposed = m.transposeB ? 1 : 0;
   l.gridBlocks = args.blockDim;
   l.stages = static_cast<int>(optionalField(d.stagesField, tiling));
+  if (args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes) {
+    l.status = reinterpret_cast<unsigned int *>(static_cast<char *>(args.workspace) + kWorkspaceMatmulStatusOffset);
+    info.usesStatusBlock = true;
+  }
   int n = 0;
   char text[256] = {0};
   kernels::MatmulPlan plan;

@@ -15,9 +15,11 @@
 namespace afir {
 
 // Workspace layout: a 256-byte status block (offset 0: u64 count of out-of-range gather indices, offset 8: u32
-// time-out flag of the staged row-reduction kernel), then kernel scratch (row-reduction partial sums).
+// time-out flag of the staged row-reduction kernel, offset 12: u32 time-out word of the matmul kernel), then kernel
+// scratch (row-reduction partial sums).
 constexpr size_t kWorkspaceStatusBytes = 256;
 constexpr size_t kWorkspaceReduceStatusOffset = 8;  // u32: a staged row-reduction kernel gave up waiting for a copy
+constexpr size_t kWorkspaceMatmulStatusOffset = 12; // u32: (1 << 8) | role of a matmul pipeline wait that ran out
 constexpr size_t kWorkspaceStatusReadBytes = 16;    // what the executor reads back after a run
 
 struct LaunchArgs {
