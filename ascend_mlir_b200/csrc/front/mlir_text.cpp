@@ -377,6 +377,17 @@ std::string printModule(const Module &m) {
   for (const auto &i : ins) edits.push_back({i.first, 0, i.second});
   for (const auto &e : m.erasures)
     if (e.second > e.first && e.second <= m.source.size()) edits.push_back({e.first, e.second - e.first, std::string()});
+  for (const auto &r : m.replacements)
+    if (r.end >= r.begin && r.end <= m.source.size()) edits.push_back({r.begin, r.end - r.begin, r.text});
+  // an attribute insertion that falls inside a replaced span belongs to text that is going away
+  edits.erase(std::remove_if(edits.begin(), edits.end(), [&](const Edit &e) {
+                if (e.erase != 0) return false;
+                for (const auto &r : m.replacements)
+                  if (e.at > r.begin && e.at < r.end) return true;
+                for (const auto &r : m.erasures)
+                  if (e.at > r.first && e.at < r.second) return true;
+                return false;
+              }), edits.end());
   std::sort(edits.begin(), edits.end(), [](const Edit &a, const Edit &b) { return a.at > b.at; });
   std::string out = m.source;
   for (const Edit &e : edits) out.replace(e.at, e.erase, e.text);

@@ -102,6 +102,9 @@ struct Module {
   size_t moduleAttrBegin = 0, moduleAttrEnd = 0;  // span of "attributes {...}" after the module keyword (0 = none)
   // spans of the source text that printModule leaves out (a pass that removes the schedule fills this)
   std::vector<std::pair<size_t, size_t>> erasures;
+  // spans [begin, end) that printModule replaces by other text (a pass that rewrites ops fills this)
+  struct Replacement { size_t begin, end; std::string text; };
+  std::vector<Replacement> replacements;
 };
 
 Status parseModule(const std::string &text, Module &out);

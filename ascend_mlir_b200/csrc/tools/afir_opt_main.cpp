@@ -4,9 +4,13 @@
 //   --mark-structured-ops               gather_dim / embedding_dim on gather generics
 //   --annotate-ascendc-kernel-kind      ascendc.kernel_kind = "vec" | "cube" | "mix" on the function
 //   --annotate-mix-matmul-semantics     abi_matmul_* attributes (epilogue kind, bias, layouts) on matmul functions
-//   --linalg-fuse-elementwise-ops, --fuse-gather-elementwise
-//                                       fusion is carried out symbolically by the conversion; these check that the
-//                                       function fuses into one group and record its size as afir.fused_group
+//   --linalg-fuse-elementwise-ops       an elementwise / broadcast / reduction chain of generics becomes ONE generic with
+//                                       the fused body (what the upstream pass leaves behind)
+//   --fuse-gather-elementwise           a gather with pre- and post-ops becomes one gather generic: pre-op ->
+//                                       tensor.extract -> post-ops, reading the index vector and the broadcast extras
+//                                       (lib/Conversion/FuseGatherElementwise/FuseGatherElementwisePass.cpp:61-303);
+//                                       both record the group as afir.fused_group; groups whose views are slices of an
+//                                       argument (split / concat) and matmul epilogues keep their ops
 //   --convert-afir-to-cuda              afir.cuda_kernel_class / afir.cuda_launch (descriptor JSON) on the function
 // Structural passes of upstream MLIR that do not change what the group computes (--canonicalize, --cse,
 // --afir-canonicalize, --afir-shape-inference, --linalg-fold-unit-extent-dims) verify and pass the module through.
@@ -35,6 +39,7 @@
 #include <iterator>
 #include <set>
 
+#include "front/fused_generic.h"
 #include "front/group_analysis.h"
 
 using namespace afir;
@@ -107,6 +112,7 @@ int main(int argc, char **argv) {
       std::cerr << (input.empty() ? "<stdin>" : input) << ": error: --transform-interpreter: the module holds no transform.named_sequence\n";
       return 1;
     }
+  std::set<std::string> rewritten;
   if (needAnalysis) {
     for (Func &f : module.funcs) {
       GroupAnalysis ga;
@@ -120,6 +126,15 @@ int main(int argc, char **argv) {
         } else if (p == "annotate-mix-matmul-semantics") {
           for (size_t i = 1; i < ga.funcAttrs.size(); ++i) f.addedAttrs.push_back(ga.funcAttrs[i]);
         } else if (p == "linalg-fuse-elementwise-ops" || p == "fuse-gather-elementwise") {
+          // The group's generics become ONE generic with the fused body (elementwise / reduction chains under the
+          // first flag, a gather with its pre- and post-ops under the second).  Groups the rewrite does not cover
+          // (slices of an argument, a matmul and its epilogue) keep their ops; either way the function records
+          // which group it fuses into.
+          const bool gatherGroup = ga.kernelClass == "gather";
+          if ((p == "fuse-gather-elementwise") == gatherGroup && !rewritten.count(f.name)) {
+            std::string why;
+            if (fuseGenericsInPlace(module, f, ga, why)) rewritten.insert(f.name);
+          }
           bool have = false;
           for (const auto &kv : f.addedAttrs) have = have || kv.first == "afir.fused_group";
           if (!have) f.addedAttrs.push_back({"afir.fused_group", "\"" + ga.kernelClass + "\""});

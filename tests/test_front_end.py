@@ -428,3 +428,94 @@ def test_reference_schedule_files_run_through_every_stage(tmp_path, example):
     want = translate(REFERENCE / example / "step0_input.mlir")
     assert got["kernel_class"] == want["kernel_class"]
     assert body_of(got) == body_of(want) and got.get("matmul") == want.get("matmul")
+
+
+# ---- fusion passes rewrite the IR -----------------------------------------------------------------------------------------
+def count_generics(text):
+    return sum(1 for line in text.splitlines() if "linalg.generic" in line and not line.strip().startswith("//"))
+
+
+def test_fuse_elementwise_ops_leaves_one_generic_with_the_fused_body(tmp_path):
+    """In the style of the reference's pass tests (test/Conversion/mark-structured-ops.mlir): the printed IR is checked."""
+    src = EXAMPLES / "broadcast_add_reduce.mlir"
+    assert count_generics(src.read_text()) == 2
+    r = opt("--linalg-fuse-elementwise-ops", src)
+    assert r.returncode == 0, r.stderr
+    out = r.stdout
+    assert count_generics(out) == 1
+    assert 'iterator_types = ["parallel", "reduction"]' in out
+    assert "ins(%b, %x : tensor<?xf32>, tensor<?x?xf32>) outs(%init : tensor<?xf32>)" in out
+    # broadcast + add inlined into the reduction body: acc + (b[m] + x[m, n])
+    assert "%f0 = arith.addf %in0, %in1 : f32" in out and "%sum = arith.addf %acc, %f0 : f32" in out
+    assert 'afir.fused_group = "row_reduce"' in out
+    # the rewritten module is the same group: it translates to the same descriptor
+    fused = tmp_path / "fused.mlir"
+    fused.write_text(out)
+    a, b = translate(src), translate(fused)
+    assert (a["kernel_class"], body_of(a), views_of(a)) == (b["kernel_class"], body_of(b), views_of(b))
+    # running the pass again changes nothing more
+    again = opt("--linalg-fuse-elementwise-ops", fused)
+    assert again.returncode == 0 and count_generics(again.stdout) == 1
+
+
+def test_fuse_elementwise_chain_with_constants_and_broadcasts(tmp_path):
+    text = """#full = affine_map<(d0, d1) -> (d0, d1)>
+#row = affine_map<(d0, d1) -> (d1)>
+func.func @gated(%x: tensor<64x128xf16>, %s: tensor<128xf16>) -> tensor<64x128xf16> {
+  %zero = arith.constant 0.0 : f16
+  %e0 = tensor.empty() : tensor<64x128xf16>
+  %a = linalg.generic {indexing_maps = [#full, #row, #full], iterator_types = ["parallel", "parallel"]}
+      ins(%x, %s : tensor<64x128xf16>, tensor<128xf16>) outs(%e0 : tensor<64x128xf16>) {
+  ^bb0(%xv: f16, %sv: f16, %o: f16):
+    %m = arith.mulf %xv, %sv : f16
+    linalg.yield %m : f16
+  } -> tensor<64x128xf16>
+  %e1 = tensor.empty() : tensor<64x128xf16>
+  %b = linalg.generic {indexing_maps = [#full, #full], iterator_types = ["parallel", "parallel"]}
+      ins(%a : tensor<64x128xf16>) outs(%e1 : tensor<64x128xf16>) {
+  ^bb0(%av: f16, %o: f16):
+    %r = arith.maximumf %av, %zero : f16
+    %t = arith.addf %r, %av : f16
+    linalg.yield %t : f16
+  } -> tensor<64x128xf16>
+  return %b : tensor<64x128xf16>
+}
+"""
+    r = opt("--linalg-fuse-elementwise-ops", stdin=text)
+    assert r.returncode == 0, r.stderr
+    assert count_generics(r.stdout) == 1
+    assert "%cst0 = arith.constant 0.000000e+00 : f16" in r.stdout
+    assert "%f0 = arith.mulf %in0, %in1 : f16" in r.stdout and "%f1 = arith.maximumf %f0, %cst0 : f16" in r.stdout
+    assert "%f2 = arith.addf %f1, %f0 : f16" in r.stdout and "linalg.yield %f2 : f16" in r.stdout
+    plain, fused = tmp_path / "plain.mlir", tmp_path / "fused.mlir"
+    plain.write_text(text)
+    fused.write_text(r.stdout)
+    a, b = translate(plain), translate(fused)
+    assert (body_of(a), views_of(a)) == (body_of(b), views_of(b))
+
+
+def test_groups_the_rewrite_does_not_cover_keep_their_ops():
+    for name in ("split_relu_broadcast_add_mul", "matmul_add_leakyrelu"):
+        src = EXAMPLES / f"{name}.mlir"
+        r = opt("--linalg-fuse-elementwise-ops", src)
+        assert r.returncode == 0, r.stderr
+        assert count_generics(r.stdout) == count_generics(src.read_text())
+        assert "afir.fused_group" in r.stdout
+
+
+@pytest.mark.skipif(REFERENCE is None or not REFERENCE.exists(), reason="AFIR_REFERENCE_EXAMPLES does not name the reference's examples/")
+def test_fuse_gather_elementwise_builds_the_reference_form(tmp_path):
+    """relu -> index_select -> add of the reference's gather example (three generics) becomes the single gather generic
+    its step2_transform.mlir holds: indices and bias as inputs, relu after the tensor.extract, gather_dim = 1."""
+    src = REFERENCE / "gather-elementwise-fusion" / "step0_input.mlir"
+    assert count_generics(src.read_text()) == 3
+    r = opt("--mark-structured-ops", "--fuse-gather-elementwise", src)
+    assert r.returncode == 0, r.stderr
+    out = r.stdout
+    assert count_generics(out) == 1 and "gather_dim = 1 : i64" in out
+    assert "%pos = linalg.index 0 : index" in out and "tensor.extract %data[%pos, %picked]" in out
+    assert "arith.maximumf %gathered, %cst0 : f16" in out
+    fused = tmp_path / "fused.mlir"
+    fused.write_text(out)
+    a, b = translate(src), translate(fused)
+    assert (a["kernel_class"], a["gather"], body_of(a)) == (b["kernel_class"], b["gather"], body_of(b))

@@ -44,7 +44,7 @@ def test_cpp_checks_under_address_and_undefined_behaviour_sanitizers(tmp_path):
                                "kernels/body_match.cpp", "execution/artifact_compiler.cpp", "execution/execution_session.cpp",
                                "execution/global_scheduler.cpp", "execution/output_comparator.cpp",
                                "execution/profile_retention.cpp", "execution/resource_scheduler.cpp",
-                               "execution/run_manifest.cpp", "execution/task_graph.cpp", "front/group_analysis.cpp",
+                               "execution/run_manifest.cpp", "execution/task_graph.cpp", "front/group_analysis.cpp", "front/fused_generic.cpp",
                                "front/mlir_text.cpp", "runtime/descriptor.cpp", "support/npy_io.cpp",
                                "support/tiling_schema.cpp")]
     objs = [str(o) for o in sorted((ROOT / "ascend_mlir_b200" / "build").glob("*.o"))
