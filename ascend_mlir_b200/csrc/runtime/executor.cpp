@@ -209,6 +209,35 @@ Status CudaExecutor::validate(const RunRequest &req, CachedKernel *&kernel, std:
   return Status::success();
 }
 
+// Below this size the driver's own staging of a pageable buffer is not worth replacing.
+static constexpr size_t kStagingMinBytes = 1u << 20;
+static bool stagingEnabled() {
+  const char *v = std::getenv("AFIR_CUDA_NO_STAGING");
+  return !(v && *v && std::string(v) != "0");
+}
+
+Status CudaExecutor::copyToDevice(void *device, const void *host, size_t bytes, void *stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bytes >= kStagingMinBytes && stagingEnabled() && HostStager::isPageable(host)) {
+    if (!stager_) stager_.reset(new HostStager());
+    if (Status st = stager_->prepare(); !st) return st;
+    return stager_->copyIn(device, host, bytes, s);
+  }
+  const cudaError_t e = cudaMemcpyAsync(device, host, bytes, cudaMemcpyHostToDevice, s);
+  return e == cudaSuccess ? Status::success() : cudaFail(e, "[cuda:memory] host-to-device copy failed");
+}
+
+Status CudaExecutor::copyToHost(void *host, const void *device, size_t bytes, void *stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bytes >= kStagingMinBytes && stagingEnabled() && HostStager::isPageable(host)) {
+    if (!stager_) stager_.reset(new HostStager());
+    if (Status st = stager_->prepare(); !st) return st;
+    return stager_->copyOut(host, device, bytes, s);
+  }
+  const cudaError_t e = cudaMemcpyAsync(host, device, bytes, cudaMemcpyDeviceToHost, s);
+  return e == cudaSuccess ? Status::success() : cudaFail(e, "[cuda:memory] device-to-host copy failed");
+}
+
 // AFIR_CUDA_CODEGEN: "auto" (default) runs elementwise / split / concat and row-reduction groups on the kernel
 // generated for them (measured at or above the library's straight-line kernels on every benchmark shape), and a
 // gather group when the library would otherwise interpret its body op by op; "always" uses generated code
@@ -338,8 +367,7 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   cudaError_t e;
   for (int i = 0; i < req.numInputs; ++i) {
     if (!req.inputBytes[i]) continue;
-    e = cudaMemcpyAsync(args.argPtrs[i], req.inputPtrs[i], req.inputBytes[i], cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] host-to-device copy failed");
+    if (Status cs = copyToDevice(args.argPtrs[i], req.inputPtrs[i], req.inputBytes[i], stream); !cs) return cs;
     if (launchTraceEnabled()) {
       // what the host handed over, and the same bytes read back from the device (reference
       // NativeExecutionRunner.cpp:391-416: input[i].host, h2d_roundtrip match=..., input[i].h2d_roundtrip)
@@ -370,9 +398,10 @@ Status CudaExecutor::runHost(const RunRequest &req) {
   if (launchTraceEnabled() && !info.plan.empty()) std::fprintf(stderr, "[cuda-launch] matmul plan: %s\n", info.plan.c_str());
   for (int i = 0; i < req.numOutputs; ++i) {
     if (!req.outputBytes[i]) continue;
-    e = cudaMemcpyAsync(req.outputPtrs[i], args.argPtrs[req.numInputs + i], req.outputBytes[i], cudaMemcpyDeviceToHost, stream);
-    if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] device-to-host copy failed");
+    if (Status cs = copyToHost(req.outputPtrs[i], args.argPtrs[req.numInputs + i], req.outputBytes[i], stream); !cs) return cs;
   }
+  if (stager_)
+    if (Status fs = stager_->finishOut(); !fs) return fs;
   statusPending_ = info.usesStatusBlock;
   statusWorkspace_ = workspace_.ptr;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
@@ -434,8 +463,7 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, CachedKernel &kerne
   // arguments every chunk needs in full go first
   for (int i = 0; i < req.numInputs; ++i) {
     if (plan.rowBytes[i] || !req.inputBytes[i]) continue;
-    if ((e = cudaMemcpyAsync(args.argPtrs[i], req.inputPtrs[i], req.inputBytes[i], cudaMemcpyHostToDevice, in)) != cudaSuccess)
-      return cudaFail(e, "[cuda:memory] host-to-device copy failed");
+    if (Status cs = copyToDevice(args.argPtrs[i], req.inputPtrs[i], req.inputBytes[i], in); !cs) return cs;
   }
   lastLaunchCount_ = 0;
   bool usesStatus = false;
@@ -444,10 +472,10 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, CachedKernel &kerne
     for (int i = 0; i < req.numInputs; ++i) {
       const size_t rb = plan.rowBytes[i];
       if (!rb) continue;
-      e = cudaMemcpyAsync(static_cast<char *>(args.argPtrs[i]) + static_cast<size_t>(b) * rb,
-                          static_cast<const char *>(req.inputPtrs[i]) + static_cast<size_t>(b) * rb,
-                          static_cast<size_t>(en - b) * rb, cudaMemcpyHostToDevice, in);
-      if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] host-to-device copy failed");
+      if (Status cs = copyToDevice(static_cast<char *>(args.argPtrs[i]) + static_cast<size_t>(b) * rb,
+                                   static_cast<const char *>(req.inputPtrs[i]) + static_cast<size_t>(b) * rb,
+                                   static_cast<size_t>(en - b) * rb, in); !cs)
+        return cs;
     }
     if (Status o = order(in, compute, 2 * c); !o) return o;  // the kernel of chunk c waits for its copy-in
     args.rowBegin = b;
@@ -471,10 +499,10 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, CachedKernel &kerne
       const size_t k = static_cast<size_t>(req.numInputs + i);
       const size_t rb = plan.rowBytes[k];
       if (!rb || !req.outputBytes[i]) continue;
-      e = cudaMemcpyAsync(static_cast<char *>(req.outputPtrs[i]) + static_cast<size_t>(b) * rb,
-                          static_cast<const char *>(args.argPtrs[k]) + static_cast<size_t>(b) * rb,
-                          static_cast<size_t>(en - b) * rb, cudaMemcpyDeviceToHost, out);
-      if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] device-to-host copy failed");
+      if (Status cs = copyToHost(static_cast<char *>(req.outputPtrs[i]) + static_cast<size_t>(b) * rb,
+                                 static_cast<const char *>(args.argPtrs[k]) + static_cast<size_t>(b) * rb,
+                                 static_cast<size_t>(en - b) * rb, out); !cs)
+        return cs;
     }
   }
   // outputs that are not row-sliced (none today) would be copied here after the last chunk
@@ -482,9 +510,10 @@ Status CudaExecutor::runHostPipelined(const RunRequest &req, CachedKernel &kerne
     const size_t k = static_cast<size_t>(req.numInputs + i);
     if (plan.rowBytes[k] || !req.outputBytes[i]) continue;
     if (Status o = order(compute, out, 2 * numChunks); !o) return o;
-    e = cudaMemcpyAsync(req.outputPtrs[i], args.argPtrs[k], req.outputBytes[i], cudaMemcpyDeviceToHost, out);
-    if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] device-to-host copy failed");
+    if (Status cs = copyToHost(req.outputPtrs[i], args.argPtrs[k], req.outputBytes[i], out); !cs) return cs;
   }
+  if (stager_)
+    if (Status fs = stager_->finishOut(); !fs) return fs;
   if ((e = cudaStreamSynchronize(in)) != cudaSuccess) return cudaFail(e, "[cuda:memory] host-to-device copy failed");
   if ((e = cudaStreamSynchronize(out)) != cudaSuccess) return cudaFail(e, "[cuda:kernel_launch] kernel execution failed");
   statusPending_ = usesStatus;

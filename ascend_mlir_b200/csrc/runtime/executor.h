@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "runtime/descriptor.h"
+#include "runtime/host_staging.h"
 #include "runtime/launcher.h"
 
 namespace afir {
@@ -103,6 +104,12 @@ private:
   void *copyIn_ = nullptr;
   void *copyOut_ = nullptr;
   std::vector<void *> events_;
+  // Pageable host buffers (what a numpy caller hands over) go through pinned slots filled by several threads;
+  // AFIR_CUDA_NO_STAGING=1 leaves them to the driver's own single-threaded staging.
+  std::unique_ptr<HostStager> stager_;
+  // Copies between the caller's buffers and the device, through the stager when the host side is pageable and large.
+  Status copyToDevice(void *device, const void *host, size_t bytes, void *stream);
+  Status copyToHost(void *host, const void *device, size_t bytes, void *stream);
   std::vector<Slot> slots_;
   Slot workspace_;
   std::unordered_map<uint64_t, CachedKernel> cache_;

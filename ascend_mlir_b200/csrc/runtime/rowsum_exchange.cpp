@@ -180,6 +180,18 @@ AFIRT_EXPORT int afirt_bcast_add_rowsum_exchange(AfirtRowsumExchange x, int elem
   return 0;
 }
 
+// A run of `count` independent reductions of the same shape (operands a[i], b[i], out[i]) enqueued back to back
+// on one stream by one call: what a caller with a queue of work (layers, micro-batches) does, without paying the
+// language binding once per reduction.  Collective like the single call: every rank passes the same count.
+AFIRT_EXPORT int afirt_bcast_add_rowsum_exchange_batch(AfirtRowsumExchange x, int elem_type, int count, const void *const *a,
+                                                       const void *const *b, void *const *out, int64_t rows, int64_t cols,
+                                                       int64_t b_row_stride, void *cuda_stream, char *err_buf, size_t err_len) {
+  if (count < 0 || (count > 0 && (!a || !b || !out))) { fail(err_buf, err_len, "count must not be negative and the pointer arrays are required"); return 1; }
+  for (int i = 0; i < count; ++i)
+    if (afirt_bcast_add_rowsum_exchange(x, elem_type, a[i], b[i], out[i], rows, cols, b_row_stride, cuda_stream, err_buf, err_len) != 0) return 1;
+  return 0;
+}
+
 namespace afir {
 
 Status nextExchangeCall(AfirtRowsumExchange x, kernels::RowReduceExchange &rx, int &device) {

@@ -49,7 +49,7 @@ def make_case(name: str, rng):
         h0, h1 = x[..., :1024], x[..., 1024:]
         want = ((np.maximum(h0, np.float16(0)) + bias[None, :, None]).astype(np.float16) * h1).astype(np.float16)
         return [x, bias], want, 0.0, 0.0
-    if name == "broadcast_add_reduce":
+    if name in ("broadcast_add_reduce", "broadcast_add_reduce_scheduled"):  # the second: already fused, with a tiling schedule beside it
         b = rng.uniform(-1, 1, 640).astype(np.float32)
         x = rng.uniform(-1, 1, (640, 512)).astype(np.float32)
         return [b, x], (b[:, None].astype(np.float64) + x).sum(axis=1).astype(np.float32), 1e-3, 1e-5

@@ -21,6 +21,7 @@ EXPORTS = [
     "afirt_runtime_version",
     "afirt_bcast_add_rowsum_no_alloc",
     "afirt_rowsum_exchange_create", "afirt_rowsum_exchange_connect", "afirt_bcast_add_rowsum_exchange",
+    "afirt_bcast_add_rowsum_exchange_batch",
     "afirt_rowsum_exchange_status", "afirt_rowsum_exchange_destroy", "afirt_executor_launch_device_exchange",
     "afirt_executor_launch_device_sharded_table", "afirt_peer_export", "afirt_peer_import", "afirt_peer_release",
 ]
@@ -94,6 +95,10 @@ def get_lib() -> ctypes.CDLL:
                                                     ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                                     ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
     lib.afirt_bcast_add_rowsum_exchange.restype = ctypes.c_int
+    lib.afirt_bcast_add_rowsum_exchange_batch.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, _vpp, _vpp, _vpp,
+                                                          ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
+                                                          ctypes.c_char_p, ctypes.c_size_t]
+    lib.afirt_bcast_add_rowsum_exchange_batch.restype = ctypes.c_int
     lib.afirt_rowsum_exchange_status.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
     lib.afirt_rowsum_exchange_status.restype = ctypes.c_int
     lib.afirt_rowsum_exchange_destroy.argtypes = [ctypes.c_void_p]

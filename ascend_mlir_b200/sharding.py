@@ -136,6 +136,18 @@ class RowsumExchange:
                                                      err, len(err)):
             raise RuntimeError(err.value.decode())
 
+    def bcast_add_rowsum_batch(self, a_ptrs, b_ptrs, out_ptrs, rows: int, cols: int, b_row_stride: int,
+                               elem_type: str = "f32", stream: int = 0) -> None:
+        """Enqueues len(a_ptrs) independent reductions of one shape back to back with one call into the library."""
+        ct = self._ct
+        n = len(a_ptrs)
+        arr = lambda ptrs: (ct.c_void_p * n)(*ptrs)  # noqa: E731
+        err = ct.create_string_buffer(512)
+        if self._lib.afirt_bcast_add_rowsum_exchange_batch(self._ptr, self.ELEM_TYPES[elem_type], n, arr(a_ptrs), arr(b_ptrs),
+                                                           arr(out_ptrs), rows, cols, b_row_stride, ct.c_void_p(stream),
+                                                           err, len(err)):
+            raise RuntimeError(err.value.decode())
+
     def check(self) -> None:
         """After the stream has been synchronised: raises when a wait inside the kernel ran out."""
         err = self._ct.create_string_buffer(512)

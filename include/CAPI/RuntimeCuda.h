@@ -104,6 +104,12 @@ int afirt_rowsum_exchange_connect(AfirtRowsumExchange exchange, const uint8_t *a
 int afirt_bcast_add_rowsum_exchange(AfirtRowsumExchange exchange, int elem_type, const void *a, const void *b, void *out,
                                     int64_t rows, int64_t cols, int64_t b_row_stride, void *cuda_stream,
                                     char *err_buf, size_t err_len);
+/* `count` independent reductions of one shape (a[i], b[i], out[i]) enqueued back to back by one call, for callers
+ * with a queue of work; collective like the single call (every rank passes the same count).  No counterpart in
+ * the reference. */
+int afirt_bcast_add_rowsum_exchange_batch(AfirtRowsumExchange exchange, int elem_type, int count, const void *const *a,
+                                          const void *const *b, void *const *out, int64_t rows, int64_t cols,
+                                          int64_t b_row_stride, void *cuda_stream, char *err_buf, size_t err_len);
 /* The same exchange for ANY compiled row-reduction group: afirt_executor_launch_device with one more argument.
  * The descriptor's tiling dims describe this rank's column slice (contiguous arguments, as always on that
  * path); the kernel sends the slice's partial row sums through the exchange and writes the sums over all ranks

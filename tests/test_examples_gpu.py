@@ -21,7 +21,7 @@ def built():
 
 def test_every_example_module_has_a_case():
     assert set(EXAMPLES) == {"elementwise_chain", "split_relu_broadcast_add_mul", "broadcast_add_reduce", "gather_elementwise",
-                             "matmul_add_leakyrelu", "transpose_2d", "transposed_add", "integer_chain"}
+                             "matmul_add_leakyrelu", "transpose_2d", "transposed_add", "integer_chain", "broadcast_add_reduce_scheduled"}
 
 
 @pytest.mark.parametrize("name", EXAMPLES)

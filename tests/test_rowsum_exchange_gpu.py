@@ -147,3 +147,28 @@ def test_argument_errors_leave_the_exchange_usable():
     x.close()
     err = ctypes.create_string_buffer(64)
     assert lib.afirt_rowsum_exchange_status(None, err, len(err)) == 1 and err.value
+
+
+def test_batch_call_enqueues_independent_reductions_back_to_back():
+    """afirt_bcast_add_rowsum_exchange_batch: five reductions (five operand sets, five outputs) by one call; each gets
+    its own call number, so the mailbox halves alternate exactly as with five single calls."""
+    import torch
+    rt = CudaRuntime()
+    rt.set_device(0)
+    rows, cols = 2048, 4096
+    x = RowsumExchange(0, 0, 1, max_rows=rows)
+    x.connect()
+    try:
+        g = torch.Generator(device="cuda").manual_seed(9)
+        sets = [(torch.rand(rows, device="cuda", generator=g) - 0.5, torch.rand(rows, cols, device="cuda", generator=g) - 0.5)
+                for _ in range(5)]
+        outs = [torch.full((rows,), float("nan"), device="cuda") for _ in sets]
+        x.bcast_add_rowsum_batch([a.data_ptr() for a, _ in sets], [b.data_ptr() for _, b in sets], [o.data_ptr() for o in outs],
+                                 rows, cols, cols)
+        torch.cuda.synchronize()
+        x.check()
+        for (a, b), out in zip(sets, outs):
+            assert torch.equal(out, _ordinary(torch, rt, a, b, 0, cols, "f32"))
+        x.bcast_add_rowsum_batch([], [], [], rows, cols, cols)  # an empty batch is a no-op
+    finally:
+        x.close()

@@ -49,7 +49,7 @@ def test_cpp_checks_under_address_and_undefined_behaviour_sanitizers(tmp_path):
                                "support/tiling_schema.cpp")]
     objs = [str(o) for o in sorted((ROOT / "ascend_mlir_b200" / "build").glob("*.o"))
             if (o.name.startswith("kernels_") and o.name != "kernels_body_match.cpp.o")
-            or o.name in ("runtime_executor.cpp.o", "runtime_launcher.cpp.o", "runtime_device_module.cpp.o")]
+            or o.name in ("runtime_executor.cpp.o", "runtime_launcher.cpp.o", "runtime_device_module.cpp.o", "runtime_host_staging.cpp.o")]
     env = {**os.environ, "ASAN_OPTIONS": "detect_leaks=1:abort_on_error=0", "UBSAN_OPTIONS": "print_stacktrace=1"}
     flags = ["-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-I", str(csrc),
              "-I", str(ROOT / "include"), "-I", "/usr/local/cuda/include"]
