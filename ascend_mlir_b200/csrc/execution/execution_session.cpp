@@ -1,5 +1,7 @@
 #include "execution/execution_session.h"
 
+#include <cstring>
+
 #include <sys/stat.h>
 #include <unistd.h>
 
@@ -95,6 +97,37 @@ public:
     // ---- artifact ----
     std::vector<uint8_t> binary;
     if (Status s = readFileBytes(task.artifact.deviceBinaryPath, binary); !s) return s.withStage("cuda:artifact");
+
+    // A tiling given as schema + named params is packed in the KERNEL's field order when the schema is not the
+    // kernel's own: a manifest written for the reference's kernel names that kernel's tile parameters (TB_M, Tb_N,
+    // ...: loop tile sizes this target has no use for) beside the dims; the dims are taken by name, launch
+    // parameters the manifest does not mention keep their defaults (0 = the library chooses), anything else is ignored.
+    if (inv.tiling.present && inv.tiling.binaryPath.empty() && !inv.tiling.schemaPath.empty()) {
+      LaunchDescriptor desc;
+      if (Status s = parseDescriptorBinary(binary.data(), binary.size(), desc); !s) return s.withStage("cuda:artifact");
+      TilingSchema schema;
+      bool same = TilingSchema::fromJsonFile(inv.tiling.schemaPath, schema) && schema.fields().size() == desc.tiling.size();
+      for (size_t i = 0; same && i < desc.tiling.size(); ++i) same = schema.fields()[i].name == desc.tiling[i].name;
+      if (!same) {
+        std::map<std::string, int64_t> named;
+        if (Status s = parseNamedTilingParams(inv.tiling.params, named); !s) return s.withStage("cuda:bindings");
+        tiling.clear();
+        for (const TilingField &f : desc.tiling) {
+          auto it = named.find(f.name);
+          if (it == named.end() && f.name.compare(0, 7, "dim_arg") == 0)
+            return Status::error("[cuda:bindings] tiling params missing field: " + f.name + " (a dimension of kernel '" + desc.kernel + "')");
+          const int64_t v = it == named.end() ? 0 : it->second;
+          uint8_t buf[8];
+          if (f.bytes == 4) {
+            const int32_t w = static_cast<int32_t>(v);
+            std::memcpy(buf, &w, 4);
+          } else {
+            std::memcpy(buf, &v, 8);
+          }
+          tiling.insert(tiling.end(), buf, buf + f.bytes);
+        }
+      }
+    }
 
     // ---- launch ----
     ExecutorLease executor_(*this);

@@ -183,3 +183,69 @@ def test_autotuner_searches_tile_parameters(tmp_path):
     r = tool("autotuner", "--space", tmp_path / "tiling_space.json", "--inputs", f"{tmp_path / 'x.npy'},{tmp_path / 'bias.npy'}",
              "--expected", tmp_path / "expected.npy", "--shape", "B=8,R=256,C2=1024,C=256,BIAS=256")
     assert r.returncode == 1 and "FAIL" in r.stdout and "no candidate passed validation" in r.stderr
+
+
+def test_reference_style_script_runs_from_mlir_to_a_validated_result(tmp_path):
+    """The stage sequence of the reference's examples/*/run.sh, stages 0 to 10, with only the tool paths changed:
+    its stage names on afir-opt, `afir-translate -mlir-to-cann` writing step8_kernel.cpp, `runtime-session --kernel
+    step8_kernel.cpp --kernel-kind vec` compiling that source, and a run manifest written for the reference's
+    kernel -- backend "sim", a hand-kept tiling_space.json that names the schedule's tile sizes (which this target
+    has no use for) beside the dims, a fixed block_dim -- executed and validated."""
+    examples = ROOT / "ascend_mlir_b200" / "examples"
+    stages = [[], ["--linalg-fuse-elementwise-ops"], ["--transform-interpreter", "--canonicalize", "--cse"],
+              ["--one-shot-bufferize=bufferize-function-boundaries=true allow-return-allocs-from-loops=true", "--cse"],
+              ["--ascendc-buffer-placement"], ["--linalg-to-ascendc", "--canonicalize", "--cse"],
+              ["--ascendc-parallelize", "--canonicalize", "--cse"], ["--ascendc-prepare-for-emit", "--canonicalize", "--cse"],
+              ["--canonicalize-cann-signature"]]
+    src = examples / "broadcast_add_reduce_scheduled.mlir"
+    for i, flags in enumerate(stages):
+        dst = tmp_path / f"step{i}.mlir"
+        r = tool("afir-opt", *flags, src, "-o", dst)
+        assert r.returncode == 0, r.stderr
+        src = dst
+    kernel_cpp = tmp_path / "step8_kernel.cpp"
+    r = tool("afir-translate", "-mlir-to-cann", src, "-o", kernel_cpp)
+    assert r.returncode == 0, r.stderr
+    name = "broadcast_add_reduce_scheduled"
+    r = tool("runtime-session", "--kernel", kernel_cpp, "--kernel-kind", "vec", "--output", tmp_path / "artifact", "--name", name)
+    assert r.returncode == 0, r.stderr
+    manifest_txt = dict(l.split("=", 1) for l in (tmp_path / "artifact" / "manifest.txt").read_text().splitlines())
+    assert manifest_txt["codegen"] == "generated"
+
+    M, N = 640, 512
+    rng = np.random.default_rng(42)
+    a = rng.uniform(-1, 1, M).astype(np.float32)
+    b = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+    np.save(tmp_path / "input_a.npy", a)
+    np.save(tmp_path / "input_b.npy", b)
+    np.save(tmp_path / "output_c.npy", oracle.bcast_add_rowsum_f32(a, b))
+    # the reference keeps this file by hand next to the example: tile sizes of ITS kernel, then dims under its names
+    (tmp_path / "tiling_space.json").write_text(json.dumps({
+        "kernel": name, "kernel_file": "step8_kernel.cpp", "soc": "Ascend910B1", "block_dim_expr": "ceil(M / TB_M)",
+        "tiling_params": [{"name": "TB_M", "type": "int64", "min": 16, "max": 16, "step": 16},
+                          {"name": "TB_N", "type": "int64", "values": [16]}, {"name": "Tb_M", "type": "int64", "values": [512]},
+                          {"name": "dim_arg0_0", "type": "int64", "fixed": True, "shape_key": "M"},
+                          {"name": "dim_arg1_1", "type": "int64", "fixed": True, "shape_key": "N"},
+                          {"name": "dim_arg1_0", "type": "int64", "fixed": True, "shape_key": "M"}]}))
+    run_manifest = tmp_path / "run_manifest.json"
+    run_manifest.write_text(json.dumps({
+        "task_id": "main", "backend": "sim", "artifact_root": str(tmp_path / "artifact"),
+        "inputs": [{"name": "a", "path": str(tmp_path / "input_a.npy")}, {"name": "b", "path": str(tmp_path / "input_b.npy")}],
+        "outputs": [{"name": "out", "path": str(tmp_path / "output.npy")}],
+        "expected_outputs": [{"name": "out", "path": str(tmp_path / "output_c.npy")}],
+        "tiling": {"schema": str(tmp_path / "tiling_space.json"),
+                   "params": f"TB_M=16,TB_N=16,Tb_M=512,dim_arg0_0={M},dim_arg1_1={N},dim_arg1_0={M}"},
+        "block_dim": 40, "workspace_size": 16777216, "profiling": True, "atol": 1e-3, "rtol": 1e-5}))
+    r = tool("runtime-session", "--run-manifest", run_manifest, "--run")
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = r.stdout.splitlines()
+    assert "session.backend=sim" in lines and "session.result=success" in lines and "session.validation=pass" in lines
+    got = np.load(tmp_path / "output.npy")
+    _, s64, abs64 = oracle.bcast_add_rowsum_f32(a, b, with_bounds=True)
+    assert np.all(np.abs(got - s64) <= 1e-5 * abs64)
+    # a dim the kernel needs and the manifest does not give is an error that names it
+    bad = json.loads(run_manifest.read_text())
+    bad["tiling"]["params"] = f"TB_M=16,TB_N=16,Tb_M=512,dim_arg0_0={M},dim_arg1_0={M}"
+    (tmp_path / "bad_manifest.json").write_text(json.dumps(bad))
+    r = tool("runtime-session", "--run-manifest", tmp_path / "bad_manifest.json", "--run")
+    assert r.returncode != 0 and "dim_arg1_1" in (r.stdout + r.stderr)
