@@ -203,7 +203,8 @@ std::string signature(const LaunchDescriptor &d, const std::string &entry, const
 }
 
 std::string rowWindowPrologue() {
-  return "  if (t.afir_row_end >= 0 && t.afir_row_end <= t.afir_row_begin) return;  // empty row window\n"
+  return "  gridDependencyPrologue();\n"
+         "  if (t.afir_row_end >= 0 && t.afir_row_end <= t.afir_row_begin) return;  // empty row window\n"
          "  const long long rowb = t.afir_row_end >= 0 ? t.afir_row_begin : 0;\n"
          "  (void)workspace; (void)rowb;\n";
 }
@@ -228,7 +229,9 @@ std::string aligned16(const std::string &ptr) { return "((reinterpret_cast<unsig
 
 const char *kPreamble =
     "// Generated for one fused group; the loops are the function templates of kernels/*_skel.cuh.\n"
-    "using namespace afir::kernels;\n\n";
+    "using namespace afir::kernels;\n\n"
+    "// Tells the runtime that every kernel of this module begins with gridDependencyPrologue().\n"
+    "extern \"C\" __global__ void afir_waits_for_grid_dependencies() {}\n\n";
 
 // ---- elementwise / broadcast / split / concat ------------------------------------------------------------------------
 bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t index, const TypeInfo &ti, std::ostringstream &bodies,

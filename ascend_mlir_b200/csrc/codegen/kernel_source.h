@@ -50,5 +50,10 @@ struct GeneratedKernel {
 
 GeneratedKernel generateKernelSource(const LaunchDescriptor &d);
 
+// An empty kernel of this name is in every generated module whose kernels start with gridDependencyPrologue()
+// (kernels/ew_common.cuh); the runtime launches only such modules with programmatic stream serialisation, so a
+// device binary from before that convention keeps the ordinary launch.
+constexpr const char *kGridDependencyMarker = "afir_waits_for_grid_dependencies";
+
 } // namespace codegen
 } // namespace afir

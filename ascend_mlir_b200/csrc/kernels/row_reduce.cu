@@ -10,6 +10,7 @@
 #include "kernels/row_reduce_skel.cuh"
 
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <mutex>
 
@@ -207,7 +208,13 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
     sp.status = l.status ? l.status : libraryStatusWord();
     if (!sp.status) return cudaErrorInvalidValue;
     sp.prog = l.body;
-    if (l.exchange) sp.xchg = *l.exchange;
+    if (l.exchange) {
+      sp.xchg = *l.exchange;
+      // A row's entries need a store over NVLink and a poll of the local mailbox, about 4 us together, before they
+      // can be read without waiting; a warp spends warps x rowBytes / (the SM's share of HBM, ~44 bytes/ns) on a row.
+      const double rowNs = static_cast<double>(plan.streamWarps) * sp.rowBytes / 44.0;
+      sp.finishLag = static_cast<int>(std::min(32.0, std::max(1.0, std::ceil(4000.0 / std::max(rowNs, 1.0)))));
+    }
     using StreamFn = void (*)(const RrStreamParams);
     StreamFn sfn = nullptr;
     if (l.elemType == kF32) sfn = body == kBodyAdd ? rowReduceStreamKernel<PackF32, kBodyAdd> : body == kBodyCopy ? rowReduceStreamKernel<PackF32, kBodyCopy> : body == kBodyMul ? rowReduceStreamKernel<PackF32, kBodyMul> : rowReduceStreamKernel<PackF32, kBodyInterpreted>;

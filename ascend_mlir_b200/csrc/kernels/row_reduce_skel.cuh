@@ -46,17 +46,26 @@ template <> __device__ __forceinline__ void storeSum<PackBF16>(void *out, long l
 // arrived" travel together and a reader never sees half an entry: no flags, no fences.  Each row's partial sum
 // is stored into every rank's mailbox (plain stores over NVLink; the own mailbox is a local store).  A reader
 // polls an entry until its epoch is the call's, then adds the world's partial sums in rank order, so all ranks
-// produce the same bits.  Who reads: in the persistent staged kernel the warp that sent a row reads that row
-// one row later (the NVLink latency hides behind the next row's stream; every rank walks its rows in the same
-// order and always sends before it reads, so no rank waits for something that itself waits); in the plain
-// kernel, whose CTAs need not all be resident, the last CTA to finish reads all rows.  Every wait is bounded:
-// after 2 s the status word is set, the remaining rows stay unwritten and the context remains usable.
+// produce the same bits.  Who reads: in the persistent staged kernel the warp that sent a row reads it several
+// rows later, a group of rows at a time with one lane per (row, rank) entry, so that neither the NVLink latency
+// nor the round trip of a poll stands between two rows of its stream (every rank walks its rows in the same
+// order and a send never waits, so no rank waits for something that itself waits); in the plain kernel, whose
+// CTAs need not all be resident, the last CTA to finish reads all rows.  Every wait is bounded: after 2 s the
+// status word is set, the remaining rows stay unwritten and the context remains usable.
 constexpr unsigned long long kExchangeWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ void sendPartial(const RowReduceExchange &x, long long row, float v) {
   const unsigned long long entry = (static_cast<unsigned long long>(x.epoch) << 32) | __float_as_uint(v);
   for (int p = 0; p < x.world; ++p)
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(x.peerEntries[p] + row), "l"(entry) : "memory");
+}
+
+// The same by a whole warp: lane p stores to rank p, so the stores leave together (v is lane 0's).
+__device__ __forceinline__ void sendPartialByWarp(const RowReduceExchange &x, long long row, float v, int lane) {
+  v = __shfl_sync(0xffffffffu, v, 0);
+  const unsigned long long entry = (static_cast<unsigned long long>(x.epoch) << 32) | __float_as_uint(v);
+  if (lane < x.world)
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(x.peerEntries[lane] + row), "l"(entry) : "memory");
 }
 
 __device__ __forceinline__ unsigned long long peekEntry(const unsigned long long *entry) {
@@ -82,15 +91,20 @@ __device__ __forceinline__ bool awaitEntry(const unsigned long long *entry, unsi
   }
 }
 
-// One warp finishes one row: lane p fetches rank p's partial sum, all lanes add them in rank order.
-template <class P> __device__ __forceinline__ bool finishRowByWarp(const RowReduceExchange &x, void *out, long long row, int lane) {
+// One warp finishes up to 32 / world rows at once: rows first, first + step, ...; lane slot * world + p fetches
+// rank p's partial sum of row `slot`, the slot's first lane adds them in rank order and stores the sum.
+template <class P>
+__device__ __forceinline__ bool finishRowsByWarp(const RowReduceExchange &x, void *out, long long first, long long step, int count, int lane) {
+  const int slot = lane / x.world, p = lane - slot * x.world;
+  const bool mine = slot < count;
+  const long long row = first + slot * step;
   unsigned long long w = 0;
   bool ok = true;
-  if (lane < x.world) ok = awaitEntry(x.myEntries + lane * x.slotStride + row, x.epoch, w);
+  if (mine) ok = awaitEntry(x.myEntries + p * x.slotStride + row, x.epoch, w);
   ok = __all_sync(0xffffffffu, ok) != 0;
   float t = 0.f;
-  for (int p = 0; p < x.world; ++p) t += __uint_as_float(__shfl_sync(0xffffffffu, static_cast<unsigned int>(w), p));
-  if (ok && lane == 0) storeSum<P>(out, row, t);
+  for (int q = 0; q < x.world; ++q) t += __uint_as_float(__shfl_sync(0xffffffffu, static_cast<unsigned int>(w), (lane + q) & 31));
+  if (ok && mine && p == 0) storeSum<P>(out, row, t);
   return ok;
 }
 
@@ -282,6 +296,7 @@ struct RrStreamParams {
   unsigned int *status;          // set to 1 when a wait for a staged copy ran out
   BodyProgram prog;
   RowReduceExchange xchg;        // world > 0: the sums are partial and go to every rank's mailbox
+  int finishLag;                 // exchange: rows a warp streams on after sending one before it reads that row's entries
 };
 
 __device__ __forceinline__ unsigned int smemU32(const void *p) { return static_cast<unsigned int>(__cvta_generic_to_shared(p)); }
@@ -339,7 +354,9 @@ __device__ __forceinline__ void rowReduceStream(const RrStreamParams &prm, unsig
   unsigned int phase = 0;
   unsigned int bcastNow[NV], bcastNext[NV];
   loadBcast(firstRow, bcastNow);
-  long long sentRow = -1;  // exchange: the row this warp has sent but not yet finished
+  long long pendFirst = firstRow;  // exchange: the oldest row this warp has sent but not yet finished ...
+  int pending = 0;                 // ... and how many such rows there are (rows pendFirst, pendFirst + totalWarps, ...)
+  const int finishGroup = XCHG ? 32 / max(prm.xchg.world, 1) : 1;
   bool peersAnswer = true;  // exchange: false once a wait for another rank ran out (the warp then only drains its stream)
   for (long long row = firstRow; row < prm.rows; row += totalWarps) {
     loadBcast(row + totalWarps, bcastNext);  // one row ahead: its latency hides behind this row's stream
@@ -406,9 +423,13 @@ __device__ __forceinline__ void rowReduceStream(const RrStreamParams &prm, unsig
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
     if constexpr (XCHG) {
-      if (lane == 0) sendPartial(prm.xchg, row, sum);
-      if (sentRow >= 0 && peersAnswer) peersAnswer = finishRowByWarp<P>(prm.xchg, prm.out, sentRow, lane);
-      sentRow = row;
+      sendPartialByWarp(prm.xchg, row, sum, lane);
+      ++pending;
+      if (pending >= finishGroup + prm.finishLag) {  // the oldest group has had finishLag rows' time to arrive
+        if (peersAnswer) peersAnswer = finishRowsByWarp<P>(prm.xchg, prm.out, pendFirst, totalWarps, finishGroup, lane);
+        pendFirst += finishGroup * totalWarps;
+        pending -= finishGroup;
+      }
     } else {
       if (lane == 0) storeSum<P>(prm.out, row, sum);
     }
@@ -416,7 +437,8 @@ __device__ __forceinline__ void rowReduceStream(const RrStreamParams &prm, unsig
     for (int k = 0; k < NV; ++k) bcastNow[k] = bcastNext[k];
   }
   if constexpr (XCHG) {
-    if (sentRow >= 0 && peersAnswer) peersAnswer = finishRowByWarp<P>(prm.xchg, prm.out, sentRow, lane);
+    for (; pending > 0; pending -= finishGroup, pendFirst += finishGroup * totalWarps)
+      if (peersAnswer) peersAnswer = finishRowsByWarp<P>(prm.xchg, prm.out, pendFirst, totalWarps, min(pending, finishGroup), lane);
     if (!peersAnswer && lane == 0) atomicExch(prm.xchg.status, 1u);
   }
 }

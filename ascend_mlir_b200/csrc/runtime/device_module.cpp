@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime_api.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace afir {
@@ -14,6 +15,8 @@ struct DriverApi {
   decltype(&cuModuleUnload) moduleUnload = nullptr;
   decltype(&cuModuleGetFunction) moduleGetFunction = nullptr;
   decltype(&cuLaunchKernel) launchKernel = nullptr;
+  decltype(&cuLaunchKernelEx) launchKernelEx = nullptr;  // optional: programmatic dependent launch
+  bool dependentLaunch = false;
   decltype(&cuFuncSetAttribute) funcSetAttribute = nullptr;
   decltype(&cuGetErrorString) getErrorString = nullptr;
 };
@@ -38,6 +41,13 @@ const DriverApi &driver() {
     resolve("cuLaunchKernel", d.launchKernel);
     resolve("cuFuncSetAttribute", d.funcSetAttribute);
     resolve("cuGetErrorString", d.getErrorString);
+    {  // optional entry point: its absence only turns programmatic dependent launch off
+      const std::string keep = d.reason;
+      resolve("cuLaunchKernelEx", d.launchKernelEx);
+      d.reason = keep;
+      const char *pdl = std::getenv("AFIR_CUDA_PDL");
+      d.dependentLaunch = d.launchKernelEx != nullptr && !(pdl && pdl[0] == '0');
+    }
   });
   return d;
 }
@@ -96,9 +106,26 @@ Status DeviceModule::reserveDynamicSharedMemory(void *fn, int bytes) {
 }
 
 Status launchDeviceFunction(void *fn, unsigned int grid, unsigned int block, size_t dynamicSmemBytes, cudaStream_t stream,
-                            void **params) {
+                            void **params, bool waitsForDependencies) {
   const DriverApi &d = driver();
   if (!d.reason.empty()) return Status::error(d.reason);
+  if (d.dependentLaunch && waitsForDependencies) {
+    // Generated kernels begin with gridDependencyPrologue(): launched with programmatic stream serialisation their
+    // CTAs are scheduled while the previous kernel of the stream drains, and wait there for it to complete.
+    CUlaunchAttribute attr;
+    attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attr.value.programmaticStreamSerializationAllowed = 1;
+    CUlaunchConfig cfg = {};
+    cfg.gridDimX = grid; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = block; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = static_cast<unsigned int>(dynamicSmemBytes);
+    cfg.hStream = reinterpret_cast<CUstream>(stream);
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const CUresult r = d.launchKernelEx(&cfg, static_cast<CUfunction>(fn), params, nullptr);
+    if (r != CUDA_SUCCESS) return driverError(d, r, "cuLaunchKernelEx");
+    return Status::success();
+  }
   const CUresult r = d.launchKernel(static_cast<CUfunction>(fn), grid, 1, 1, block, 1, 1, static_cast<unsigned int>(dynamicSmemBytes),
                                     reinterpret_cast<CUstream>(stream), params, nullptr);
   if (r != CUDA_SUCCESS) return driverError(d, r, "cuLaunchKernel");

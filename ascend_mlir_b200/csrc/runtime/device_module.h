@@ -39,7 +39,9 @@ private:
 };
 
 // cuLaunchKernel: a 1-D grid of `grid` CTAs of `block` threads; params[i] points at the i-th kernel argument.
+// `waitsForDependencies`: the kernel begins with gridDependencyPrologue(), so it may be launched with programmatic
+// stream serialisation (cuLaunchKernelEx; AFIR_CUDA_PDL=0 turns that off) and start up under the previous kernel's tail.
 Status launchDeviceFunction(void *fn, unsigned int grid, unsigned int block, size_t dynamicSmemBytes, cudaStream_t stream,
-                            void **params);
+                            void **params, bool waitsForDependencies = false);
 
 } // namespace afir

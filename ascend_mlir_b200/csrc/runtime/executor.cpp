@@ -273,6 +273,8 @@ bool CudaExecutor::prepareGenerated(CachedKernel &kernel) {
     if (!kernel.binding.module->function(d.kernel + "__staged", kernel.binding.stagedFn)) kernel.binding.stagedFn = nullptr;
     if (!kernel.binding.module->function(d.kernel + "__finalize", kernel.binding.finalizeFn)) kernel.binding.finalizeFn = nullptr;
   }
+  void *marker = nullptr;  // present in modules whose kernels wait for their grid dependencies themselves
+  kernel.binding.waitsForDependencies = static_cast<bool>(kernel.binding.module->function(codegen::kGridDependencyMarker, marker));
   kernel.generatedUsable = true;
   return true;
 }

@@ -660,7 +660,7 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
     if (totalElems == 0) return Status::success();
     int64_t grid = args.blockDim > 0 ? std::min<int64_t>(args.blockDim, tiles) : tiles;
     grid = std::max<int64_t>(1, std::min<int64_t>(grid, 0x7fffffff));
-    if (Status s = launchDeviceFunction(binding.mainFn, static_cast<unsigned int>(grid), static_cast<unsigned int>(threads), 0, args.stream, ga.finish()); !s)
+    if (Status s = launchDeviceFunction(binding.mainFn, static_cast<unsigned int>(grid), static_cast<unsigned int>(threads), 0, args.stream, ga.finish(), binding.waitsForDependencies); !s)
       return s;
     info.kernelsLaunched = 1;
     return Status::success();
@@ -680,7 +680,7 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
       ga.setPlan(1, plan.streamChunkBytes);
       if (Status s = binding.module->reserveDynamicSharedMemory(binding.stagedFn, static_cast<int>(plan.smemBytes)); !s) return s;
       if (Status s = launchDeviceFunction(binding.stagedFn, static_cast<unsigned int>(plan.grid), static_cast<unsigned int>(plan.threads),
-                                          plan.smemBytes, args.stream, ga.finish()); !s)
+                                          plan.smemBytes, args.stream, ga.finish(), binding.waitsForDependencies); !s)
         return s;
       info.kernelsLaunched = 1;
       return Status::success();
@@ -695,13 +695,13 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
     ga.setPlan(2, plan.vecPerSlice);
     ga.setPlan(3, plan.lanes);
     if (Status s = launchDeviceFunction(binding.mainFn, static_cast<unsigned int>(plan.grid), static_cast<unsigned int>(plan.threads), 0,
-                                        args.stream, ga.finish()); !s)
+                                        args.stream, ga.finish(), binding.waitsForDependencies); !s)
       return s;
     info.kernelsLaunched = 1;
     if (plan.slices > 1) {
       if (!binding.finalizeFn) return Status::error("kernel '" + d.kernel + "' has no finalize entry for its column slices");
       if (Status s = launchDeviceFunction(binding.finalizeFn, static_cast<unsigned int>(plan.finalizeGrid),
-                                          static_cast<unsigned int>(plan.finalizeThreads), 0, args.stream, ga.finish()); !s)
+                                          static_cast<unsigned int>(plan.finalizeThreads), 0, args.stream, ga.finish(), binding.waitsForDependencies); !s)
         return s;
       info.kernelsLaunched = 2;
     }
@@ -734,7 +734,7 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
     const int64_t tiles = (l.rows * vecPerRow + tileVecs - 1) / tileVecs;
     int64_t grid = args.blockDim > 0 ? std::min<int64_t>(args.blockDim, tiles) : tiles;
     grid = std::max<int64_t>(1, std::min<int64_t>(grid, 0x7fffffff));
-    if (Status s = launchDeviceFunction(binding.mainFn, static_cast<unsigned int>(grid), static_cast<unsigned int>(threads), 0, args.stream, ga.finish()); !s)
+    if (Status s = launchDeviceFunction(binding.mainFn, static_cast<unsigned int>(grid), static_cast<unsigned int>(threads), 0, args.stream, ga.finish(), binding.waitsForDependencies); !s)
       return s;
     info.kernelsLaunched = 1;
     return Status::success();

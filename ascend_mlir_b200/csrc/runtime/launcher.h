@@ -76,6 +76,7 @@ struct GeneratedBinding {
   void *mainFn = nullptr;      // <kernel>
   void *stagedFn = nullptr;    // <kernel>__staged (row reductions with one streamed view), or null
   void *finalizeFn = nullptr;  // <kernel>__finalize (row reductions), or null
+  bool waitsForDependencies = false;  // every entry begins with gridDependencyPrologue() (the module says so by a marker kernel)
 };
 
 // True when this launch can run on the descriptor's generated kernel: the features the generated code does not

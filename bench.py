@@ -660,6 +660,7 @@ def run_gpu_arm(args):
 
     # Strong scaling of the stated configurations: ONE full-size problem cut into contiguous row shards.
     if world > 1 and args.all_groups:
+        floor_us = None
         for name in configs.CONFIGS:
             rec = results.get(name)
             if not isinstance(rec, dict) or "error" in rec:
@@ -672,11 +673,19 @@ def run_gpu_arm(args):
                 # more than every timed region of this run together)
                 full = weak_workloads[name]
                 mine = full.shard(rank, world)
-                g = DeviceGroup(torch, rt, mine, device, stream, args.buffer_sets, pinned=False)
+                # a shard is small: rotate enough buffer sets that a step's memory was last used >= 2 x L2 of traffic ago
+                touched = sum(x.nbytes for x in mine.inputs) + int(np.prod(mine.out_shape)) * mine.out_dtype.itemsize
+                n_sets = int(min(12, max(args.buffer_sets, -(-2 * 126_000_000 // max(touched, 1)))))
+                g = DeviceGroup(torch, rt, mine, device, stream, n_sets, pinned=False)
                 steps = max(20, min(args.steps, 200))
                 ms, _ = g.timed(steps, args.warmup, sync, use_graph=not args.no_graph)
                 del g
                 torch.cuda.empty_cache()
+                if floor_us is None:  # what one more launch in a replayed graph costs when it moves almost nothing
+                    tiny = DeviceGroup(torch, rt, configs.elementwise_chain(8, 1024), device, stream, 1, pinned=False)
+                    floor_ms, _ = tiny.timed(200, args.warmup, sync, use_graph=not args.no_graph)
+                    floor_us = floor_ms * 1e3
+                    del tiny
             except Exception as e:
                 error = f"{type(e).__name__}: {e}"
             if not all_ranks(error is None):
@@ -687,7 +696,8 @@ def run_gpu_arm(args):
             value = work / (ms * 1e-3) / scale
             single = rec["value"] / world  # this run's per-GPU figure on a full-size batch
             rec["strong"] = {"value": value, "unit": unit, "ms_per_step": ms, "scaling": "strong",
-                             "rows_per_gpu": mine.units, "total_work_per_step": work,
+                             "rows_per_gpu": mine.units, "total_work_per_step": work, "buffer_sets": n_sets,
+                             "launch_floor_us": floor_us,
                              "per_gpu": value / world, "per_gpu_frac_of_full_batch_rate": (value / world) / single,
                              "sharding": "contiguous row shards of one full-size configuration, no collective (rank r times "
                                          "shard r; table, B and bias replicated)"}

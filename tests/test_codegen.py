@@ -139,7 +139,9 @@ def test_multi_group_descriptor_is_one_kernel(tmp_path):
     """Split rows / concat: two groups writing the two halves of one output become two blocks of one kernel."""
     _, cubin, src = compiled(tmp_path, descriptors.split_rows_relu_bias_scale())
     assert cubin[:4] == b"\x7fELF"
-    assert src.count('extern "C" __global__') == 1
+    # one kernel for all groups, beside the empty marker kernel that says "these kernels wait for their grid dependencies"
+    assert src.count('extern "C" __global__') == 2 and 'void afir_waits_for_grid_dependencies() {}' in src
+    assert src.count("gridDependencyPrologue();") == 1
     assert "// group 0" in src and "// group 1" in src and "FusedBody1" in src
     # the second half starts dim_arg1_0 rows into argument 0 and argument 5
     assert "(t.dim_arg1_0) * (t.dim_arg0_1)" in src
