@@ -38,7 +38,7 @@ CU_SOURCES = {
     "kernels/matmul_tcgen05.cu": [],
 }
 CPP_SOURCES = ["common/json.cpp", "kernels/matmul_plan.cpp", "kernels/body_match.cpp", "codegen/kernel_source.cpp",
-               "codegen/nvrtc_compile.cpp", "codegen/embedded_headers.cpp", "runtime/device_module.cpp", "runtime/host_staging.cpp", "runtime/descriptor.cpp", "runtime/launcher.cpp", "runtime/executor.cpp",
+               "codegen/nvrtc_compile.cpp", "codegen/embedded_headers.cpp", "runtime/device_module.cpp", "runtime/caller_device.cpp", "runtime/host_staging.cpp", "runtime/descriptor.cpp", "runtime/launcher.cpp", "runtime/executor.cpp",
                "support/npy_io.cpp", "support/tiling_schema.cpp", "execution/output_comparator.cpp",
                "execution/task_graph.cpp", "execution/run_manifest.cpp", "execution/artifact_compiler.cpp",
                "execution/execution_session.cpp", "execution/resource_scheduler.cpp", "execution/global_scheduler.cpp",

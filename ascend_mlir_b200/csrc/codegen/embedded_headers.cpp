@@ -14,6 +14,7 @@
   extern "C" const char symbol##_end[];
 
 AFIR_EMBED(afir_hdr_kernels, "kernels/kernels.h")
+AFIR_EMBED(afir_hdr_grid_dependency, "kernels/grid_dependency.cuh")
 AFIR_EMBED(afir_hdr_ew_common, "kernels/ew_common.cuh")
 AFIR_EMBED(afir_hdr_elementwise_skel, "kernels/elementwise_skel.cuh")
 AFIR_EMBED(afir_hdr_row_reduce_skel, "kernels/row_reduce_skel.cuh")
@@ -25,6 +26,7 @@ namespace codegen {
 const std::vector<EmbeddedHeader> &embeddedHeaders() {
   static const std::vector<EmbeddedHeader> headers = {
       {"kernels/kernels.h", afir_hdr_kernels_begin, afir_hdr_kernels_end},
+      {"kernels/grid_dependency.cuh", afir_hdr_grid_dependency_begin, afir_hdr_grid_dependency_end},
       {"kernels/ew_common.cuh", afir_hdr_ew_common_begin, afir_hdr_ew_common_end},
       {"kernels/elementwise_skel.cuh", afir_hdr_elementwise_skel_begin, afir_hdr_elementwise_skel_end},
       {"kernels/row_reduce_skel.cuh", afir_hdr_row_reduce_skel_begin, afir_hdr_row_reduce_skel_end},

@@ -202,8 +202,11 @@ std::string signature(const LaunchDescriptor &d, const std::string &entry, const
   return os.str();
 }
 
-std::string rowWindowPrologue() {
-  return "  gridDependencyPrologue();\n"
+// `dependent`: the kernel starts with gridDependencyPrologue() and its module carries the marker kernel, so the
+// runtime launches it with programmatic stream serialisation.  Gather kernels do not: with one short CTA per tile
+// the prologue's two instructions, executed by every CTA, were measured to cost more than the overlap gains.
+std::string rowWindowPrologue(bool dependent = true) {
+  return std::string(dependent ? "  gridDependencyPrologue();\n" : "") +
          "  if (t.afir_row_end >= 0 && t.afir_row_end <= t.afir_row_begin) return;  // empty row window\n"
          "  const long long rowb = t.afir_row_end >= 0 ? t.afir_row_begin : 0;\n"
          "  (void)workspace; (void)rowb;\n";
@@ -229,7 +232,8 @@ std::string aligned16(const std::string &ptr) { return "((reinterpret_cast<unsig
 
 const char *kPreamble =
     "// Generated for one fused group; the loops are the function templates of kernels/*_skel.cuh.\n"
-    "using namespace afir::kernels;\n\n"
+    "using namespace afir::kernels;\n\n";
+const char *kDependencyMarker =
     "// Tells the runtime that every kernel of this module begins with gridDependencyPrologue().\n"
     "extern \"C\" __global__ void afir_waits_for_grid_dependencies() {}\n\n";
 
@@ -313,7 +317,7 @@ GeneratedKernel generateElementwise(const LaunchDescriptor &d) {
   for (size_t i = 0; i < d.groups.size(); ++i)
     if (!emitElementwiseGroup(d, d.groups[i], i, ti, bodies, kernel, out.whyNot)) return out;
   std::ostringstream src;
-  src << "#include \"kernels/elementwise_skel.cuh\"\n" << kPreamble << tilingStruct(d) << "\n" << bodies.str()
+  src << "#include \"kernels/elementwise_skel.cuh\"\n" << kPreamble << kDependencyMarker << tilingStruct(d) << "\n" << bodies.str()
       << signature(d, d.kernel, "__launch_bounds__(512)") << " {\n" << rowWindowPrologue() << kernel.str() << "}\n";
   out.source = src.str();
   out.entry = d.kernel;
@@ -364,7 +368,7 @@ GeneratedKernel generateRowReduce(const LaunchDescriptor &d) {
   const int ve = 16 / ti.bytes;
 
   std::ostringstream src;
-  src << "#include \"kernels/row_reduce_skel.cuh\"\n" << kPreamble << tilingStruct(d) << "\n"
+  src << "#include \"kernels/row_reduce_skel.cuh\"\n" << kPreamble << kDependencyMarker << tilingStruct(d) << "\n"
       << bodyStruct("FusedBody0", g.body, static_cast<int>(g.loads.size()), false) << "\n";
 
   // entry 1: one team of lanes per row (and per column slice), plain loads
@@ -456,7 +460,7 @@ GeneratedKernel generateGatherRows(const LaunchDescriptor &d) {
   std::ostringstream src;
   src << "#include \"kernels/gather_skel.cuh\"\n" << kPreamble << tilingStruct(d) << "\n"
       << bodyStruct("FusedBody0", g.body, static_cast<int>(g.loads.size()), false) << "\n"
-      << signature(d, d.kernel, "__launch_bounds__(512)") << " {\n" << rowWindowPrologue() << "  {\n" << rowsDecl(g.domain[0]);
+      << signature(d, d.kernel, "__launch_bounds__(512)") << " {\n" << rowWindowPrologue(false) << "  {\n" << rowsDecl(g.domain[0]);
   src << "    GaParams prm = {};\n"
       << "    prm.table = static_cast<const char *>(arg" << table.arg << ");\n"
       << "    prm.tableRows = " << code(symOf(table.shape[0])) << "; prm.tableCols = " << tcols << "; prm.tableRowStride = " << tcols << ";\n"

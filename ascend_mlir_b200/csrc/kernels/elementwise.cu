@@ -6,6 +6,7 @@
 // once are loaded with the streaming (evict-first) policy, broadcast operands through the read-only
 // path.  No shared memory: there is no reuse to stage.  Arithmetic rounds after every op.
 #include "kernels/elementwise_skel.cuh"
+#include "kernels/launch_util.h"
 #include "kernels/reg_block.cuh"
 
 #include <algorithm>
@@ -17,6 +18,7 @@ namespace {
 
 template <class P, int BODY, int UNROLL, bool VECTOR, bool OUTER = false>
 __global__ void __launch_bounds__(512) elementwiseKernel(const __grid_constant__ EwParams prm) {
+  gridDependencyPrologue();
   elementwiseTiles<P, Body<BODY>, UNROLL, VECTOR, OUTER>(prm);
 }
 
@@ -84,6 +86,7 @@ struct EbParams {
 
 template <class P, int BODY, int NVL>  // NVL = views actually loaded (<= Body::kViews)
 __global__ void __launch_bounds__(256) elementwiseBlocksKernel(const __grid_constant__ EbParams prm) {
+  gridDependencyPrologue();
   using B = Body<BODY>;
   constexpr int NV = B::kViews;
   constexpr int EB = sizeof(typename P::Scalar);
@@ -230,7 +233,7 @@ bool tryLaunchBlocks(const ElementwiseLaunch &l, cudaStream_t stream, cudaError_
   p.prog = l.body;
   unsigned long long grid = l.gridBlocks > 0 ? static_cast<unsigned long long>(l.gridBlocks) : p.numTiles;
   grid = std::max<unsigned long long>(1, std::min<unsigned long long>(std::min(grid, p.numTiles), 1u << 30));
-  fn<<<static_cast<unsigned int>(grid), 256, 0, stream>>>(p);
+  launchDependent(fn, static_cast<unsigned int>(grid), 256, 0, stream, p);
   err = cudaGetLastError();
   return true;
 }
@@ -402,7 +405,7 @@ int launchElementwise(const ElementwiseLaunch &given, cudaStream_t stream, int *
   int64_t grid = l.gridBlocks > 0 ? l.gridBlocks : numTiles;
   grid = std::max<int64_t>(1, std::min<int64_t>(grid, numTiles));
   const dim3 blocks(static_cast<unsigned int>(grid), outerInGrid ? static_cast<unsigned int>(l.outerCount) : 1u);
-  fn<<<blocks, threads, 0, stream>>>(p);
+  launchDependent(fn, blocks, threads, 0, stream, p);
   if (launched) *launched = 1;
   return cudaGetLastError();
 }

@@ -14,6 +14,7 @@
 // 16-byte output vector from scalar loads of the (cache-resident) table row.
 // Indices outside the table raise *status and leave the output untouched; nothing is clamped.
 #include "kernels/gather_skel.cuh"
+#include "kernels/launch_util.h"
 
 #include <algorithm>
 
@@ -509,7 +510,7 @@ int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched) {
         const int64_t groups = (chunks + warps - 1) / warps;
         int64_t sgrid = l.gridBlocks > 0 ? l.gridBlocks : sms;
         sgrid = std::max<int64_t>(1, std::min<int64_t>(sgrid, groups));
-        sfn<<<static_cast<unsigned int>(sgrid), warps * 32, smem, stream>>>(sp);
+        launchOrdinary(sfn, static_cast<unsigned int>(sgrid), warps * 32, smem, stream, sp);
         if (launched) *launched = 1;
         return cudaGetLastError();
       }
@@ -545,7 +546,7 @@ int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched) {
   p.divVpr = makeFastDiv(p.vecPerRow);
   int64_t grid = l.gridBlocks > 0 ? l.gridBlocks : numTiles;
   grid = std::max<int64_t>(1, std::min<int64_t>(grid, numTiles));
-  fn<<<static_cast<unsigned int>(grid), threads, 0, stream>>>(p);
+  launchOrdinary(fn, static_cast<unsigned int>(grid), threads, 0, stream, p);
   if (launched) *launched = 1;
   return cudaGetLastError();
 }

@@ -124,13 +124,18 @@ int launchElementwise(const ElementwiseLaunch &l, cudaStream_t stream, int *laun
 // into GPU p's mailbox (peer-mapped), at the place reserved for this rank.
 constexpr int kMaxExchangeRanks = 8;
 struct RowReduceExchange {
-  unsigned long long *peerEntries[kMaxExchangeRanks];  // where this rank's entries go on rank p: [rows] x {f32 sum, epoch}
-  const unsigned long long *myEntries;                 // local mailbox of this epoch: [world, slotStride] entries, filled by all ranks
-  unsigned int *doneCounter;                           // local: CTAs of this launch that have sent all their rows
+  // The mailbox has two halves used by alternate calls; the pointers below are those of half 0, the kernel adds
+  // halfStride for odd call numbers.  The call number lives on the device (callWord), so that a launch carries
+  // nothing that changes from call to call and a captured CUDA graph of such launches can be replayed.
+  unsigned long long *peerEntries[kMaxExchangeRanks];  // where this rank's entries go on rank p: [rows] x {f32 sum, call number}
+  const unsigned long long *myEntries;                 // local mailbox: [world, slotStride] entries, filled by all ranks
+  unsigned int *doneCounter;                           // local: CTAs of the running launch that are done (plain kernel)
   unsigned int *status;                                // local: set to 1 when the wait for a rank ran out
+  unsigned long long *callWord;                        // local: {completed calls : arrivals of the running launch}, 0 at creation
   int world;                                           // 0 = no exchange
-  unsigned int epoch;                                  // 1, 2, ... identical on every rank for the same call, never 0
+  unsigned int epoch;                                  // device side only: the running call's number (filled in by the kernel)
   long long slotStride;                                // entries between two ranks' slots
+  long long halfStride;                                // entries between the two halves
 };
 
 struct RowReduceLaunch {

@@ -30,6 +30,7 @@
 #include <mutex>
 
 #include "kernels/kernels.h"
+#include "kernels/launch_util.h"
 #include "kernels/matmul_plan.h"
 
 namespace afir {
@@ -797,7 +798,7 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmPa
     fail(errorText, "matmul: cannot reserve shared memory for the operand ring");
     return static_cast<int>(attrErr);
   }
-  kernel<<<grid, S::kThreads, S::kSmemBytes, stream>>>(mapA, mapB, p);
+  launchOrdinary(kernel, grid, S::kThreads, S::kSmemBytes, stream, mapA, mapB, p);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -8,6 +8,7 @@
 // accumulators throughout.  Short-and-wide problems split each row into column slices whose partial
 // sums go to the workspace and are added in slice order by a second kernel (deterministic).
 #include "kernels/row_reduce_skel.cuh"
+#include "kernels/launch_util.h"
 
 #include <algorithm>
 #include <cmath>
@@ -22,17 +23,20 @@ __device__ unsigned int g_rowReduceStatus = 0;  // wait time-outs of launches th
 
 template <class P, int BODY, bool VECTOR, bool XCHG = false>
 __global__ void __launch_bounds__(512) rowReduceKernel(const __grid_constant__ RrParams prm) {
+  gridDependencyPrologue();
   rowReduceTeams<P, Body<BODY>, VECTOR, XCHG>(prm);
 }
 
 template <class P, int BODY, bool XCHG = false>
 __global__ void __launch_bounds__(512, 1) rowReduceStreamKernel(const __grid_constant__ RrStreamParams prm) {
+  gridDependencyPrologue();
   extern __shared__ __align__(128) unsigned char streamSmem[];
   rowReduceStream<P, Body<BODY>, XCHG>(prm, streamSmem);
 }
 
 template <class P>
 __global__ void rowReduceFinalizeKernel(const float *__restrict__ partial, void *out, long long rows, int slices) {
+  gridDependencyPrologue();
   rowReduceFinalize<P>(partial, out, rows, slices);
 }
 
@@ -227,7 +231,7 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
     }
     cudaError_t ae = cudaFuncSetAttribute(sfn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smemBytes));
     if (ae != cudaSuccess) return ae;
-    sfn<<<static_cast<unsigned int>(plan.grid), plan.threads, plan.smemBytes, stream>>>(sp);
+    launchDependent(sfn, static_cast<unsigned int>(plan.grid), plan.threads, plan.smemBytes, stream, sp);
     if (launched) *launched = 1;
     return cudaGetLastError();
   }
@@ -261,15 +265,15 @@ int launchRowReduce(const RowReduceLaunch &l, cudaStream_t stream, int *launched
     else fn = vector ? pickBodyExchange<PackBF16, true>(body) : pickBodyExchange<PackBF16, false>(body);
   }
 
-  fn<<<static_cast<unsigned int>(plan.grid), plan.threads, 0, stream>>>(p);
+  launchDependent(fn, static_cast<unsigned int>(plan.grid), plan.threads, 0, stream, p);
   int n = 1;
   cudaError_t err = cudaGetLastError();
   if (err == cudaSuccess && slices > 1) {
     const int ft = plan.finalizeThreads;
     const unsigned int fg = static_cast<unsigned int>(plan.finalizeGrid);
-    if (l.elemType == kF32) rowReduceFinalizeKernel<PackF32><<<fg, ft, 0, stream>>>(p.partial, l.out, l.rows, slices);
-    else if (l.elemType == kF16) rowReduceFinalizeKernel<PackF16><<<fg, ft, 0, stream>>>(p.partial, l.out, l.rows, slices);
-    else rowReduceFinalizeKernel<PackBF16><<<fg, ft, 0, stream>>>(p.partial, l.out, l.rows, slices);
+    if (l.elemType == kF32) launchDependent(rowReduceFinalizeKernel<PackF32>, fg, ft, 0, stream, p.partial, l.out, l.rows, slices);
+    else if (l.elemType == kF16) launchDependent(rowReduceFinalizeKernel<PackF16>, fg, ft, 0, stream, p.partial, l.out, l.rows, slices);
+    else launchDependent(rowReduceFinalizeKernel<PackBF16>, fg, ft, 0, stream, p.partial, l.out, l.rows, slices);
     n = 2;
     err = cudaGetLastError();
   }

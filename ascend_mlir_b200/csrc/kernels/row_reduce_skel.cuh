@@ -54,6 +54,48 @@ template <> __device__ __forceinline__ void storeSum<PackBF16>(void *out, long l
 // status word is set, the remaining rows stay unwritten and the context remains usable.
 constexpr unsigned long long kExchangeWaitLimitNs = 2000000000ull;
 
+// The call number is kept on the device in one 64-bit word, {completed calls : arrivals of the running launch}.
+// Each CTA of a launch takes a ticket with ONE atomic add (per CTA, not per warp: a thousand warps adding to one
+// word at kernel start were measured to cost over a microsecond).  The high half tells it the running call's
+// number (one more than the completed calls; 0 is skipped, it is what an untouched entry holds, and 2 follows
+// 2^32 - 1 so that the halves keep alternating), the low half its arrival index.  The last CTA to arrive moves the
+// word on to {this call : 0}; by then every CTA of the launch has its number, and the next launch on the stream
+// starts from the new word.  Nothing else of a launch reads the word.
+__device__ __forceinline__ unsigned long long takeExchangeTicket(const RowReduceExchange &in) {
+  return atomicAdd(in.callWord, 1ull);
+}
+
+// The running call's view of the exchange: its number and the pointers of its half of the mailbox.
+__device__ __forceinline__ RowReduceExchange resolveExchange(const RowReduceExchange &in, unsigned long long ticket) {
+  RowReduceExchange x = in;
+  unsigned int e = static_cast<unsigned int>(ticket >> 32) + 1u;
+  if (e == 0u) e = 2u;
+  x.epoch = e;
+  const long long shift = (e & 1u) ? in.halfStride : 0ll;
+#pragma unroll
+  for (int p = 0; p < kMaxExchangeRanks; ++p) x.peerEntries[p] = in.peerEntries[p] + shift;
+  x.myEntries = in.myEntries + shift;
+  return x;
+}
+
+__device__ __forceinline__ void advanceExchangeIfLast(const RowReduceExchange &x, unsigned long long ticket, unsigned int parts) {
+  if (static_cast<unsigned int>(ticket) != parts - 1u) return;
+  const unsigned int step = x.epoch - static_cast<unsigned int>(ticket >> 32);  // 1, or 3 across the wrap
+  atomicAdd(x.callWord, (static_cast<unsigned long long>(step) << 32) - parts);
+}
+
+// All threads of the CTA call this once, before any of them sends: thread 0 takes the CTA's ticket, everybody gets
+// the call's view of the exchange.
+__device__ __forceinline__ RowReduceExchange joinExchangeCall(const RowReduceExchange &in) {
+  __shared__ unsigned long long ctaTicket;
+  if (threadIdx.x == 0) ctaTicket = takeExchangeTicket(in);
+  __syncthreads();
+  const unsigned long long ticket = ctaTicket;
+  const RowReduceExchange x = resolveExchange(in, ticket);
+  if (threadIdx.x == 0) advanceExchangeIfLast(x, ticket, gridDim.x);
+  return x;
+}
+
 __device__ __forceinline__ void sendPartial(const RowReduceExchange &x, long long row, float v) {
   const unsigned long long entry = (static_cast<unsigned long long>(x.epoch) << 32) | __float_as_uint(v);
   for (int p = 0; p < x.world; ++p)
@@ -165,6 +207,8 @@ __device__ __forceinline__ void rowReduceTeams(const RrParams &prm) {
   const int lane = threadIdx.x % L;  // position within the row team
   const long long rowGroups = (prm.rows + rowsPerCta - 1) / rowsPerCta;
   const long long work = rowGroups * prm.slices;
+  RowReduceExchange xr = RowReduceExchange();
+  if constexpr (XCHG) xr = joinExchangeCall(prm.xchg);
 
   for (long long w = blockIdx.x; w < work; w += gridDim.x) {
     const long long row = (w / prm.slices) * rowsPerCta + sub;
@@ -253,12 +297,12 @@ __device__ __forceinline__ void rowReduceTeams(const RrParams &prm) {
       }
     }
     if (lane == 0 && rowLive) {
-      if (XCHG) sendPartial(prm.xchg, row, sum);
+      if (XCHG) sendPartial(xr, row, sum);
       else if (prm.slices > 1) prm.partial[row * prm.slices + slice] = sum;
       else storeSum<P>(prm.out, row, sum);
     }
   }
-  if constexpr (XCHG) exchangeTail<P>(prm.xchg, prm.out, prm.rows);
+  if constexpr (XCHG) exchangeTail<P>(xr, prm.out, prm.rows);
 }
 
 // ---- bulk-copy staged variant -------------------------------------------------------------------------
@@ -356,7 +400,9 @@ __device__ __forceinline__ void rowReduceStream(const RrStreamParams &prm, unsig
   loadBcast(firstRow, bcastNow);
   long long pendFirst = firstRow;  // exchange: the oldest row this warp has sent but not yet finished ...
   int pending = 0;                 // ... and how many such rows there are (rows pendFirst, pendFirst + totalWarps, ...)
-  const int finishGroup = XCHG ? 32 / max(prm.xchg.world, 1) : 1;
+  RowReduceExchange xr = RowReduceExchange();
+  if constexpr (XCHG) xr = joinExchangeCall(prm.xchg);  // the ring's first copies are already in flight
+  const int finishGroup = XCHG ? 32 / max(xr.world, 1) : 1;
   bool peersAnswer = true;  // exchange: false once a wait for another rank ran out (the warp then only drains its stream)
   for (long long row = firstRow; row < prm.rows; row += totalWarps) {
     loadBcast(row + totalWarps, bcastNext);  // one row ahead: its latency hides behind this row's stream
@@ -423,10 +469,10 @@ __device__ __forceinline__ void rowReduceStream(const RrStreamParams &prm, unsig
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
     if constexpr (XCHG) {
-      sendPartialByWarp(prm.xchg, row, sum, lane);
+      sendPartialByWarp(xr, row, sum, lane);
       ++pending;
       if (pending >= finishGroup + prm.finishLag) {  // the oldest group has had finishLag rows' time to arrive
-        if (peersAnswer) peersAnswer = finishRowsByWarp<P>(prm.xchg, prm.out, pendFirst, totalWarps, finishGroup, lane);
+        if (peersAnswer) peersAnswer = finishRowsByWarp<P>(xr, prm.out, pendFirst, totalWarps, finishGroup, lane);
         pendFirst += finishGroup * totalWarps;
         pending -= finishGroup;
       }
@@ -438,8 +484,8 @@ __device__ __forceinline__ void rowReduceStream(const RrStreamParams &prm, unsig
   }
   if constexpr (XCHG) {
     for (; pending > 0; pending -= finishGroup, pendFirst += finishGroup * totalWarps)
-      if (peersAnswer) peersAnswer = finishRowsByWarp<P>(prm.xchg, prm.out, pendFirst, totalWarps, min(pending, finishGroup), lane);
-    if (!peersAnswer && lane == 0) atomicExch(prm.xchg.status, 1u);
+      if (peersAnswer) peersAnswer = finishRowsByWarp<P>(xr, prm.out, pendFirst, totalWarps, min(pending, finishGroup), lane);
+    if (!peersAnswer && lane == 0) atomicExch(xr.status, 1u);
   }
 }
 

@@ -19,7 +19,9 @@
 #include <cstdint>
 #include <type_traits>
 
+#include "kernels/ew_common.cuh"
 #include "kernels/kernels.h"
+#include "kernels/launch_util.h"
 #include "kernels/reg_block.cuh"
 
 namespace afir {
@@ -32,6 +34,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) transposeKernel(const T *__restrict__ in, T *__restrict__ out, long long rows,
                                                        long long cols, long long inStride, long long outStride,
                                                        unsigned int tilesX, unsigned long long numTiles) {
+  gridDependencyPrologue();
   __shared__ T tile[kTile][kTile + 1];
   const int tx = threadIdx.x & 63;  // fast index inside the tile
   const int ty = threadIdx.x >> 6;  // 0..3
@@ -69,6 +72,7 @@ struct TrParams {
 // (LOADFULL = true); every thread takes NB blocks, spaced so that the warp's short side grows to NB x 4 blocks.
 template <int EB, int WR, bool LOADFULL, int NB>
 __global__ void __launch_bounds__(256) transposeBlocksKernel(const __grid_constant__ TrParams p) {
+  gridDependencyPrologue();
   using RB = RegBlock<EB>;
   using T = typename std::conditional<EB == 2, unsigned short, unsigned int>::type;
   constexpr int E = RB::kEdge;
@@ -138,10 +142,10 @@ void launchBlocksAs(const TrParams &base, int warpRows, long long rows, long lon
   unsigned long long want = ctasPerSm > 0 ? static_cast<unsigned long long>(smCount) * ctasPerSm : p.numTiles;
   const unsigned int grid = static_cast<unsigned int>(std::min<unsigned long long>(std::min(p.numTiles, want), 1u << 30));
   switch (wr) {
-  case 8: transposeBlocksKernel<EB, 8, LOADFULL, NB><<<grid, 256, 0, stream>>>(p); break;
-  case 4: transposeBlocksKernel<EB, 4, LOADFULL, NB><<<grid, 256, 0, stream>>>(p); break;
-  case 1: transposeBlocksKernel<EB, 1, LOADFULL, NB><<<grid, 256, 0, stream>>>(p); break;
-  default: transposeBlocksKernel<EB, 2, LOADFULL, NB><<<grid, 256, 0, stream>>>(p); break;
+  case 8: launchDependent(transposeBlocksKernel<EB, 8, LOADFULL, NB>, grid, 256, 0, stream, p); break;
+  case 4: launchDependent(transposeBlocksKernel<EB, 4, LOADFULL, NB>, grid, 256, 0, stream, p); break;
+  case 1: launchDependent(transposeBlocksKernel<EB, 1, LOADFULL, NB>, grid, 256, 0, stream, p); break;
+  default: launchDependent(transposeBlocksKernel<EB, 2, LOADFULL, NB>, grid, 256, 0, stream, p); break;
   }
 }
 
@@ -201,12 +205,12 @@ int launchTranspose(const TransposeLaunch &l, cudaStream_t stream, int *launched
   if (tilesX >= (1ll << 31)) return cudaErrorInvalidValue;
   const unsigned int grid = static_cast<unsigned int>(std::min<unsigned long long>(numTiles, 1u << 30));
   if (l.elemBytes == 2)
-    transposeKernel<unsigned short><<<grid, 256, 0, stream>>>(static_cast<const unsigned short *>(l.in),
+    launchDependent(transposeKernel<unsigned short>, grid, 256, 0, stream, static_cast<const unsigned short *>(l.in),
                                                               static_cast<unsigned short *>(l.out), l.rows, l.cols,
                                                               l.inRowStride, l.outRowStride,
                                                               static_cast<unsigned int>(tilesX), numTiles);
   else
-    transposeKernel<unsigned int><<<grid, 256, 0, stream>>>(static_cast<const unsigned int *>(l.in),
+    launchDependent(transposeKernel<unsigned int>, grid, 256, 0, stream, static_cast<const unsigned int *>(l.in),
                                                             static_cast<unsigned int *>(l.out), l.rows, l.cols,
                                                             l.inRowStride, l.outRowStride,
                                                             static_cast<unsigned int>(tilesX), numTiles);

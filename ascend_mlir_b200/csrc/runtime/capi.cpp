@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "execution/artifact_compiler.h"
+#include "runtime/caller_device.h"
 #include "runtime/executor.h"
 #include "runtime/rowsum_exchange.h"
 
@@ -111,7 +112,10 @@ AFIR_EXPORT AfirtExecutor afirt_executor_create(void) {
   return reinterpret_cast<AfirtExecutor>(new (std::nothrow) CudaExecutor());
 }
 
-AFIR_EXPORT void afirt_executor_destroy(AfirtExecutor executor) { delete reinterpret_cast<CudaExecutor *>(executor); }
+AFIR_EXPORT void afirt_executor_destroy(AfirtExecutor executor) {
+  CallerDeviceScope keepCallerDevice;
+  delete reinterpret_cast<CudaExecutor *>(executor);
+}
 
 AFIR_EXPORT int afirt_executor_initialize(AfirtExecutor executor, int device_id, char *err_buf, size_t err_len) {
   auto *ex = reinterpret_cast<CudaExecutor *>(executor);
@@ -130,6 +134,7 @@ AFIR_EXPORT int afirt_executor_run(AfirtExecutor executor, const uint8_t *binary
   if (!binary_data || binary_len == 0) { writeErr(err_buf, err_len, "binary data is required"); return 1; }
   RunRequest r = makeRequest(binary_data, binary_len, function_name, num_inputs, input_ptrs, input_bytes, num_outputs,
                              output_ptrs, output_bytes, tiling_data, tiling_len, block_dim, magic);
+  CallerDeviceScope keepCallerDevice;
   if (Status s = ex->runHost(r); !s) { writeErr(err_buf, err_len, s.message()); return 1; }
   return 0;
 }
@@ -159,6 +164,7 @@ AFIR_EXPORT int afirt_executor_launch_device(AfirtExecutor executor, const uint8
   if (!ex || !ex->initialized()) { writeErr(err_buf, err_len, "executor has not been initialized"); return 1; }
   RunRequest r = makeRequest(binary_data, binary_len, function_name, num_inputs, input_ptrs, input_bytes, num_outputs,
                              output_ptrs, output_bytes, tiling_data, tiling_len, block_dim, magic);
+  CallerDeviceScope keepCallerDevice;
   if (Status s = ex->launchDevice(r, workspace, workspace_bytes, cuda_stream); !s) {
     writeErr(err_buf, err_len, s.message());
     return 1;
@@ -180,6 +186,7 @@ AFIR_EXPORT int afirt_executor_launch_device_exchange(AfirtExecutor executor, co
   if (mailboxDevice != ex->device()) { writeErr(err_buf, err_len, "the exchange's mailbox is on another device than the executor"); return 1; }
   RunRequest r = makeRequest(binary_data, binary_len, function_name, num_inputs, input_ptrs, input_bytes, num_outputs,
                              output_ptrs, output_bytes, tiling_data, tiling_len, block_dim, magic);
+  CallerDeviceScope keepCallerDevice;
   if (Status s = ex->launchDevice(r, workspace, workspace_bytes, cuda_stream, &record); !s) {
     writeErr(err_buf, err_len, s.message());
     return 1;
@@ -202,6 +209,7 @@ AFIR_EXPORT int afirt_executor_launch_device_sharded_table(AfirtExecutor executo
   std::vector<const void *> shards(shard_ptrs, shard_ptrs + num_shards);
   RunRequest r = makeRequest(binary_data, binary_len, function_name, num_inputs, input_ptrs, input_bytes, num_outputs,
                              output_ptrs, output_bytes, tiling_data, tiling_len, block_dim, magic);
+  CallerDeviceScope keepCallerDevice;
   if (Status s = ex->launchDevice(r, workspace, workspace_bytes, cuda_stream, nullptr, shards, rows_per_shard); !s) {
     writeErr(err_buf, err_len, s.message());
     return 1;
@@ -212,6 +220,7 @@ AFIR_EXPORT int afirt_executor_launch_device_sharded_table(AfirtExecutor executo
 AFIR_EXPORT int afirt_executor_synchronize(AfirtExecutor executor, void *cuda_stream, char *err_buf, size_t err_len) {
   auto *ex = reinterpret_cast<CudaExecutor *>(executor);
   if (!ex || !ex->initialized()) { writeErr(err_buf, err_len, "executor has not been initialized"); return 1; }
+  CallerDeviceScope keepCallerDevice;
   if (Status s = ex->synchronize(cuda_stream); !s) { writeErr(err_buf, err_len, s.message()); return 1; }
   return 0;
 }
@@ -227,6 +236,7 @@ AFIR_EXPORT int afirt_executor_workspace_bytes(AfirtExecutor executor, const uin
   std::map<std::string, int64_t> tiling;
   if (Status s = unpackTiling(desc, tiling_data, tiling_len, tiling); !s) { writeErr(err_buf, err_len, s.message()); return 1; }
   size_t bytes = 0;
+  CallerDeviceScope keepCallerDevice;
   if (Status s = requiredWorkspaceBytes(desc, tiling, ex->device(), bytes); !s) { writeErr(err_buf, err_len, s.message()); return 1; }
   *out_bytes = bytes;
   return 0;

@@ -6,6 +6,8 @@
 #include "CAPI/RuntimeCuda.h"
 
 #include <cuda.h>
+#include "runtime/caller_device.h"
+
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -64,6 +66,7 @@ AFIRT_EXPORT int afirt_peer_export(const void *device_ptr, uint8_t *out_handle, 
     fail(err_buf, err_len, "afirt_peer_export: not a device pointer");
     return 1;
   }
+  afir::CallerDeviceScope keepCallerDevice;
   e = cudaSetDevice(attr.device);
   if (e != cudaSuccess) { fail(err_buf, err_len, "cudaSetDevice", e); return 1; }
   GetAddressRangeFn range = addressRangeFn();
@@ -90,6 +93,7 @@ AFIRT_EXPORT int afirt_peer_import(int device_id, const uint8_t *handle, void **
   *out_ptr = nullptr;
   PeerHandle h;
   std::memcpy(&h, handle, sizeof(h));
+  afir::CallerDeviceScope keepCallerDevice;
   cudaError_t e = cudaSetDevice(device_id);
   if (e != cudaSuccess) { fail(err_buf, err_len, "cudaSetDevice", e); return 1; }
   if (h.pid == static_cast<uint64_t>(getpid())) {

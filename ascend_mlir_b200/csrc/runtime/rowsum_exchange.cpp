@@ -3,13 +3,18 @@
 // The device side is exchangeTail() in kernels/row_reduce.cu.
 //
 // Mailbox layout (one cudaMalloc, so that one IPC handle covers it):
-//   [256, 260)   CTAs of the running launch that are done (local use)
+//   [256, 260)   CTAs or warps of the running launch that are done (local use)
 //   [260, 264)   status word (local use)
+//   [272, 280)   {completed calls : arrivals of the running launch} (local use): every CTA of a launch adds one
+//                and learns the call's number from what it gets back; the last one moves the word on, so a launch
+//                has no argument that changes from call to call
 //   [512, ...)   entries[2][world][maxRows], eight bytes each: {f32 partial sum, epoch}.  The epoch's parity picks
 //                the half, so a rank that is already sending call e+1 cannot overwrite an entry a slower rank has
 //                not yet read for call e; it can send call e+2 only after it finished e+1, which needs every
 //                rank's e+1 entries, which they send after they finished reading e.
 #include "runtime/rowsum_exchange.h"
+
+#include "runtime/caller_device.h"
 
 #include <cuda_runtime.h>
 
@@ -19,7 +24,7 @@
 
 namespace {
 
-constexpr size_t kDoneOffset = 256, kStatusOffset = 260, kSlotsOffset = 512;
+constexpr size_t kDoneOffset = 256, kStatusOffset = 260, kCallWordOffset = 272, kSlotsOffset = 512;
 
 struct Handle {  // AFIRT_EXCHANGE_HANDLE_BYTES
   cudaIpcMemHandle_t ipc;  // 64 bytes
@@ -46,7 +51,7 @@ struct AfirtRowsumExchange_s {
   char *peer[AFIRT_EXCHANGE_MAX_RANKS] = {nullptr};
   bool viaIpc[AFIRT_EXCHANGE_MAX_RANKS] = {false};
   bool connected = false;
-  unsigned int epoch = 0;
+  unsigned long long callsIssued = 0;  // launches enqueued through this handle (the call number itself lives in the mailbox)
   int64_t slotStride() const { return maxRows; }  // entries
   size_t slotsBytesPerHalf() const { return static_cast<size_t>(world) * static_cast<size_t>(slotStride()) * sizeof(unsigned long long); }
 };
@@ -61,6 +66,7 @@ AFIRT_EXPORT int afirt_rowsum_exchange_create(int device_id, int rank, int world
   if (world_size < 1 || world_size > AFIRT_EXCHANGE_MAX_RANKS) { fail(err_buf, err_len, "world_size must be 1..8"); return 1; }
   if (rank < 0 || rank >= world_size) { fail(err_buf, err_len, "rank must be in [0, world_size)"); return 1; }
   if (max_rows < 1 || max_rows > (1ll << 28)) { fail(err_buf, err_len, "max_rows must be in [1, 2^28]"); return 1; }
+  afir::CallerDeviceScope keepCallerDevice;
   cudaError_t e = cudaSetDevice(device_id);
   if (e != cudaSuccess) { fail(err_buf, err_len, "cudaSetDevice", e); return 1; }
   auto *x = new AfirtRowsumExchange_s;
@@ -94,6 +100,7 @@ AFIRT_EXPORT int afirt_rowsum_exchange_create(int device_id, int rank, int world
 AFIRT_EXPORT int afirt_rowsum_exchange_connect(AfirtRowsumExchange x, const uint8_t *all_handles, char *err_buf, size_t err_len) {
   if (!x || !all_handles) { fail(err_buf, err_len, "exchange and all_handles are required"); return 1; }
   if (x->connected) { fail(err_buf, err_len, "exchange is already connected"); return 1; }
+  afir::CallerDeviceScope keepCallerDevice;
   cudaError_t e = cudaSetDevice(x->device);
   if (e != cudaSuccess) { fail(err_buf, err_len, "cudaSetDevice", e); return 1; }
   for (int p = 0; p < x->world; ++p) {
@@ -149,6 +156,7 @@ AFIRT_EXPORT int afirt_bcast_add_rowsum_exchange(AfirtRowsumExchange x, int elem
   if (rows < 1 || rows > x->maxRows) { fail(err_buf, err_len, "rows must be in [1, max_rows]"); return 1; }
   if (cols < 0 || b_row_stride < cols) { fail(err_buf, err_len, "cols must not be negative and b_row_stride at least cols"); return 1; }
   if (!a || !out || (!b && cols > 0)) { fail(err_buf, err_len, "a, b and out are required"); return 1; }
+  afir::CallerDeviceScope keepCallerDevice;
   cudaError_t e = cudaSetDevice(x->device);
   if (e != cudaSuccess) { fail(err_buf, err_len, "cudaSetDevice", e); return 1; }
 
@@ -196,28 +204,27 @@ namespace afir {
 
 Status nextExchangeCall(AfirtRowsumExchange x, kernels::RowReduceExchange &rx, int &device) {
   if (!x || !x->connected) return Status::error("exchange is not connected");
-  unsigned int epoch = x->epoch + 1;
-  if (epoch == 0) epoch = 2;  // 0 is what an untouched entry holds; 2 keeps the alternation of the halves
-  const size_t half = (epoch & 1u) * x->slotsBytesPerHalf();
   rx = kernels::RowReduceExchange();
   for (int p = 0; p < x->world; ++p)
-    rx.peerEntries[p] = reinterpret_cast<unsigned long long *>(x->peer[p] + kSlotsOffset + half) + static_cast<size_t>(x->rank) * x->slotStride();
-  rx.myEntries = reinterpret_cast<const unsigned long long *>(x->mailbox + kSlotsOffset + half);
+    rx.peerEntries[p] = reinterpret_cast<unsigned long long *>(x->peer[p] + kSlotsOffset) + static_cast<size_t>(x->rank) * x->slotStride();
+  rx.myEntries = reinterpret_cast<const unsigned long long *>(x->mailbox + kSlotsOffset);
   rx.doneCounter = reinterpret_cast<unsigned int *>(x->mailbox + kDoneOffset);
   rx.status = reinterpret_cast<unsigned int *>(x->mailbox + kStatusOffset);
+  rx.callWord = reinterpret_cast<unsigned long long *>(x->mailbox + kCallWordOffset);
   rx.world = x->world;
-  rx.epoch = epoch;
   rx.slotStride = x->slotStride();
+  rx.halfStride = static_cast<long long>(x->slotsBytesPerHalf() / sizeof(unsigned long long));
   device = x->device;
   return Status::success();
 }
 
-void commitExchangeCall(AfirtRowsumExchange x, const kernels::RowReduceExchange &rx) { x->epoch = rx.epoch; }
+void commitExchangeCall(AfirtRowsumExchange x, const kernels::RowReduceExchange &) { ++x->callsIssued; }
 
 } // namespace afir
 
 AFIRT_EXPORT int afirt_rowsum_exchange_status(AfirtRowsumExchange x, char *err_buf, size_t err_len) {
   if (!x) { fail(err_buf, err_len, "exchange is required"); return 1; }
+  afir::CallerDeviceScope keepCallerDevice;
   cudaError_t e = cudaSetDevice(x->device);
   unsigned int words[2] = {0, 0};  // done counter, status
   if (e == cudaSuccess) e = cudaMemcpy(words, x->mailbox + kDoneOffset, sizeof(words), cudaMemcpyDeviceToHost);
@@ -235,6 +242,7 @@ AFIRT_EXPORT int afirt_rowsum_exchange_status(AfirtRowsumExchange x, char *err_b
 
 AFIRT_EXPORT void afirt_rowsum_exchange_destroy(AfirtRowsumExchange x) {
   if (!x) return;
+  afir::CallerDeviceScope keepCallerDevice;
   if (cudaSetDevice(x->device) == cudaSuccess) {
     cudaDeviceSynchronize();
     for (int p = 0; p < x->world; ++p)

@@ -473,9 +473,10 @@ def column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local, s
             if not all_ok(error is None):
                 return {"error": error or "another rank failed the first exchange"}
             # How each arm's `steps` calls are issued, so that the figure is device time and not the cost of calling
-            # through Python: the slice kernel alone is captured into a CUDA graph and replayed; the fused exchange
-            # (whose call number is a kernel argument, so a replayed graph would repeat old numbers) is enqueued by ONE
-            # call of the batch entry point; kernel + NCCL stays a Python loop (its all-reduce dominates anyway).
+            # through Python: the slice kernel alone and the fused exchange (whose call number lives on the device, so
+            # a replay continues the sequence) are each captured into a CUDA graph and replayed; kernel + NCCL stays a
+            # Python loop (its all-reduce dominates anyway).  If a capture is refused on any rank, every rank falls
+            # back to one call of the batch entry point.
             def fused_batch(n):
                 picks = [sets[i % 3] for i in range(n)]
                 exchange.bcast_add_rowsum_batch([a.data_ptr() for a, _ in picks], [b.data_ptr() + lo * 4 for _, b in picks],
@@ -493,12 +494,30 @@ def column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local, s
                 slice_graph = g_
             except Exception:
                 slice_graph = None
+            fused_graph = None
+            try:
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=stream, capture_error_mode="thread_local"):
+                    cap = torch.cuda.current_stream().cuda_stream
+                    picks = [sets[i % 3] for i in range(steps)]
+                    exchange.bcast_add_rowsum_batch([a.data_ptr() for a, _ in picks], [b.data_ptr() + lo * 4 for _, b in picks],
+                                                    [out.data_ptr()] * steps, M, hi - lo, N, "f32", cap)
+                fused_graph = g_
+            except Exception:
+                fused_graph = None
+            if not all_ok(fused_graph is not None):  # every rank must issue the same number of calls the same way
+                fused_graph = None
             issue = {"slice_kernel_only": "cuda_graph" if slice_graph is not None else "python loop",
-                     "kernel_plus_nccl_allreduce": "python loop", "fused_exchange": "one batch call"}
+                     "kernel_plus_nccl_allreduce": "python loop",
+                     "fused_exchange": "cuda_graph" if fused_graph is not None else "one batch call"}
             micros = {}
             for name, fn in (("slice_kernel_only", local_only), ("kernel_plus_nccl_allreduce", two_step), ("fused_exchange", fused)):
                 for i in range(warmup):
                     fn(i)
+                graph_ = slice_graph if name == "slice_kernel_only" else fused_graph if name == "fused_exchange" else None
+                if graph_ is not None:  # one untimed replay: the graph's upload stays out of the timing
+                    with torch.cuda.stream(stream):
+                        graph_.replay()
                 stream.synchronize()
                 if name == "fused_exchange":
                     try:
@@ -513,6 +532,8 @@ def column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local, s
                 e0.record(stream)
                 if name == "slice_kernel_only" and slice_graph is not None:
                     slice_graph.replay()
+                elif name == "fused_exchange" and fused_graph is not None:
+                    fused_graph.replay()
                 elif name == "fused_exchange":
                     fused_batch(steps)
                 else:

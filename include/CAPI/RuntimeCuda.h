@@ -78,9 +78,12 @@ int afirt_bcast_add_rowsum_no_alloc(int device_id, int elem_type, const void *a,
  * One kernel per rank does the local reduction and the exchange: each row's partial sum is stored straight
  * into every rank's mailbox over NVLink (peer-mapped memory) as one 8-byte entry {f32 sum, call number}, so
  * the value and the fact that it has arrived travel in the same store; the warp that sent a row picks up the
- * other ranks' entries for it one row later (2 s at most) and adds them in rank order, so every rank ends with
- * the same bits.  No flags, no fences, no library collective.  (Few or short rows take the kernel without
- * the staged stream; there the last CTA to finish reads all rows.)
+ * other ranks' entries a few rows later, a group of rows at a time with one lane per entry (waiting 2 s at
+ * most), and adds them in rank order, so every rank ends with the same bits.  No flags, no fences, no library
+ * collective.  (Few or short rows take the kernel without the staged stream; there the last CTA to finish
+ * reads all rows.)  The call number lives in the mailbox and the kernel advances it itself, so a launch has no
+ * argument that changes from call to call: a stream capture of these calls can be replayed as a CUDA graph, as
+ * long as every rank replays the same number of calls.
  *
  *   create   allocates this rank's mailbox on device_id (2 x world_size x max_rows entries of 8 bytes) and
  *            writes AFIRT_EXCHANGE_HANDLE_BYTES bytes describing it to out_handle;

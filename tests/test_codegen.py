@@ -98,6 +98,19 @@ def test_row_reduction_has_three_entries(tmp_path):
     assert "sp.streamViewIndex = 1;" in src  # b[m, n] is the streamed view, a[m] the broadcast one
 
 
+def test_which_generated_kernels_wait_for_their_grid_dependencies(tmp_path):
+    """Elementwise and row-reduction kernels begin with gridDependencyPrologue() and their module says so with a marker
+    kernel (the runtime then launches them with programmatic stream serialisation); gather kernels, one short CTA per
+    tile, have neither."""
+    marker = "void afir_waits_for_grid_dependencies() {}"
+    _, _, src = compiled(tmp_path, descriptors.bcast_add_rowsum("f32"))
+    assert marker in src and src.count("gridDependencyPrologue();") == 3  # main, staged, finalize
+    _, _, src = compiled(tmp_path, descriptors.add_mul())
+    assert marker in src and src.count("gridDependencyPrologue();") == 1
+    _, cubin, src = compiled(tmp_path, descriptors.gather_rows_scale_resid())
+    assert cubin[:4] == b"\x7fELF" and marker not in src and "gridDependencyPrologue" not in src
+
+
 def test_sixteen_bit_groups_compile_with_their_packs(tmp_path):
     for spec in (descriptors.split_relu_bias_mul(), descriptors.gather_rows_scale_resid(), descriptors.bcast_add_rowsum("f16")):
         _, cubin, src = compiled(tmp_path, spec)

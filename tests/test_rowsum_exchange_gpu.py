@@ -57,6 +57,49 @@ def test_world_of_one_matches_the_ordinary_entry_point_over_several_epochs(rows,
         x.close()
 
 
+def test_captured_calls_replay_as_a_graph():
+    """The call number is kept on the device, so a captured sequence of exchange calls can be replayed: three calls
+    (odd count: the replays start on alternating halves of the mailbox) captured once, replayed three times."""
+    import torch
+    rt = CudaRuntime()
+    rt.set_device(0)
+    rows, cols = 2048, 4096
+    x = RowsumExchange(0, 0, 1, max_rows=rows)
+    x.connect()
+    try:
+        g = torch.Generator(device="cuda").manual_seed(11)
+        a = [torch.randn(rows, device="cuda", generator=g) for _ in range(3)]
+        b = [torch.randn(rows, cols, device="cuda", generator=g) for _ in range(3)]
+        out = [torch.zeros(rows, device="cuda") for _ in range(3)]
+        stream = torch.cuda.Stream()
+        x.bcast_add_rowsum(a[0].data_ptr(), b[0].data_ptr(), out[0].data_ptr(), rows, cols, cols, "f32", stream.cuda_stream)  # set-up outside the capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            cap = torch.cuda.current_stream().cuda_stream
+            x.bcast_add_rowsum_batch([t.data_ptr() for t in a], [t.data_ptr() for t in b], [t.data_ptr() for t in out], rows, cols, cols, "f32", cap)
+        want = [_ordinary(torch, rt, a[i], b[i], 0, cols, "f32") for i in range(3)]
+        for replay in range(3):
+            for t in out:
+                t.fill_(float("nan"))
+            torch.cuda.synchronize()
+            with torch.cuda.stream(stream):
+                graph.replay()
+            stream.synchronize()
+            x.check()
+            for i in range(3):
+                assert torch.equal(out[i], want[i]), (replay, i)
+        # and an ordinary call after the replays continues the sequence
+        out[0].fill_(float("nan"))
+        torch.cuda.synchronize()
+        x.bcast_add_rowsum(a[1].data_ptr(), b[1].data_ptr(), out[0].data_ptr(), rows, cols, cols, "f32", stream.cuda_stream)
+        stream.synchronize()
+        x.check()
+        assert torch.equal(out[0], want[1])
+    finally:
+        x.close()
+
+
 def test_world_of_one_bf16_rounds_once_after_the_f32_sum():
     import torch
     rt = CudaRuntime()

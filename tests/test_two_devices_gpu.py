@@ -19,6 +19,9 @@ def _two_gpus():
 
 @pytest.mark.skipif(not _two_gpus(), reason="needs two GPUs")
 def test_same_descriptors_on_device_0_then_device_1():
+    import torch
+    torch.cuda.set_device(0)
+    torch.zeros(1, device="cuda")  # this thread now has device 0 current, as a framework-hosted caller would
     runtimes = []
     for device in (0, 1):
         rt = CudaRuntime()
@@ -41,3 +44,5 @@ def test_same_descriptors_on_device_0_then_device_1():
         rt.run(ew.spec.binary, ew.spec.name, ew.inputs, [out], ew.tiling())
         assert rt.last_launch_generated
         assert np.array_equal(out, ew.expected())
+        # the library made its own device current for the calls and put the caller's back
+        assert torch.cuda.current_device() == 0
