@@ -202,6 +202,22 @@ std::string signature(const LaunchDescriptor &d, const std::string &entry, const
   return os.str();
 }
 
+// The same parameters as signature(), for a device function, and the matching argument list of a call.
+std::string parameterList(const LaunchDescriptor &d) {
+  std::ostringstream os;
+  for (int i = 0; i < d.numInputs; ++i) os << "const void *arg" << i << ", ";
+  for (int i = 0; i < d.numOutputs; ++i) os << "void *arg" << (d.numInputs + i) << ", ";
+  os << "void *workspace, const TilingData &t";
+  return os.str();
+}
+
+std::string argumentList(const LaunchDescriptor &d) {
+  std::ostringstream os;
+  for (int i = 0; i < d.numInputs + d.numOutputs; ++i) os << "arg" << i << ", ";
+  os << "workspace, t";
+  return os.str();
+}
+
 // `dependent`: the kernel starts with gridDependencyPrologue() and its module carries the marker kernel, so the
 // runtime launches it with programmatic stream serialisation.  Gather kernels do not: with one short CTA per tile
 // the prologue's two instructions, executed by every CTA, were measured to cost more than the overlap gains.
@@ -460,7 +476,13 @@ GeneratedKernel generateGatherRows(const LaunchDescriptor &d) {
   std::ostringstream src;
   src << "#include \"kernels/gather_skel.cuh\"\n" << kPreamble << tilingStruct(d) << "\n"
       << bodyStruct("FusedBody0", g.body, static_cast<int>(g.loads.size()), false) << "\n"
-      << signature(d, d.kernel, "__launch_bounds__(512)") << " {\n" << rowWindowPrologue(false) << "  {\n" << rowsDecl(g.domain[0]);
+      // The loop body once, as a function template: PAIR = the variant with two vectors per thread in flight is
+      // compiled in.  That variant needs about twice the registers of the others, and a kernel's register count is
+      // that of its hungriest path, so the entry used by default (<kernel>__one) leaves it out and keeps every warp
+      // slot of the SM usable (measured on the 262 144 x 256 bf16 gather: 40 registers and 66 % of the warp slots
+      // active with all three paths in one kernel, 22 registers and 85 % without).
+      << "template <bool PAIR>\n__device__ __forceinline__ void " << d.kernel << "__body(" << parameterList(d) << ") {\n"
+      << rowWindowPrologue(false) << "  {\n" << rowsDecl(g.domain[0]);
   src << "    GaParams prm = {};\n"
       << "    prm.table = static_cast<const char *>(arg" << table.arg << ");\n"
       << "    prm.tableRows = " << code(symOf(table.shape[0])) << "; prm.tableCols = " << tcols << "; prm.tableRowStride = " << tcols << ";\n"
@@ -486,14 +508,16 @@ GeneratedKernel generateGatherRows(const LaunchDescriptor &d) {
       << "    prm.divVpr.magic = static_cast<unsigned int>(mg); prm.divVpr.shift = static_cast<unsigned int>(mg >> 32); prm.divVpr.divisor = prm.vecPerRow;\n"
       << "    prm.totalVec = static_cast<unsigned int>(rows0 * prm.vecPerRow);\n"
       << "    const unsigned int inFlight = t.afir_p0 == 1 ? 1u : 2u;\n"
-      << "    const unsigned int tileVecs = blockDim.x * (vec ? inFlight : 2u);\n"
-      << "    prm.numTiles = (prm.totalVec + tileVecs - 1u) / tileVecs;\n"
       << "    if (!vec) gatherRowsTiles<" << ti.pack << ", FusedBody0, 2, false>(prm);\n"
-      << "    else if (inFlight == 1u) gatherRowsTiles<" << ti.pack << ", FusedBody0, 1, true>(prm);\n"
+      << "    else if (!PAIR || inFlight == 1u) gatherRowsTiles<" << ti.pack << ", FusedBody0, 1, true>(prm);\n"
       << "    else gatherRowsTiles<" << ti.pack << ", FusedBody0, 2, true>(prm);\n"
-      << "  }\n}\n";
+      << "  }\n}\n\n"
+      << signature(d, d.kernel, "__launch_bounds__(512)") << " {\n  " << d.kernel << "__body<true>(" << argumentList(d) << ");\n}\n\n"
+      << "// one vector per thread in flight (the default plan): the entry the runtime launches unless the plan asks for two\n"
+      << signature(d, d.kernel + "__one", "__launch_bounds__(512)") << " {\n  " << d.kernel << "__body<false>(" << argumentList(d) << ");\n}\n";
   out.source = src.str();
   out.entry = d.kernel;
+  out.hasSingleVectorEntry = true;
   if (ti.define) out.defines.push_back(ti.define);
   out.supported = true;
   return out;

@@ -36,7 +36,9 @@ enum HiddenWord : int { kRowBegin = 0, kRowEnd = 1, kPlan0 = 2 };  // kPlan0 .. 
 //   row_reduce, entry <kernel>__staged:   p0 = ring stages per warp, p1 = bytes per stage
 //   row_reduce, entry <kernel>__finalize: p1 = column slices
 //   gather (rows): p0 = vectors in flight per thread (1 or 2); p1, p2 = multiply-shift constants (magic | shift << 32)
-//                  of the division by the row length in 16-byte vectors (p1) and in elements (p2)
+//                  of the division by the row length in 16-byte vectors (p1) and in elements (p2); entry
+//                  <kernel>__one is the same kernel without the two-in-flight path (fewer registers), launched
+//                  when p0 = 1
 
 struct GeneratedKernel {
   bool supported = false;
@@ -45,6 +47,7 @@ struct GeneratedKernel {
   std::string entry;               // the main kernel: the descriptor's kernel name
   bool hasStaged = false;          // row_reduce: <entry>__staged exists (exactly one streamed view)
   bool hasFinalize = false;        // row_reduce: <entry>__finalize exists
+  bool hasSingleVectorEntry = false;  // gather: <entry>__one exists (the plan with one vector per thread in flight)
   std::vector<std::string> defines;  // AFIR_CG_F16 / AFIR_CG_BF16 as the group's element type needs
 };
 

@@ -74,6 +74,10 @@ Status compileArtifact(const CompileRequest &request, KernelArtifact &artifact) 
         cubin = std::move(compiled.cubin);
         source = kernel.source;
         codegenNote = "generated";
+        if (!compiled.log.empty()) {  // warnings, or the register / spill report asked for with AFIR_CUDA_NVRTC_PTXAS_INFO=1
+          std::ofstream log(request.outputDir + "/" + name + ".compile.log", std::ios::trunc);
+          log << compiled.log << "\n";
+        }
         sourcePath = request.outputDir + "/" + name + ".cu";
         std::ofstream os(sourcePath, std::ios::trunc);
         os << source;

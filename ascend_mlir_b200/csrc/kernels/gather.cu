@@ -542,7 +542,6 @@ int launchGather(const GatherLaunch &l, cudaStream_t stream, int *launched) {
     numTiles = (totalVec + threads - 1) / threads;
   }
   p.totalVec = static_cast<unsigned int>(totalVec);
-  p.numTiles = static_cast<unsigned int>(numTiles);
   p.divVpr = makeFastDiv(p.vecPerRow);
   int64_t grid = l.gridBlocks > 0 ? l.gridBlocks : numTiles;
   grid = std::max<int64_t>(1, std::min<int64_t>(grid, numTiles));

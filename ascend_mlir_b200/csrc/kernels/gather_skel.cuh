@@ -22,7 +22,6 @@ struct GaParams {
   long long outRowStride;
   unsigned int vecPerRow;
   unsigned int totalVec;
-  unsigned int numTiles;
   FastDiv divVpr;
   unsigned long long *status;
   BodyProgram prog;
@@ -58,8 +57,11 @@ __device__ __forceinline__ void gatherRowsTiles(const GaParams &prm) {
   constexpr int kElemBytes = sizeof(typename P::Scalar);
   const unsigned int tileVecs = blockDim.x * UNROLL;
 
-  for (unsigned int tile = blockIdx.x; tile < prm.numTiles; tile += gridDim.x) {
-    const unsigned int g0 = tile * tileVecs + threadIdx.x;
+  // Tiles are walked until one starts past the last vector: no tile count (and no division to get it) is needed.
+  for (unsigned int tile = blockIdx.x;; tile += gridDim.x) {
+    const unsigned long long tileBase = static_cast<unsigned long long>(tile) * tileVecs;
+    if (tileBase >= prm.totalVec) break;
+    const unsigned int g0 = static_cast<unsigned int>(tileBase) + threadIdx.x;
     unsigned int row[UNROLL], col[UNROLL];
     long long src[UNROLL];
     bool live[UNROLL];

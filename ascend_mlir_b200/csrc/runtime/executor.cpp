@@ -238,10 +238,11 @@ Status CudaExecutor::copyToHost(void *host, const void *device, size_t bytes, vo
   return e == cudaSuccess ? Status::success() : cudaFail(e, "[cuda:memory] device-to-host copy failed");
 }
 
-// AFIR_CUDA_CODEGEN: "auto" (default) runs elementwise / split / concat and row-reduction groups on the kernel
-// generated for them (measured at or above the library's straight-line kernels on every benchmark shape), and a
-// gather group when the library would otherwise interpret its body op by op; "always" uses generated code
-// whenever a generated kernel exists; "never" keeps every launch on the library's prebuilt kernels.
+// AFIR_CUDA_CODEGEN: "auto" (default) and "always" run elementwise / split / concat, row-reduction and row-gather
+// groups on the kernel generated for them whenever one exists and the launch uses nothing the generated code leaves
+// to the library (an exchange between GPUs, a sharded table, a tuning value of the library's own loops): measured
+// at or above the library's straight-line kernels on every benchmark shape.  "never" keeps every launch on the
+// library's prebuilt kernels.
 static int codegenMode() {
   const char *v = std::getenv("AFIR_CUDA_CODEGEN");
   if (!v || !*v) return 1;
@@ -273,6 +274,9 @@ bool CudaExecutor::prepareGenerated(CachedKernel &kernel) {
     if (!kernel.binding.module->function(d.kernel + "__staged", kernel.binding.stagedFn)) kernel.binding.stagedFn = nullptr;
     if (!kernel.binding.module->function(d.kernel + "__finalize", kernel.binding.finalizeFn)) kernel.binding.finalizeFn = nullptr;
   }
+  if (d.kernelClass == KernelClass::Gather &&
+      !kernel.binding.module->function(d.kernel + "__one", kernel.binding.singleVectorFn))
+    kernel.binding.singleVectorFn = nullptr;  // a module from before that entry existed: the main entry does everything
   void *marker = nullptr;  // present in modules whose kernels wait for their grid dependencies themselves
   kernel.binding.waitsForDependencies = static_cast<bool>(kernel.binding.module->function(codegen::kGridDependencyMarker, marker));
   kernel.generatedUsable = true;
@@ -285,7 +289,7 @@ Status CudaExecutor::dispatch(CachedKernel &kernel, const std::map<std::string, 
   const bool classHasCode = d.kernelClass == KernelClass::Elementwise || d.kernelClass == KernelClass::RowReduce ||
                             d.kernelClass == KernelClass::Gather;
   if (mode != 0 && classHasCode && !(kernel.generatedTried && !kernel.generatedUsable) &&
-      (mode == 2 || d.kernelClass != KernelClass::Gather || prebuiltWouldInterpret(d)) && generatedLaunchApplies(d, tiling, args) &&
+      generatedLaunchApplies(d, tiling, args) &&
       prepareGenerated(kernel)) {
     Status s = launchGenerated(d, tiling, args, kernel.binding, info);
     // sizes the generated loop does not count (beyond 32 bits of elements) go to the library's kernels

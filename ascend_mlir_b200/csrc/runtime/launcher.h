@@ -76,6 +76,7 @@ struct GeneratedBinding {
   void *mainFn = nullptr;      // <kernel>
   void *stagedFn = nullptr;    // <kernel>__staged (row reductions with one streamed view), or null
   void *finalizeFn = nullptr;  // <kernel>__finalize (row reductions), or null
+  void *singleVectorFn = nullptr;  // <kernel>__one (row gathers: one vector per thread in flight), or null
   bool waitsForDependencies = false;  // every entry begins with gridDependencyPrologue() (the module says so by a marker kernel)
 };
 
@@ -83,9 +84,6 @@ struct GeneratedBinding {
 // cover (an exchange of partial sums between GPUs, a sharded gather table, a tuning value of the prebuilt
 // kernels' unroll or staged-copy options) stay on the library's kernels.
 bool generatedLaunchApplies(const LaunchDescriptor &d, const std::map<std::string, int64_t> &tiling, const LaunchArgs &args);
-// True when the library's prebuilt kernels would run this descriptor's body through the op-by-op interpreter
-// (no straight-line specialisation matches, or the element type is an integer).
-bool prebuiltWouldInterpret(const LaunchDescriptor &d);
 
 // Same contract as launchDescriptor, on the generated kernel: same checks of sizes and bounds, same launch plan,
 // the kernel arguments in the reference's order (inputs..., outputs..., workspace, TilingData).
