@@ -567,6 +567,73 @@ def column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local, s
             exchange.close()
 
 
+def exchange_world_of_one(torch, rt, device, stream, local, peaks, steps=200, warmup=5):
+    """One GPU: the reduction kernel that exchanges its partial sums itself, with a world of one rank (its mailbox is
+    its own memory), beside the ordinary reduction kernel on the same 8192 x 8192 f32 matrix.  The difference is what
+    the exchange costs inside the kernel (ticket, sends, the wait for the entries) before any NVLink latency; the
+    result is compared bit for bit with the ordinary kernel's.  Both arms are CUDA graphs of `steps` launches."""
+    from ascend_mlir_b200 import descriptors, sharding
+    M = N = 8192
+    spec = descriptors.bcast_add_rowsum("f32")
+    exchange = None
+    try:
+        exchange = sharding.RowsumExchange(local, 0, 1, max_rows=M)
+        exchange.connect()
+        nbytes = lambda t: t.numel() * t.element_size()
+        with torch.cuda.stream(stream):
+            sets = [(torch.rand(M, device=device) - 0.5, torch.rand(M, N, device=device) - 0.5) for _ in range(3)]
+            out = [torch.empty(M, device=device), torch.empty(M, device=device)]
+            tiling = spec.pack({"M": M, "N": N})
+
+            def ordinary(s, n):
+                for i in range(n):
+                    a, b = sets[i % 3]
+                    rt.launch_device(spec.binary, spec.name, [(a.data_ptr(), nbytes(a)), (b.data_ptr(), nbytes(b))],
+                                     [(out[0].data_ptr(), nbytes(out[0]))], tiling, 0, spec.magic, stream=s)
+
+            def fused(s, n):
+                picks = [sets[i % 3] for i in range(n)]
+                exchange.bcast_add_rowsum_batch([a.data_ptr() for a, _ in picks], [b.data_ptr() for _, b in picks],
+                                                [out[1].data_ptr()] * n, M, N, N, "f32", s)
+
+            micros = {}
+            for name, fn in (("ordinary_kernel", ordinary), ("exchange_kernel", fused)):
+                fn(stream.cuda_stream, max(warmup, 1))  # set-up and warm-up outside the capture
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                    fn(torch.cuda.current_stream().cuda_stream, steps)
+                times = []
+                for _ in range(REPLAYS + 1):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    graph.replay()
+                    e1.record(stream)
+                    stream.synchronize()
+                    times.append(e0.elapsed_time(e1) / steps * 1000.0)
+                times = sorted(times[1:])  # the first replay uploads the graph
+                micros[name] = times[len(times) // 2]
+            exchange.check()
+            same = bool(torch.equal(out[0], out[1]))  # both hold the sums of buffer set (steps - 1) % 3
+        work = M * N * 4 + 2 * M * 4
+        gbs = work / (micros["exchange_kernel"] * 1e-6) / 1e9
+        return {"value": gbs, "unit": "GB/s", "shape": {"M": M, "N": N, "dtype": "f32"}, "steps": steps, "launches_per_step": 1.0,
+                "launch_mode": "cuda_graph", "microseconds_per_call": micros, "algorithmic_work_per_step": work,
+                "bit_equal_to_ordinary_kernel": same, "code": "library",
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                             "traffic": None, "peak_source": peaks["source"], "frac_of_nominal": gbs / NOMINAL_HBM_GBS},
+                "note": "world of one rank: the exchange's cost inside the kernel, no NVLink; the multi-GPU figures are in "
+                        "groups.broadcast_add_reduce_column_sharded of a --gpus N run"}
+    except Exception as e:
+        return {"error": f"{type(e).__name__}: {e}"}
+    finally:
+        if exchange is not None:
+            try:
+                torch.cuda.synchronize(device)
+            finally:
+                exchange.close()
+
+
 def roofline_of(name, unit, per_gpu, region_seconds, peaks, traffic):
     if unit == "TFLOP/s":
         # a short region runs at boost clocks, a long one settles under the board's power cap: compare like with like
@@ -624,6 +691,8 @@ def run_gpu_arm(args):
 
     everything = all_workloads()
     names = [args.workload] + ([n for n in everything if n != args.workload] if args.all_groups else [])
+    if args.exchange_only:
+        names = []
     results, main = {}, None
     weak_workloads = {}
     sampler = ClockSampler(local)
@@ -723,7 +792,14 @@ def run_gpu_arm(args):
                              "sharding": "contiguous row shards of one full-size configuration, no collective (rank r times "
                                          "shard r; table, B and bias replicated)"}
         results["broadcast_add_reduce_column_sharded"] = column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local)
+    if world == 1 and (args.all_groups or args.exchange_only):
+        results["broadcast_add_reduce_exchange_world_of_one"] = exchange_world_of_one(
+            torch, rt, device, stream, local, peaks, steps=max(3, min(args.steps, 200)), warmup=min(args.warmup, 5))
     clocks = sampler.finish()
+    if args.exchange_only:
+        print(json.dumps({"groups": {"broadcast_add_reduce_exchange_world_of_one": results["broadcast_add_reduce_exchange_world_of_one"]},
+                          "clocks": clocks}), flush=True)
+        return
 
     if rank == 0:
         w, rec = main
@@ -762,6 +838,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--one-group", dest="all_groups", action="store_false", help="time only --workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-CPU baseline legs")
+    ap.add_argument("--exchange-only", action="store_true",
+                    help="N=1: time only the world-of-one exchange kernel beside the ordinary reduction kernel")
     ap.add_argument("--buffer-sets", type=int, default=3, help="identical device buffer sets per group, used in rotation")
     ap.add_argument("--no-graph", action="store_true", help="issue the timed launches one by one instead of replaying a CUDA graph")
     args = ap.parse_args()
