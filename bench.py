@@ -567,7 +567,7 @@ def column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local, s
             exchange.close()
 
 
-def exchange_world_of_one(torch, rt, device, stream, local, peaks, steps=200, warmup=5):
+def exchange_world_of_one(torch, rt, device, stream, local, peaks, traffic, steps=200, warmup=5):
     """One GPU: the reduction kernel that exchanges its partial sums itself, with a world of one rank (its mailbox is
     its own memory), beside the ordinary reduction kernel on the same 8192 x 8192 f32 matrix.  The difference is what
     the exchange costs inside the kernel (ticket, sends, the wait for the entries) before any NVLink latency; the
@@ -621,7 +621,8 @@ def exchange_world_of_one(torch, rt, device, stream, local, peaks, steps=200, wa
                 "launch_mode": "cuda_graph", "microseconds_per_call": micros, "algorithmic_work_per_step": work,
                 "bit_equal_to_ordinary_kernel": same, "code": "library",
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                             "traffic": None, "peak_source": peaks["source"], "frac_of_nominal": gbs / NOMINAL_HBM_GBS},
+                             "traffic": traffic.get("broadcast_add_reduce_exchange_world_of_one"), "peak_source": peaks["source"],
+                             "frac_of_nominal": gbs / NOMINAL_HBM_GBS},
                 "note": "world of one rank: the exchange's cost inside the kernel, no NVLink; the multi-GPU figures are in "
                         "groups.broadcast_add_reduce_column_sharded of a --gpus N run"}
     except Exception as e:
@@ -794,7 +795,7 @@ def run_gpu_arm(args):
         results["broadcast_add_reduce_column_sharded"] = column_sharded_reduce(torch, dist, rt, device, stream, rank, world, local)
     if world == 1 and (args.all_groups or args.exchange_only):
         results["broadcast_add_reduce_exchange_world_of_one"] = exchange_world_of_one(
-            torch, rt, device, stream, local, peaks, steps=max(3, min(args.steps, 200)), warmup=min(args.warmup, 5))
+            torch, rt, device, stream, local, peaks, traffic, steps=max(3, min(args.steps, 200)), warmup=min(args.warmup, 5))
     clocks = sampler.finish()
     if args.exchange_only:
         print(json.dumps({"groups": {"broadcast_add_reduce_exchange_world_of_one": results["broadcast_add_reduce_exchange_world_of_one"]},
