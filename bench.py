@@ -352,6 +352,31 @@ class DeviceGroup:
         self.spread = {"replays": len(times), "min_ms": times[0], "max_ms": times[-1]}
         return times[len(times) // 2], launches
 
+    def timed_burst(self, sync, launches=20, pause_s=1.5, repeats=3):
+        """Tensor-bound groups: milliseconds per launch of ONE short graph replay started after a pause, i.e. at boost
+        clocks before the board's power cap bites (it does within about 60 launches of the 8192^3 GEMM).  Median of
+        `repeats` such replays.  The long timed region of timed() reports the power-capped regime; this is the other one."""
+        torch = self.torch
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.stream, capture_error_mode="thread_local"):
+            for _ in range(launches):
+                self.launch(torch.cuda.current_stream().cuda_stream)
+        with torch.cuda.stream(self.stream):
+            g.replay()
+        sync()
+        times = []
+        for _ in range(repeats):
+            time.sleep(pause_s)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(self.stream):
+                e0.record(self.stream)
+                g.replay()
+                e1.record(self.stream)
+            sync()
+            times.append(e0.elapsed_time(e1) / launches)
+        times.sort()
+        return times[len(times) // 2], launches
+
     def timed_e2e(self, steps, warmup, sync, host_in_args=None, host_out_args=None):
         for _ in range(warmup):
             self.run_host(host_in_args, host_out_args)
@@ -738,6 +763,24 @@ def run_gpu_arm(args):
                 rec["steps"] = steps
                 main = (w, rec)
             rec["roofline"] = roofline_of(name, unit, value / world, REPLAYS * steps * ms * 1e-3, peaks, traffic)
+            if unit == "TFLOP/s":
+                # the same kernel in the other regime: one short replay after a pause, against the library's burst figure
+                bms, blaunches, berr = 0.0, 0, None
+                try:
+                    bms, blaunches = g.timed_burst(sync)
+                except Exception as e:
+                    berr = f"{type(e).__name__}: {e}"
+                try:
+                    if not all_ranks(berr is None):  # every rank goes on, or none
+                        raise RuntimeError(berr or "another rank failed")
+                    bms = max_over_ranks(bms)
+                    per_gpu = work / (bms * 1e-3) / scale
+                    rec["burst"] = {"value": world * per_gpu, "unit": unit, "ms_per_step": bms, "launches": blaunches, "pause_s": 1.5,
+                                    "frac_of_burst_peak": per_gpu / peaks["bf16_tflops"], "frac_of_nominal": per_gpu / NOMINAL_BF16_TFLOPS,
+                                    "note": "one graph replay of `launches` launches after a pause (boost clocks); `value` above is the "
+                                            "median of back-to-back replays (power-capped)"}
+                except Exception as e:
+                    rec["burst"] = {"error": f"{type(e).__name__}: {e}"}
             if name in traffic and traffic[name] < work and unit == "GB/s":
                 rec["roofline"]["traffic_note"] = "single launch under ncu: part of the output was still dirty in L2 when the counters stopped"
             results[name] = rec
@@ -813,6 +856,7 @@ def run_gpu_arm(args):
                                 "host_affinity": affinity},
                 "roofline": rec["roofline"], "e2e": rec["e2e"], "e2e_pageable": rec["e2e_pageable"],
                 **({"strong": rec["strong"]} if "strong" in rec else {}),
+                **({"burst": rec["burst"]} if "burst" in rec else {}),
                 "gpu_launches": rec["gpu_launches"], "clocks": clocks,
                 "groups": {k: v for k, v in results.items() if k != args.workload}}
         if world == 1 and not args.no_cpu:
