@@ -160,6 +160,20 @@ def test_gather_with_an_unmatched_body_runs_generated_code(rt, T, W, R):
     assert np.array_equal(out, want)
 
 
+@pytest.mark.parametrize("unroll", [1, 2])
+@pytest.mark.parametrize("threads,block_dim", [(128, 0), (256, 0), (512, 5), (128, 100000)])
+def test_generated_gather_entries_and_grids(rt, unroll, threads, block_dim):
+    """Both entries of a generated row gather (one or two vectors per thread in flight), with the default bounded grid
+    (more tiles than CTAs: every CTA walks several), a grid of five CTAs and one asked for above the tile count; 300 000
+    rows of 24 columns (48-byte rows: 16-byte vectors, three per row) and an unaligned width (element access)."""
+    for T, W, R in ((70000, 24, 300000), (3000, 7, 9001)):
+        w = configs.gather_elementwise(T, W, R, seed=87)
+        out = w.new_output()
+        rt.run(w.spec.binary, w.spec.name, w.inputs, [out], w.tiling(UNROLL=unroll, CTA_THREADS=threads), block_dim=block_dim)
+        assert rt.last_launch_generated
+        assert np.array_equal(out, oracle.gather_rows_scale_resid_bf16(*w.inputs)), (T, W, R)
+
+
 def test_gather_out_of_range_indices_are_counted_by_generated_code(rt):
     from ascend_mlir_b200.runtime import ExecutorError
     w = configs.gather_elementwise(100, 16, 40, seed=13)
