@@ -36,11 +36,22 @@ std::string buildMatmulPlan(const MatmulProblem &problem, const MatmulHints &hin
   // 148 SMs exactly where 4 x 32 = 128 tiles of 256 x 256 leave 20 idle, but measured a 224-column tile takes as
   // long as a 256-column one (100.3 us vs 103.1 us at M = 1024, 396 vs 385 us at M = 4096, 727 vs 767 us at
   // M = 8192): the B stage is loaded 256 columns wide either way and the kernel is not MMA-issue bound, so
-  // narrowing buys nothing and is never chosen by default.  The CTA pair is never chosen by default either (no
-  // faster under the power cap) and cannot take B as [N, K], whose tiles it would have to split along K-major rows.
+  // narrowing buys nothing and is never chosen by default.
+  // The CTA pair works a 256 x 256 tile in a little over half the time one SM needs (measured: 0.55 of it), and half
+  // as many pairs as SMs share the tiles: it is chosen where that still comes out ahead because the tiles divide
+  // better over 74 pairs than over 148 SMs.  Measured (us per launch, one CTA per SM / pairs): M = 8192, 1024 tiles,
+  // 7 waves against 14 rounds: 775 / 855; M = 4096, 512 tiles, 4 waves against 7 rounds: **390 / 381**; M = 2048,
+  // 256 tiles, 2 against 4: 195 / 206; M = 1024, 128 tiles, 1 against 2: 100 / 108.  It cannot take B as [N, K], whose
+  // tiles it would have to split along K-major rows.
   const int64_t ctasWanted = hints.blockDim > 0 ? hints.blockDim : smCount;
   const int64_t tiles256 = ceilDiv(problem.M, 256) * ceilDiv(problem.N, kTileN);
   MatmulVariant v = 2 * tiles256 >= smCount ? MatmulVariant::Rows256 : MatmulVariant::Rows128;
+  if (v == MatmulVariant::Rows256 && hints.variant == 0 && hints.blockDim <= 0 && hints.tileN <= 0 && !problem.transposeB &&
+      smCount >= 2) {
+    const double single = static_cast<double>(ceilDiv(tiles256, smCount));
+    const double pair = 0.55 * static_cast<double>(ceilDiv(tiles256, smCount / 2));
+    if (pair < 0.99 * single) v = MatmulVariant::CtaPair;
+  }
   if (hints.variant != 0) v = static_cast<MatmulVariant>(hints.variant);
   if (v == MatmulVariant::CtaPair && problem.transposeB) v = MatmulVariant::Rows256;
   int tileN = kTileN;

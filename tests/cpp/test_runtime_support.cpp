@@ -338,13 +338,25 @@ static void testMatmulPlanner() {
   EXPECT(plan.tileN == 256 && plan.tilesM == 8 && plan.tilesN == 8 && plan.kBlocks == 5 && plan.blockDim == 64, "grid capped by the number of tiles");
 
   // The 8192^3 problem M-sharded over 2, 4 and 8 GPUs keeps the 256-row tiles (at M = 1024, 128 tiles in one wave beat
-  // 256 tiles of 128 rows in two: measured 101 us against 112 us).
+  // 256 tiles of 128 rows in two: measured 101 us against 112 us).  At M = 4096 the 512 tiles are 4 waves over 148 SMs
+  // but 7 rounds over 74 CTA pairs, each a little over half as long: the pair is chosen there (measured 381 against 390 us).
   for (int gpus : {2, 4, 8}) {
     MatmulProblem shard = big;
     shard.M = 8192 / gpus;
     EXPECT(buildMatmulPlan(shard, MatmulHints(), 148, plan).empty(), "shard plan builds");
-    EXPECT(plan.variant == MatmulVariant::Rows256 && plan.tileN == 256 && plan.tilesN == 32 && plan.tilesM == 32 / gpus,
+    EXPECT(plan.variant == (gpus == 2 ? MatmulVariant::CtaPair : MatmulVariant::Rows256) && plan.tileN == 256 && plan.tilesN == 32 &&
+               plan.tilesM == 32 / gpus,
            "M = 8192 / " + std::to_string(gpus) + ": 256 x 256 tiles, " + describeMatmulPlan(plan));
+  }
+  {
+    MatmulProblem half = big;
+    half.M = 4096;
+    half.transposeB = true;  // B as [N, K]: the pair cannot split those tiles
+    EXPECT(buildMatmulPlan(half, MatmulHints(), 148, plan).empty() && plan.variant == MatmulVariant::Rows256, "no pair for B as [N, K]");
+    MatmulHints grid;
+    grid.blockDim = 100;     // a grid asked for by the caller keeps the one-CTA-per-tile kernel
+    half.transposeB = false;
+    EXPECT(buildMatmulPlan(half, grid, 148, plan).empty() && plan.variant == MatmulVariant::Rows256, "no pair under a grid hint");
   }
   // a narrower tile is a hint: 148 tiles of 256 x 224 fill 148 SMs in whole waves
   MatmulHints width;
