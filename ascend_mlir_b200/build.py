@@ -35,6 +35,7 @@ CU_SOURCES = {
     "kernels/row_reduce.cu": NO_FMA,
     "kernels/gather.cu": NO_FMA,
     "kernels/transpose.cu": [],
+    "kernels/transpose_tma.cu": [],
     "kernels/matmul_tcgen05.cu": [],
 }
 CPP_SOURCES = ["common/json.cpp", "kernels/matmul_plan.cpp", "kernels/body_match.cpp", "codegen/kernel_source.cpp",

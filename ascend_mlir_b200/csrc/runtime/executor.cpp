@@ -571,7 +571,8 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   // The status words (bad gather indices, a staged reduction's time-out) accumulate over the launches queued since
   // the last synchronize: they are cleared only when nothing unread is pending on this workspace.
   const bool hasStatusWords = (desc->kernelClass == KernelClass::Gather || desc->kernelClass == KernelClass::RowReduce ||
-                               desc->kernelClass == KernelClass::Matmul) &&
+                               desc->kernelClass == KernelClass::Matmul || desc->kernelClass == KernelClass::Transpose ||
+                               desc->kernelClass == KernelClass::Elementwise) &&
                               args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes;
   if (hasStatusWords && !(statusPending_ && statusWorkspace_ == args.workspace)) {
     e = cudaMemsetAsync(args.workspace, 0, kWorkspaceStatusReadBytes, args.stream);
@@ -588,6 +589,8 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   if (info.usesStatusBlock) statusWorkspace_ = args.workspace;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
   reducePending_ = desc->kernelClass == KernelClass::RowReduce;
+  transposePending_ = transposePending_ || ((desc->kernelClass == KernelClass::Transpose || desc->kernelClass == KernelClass::Elementwise) &&
+                                            !info.generated && !info.usesStatusBlock);
   return Status::success();
 }
 
@@ -642,7 +645,7 @@ Status CudaExecutor::synchronize(void *stream) {
   if (e != cudaSuccess) return cudaFail(e, "[cuda:kernel_launch] kernel execution failed");
   if (statusPending_ && statusWorkspace_) {
     statusPending_ = false;
-    unsigned long long words[kWorkspaceStatusReadBytes / 8] = {0, 0};
+    unsigned long long words[kWorkspaceStatusReadBytes / 8] = {0, 0, 0};
     e = cudaMemcpy(words, statusWorkspace_, sizeof(words), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cudaFail(e, "[cuda:memory] status read failed");
     const unsigned long long bad = words[0];
@@ -655,6 +658,8 @@ Status CudaExecutor::synchronize(void *stream) {
                     roles[std::min(2u, mm & 0xffu)], mm);
       return Status::error(text);
     }
+    if (static_cast<unsigned int>(words[2] & 0xffffffffull) != 0)
+      return Status::error("[cuda:kernel_launch] transpose: a wait for a staged tile ran out after 2 s");
     constexpr unsigned long long kGatherTimeoutFlag = 1ull << 62;  // set by the staged gather kernel when a stage wait ran out
     if (bad & kGatherTimeoutFlag) return Status::error("[cuda:kernel_launch] gather kernel gave up waiting for a staged copy");
     if (bad) return Status::error("[cuda:kernel_launch] gather index out of range (" + std::to_string(bad) + " indices)");
@@ -670,6 +675,12 @@ Status CudaExecutor::synchronize(void *stream) {
     char text[256] = {0};
     if (kernels::matmulCheckStatus(device_, text) != 0)
       return Status::error(std::string("[cuda:kernel_launch] ") + (text[0] ? text : "matmul kernel reported a wait timeout"));
+  }
+  if (transposePending_) {
+    transposePending_ = false;
+    char text[256] = {0};
+    if (kernels::transposeTmaCheckStatus(text, sizeof(text)) != 0)
+      return Status::error(std::string("[cuda:kernel_launch] ") + (text[0] ? text : "transpose kernel reported a wait timeout"));
   }
   return Status::success();
 }

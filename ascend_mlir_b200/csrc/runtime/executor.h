@@ -126,6 +126,7 @@ private:
   size_t guardBytes_ = 0;
   Status verifyGuards();
   bool matmulPending_ = false;
+  bool transposePending_ = false;  // a transpose-capable launch ran without a status block: the library's own word is checked
   bool reducePending_ = false;
 };
 

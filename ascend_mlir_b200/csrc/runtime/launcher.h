@@ -20,7 +20,8 @@ namespace afir {
 constexpr size_t kWorkspaceStatusBytes = 256;
 constexpr size_t kWorkspaceReduceStatusOffset = 8;  // u32: a staged row-reduction kernel gave up waiting for a copy
 constexpr size_t kWorkspaceMatmulStatusOffset = 12; // u32: (1 << 8) | role of a matmul pipeline wait that ran out
-constexpr size_t kWorkspaceStatusReadBytes = 16;    // what the executor reads back after a run
+constexpr size_t kWorkspaceTransposeStatusOffset = 16;  // u32: the copy-engine transpose gave up waiting for a tile
+constexpr size_t kWorkspaceStatusReadBytes = 24;    // what the executor reads back after a run
 
 struct LaunchArgs {
   std::vector<void *> argPtrs;  // device pointers, inputs first then outputs
