@@ -322,7 +322,7 @@ constexpr int kStreamChunkBytesDefault = 8192;
 constexpr int kStreamStagesDefault = 2;
 constexpr int kStreamWarpsDefault = 8;
 constexpr int kStreamMaxChunkBytes = 16384;
-constexpr unsigned int kStreamBytesInFlight = 128 * 1024;  // per SM: warps x stages x chunk aims at this
+constexpr unsigned int kStreamBytesInFlight = 64 * 1024;   // per SM: short rows deepen the ring until warps x stages x chunk reaches this
 constexpr int kStreamMinRowBytes = 4096;                   // shorter rows go to the team-per-row kernel (measured: 2 KB rows
                                                            // reach 0.63 of the copy rate staged, 0.75 with plain loads)
 constexpr unsigned long long kStreamWaitLimitNs = 2000000000ull;
