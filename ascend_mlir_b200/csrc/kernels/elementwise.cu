@@ -319,8 +319,7 @@ int launchElementwise(const ElementwiseLaunch &given, cudaStream_t stream, int *
     t.inRowStride = l.views[0].stride[2];
     t.out = l.outBase;
     t.outRowStride = l.outStride[1];
-    t.status = l.status;
-    return launchTranspose(t, stream, launched);
+    return launchTranspose(t, stream, launched);  // (variant 0: the register-block kernel, which waits for nothing)
   }
   {  // a transposed operand: the block variant keeps every access 16 bytes wide
     cudaError_t berr = cudaSuccess;

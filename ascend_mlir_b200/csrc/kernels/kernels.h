@@ -109,7 +109,6 @@ struct ElementwiseLaunch {
   int64_t outerCount = 1;
   int64_t viewOuterStride[kMaxViews] = {0, 0, 0, 0, 0, 0};
   int64_t outOuterStride = 0;
-  unsigned int *status = nullptr;  // device word for wait time-outs (a copy that runs as a copy-engine transpose), or null
 };
 #ifndef __CUDACC_RTC__
 // Returns a cudaError_t value (0 = success); *launched gets the number of kernels launched.
@@ -242,8 +241,7 @@ struct TransposeLaunch {
   int64_t outRowStride;
   int warpRows = 0;         // warps of a CTA stacked along the input rows: 1, 2, 4 or 8 (0 = default)
   int ctasPerSm = 0;        // persistent grid of SMs x this many CTAs (0 = one CTA per tile)
-  int diagonalOrder = 0;    // tile order: 0 row-major (column-major when the input has few rows), 1 diagonal, 2 column-major,
-                            // 3 squares of 4 x 4 tiles
+  int diagonalOrder = 0;    // tile order: 0 row-major (column-major when the input has few rows), 1 diagonal, 2 column-major
   int variant = 0;          // register blocks: 0 = whole lines stored (default), 1 = same with 2 blocks per thread, 2 = whole
                             // lines loaded, 3 = same, 2 blocks; 4 = the copy-engine kernel (16-bit elements; else as 0)
   int forceTileKernel = 0;  // 1: use the shared-memory tile kernel even when the operands are aligned

@@ -92,17 +92,6 @@ __global__ void __launch_bounds__(256) transposeBlocksKernel(const __grid_consta
       ty = static_cast<unsigned int>(t % p.tilesY);
       tx = static_cast<unsigned int>(t / p.tilesY);
     }
-    // Blocked order: squares of kSuper x kSuper tiles, so that the tiles in flight at one time are neighbours along
-    // the input rows AND along the output rows (both sides then touch runs of kSuper tile widths within a short time).
-    if (p.diagonalOrder == 3) {
-      constexpr unsigned int kSuper = 4;
-      const unsigned int supersX = (p.tilesX + kSuper - 1) / kSuper;
-      const unsigned long long st = t / (kSuper * kSuper);
-      const unsigned int within = static_cast<unsigned int>(t % (kSuper * kSuper));
-      tx = static_cast<unsigned int>(st % supersX) * kSuper + within % kSuper;
-      ty = static_cast<unsigned int>(st / supersX) * kSuper + within / kSuper;
-      if (tx >= p.tilesX || ty >= p.tilesY) continue;
-    }
     const long long rw = static_cast<long long>(ty) * kTileRows + (warp / WC) * kWarpRows;
     const long long cw = static_cast<long long>(tx) * kTileCols + (warp % WC) * kWarpCols;
     long long r0[NB], c0[NB];
@@ -149,8 +138,6 @@ void launchBlocksAs(const TrParams &base, int warpRows, long long rows, long lon
   p.tilesX = static_cast<unsigned int>(tilesX);
   p.tilesY = static_cast<unsigned int>(tilesY);
   p.numTiles = static_cast<unsigned long long>(tilesX) * static_cast<unsigned long long>(tilesY);
-  if (p.diagonalOrder == 3)  // whole squares of 4 x 4 tiles; the kernel skips the tiles of a square that lie outside
-    p.numTiles = static_cast<unsigned long long>((tilesX + 3) / 4) * static_cast<unsigned long long>((tilesY + 3) / 4) * 16ull;
   // one tile per CTA unless a persistent grid (SMs x ctasPerSm) is asked for
   unsigned long long want = ctasPerSm > 0 ? static_cast<unsigned long long>(smCount) * ctasPerSm : p.numTiles;
   const unsigned int grid = static_cast<unsigned int>(std::min<unsigned long long>(std::min(p.numTiles, want), 1u << 30));
@@ -208,7 +195,7 @@ int launchTranspose(const TransposeLaunch &l, cudaStream_t stream, int *launched
     p.outStrideBytes = l.outRowStride * l.elemBytes;
     const int ctasPerSm = l.ctasPerSm > 0 ? l.ctasPerSm : 0;
     const int warpRows = l.warpRows > 0 ? l.warpRows : 2;
-    p.diagonalOrder = l.diagonalOrder == 3 ? 3 : l.diagonalOrder == 2 ? 2 : l.diagonalOrder ? 1 : 0;
+    p.diagonalOrder = l.diagonalOrder == 2 ? 2 : l.diagonalOrder ? 1 : 0;
     // Few input rows (a wide-and-low input, a tall-and-thin output whose rows are at most 4 KB): in row-major tile
     // order each output row would be finished by CTAs that run far apart in time, so the default walks the input
     // rows fastest there.

@@ -571,8 +571,7 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   // The status words (bad gather indices, a staged reduction's time-out) accumulate over the launches queued since
   // the last synchronize: they are cleared only when nothing unread is pending on this workspace.
   const bool hasStatusWords = (desc->kernelClass == KernelClass::Gather || desc->kernelClass == KernelClass::RowReduce ||
-                               desc->kernelClass == KernelClass::Matmul || desc->kernelClass == KernelClass::Transpose ||
-                               desc->kernelClass == KernelClass::Elementwise) &&
+                               desc->kernelClass == KernelClass::Matmul || desc->kernelClass == KernelClass::Transpose) &&
                               args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes;
   if (hasStatusWords && !(statusPending_ && statusWorkspace_ == args.workspace)) {
     e = cudaMemsetAsync(args.workspace, 0, kWorkspaceStatusReadBytes, args.stream);
@@ -589,8 +588,7 @@ Status CudaExecutor::launchDevice(const RunRequest &req, void *workspace, size_t
   if (info.usesStatusBlock) statusWorkspace_ = args.workspace;
   matmulPending_ = desc->kernelClass == KernelClass::Matmul;
   reducePending_ = desc->kernelClass == KernelClass::RowReduce;
-  transposePending_ = transposePending_ || ((desc->kernelClass == KernelClass::Transpose || desc->kernelClass == KernelClass::Elementwise) &&
-                                            !info.generated && !info.usesStatusBlock);
+  transposePending_ = transposePending_ || (desc->kernelClass == KernelClass::Transpose && !info.usesStatusBlock);
   return Status::success();
 }
 

@@ -189,10 +189,6 @@ Status launchElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, con
   l.ctaThreads = static_cast<int>(optionalField(d.ctaThreadsField, tiling));
   l.unroll = static_cast<int>(optionalField(d.unrollField, tiling));
   l.gridBlocks = args.blockDim;
-  if (args.workspace && args.workspaceBytes >= kWorkspaceStatusBytes) {  // a bare transposed copy may run on the copy-engine kernel
-    l.status = reinterpret_cast<unsigned int *>(static_cast<char *>(args.workspace) + kWorkspaceTransposeStatusOffset);
-    info.usesStatusBlock = true;
-  }
   // the innermost of the outer dims goes to the kernel library (it takes one as the grid's second dimension where
   // the group allows, and walks it itself where not); the others are walked here
   if (!outer.empty()) {

@@ -202,7 +202,7 @@ def transpose_2d(dtype: str = "f16", name: str = "transpose_2d") -> KernelSpec:
             "loads": [{"arg": 0, "shape": ["dim_arg0_0", "dim_arg0_1"], "map": [1, 0]}],
             "store": {"arg": 1, "shape": ["dim_arg0_1", "dim_arg0_0"], "map": [0, 1]}, "body": []}
     tile = [("WARP_ROWS", 0, (0, 1, 2, 4, 8)), ("CTAS_PER_SM", 0, (0, 4, 8, 16)), ("TILE_KERNEL", 0, (0, 1)),
-            ("TILE_ORDER", 0, (0, 1, 2, 3)), ("VARIANT", 0, (0, 1, 2, 3, 4))]
+            ("TILE_ORDER", 0, (0, 1, 2)), ("VARIANT", 0, (0, 1, 2, 3, 4))]
     return _spec(name, "transpose", dtype, 1, 1, tile, dims, body,
                  {"warp_rows": "WARP_ROWS", "ctas_per_sm": "CTAS_PER_SM", "tile_kernel": "TILE_KERNEL",
                   "tile_order": "TILE_ORDER", "variant": "VARIANT"})

@@ -150,22 +150,17 @@ def test_transpose_2d_every_warp_arrangement(rt, dtype, warp_rows):
 
 
 @pytest.mark.parametrize("R,C", [(64, 64), (512, 256), (520, 264), (8, 8), (1000, 24), (24, 1000), (4104, 600), (72, 4104)])
-def test_transpose_2d_copy_engine_kernel_and_blocked_tile_order(rt, R, C):
+def test_transpose_2d_copy_engine_kernel(rt, R, C):
     """The copy-engine transpose (tensor-map loads, ldmatrix.trans / stmatrix, tensor-map stores; 16-bit elements,
     asked for with VARIANT=4): whole tiles, tiles ragged in either direction (loads past the edge read zeros, stores are
-    clipped), a matrix smaller than one tile, more tiles than CTAs.  And the register-block kernel walking its tiles
-    in squares (TILE_ORDER=3), whose border squares hold tiles that lie outside the matrix."""
+    clipped), a matrix smaller than one tile, more tiles than CTAs (its tiles are walked in squares of 8 x 8, whose
+    border squares hold tiles that lie outside the matrix)."""
     rng = np.random.default_rng(R + C)
     x = rng.standard_normal((R, C)).astype(np.float16)
     want = oracle.transpose_2d(x).tobytes()
     spec = descriptors.transpose_2d("f16")
     out = run(rt, spec, [x], np.full((C, R), np.float16(7), np.float16), {"R": R, "C": C}, VARIANT=4)
     assert out.tobytes() == want, "copy engine"
-    for dtype in (np.float16, np.float32):
-        xd = x.astype(dtype)
-        sd = descriptors.transpose_2d("f16" if dtype == np.float16 else "f32")
-        out = run(rt, sd, [xd], np.zeros((C, R), dtype), {"R": R, "C": C}, TILE_ORDER=3)
-        assert out.tobytes() == oracle.transpose_2d(xd).tobytes(), ("blocked order", dtype)
     # 32-bit elements have no copy-engine kernel: the hint falls back to the register blocks
     x32 = x.astype(np.float32)
     out = run(rt, descriptors.transpose_2d("f32"), [x32], np.zeros((C, R), np.float32), {"R": R, "C": C}, VARIANT=4)
