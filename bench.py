@@ -808,7 +808,9 @@ def run_gpu_arm(args):
                 full = weak_workloads[name]
                 mine = full.shard(rank, world)
                 # a shard is small: rotate enough buffer sets that a step's memory was last used >= 2 x L2 of traffic ago
-                touched = sum(x.nbytes for x in mine.inputs) + int(np.prod(mine.out_shape)) * mine.out_dtype.itemsize
+                # (what a step streams: the algorithmic bytes; a replicated gather table is read at random and does not count)
+                touched = mine.algorithmic_bytes if mine.bound == "hbm" and mine.algorithmic_bytes else (
+                    sum(x.nbytes for x in mine.inputs) + int(np.prod(mine.out_shape)) * mine.out_dtype.itemsize)
                 n_sets = int(min(12, max(args.buffer_sets, -(-2 * 126_000_000 // max(touched, 1)))))
                 g = DeviceGroup(torch, rt, mine, device, stream, n_sets, pinned=False)
                 steps = max(20, min(args.steps, 200))
