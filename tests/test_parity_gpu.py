@@ -2,6 +2,8 @@
 same seeded inputs, plus the reference's own golden fixtures.  Bars: bit-exact for f32 elementwise,
 for f16/bf16 chains (per-op rounding on both sides) and for all indexing; reductions within
 1e-5 * sum|x| per row."""
+import copy
+
 import numpy as np
 import pytest
 
@@ -543,6 +545,28 @@ def test_integer_body_ops_division_max_min_constants_and_a_transposed_operand(rt
     out = run(rt, spec, [a2, b2], np.zeros((29, 37), dtype), {"M": 37, "N": 29})
     t = np.maximum(a2.T.astype(np.int64), -100)
     assert np.array_equal(out, np.minimum(np.trunc(t / b2.astype(np.int64)).astype(np.int64) - 3, 40).astype(dtype))
+
+
+@pytest.mark.parametrize("M,N", [(7, 5), (33, 37), (64, 256)])
+def test_int16_add_sub_max_min_one_element_at_a_time_and_in_vectors(rt, M, N):
+    """((a + 3) - b, max with -7, + b, - 5, min with 1000) on int16 over the whole value range, with wrap-around: on
+    ragged shapes the kernels evaluate the two-lane pack on one splatted element and keep its low lane, a context in
+    which the compiler's two-lane add / subtract intrinsics came back wrong, so the pack spells the arithmetic out."""
+    rng = np.random.default_rng(43)
+    info = np.iinfo(np.int16)
+    a = rng.integers(info.min, info.max, (M, N), dtype=np.int16, endpoint=True)
+    b = rng.integers(info.min, info.max, (M, N), dtype=np.int16, endpoint=True)
+    spec = descriptors.add_mul("i16")
+    d = copy.deepcopy(spec.descriptor)
+    d["kernel"] = "int16_lanes"
+    d["body"] = [descriptors.op("addi", "v0", 3), descriptors.op("subi", "%0", "v1"), descriptors.op("maxsi", "%1", -7),
+                 descriptors.op("addi", "%2", "v1"), descriptors.op("subi", "%3", 5), descriptors.op("minsi", "%4", 1000)]
+    out = np.zeros((M, N), np.int16)
+    rt.run(descriptors.container(d), d["kernel"], [a, b], [out], spec.pack({"M": M, "N": N}))
+    with np.errstate(over="ignore"):
+        t = np.maximum(((a + np.int16(3)).astype(np.int16) - b).astype(np.int16), np.int16(-7))
+        want = np.minimum(((t + b).astype(np.int16) - np.int16(5)).astype(np.int16), np.int16(1000))
+    assert np.array_equal(out, want)
 
 
 def test_integer_division_by_zero_is_defined_as_zero(rt):
