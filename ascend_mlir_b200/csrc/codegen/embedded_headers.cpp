@@ -17,6 +17,8 @@ AFIR_EMBED(afir_hdr_kernels, "kernels/kernels.h")
 AFIR_EMBED(afir_hdr_grid_dependency, "kernels/grid_dependency.cuh")
 AFIR_EMBED(afir_hdr_ew_common, "kernels/ew_common.cuh")
 AFIR_EMBED(afir_hdr_elementwise_skel, "kernels/elementwise_skel.cuh")
+AFIR_EMBED(afir_hdr_elementwise_blocks_skel, "kernels/elementwise_blocks_skel.cuh")
+AFIR_EMBED(afir_hdr_reg_block, "kernels/reg_block.cuh")
 AFIR_EMBED(afir_hdr_row_reduce_skel, "kernels/row_reduce_skel.cuh")
 AFIR_EMBED(afir_hdr_gather_skel, "kernels/gather_skel.cuh")
 
@@ -29,6 +31,8 @@ const std::vector<EmbeddedHeader> &embeddedHeaders() {
       {"kernels/grid_dependency.cuh", afir_hdr_grid_dependency_begin, afir_hdr_grid_dependency_end},
       {"kernels/ew_common.cuh", afir_hdr_ew_common_begin, afir_hdr_ew_common_end},
       {"kernels/elementwise_skel.cuh", afir_hdr_elementwise_skel_begin, afir_hdr_elementwise_skel_end},
+      {"kernels/elementwise_blocks_skel.cuh", afir_hdr_elementwise_blocks_skel_begin, afir_hdr_elementwise_blocks_skel_end},
+      {"kernels/reg_block.cuh", afir_hdr_reg_block_begin, afir_hdr_reg_block_end},
       {"kernels/row_reduce_skel.cuh", afir_hdr_row_reduce_skel_begin, afir_hdr_row_reduce_skel_end},
       {"kernels/gather_skel.cuh", afir_hdr_gather_skel_begin, afir_hdr_gather_skel_end},
   };

@@ -255,7 +255,7 @@ const char *kDependencyMarker =
 
 // ---- elementwise / broadcast / split / concat ------------------------------------------------------------------------
 bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t index, const TypeInfo &ti, std::ostringstream &bodies,
-                          std::ostringstream &kernel, std::string &why) {
+                          std::ostringstream &kernel, std::string &why, bool &usesBlocks) {
   const size_t rank = g.domain.size();
   if (rank == 0) { why = "empty iteration domain"; return false; }
   if (g.loads.empty() || g.loads.size() > static_cast<size_t>(kernels::kMaxViews)) { why = "group loads no view or too many"; return false; }
@@ -280,13 +280,24 @@ bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t 
   const bool innerIsOne = extent[2].isLiteral(1);
   SymView &store = views.back();
   if (!store.stride[2].isLiteral(1) && !innerIsOne) { why = "the store is not contiguous along the inner dim"; return false; }
+  // A view whose unit stride runs along the middle dim is read through a transpose (out[n, m] = f(a[m, n], ...)):
+  // such a group gets the register-block loop beside the element-wise one.
+  bool transposedGroup = false;
   for (size_t i = 0; i < g.loads.size(); ++i) {
     if (innerIsOne) views[i].stride[2] = Sym::literal(1);
     if (!views[i].stride[2].isLiteral(0) && !views[i].stride[2].isLiteral(1)) {
-      why = "an operand is not contiguous along the inner dim (a transposed view)";
-      return false;
+      if (!views[i].stride[1].isLiteral(1)) {
+        why = "an operand is contiguous along neither of the two inner dims";
+        return false;
+      }
+      transposedGroup = true;
     }
   }
+  if (transposedGroup && g.body.numOps == 0) {
+    why = "a bare permutation runs on the library's transpose kernels";
+    return false;
+  }
+  if (transposedGroup) usesBlocks = true;
   const int ve = 16 / ti.bytes;
   const std::string bodyName = "FusedBody" + std::to_string(index);
   bodies << bodyStruct(bodyName, g.body, static_cast<int>(g.loads.size()), ti.integer) << "\n";
@@ -308,6 +319,7 @@ bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t 
   os << "    prm.obase = " << baseCode(store, ti.bytes, false) << ";\n";
   os << "    prm.os0 = " << code(store.stride[0]) << "; prm.os1 = " << code(store.stride[1]) << ";\n";
   vec += " && " + aligned16("prm.obase") + " && prm.os0 % " + std::to_string(ve) + " == 0 && prm.os1 % " + std::to_string(ve) + " == 0";
+  if (transposedGroup) vec = "false";  // (the transposed view has no 16-byte pieces along the inner dim)
   os << "    const bool vec = " << vec << ";\n";
   os << "    const long long vpr = vec ? d2 / " << ve << " : d2;\n";
   os << "    prm.vecPerRow = static_cast<unsigned int>(vpr);\n"
@@ -317,8 +329,33 @@ bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t 
      << "    prm.flat = (d0 == 1 && d1 == 1) ? 1 : 0;\n"
      << "    prm.numViews = " << g.loads.size() << ";\n"
      << "    const unsigned int tileVecs = blockDim.x * 2u;\n"
-     << "    prm.numTiles = (prm.totalVec + tileVecs - 1u) / tileVecs;\n"
-     << "    if (vec) elementwiseTiles<" << ti.pack << ", " << bodyName << ", 2, true, false, true>(prm);\n"
+     << "    prm.numTiles = (prm.totalVec + tileVecs - 1u) / tileVecs;\n";
+  if (transposedGroup) {
+    // The register-block loop when the launch has its CTA shape (256 threads) and everything is aligned for 16-byte
+    // row pieces: row-major views along their rows, transposed views along theirs; else element by element.
+    const int tileRows = 2 * 4 * ve, tileCols = 4 * 8 * ve;
+    std::string ok = "blockDim.x == 256u && " + aligned16("prm.obase") + " && prm.os0 % " + std::to_string(ve) + " == 0 && prm.os1 % " +
+                     std::to_string(ve) + " == 0";
+    os << "    EbParams bp = {};\n";
+    for (size_t i = 0; i < g.loads.size(); ++i) {
+      const SymView &v = views[i];
+      const char *kind = v.stride[2].isLiteral(1) ? "kViewRowMajor" : v.stride[2].isLiteral(0) ? "kViewInnerBroadcast" : "kViewTransposed";
+      os << "    bp.vbase[" << i << "] = prm.vbase[" << i << "]; bp.s0[" << i << "] = prm.vs0[" << i << "]; bp.s1[" << i << "] = prm.vs1[" << i
+         << "]; bp.s2[" << i << "] = prm.vs2[" << i << "]; bp.kind[" << i << "] = " << kind << ";\n";
+      const std::string n = std::to_string(i), e = std::to_string(ve);
+      if (v.stride[2].isLiteral(1)) ok += " && " + aligned16("prm.vbase[" + n + "]") + " && prm.vs0[" + n + "] % " + e + " == 0 && prm.vs1[" + n + "] % " + e + " == 0";
+      else if (!v.stride[2].isLiteral(0)) ok += " && " + aligned16("prm.vbase[" + n + "]") + " && prm.vs0[" + n + "] % " + e + " == 0 && prm.vs2[" + n + "] % " + e + " == 0";
+    }
+    os << "    bp.numViews = " << g.loads.size() << "; bp.obase = prm.obase; bp.os0 = prm.os0; bp.os1 = prm.os1; bp.d1 = d1; bp.d2 = d2;\n"
+       << "    bp.tilesX = static_cast<unsigned int>((d2 + " << (tileCols - 1) << ") / " << tileCols << ");\n"
+       << "    bp.tilesY = static_cast<unsigned int>((d1 + " << (tileRows - 1) << ") / " << tileRows << ");\n"
+       << "    bp.numTiles = static_cast<unsigned long long>(d0) * bp.tilesX * bp.tilesY;\n"
+       << "    if (" << ok << ") elementwiseBlocksTiles<" << ti.pack << ", " << bodyName << ", " << g.loads.size() << ">(bp);\n"
+       << "    else elementwiseTiles<" << ti.pack << ", " << bodyName << ", 2, false, false, true>(prm);\n"
+       << "  }\n";
+    return true;
+  }
+  os << "    if (vec) elementwiseTiles<" << ti.pack << ", " << bodyName << ", 2, true, false, true>(prm);\n"
      << "    else elementwiseTiles<" << ti.pack << ", " << bodyName << ", 2, false, false, true>(prm);\n"
      << "  }\n";
   return true;
@@ -330,11 +367,18 @@ GeneratedKernel generateElementwise(const LaunchDescriptor &d) {
   if (!typeInfo(d.dtype, true, ti)) { out.whyNot = "element type"; return out; }
   if (d.groups.empty()) { out.whyNot = "no groups"; return out; }
   std::ostringstream bodies, kernel;
+  bool usesBlocks = false;
   for (size_t i = 0; i < d.groups.size(); ++i)
-    if (!emitElementwiseGroup(d, d.groups[i], i, ti, bodies, kernel, out.whyNot)) return out;
+    if (!emitElementwiseGroup(d, d.groups[i], i, ti, bodies, kernel, out.whyNot, usesBlocks)) return out;
+  out.hasTransposedOperand = usesBlocks;
   std::ostringstream src;
-  src << "#include \"kernels/elementwise_skel.cuh\"\n" << kPreamble << kDependencyMarker << tilingStruct(d) << "\n" << bodies.str()
-      << signature(d, d.kernel, "__launch_bounds__(512)") << " {\n" << rowWindowPrologue() << kernel.str() << "}\n";
+  src << (usesBlocks ? "#include \"kernels/elementwise_blocks_skel.cuh\"\n" : "#include \"kernels/elementwise_skel.cuh\"\n") << kPreamble << kDependencyMarker
+      << (usesBlocks ? "// Tells the runtime that this module's kernel is launched with CTAs of 256 threads.\nextern \"C\" __global__ void afir_ctas_of_256_threads() {}\n\n" : "")
+      << tilingStruct(d) << "\n" << bodies.str()
+      // (a kernel with the register-block loop is launched with 256 threads, like the library's instantiations, which take
+      // 94-128 registers)
+      << signature(d, d.kernel, usesBlocks ? "__launch_bounds__(256)" : "__launch_bounds__(512)") << " {\n" << rowWindowPrologue()
+      << kernel.str() << "}\n";
   out.source = src.str();
   out.entry = d.kernel;
   if (ti.define) out.defines.push_back(ti.define);

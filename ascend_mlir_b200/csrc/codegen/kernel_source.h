@@ -48,6 +48,7 @@ struct GeneratedKernel {
   bool hasStaged = false;          // row_reduce: <entry>__staged exists (exactly one streamed view)
   bool hasFinalize = false;        // row_reduce: <entry>__finalize exists
   bool hasSingleVectorEntry = false;  // gather: <entry>__one exists (the plan with one vector per thread in flight)
+  bool hasTransposedOperand = false;  // elementwise: a group reads an operand through a transposed view (register-block loop)
   std::vector<std::string> defines;  // AFIR_CG_F16 / AFIR_CG_BF16 as the group's element type needs
 };
 
@@ -57,6 +58,11 @@ GeneratedKernel generateKernelSource(const LaunchDescriptor &d);
 // (kernels/ew_common.cuh); the runtime launches only such modules with programmatic stream serialisation, so a
 // device binary from before that convention keeps the ordinary launch.
 constexpr const char *kGridDependencyMarker = "afir_waits_for_grid_dependencies";
+
+// An empty kernel of this name is in every generated elementwise module whose kernel holds the register-block loop of
+// groups with a transposed operand: that kernel is compiled for CTAs of at most 256 threads, so the runtime launches it
+// with exactly 256 whatever the tiling says.
+constexpr const char *kRegisterBlockMarker = "afir_ctas_of_256_threads";
 
 } // namespace codegen
 } // namespace afir

@@ -3,7 +3,9 @@
 // and by the elementwise kernel for operands that are read through a transposed view.
 #pragma once
 
+#ifndef __CUDACC_RTC__
 #include <cuda_runtime.h>
+#endif
 
 namespace afir {
 namespace kernels {

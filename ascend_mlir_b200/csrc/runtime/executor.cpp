@@ -279,6 +279,7 @@ bool CudaExecutor::prepareGenerated(CachedKernel &kernel) {
     kernel.binding.singleVectorFn = nullptr;  // a module from before that entry existed: the main entry does everything
   void *marker = nullptr;  // present in modules whose kernels wait for their grid dependencies themselves
   kernel.binding.waitsForDependencies = static_cast<bool>(kernel.binding.module->function(codegen::kGridDependencyMarker, marker));
+  kernel.binding.ctasOf256Threads = static_cast<bool>(kernel.binding.module->function(codegen::kRegisterBlockMarker, marker));
   kernel.generatedUsable = true;
   return true;
 }

@@ -624,7 +624,8 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
   GeneratedArgs ga(d, tiling, args);
 
   if (d.kernelClass == KernelClass::Elementwise) {
-    const int threads = clampThreads(optionalField(d.ctaThreadsField, tiling));
+    // (a kernel with the register-block loop of transposed operands is compiled for CTAs of 256 threads)
+    const int threads = binding.ctasOf256Threads ? 256 : clampThreads(optionalField(d.ctaThreadsField, tiling));
     int64_t tiles = 1;
     int64_t totalElems = 0;
     for (const GroupSpec &g : d.groups) {
@@ -635,6 +636,33 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
       if (Status s = resolveElementwiseGroup(d, g, tiling, args, et, domain, loads, store); !s) return s;
       int64_t elems = 1;
       for (int64_t e : domain) elems *= e;
+      {
+        // A group that reads an operand through a transposed view has the register-block loop in its kernel, which
+        // wants one CTA per tile of 2 x 4 warps x 4 x 8 blocks.  Whether it runs is the kernel's decision (alignment
+        // of what it is given); the grid below only has to be large enough for either loop, both walk their tiles
+        // with a grid stride.
+        std::vector<ResolvedView> copies = loads;
+        ResolvedView storeCopy = store;
+        std::vector<int64_t> dom = domain;
+        std::vector<ResolvedView *> all;
+        for (auto &v : copies) all.push_back(&v);
+        all.push_back(&storeCopy);
+        collapseDomain(dom, all);
+        if (dom.size() <= 3 && !dom.empty()) {
+          while (dom.size() < 3) {
+            dom.insert(dom.begin(), 1);
+            for (auto *v : all) v->stride.insert(v->stride.begin(), 0);
+          }
+          bool transposed = false;
+          for (const ResolvedView &v : copies)
+            if (dom[2] != 1 && v.stride[2] != 0 && v.stride[2] != 1 && v.stride[1] == 1) transposed = true;
+          if (transposed) {
+            const int64_t e = 16 / static_cast<int64_t>(dtypeBytes(d.dtype));
+            const int64_t blockTiles = dom[0] * ((dom[2] + 32 * e - 1) / (32 * e)) * ((dom[1] + 8 * e - 1) / (8 * e));
+            tiles = std::max(tiles, blockTiles);
+          }
+        }
+      }
       // the kernel counts 16-byte vectors (or elements, when something is unaligned) in 32 bits
       if (elems >= (1ll << 32) - (1 << 20)) return Status::error("[generated:unsupported] more than 2^32 elements in one group");
       totalElems += elems;

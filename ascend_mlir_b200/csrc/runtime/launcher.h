@@ -78,6 +78,7 @@ struct GeneratedBinding {
   void *stagedFn = nullptr;    // <kernel>__staged (row reductions with one streamed view), or null
   void *finalizeFn = nullptr;  // <kernel>__finalize (row reductions), or null
   void *singleVectorFn = nullptr;  // <kernel>__one (row gathers: one vector per thread in flight), or null
+  bool ctasOf256Threads = false;  // elementwise: the kernel holds the register-block loop and is compiled for CTAs of 256 threads
   bool waitsForDependencies = false;  // every entry begins with gridDependencyPrologue() (the module says so by a marker kernel)
 };
 

@@ -131,11 +131,31 @@ def test_groups_of_the_library_get_no_generated_source(tmp_path):
     assert r.returncode == 1 and "hand-written tcgen05 kernel" in r.stderr
     r = kernel_source(EXAMPLES / "transpose_2d.mlir")
     assert r.returncode == 1 and "no kernel source is generated" in r.stderr
-    # a transposed operand: the prebuilt block kernel keeps it; the compile step still succeeds, descriptor only
-    r = kernel_source(EXAMPLES / "transposed_add.mlir")
-    assert r.returncode == 1 and "transposed view" in r.stderr
-    _, cubin, src = compiled(tmp_path, descriptors.transposed_add_mul("f16"))
+    # a bare permutation written as an elementwise group (a copy through a transposed view) stays with the library's
+    # transpose kernels: the compile step succeeds, descriptor only
+    d = copy.deepcopy(descriptors.transposed_add_mul("f16").descriptor)
+    d["kernel"] = "transposed_copy"
+    d["num_inputs"] = 1
+    d["loads"] = d["loads"][:1]
+    d["store"]["arg"] = 1
+    d["body"] = []
+    _, cubin, src = compiled(tmp_path, None, d)
     assert cubin == b"" and src == ""
+
+
+def test_transposed_operand_gets_the_register_block_loop(tmp_path):
+    """A group that reads an operand through a transposed view: its kernel holds the register-block loop (16-byte pieces
+    on every side, transposed in registers) beside the element-wise one and picks at run time; CTAs of 256 threads."""
+    r = kernel_source(EXAMPLES / "transposed_add.mlir")
+    assert r.returncode == 0, r.stderr
+    assert "elementwiseBlocksTiles<" in r.stdout and "kViewTransposed" in r.stdout and "__launch_bounds__(256)" in r.stdout
+    for dtype in ("f16", "f32"):
+        _, cubin, src = compiled(tmp_path, descriptors.transposed_add_mul(dtype))
+        assert cubin[:4] == b"\x7fELF"
+        assert '#include "kernels/elementwise_blocks_skel.cuh"' in src
+        assert "bp.kind[0] = kViewTransposed" in src and "bp.kind[1] = kViewRowMajor" in src and "bp.kind[2] = kViewInnerBroadcast" in src
+        assert "elementwiseTiles<" in src  # the element-wise fallback for unaligned operands
+        assert "void afir_ctas_of_256_threads() {}" in src  # the runtime launches 256 threads whatever the tiling says
 
 
 @pytest.mark.parametrize("example", ["elementwise_chain", "split_relu_broadcast_add_mul", "broadcast_add_reduce",

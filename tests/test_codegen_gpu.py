@@ -160,6 +160,25 @@ def test_gather_with_an_unmatched_body_runs_generated_code(rt, T, W, R):
     assert np.array_equal(out, want)
 
 
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("M,N", [(512, 256), (520, 264), (1000, 24), (24, 1000), (3, 5), (257, 129), (1, 4096), (4096, 1), (1, 1)])
+def test_transposed_operand_with_an_unmatched_body_runs_the_generated_block_loop(rt, dtype, M, N):
+    """out[n, m] = min(a[m, n] - b[n, m], c[n]): no body of the library matches, so before generated code covered
+    transposed operands this ran op by op; whole blocks, ragged blocks and shapes whose strides rule 16-byte pieces out
+    (the kernel's element-wise loop), and extents of one (where the runtime's view of the collapsed domain has no transposed
+    operand left, while the kernel is still the 256-thread one), against numpy with rounding after every op."""
+    rng = np.random.default_rng(91)
+    a = rng.standard_normal((M, N)).astype(dtype)
+    b = rng.standard_normal((N, M)).astype(dtype)
+    c = rng.standard_normal(N).astype(dtype)
+    spec = descriptors.transposed_add_mul("f16" if dtype == np.float16 else "f32")
+    d = variant(spec, "transposed_sub_min", [descriptors.op("subf", "v0", "v1"), descriptors.op("minimumf", "%0", "v2")])
+    out = run_descriptor(rt, d, spec, [a, b, c], np.zeros((N, M), dtype), {"M": M, "N": N})
+    assert rt.last_launch_generated
+    want = np.minimum((a.T - b).astype(dtype), c[:, None]).astype(dtype)
+    assert out.tobytes() == want.tobytes()
+
+
 @pytest.mark.parametrize("unroll", [1, 2])
 @pytest.mark.parametrize("threads,block_dim", [(128, 0), (256, 0), (512, 5), (128, 100000)])
 def test_generated_gather_entries_and_grids(rt, unroll, threads, block_dim):
