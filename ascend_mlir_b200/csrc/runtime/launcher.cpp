@@ -636,11 +636,12 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
       if (Status s = resolveElementwiseGroup(d, g, tiling, args, et, domain, loads, store); !s) return s;
       int64_t elems = 1;
       for (int64_t e : domain) elems *= e;
-      {
-        // A group that reads an operand through a transposed view has the register-block loop in its kernel, which
-        // wants one CTA per tile of 2 x 4 warps x 4 x 8 blocks.  Whether it runs is the kernel's decision (alignment
-        // of what it is given); the grid below only has to be large enough for either loop, both walk their tiles
-        // with a grid stride.
+      // A group that reads an operand through a transposed view has the register-block loop in its kernel: one CTA
+      // per tile of 2 x 4 warps x 4 x 8 blocks when everything is aligned for 16-byte pieces (the kernel tests the
+      // same, on its own view of the dims), else one element per thread and step.  Both loops walk their tiles with a
+      // grid stride, so a grid that guesses the other loop costs time, not results.
+      int64_t transposedTiles = 0;
+      if (binding.ctasOf256Threads) {
         std::vector<ResolvedView> copies = loads;
         ResolvedView storeCopy = store;
         std::vector<int64_t> dom = domain;
@@ -653,21 +654,26 @@ Status launchGenerated(const LaunchDescriptor &d, const std::map<std::string, in
             dom.insert(dom.begin(), 1);
             for (auto *v : all) v->stride.insert(v->stride.begin(), 0);
           }
-          bool transposed = false;
-          for (const ResolvedView &v : copies)
-            if (dom[2] != 1 && v.stride[2] != 0 && v.stride[2] != 1 && v.stride[1] == 1) transposed = true;
-          if (transposed) {
-            const int64_t e = 16 / static_cast<int64_t>(dtypeBytes(d.dtype));
-            const int64_t blockTiles = dom[0] * ((dom[2] + 32 * e - 1) / (32 * e)) * ((dom[1] + 8 * e - 1) / (8 * e));
-            tiles = std::max(tiles, blockTiles);
+          const int64_t e = 16 / static_cast<int64_t>(dtypeBytes(d.dtype));
+          auto aligned = [&](const ResolvedView &v, int64_t sa, int64_t sb) {
+            return (reinterpret_cast<uintptr_t>(argAt(args, v)) & 15u) == 0 && sa % e == 0 && sb % e == 0;
+          };
+          bool transposed = false, blocks = aligned(storeCopy, storeCopy.stride[0], storeCopy.stride[1]);
+          for (const ResolvedView &v : copies) {
+            if (v.stride[2] == 1) blocks = blocks && aligned(v, v.stride[0], v.stride[1]);
+            else if (v.stride[2] != 0 && v.stride[1] == 1 && dom[2] != 1) { transposed = true; blocks = blocks && aligned(v, v.stride[0], v.stride[2]); }
+            else if (v.stride[2] != 0) blocks = false;
           }
+          if (transposed)
+            transposedTiles = blocks ? dom[0] * ((dom[2] + 32 * e - 1) / (32 * e)) * ((dom[1] + 8 * e - 1) / (8 * e))
+                                     : (elems + threads * 2 - 1) / (threads * 2);
         }
       }
       // the kernel counts 16-byte vectors (or elements, when something is unaligned) in 32 bits
       if (elems >= (1ll << 32) - (1 << 20)) return Status::error("[generated:unsupported] more than 2^32 elements in one group");
       totalElems += elems;
       const int64_t vecs = (elems + (16 / static_cast<int64_t>(dtypeBytes(d.dtype))) - 1) / (16 / static_cast<int64_t>(dtypeBytes(d.dtype)));
-      tiles = std::max(tiles, (vecs + threads * 2 - 1) / (threads * 2));
+      tiles = std::max(tiles, transposedTiles > 0 ? transposedTiles : (vecs + threads * 2 - 1) / (threads * 2));
     }
     if (totalElems == 0) return Status::success();
     int64_t grid = args.blockDim > 0 ? std::min<int64_t>(args.blockDim, tiles) : tiles;
