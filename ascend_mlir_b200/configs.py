@@ -196,6 +196,28 @@ def relu_broadcast_transpose_add(M: int = 8192, N: int = 8192, seed: int = 0) ->
     return make(d1)
 
 
+def transposed_add_mul(M: int = 8192, N: int = 8192, seed: int = 0) -> Workload:
+    """out[n, m] = (a[m, n] + b[n, m]) * c[n] on f16: `a` is read through a transposed view (register blocks of 8 x 8
+    elements, transposed in registers), `c` is constant along the inner dim.  Sharded by output rows: columns of `a`."""
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((M, N), dtype=np.float32).astype(np.float16)
+    b = rng.standard_normal((N, M), dtype=np.float32).astype(np.float16)
+    c = rng.standard_normal(N, dtype=np.float32).astype(np.float16)
+    spec = descriptors.transposed_add_mul("f16")
+
+    def make(a_, b_, c_):
+        n = b_.shape[0]
+        w = Workload("transposed_add_mul", spec, {"M": M, "N": n}, [a_, b_, c_], (n, M), np.dtype(np.float16),
+                     algorithmic_bytes=3 * n * M * 2 + n * 2, units=n, notes="one operand through a transposed view")
+        w.expected = lambda: ((a_.T + b_).astype(np.float16) * c_[:, None]).astype(np.float16)
+        w.sharder = lambda r, k: make(np.ascontiguousarray(a_[:, slice(*row_range(n, r, k))]),
+                                      np.ascontiguousarray(b_[slice(*row_range(n, r, k))]),
+                                      np.ascontiguousarray(c_[slice(*row_range(n, r, k))]))
+        return w
+
+    return make(a, b, c)
+
+
 # ---- generic chains: fused bodies the library has no straight-line kernel for ----------------------------------------
 # They run on the kernel generated for the group (codegen/kernel_source -> NVRTC); before the generator existed
 # they ran through the op-by-op interpreter at a third of the HBM roofline.
@@ -293,6 +315,7 @@ GENERIC_CHAINS: Dict[str, Callable[..., Workload]] = {
 EXTRA_CONFIGS: Dict[str, Callable[..., Workload]] = {
     "transpose_2d": transpose_2d,
     "relu_broadcast_transpose_add": relu_broadcast_transpose_add,
+    "transposed_add_mul": transposed_add_mul,
 }
 
 CONFIGS: Dict[str, Callable[..., Workload]] = {

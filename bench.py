@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 A step is one pass of one fused group over one batch of seeded synthetic input.  The default workload is the
-split-relu-broadcast-add-mul group (f16 [32,1024,2048] -> [32,1024,1024]); the other four benchmark groups, two
+split-relu-broadcast-add-mul group (f16 [32,1024,2048] -> [32,1024,1024]); the other four benchmark groups, three
 transpose-class groups and three generic chains (bodies that run on the kernel GENERATED for the group) are timed
 the same way and reported under "groups".
 
@@ -148,7 +148,7 @@ def all_workloads():
 def dtype_of(name):
     return {"elementwise_chain": "f32", "split_relu_broadcast_add_mul": "f16", "broadcast_add_reduce": "f32",
             "gather_elementwise": "bf16", "matmul_add_leakyrelu": "bf16", "transpose_2d": "f16",
-            "relu_broadcast_transpose_add": "f16"}.get(name, "f32")
+            "relu_broadcast_transpose_add": "f16", "transposed_add_mul": "f16"}.get(name, "f32")
 
 
 def cpu_sample(name: str):
@@ -176,6 +176,9 @@ def cpu_sample(name: str):
     if name == "relu_broadcast_transpose_add":
         w = configs.relu_broadcast_transpose_add()
         return w, (lambda: oracle.relu_bcast_transpose_add_f16(*w.inputs)), "full size, f16 [8192,8192]", None
+    if name == "transposed_add_mul":
+        w = configs.transposed_add_mul()
+        return w, w.expected, "full size, f16 [8192,8192] (numpy, one pass per op)", None
     if name in configs.GENERIC_CHAINS and name != "chain_torch_model":
         w = configs.GENERIC_CHAINS[name]()
         return w, w.expected, "full size, f32 [4096,4096] (numpy, one pass per op, all cores of its BLAS-free ufuncs)", None
@@ -212,7 +215,7 @@ def time_cpu(name: str, steps: int, warmup: int, budget_s: float = CPU_BUDGET_SE
     best = min(times)
     rec = {"value": work / best / scale, "unit": unit, "cores": oracle.num_threads(), "kind": "port", "sample": what,
            "seconds_per_pass": best, "passes": len(times)}
-    if name in configs.GENERIC_CHAINS:
+    if w.expected is not None:
         rec["cores"] = 1  # plain numpy ufuncs: one thread
     if extrapolated:
         rec["extrapolated"] = extrapolated

@@ -59,6 +59,23 @@ def test_shards_reassemble_to_the_unsharded_result(name, world):
     assert np.array_equal(np.concatenate(parts, axis=0), want)
 
 
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_transposed_operand_shards_by_columns_of_the_transposed_input(world):
+    """out[n, m] = (a[m, n] + b[n, m]) * c[n] sharded by output rows: a rank owns columns of `a`, rows of `b`, a piece
+    of `c`; the shards' results stack to the unsharded one and the tiling dims of a shard are (M, its rows)."""
+    full = configs.transposed_add_mul(M=24, N=37)
+    want = full.expected()
+    parts, units = [], 0
+    for r in range(world):
+        s = full.shard(r, world)
+        units += s.units
+        assert s.spec is full.spec and s.shape == {"M": 24, "N": s.units}
+        assert s.inputs[0].shape == (24, s.units) and s.inputs[0].flags["C_CONTIGUOUS"] and s.out_shape == (s.units, 24)
+        parts.append(s.expected())
+    assert units == full.units == 37
+    assert np.array_equal(np.concatenate(parts, axis=0).view(np.uint16), want.view(np.uint16))
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
