@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <sstream>
 
 namespace afir {
@@ -255,7 +256,7 @@ const char *kDependencyMarker =
 
 // ---- elementwise / broadcast / split / concat ------------------------------------------------------------------------
 bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t index, const TypeInfo &ti, std::ostringstream &bodies,
-                          std::ostringstream &kernel, std::string &why, bool &usesBlocks) {
+                          std::ostringstream &kernel, std::string &why, int &blockCtasPerSm) {
   const size_t rank = g.domain.size();
   if (rank == 0) { why = "empty iteration domain"; return false; }
   if (g.loads.empty() || g.loads.size() > static_cast<size_t>(kernels::kMaxViews)) { why = "group loads no view or too many"; return false; }
@@ -297,7 +298,17 @@ bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t 
     why = "a bare permutation runs on the library's transpose kernels";
     return false;
   }
-  if (transposedGroup) usesBlocks = true;
+  if (transposedGroup) {
+    // CTAs per SM the kernel is compiled for.  Three (80 registers) where the blocks of all views fit without spilling:
+    // a view that is not constant along the inner dim holds 16 bytes per block row, 8 rows of 16-bit elements or 4 of
+    // 32-bit ones (measured on (a^T + b) * c, f16 8192 x 8192: 64.0 us against 68.3 us at two CTAs per SM, the
+    // difference being the last, partly filled round of tiles).  Two (128 registers) for wider groups.
+    int fullViews = 0;
+    for (size_t i = 0; i < g.loads.size(); ++i)
+      if (!views[i].stride[2].isLiteral(0)) ++fullViews;
+    const int ctas = fullViews <= (ti.bytes == 2 ? 2 : 5) ? 3 : 2;
+    blockCtasPerSm = blockCtasPerSm == 0 ? ctas : std::min(blockCtasPerSm, ctas);
+  }
   const int ve = 16 / ti.bytes;
   const std::string bodyName = "FusedBody" + std::to_string(index);
   bodies << bodyStruct(bodyName, g.body, static_cast<int>(g.loads.size()), ti.integer) << "\n";
@@ -367,17 +378,18 @@ GeneratedKernel generateElementwise(const LaunchDescriptor &d) {
   if (!typeInfo(d.dtype, true, ti)) { out.whyNot = "element type"; return out; }
   if (d.groups.empty()) { out.whyNot = "no groups"; return out; }
   std::ostringstream bodies, kernel;
-  bool usesBlocks = false;
+  int blockCtasPerSm = 0;  // 0 = no group with a transposed operand
   for (size_t i = 0; i < d.groups.size(); ++i)
-    if (!emitElementwiseGroup(d, d.groups[i], i, ti, bodies, kernel, out.whyNot, usesBlocks)) return out;
+    if (!emitElementwiseGroup(d, d.groups[i], i, ti, bodies, kernel, out.whyNot, blockCtasPerSm)) return out;
+  const bool usesBlocks = blockCtasPerSm > 0;
   out.hasTransposedOperand = usesBlocks;
   std::ostringstream src;
   src << (usesBlocks ? "#include \"kernels/elementwise_blocks_skel.cuh\"\n" : "#include \"kernels/elementwise_skel.cuh\"\n") << kPreamble << kDependencyMarker
       << (usesBlocks ? "// Tells the runtime that this module's kernel is launched with CTAs of 256 threads.\nextern \"C\" __global__ void afir_ctas_of_256_threads() {}\n\n" : "")
       << tilingStruct(d) << "\n" << bodies.str()
-      // (a kernel with the register-block loop is launched with 256 threads, like the library's instantiations, which take
-      // 94-128 registers)
-      << signature(d, d.kernel, usesBlocks ? "__launch_bounds__(256)" : "__launch_bounds__(512)") << " {\n" << rowWindowPrologue()
+      // (a kernel with the register-block loop is launched with 256 threads, like the library's instantiations)
+      << signature(d, d.kernel, !usesBlocks ? "__launch_bounds__(512)" : blockCtasPerSm == 3 ? "__launch_bounds__(256, 3)" : "__launch_bounds__(256)")
+      << " {\n" << rowWindowPrologue()
       << kernel.str() << "}\n";
   out.source = src.str();
   out.entry = d.kernel;

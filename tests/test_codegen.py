@@ -148,7 +148,7 @@ def test_transposed_operand_gets_the_register_block_loop(tmp_path):
     on every side, transposed in registers) beside the element-wise one and picks at run time; CTAs of 256 threads."""
     r = kernel_source(EXAMPLES / "transposed_add.mlir")
     assert r.returncode == 0, r.stderr
-    assert "elementwiseBlocksTiles<" in r.stdout and "kViewTransposed" in r.stdout and "__launch_bounds__(256)" in r.stdout
+    assert "elementwiseBlocksTiles<" in r.stdout and "kViewTransposed" in r.stdout and "__launch_bounds__(256, 3)" in r.stdout
     for dtype in ("f16", "f32"):
         _, cubin, src = compiled(tmp_path, descriptors.transposed_add_mul(dtype))
         assert cubin[:4] == b"\x7fELF"
