@@ -299,10 +299,11 @@ bool emitElementwiseGroup(const LaunchDescriptor &d, const GroupSpec &g, size_t 
     return false;
   }
   if (transposedGroup) {
-    // CTAs per SM the kernel is compiled for.  Three (80 registers) where the blocks of all views fit without spilling:
-    // a view that is not constant along the inner dim holds 16 bytes per block row, 8 rows of 16-bit elements or 4 of
-    // 32-bit ones (measured on (a^T + b) * c, f16 8192 x 8192: 64.0 us against 68.3 us at two CTAs per SM, the
-    // difference being the last, partly filled round of tiles).  Two (128 registers) for wider groups.
+    // CTAs per SM the kernel is compiled for.  Three (a budget of 80 registers) where the blocks of all views fit
+    // without spilling: a view that is not constant along the inner dim holds 16 bytes per block row, 8 rows of 16-bit
+    // elements or 4 of 32-bit ones.  Two (up to 128 registers) for wider groups.  Measured on (a^T + b) * c, f16
+    // 8192 x 8192: 64.0 us with the budget of 80 stated against 68.3 us without (the run-time compiler then settled
+    // on 73 registers, three CTAs per SM as well, and issued fewer loads ahead of their first use).
     int fullViews = 0;
     for (size_t i = 0; i < g.loads.size(); ++i)
       if (!views[i].stride[2].isLiteral(0)) ++fullViews;
