@@ -212,8 +212,13 @@ struct PackI16 {
   __device__ __forceinline__ static PackI16 div(PackI16 a, PackI16 b) {
     return join(PackI32::divide(lo(a.x), lo(b.x)), PackI32::divide(hi(a.x), hi(b.x)));
   }
-  __device__ __forceinline__ static PackI16 max(PackI16 a, PackI16 b) { return {__vmaxs2(a.x, b.x)}; }
-  __device__ __forceinline__ static PackI16 min(PackI16 a, PackI16 b) { return {__vmins2(a.x, b.x)}; }
+  // (signed max / min lane by lane, for the same reason: no __vmaxs2 / __vmins2)
+  __device__ __forceinline__ static PackI16 max(PackI16 a, PackI16 b) {
+    return join(::max(lo(a.x), lo(b.x)), ::max(hi(a.x), hi(b.x)));
+  }
+  __device__ __forceinline__ static PackI16 min(PackI16 a, PackI16 b) {
+    return join(::min(lo(a.x), lo(b.x)), ::min(hi(a.x), hi(b.x)));
+  }
   __device__ __forceinline__ float lane(int i) const { return static_cast<float>(i ? hi(x) : lo(x)); }
 };
 
