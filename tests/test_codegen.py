@@ -158,6 +158,22 @@ def test_transposed_operand_gets_the_register_block_loop(tmp_path):
         assert "void afir_ctas_of_256_threads() {}" in src  # the runtime launches 256 threads whatever the tiling says
 
 
+def test_register_block_kernels_are_compiled_for_three_ctas_per_sm_where_the_blocks_fit(tmp_path):
+    """(a^T + b) * c keeps two views of 8 x 8 blocks in registers (c is one element per row): three CTAs per SM.  With
+    three row-major operands beside the transposed one, 16-bit blocks no longer fit in 80 registers: two CTAs per SM."""
+    _, _, src = compiled(tmp_path, descriptors.transposed_add_mul("f16"))
+    assert "__launch_bounds__(256, 3)" in src
+    dims = [("dim_arg0_0", "M"), ("dim_arg0_1", "N")]
+    dom = ["dim_arg0_1", "dim_arg0_0"]
+    loads = [{"arg": 0, "shape": ["dim_arg0_0", "dim_arg0_1"], "map": [1, 0]}] + [{"arg": i, "shape": dom, "map": [0, 1]} for i in (1, 2, 3)]
+    body = {"domain": dom, "loads": loads, "store": {"arg": 4, "shape": dom, "map": [0, 1]},
+            "body": [descriptors.op("addf", "v0", "v1"), descriptors.op("addf", "%0", "v2"), descriptors.op("mulf", "%1", "v3")]}
+    for dtype, bounds in (("f16", "__launch_bounds__(256) "), ("f32", "__launch_bounds__(256, 3) ")):
+        wide = descriptors._spec("four_operands", "elementwise", dtype, 4, 1, descriptors._EW_TILE, dims, body, descriptors._EW_LAUNCH)
+        _, cubin, src = compiled(tmp_path, wide)
+        assert cubin[:4] == b"\x7fELF" and bounds + "four_operands(" in src
+
+
 @pytest.mark.parametrize("example", ["elementwise_chain", "split_relu_broadcast_add_mul", "broadcast_add_reduce",
                                      "gather_elementwise", "integer_chain"])
 def test_every_generated_example_compiles_to_a_cubin(tmp_path, example):
