@@ -83,3 +83,20 @@ def test_reference_arm_prints_the_line_the_driver_parses():
 
 def bench_metric():
     return "fused_group_hbm_throughput"
+
+
+def test_reference_arm_under_torchrun_prints_once_and_every_rank_exits_zero():
+    """Launched like the GPU arm for N = 2: rank 0 alone times the CPU restatement and prints the line, the other rank
+    leaves without work, no process group is formed."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", str(port), str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+                        "--warmup", "1"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["cpu_baseline"]["value"] == line["value"]
