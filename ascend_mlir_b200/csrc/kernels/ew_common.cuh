@@ -200,7 +200,7 @@ struct PackI16 {
   // Wrapping add / subtract of both lanes, written out: the low 15 bits of each lane in one 32-bit operation that
   // cannot carry or borrow across the lane boundary, the top bits by exclusive or.  (Not __vadd2 / __vsub2: where
   // only the low lane of the result is used -- the element-by-element loops store the low lane of a splatted value --
-  // nvcc and NVRTC 12.9 for sm_100a returned wrong low lanes for them, e.g. x + 1 for __vsub2(x, 3 in both lanes);
+  // nvcc 12.9 and NVRTC 12.8 for sm_100a returned wrong low lanes for them, e.g. x + 1 for __vsub2(x, 3 in both lanes);
   // which of the two, and with a constant or a variable operand, depended on the surrounding code.)
   __device__ __forceinline__ static PackI16 add(PackI16 a, PackI16 b) {
     return {((a.x & 0x7fff7fffu) + (b.x & 0x7fff7fffu)) ^ ((a.x ^ b.x) & 0x80008000u)};
