@@ -44,7 +44,7 @@ CPP_SOURCES = ["common/json.cpp", "kernels/matmul_plan.cpp", "kernels/body_match
                "execution/task_graph.cpp", "execution/run_manifest.cpp", "execution/artifact_compiler.cpp",
                "execution/execution_session.cpp", "execution/resource_scheduler.cpp", "execution/global_scheduler.cpp",
                "execution/profile_retention.cpp",
-               "front/mlir_text.cpp", "front/group_analysis.cpp", "front/fused_generic.cpp", "runtime/capi.cpp", "runtime/rowsum_exchange.cpp", "runtime/peer_memory.cpp"]
+               "front/mlir_text.cpp", "front/group_analysis.cpp", "front/fused_generic.cpp", "front/shape_inference.cpp", "runtime/capi.cpp", "runtime/rowsum_exchange.cpp", "runtime/peer_memory.cpp"]
 # command-line tools (reference: tools/runtime-session, tools/autotuner), linked with the same objects
 TOOLS = {"runtime-session": "tools/runtime_session_main.cpp", "autotuner": "tools/autotuner_main.cpp",
          "afir-opt": "tools/afir_opt_main.cpp", "afir-translate": "tools/afir_translate_main.cpp"}

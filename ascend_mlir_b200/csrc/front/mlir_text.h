@@ -59,6 +59,7 @@ struct Op {
   int64_t dim = 0;
   // printing
   size_t srcBegin = 0, srcEnd = 0;    // span in the source text
+  size_t typesBegin = 0;              // afir ops, return: where the trailing type signature starts (it ends at srcEnd)
   size_t attrInsertPos = 0;           // where "attrs = {...}" / "{...}" can be inserted (0 = none)
   std::vector<std::pair<std::string, std::string>> addedAttrs;
   int line = 0;
@@ -73,6 +74,7 @@ struct Func {
   std::string name;
   std::vector<FuncArg> args;
   std::vector<Type> resultTypes;
+  size_t resultTypesBegin = 0, resultTypesEnd = 0;  // span of the result type(s) after "->", parentheses included (0 = none)
   std::vector<Op> ops;
   size_t attrInsertPos = 0;           // just before the body's '{'
   size_t attrDictPos = 0;             // position of the '{' of an existing "attributes {...}" (0 = none)

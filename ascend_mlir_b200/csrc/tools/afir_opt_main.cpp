@@ -12,8 +12,11 @@
 //                                       both record the group as afir.fused_group; groups whose views are slices of an
 //                                       argument (split / concat) and matmul epilogues keep their ops
 //   --convert-afir-to-cuda              afir.cuda_kernel_class / afir.cuda_launch (descriptor JSON) on the function
+//   --afir-shape-inference              result types of afir.add / sub / mul / div refined from their operands (numpy-style
+//                                       trailing-aligned broadcast), carried to the users, the return op and the
+//                                       function's result types (lib/Dialect/AFIR/Transforms/AFIRInferShapes.cpp:94-176)
 // Structural passes of upstream MLIR that do not change what the group computes (--canonicalize, --cse,
-// --afir-canonicalize, --afir-shape-inference, --linalg-fold-unit-extent-dims) verify and pass the module through.
+// --afir-canonicalize, --linalg-fold-unit-extent-dims) verify and pass the module through.
 //
 // The reference's device-lowering stages are accepted under their own names, so that its example scripts and its
 // torch pipeline (examples/*/run.sh, python/torch/framework/pipeline.py:_run_mlir_pipeline) drive this tool with
@@ -41,6 +44,7 @@
 
 #include "front/fused_generic.h"
 #include "front/group_analysis.h"
+#include "front/shape_inference.h"
 
 using namespace afir;
 using namespace afir::front;
@@ -59,8 +63,9 @@ std::string escapeForAttr(const std::string &s) {
 int main(int argc, char **argv) {
   const std::set<std::string> analysisPasses = {"mark-structured-ops", "annotate-ascendc-kernel-kind", "annotate-mix-matmul-semantics",
                                                 "linalg-fuse-elementwise-ops", "fuse-gather-elementwise", "convert-afir-to-cuda"};
-  const std::set<std::string> passThrough = {"canonicalize", "cse", "afir-canonicalize", "afir-shape-inference",
-                                             "linalg-fold-unit-extent-dims", "allow-unregistered-dialect"};
+  const std::set<std::string> passThrough = {"canonicalize", "cse", "afir-canonicalize", "linalg-fold-unit-extent-dims",
+                                             "allow-unregistered-dialect"};
+  const std::set<std::string> typePasses = {"afir-shape-inference"};
   // the reference's lowering stages (see the header comment)
   const std::set<std::string> loweringStages = {"one-shot-bufferize", "ascendc-buffer-placement", "linalg-to-ascendc",
                                                 "ascendc-parallelize", "ascendc-prepare-for-emit"};
@@ -77,13 +82,15 @@ int main(int argc, char **argv) {
       for (const auto &p : analysisPasses) std::cout << "  --" << p << "\n";
       for (const auto &p : scheduleStages) std::cout << "  --" << p << "\n";
       for (const auto &p : loweringStages) std::cout << "  --" << p << "\n";
+      for (const auto &p : typePasses) std::cout << "  --" << p << "\n";
       for (const auto &p : passThrough) std::cout << "  --" << p << "\n";
       return 0;
     } else if (a.size() > 1 && a[0] == '-' && a != "-") {
       std::string name = a.substr(a[1] == '-' ? 2 : 1);
       const size_t eq = name.find('=');  // --one-shot-bufferize=bufferize-function-boundaries=true ...: options are not needed here
       if (eq != std::string::npos) name = name.substr(0, eq);
-      if (!analysisPasses.count(name) && !passThrough.count(name) && !loweringStages.count(name) && !scheduleStages.count(name)) {
+      if (!analysisPasses.count(name) && !passThrough.count(name) && !loweringStages.count(name) && !scheduleStages.count(name) &&
+          !typePasses.count(name)) {
         std::cerr << "afir-opt: Unknown command line argument '" << a << "'\n";
         return 1;
       }
@@ -104,6 +111,10 @@ int main(int argc, char **argv) {
   }
   Module module;
   if (Status s = parseModule(text, module); !s) { std::cerr << (input.empty() ? "<stdin>" : input) << ": error: " << s.message() << "\n"; return 1; }
+
+  // types first: the analyses below then see the refined shapes
+  for (const auto &p : passes)
+    if (p == "afir-shape-inference") { inferAfirShapes(module); break; }
 
   bool needAnalysis = false;
   for (const auto &p : passes) needAnalysis = needAnalysis || analysisPasses.count(p) || loweringStages.count(p) || scheduleStages.count(p);

@@ -15,6 +15,7 @@
 #include "execution/execution_session.h"
 #include "execution/profile_retention.h"
 #include "execution/run_manifest.h"
+#include "front/shape_inference.h"
 #include "kernels/matmul_plan.h"
 #include "support/npy_io.h"
 #include "support/tiling_schema.h"
@@ -392,6 +393,47 @@ static void testMatmulPlanner() {
   EXPECT(!buildMatmulPlan(big, hints, 148, plan).empty(), "an unknown variant hint is refused");
 }
 
+// The shape rules of --afir-shape-inference (reference: lib/Dialect/AFIR/Ops/Basic/math.cpp:275-312 for the broadcast,
+// include/Utils/AFIRShapeInferUtils.h:80-125 for the join with the declared result type).
+static void testShapeInference() {
+  using front::inferBroadcastShape;
+  using front::joinShapes;
+  using Shape = std::vector<int64_t>;
+  Shape out;
+  EXPECT(inferBroadcastShape({{4, 1, 31}, {1, 30, 1}}, out) && out == Shape({4, 30, 31}), "the reference's lit case");
+  EXPECT(inferBroadcastShape({{8, -1}, {16}}, out) && out == Shape({8, 16}), "a later static extent replaces a dynamic one");
+  EXPECT(inferBroadcastShape({{16}, {8, -1}}, out) && out == Shape({8, 16}), "a later dynamic extent changes nothing");
+  EXPECT(inferBroadcastShape({{-1, 4}, {-1, 1}}, out) && out == Shape({-1, 4}), "unknown stays unknown");
+  EXPECT(inferBroadcastShape({{1, 1}, {1}}, out) && out == Shape({1, 1}), "all ones");
+  EXPECT(inferBroadcastShape({{}, {3}}, out) && out == Shape({3}), "rank 0 with rank 1");
+  EXPECT(inferBroadcastShape({{5, 7}}, out) && out == Shape({5, 7}), "one operand");
+  EXPECT(!inferBroadcastShape({{8, 4}, {8, 5}}, out), "static extents that differ do not broadcast");
+  EXPECT(!inferBroadcastShape({{2, 3}, {4, 1, 3}, {5, 3}}, out), "a conflict in a middle position of three operands");
+  EXPECT(joinShapes({-1, -1}, {8, 16}, out) && out == Shape({8, 16}), "a dynamic declaration takes the inference");
+  EXPECT(joinShapes({8, -1}, {-1, 16}, out) && out == Shape({8, 16}), "each side fills the other's unknowns");
+  EXPECT(joinShapes({8, 16}, {8, 16}, out) && out == Shape({8, 16}), "agreement");
+  EXPECT(!joinShapes({8, 7}, {8, 4}, out), "a declared extent that contradicts the inference");
+  EXPECT(!joinShapes({8}, {8, 4}, out), "ranks that differ");
+
+  // the pass itself: text in, replacements out, a second run finds nothing
+  front::Module m;
+  const std::string text = "func.func @f(%a: tensor<2x1xf32>, %b: tensor<3xf32>) -> (tensor<?x?xf32>) {\n"
+                           "  %0 = afir.add %a, %b : (tensor<2x1xf32>, tensor<3xf32>) -> tensor<?x?xf32>\n"
+                           "  return %0 : tensor<?x?xf32>\n}\n";
+  EXPECT(static_cast<bool>(front::parseModule(text, m)), "parse");
+  int refined = 0;
+  front::inferAfirShapes(m, &refined);
+  const std::string printed = front::printModule(m);
+  EXPECT(refined == 1 && m.replacements.size() == 3, "one op refined: op, return and function result rewritten");
+  EXPECT(printed.find("-> tensor<2x3xf32> {") != std::string::npos && printed.find("return %0 : tensor<2x3xf32>\n}") != std::string::npos &&
+             printed.find("(tensor<2x1xf32>, tensor<3xf32>) -> tensor<2x3xf32>\n") != std::string::npos,
+         "printed module carries the refined types: " + printed);
+  front::Module again;
+  EXPECT(static_cast<bool>(front::parseModule(printed, again)), "the printed module parses");
+  front::inferAfirShapes(again, &refined);
+  EXPECT(refined == 0 && again.replacements.empty(), "idempotent");
+}
+
 int main() {
   char tmpl[] = "/tmp/afir-runtime-test-XXXXXX";
   if (!::mkdtemp(tmpl)) return 99;
@@ -403,6 +445,7 @@ int main() {
   testManifestAndSession();
   testProfileRetention();
   testMatmulPlanner();
+  testShapeInference();
   std::cout << g_pass << " passed, " << g_fail << " failed\n";
   return g_fail;
 }

@@ -222,6 +222,79 @@ def test_afir_broadcast_follows_numpy_trailing_alignment():
     assert body_of(d) == [("addf", "v0", "v1"), ("mulf", "%0", "v2")]
 
 
+def test_shape_inference_refines_result_types_like_the_reference_pass():
+    """--afir-shape-inference on the first function of the reference's test/Dialect/AFIR/Transforms/shapeInference.mlir
+    (tensor<4x1x31xf32> with tensor<1x30x1xf32>; its FileCheck line wants "-> tensor<4x30x31xf32>"): every op result,
+    the operand types of the users, the return op and the function's result type carry the inferred shape."""
+    text = """func.func @HashCopyAscGraph(%arg0: tensor<4x1x31xf32>, %arg1: tensor<1x30x1xf32>) -> tensor<?x?x?xf32> {
+    %2 = afir.add %arg0, %arg1 : (tensor<4x1x31xf32>, tensor<1x30x1xf32>) -> tensor<?x?x?xf32>
+    %3 = afir.mul %2, %arg1 : (tensor<?x?x?xf32>, tensor<1x30x1xf32>) -> tensor<?x?x?xf32>
+    %4 = afir.sub %arg1, %3 : (tensor<1x30x1xf32>, tensor<?x?x?xf32>) -> tensor<?x?x?xf32>
+    return %4 : tensor<?x?x?xf32>
+  }
+"""
+    r = opt("--afir-shape-inference", "-", stdin=text)
+    assert r.returncode == 0, r.stderr
+    out = r.stdout
+    assert out.count("-> tensor<4x30x31xf32>") == 4 and "?" not in out
+    assert "%3 = afir.mul %2, %arg1 : (tensor<4x30x31xf32>, tensor<1x30x1xf32>) -> tensor<4x30x31xf32>" in out
+    assert "%4 = afir.sub %arg1, %3 : (tensor<1x30x1xf32>, tensor<4x30x31xf32>) -> tensor<4x30x31xf32>" in out
+    assert "return %4 : tensor<4x30x31xf32>\n  }" in out
+    # a second run changes nothing
+    again = opt("--afir-shape-inference", "-", stdin=out)
+    assert again.returncode == 0 and again.stdout == out
+
+
+def test_shape_inference_rules_for_ranks_dynamic_extents_and_conflicts():
+    """Trailing alignment across ranks; a dynamic extent yields to a static one from another operand whatever the order;
+    extents that stay unknown stay '?'; an op whose operands do not broadcast, or whose declared result contradicts the
+    inference, keeps its types (the reference's pass skips such an op without failing)."""
+    text = """func.func @ranks(%a: tensor<8x?xf16>, %b: tensor<16xf16>, %c: tensor<?x?xf16>) -> tensor<?x?xf16> {
+    %0 = afir.mul %a, %b : (tensor<8x?xf16>, tensor<16xf16>) -> tensor<?x?xf16>
+    %1 = afir.div %c, %0 : (tensor<?x?xf16>, tensor<?x?xf16>) -> tensor<?x?xf16>
+    return %1 : tensor<?x?xf16>
+}
+func.func @unknown(%a: tensor<?x4xi32>, %b: tensor<?x1xi32>) -> tensor<?x?xi32> {
+    %0 = afir.add %a, %b : (tensor<?x4xi32>, tensor<?x1xi32>) -> tensor<?x?xi32>
+    return %0 : tensor<?x?xi32>
+}
+func.func @conflict(%a: tensor<8x4xf32>, %b: tensor<8x5xf32>) -> tensor<?x?xf32> {
+    %0 = afir.add %a, %b : (tensor<8x4xf32>, tensor<8x5xf32>) -> tensor<?x?xf32>
+    return %0 : tensor<?x?xf32>
+}
+func.func @contradiction(%a: tensor<8x4xf32>, %b: tensor<8x4xf32>) -> tensor<8x7xf32> {
+    %0 = afir.add %a, %b : (tensor<8x4xf32>, tensor<8x4xf32>) -> tensor<8x7xf32>
+    return %0 : tensor<8x7xf32>
+}
+"""
+    r = opt("--afir-shape-inference", "-", stdin=text)
+    assert r.returncode == 0, r.stderr
+    out = r.stdout
+    assert "%0 = afir.mul %a, %b : (tensor<8x?xf16>, tensor<16xf16>) -> tensor<8x16xf16>" in out
+    assert "%1 = afir.div %c, %0 : (tensor<?x?xf16>, tensor<8x16xf16>) -> tensor<8x16xf16>" in out
+    assert "@ranks(%a: tensor<8x?xf16>, %b: tensor<16xf16>, %c: tensor<?x?xf16>) -> tensor<8x16xf16> {" in out
+    assert "%0 = afir.add %a, %b : (tensor<?x4xi32>, tensor<?x1xi32>) -> tensor<?x4xi32>" in out and "-> tensor<?x4xi32> {" in out
+    assert "(tensor<8x4xf32>, tensor<8x5xf32>) -> tensor<?x?xf32>" in out and "return %0 : tensor<?x?xf32>" in out
+    assert "(tensor<8x4xf32>, tensor<8x4xf32>) -> tensor<8x7xf32>" in out
+
+
+def test_shape_inference_before_the_conversion_gives_literal_extents(tmp_path):
+    src = tmp_path / "chain.mlir"
+    src.write_text("""func.func @chain(%a: tensor<64x1xf32>, %b: tensor<1x256xf32>) -> tensor<?x?xf32> {
+  %0 = afir.add %a, %b : (tensor<64x1xf32>, tensor<1x256xf32>) -> tensor<?x?xf32>
+  %1 = afir.mul %0, %b : (tensor<?x?xf32>, tensor<1x256xf32>) -> tensor<?x?xf32>
+  return %1 : tensor<?x?xf32>
+}
+""")
+    refined = tmp_path / "refined.mlir"
+    r = opt("--afir-shape-inference", src, "-o", refined)
+    assert r.returncode == 0, r.stderr
+    assert "-> tensor<64x256xf32> {" in refined.read_text()
+    d = translate(refined)
+    assert d["kernel_class"] == "elementwise" and d["domain"] == [64, 256]
+    assert [v["map"] for v in d["loads"]] == [[0, -1], [-1, 1]] and body_of(d) == [("addf", "v0", "v1"), ("mulf", "%0", "v1")]
+
+
 @pytest.mark.skipif(REFERENCE is None or not REFERENCE.exists(), reason="AFIR_REFERENCE_EXAMPLES does not name the reference's examples/")
 @pytest.mark.parametrize("example,cls", [("add-broadcast-concat", "elementwise"), ("broadcast-add-reduce", "row_reduce"),
                                          ("gather-elementwise-fusion", "gather"), ("matmul-add-leakyrelu", "matmul"),

@@ -45,7 +45,7 @@ def test_cpp_checks_under_address_and_undefined_behaviour_sanitizers(tmp_path):
                                "execution/global_scheduler.cpp", "execution/output_comparator.cpp",
                                "execution/profile_retention.cpp", "execution/resource_scheduler.cpp",
                                "execution/run_manifest.cpp", "execution/task_graph.cpp", "front/group_analysis.cpp", "front/fused_generic.cpp",
-                               "front/mlir_text.cpp", "runtime/descriptor.cpp", "support/npy_io.cpp",
+                               "front/mlir_text.cpp", "front/shape_inference.cpp", "runtime/descriptor.cpp", "support/npy_io.cpp",
                                "support/tiling_schema.cpp")]
     objs = [str(o) for o in sorted((ROOT / "ascend_mlir_b200" / "build").glob("*.o"))
             if (o.name.startswith("kernels_") and o.name != "kernels_body_match.cpp.o")
