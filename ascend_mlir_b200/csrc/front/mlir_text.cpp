@@ -329,6 +329,8 @@ private:
   Status func();
   Status op(Op &o, bool inBody);
   Status generic(Op &o);
+  std::string unitIn(size_t from) const;
+  std::string unitInDict(size_t begin, size_t end) const;
   Status opList(std::vector<Op> &ops, bool inBody);
 };
 

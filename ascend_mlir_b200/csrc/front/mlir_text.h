@@ -51,6 +51,7 @@ struct Op {
   std::vector<AffineMap> maps;
   std::vector<std::string> iterators;
   int numIns = 0;                     // operands[0..numIns) are ins, the rest outs
+  std::string unit;                   // value of an ascendc.unit attribute on the op ("AiCore.Cube", "AiCore.Vector"), if any
   std::vector<std::string> blockArgs;
   std::vector<Type> blockArgTypes;
   std::vector<Op> body;

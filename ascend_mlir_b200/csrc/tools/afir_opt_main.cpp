@@ -2,7 +2,10 @@
 // passes and prints the module.  The pass names are the reference's (tools/afir-opt/afir-opt.cpp:28-50 registers
 // them on MlirOptMain) plus --convert-afir-to-cuda, the sibling of its AFIRToASCIR conversion:
 //   --mark-structured-ops               gather_dim / embedding_dim on gather generics
-//   --annotate-ascendc-kernel-kind      ascendc.kernel_kind = "vec" | "cube" | "mix" on the function
+//   --annotate-ascendc-kernel-kind      ascendc.kernel_kind = "vec" | "cube" | "mix" on the function: from the ops'
+//                                       ascendc.unit attributes where a lowering stage has set them (the reference's rule,
+//                                       lib/Conversion/MarkStructuredOps/AnnotateAscendCKernelKindPass.cpp:46-82: Cube and
+//                                       Vector units together = "mix"), else from the fused group
 //   --annotate-mix-matmul-semantics     abi_matmul_* attributes (epilogue kind, bias, layouts) on matmul functions
 //   --linalg-fuse-elementwise-ops       an elementwise / broadcast / reduction chain of generics becomes ONE generic with
 //                                       the fused body (what the upstream pass leaves behind)
@@ -123,9 +126,39 @@ int main(int argc, char **argv) {
       std::cerr << (input.empty() ? "<stdin>" : input) << ": error: --transform-interpreter: the module holds no transform.named_sequence\n";
       return 1;
     }
+  // Functions whose ops carry ascendc.unit attributes (the buffer-level form a lowering stage leaves behind) get their
+  // kernel kind from those; such a function is not a fused group on tensors and the group analysis is not asked.
+  std::set<std::string> kindFromUnits;
+  for (const auto &p : passes) {
+    if (p != "annotate-ascendc-kernel-kind") continue;
+    for (Func &f : module.funcs) {
+      bool cube = false, vector = false, any = false;
+      std::string bad;
+      std::vector<const Op *> work;
+      for (const Op &o : f.ops) work.push_back(&o);
+      while (!work.empty()) {
+        const Op *o = work.back();
+        work.pop_back();
+        for (const Op &inner : o->body) work.push_back(&inner);
+        if (o->unit.empty()) continue;
+        any = true;
+        if (o->unit == "AiCore.Cube") cube = true;
+        else if (o->unit == "AiCore.Vector") vector = true;
+        else if (bad.empty()) bad = "line " + std::to_string(o->line) + ": unsupported ascendc.unit value for kernel kind: " + o->unit;
+      }
+      if (!bad.empty()) { std::cerr << (input.empty() ? "<stdin>" : input) << ": error: " << bad << "\n"; return 1; }
+      if (!any || kindFromUnits.count(f.name)) continue;
+      f.addedAttrs.push_back({"ascendc.kernel_kind", cube && vector ? "\"mix\"" : cube ? "\"cube\"" : "\"vec\""});
+      kindFromUnits.insert(f.name);
+    }
+  }
+  bool onlyKind = true;  // no other analysis pass asked for
+  for (const auto &p : passes) onlyKind = onlyKind && !((analysisPasses.count(p) && p != "annotate-ascendc-kernel-kind") || loweringStages.count(p) || scheduleStages.count(p));
+
   std::set<std::string> rewritten;
   if (needAnalysis) {
     for (Func &f : module.funcs) {
+      if (onlyKind && kindFromUnits.count(f.name)) continue;
       GroupAnalysis ga;
       if (Status s = analyzeFunction(module, f, ga); !s) { std::cerr << (input.empty() ? "<stdin>" : input) << ": error: " << s.message() << "\n"; return 1; }
       for (const auto &p : passes) {
@@ -133,7 +166,7 @@ int main(int argc, char **argv) {
           for (const auto &oa : ga.opAttrs)
             for (const auto &kv : oa.second) f.ops[oa.first].addedAttrs.push_back(kv);
         } else if (p == "annotate-ascendc-kernel-kind") {
-          f.addedAttrs.push_back(ga.funcAttrs.front());
+          if (!kindFromUnits.count(f.name)) f.addedAttrs.push_back(ga.funcAttrs.front());
         } else if (p == "annotate-mix-matmul-semantics") {
           for (size_t i = 1; i < ga.funcAttrs.size(); ++i) f.addedAttrs.push_back(ga.funcAttrs[i]);
         } else if (p == "linalg-fuse-elementwise-ops" || p == "fuse-gather-elementwise") {

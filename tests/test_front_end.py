@@ -222,6 +222,48 @@ def test_afir_broadcast_follows_numpy_trailing_alignment():
     assert body_of(d) == [("addf", "v0", "v1"), ("mulf", "%0", "v2")]
 
 
+def test_kernel_kind_follows_the_units_a_lowering_stage_assigned():
+    """--annotate-ascendc-kernel-kind on buffer-level functions whose ops carry ascendc.unit (what the reference's
+    test/Conversion/annotate-ascendc-kernel-kind.mlir feeds the pass): Cube only = "cube", Vector only = "vec", both =
+    "mix"; the attribute may sit after the op name, in linalg.generic's dictionary or in its trailing attrs; a unit
+    the rule does not know is an error; a function without units is classified from its fused group as before."""
+    copy = """linalg.generic {UNIT indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0, d1)>],
+      iterator_types = ["parallel", "parallel"]} ins(%src : memref<8x16xf32>) outs(%dst : memref<8x16xf32>) TRAILING {
+    ^bb0(%x: f32, %y: f32):
+      linalg.yield %x : f32
+    }"""
+    text = f"""func.func @product(%a: memref<8x8xf16>, %b: memref<8x16xf16>, %c: memref<8x16xf32>) {{
+  linalg.matmul {{ascendc.unit = "AiCore.Cube"}} ins(%a, %b : memref<8x8xf16>, memref<8x16xf16>) outs(%c : memref<8x16xf32>)
+  return
+}}
+func.func @copy_front(%src: memref<8x16xf32>, %dst: memref<8x16xf32>) {{
+  {copy.replace("UNIT", 'ascendc.unit = "AiCore.Vector",').replace("TRAILING", "")}
+  return
+}}
+func.func @copy_trailing(%src: memref<8x16xf32>, %dst: memref<8x16xf32>) {{
+  {copy.replace("UNIT", "").replace("TRAILING", 'attrs = {ascendc.unit = "AiCore.Vector"}')}
+  return
+}}
+func.func @both(%a: memref<8x8xf16>, %b: memref<8x16xf16>, %c: memref<8x16xf32>, %src: memref<8x16xf32>, %dst: memref<8x16xf32>) {{
+  linalg.matmul {{ascendc.unit = "AiCore.Cube"}} ins(%a, %b : memref<8x8xf16>, memref<8x16xf16>) outs(%c : memref<8x16xf32>)
+  {copy.replace("UNIT", 'ascendc.unit = "AiCore.Vector",').replace("TRAILING", "")}
+  return
+}}
+"""
+    r = opt("--annotate-ascendc-kernel-kind", "-", stdin=text)
+    assert r.returncode == 0, r.stderr
+    kinds = {}
+    for line in r.stdout.splitlines():
+        if line.startswith("func.func @"):
+            kinds[line.split("@")[1].split("(")[0]] = line.split('ascendc.kernel_kind = "')[1].split('"')[0]
+    assert kinds == {"product": "cube", "copy_front": "vec", "copy_trailing": "vec", "both": "mix"}
+    bad = opt("--annotate-ascendc-kernel-kind", "-", stdin=text.replace("AiCore.Cube", "AiCore.Scalar", 1))
+    assert bad.returncode == 1 and "unsupported ascendc.unit value for kernel kind: AiCore.Scalar" in bad.stderr
+    # tensor-level groups without units: from the group, as before
+    r = opt("--annotate-ascendc-kernel-kind", EXAMPLES / "matmul_add_leakyrelu.mlir")
+    assert r.returncode == 0 and 'ascendc.kernel_kind = "mix"' in r.stdout
+
+
 def test_shape_inference_refines_result_types_like_the_reference_pass():
     """--afir-shape-inference on the first function of the reference's test/Dialect/AFIR/Transforms/shapeInference.mlir
     (tensor<4x1x31xf32> with tensor<1x30x1xf32>; its FileCheck line wants "-> tensor<4x30x31xf32>"): every op result,
