@@ -114,9 +114,24 @@ public:
         tiling.clear();
         for (const TilingField &f : desc.tiling) {
           auto it = named.find(f.name);
-          if (it == named.end() && f.name.compare(0, 7, "dim_arg") == 0)
-            return Status::error("[cuda:bindings] tiling params missing field: " + f.name + " (a dimension of kernel '" + desc.kernel + "')");
-          const int64_t v = it == named.end() ? 0 : it->second;
+          int64_t v = it == named.end() ? 0 : it->second;
+          if (it == named.end() && f.name.compare(0, 7, "dim_arg") == 0) {
+            // dim_arg<N>_<D> is extent D of kernel argument N (inputs, then outputs): a dimension the manifest's
+            // schema does not carry (the reference's kernel derives an output's extents from its inputs') is read
+            // off the tensor bound to that argument
+            const size_t us = f.name.find('_', 7);
+            char *end = nullptr;
+            const long argIndex = us == std::string::npos ? -1 : std::strtol(f.name.c_str() + 7, &end, 10);
+            const bool argOk = us != std::string::npos && end == f.name.c_str() + us && argIndex >= 0;
+            const long dimIndex = argOk ? std::strtol(f.name.c_str() + us + 1, &end, 10) : -1;
+            const bool dimOk = argOk && *end == '\0' && end != f.name.c_str() + us + 1 && dimIndex >= 0;
+            const NDArray *bound = nullptr;
+            if (dimOk && static_cast<size_t>(argIndex) < inputs.size()) bound = &inputs[argIndex];
+            else if (dimOk && static_cast<size_t>(argIndex) < inputs.size() + outputs.size()) bound = &outputs[argIndex - inputs.size()];
+            if (!bound || static_cast<size_t>(dimIndex) >= bound->shape.size())
+              return Status::error("[cuda:bindings] tiling params missing field: " + f.name + " (a dimension of kernel '" + desc.kernel + "')");
+            v = bound->shape[dimIndex];
+          }
           uint8_t buf[8];
           if (f.bytes == 4) {
             const int32_t w = static_cast<int32_t>(v);

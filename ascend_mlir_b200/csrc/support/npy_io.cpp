@@ -118,11 +118,32 @@ Status loadNpy(const std::string &path, NDArray &out) {
   else if (descr == "<i8" || descr == "=i8") out.dtype = NpyDType::INT64;
   else if (descr == "<i2" || descr == "=i2") out.dtype = NpyDType::INT16;
   else return Status::error("Unsupported dtype '" + descr + "': " + path);
-  if (headerField(header, "fortran_order").find("True") != std::string::npos)
-    return Status::error("Fortran-ordered arrays are not supported: " + path);
+  const bool fortran = headerField(header, "fortran_order").find("True") != std::string::npos;
   out.allocate();
   f.read(reinterpret_cast<char *>(out.bytes.data()), static_cast<std::streamsize>(out.bytes.size()));
   if (static_cast<size_t>(f.gcount()) != out.bytes.size()) return Status::error("Truncated data in: " + path);
+  // A column-major file (numpy writes one for, e.g., the result of indexing columns with an index array: the
+  // reference's gather example saves its expected output that way) is brought into row-major order, which is what
+  // every consumer of an NDArray assumes.  The reference's reader takes the bytes as they come
+  // (lib/Runtime/Support/NpyIO.cpp:17-120 never looks at fortran_order) and so compares against permuted data.
+  if (fortran && out.shape.size() > 1 && out.numElements() > 1) {
+    const size_t eb = npyDTypeBytes(out.dtype), rank = out.shape.size();
+    std::vector<uint8_t> rowMajor(out.bytes.size());
+    std::vector<size_t> columnStride(rank, 1);  // element stride of every dim in the file's order
+    for (size_t d = 1; d < rank; ++d) columnStride[d] = columnStride[d - 1] * static_cast<size_t>(out.shape[d - 1]);
+    std::vector<int64_t> index(rank, 0);
+    size_t from = 0;  // offset of `index` in the file's order, kept up to date while the row-major index advances
+    for (size_t to = 0, n = out.numElements(); to < n; ++to) {
+      std::memcpy(rowMajor.data() + to * eb, out.bytes.data() + from * eb, eb);
+      for (size_t d = rank; d-- > 0;) {
+        from += columnStride[d];
+        if (++index[d] < out.shape[d]) break;
+        from -= columnStride[d] * static_cast<size_t>(out.shape[d]);
+        index[d] = 0;
+      }
+    }
+    out.bytes.swap(rowMajor);
+  }
   return Status::success();
 }
 

@@ -19,7 +19,8 @@
 //                                       trailing-aligned broadcast), carried to the users, the return op and the
 //                                       function's result types (lib/Dialect/AFIR/Transforms/AFIRInferShapes.cpp:94-176)
 // Structural passes of upstream MLIR that do not change what the group computes (--canonicalize, --cse,
-// --afir-canonicalize, --linalg-fold-unit-extent-dims) verify and pass the module through.
+// --afir-canonicalize, --linalg-fold-unit-extent-dims, --linalg-generalize-named-ops: the named ops of the subset,
+// linalg.matmul and linalg.fill, are analysed as they are) verify and pass the module through.
 //
 // The reference's device-lowering stages are accepted under their own names, so that its example scripts and its
 // torch pipeline (examples/*/run.sh, python/torch/framework/pipeline.py:_run_mlir_pipeline) drive this tool with
@@ -30,8 +31,12 @@
 //                                       afir.tile_sizes, afir.schedule_annotations); no loops are materialised -- the
 //                                       sm_100a kernel is generated from the fused group as a whole and its launch
 //                                       parameters are tuned through the tiling space, not through scf.for nests
-//   --one-shot-bufferize[=opts], --ascendc-buffer-placement, --linalg-to-ascendc, --ascendc-parallelize,
-//   --ascendc-prepare-for-emit          bufferisation, on-chip buffer placement, AscendC op selection, multi-core
+//   --transform-preload-library=transform-library-paths=<file>[,...]
+//                                       the schedule lives in a file of its own: its named sequences are read as if they
+//                                       stood beside the payload
+//   --one-shot-bufferize[=opts], --ascendc-buffer-placement, --ascendc-fold-concat-alloc, --linalg-to-ascendc,
+//   --ascendc-parallelize, --ascendc-prepare-for-emit
+//                                       bufferisation, on-chip buffer placement, AscendC op selection, multi-core
 //                                       dispatch and emit preparation have no counterpart on this target (global
 //                                       memory is addressed directly, the grid is the dispatch): each verifies that
 //                                       every function is still one fused group and records itself in afir.stages
@@ -67,13 +72,14 @@ int main(int argc, char **argv) {
   const std::set<std::string> analysisPasses = {"mark-structured-ops", "annotate-ascendc-kernel-kind", "annotate-mix-matmul-semantics",
                                                 "linalg-fuse-elementwise-ops", "fuse-gather-elementwise", "convert-afir-to-cuda"};
   const std::set<std::string> passThrough = {"canonicalize", "cse", "afir-canonicalize", "linalg-fold-unit-extent-dims",
-                                             "allow-unregistered-dialect"};
+                                             "linalg-generalize-named-ops", "allow-unregistered-dialect", "transform-preload-library"};
   const std::set<std::string> typePasses = {"afir-shape-inference"};
   // the reference's lowering stages (see the header comment)
-  const std::set<std::string> loweringStages = {"one-shot-bufferize", "ascendc-buffer-placement", "linalg-to-ascendc",
-                                                "ascendc-parallelize", "ascendc-prepare-for-emit"};
+  const std::set<std::string> loweringStages = {"one-shot-bufferize", "ascendc-buffer-placement", "ascendc-fold-concat-alloc",
+                                                "linalg-to-ascendc", "ascendc-parallelize", "ascendc-prepare-for-emit"};
   const std::set<std::string> scheduleStages = {"transform-interpreter", "canonicalize-cann-signature"};
   std::vector<std::string> passes;
+  std::vector<std::string> scheduleLibraries;  // --transform-preload-library=transform-library-paths=a.mlir[,b.mlir]
   std::string input, output;
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
@@ -91,7 +97,23 @@ int main(int argc, char **argv) {
     } else if (a.size() > 1 && a[0] == '-' && a != "-") {
       std::string name = a.substr(a[1] == '-' ? 2 : 1);
       const size_t eq = name.find('=');  // --one-shot-bufferize=bufferize-function-boundaries=true ...: options are not needed here
+      const std::string options = eq != std::string::npos ? name.substr(eq + 1) : std::string();
       if (eq != std::string::npos) name = name.substr(0, eq);
+      if (name == "transform-preload-library") {
+        const std::string key = "transform-library-paths=";
+        const size_t at = options.find(key);
+        if (at == std::string::npos) { std::cerr << "afir-opt: --transform-preload-library needs transform-library-paths=<file>[,<file>]\n"; return 1; }
+        std::string list = options.substr(at + key.size());
+        const size_t stop = list.find(' ');
+        if (stop != std::string::npos) list = list.substr(0, stop);
+        for (size_t b = 0; b <= list.size();) {
+          const size_t c = list.find(',', b);
+          const std::string one = list.substr(b, c == std::string::npos ? std::string::npos : c - b);
+          if (!one.empty()) scheduleLibraries.push_back(one);
+          if (c == std::string::npos) break;
+          b = c + 1;
+        }
+      }
       if (!analysisPasses.count(name) && !passThrough.count(name) && !loweringStages.count(name) && !scheduleStages.count(name) &&
           !typePasses.count(name)) {
         std::cerr << "afir-opt: Unknown command line argument '" << a << "'\n";
@@ -114,6 +136,22 @@ int main(int argc, char **argv) {
   }
   Module module;
   if (Status s = parseModule(text, module); !s) { std::cerr << (input.empty() ? "<stdin>" : input) << ": error: " << s.message() << "\n"; return 1; }
+
+  // Schedules kept in files of their own (the reference's gather example preloads step2_transform.mlir as a transform
+  // library and runs the interpreter on the payload file): their named sequences join the module's; nothing of a
+  // library is printed.
+  for (const std::string &lib : scheduleLibraries) {
+    std::ifstream is(lib);
+    if (!is) { std::cerr << "afir-opt: cannot open transform library " << lib << "\n"; return 1; }
+    const std::string libText((std::istreambuf_iterator<char>(is)), std::istreambuf_iterator<char>());
+    Module library;
+    if (Status s = parseModule(libText, library); !s) { std::cerr << lib << ": error: " << s.message() << "\n"; return 1; }
+    if (library.schedules.empty()) { std::cerr << lib << ": error: the transform library holds no transform.named_sequence\n"; return 1; }
+    for (TransformSchedule sched : library.schedules) {
+      sched.srcBegin = sched.srcEnd = 0;  // not part of this module's text
+      module.schedules.push_back(sched);
+    }
+  }
 
   // types first: the analyses below then see the refined shapes
   for (const auto &p : passes)

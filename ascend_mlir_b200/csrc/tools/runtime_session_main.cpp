@@ -55,8 +55,16 @@ void usage() {
                "  --run                   Execute the prepared task graph runtime session\n";
 }
 
-void printRunError(const ExecutionSession &session, const SessionRunSummary &summary) {
-  std::cerr << "session.backend=" << session.backendName() << "\n";
+// `asked`: the backend name of the manifest.  The reference's names "sim" and "npu" are accepted for this backend, and
+// session.backend repeats the name that was asked for (its example scripts look for the line session.backend=sim);
+// session.device_backend says what ran.
+void printBackend(std::ostream &os, const ExecutionSession &session, const std::string &asked) {
+  os << "session.backend=" << (asked.empty() ? session.backendName() : asked) << "\n";
+  if (!asked.empty() && asked != session.backendName()) os << "session.device_backend=" << session.backendName() << "\n";
+}
+
+void printRunError(const ExecutionSession &session, const std::string &asked, const SessionRunSummary &summary) {
+  printBackend(std::cerr, session, asked);
   std::cerr << "session.result=error\n";
   if (summary.validationRan && summary.errorStage == "validate") std::cerr << "session.validation=fail\n";
   if (!summary.errorStage.empty()) std::cerr << "session.error_stage=" << summary.errorStage << "\n";
@@ -78,11 +86,13 @@ int main(int argc, char **argv) {
   if (args.help()) { usage(); return 0; }
 
   std::string backendName = "cuda";
+  std::string askedBackend;  // from the manifest, when there is one
   TaskGraph graph;
   if (args.has("run-manifest")) {
     RunManifestSpec spec;
     if (Status s = loadRunManifest(args.get("run-manifest"), spec); !s) { std::cerr << "Error: " << s.message() << "\n"; return 4; }
     if (Status s = buildTaskGraph(spec, graph); !s) { std::cerr << "Error: " << s.message() << "\n"; return 4; }
+    askedBackend = spec.backendName;
   } else {
     const bool hasRoot = args.has("artifact-root"), hasKernel = args.has("kernel");
     if (hasRoot == hasKernel) { std::cerr << "Error: provide exactly one of --artifact-root or --kernel\n"; return 4; }
@@ -138,7 +148,7 @@ int main(int argc, char **argv) {
 
   SessionRunSummary summary = session.run(graph);
   if (!summary.success) {
-    printRunError(session, summary);
+    printRunError(session, askedBackend, summary);
     return 2;
   }
   std::string retainedSummary;
@@ -150,7 +160,7 @@ int main(int argc, char **argv) {
       summary.success = false;
       summary.errorStage = "profiling";
       summary.errorMessage = s.message();
-      printRunError(session, summary);
+      printRunError(session, askedBackend, summary);
       return 2;
     }
     summary.profileTrace = kept.trace;
@@ -158,7 +168,7 @@ int main(int argc, char **argv) {
     for (const ProfileEvent &ev : kept.trace.events) summary.profileArtifactPaths.push_back(ev.artifactPath);
     retainedSummary = kept.summaryPath;
   }
-  std::cout << "session.backend=" << session.backendName() << "\n";
+  printBackend(std::cout, session, askedBackend);
   std::cout << "session.result=success\n";
   if (summary.validationRan && summary.validationPassed) std::cout << "session.validation=pass\n";
   std::cout << "session.profile.session_id=" << summary.profileTrace.sessionId << "\n";

@@ -85,6 +85,44 @@ static void testNpy() {
     EXPECT(saveNpy(path("t.npy"), x).ok() && loadNpy(path("t.npy"), y).ok() && y.dtype == t && y.shape == x.shape && y.bytes == x.bytes,
            std::string("round trip ") + npyDTypeName(t));
   }
+  // a column-major file (numpy writes one for the result of indexing columns with an index array) is brought into
+  // row-major order: take a saved [2,3,4] i32 array, store its elements in column-major order, flip the header flag
+  {
+    NDArray x;
+    x.dtype = NpyDType::INT32;
+    x.shape = {2, 3, 4};
+    x.allocate();
+    for (int i = 0; i < 24; ++i) std::memcpy(x.bytes.data() + 4 * i, &i, 4);
+    EXPECT(saveNpy(path("c_order.npy"), x).ok(), "save i32 [2,3,4]");
+    std::ifstream in(path("c_order.npy"), std::ios::binary);
+    std::string file((std::istreambuf_iterator<char>(in)), std::istreambuf_iterator<char>());
+    const size_t flag = file.find("'fortran_order': False");
+    EXPECT(flag != std::string::npos, "the header names the order");
+    file.replace(flag, 22, "'fortran_order': True ");
+    const size_t data = file.size() - 96;
+    for (int i0 = 0; i0 < 2; ++i0)
+      for (int i1 = 0; i1 < 3; ++i1)
+        for (int i2 = 0; i2 < 4; ++i2) {
+          const int value = (i0 * 3 + i1) * 4 + i2, at = i0 + 2 * (i1 + 3 * i2);
+          std::memcpy(&file[data + 4 * at], &value, 4);
+        }
+    { std::ofstream(path("f_order.npy"), std::ios::binary) << file; }
+    NDArray y;
+    EXPECT(loadNpy(path("f_order.npy"), y).ok() && y.shape == x.shape && y.bytes == x.bytes, "column-major [2,3,4] loads in row-major order");
+    // rank 1 and single elements have one order only
+    NDArray v;
+    v.dtype = NpyDType::F32;
+    v.shape = {5};
+    v.allocate();
+    for (size_t i = 0; i < v.bytes.size(); ++i) v.bytes[i] = static_cast<uint8_t>(i);
+    EXPECT(saveNpy(path("v.npy"), v).ok(), "save f32 [5]");
+    std::ifstream vin(path("v.npy"), std::ios::binary);
+    std::string vfile((std::istreambuf_iterator<char>(vin)), std::istreambuf_iterator<char>());
+    vfile.replace(vfile.find("'fortran_order': False"), 22, "'fortran_order': True ");
+    { std::ofstream(path("vf.npy"), std::ios::binary) << vfile; }
+    NDArray w;
+    EXPECT(loadNpy(path("vf.npy"), w).ok() && w.bytes == v.bytes, "rank 1 is the same in both orders");
+  }
   NDArray e;
   EXPECT(loadNpy(path("missing.npy"), e).message().find("Cannot open:") == 0, "missing file message");
   writeText(path("junk.npy"), "not an npy file at all");

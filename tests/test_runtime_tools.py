@@ -93,6 +93,43 @@ def test_runtime_session_usage_errors_exit_4():
     assert r.returncode == 0 and "--run-manifest" in r.stdout
 
 
+def test_a_dim_the_foreign_schema_lacks_is_read_off_the_bound_tensor(tmp_path):
+    """A manifest written for the reference's kernel packs by field name; a dim_arg<N>_<D> it does not carry (the
+    reference's kernel derives an output's extents from its inputs') is extent D of the tensor bound to argument N.
+    Without a GPU the run then stops at the device stage, not at the bindings; a dim of an argument that is not bound
+    at all is still a bindings error that names the field."""
+    spec = descriptors.add_mul("f32")
+    src = tmp_path / "add_mul.cuda.json"
+    src.write_text(spec.descriptor_json())
+    r = run_tool("--kernel", src, "--output", tmp_path / "artifact")
+    assert r.returncode == 0, r.stderr
+    M, N = 6, 16
+    a = np.arange(M * N, dtype=np.float32).reshape(M, N)
+    np.save(tmp_path / "a.npy", a)
+    np.save(tmp_path / "b.npy", a + 1)
+    np.save(tmp_path / "want.npy", (a + (a + 1)) * (a + 1))
+    (tmp_path / "tiling_space.json").write_text(json.dumps({
+        "kernel": "add_mul", "kernel_file": "step8_kernel.cpp", "soc": "Ascend910B1", "block_dim_expr": "ceil(M / TB_M)",
+        "tiling_params": [{"name": "TB_M", "type": "int64", "values": [16]},
+                          {"name": "dim_arg0_0", "type": "int64", "fixed": True, "shape_key": "M"}]}))
+    manifest = {"task_id": "main", "backend": "sim", "artifact_root": str(tmp_path / "artifact"),
+                "inputs": [{"name": "a", "path": str(tmp_path / "a.npy")}, {"name": "b", "path": str(tmp_path / "b.npy")}],
+                "outputs": [{"name": "out", "path": str(tmp_path / "out.npy")}],
+                "expected_outputs": [{"name": "out", "path": str(tmp_path / "want.npy")}],
+                "tiling": {"schema": str(tmp_path / "tiling_space.json"), "params": f"TB_M=16,dim_arg0_0={M}"},   # no dim_arg0_1
+                "block_dim": 0, "atol": 0.0, "rtol": 0.0}
+    (tmp_path / "m.json").write_text(json.dumps(manifest))
+    r = run_tool("--run-manifest", tmp_path / "m.json", "--run")
+    out = r.stdout + r.stderr
+    assert "session.error_stage=bindings" not in out and "missing field" not in out
+    assert "session.error_stage=device" in out or "session.validation=pass" in out
+    # with the second input unbound, the kernel's argument count no longer matches: still an error, and not a crash
+    manifest["inputs"] = manifest["inputs"][:1]
+    (tmp_path / "m1.json").write_text(json.dumps(manifest))
+    r = run_tool("--run-manifest", tmp_path / "m1.json", "--run")
+    assert r.returncode != 0 and "takes 2 inputs and 1 outputs, got 1 and 1" in r.stdout + r.stderr
+
+
 def test_runtime_session_compiles_and_plans(tmp_path):
     spec = descriptors.add_mul()
     src = tmp_path / "add_mul.cuda.json"
