@@ -176,7 +176,9 @@ std::string arithName(const std::string &op) {
   if (op == "arith.addf" || op == "arith.addi" || op == "afir.add") return "addf";
   if (op == "arith.subf" || op == "arith.subi" || op == "afir.sub") return "subf";
   if (op == "arith.mulf" || op == "arith.muli" || op == "afir.mul") return "mulf";
-  if (op == "arith.divf" || op == "arith.divsi" || op == "afir.div") return "divf";
+  if (op == "arith.divf" || op == "arith.divsi" || op == "afir.div" || op == "afir.truediv") return "divf";
+  if (op == "afir.maximum") return "maximumf";
+  if (op == "afir.minimum") return "minimumf";
   if (op == "arith.maximumf" || op == "arith.maxsi") return "maximumf";
   if (op == "arith.minimumf" || op == "arith.minsi") return "minimumf";
   return "";

@@ -82,7 +82,10 @@ void inferAfirShapes(Module &m, int *refined) {
         bool changed = !sameType(result, o.resultType);
         for (size_t i = 0; i < operandTypes.size(); ++i) changed = changed || !sameType(operandTypes[i], o.operandTypes[i]);
         if (changed) {
-          m.replacements.push_back({o.typesBegin, trimmedEnd(m.source, o.typesBegin, o.srcEnd), "(" + typeListText(operandTypes) + ") -> " + result.str()});
+          // (unary ops print their operand type without parentheses; the form found in the source is kept)
+          const bool parens = o.typesBegin < m.source.size() && m.source[o.typesBegin] == '(';
+          m.replacements.push_back({o.typesBegin, trimmedEnd(m.source, o.typesBegin, o.srcEnd),
+                                    (parens ? "(" : "") + typeListText(operandTypes) + (parens ? ")" : "") + " -> " + result.str()});
           o.operandTypes = operandTypes;
           o.resultType = result;
         }

@@ -7,6 +7,7 @@ import os
 import subprocess
 from pathlib import Path
 
+import numpy as np
 import pytest
 
 from ascend_mlir_b200 import build as lib_build
@@ -318,6 +319,55 @@ func.func @contradiction(%a: tensor<8x4xf32>, %b: tensor<8x4xf32>) -> tensor<8x7
     assert "%0 = afir.add %a, %b : (tensor<?x4xi32>, tensor<?x1xi32>) -> tensor<?x4xi32>" in out and "-> tensor<?x4xi32> {" in out
     assert "(tensor<8x4xf32>, tensor<8x5xf32>) -> tensor<?x?xf32>" in out and "return %0 : tensor<?x?xf32>" in out
     assert "(tensor<8x4xf32>, tensor<8x4xf32>) -> tensor<8x7xf32>" in out
+
+
+def test_wider_afir_elementwise_family_lowers_to_the_fused_body_ops(tmp_path):
+    """afir.relu / leaky_relu / maximum / minimum / truediv / clip_by_value (include/Dialect/AFIR/Ops/Basic/math.td:60-121):
+    unary ops print "T -> R", leaky_relu carries negative_slop; relu = max(x, 0), leaky_relu = max(x, slope * x) with the
+    slope as an f32, clip_by_value = min(max(x, low), high); shapes broadcast like add / mul.  The second function is
+    the clip case of the reference's shapeInference.mlir, whose FileCheck line wants "-> tensor<4x20x32xf32>"."""
+    text = """func.func @act(%x: tensor<?x64xf16>, %y: tensor<64xf16>) -> tensor<?x?xf16> {
+    %0 = afir.relu %x : tensor<?x64xf16> -> tensor<?x?xf16>
+    %1 = afir.leaky_relu %0 {negative_slop = 0.01 : f32} : tensor<?x?xf16> -> tensor<?x?xf16>
+    %2 = afir.maximum %1, %y : (tensor<?x?xf16>, tensor<64xf16>) -> tensor<?x?xf16>
+    %3 = afir.truediv %2, %y : (tensor<?x?xf16>, tensor<64xf16>) -> tensor<?x?xf16>
+    %4 = afir.minimum %3, %x : (tensor<?x?xf16>, tensor<?x64xf16>) -> tensor<?x?xf16>
+    return %4 : tensor<?x?xf16>
+}
+func.func @test_clip_by_value(%arg0: tensor<4x1x1xf32>, %arg1: tensor<1x20x1xf32>, %arg2: tensor<1x1x32xf32>) -> tensor<?x?x?xf32> {
+    %0 = afir.clip_by_value %arg0, %arg1, %arg2 : (tensor<4x1x1xf32>, tensor<1x20x1xf32>, tensor<1x1x32xf32>) -> tensor<?x?x?xf32>
+    return %0 : tensor<?x?x?xf32>
+}
+"""
+    src = tmp_path / "family.mlir"
+    src.write_text(text)
+    r = opt("--afir-shape-inference", src)
+    assert r.returncode == 0, r.stderr
+    assert "%0 = afir.relu %x : tensor<?x64xf16> -> tensor<?x64xf16>" in r.stdout  # the unary form keeps its bare operand type
+    assert "%1 = afir.leaky_relu %0 {negative_slop = 0.01 : f32} : tensor<?x64xf16> -> tensor<?x64xf16>" in r.stdout
+    assert "-> tensor<4x20x32xf32> {" in r.stdout and r.stdout.count("-> tensor<4x20x32xf32>") == 2
+    act = translate(src, "--function", "act")
+    slope = float(np.float32(0.01))
+    assert act["kernel_class"] == "elementwise" and act["dtype"] == "f16" and act["domain"] == ["dim_arg0_0", 64]
+    assert body_of(act) == [("maximumf", "v0", 0.0), ("mulf", "%0", slope), ("maximumf", "%0", "%1"), ("maximumf", "%2", "v1"),
+                            ("divf", "%3", "v1"), ("minimumf", "%4", "v0")]
+    assert [v["map"] for v in act["loads"]] == [[0, 1], [1]]
+    clip = translate(src, "--function", "test_clip_by_value")
+    assert clip["domain"] == [4, 20, 32] and body_of(clip) == [("maximumf", "v0", "v1"), ("minimumf", "%0", "v2")]
+    assert [v["map"] for v in clip["loads"]] == [[0, -1, -1], [-1, 1, -1], [-1, -1, 2]]
+    # the group's kernel is generated and compiles for sm_100a
+    cubin = tmp_path / "act.cubin"
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda-kernel", str(src), "--function", "act", "-o", str(tmp_path / "act.cu"),
+                        "--cubin-out", str(cubin)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert cubin.read_bytes()[:4] == b"\x7fELF" and "P::max(r0, r1)" in (tmp_path / "act.cu").read_text()
+    # what stays outside: a slope the max form does not express, an op of the family with no body op, wrong arity
+    for bad, needle in [(text.replace("0.01 : f32", "1.5 : f32"), "negative_slop outside [0, 1]"),
+                        (text.replace("afir.relu %x :", "afir.abs %x :"), "outside the supported elementwise set"),
+                        (text.replace("{negative_slop = 0.01 : f32} ", ""), "needs its negative_slop attribute"),
+                        (text.replace("afir.maximum %1, %y :", "afir.maximum %1 :"), "takes 2 operands")]:
+        r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-", "--function", "act"], capture_output=True, text=True, input=bad)
+        assert r.returncode == 1 and needle in r.stderr, (needle, r.stderr)
 
 
 def test_shape_inference_before_the_conversion_gives_literal_extents(tmp_path):
