@@ -361,6 +361,12 @@ func.func @test_clip_by_value(%arg0: tensor<4x1x1xf32>, %arg1: tensor<1x20x1xf32
                         "--cubin-out", str(cubin)], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     assert cubin.read_bytes()[:4] == b"\x7fELF" and "P::max(r0, r1)" in (tmp_path / "act.cu").read_text()
+    # afir.neg: x * -1 on floats (exact, zeros and infinities included), 0 - x on integers (wraps like the type)
+    for elem, want in (("f32", [("mulf", "v0", -1.0)]), ("i32", [("subi", 0, "v0")])):
+        neg = f"func.func @n(%x: tensor<8x?x{elem}>) -> tensor<8x?x{elem}> {{\n  %0 = afir.neg %x : tensor<8x?x{elem}> -> tensor<8x?x{elem}>\n  return %0 : tensor<8x?x{elem}>\n}}\n"
+        r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-"], capture_output=True, text=True, input=neg)
+        assert r.returncode == 0, r.stderr
+        assert body_of(json.loads(r.stdout)) == want
     # what stays outside: a slope the max form does not express, an op of the family with no body op, wrong arity
     for bad, needle in [(text.replace("0.01 : f32", "1.5 : f32"), "negative_slop outside [0, 1]"),
                         (text.replace("afir.relu %x :", "afir.abs %x :"), "outside the supported elementwise set"),
