@@ -24,6 +24,23 @@ bool inferBroadcastShape(const std::vector<std::vector<int64_t>> &operands, std:
   return true;
 }
 
+bool inferConcatShape(const std::vector<std::vector<int64_t>> &operands, int64_t axis, std::vector<int64_t> &out) {
+  if (operands.empty()) return false;
+  const size_t rank = operands[0].size();
+  for (const auto &shape : operands)
+    if (shape.size() != rank) return false;
+  if (axis < 0 || static_cast<size_t>(axis) >= rank) return false;
+  out.assign(rank, 0);  // 0 = nothing seen yet at a position that is not the axis
+  for (const auto &shape : operands)
+    for (size_t j = 0; j < rank; ++j) {
+      if (shape[j] < 0) out[j] = -1;
+      else if (j == static_cast<size_t>(axis)) { if (out[j] >= 0) out[j] += shape[j]; }
+      else if (out[j] == 0) out[j] = shape[j];
+      else if (out[j] >= 0 && out[j] != shape[j]) return false;
+    }
+  return true;
+}
+
 bool joinShapes(const std::vector<int64_t> &current, const std::vector<int64_t> &inferred, std::vector<int64_t> &out) {
   if (current.size() != inferred.size()) return false;
   out.assign(current.size(), -1);
@@ -75,7 +92,8 @@ void inferAfirShapes(Module &m, int *refined) {
           shapes.push_back(t.dims);
         }
         std::vector<int64_t> inferred, joined;
-        if (ranked && inferBroadcastShape(shapes, inferred) && joinShapes(result.dims, inferred, joined) && joined != result.dims) {
+        const bool inferredOk = o.name == "afir.concat" ? inferConcatShape(shapes, o.dim, inferred) : inferBroadcastShape(shapes, inferred);
+        if (ranked && inferredOk && joinShapes(result.dims, inferred, joined) && joined != result.dims) {
           result.dims = joined;
           if (refined) ++*refined;
         }

@@ -18,6 +18,12 @@ namespace front {
 // make the inference fail (false; `out` is then unspecified).
 bool inferBroadcastShape(const std::vector<std::vector<int64_t>> &operands, std::vector<int64_t> &out);
 
+// afir.concat (lib/Dialect/AFIR/Ops/Adv/concat.cpp:86-131): operands of one rank; along `axis` the static extents add up
+// (one dynamic extent makes the sum dynamic), every other position takes the operands' common static extent and is
+// dynamic as soon as one operand is dynamic there; operands that disagree, ranks that differ or an axis outside the
+// rank make the inference fail.
+bool inferConcatShape(const std::vector<std::vector<int64_t>> &operands, int64_t axis, std::vector<int64_t> &out);
+
 // What two descriptions of one shape agree on: a dynamic entry yields to a static one, equal entries stay; ranks
 // or static extents that differ are a conflict (false).
 bool joinShapes(const std::vector<int64_t> &current, const std::vector<int64_t> &inferred, std::vector<int64_t> &out);

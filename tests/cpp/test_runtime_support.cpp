@@ -453,6 +453,16 @@ static void testShapeInference() {
   EXPECT(!joinShapes({8, 7}, {8, 4}, out), "a declared extent that contradicts the inference");
   EXPECT(!joinShapes({8}, {8, 4}, out), "ranks that differ");
 
+  using front::inferConcatShape;
+  EXPECT(inferConcatShape({{2, 4}, {3, 4}, {4, 4}}, 0, out) && out == Shape({9, 4}), "the reference's concat lit case");
+  EXPECT(inferConcatShape({{4, 4}, {4, 4}}, 1, out) && out == Shape({4, 8}), "along the inner axis");
+  EXPECT(inferConcatShape({{-1, 64}, {8, 64}}, 0, out) && out == Shape({-1, 64}), "a dynamic extent along the axis makes the sum dynamic");
+  EXPECT(inferConcatShape({{8, 64}, {-1, 64}}, 0, out) && out == Shape({-1, 64}), "whatever the order");
+  EXPECT(inferConcatShape({{8, -1}, {8, 64}}, 0, out) && out == Shape({16, -1}), "a dynamic extent elsewhere stays dynamic");
+  EXPECT(!inferConcatShape({{8, 4}, {8, 5}}, 0, out), "parts that disagree off the axis");
+  EXPECT(!inferConcatShape({{8, 4}, {8}}, 0, out), "ranks that differ");
+  EXPECT(!inferConcatShape({{8, 4}}, 2, out) && !inferConcatShape({{8, 4}}, -1, out) && !inferConcatShape({}, 0, out), "axis outside the rank; no operand");
+
   // the pass itself: text in, replacements out, a second run finds nothing
   front::Module m;
   const std::string text = "func.func @f(%a: tensor<2x1xf32>, %b: tensor<3xf32>) -> (tensor<?x?xf32>) {\n"

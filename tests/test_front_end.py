@@ -376,6 +376,46 @@ func.func @test_clip_by_value(%arg0: tensor<4x1x1xf32>, %arg1: tensor<1x20x1xf32
         assert r.returncode == 1 and needle in r.stderr, (needle, r.stderr)
 
 
+def test_afir_concat_infers_like_the_reference_and_lowers_to_row_ranges_of_one_output(tmp_path):
+    """afir.concat (concat_axis in its attributes, "T, U -> R" type form).  Shapes as in the reference's shapeInference.mlir
+    (2x4, 3x4, 4x4 along axis 0: its FileCheck line wants "-> tensor<9x4xf32>"; a concat of a concat along axis 1), and a
+    concat along axis 0 of two elementwise chains becomes one kernel of two groups that write their own row ranges."""
+    text = """func.func @test_concat(%arg0: tensor<2x4xf32>, %arg1: tensor<3x4xf32>, %arg2: tensor<4x4xf32>) -> tensor<?x?xf32> {
+  %0 = afir.concat %arg0, %arg1, %arg2 {concat_axis = 0 : i32} : tensor<2x4xf32>, tensor<3x4xf32>, tensor<4x4xf32> -> tensor<?x?xf32>
+  return %0 : tensor<?x?xf32>
+}
+func.func @two(%arg0: tensor<2x4xf32>, %arg1: tensor<2x4xf32>, %arg2: tensor<4x4xf32>) -> tensor<?x?xf32> {
+  %0 = afir.concat %arg0, %arg1 {concat_axis = 0 : i32} : tensor<2x4xf32>, tensor<2x4xf32> -> tensor<?x?xf32>
+  %1 = afir.concat %0, %arg2 {concat_axis = 1 : i32} : tensor<?x?xf32>, tensor<4x4xf32> -> tensor<?x?xf32>
+  return %1 : tensor<?x?xf32>
+}
+func.func @halves(%a: tensor<?x64xf16>, %b: tensor<?x64xf16>, %s: tensor<64xf16>) -> tensor<?x?xf16> {
+  %0 = afir.relu %a : tensor<?x64xf16> -> tensor<?x?xf16>
+  %1 = afir.mul %b, %s : (tensor<?x64xf16>, tensor<64xf16>) -> tensor<?x?xf16>
+  %2 = afir.concat %0, %1 {concat_axis = 0 : i32} : tensor<?x?xf16>, tensor<?x?xf16> -> tensor<?x?xf16>
+  return %2 : tensor<?x?xf16>
+}
+"""
+    src = tmp_path / "concat.mlir"
+    src.write_text(text)
+    out = opt("--afir-shape-inference", src).stdout
+    assert "tensor<2x4xf32>, tensor<3x4xf32>, tensor<4x4xf32> -> tensor<9x4xf32>" in out and "@test_concat(" in out and "-> tensor<9x4xf32> {" in out
+    assert "%0 = afir.concat %arg0, %arg1 {concat_axis = 0 : i32} : tensor<2x4xf32>, tensor<2x4xf32> -> tensor<4x4xf32>" in out
+    assert "%1 = afir.concat %0, %arg2 {concat_axis = 1 : i32} : tensor<4x4xf32>, tensor<4x4xf32> -> tensor<4x8xf32>" in out
+    assert "%2 = afir.concat %0, %1 {concat_axis = 0 : i32} : tensor<?x64xf16>, tensor<?x64xf16> -> tensor<?x64xf16>" in out  # dynamic rows stay dynamic
+    d = translate(src, "--function", "halves")
+    assert d["kernel_class"] == "elementwise" and len(d["groups"]) == 2
+    first, second = d["groups"]
+    assert body_of(first) == [("maximumf", "v0", 0.0)] and body_of(second) == [("mulf", "v0", "v1")]
+    assert first["store"]["arg"] == second["store"]["arg"] == 3 and "offset" not in first["store"]
+    assert second["store"]["offset"] == ["dim_arg0_0", 0]  # the second half starts where the first ends
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", str(src), "--function", "two"], capture_output=True, text=True)
+    assert r.returncode == 1 and "only concatenation along dim 0 is supported" in r.stderr
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-"], capture_output=True, text=True,
+                       input=text.replace("{concat_axis = 0 : i32} : tensor<2x4xf32>, tensor<3x4xf32>", "{} : tensor<2x4xf32>, tensor<3x4xf32>"))
+    assert r.returncode == 1 and "needs its concat_axis attribute" in r.stderr
+
+
 def test_shape_inference_before_the_conversion_gives_literal_extents(tmp_path):
     src = tmp_path / "chain.mlir"
     src.write_text("""func.func @chain(%a: tensor<64x1xf32>, %b: tensor<1x256xf32>) -> tensor<?x?xf32> {
