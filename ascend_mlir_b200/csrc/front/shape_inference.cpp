@@ -41,6 +41,13 @@ bool inferConcatShape(const std::vector<std::vector<int64_t>> &operands, int64_t
   return true;
 }
 
+bool inferReducedShape(const std::vector<int64_t> &operand, int64_t axis, std::vector<int64_t> &out) {
+  if (axis < 0 || static_cast<size_t>(axis) >= operand.size()) return false;
+  out = operand;
+  out.erase(out.begin() + axis);
+  return true;
+}
+
 bool joinShapes(const std::vector<int64_t> &current, const std::vector<int64_t> &inferred, std::vector<int64_t> &out) {
   if (current.size() != inferred.size()) return false;
   out.assign(current.size(), -1);
@@ -92,7 +99,12 @@ void inferAfirShapes(Module &m, int *refined) {
           shapes.push_back(t.dims);
         }
         std::vector<int64_t> inferred, joined;
-        const bool inferredOk = o.name == "afir.concat" ? inferConcatShape(shapes, o.dim, inferred) : inferBroadcastShape(shapes, inferred);
+        const std::string kind = o.name.substr(5);
+        const bool reduction = kind == "sum" || kind == "max" || kind == "min" || kind == "mean" || kind == "prod" || kind == "any" || kind == "all";
+        bool inferredOk;
+        if (kind == "concat") inferredOk = inferConcatShape(shapes, o.dim, inferred);
+        else if (reduction) inferredOk = shapes.size() == 1 && inferReducedShape(shapes[0], o.dim, inferred);
+        else inferredOk = inferBroadcastShape(shapes, inferred);
         if (ranked && inferredOk && joinShapes(result.dims, inferred, joined) && joined != result.dims) {
           result.dims = joined;
           if (refined) ++*refined;

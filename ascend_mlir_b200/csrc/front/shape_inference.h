@@ -24,6 +24,10 @@ bool inferBroadcastShape(const std::vector<std::vector<int64_t>> &operands, std:
 // rank make the inference fail.
 bool inferConcatShape(const std::vector<std::vector<int64_t>> &operands, int64_t axis, std::vector<int64_t> &out);
 
+// The afir reductions (sum, max, min, mean, prod, any, all; lib/Dialect/AFIR/Ops/Adv/reduce.cpp:72-91): the operand's
+// shape with `axis` removed; an axis outside the rank makes the inference fail.
+bool inferReducedShape(const std::vector<int64_t> &operand, int64_t axis, std::vector<int64_t> &out);
+
 // What two descriptions of one shape agree on: a dynamic entry yields to a static one, equal entries stay; ranks
 // or static extents that differ are a conflict (false).
 bool joinShapes(const std::vector<int64_t> &current, const std::vector<int64_t> &inferred, std::vector<int64_t> &out);

@@ -463,6 +463,11 @@ static void testShapeInference() {
   EXPECT(!inferConcatShape({{8, 4}, {8}}, 0, out), "ranks that differ");
   EXPECT(!inferConcatShape({{8, 4}}, 2, out) && !inferConcatShape({{8, 4}}, -1, out) && !inferConcatShape({}, 0, out), "axis outside the rank; no operand");
 
+  using front::inferReducedShape;
+  EXPECT(inferReducedShape({4, 5}, 0, out) && out == Shape({5}) && inferReducedShape({4, 5}, 1, out) && out == Shape({4}), "the reference's reduce lit case");
+  EXPECT(inferReducedShape({2, -1, 8}, 2, out) && out == Shape({2, -1}), "dynamic extents pass through");
+  EXPECT(!inferReducedShape({4, 5}, 2, out) && !inferReducedShape({4, 5}, -1, out) && !inferReducedShape({}, 0, out), "axis outside the rank");
+
   // the pass itself: text in, replacements out, a second run finds nothing
   front::Module m;
   const std::string text = "func.func @f(%a: tensor<2x1xf32>, %b: tensor<3xf32>) -> (tensor<?x?xf32>) {\n"

@@ -416,6 +416,46 @@ func.func @halves(%a: tensor<?x64xf16>, %b: tensor<?x64xf16>, %s: tensor<64xf16>
     assert r.returncode == 1 and "needs its concat_axis attribute" in r.stderr
 
 
+def test_afir_reductions_infer_their_shape_and_a_last_axis_sum_is_the_row_reduction(tmp_path):
+    """The afir reductions (reduce.td:43-49) drop their axis (the max case of the reference's shapeInference.mlir: a
+    4x5 input gives "-> tensor<5xf16>" along axis 0 and "-> tensor<4xf16>" along axis 1, two results, both carried to the
+    return op and the function type; `axis` is told apart from vectorized_axis).  afir.add with a column operand followed
+    by afir.sum along the last axis is the broadcast-add-reduce group: same descriptor as its linalg form."""
+    text = """func.func @test_max_reduce_f16(%arg0: tensor<4x5xf16>) -> (tensor<?xf16>, tensor<?xf16>) {
+  %0 = afir.max %arg0 {vectorized_axis = [0], axis = 0 : i32} : tensor<4x5xf16> -> tensor<?xf16>
+  %1 = afir.max %arg0 {axis = 1 : i32} : tensor<4x5xf16> -> tensor<?xf16>
+  return %0, %1 : tensor<?xf16>, tensor<?xf16>
+}
+func.func @broadcast_add_reduce(%a: tensor<?x1xf32>, %b: tensor<?x?xf32>) -> tensor<?xf32> {
+  %0 = afir.add %a, %b : (tensor<?x1xf32>, tensor<?x?xf32>) -> tensor<?x?xf32>
+  %1 = afir.sum %0 {axis = 1 : i32} : tensor<?x?xf32> -> tensor<?xf32>
+  return %1 : tensor<?xf32>
+}
+"""
+    src = tmp_path / "reduce.mlir"
+    src.write_text(text)
+    out = opt("--afir-shape-inference", src).stdout
+    assert "-> (tensor<5xf16>, tensor<4xf16>) {" in out and "return %0, %1 : tensor<5xf16>, tensor<4xf16>" in out
+    assert "axis = 0 : i32} : tensor<4x5xf16> -> tensor<5xf16>" in out and "{axis = 1 : i32} : tensor<4x5xf16> -> tensor<4xf16>" in out
+    got = translate(src, "--function", "broadcast_add_reduce")
+    want = translate(EXAMPLES / "broadcast_add_reduce.mlir")
+    assert got["kernel_class"] == want["kernel_class"] == "row_reduce"
+    assert body_of(got) == body_of(want) == [("addf", "v0", "v1")]
+    assert [(v["arg"], v["map"][0]) for v in got["loads"]] == [(v["arg"], v["map"][0]) for v in want["loads"]] == [(0, 0), (1, 0)]
+    assert got["store"]["arg"] == want["store"]["arg"] == 2 and got["tiling"][:6] == want["tiling"][:6]
+    # a kernel is generated for it (the staged and the finalize entries beside the main one) and compiles
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda-kernel", str(src), "--function", "broadcast_add_reduce",
+                        "-o", str(tmp_path / "k.cu"), "--cubin-out", str(tmp_path / "k.cubin")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert (tmp_path / "k.cubin").read_bytes()[:4] == b"\x7fELF" and "broadcast_add_reduce__staged" in (tmp_path / "k.cu").read_text()
+    for bad, needle in [(text.replace("afir.sum %0 {axis = 1", "afir.sum %0 {axis = 0"), "only a sum along the last axis is lowered"),
+                        (text.replace("afir.sum %0 {axis = 1 : i32}", "afir.sum %0 {vectorized_axis = [0]}"), "needs its axis attribute"),
+                        (text.replace("afir.sum", "afir.mean"), "only afir.sum is lowered")]:
+        r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-", "--function", "broadcast_add_reduce"],
+                           capture_output=True, text=True, input=bad)
+        assert r.returncode == 1 and needle in r.stderr, (needle, r.stderr)
+
+
 def test_shape_inference_before_the_conversion_gives_literal_extents(tmp_path):
     src = tmp_path / "chain.mlir"
     src.write_text("""func.func @chain(%a: tensor<64x1xf32>, %b: tensor<1x256xf32>) -> tensor<?x?xf32> {
