@@ -119,6 +119,7 @@ private:
       const char c = s_[pos_++];
       if (c == '"') {
         while (!eof() && s_[pos_] != '"') pos_ += s_[pos_] == '\\' ? 2 : 1;
+        if (eof()) { pos_ = s_.size(); return fail("unterminated string"); }
         ++pos_;
       } else if (c == open) ++depth;
       else if (c == close && --depth == 0) return Status::success();

@@ -223,6 +223,27 @@ def test_afir_broadcast_follows_numpy_trailing_alignment():
     assert body_of(d) == [("addf", "v0", "v1"), ("mulf", "%0", "v2")]
 
 
+def test_a_string_that_never_ends_is_an_error_not_a_crash():
+    """An attribute string without its closing quote (after an op name, in linalg.generic's dictionary, in an afir
+    op's attributes): the tools stop with a message; found by mutating inputs."""
+    cases = ["""func.func @f(%a: memref<8x8xf16>, %b: memref<8x16xf16>, %c: memref<8x16xf32>) {
+  linalg.matmul {ascendc.unit = "AiCore.Cube} ins(%a, %b : memref<8x8xf16>, memref<8x16xf16>) outs(%c : memref<8x16xf32>)
+  return
+}""", """func.func @f(%x: tensor<4xf32>) -> tensor<4xf32> {
+  %0 = afir.relu %x {note = "never closed} : tensor<4xf32> -> tensor<4xf32>
+  return %0 : tensor<4xf32>
+}""", """func.func @f(%s: memref<4xf32>, %d: memref<4xf32>) {
+  linalg.generic {indexing_maps = [affine_map<(d0) -> (d0)>, affine_map<(d0) -> (d0)>], iterator_types = ["parallel]} ins(%s : memref<4xf32>) outs(%d : memref<4xf32>) {
+  ^bb0(%x: f32, %y: f32):
+    linalg.yield %x : f32
+  }
+  return
+}"""]
+    for text in cases:
+        r = opt("--annotate-ascendc-kernel-kind", "-", stdin=text)
+        assert r.returncode == 1 and "error: line" in r.stderr, (r.returncode, r.stderr)
+
+
 def test_kernel_kind_follows_the_units_a_lowering_stage_assigned():
     """--annotate-ascendc-kernel-kind on buffer-level functions whose ops carry ascendc.unit (what the reference's
     test/Conversion/annotate-ascendc-kernel-kind.mlir feeds the pass): Cube only = "cube", Vector only = "vec", both =
