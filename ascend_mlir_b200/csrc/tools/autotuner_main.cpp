@@ -274,8 +274,15 @@ int main(int argc, char **argv) {
     exp.name = "expected";
     exp.path = args.get("expected");
     task.invocation.expectedOutputs.push_back(exp);
+    // Handed over as schema + named values (tiling.bin above is kept beside the candidate for the record): the session
+    // packs them in the schema's order when the space is the kernel's own -- the bytes written above -- and by field
+    // name when the space was written for the reference's kernel (its loop tile sizes are then ignored and a
+    // dimension the space lacks is read off the bound tensor), as for a run manifest.
+    std::string named;
+    for (const auto &kv : ordered) named += (named.empty() ? "" : ",") + kv.first + "=" + std::to_string(kv.second);
     task.invocation.tiling.present = true;
-    task.invocation.tiling.binaryPath = tilingPath;
+    task.invocation.tiling.schemaPath = args.get("space");
+    task.invocation.tiling.params = named;
     task.invocation.blockDim = static_cast<int>(sr.blockDim);
     task.invocation.enableProfiling = true;
     task.invocation.atol = atol;

@@ -130,6 +130,33 @@ def test_a_dim_the_foreign_schema_lacks_is_read_off_the_bound_tensor(tmp_path):
     assert r.returncode != 0 and "takes 2 inputs and 1 outputs, got 1 and 1" in r.stdout + r.stderr
 
 
+def test_autotuner_takes_a_tiling_space_written_for_the_reference_kernel(tmp_path):
+    """A hand-kept tiling_space.json of the reference's examples names that kernel's loop tile sizes beside the dims, in
+    its own order.  The autotuner hands schema and named values to the session, which packs them for THIS kernel by
+    field name: the candidate gets past the bindings (and stops at the device on a machine without a GPU), where bytes
+    packed in the space's own order would be refused for their size."""
+    spec = descriptors.add_mul("f32")
+    kernel = tmp_path / "add_mul.cuda.json"
+    kernel.write_text(spec.descriptor_json())
+    M, N = 6, 16
+    a = np.arange(M * N, dtype=np.float32).reshape(M, N)
+    np.save(tmp_path / "a.npy", a)
+    np.save(tmp_path / "b.npy", a + 1)
+    np.save(tmp_path / "want.npy", (a + (a + 1)) * (a + 1))
+    (tmp_path / "tiling_space.json").write_text(json.dumps({
+        "kernel": "add_mul", "kernel_file": kernel.name, "soc": "Ascend910B1", "block_dim_expr": "ceil(M / TB_M)",
+        "tiling_params": [{"name": "TB_M", "type": "int64", "values": [2, 3]},
+                          {"name": "dim_arg0_1", "type": "int64", "fixed": True, "shape_key": "N"},
+                          {"name": "dim_arg0_0", "type": "int64", "fixed": True, "shape_key": "M"}]}))
+    r = subprocess.run([str(BIN / "autotuner"), "--space", str(tmp_path / "tiling_space.json"), "--inputs",
+                        f"{tmp_path / 'a.npy'},{tmp_path / 'b.npy'}", "--expected", str(tmp_path / "want.npy"), "--shape", f"M={M},N={N}",
+                        "--atol", "0", "--rtol", "0", "--output", str(tmp_path / "best.json")], capture_output=True, text=True)
+    out = r.stdout + r.stderr
+    assert "Search space: 2 candidate(s) over 1 parameter(s)" in out and "block_dim=3" in out and "block_dim=2" in out
+    assert "[cuda:bindings]" not in out, out
+    assert out.count("[cuda:device]") == 2 or out.count(" PASS score=") == 2, out
+
+
 def test_runtime_session_compiles_and_plans(tmp_path):
     spec = descriptors.add_mul()
     src = tmp_path / "add_mul.cuda.json"
