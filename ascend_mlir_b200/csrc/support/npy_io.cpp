@@ -119,6 +119,20 @@ Status loadNpy(const std::string &path, NDArray &out) {
   else if (descr == "<i2" || descr == "=i2") out.dtype = NpyDType::INT16;
   else return Status::error("Unsupported dtype '" + descr + "': " + path);
   const bool fortran = headerField(header, "fortran_order").find("True") != std::string::npos;
+  // The header's shape is checked against what the file holds before anything of that size is allocated (a damaged
+  // header can claim terabytes).
+  {
+    const std::streampos dataBegin = f.tellg();
+    f.seekg(0, std::ios::end);
+    const std::streampos fileEnd = f.tellg();
+    f.seekg(dataBegin);
+    const unsigned long long available = fileEnd >= dataBegin ? static_cast<unsigned long long>(fileEnd - dataBegin) : 0ull;
+    unsigned long long claimed = npyDTypeBytes(out.dtype);
+    for (int64_t d : out.shape) {
+      if (d != 0 && claimed > available / static_cast<unsigned long long>(d)) return Status::error("Truncated data in: " + path);
+      claimed *= static_cast<unsigned long long>(d);
+    }
+  }
   out.allocate();
   f.read(reinterpret_cast<char *>(out.bytes.data()), static_cast<std::streamsize>(out.bytes.size()));
   if (static_cast<size_t>(f.gcount()) != out.bytes.size()) return Status::error("Truncated data in: " + path);

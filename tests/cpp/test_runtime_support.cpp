@@ -133,6 +133,18 @@ static void testNpy() {
     EXPECT(loadNpy(path("trunc.npy"), e).message().find("Truncated data in:") == 0, "truncated data message");
   }
   {
+    // a header that claims far more than the file holds is refused before anything of that size is allocated
+    std::string huge = all;
+    const size_t at = huge.find("'shape': (4,)");
+    huge.replace(at, 13, "'shape': (99999999994, 6)");
+    std::ofstream(path("huge.npy"), std::ios::binary) << huge;
+    EXPECT(loadNpy(path("huge.npy"), e).message().find("Truncated data in:") == 0, "a claimed shape beyond the file's size");
+    std::string wrap = all;
+    wrap.replace(wrap.find("'shape': (4,)"), 13, "'shape': (4294967296, 4294967296, 4294967296)");
+    std::ofstream(path("wrap.npy"), std::ios::binary) << wrap;
+    EXPECT(loadNpy(path("wrap.npy"), e).message().find("Truncated data in:") == 0, "a shape whose byte count wraps around 64 bits");
+  }
+  {
     std::string f8 = all;
     f8.replace(f8.find("<V2"), 3, "<f8");
     std::ofstream(path("f8.npy"), std::ios::binary) << f8;
