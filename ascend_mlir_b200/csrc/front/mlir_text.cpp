@@ -69,6 +69,7 @@ private:
   Module &m_;
   size_t pos_ = 0;
   int moduleDepth_ = 0;
+  int regionDepth_ = 0;  // linalg.generic bodies being parsed (a body that holds another generic, and so on)
 
   bool eof() const { return pos_ >= s_.size(); }
   char peek() const { return eof() ? '\0' : s_[pos_]; }

@@ -244,6 +244,14 @@ def test_a_string_that_never_ends_is_an_error_not_a_crash():
         assert r.returncode == 1 and "error: line" in r.stderr, (r.returncode, r.stderr)
 
 
+def test_generics_nested_without_end_are_an_error_not_a_stack_overflow():
+    opening = ('%r = linalg.generic {indexing_maps = [affine_map<(d0) -> (d0)>, affine_map<(d0) -> (d0)>], iterator_types = ["parallel"]} '
+               'ins(%s : tensor<4xf32>) outs(%d : tensor<4xf32>) {\n^bb0(%x: f32, %y: f32):\n')
+    text = "func.func @f(%s: tensor<4xf32>, %d: tensor<4xf32>) -> tensor<4xf32> {\n" + opening * 50000
+    r = opt("-", stdin=text)
+    assert r.returncode == 1 and "regions nested too deep" in r.stderr
+
+
 def test_kernel_kind_follows_the_units_a_lowering_stage_assigned():
     """--annotate-ascendc-kernel-kind on buffer-level functions whose ops carry ascendc.unit (what the reference's
     test/Conversion/annotate-ascendc-kernel-kind.mlir feeds the pass): Cube only = "cube", Vector only = "vec", both =
