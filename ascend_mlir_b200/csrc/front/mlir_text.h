@@ -1,7 +1,7 @@
 // Self-contained reader for the textual MLIR subset the fused-group front end consumes (MLIR itself is not
 // a dependency): module / func.func, affine_map aliases, tensor types with dynamic dims, arith.constant,
 // tensor.{dim,empty,extract_slice,concat,extract}, linalg.{generic,matmul,fill,index,yield}, the arith ops
-// fused bodies use, afir.{add,sub,mul,div,truediv,minimum,maximum,relu,leaky_relu,neg,clip_by_value,concat,sum} (the other
+// fused bodies use, afir.{add,sub,mul,div,truediv,minimum,maximum,relu,leaky_relu,neg,abs,clip_by_value,concat,sum} (the other
 // reductions parse and take part in shape inference only), return.  This is the input language of the reference's examples
 // (examples/*/step0_input.mlir) and of its AFIR elementwise ops (include/Dialect/AFIR/Ops/Basic/math.td:60-121).
 // Anything outside the subset is a parse error naming the op: nothing is skipped silently.

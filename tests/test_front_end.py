@@ -396,9 +396,13 @@ func.func @test_clip_by_value(%arg0: tensor<4x1x1xf32>, %arg1: tensor<1x20x1xf32
         r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-"], capture_output=True, text=True, input=neg)
         assert r.returncode == 0, r.stderr
         assert body_of(json.loads(r.stdout)) == want
+    # afir.abs: max(x, x * -1)
+    r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-"], capture_output=True, text=True,
+                       input="func.func @a(%x: tensor<?x8xf16>) -> tensor<?x8xf16> {\n  %0 = afir.abs %x : tensor<?x8xf16> -> tensor<?x8xf16>\n  return %0 : tensor<?x8xf16>\n}\n")
+    assert r.returncode == 0 and body_of(json.loads(r.stdout)) == [("mulf", "v0", -1.0), ("maximumf", "v0", "%0")], r.stderr
     # what stays outside: a slope the max form does not express, an op of the family with no body op, wrong arity
     for bad, needle in [(text.replace("0.01 : f32", "1.5 : f32"), "negative_slop outside [0, 1]"),
-                        (text.replace("afir.relu %x :", "afir.abs %x :"), "outside the supported elementwise set"),
+                        (text.replace("afir.relu %x :", "afir.exp %x :"), "outside the supported elementwise set"),
                         (text.replace("{negative_slop = 0.01 : f32} ", ""), "needs its negative_slop attribute"),
                         (text.replace("afir.maximum %1, %y :", "afir.maximum %1 :"), "takes 2 operands")]:
         r = subprocess.run([str(BIN / "afir-translate"), "-mlir-to-cuda", "-", "--function", "act"], capture_output=True, text=True, input=bad)
